@@ -1,0 +1,182 @@
+/*
+ * pmoe.h -- C ABI of libpmoe: the Qwen3-Next quantised mixture-of-experts FFN block
+ * for NVIDIA B200 (sm_100a).
+ *
+ * The entry points are what paramecia-model's FFI for this path binds.  Each one names
+ * the reference interface it stands in for (path inside nicksenger/paramecia : lines).
+ * Plain pointers and sizes only.  Unless stated otherwise every data pointer is a
+ * DEVICE pointer on the layer's device and `stream` is a cudaStream_t passed as void*
+ * (NULL = the default stream).  Calls are asynchronous on that stream.
+ *
+ * Every function returns 0 on success or a negative pmoe_status; the message of the
+ * last failure on the calling thread is available from pmoe_last_error().  Nothing
+ * here aborts, traps or falls back to the CPU.
+ *
+ * A layer handle serves one call at a time (the reference serialises forwards behind
+ * Arc<tokio::Mutex<ModelWeights>>, paramecia-llm/src/backend/local.rs:60,741) but may
+ * be used from any host thread.
+ */
+#ifndef PMOE_H
+#define PMOE_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define PMOE_VERSION 1
+
+/* GGML tensor-type ids, the numbering of candle's GgmlDType / GGUF files. */
+typedef enum {
+    PMOE_F32 = 0,
+    PMOE_F16 = 1,
+    PMOE_Q8_0 = 8,
+    PMOE_Q4_K = 12,
+    PMOE_Q6_K = 14,
+    PMOE_BF16 = 30
+} pmoe_dtype;
+
+typedef enum {
+    PMOE_OK = 0,
+    PMOE_ERR_INVALID_ARG = -1,
+    PMOE_ERR_UNSUPPORTED_DTYPE = -2,
+    PMOE_ERR_UNSUPPORTED_SHAPE = -3,
+    PMOE_ERR_CUDA = -4,
+    PMOE_ERR_TOO_MANY_TOKENS = -5,
+    /* block-scale multipliers are installed (EGGROLL/QZO training): the fast paths are
+       bypassed in the reference too (qwen3_next.rs:1977,1989); the caller falls back */
+    PMOE_ERR_TRAINING_MODE = -6,
+    PMOE_ERR_TIMEOUT = -7,   /* a bounded device-side wait ran out */
+    PMOE_ERR_BAD_INDEX = -8, /* a device-side range check failed */
+    PMOE_ERR_NO_DEVICE = -9
+} pmoe_status;
+
+typedef struct pmoe_layer pmoe_layer; /* opaque */
+
+/*
+ * One MoE block.  Mirrors what MoeBlock::new / MoeExperts::new / SharedExpert::new read
+ * from a GGUF file (qwen3_next.rs:1864-1895, 1256-1258, 1749-1774):
+ *   blk.N.ffn_gate_inp.weight             router_w       [E, H]
+ *   blk.N.ffn_{gate,up}_exps.weight       gate/up_exps   [E_local, F, H]
+ *   blk.N.ffn_down_exps.weight            down_exps      [E_local, H, F]
+ *   blk.N.ffn_{gate,up,down}_shexp.weight sh_gate/up/down
+ *   blk.N.ffn_gate_inp_shexp[.weight]     sh_gate_inp    [H] (dequantised to f32 at load)
+ * Expert tensors are raw GGUF blocks, row-major, expert e one contiguous slice
+ * (QTensor::data(), slice_first_dim; qwen3_next.rs:1052,1548).
+ */
+typedef struct {
+    uint32_t struct_size;  /* sizeof(pmoe_layer_desc) */
+    int32_t device;        /* CUDA device ordinal */
+    int32_t H, F, E, k;    /* hidden, expert intermediate, experts (global), experts per token */
+    int32_t max_tokens;    /* workspace is sized for this many tokens per call */
+
+    /* Routed experts held by this handle: global ids [expert_base, expert_base+E_local).
+       E_local == 0 means all E.  Indices outside the range are skipped, the way the
+       reference skips indices >= num_experts (qwen3_next.rs:2045); expert parallelism
+       gives every rank one slice. */
+    int32_t expert_base, E_local;
+
+    int32_t gate_dtype, up_dtype, down_dtype;
+    const void *gate_exps, *up_exps, *down_exps;
+
+    int32_t has_shared;
+    int32_t sh_gate_dtype, sh_up_dtype, sh_down_dtype;
+    const void *sh_gate, *sh_up, *sh_down;
+    const float *sh_gate_inp;
+
+    int32_t router_dtype;     /* PMOE_F32 */
+    const void *router_w;
+    const float *router_bias; /* [E] added to the logits, or NULL (not in the reference;
+                                 used to skew synthetic routing) */
+
+    /* 0: the pointers above are host memory, copied to the device at create.
+       1: device memory, copied into storage the handle owns.
+       2: device memory, adopted in place (no copy); it must outlive the handle and be
+          16-byte aligned.  This is how a candle QTensor already on the GPU is used. */
+    int32_t weights_location;
+
+    /* non-zero when custom block multipliers are installed (MoeExperts::set_block_multipliers,
+       qwen3_next.rs:1705-1720): every forward then returns PMOE_ERR_TRAINING_MODE */
+    int32_t training_mode;
+} pmoe_layer_desc;
+
+/* MoeBlock::new (qwen3_next.rs:1864-1895) */
+int pmoe_layer_create(const pmoe_layer_desc *desc, pmoe_layer **out);
+/* Drop for MoeBlock */
+int pmoe_layer_destroy(pmoe_layer *layer);
+
+/*
+ * MoeBlock::forward_with_stats (qwen3_next.rs:1903-1940).
+ *   x       [n, H]  x_dtype in {PMOE_F32, PMOE_BF16}
+ *   out     [n, H]  out_dtype in {PMOE_F32, PMOE_BF16}
+ *   logits_out [n, E] f32, the UNCLAMPED router logits (qwen3_next.rs:1939), or NULL
+ *   idx_out    [n, k] u32 top-k expert ids, descending probability, or NULL
+ *   w_out      [n, k] f32 renormalised routing weights, or NULL
+ */
+int pmoe_forward(pmoe_layer *layer, const void *x, int x_dtype, int n, void *out, int out_dtype,
+                 float *logits_out, uint32_t *idx_out, float *w_out, void *stream);
+
+/*
+ * The same call with HOST buffers: copies x to the device, runs the block, copies the
+ * results back and synchronises the stream.  This is the shape of the reference's own
+ * offload paths (Tensor::to_device around the expert computation, ops.rs:188-198,291-293).
+ */
+int pmoe_forward_host(pmoe_layer *layer, const void *x_host, int x_dtype, int n, void *out_host,
+                      int out_dtype, float *logits_host, uint32_t *idx_host, float *w_host,
+                      void *stream);
+
+/*
+ * Router only: gate.forward, clamp, softmax, ops::topk_moe_routing
+ * (qwen3_next.rs:1916-1925, ops.rs:28-59).  Any output may be NULL.
+ */
+int pmoe_route(pmoe_layer *layer, const void *x, int x_dtype, int n, float *logits_out,
+               uint32_t *idx_out, float *w_out, void *stream);
+
+/*
+ * MoeExperts::forward_batched (qwen3_next.rs:1347-1394): routed experts only, with the
+ * caller's routing.  idx [n, top_k] u32 (global expert ids), w [n, top_k] f32.
+ */
+int pmoe_experts_forward(pmoe_layer *layer, const void *x, int x_dtype, const uint32_t *idx,
+                         const float *w, int n, int top_k, void *out, int out_dtype, void *stream);
+
+/* SharedExpert::forward (qwen3_next.rs:1776-1823), sigmoid gate included. */
+int pmoe_shared_forward(pmoe_layer *layer, const void *x, int x_dtype, int n, void *out,
+                        int out_dtype, void *stream);
+
+/*
+ * QMatMul::forward on a quantised tensor (models/with_tracing.rs:324-335):
+ * y[m, rows] = x[m, cols] * W[rows, cols]^T, activations quantised to the weight type's
+ * dot type as the reference CPU path does.  x, y f32.  m <= 64 per call.
+ */
+int pmoe_qmatmul(int device, int dtype, const void *w, size_t rows, size_t cols, const float *x,
+                 size_t m, float *y, void *stream);
+
+/* QTensor::dequantize: blocks -> f32 (the "dequantised weights bit-exact" check). */
+int pmoe_dequantize(int device, int dtype, const void *blocks, size_t n_elems, float *out,
+                    void *stream);
+
+/* RmsNorm::forward (quantized_nn.rs:172-190) fused with the residual add of
+ * LayerWeights::forward_with_stats (qwen3_next.rs:4273-4286):
+ *   resid_out = resid_in + delta (delta may be NULL), y = rms_norm(resid_out) * weight.
+ * f32 throughout; weight NULL = all ones. */
+int pmoe_add_rms_norm(int device, const float *resid_in, const float *delta, const float *weight,
+                      int n, int H, float eps, float *resid_out, float *y, void *stream);
+
+/* Synchronises the stream and reports the device-side status word of the layer
+ * (PMOE_OK, PMOE_ERR_TIMEOUT, PMOE_ERR_BAD_INDEX), clearing it. */
+int pmoe_layer_status(pmoe_layer *layer, void *stream);
+
+/* number of kernels of this library launched by this process so far */
+uint64_t pmoe_launch_count(void);
+
+size_t pmoe_block_size(int dtype); /* weights per block */
+size_t pmoe_type_size(int dtype);  /* bytes per block */
+const char *pmoe_last_error(void);
+int pmoe_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,449 @@
+// C ABI of libpmoe (include/pmoe.h): layer handles, argument checks, workspace layout and the
+// kernel sequence of one MoE block.  Host code only; every kernel lives in the other .cu files.
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <string>
+#include <vector>
+
+#include "pmoe_common.cuh"
+
+namespace pmoe {
+
+static std::atomic<uint64_t> g_launches{0};
+void count_launch(int n) { g_launches.fetch_add((uint64_t)n, std::memory_order_relaxed); }
+
+static thread_local std::string g_last_error;
+
+static int fail(int code, const char *fmt, ...)
+{
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    g_last_error = buf;
+    return code;
+}
+
+static int fail_cuda(cudaError_t e, const char *what)
+{
+    return fail(PMOE_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+}
+
+#define CU(call)                                                  \
+    do {                                                          \
+        cudaError_t _e = (call);                                  \
+        if (_e != cudaSuccess) return fail_cuda(_e, #call);       \
+    } while (0)
+
+// Makes `device` current for the calling thread and restores the previous one on exit.
+struct DeviceGuard {
+    int prev = -1;
+    bool ok = false;
+    explicit DeviceGuard(int device)
+    {
+        if (cudaGetDevice(&prev) != cudaSuccess) prev = -1;
+        ok = cudaSetDevice(device) == cudaSuccess;
+    }
+    ~DeviceGuard()
+    {
+        if (prev >= 0) cudaSetDevice(prev);
+    }
+};
+
+static bool dtype_known(int dt)
+{
+    return dt == PMOE_F32 || dt == PMOE_F16 || dt == PMOE_BF16 || dt == PMOE_Q8_0 || dt == PMOE_Q4_K || dt == PMOE_Q6_K;
+}
+
+}  // namespace pmoe
+
+using namespace pmoe;
+
+struct pmoe_layer {
+    pmoe_layer_desc desc;
+    LayerDev dev;
+    Workspace ws;
+    int device;
+    std::vector<void *> owned;  // device allocations freed at destroy
+    // device staging for the host-buffer entry point
+    void *st_x = nullptr, *st_out = nullptr;
+    float *st_logits = nullptr;
+    uint32_t *st_idx = nullptr;
+    float *st_w = nullptr;
+};
+
+namespace {
+
+size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+// Bump allocator over one device block.  First pass (base == nullptr) only measures.
+struct Carver {
+    uint8_t *base;
+    size_t off = 0;
+    template <typename T> T *take(size_t count)
+    {
+        off = align_up(off, 256);
+        T *p = base ? reinterpret_cast<T *>(base + off) : nullptr;
+        off += count * sizeof(T);
+        return p;
+    }
+};
+
+void carve_workspace(pmoe_layer *L, Carver &c)
+{
+    const pmoe_layer_desc &d = L->desc;
+    const size_t n = (size_t)d.max_tokens, H = d.H, F = d.F, E = d.E, k = d.k;
+    const size_t El = L->dev.E_local;
+    const size_t rows = n * (k + 1);
+    Workspace &w = L->ws;
+    w.max_tokens = d.max_tokens;
+    w.status = c.take<DevStatus>(1);
+    w.logits = c.take<float>(n * E);
+    w.topk_idx = c.take<uint32_t>(n * k);
+    w.topk_w = c.take<float>(n * k);
+    w.x_q8k.qs = c.take<int8_t>(n * H);
+    w.x_q8k.d = c.take<float>(n * (H / QK_K));
+    w.x_q8k.bsums = c.take<int16_t>(n * (H / 16));
+    w.x_q80.qs = c.take<int8_t>(n * H);
+    w.x_q80.d = c.take<float>(n * (H / QK8_0));
+    w.x_q80.bsums = nullptr;
+    w.sh_sigmoid = c.take<float>(n);
+    w.groups.count = c.take<int>(El);
+    w.groups.offset = c.take<int>(El + 1);
+    w.groups.pos = c.take<int>(n * k);
+    w.groups.pairs = c.take<int>(n * k);
+    w.groups.active = c.take<int>(El);
+    w.groups.n_active = c.take<int>(1);
+    w.act = c.take<float>(rows * F);
+    w.act_q8k.qs = c.take<int8_t>(rows * F);
+    w.act_q8k.d = c.take<float>(rows * (F / QK_K));
+    w.act_q8k.bsums = c.take<int16_t>(rows * (F / 16));
+    w.act_q80.qs = c.take<int8_t>(rows * F);
+    w.act_q80.d = c.take<float>(rows * (F / QK8_0));
+    w.act_q80.bsums = nullptr;
+    w.partial = c.take<float>(rows * H);
+    L->st_x = c.take<float>(n * H);
+    L->st_out = c.take<float>(n * H);
+    L->st_logits = c.take<float>(n * E);
+    L->st_idx = c.take<uint32_t>(n * k);
+    L->st_w = c.take<float>(n * k);
+}
+
+int place_tensor(pmoe_layer *L, const void *src, size_t bytes, int location, const uint8_t **dst, const char *name)
+{
+    if (!src) return fail(PMOE_ERR_INVALID_ARG, "%s is NULL", name);
+    if (location == 2) {
+        if ((uintptr_t)src & 15) return fail(PMOE_ERR_INVALID_ARG, "%s: adopted pointers must be 16-byte aligned", name);
+        *dst = (const uint8_t *)src;
+        return PMOE_OK;
+    }
+    void *p = nullptr;
+    cudaError_t e = cudaMalloc(&p, bytes ? bytes : 16);
+    if (e != cudaSuccess) return fail_cuda(e, name);
+    L->owned.push_back(p);
+    e = cudaMemcpy(p, src, bytes, location == 0 ? cudaMemcpyHostToDevice : cudaMemcpyDeviceToDevice);
+    if (e != cudaSuccess) return fail_cuda(e, name);
+    *dst = (const uint8_t *)p;
+    return PMOE_OK;
+}
+
+int check_call(pmoe_layer *L, const void *x, int x_dtype, int n, const void *out, int out_dtype)
+{
+    if (!L) return fail(PMOE_ERR_INVALID_ARG, "layer is NULL");
+    if (L->desc.training_mode)
+        return fail(PMOE_ERR_TRAINING_MODE, "block-scale multipliers are installed; use the reference path");
+    if (n < 0) return fail(PMOE_ERR_INVALID_ARG, "n must be >= 0");
+    if (n > L->desc.max_tokens)
+        return fail(PMOE_ERR_TOO_MANY_TOKENS, "n = %d exceeds max_tokens = %d", n, L->desc.max_tokens);
+    if (n > 0 && (!x || !out)) return fail(PMOE_ERR_INVALID_ARG, "x / out is NULL");
+    if (x_dtype != PMOE_F32 && x_dtype != PMOE_BF16)
+        return fail(PMOE_ERR_UNSUPPORTED_DTYPE, "activations must be F32 or BF16 (got %d)", x_dtype);
+    if (out_dtype != PMOE_F32 && out_dtype != PMOE_BF16)
+        return fail(PMOE_ERR_UNSUPPORTED_DTYPE, "outputs must be F32 or BF16 (got %d)", out_dtype);
+    return PMOE_OK;
+}
+
+struct Needs {
+    bool q8k, q80;
+};
+
+Needs input_needs(const LayerDev &d, bool routed, bool shared)
+{
+    Needs nd{false, false};
+    if (routed) (is_kquant(d.gate_dtype) ? nd.q8k : nd.q80) = true;
+    if (shared) (is_kquant(d.sh_gate_dtype) ? nd.q8k : nd.q80) = true;
+    return nd;
+}
+
+// experts (+ shared) given routing already in device memory
+int run_experts(pmoe_layer *L, const void *x, int x_dtype, const uint32_t *idx, const float *w, int n, int top_k,
+                bool routed, bool shared, bool prep_done, void *out, int out_dtype, cudaStream_t s)
+{
+    const LayerDev &d = L->dev;
+    if (!prep_done) {
+        Needs nd = input_needs(d, routed, shared);
+        CU(launch_prep(d, L->ws, x, x_dtype, n, nd.q8k, nd.q80, shared, s));
+    }
+    if (routed) CU(launch_group(d, L->ws, idx, n, top_k, s));
+    CU(launch_gate_up(d, L->ws, n, top_k, routed, shared, s));
+    CU(launch_act_quant(d, L->ws, idx, n, top_k, routed, shared, s));
+    CU(launch_down(d, L->ws, w, n, top_k, routed, shared, s));
+    CU(launch_combine(d, L->ws, idx, n, top_k, routed, shared, out, out_dtype, s));
+    return PMOE_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int pmoe_version(void) { return PMOE_VERSION; }
+const char *pmoe_last_error(void) { return g_last_error.c_str(); }
+uint64_t pmoe_launch_count(void) { return g_launches.load(); }
+size_t pmoe_block_size(int dtype) { return (size_t)block_elems(dtype); }
+size_t pmoe_type_size(int dtype) { return (size_t)block_bytes(dtype); }
+
+int pmoe_layer_create(const pmoe_layer_desc *desc, pmoe_layer **out)
+{
+    if (!desc || !out) return fail(PMOE_ERR_INVALID_ARG, "desc / out is NULL");
+    *out = nullptr;
+    if (desc->struct_size != sizeof(pmoe_layer_desc))
+        return fail(PMOE_ERR_INVALID_ARG, "struct_size %u does not match this library (%zu)", desc->struct_size,
+                    sizeof(pmoe_layer_desc));
+    const pmoe_layer_desc &d = *desc;
+    if (d.H <= 0 || d.F <= 0 || d.E <= 0 || d.k <= 0 || d.max_tokens <= 0)
+        return fail(PMOE_ERR_INVALID_ARG, "H, F, E, k and max_tokens must be positive");
+    if (d.k > 32 || d.k > d.E) return fail(PMOE_ERR_UNSUPPORTED_SHAPE, "k must be <= min(32, E)");
+    if (d.E > 1024) return fail(PMOE_ERR_UNSUPPORTED_SHAPE, "E must be <= 1024");
+    if (d.H % 128) return fail(PMOE_ERR_UNSUPPORTED_SHAPE, "H must be a multiple of 128");
+    int E_local = d.E_local > 0 ? d.E_local : d.E;
+    if (d.expert_base < 0 || d.expert_base + E_local > d.E)
+        return fail(PMOE_ERR_INVALID_ARG, "expert slice [%d, %d) is outside [0, %d)", d.expert_base,
+                    d.expert_base + E_local, d.E);
+    if (d.weights_location < 0 || d.weights_location > 2)
+        return fail(PMOE_ERR_INVALID_ARG, "weights_location must be 0, 1 or 2");
+    const int dts[3] = {d.gate_dtype, d.up_dtype, d.down_dtype};
+    for (int dt : dts)
+        if (!dtype_known(dt)) return fail(PMOE_ERR_UNSUPPORTED_DTYPE, "unknown GGML dtype id %d", dt);
+    if (d.gate_dtype != d.up_dtype)
+        return fail(PMOE_ERR_UNSUPPORTED_DTYPE, "gate and up experts must share one dtype (got %d and %d)", d.gate_dtype,
+                    d.up_dtype);
+    if (d.router_dtype != PMOE_F32) return fail(PMOE_ERR_UNSUPPORTED_DTYPE, "router weights must be F32");
+    const char *why = "";
+    if (!gemv_supported(d.gate_dtype, d.H, d.F, &why) || !gemv_supported(d.down_dtype, d.F, d.H, &why))
+        return fail(dtype_known(d.gate_dtype) && (block_elems(d.gate_dtype) > 1) && (block_elems(d.down_dtype) > 1)
+                        ? PMOE_ERR_UNSUPPORTED_SHAPE
+                        : PMOE_ERR_UNSUPPORTED_DTYPE,
+                    "experts: %s", why);
+    if (d.F > 512) return fail(PMOE_ERR_UNSUPPORTED_SHAPE, "F must be <= 512");
+    if (d.has_shared) {
+        if (d.sh_gate_dtype != d.sh_up_dtype)
+            return fail(PMOE_ERR_UNSUPPORTED_DTYPE, "shared gate and up must share one dtype");
+        if (!gemv_supported(d.sh_gate_dtype, d.H, d.F, &why) || !gemv_supported(d.sh_down_dtype, d.F, d.H, &why))
+            return fail(PMOE_ERR_UNSUPPORTED_DTYPE, "shared expert: %s", why);
+    }
+    int ndev = 0;
+    if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev == 0) {
+        cudaGetLastError();
+        return fail(PMOE_ERR_NO_DEVICE, "no CUDA device is available; libpmoe has no CPU path");
+    }
+    if (d.device < 0 || d.device >= ndev) return fail(PMOE_ERR_INVALID_ARG, "device %d of %d", d.device, ndev);
+    DeviceGuard guard(d.device);
+    if (!guard.ok) return fail(PMOE_ERR_CUDA, "cannot select device %d", d.device);
+
+    pmoe_layer *L = new pmoe_layer();
+    L->desc = d;
+    L->desc.E_local = E_local;
+    L->device = d.device;
+    LayerDev &v = L->dev;
+    v.H = d.H; v.F = d.F; v.E = d.E; v.k = d.k;
+    v.expert_base = d.expert_base; v.E_local = E_local;
+    v.gate_dtype = d.gate_dtype; v.up_dtype = d.up_dtype; v.down_dtype = d.down_dtype;
+    v.has_shared = d.has_shared ? 1 : 0;
+    v.sh_gate_dtype = d.sh_gate_dtype; v.sh_up_dtype = d.sh_up_dtype; v.sh_down_dtype = d.sh_down_dtype;
+    int rc = PMOE_OK;
+    const int loc = d.weights_location;
+    const size_t El = (size_t)E_local;
+    const uint8_t *tmp = nullptr;
+    if (!rc) rc = place_tensor(L, d.gate_exps, El * d.F * row_bytes(d.gate_dtype, d.H), loc, &v.gate_exps, "gate_exps");
+    if (!rc) rc = place_tensor(L, d.up_exps, El * d.F * row_bytes(d.up_dtype, d.H), loc, &v.up_exps, "up_exps");
+    if (!rc) rc = place_tensor(L, d.down_exps, El * d.H * row_bytes(d.down_dtype, d.F), loc, &v.down_exps, "down_exps");
+    if (!rc && d.has_shared) {
+        rc = place_tensor(L, d.sh_gate, (size_t)d.F * row_bytes(d.sh_gate_dtype, d.H), loc, &v.sh_gate, "sh_gate");
+        if (!rc) rc = place_tensor(L, d.sh_up, (size_t)d.F * row_bytes(d.sh_up_dtype, d.H), loc, &v.sh_up, "sh_up");
+        if (!rc) rc = place_tensor(L, d.sh_down, (size_t)d.H * row_bytes(d.sh_down_dtype, d.F), loc, &v.sh_down, "sh_down");
+        if (!rc) rc = place_tensor(L, d.sh_gate_inp, (size_t)d.H * 4, loc, &tmp, "sh_gate_inp");
+        v.sh_gate_inp = (const float *)tmp;
+    }
+    if (!rc) rc = place_tensor(L, d.router_w, (size_t)d.E * d.H * 4, loc, &tmp, "router_w");
+    v.router_w = (const float *)tmp;
+    v.router_bias = nullptr;
+    if (!rc && d.router_bias) {
+        rc = place_tensor(L, d.router_bias, (size_t)d.E * 4, loc, &tmp, "router_bias");
+        v.router_bias = (const float *)tmp;
+    }
+    if (!rc) {
+        Carver measure{nullptr};
+        carve_workspace(L, measure);
+        void *block = nullptr;
+        cudaError_t e = cudaMalloc(&block, measure.off + 256);
+        if (e != cudaSuccess) {
+            rc = fail_cuda(e, "workspace");
+        } else {
+            L->owned.push_back(block);
+            Carver real{(uint8_t *)block};
+            carve_workspace(L, real);
+            e = cudaMemset(L->ws.status, 0, sizeof(DevStatus));
+            if (e != cudaSuccess) rc = fail_cuda(e, "workspace");
+        }
+    }
+    if (rc) {
+        for (void *p : L->owned) cudaFree(p);
+        delete L;
+        return rc;
+    }
+    *out = L;
+    return PMOE_OK;
+}
+
+int pmoe_layer_destroy(pmoe_layer *L)
+{
+    if (!L) return PMOE_OK;
+    DeviceGuard guard(L->device);
+    cudaDeviceSynchronize();
+    for (void *p : L->owned) cudaFree(p);
+    delete L;
+    return PMOE_OK;
+}
+
+int pmoe_route(pmoe_layer *L, const void *x, int x_dtype, int n, float *logits_out, uint32_t *idx_out, float *w_out,
+               void *stream)
+{
+    float dummy;
+    int rc = check_call(L, x, x_dtype, n, &dummy, PMOE_F32);
+    if (rc) return rc;
+    if (n == 0) return PMOE_OK;
+    DeviceGuard guard(L->device);
+    cudaStream_t s = (cudaStream_t)stream;
+    float *logits = logits_out ? logits_out : L->ws.logits;
+    CU(launch_router(L->dev, L->ws, x, x_dtype, n, logits, s));
+    if (idx_out || w_out) CU(launch_topk(L->dev, L->ws, logits, n, idx_out, w_out, s));
+    return PMOE_OK;
+}
+
+int pmoe_forward(pmoe_layer *L, const void *x, int x_dtype, int n, void *out, int out_dtype, float *logits_out,
+                 uint32_t *idx_out, float *w_out, void *stream)
+{
+    int rc = check_call(L, x, x_dtype, n, out, out_dtype);
+    if (rc) return rc;
+    if (n == 0) return PMOE_OK;
+    DeviceGuard guard(L->device);
+    cudaStream_t s = (cudaStream_t)stream;
+    const LayerDev &d = L->dev;
+    float *logits = logits_out ? logits_out : L->ws.logits;
+    uint32_t *idx = idx_out ? idx_out : L->ws.topk_idx;
+    float *w = w_out ? w_out : L->ws.topk_w;
+    Needs nd = input_needs(d, true, d.has_shared);
+    CU(launch_prep(d, L->ws, x, x_dtype, n, nd.q8k, nd.q80, d.has_shared, s));
+    CU(launch_router(d, L->ws, x, x_dtype, n, logits, s));
+    CU(launch_topk(d, L->ws, logits, n, idx, w, s));
+    return run_experts(L, x, x_dtype, idx, w, n, d.k, true, d.has_shared, true, out, out_dtype, s);
+}
+
+int pmoe_experts_forward(pmoe_layer *L, const void *x, int x_dtype, const uint32_t *idx, const float *w, int n,
+                         int top_k, void *out, int out_dtype, void *stream)
+{
+    int rc = check_call(L, x, x_dtype, n, out, out_dtype);
+    if (rc) return rc;
+    if (n == 0) return PMOE_OK;
+    if (!idx || !w) return fail(PMOE_ERR_INVALID_ARG, "idx / w is NULL");
+    if (top_k <= 0 || top_k > L->desc.k)
+        return fail(PMOE_ERR_INVALID_ARG, "top_k = %d must be in [1, %d]", top_k, L->desc.k);
+    DeviceGuard guard(L->device);
+    return run_experts(L, x, x_dtype, idx, w, n, top_k, true, false, false, out, out_dtype, (cudaStream_t)stream);
+}
+
+int pmoe_shared_forward(pmoe_layer *L, const void *x, int x_dtype, int n, void *out, int out_dtype, void *stream)
+{
+    int rc = check_call(L, x, x_dtype, n, out, out_dtype);
+    if (rc) return rc;
+    if (n == 0) return PMOE_OK;
+    if (!L->dev.has_shared) return fail(PMOE_ERR_INVALID_ARG, "the layer has no shared expert");
+    DeviceGuard guard(L->device);
+    return run_experts(L, x, x_dtype, nullptr, nullptr, n, L->desc.k, false, true, false, out, out_dtype,
+                       (cudaStream_t)stream);
+}
+
+int pmoe_forward_host(pmoe_layer *L, const void *x_host, int x_dtype, int n, void *out_host, int out_dtype,
+                      float *logits_host, uint32_t *idx_host, float *w_host, void *stream)
+{
+    int rc = check_call(L, x_host, x_dtype, n, out_host, out_dtype);
+    if (rc) return rc;
+    if (n == 0) return PMOE_OK;
+    DeviceGuard guard(L->device);
+    cudaStream_t s = (cudaStream_t)stream;
+    const pmoe_layer_desc &d = L->desc;
+    const size_t xin = (size_t)n * d.H * (x_dtype == PMOE_F32 ? 4 : 2);
+    const size_t xout = (size_t)n * d.H * (out_dtype == PMOE_F32 ? 4 : 2);
+    CU(cudaMemcpyAsync(L->st_x, x_host, xin, cudaMemcpyHostToDevice, s));
+    rc = pmoe_forward(L, L->st_x, x_dtype, n, L->st_out, out_dtype, logits_host ? L->st_logits : nullptr,
+                      idx_host ? L->st_idx : nullptr, w_host ? L->st_w : nullptr, stream);
+    if (rc) return rc;
+    CU(cudaMemcpyAsync(out_host, L->st_out, xout, cudaMemcpyDeviceToHost, s));
+    if (logits_host) CU(cudaMemcpyAsync(logits_host, L->st_logits, (size_t)n * d.E * 4, cudaMemcpyDeviceToHost, s));
+    if (idx_host) CU(cudaMemcpyAsync(idx_host, L->st_idx, (size_t)n * d.k * 4, cudaMemcpyDeviceToHost, s));
+    if (w_host) CU(cudaMemcpyAsync(w_host, L->st_w, (size_t)n * d.k * 4, cudaMemcpyDeviceToHost, s));
+    CU(cudaStreamSynchronize(s));
+    return PMOE_OK;
+}
+
+int pmoe_layer_status(pmoe_layer *L, void *stream)
+{
+    if (!L) return fail(PMOE_ERR_INVALID_ARG, "layer is NULL");
+    DeviceGuard guard(L->device);
+    cudaStream_t s = (cudaStream_t)stream;
+    DevStatus st{};
+    CU(cudaMemcpyAsync(&st, L->ws.status, sizeof st, cudaMemcpyDeviceToHost, s));
+    CU(cudaStreamSynchronize(s));
+    if (st.code) {
+        CU(cudaMemsetAsync(L->ws.status, 0, sizeof st, s));
+        CU(cudaStreamSynchronize(s));
+        return fail(st.code, "device status %d raised by kernel tag %d (detail %d)", st.code, st.where, st.detail);
+    }
+    return PMOE_OK;
+}
+
+int pmoe_dequantize(int device, int dtype, const void *blocks, size_t n_elems, float *out, void *stream)
+{
+    if (!dtype_known(dtype)) return fail(PMOE_ERR_UNSUPPORTED_DTYPE, "unknown GGML dtype id %d", dtype);
+    if (n_elems % (size_t)block_elems(dtype))
+        return fail(PMOE_ERR_INVALID_ARG, "n_elems must be a multiple of the block size %d", block_elems(dtype));
+    if (n_elems && (!blocks || !out)) return fail(PMOE_ERR_INVALID_ARG, "blocks / out is NULL");
+    if (n_elems > ((size_t)1 << 39)) return fail(PMOE_ERR_INVALID_ARG, "n_elems too large");
+    DeviceGuard guard(device);
+    if (!guard.ok) return fail(PMOE_ERR_NO_DEVICE, "cannot select device %d", device);
+    CU(launch_dequantize(dtype, blocks, n_elems, out, (cudaStream_t)stream));
+    return PMOE_OK;
+}
+
+int pmoe_add_rms_norm(int device, const float *resid_in, const float *delta, const float *weight, int n, int H,
+                      float eps, float *resid_out, float *y, void *stream)
+{
+    if (n < 0 || H <= 0 || H > 12288) return fail(PMOE_ERR_INVALID_ARG, "bad n / H");
+    if (n && (!resid_in || !y)) return fail(PMOE_ERR_INVALID_ARG, "resid_in / y is NULL");
+    DeviceGuard guard(device);
+    if (!guard.ok) return fail(PMOE_ERR_NO_DEVICE, "cannot select device %d", device);
+    CU(launch_add_rms_norm(resid_in, delta, weight, n, H, eps, resid_out, y, (cudaStream_t)stream));
+    return PMOE_OK;
+}
+
+int pmoe_qmatmul(int device, int dtype, const void *w, size_t rows, size_t cols, const float *x, size_t m, float *y,
+                 void *stream)
+{
+    (void)device; (void)dtype; (void)w; (void)rows; (void)cols; (void)x; (void)m; (void)y; (void)stream;
+    return fail(PMOE_ERR_UNSUPPORTED_SHAPE, "pmoe_qmatmul is not available in this build");
+}
+
+}  // extern "C"

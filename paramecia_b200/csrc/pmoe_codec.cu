@@ -1,0 +1,119 @@
+// Block codecs and the small f32 kernels around the MoE block.
+//
+// k_dequantize restates candle's GgmlType::to_float for BlockQ8_0 / BlockQ4K / BlockQ6K (the
+// QTensor::dequantize the reference calls, e.g. paramecia-model/src/qwen3_next.rs:1758-1762);
+// products are rounded one by one so the f32 bits equal the host codec's.
+// k_add_rms_norm is RmsNorm::forward (paramecia-model/src/quantized_nn.rs:172-190) fused with
+// the residual add of LayerWeights::forward_with_stats (qwen3_next.rs:4273-4286).
+#include "pmoe_common.cuh"
+
+namespace pmoe {
+
+__device__ inline void q4k_scale_min(int j, const uint8_t *q, int &sc, int &m)
+{
+    if (j < 4) {
+        sc = q[j] & 63;
+        m = q[j + 4] & 63;
+    } else {
+        sc = (q[j + 4] & 0xF) | ((q[j - 4] >> 6) << 4);
+        m = (q[j + 4] >> 4) | ((q[j] >> 6) << 4);
+    }
+}
+
+// one thread per output element; consecutive threads read one block's bytes and write
+// consecutive floats
+__global__ void __launch_bounds__(256) k_dequantize(int dtype, const uint8_t *__restrict__ blocks, size_t n,
+                                                    float *__restrict__ out)
+{
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    if (dtype == PMOE_Q8_0) {
+        const uint8_t *b = blocks + (i / QK8_0) * Q8_0_BYTES;
+        float d = half_bits_to_float((uint16_t)(b[0] | (b[1] << 8)));
+        out[i] = __fmul_rn((float)(int8_t)b[2 + i % QK8_0], d);
+    } else if (dtype == PMOE_Q4_K) {
+        const uint8_t *b = blocks + (i / QK_K) * Q4_K_BYTES;
+        int w = (int)(i % QK_K);
+        int sub = w / 32, l = w % 32, grp = w / 64;
+        float d = half_bits_to_float((uint16_t)(b[0] | (b[1] << 8)));
+        float dmin = half_bits_to_float((uint16_t)(b[2] | (b[3] << 8)));
+        int sc, m;
+        q4k_scale_min(sub, b + 4, sc, m);
+        uint8_t q = b[16 + 32 * grp + l];
+        int v = (sub & 1) ? (q >> 4) : (q & 0xF);
+        out[i] = __fsub_rn(__fmul_rn(__fmul_rn(d, (float)sc), (float)v), __fmul_rn(dmin, (float)m));
+    } else if (dtype == PMOE_Q6_K) {
+        const uint8_t *b = blocks + (i / QK_K) * Q6_K_BYTES;
+        int w = (int)(i % QK_K);
+        int half = w / 128, r = w % 128, quad = r / 32, l = r % 32;
+        const uint8_t *ql = b + 64 * half, *qh = b + 128 + 32 * half;
+        const int8_t *sc = reinterpret_cast<const int8_t *>(b + 192 + 8 * half);
+        float d = half_bits_to_float((uint16_t)(b[208] | (b[209] << 8)));
+        uint8_t lo = ql[l + 32 * (quad & 1)];
+        int nib = quad >= 2 ? (lo >> 4) : (lo & 0xF);
+        int q = (nib | (((qh[l] >> (2 * quad)) & 3) << 4)) - 32;
+        out[i] = __fmul_rn(__fmul_rn(d, (float)sc[l / 16 + 2 * quad]), (float)q);
+    } else if (dtype == PMOE_F16) {
+        out[i] = half_bits_to_float(reinterpret_cast<const uint16_t *>(blocks)[i]);
+    } else if (dtype == PMOE_BF16) {
+        out[i] = __uint_as_float((uint32_t)reinterpret_cast<const uint16_t *>(blocks)[i] << 16);
+    } else {
+        out[i] = reinterpret_cast<const float *>(blocks)[i];
+    }
+}
+
+cudaError_t launch_dequantize(int dtype, const void *blocks, size_t n_elems, float *out, cudaStream_t s)
+{
+    if (!n_elems) return cudaSuccess;
+    size_t grid = (n_elems + 255) / 256;
+    k_dequantize<<<(unsigned)grid, 256, 0, s>>>(dtype, (const uint8_t *)blocks, n_elems, out);
+    count_launch();
+    return cudaGetLastError();
+}
+
+// resid_out = resid_in + delta; y = resid_out / sqrt(mean(resid_out^2) + eps) * weight
+__global__ void __launch_bounds__(256) k_add_rms_norm(const float *__restrict__ resid_in,
+                                                      const float *__restrict__ delta,
+                                                      const float *__restrict__ weight, int H, float eps,
+                                                      float *__restrict__ resid_out, float *__restrict__ y)
+{
+    extern __shared__ float row[];
+    __shared__ float red[8];
+    __shared__ float inv_m;
+    const int t = blockIdx.x;
+    float ss = 0.f;
+    for (int h = threadIdx.x; h < H; h += blockDim.x) {
+        float v = resid_in[(size_t)t * H + h];
+        if (delta) v = __fadd_rn(v, delta[(size_t)t * H + h]);
+        row[h] = v;
+        ss += v * v;
+    }
+#pragma unroll
+    for (int s = 16; s >= 1; s >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, s);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float tot = 0.f;
+        for (int w = 0; w < (int)(blockDim.x >> 5); w++) tot += red[w];
+        inv_m = sqrtf(tot / (float)H + eps);
+    }
+    __syncthreads();
+    const float m = inv_m;
+    for (int h = threadIdx.x; h < H; h += blockDim.x) {
+        float v = row[h];
+        if (resid_out) resid_out[(size_t)t * H + h] = v;
+        float o = __fdiv_rn(v, m);
+        y[(size_t)t * H + h] = weight ? __fmul_rn(o, weight[h]) : o;
+    }
+}
+
+cudaError_t launch_add_rms_norm(const float *resid_in, const float *delta, const float *weight, int n, int H,
+                                float eps, float *resid_out, float *y, cudaStream_t s)
+{
+    if (n <= 0) return cudaSuccess;
+    k_add_rms_norm<<<n, 256, (size_t)H * sizeof(float), s>>>(resid_in, delta, weight, H, eps, resid_out, y);
+    count_launch();
+    return cudaGetLastError();
+}
+
+}  // namespace pmoe

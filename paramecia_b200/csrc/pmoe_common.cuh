@@ -1,0 +1,217 @@
+// Shared device/host definitions of libpmoe: GGUF block layouts, small PTX wrappers,
+// the workspace layout and the internal launch interface between the .cu files.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/pmoe.h"
+
+#define QK_K 256
+#define QK8_0 32
+
+namespace pmoe {
+
+// ---------------------------------------------------------------- GGUF block layouts
+// Q8_0:  34 B = f16 d, int8 qs[32]
+// Q4_K: 144 B = f16 d, f16 dmin, u8 scales[12] (8x 6-bit scale + 8x 6-bit min), u8 qs[128]
+// Q6_K: 210 B = u8 ql[128], u8 qh[64], i8 scales[16], f16 d
+constexpr int Q8_0_BYTES = 34;
+constexpr int Q4_K_BYTES = 144;
+constexpr int Q6_K_BYTES = 210;
+
+__host__ __device__ inline int block_elems(int dtype)
+{
+    switch (dtype) {
+    case PMOE_F32: case PMOE_F16: case PMOE_BF16: return 1;
+    case PMOE_Q8_0: return QK8_0;
+    case PMOE_Q4_K: case PMOE_Q6_K: return QK_K;
+    default: return 0;
+    }
+}
+
+__host__ __device__ inline int block_bytes(int dtype)
+{
+    switch (dtype) {
+    case PMOE_F32: return 4;
+    case PMOE_F16: case PMOE_BF16: return 2;
+    case PMOE_Q8_0: return Q8_0_BYTES;
+    case PMOE_Q4_K: return Q4_K_BYTES;
+    case PMOE_Q6_K: return Q6_K_BYTES;
+    default: return 0;
+    }
+}
+
+__host__ __device__ inline size_t row_bytes(int dtype, size_t cols)
+{
+    int be = block_elems(dtype);
+    return be ? cols / be * (size_t)block_bytes(dtype) : 0;
+}
+
+// Activation blocks follow the weight type's dot type on the reference CPU path:
+// Q4_K, Q6_K -> Q8_K (256 values, f32 scale, 16 sums of 16); Q8_0 -> Q8_0 (32 values, f16 scale).
+__host__ __device__ inline bool is_kquant(int dtype) { return dtype == PMOE_Q4_K || dtype == PMOE_Q6_K; }
+
+// ---------------------------------------------------------------- status word
+// Kernels never trap: a failed range check or an expired wait records a code here.
+struct DevStatus {
+    int code;   // 0, PMOE_ERR_TIMEOUT or PMOE_ERR_BAD_INDEX
+    int where;  // kernel tag
+    int detail;
+};
+
+__device__ inline void set_status(DevStatus *st, int code, int where, int detail)
+{
+    if (st && atomicCAS(&st->code, 0, code) == 0) {
+        st->where = where;
+        st->detail = detail;
+    }
+}
+
+// ---------------------------------------------------------------- PTX helpers
+__device__ inline uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ inline void mbar_init(uint64_t *bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+
+__device__ inline void mbar_expect_tx(uint64_t *bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+                 : "memory");
+}
+
+__device__ inline void fence_mbar_init()
+{
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+
+__device__ inline void fence_proxy_async()
+{
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+// One bounded wait on an mbarrier phase.  Returns false when the limit ran out.
+__device__ inline bool mbar_wait(uint64_t *bar, uint32_t parity, uint32_t max_polls = (1u << 22))
+{
+    uint32_t addr = smem_u32(bar);
+    for (uint32_t i = 0; i < max_polls; i++) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+
+// 1-D bulk copy global -> this CTA's shared memory through the TMA unit (no multicast).
+// Both addresses 16-byte aligned, size a multiple of 16.
+__device__ inline void bulk_g2s(void *smem_dst, const void *gmem_src, uint32_t bytes, uint64_t *bar)
+{
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+            smem_u32(smem_dst)),
+        "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar))
+        : "memory");
+}
+
+// programmatic dependent launch
+__device__ inline void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ inline void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// 32-bit load from a 2-byte aligned shared-memory address
+__device__ inline uint32_t lds_u32_a2(const uint8_t *p)
+{
+    const uint16_t *h = reinterpret_cast<const uint16_t *>(p);
+    return (uint32_t)h[0] | ((uint32_t)h[1] << 16);
+}
+
+__device__ inline float half_bits_to_float(uint16_t h) { return __half2float(__ushort_as_half(h)); }
+
+__device__ inline float load_as_float(const float *p, size_t i) { return p[i]; }
+__device__ inline float load_as_float(const __nv_bfloat16 *p, size_t i) { return __bfloat162float(p[i]); }
+__device__ inline void store_from_float(float *p, size_t i, float v) { p[i] = v; }
+__device__ inline void store_from_float(__nv_bfloat16 *p, size_t i, float v) { p[i] = __float2bfloat16_rn(v); }
+
+// ---------------------------------------------------------------- activation blocks in the workspace
+// Q8_K rows: qs int8 [rows, K], d f32 [rows, K/256], bsums i16 [rows, K/16]
+// Q8_0 rows: qs int8 [rows, K], d f32 [rows, K/32] (the f16-rounded scale, widened)
+struct QAct {
+    int8_t *qs;
+    float *d;
+    int16_t *bsums;  // Q8_K only
+};
+
+// ---------------------------------------------------------------- expert lists (device)
+// Built by the grouping kernels from the [n, k] routing table.
+struct Groups {
+    int *count;       // [E_local]
+    int *offset;      // [E_local + 1] exclusive scan of count
+    int *pos;         // [n*k] position of pair p inside its expert's list, -1 if not local
+    int *pairs;       // [n*k] pair ids (t*k + j) sorted by expert
+    int *active;      // [E_local] local expert ids with count > 0, ascending
+    int *n_active;    // [1]
+};
+
+// Everything a forward call needs, resolved to raw pointers.
+struct LayerDev {
+    int H, F, E, k;
+    int expert_base, E_local;
+    int gate_dtype, up_dtype, down_dtype;
+    const uint8_t *gate_exps, *up_exps, *down_exps;
+    int has_shared, sh_gate_dtype, sh_up_dtype, sh_down_dtype;
+    const uint8_t *sh_gate, *sh_up, *sh_down;
+    const float *sh_gate_inp;
+    const float *router_w, *router_bias;
+};
+
+struct Workspace {
+    int max_tokens;
+    DevStatus *status;
+    float *logits;       // [n, E]
+    uint32_t *topk_idx;  // [n, k]
+    float *topk_w;       // [n, k]
+    QAct x_q8k, x_q80;   // quantised input rows [n, H]
+    float *sh_sigmoid;   // [n]
+    Groups groups;
+    float *act;          // [n*(k+1), F]  silu(gate)*up ; routed pair p at row p, shared token t at row n_cap*k + t
+    QAct act_q8k, act_q80;
+    float *partial;      // [n*(k+1), H]  weighted down-projection rows
+};
+
+// ---------------------------------------------------------------- launch interface
+// pmoe_route.cu
+cudaError_t launch_prep(const LayerDev &L, const Workspace &ws, const void *x, int x_dtype, int n,
+                        bool need_q8k, bool need_q80, bool need_gate, cudaStream_t s);
+cudaError_t launch_router(const LayerDev &L, const Workspace &ws, const void *x, int x_dtype, int n,
+                          float *logits, cudaStream_t s);
+cudaError_t launch_topk(const LayerDev &L, const Workspace &ws, const float *logits, int n,
+                        uint32_t *idx, float *w, cudaStream_t s);
+cudaError_t launch_group(const LayerDev &L, const Workspace &ws, const uint32_t *idx, int n, int top_k,
+                         cudaStream_t s);
+// pmoe_gemv.cu
+cudaError_t launch_gate_up(const LayerDev &L, const Workspace &ws, int n, int top_k, bool routed,
+                           bool shared, cudaStream_t s);
+cudaError_t launch_act_quant(const LayerDev &L, const Workspace &ws, const uint32_t *idx, int n, int top_k,
+                             bool routed, bool shared, cudaStream_t s);
+cudaError_t launch_down(const LayerDev &L, const Workspace &ws, const float *w, int n, int top_k,
+                        bool routed, bool shared, cudaStream_t s);
+cudaError_t launch_combine(const LayerDev &L, const Workspace &ws, const uint32_t *idx, int n, int top_k,
+                           bool routed, bool shared, void *out, int out_dtype, cudaStream_t s);
+bool gemv_supported(int dtype, int K, int rows, const char **why);
+// pmoe_codec.cu
+cudaError_t launch_dequantize(int dtype, const void *blocks, size_t n_elems, float *out, cudaStream_t s);
+cudaError_t launch_add_rms_norm(const float *resid_in, const float *delta, const float *weight, int n, int H,
+                                float eps, float *resid_out, float *y, cudaStream_t s);
+
+void count_launch(int n = 1);
+
+}  // namespace pmoe

@@ -1,0 +1,277 @@
+// Routing side of the MoE block: activation quantisation of the input rows, the router
+// GEMV in a fixed summation order, clamp + softmax + top-k + renormalisation, and the
+// device-side grouping of (token, slot) pairs by expert.
+//
+// Reference semantics: MoeBlock::forward_with_stats (paramecia-model/src/qwen3_next.rs:1903-1940),
+// ops::topk_moe_routing (paramecia-model/src/ops.rs:28-59), the host-side grouping of
+// apply_experts_sequential (qwen3_next.rs:2037-2050) and ops::group_tokens_by_expert (ops.rs:74-157).
+#include "pmoe_common.cuh"
+#include "pmoe_quant.cuh"
+
+namespace pmoe {
+
+// ---------------------------------------------------------------- prep: per-token work
+// One CTA per token: widen the row to f32 in shared memory, quantise it for the expert
+// mat-muls and evaluate the shared expert's gate sigmoid(sum_j x_j * w_j)
+// (SharedExpert::forward, qwen3_next.rs:1811-1812).
+template <typename XT>
+__global__ void __launch_bounds__(256) k_prep(const XT *__restrict__ x, int H, bool q8k, bool q80, QAct a8k,
+                                              QAct a80, const float *__restrict__ gate_inp,
+                                              float *__restrict__ sh_sigmoid)
+{
+    extern __shared__ __align__(16) float xrow[];
+    __shared__ float red[8];
+    const int t = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    float part = 0.f;
+    for (int h = threadIdx.x; h < H; h += blockDim.x) {
+        float v = load_as_float(x, (size_t)t * H + h);
+        xrow[h] = v;
+        if (gate_inp) part += v * gate_inp[h];
+    }
+    __syncthreads();
+    block_quant_row(xrow, H, q8k, q80, a8k, a80, t, warp, blockDim.x >> 5, lane);
+    if (gate_inp) {
+#pragma unroll
+        for (int s = 16; s >= 1; s >>= 1) part += __shfl_xor_sync(0xffffffffu, part, s);
+        if (lane == 0) red[warp] = part;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            float s = 0.f;
+            for (int w = 0; w < (int)(blockDim.x >> 5); w++) s += red[w];
+            sh_sigmoid[t] = 1.f / (1.f + expf(-s));
+        }
+    }
+}
+
+cudaError_t launch_prep(const LayerDev &L, const Workspace &ws, const void *x, int x_dtype, int n, bool need_q8k,
+                        bool need_q80, bool need_gate, cudaStream_t s)
+{
+    if (n <= 0) return cudaSuccess;
+    size_t smem = (size_t)L.H * sizeof(float);
+    const float *gi = need_gate ? L.sh_gate_inp : nullptr;
+    if (x_dtype == PMOE_F32)
+        k_prep<float><<<n, 256, smem, s>>>((const float *)x, L.H, need_q8k, need_q80, ws.x_q8k, ws.x_q80, gi,
+                                           ws.sh_sigmoid);
+    else
+        k_prep<__nv_bfloat16><<<n, 256, smem, s>>>((const __nv_bfloat16 *)x, L.H, need_q8k, need_q80, ws.x_q8k,
+                                                   ws.x_q80, gi, ws.sh_sigmoid);
+    count_launch();
+    return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------- router logits
+// logits[t, e] = sum_h x[t, h] * W[e, h] (+ bias[e]) in f32.  The summation order is part of
+// the contract (the top-k indices must equal the CPU oracle's): lane p of a warp owns
+// elements 128*i + 4*p + j, takes them i ascending then j = 0..3 with one fused
+// multiply-add each, and the 32 partial sums fold through v += shfl_xor(v, s), s = 16..1.
+__device__ inline float4 load_x4(const float *x, size_t off) { return *reinterpret_cast<const float4 *>(x + off); }
+__device__ inline float4 load_x4(const __nv_bfloat16 *x, size_t off)
+{
+    uint2 r = *reinterpret_cast<const uint2 *>(x + off);
+    __nv_bfloat162 a = *reinterpret_cast<__nv_bfloat162 *>(&r.x);
+    __nv_bfloat162 b = *reinterpret_cast<__nv_bfloat162 *>(&r.y);
+    return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
+}
+
+constexpr int ROUTER_WPB = 2;
+
+template <typename XT, int TT>
+__global__ void __launch_bounds__(ROUTER_WPB * 32) k_router(const float *__restrict__ W,
+                                                            const float *__restrict__ bias,
+                                                            const XT *__restrict__ x, int n, int E, int H,
+                                                            float *__restrict__ logits)
+{
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int e = blockIdx.x * ROUTER_WPB + warp;
+    if (e >= E) return;
+    const float4 *w4 = reinterpret_cast<const float4 *>(W + (size_t)e * H);
+    const int steps = H / 128;
+    for (int t0 = 0; t0 < n; t0 += TT) {
+        float acc[TT];
+#pragma unroll
+        for (int tt = 0; tt < TT; tt++) acc[tt] = 0.f;
+#pragma unroll 4
+        for (int i = 0; i < steps; i++) {
+            float4 wv = w4[32 * i + lane];
+#pragma unroll
+            for (int tt = 0; tt < TT; tt++) {
+                if (t0 + tt < n) {
+                    float4 xv = load_x4(x, (size_t)(t0 + tt) * H + 128 * i + 4 * lane);
+                    acc[tt] = fmaf(xv.x, wv.x, acc[tt]);
+                    acc[tt] = fmaf(xv.y, wv.y, acc[tt]);
+                    acc[tt] = fmaf(xv.z, wv.z, acc[tt]);
+                    acc[tt] = fmaf(xv.w, wv.w, acc[tt]);
+                }
+            }
+        }
+#pragma unroll
+        for (int tt = 0; tt < TT; tt++) {
+            float v = acc[tt];
+#pragma unroll
+            for (int s = 16; s >= 1; s >>= 1) v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, s));
+            if (lane == 0 && t0 + tt < n) logits[(size_t)(t0 + tt) * E + e] = bias ? __fadd_rn(v, bias[e]) : v;
+        }
+    }
+}
+
+cudaError_t launch_router(const LayerDev &L, const Workspace &ws, const void *x, int x_dtype, int n, float *logits,
+                          cudaStream_t s)
+{
+    (void)ws;
+    if (n <= 0) return cudaSuccess;
+    dim3 grid((L.E + ROUTER_WPB - 1) / ROUTER_WPB), block(ROUTER_WPB * 32);
+    if (x_dtype == PMOE_F32) {
+        if (n == 1)
+            k_router<float, 1><<<grid, block, 0, s>>>(L.router_w, L.router_bias, (const float *)x, n, L.E, L.H, logits);
+        else
+            k_router<float, 8><<<grid, block, 0, s>>>(L.router_w, L.router_bias, (const float *)x, n, L.E, L.H, logits);
+    } else {
+        if (n == 1)
+            k_router<__nv_bfloat16, 1><<<grid, block, 0, s>>>(L.router_w, L.router_bias, (const __nv_bfloat16 *)x, n,
+                                                              L.E, L.H, logits);
+        else
+            k_router<__nv_bfloat16, 8><<<grid, block, 0, s>>>(L.router_w, L.router_bias, (const __nv_bfloat16 *)x, n,
+                                                              L.E, L.H, logits);
+    }
+    count_launch();
+    return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------- softmax + top-k
+// One warp per token.  clamp(+-100) (qwen3_next.rs:1923), softmax over E (1924), then the
+// first k entries of a stable descending sort with the weights divided by their sum
+// (ops.rs:44-52): k rounds of arg-max where a tie goes to the lower expert id.
+constexpr int TOPK_WPB = 4;
+
+__global__ void __launch_bounds__(TOPK_WPB * 32) k_topk(const float *__restrict__ logits, int n, int E, int k,
+                                                        uint32_t *__restrict__ idx_out, float *__restrict__ w_out)
+{
+    extern __shared__ float sprob[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * TOPK_WPB + warp;
+    if (t >= n) return;
+    float *p = sprob + (size_t)warp * E;
+    float mx = -INFINITY;
+    for (int e = lane; e < E; e += 32) {
+        float v = logits[(size_t)t * E + e];
+        v = fminf(fmaxf(v, -100.f), 100.f);
+        p[e] = v;
+        mx = fmaxf(mx, v);
+    }
+#pragma unroll
+    for (int s = 16; s >= 1; s >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, s));
+    float sum = 0.f;
+    for (int e = lane; e < E; e += 32) {
+        float v = expf(p[e] - mx);
+        p[e] = v;
+        sum += v;
+    }
+#pragma unroll
+    for (int s = 16; s >= 1; s >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, s);
+    for (int e = lane; e < E; e += 32) p[e] = __fdiv_rn(p[e], sum);
+    __syncwarp();
+    float my_w = 0.f;      // lane j keeps the j-th selection
+    uint32_t my_i = 0;
+    for (int j = 0; j < k; j++) {
+        float bv = -1.f;
+        int bi = 0x7fffffff;
+        for (int e = lane; e < E; e += 32) {
+            float v = p[e];
+            if (v > bv) { bv = v; bi = e; }
+        }
+#pragma unroll
+        for (int s = 16; s >= 1; s >>= 1) {
+            float ov = __shfl_xor_sync(0xffffffffu, bv, s);
+            int oi = __shfl_xor_sync(0xffffffffu, bi, s);
+            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+        }
+        if (lane == j) { my_w = bv; my_i = (uint32_t)bi; }
+        if (lane == 0) p[bi] = -2.f;
+        __syncwarp();
+    }
+    float wsum = 0.f;
+    for (int j = 0; j < k; j++) wsum += __shfl_sync(0xffffffffu, my_w, j);
+    if (lane < k) {
+        if (idx_out) idx_out[(size_t)t * k + lane] = my_i;
+        if (w_out) w_out[(size_t)t * k + lane] = __fdiv_rn(my_w, wsum);
+    }
+}
+
+cudaError_t launch_topk(const LayerDev &L, const Workspace &ws, const float *logits, int n, uint32_t *idx, float *w,
+                        cudaStream_t s)
+{
+    (void)ws;
+    if (n <= 0) return cudaSuccess;
+    size_t smem = (size_t)TOPK_WPB * L.E * sizeof(float);
+    k_topk<<<(n + TOPK_WPB - 1) / TOPK_WPB, TOPK_WPB * 32, smem, s>>>(logits, n, L.E, L.k, idx, w);
+    count_launch();
+    return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------- grouping by expert
+// Counting sort of the n*k (token, slot) pairs by local expert id in one CTA:
+// counts through shared-memory atomics, an exclusive scan, then the scatter.  The order of
+// pairs inside one expert's list depends on atomic arrival order; no result depends on it
+// (every pair's rows are computed on their own and combined in slot order).
+constexpr int GROUP_THREADS = 1024;
+
+__global__ void __launch_bounds__(GROUP_THREADS) k_group(const uint32_t *__restrict__ idx, int npairs, int base,
+                                                         int E_local, Groups g)
+{
+    __shared__ int cnt[1024];
+    __shared__ int scan[1024];
+    __shared__ int act_scan[1024];
+    const int tid = threadIdx.x;
+    cnt[tid] = 0;
+    __syncthreads();
+    for (int p = tid; p < npairs; p += GROUP_THREADS) {
+        uint32_t e = idx[p] - (uint32_t)base;  // wraps to a large value when below base
+        int pos = -1;
+        if (e < (uint32_t)E_local) pos = atomicAdd(&cnt[e], 1);
+        g.pos[p] = pos;
+    }
+    __syncthreads();
+    int c = tid < E_local ? cnt[tid] : 0;
+    int flag = c > 0 ? 1 : 0;
+    scan[tid] = c;
+    act_scan[tid] = flag;
+    __syncthreads();
+    for (int off = 1; off < GROUP_THREADS; off <<= 1) {  // Hillis-Steele inclusive scans
+        int a = tid >= off ? scan[tid - off] : 0;
+        int b = tid >= off ? act_scan[tid - off] : 0;
+        __syncthreads();
+        scan[tid] += a;
+        act_scan[tid] += b;
+        __syncthreads();
+    }
+    int excl = scan[tid] - c;
+    if (tid < E_local) {
+        g.count[tid] = c;
+        g.offset[tid] = excl;
+        if (flag) g.active[act_scan[tid] - 1] = tid;
+    }
+    if (tid == GROUP_THREADS - 1) {
+        g.offset[E_local] = scan[tid];
+        *g.n_active = act_scan[tid];
+    }
+    cnt[tid] = excl;  // reuse as the per-expert base
+    __syncthreads();
+    for (int p = tid; p < npairs; p += GROUP_THREADS) {
+        int pos = g.pos[p];
+        if (pos >= 0) {
+            uint32_t e = idx[p] - (uint32_t)base;
+            g.pairs[cnt[e] + pos] = p;
+        }
+    }
+}
+
+cudaError_t launch_group(const LayerDev &L, const Workspace &ws, const uint32_t *idx, int n, int top_k,
+                         cudaStream_t s)
+{
+    k_group<<<1, GROUP_THREADS, 0, s>>>(idx, n * top_k, L.expert_base, L.E_local, ws.groups);
+    count_launch();
+    return cudaGetLastError();
+}
+
+}  // namespace pmoe

@@ -1,0 +1,302 @@
+"""Host-side mirror of the reference's MoE block interface over libpmoe.
+
+Names and argument meaning follow paramecia-model/src/qwen3_next.rs:
+
+* ``QTensor``            -- candle's quantised tensor as the reference uses it: raw GGUF blocks,
+                            a GGML dtype and a shape; ``dequantize`` is QTensor::dequantize.
+* ``MoeBlock``           -- MoeBlock (1840-2218): ``forward`` / ``forward_with_stats`` return what
+                            the Rust methods return; ``top_k`` is ops::topk_moe_routing on the
+                            block's own router; ``experts_forward_batched`` is
+                            MoeExperts::forward_batched (1347-1394); ``shared_forward`` is
+                            SharedExpert::forward (1776-1823).
+
+Tensors are torch CUDA tensors; this module only checks shapes, allocates outputs and passes
+raw pointers and the current stream to the C ABI.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+from typing import Optional, Tuple
+
+import numpy as np
+import torch
+
+from . import _lib
+from ._lib import BF16, F32, LayerDesc, PmoeError, check, lib, row_bytes
+
+_TORCH_TO_PMOE = {torch.float32: F32, torch.bfloat16: BF16}
+
+
+def _stream_ptr(device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _as_u8(data, device=None) -> torch.Tensor:
+    if isinstance(data, np.ndarray):
+        data = torch.from_numpy(np.ascontiguousarray(data).view(np.uint8).reshape(-1))
+    if data.dtype != torch.uint8:
+        data = data.contiguous().view(torch.uint8)
+    data = data.reshape(-1).contiguous()
+    if device is not None:
+        data = data.to(device)
+    return data
+
+
+class QTensor:
+    """Raw GGUF blocks with a GGML dtype id and a logical shape (rows..., cols)."""
+
+    def __init__(self, data, dtype: int, shape: Tuple[int, ...]):
+        self.data = _as_u8(data)
+        self.dtype = int(dtype)
+        self.shape = tuple(int(s) for s in shape)
+        n = 1
+        for s in self.shape:
+            n *= s
+        expect = n // _lib.block_size(self.dtype) * _lib.type_size(self.dtype)
+        if self.data.numel() != expect:
+            raise ValueError(f"QTensor: {self.data.numel()} bytes given, shape {self.shape} needs {expect}")
+
+    @property
+    def device(self):
+        return self.data.device
+
+    def to(self, device) -> "QTensor":
+        return QTensor(self.data.to(device), self.dtype, self.shape)
+
+    def numel(self) -> int:
+        n = 1
+        for s in self.shape:
+            n *= s
+        return n
+
+    def slice_first_dim(self, index: int) -> "QTensor":
+        """QTensor::slice_first_dim: expert `index` is one contiguous byte range."""
+        per = self.data.numel() // self.shape[0]
+        return QTensor(self.data[index * per:(index + 1) * per], self.dtype, self.shape[1:])
+
+    def dequantize(self, device=None) -> torch.Tensor:
+        dev = torch.device(device) if device is not None else self.data.device
+        return dequantize(self.data.to(dev), self.dtype, self.numel()).reshape(self.shape)
+
+
+def dequantize(blocks: torch.Tensor, dtype: int, n_elems: int) -> torch.Tensor:
+    """QTensor::dequantize on the GPU: raw blocks (uint8, CUDA) -> f32."""
+    if not blocks.is_cuda:
+        raise PmoeError(-9, "dequantize needs CUDA tensors; libpmoe has no CPU path")
+    blocks = blocks.contiguous()
+    out = torch.empty(n_elems, dtype=torch.float32, device=blocks.device)
+    check(lib().pmoe_dequantize(blocks.device.index or 0, dtype, blocks.data_ptr(), n_elems, out.data_ptr(),
+                                _stream_ptr(blocks.device)))
+    return out
+
+
+def add_rms_norm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: Optional[torch.Tensor],
+                 eps: float) -> Tuple[torch.Tensor, torch.Tensor]:
+    """(resid + delta, RmsNorm(resid + delta)): quantized_nn.rs:172-190 with the residual add
+    of LayerWeights::forward_with_stats (qwen3_next.rs:4273-4286)."""
+    n, H = resid.shape
+    resid = resid.contiguous()
+    new_resid = torch.empty_like(resid)
+    y = torch.empty_like(resid)
+    check(lib().pmoe_add_rms_norm(resid.device.index or 0, resid.data_ptr(),
+                                  None if delta is None else delta.contiguous().data_ptr(),
+                                  None if weight is None else weight.contiguous().data_ptr(),
+                                  n, H, float(eps), new_resid.data_ptr(), y.data_ptr(), _stream_ptr(resid.device)))
+    return new_resid, y
+
+
+@dataclass
+class SharedExpertWeights:
+    """ffn_{gate,up,down}_shexp.weight and ffn_gate_inp_shexp (qwen3_next.rs:1749-1774)."""
+    gate_proj: QTensor   # [F, H]
+    up_proj: QTensor     # [F, H]
+    down_proj: QTensor   # [H, F]
+    shared_gate: torch.Tensor  # [H] f32
+
+
+class MoeBlock:
+    """One Qwen3-Next sparse MoE FFN block resident on one GPU.
+
+    gate_exps / up_exps: QTensor [E_local, F, H]; down_exps: QTensor [E_local, H, F];
+    gate (router): f32 tensor [E, H].  With expert parallelism a rank passes its slice of the
+    experts and ``expert_base``; indices outside the slice contribute nothing.
+    """
+
+    def __init__(self, gate_exps: QTensor, up_exps: QTensor, down_exps: QTensor, gate: torch.Tensor,
+                 num_experts_per_tok: int, shared_expert: Optional[SharedExpertWeights] = None,
+                 device="cuda:0", max_tokens: int = 256, router_bias: Optional[torch.Tensor] = None,
+                 num_experts: Optional[int] = None, expert_base: int = 0, training_mode: bool = False):
+        self.device = torch.device(device)
+        if self.device.type != "cuda":
+            raise PmoeError(-9, "MoeBlock needs a CUDA device; libpmoe has no CPU path")
+        if self.device.index is None:
+            self.device = torch.device("cuda", torch.cuda.current_device())
+        E_local, F, H = gate_exps.shape
+        self.hidden_dim, self.n_ff = H, F
+        self.num_experts = int(num_experts) if num_experts is not None else int(gate.shape[0])
+        self.num_experts_local = E_local
+        self.expert_base = int(expert_base)
+        self.num_experts_per_tok = int(num_experts_per_tok)
+        self.max_tokens = int(max_tokens)
+        if tuple(up_exps.shape) != (E_local, F, H) or tuple(down_exps.shape) != (E_local, H, F):
+            raise ValueError("expert tensor shapes must be [E,F,H], [E,F,H], [E,H,F]")
+        if tuple(gate.shape) != (self.num_experts, H):
+            raise ValueError("router weight must be [E, H]")
+        # the library adopts these device buffers in place (weights_location = 2); keep them alive
+        self._keep = dict(
+            gate=gate_exps.data.to(self.device), up=up_exps.data.to(self.device),
+            down=down_exps.data.to(self.device),
+            router=gate.to(self.device, torch.float32).contiguous(),
+            bias=None if router_bias is None else router_bias.to(self.device, torch.float32).contiguous())
+        d = LayerDesc()
+        d.struct_size = C.sizeof(LayerDesc)
+        d.device = self.device.index
+        d.H, d.F, d.E, d.k = H, F, self.num_experts, self.num_experts_per_tok
+        d.max_tokens = self.max_tokens
+        d.expert_base, d.E_local = self.expert_base, E_local
+        d.gate_dtype, d.up_dtype, d.down_dtype = gate_exps.dtype, up_exps.dtype, down_exps.dtype
+        d.gate_exps, d.up_exps, d.down_exps = (self._keep[k].data_ptr() for k in ("gate", "up", "down"))
+        d.has_shared = 0
+        if shared_expert is not None:
+            s = shared_expert
+            self._keep.update(sg=s.gate_proj.data.to(self.device), su=s.up_proj.data.to(self.device),
+                              sd=s.down_proj.data.to(self.device),
+                              sgi=s.shared_gate.to(self.device, torch.float32).contiguous())
+            d.has_shared = 1
+            d.sh_gate_dtype, d.sh_up_dtype, d.sh_down_dtype = s.gate_proj.dtype, s.up_proj.dtype, s.down_proj.dtype
+            d.sh_gate, d.sh_up, d.sh_down = (self._keep[k].data_ptr() for k in ("sg", "su", "sd"))
+            d.sh_gate_inp = self._keep["sgi"].data_ptr()
+        d.router_dtype = F32
+        d.router_w = self._keep["router"].data_ptr()
+        d.router_bias = None if self._keep["bias"] is None else self._keep["bias"].data_ptr()
+        d.weights_location = 2
+        d.training_mode = 1 if training_mode else 0
+        self.has_shared = shared_expert is not None
+        self._desc = d
+        self._h = C.c_void_p()
+        with torch.cuda.device(self.device):
+            check(lib().pmoe_layer_create(C.byref(d), C.byref(self._h)))
+
+    # -- lifetime -------------------------------------------------------------------
+    def close(self):
+        if getattr(self, "_h", None) is not None and self._h.value:
+            lib().pmoe_layer_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # -- helpers --------------------------------------------------------------------
+    def _flat(self, hidden_states: torch.Tensor) -> torch.Tensor:
+        if hidden_states.dtype not in _TORCH_TO_PMOE:
+            raise PmoeError(-2, f"activations must be float32 or bfloat16, got {hidden_states.dtype}")
+        if not hidden_states.is_cuda:
+            raise PmoeError(-9, "activations must be CUDA tensors; use forward_host for host buffers")
+        if hidden_states.shape[-1] != self.hidden_dim:
+            raise ValueError(f"last dim must be {self.hidden_dim}")
+        return hidden_states.reshape(-1, self.hidden_dim).contiguous()
+
+    def weight_bytes(self, distinct_experts: int) -> int:
+        """Algorithmic weight bytes one decode call streams when `distinct_experts` experts are hit."""
+        d = self._desc
+        per = self.n_ff * (row_bytes(d.gate_dtype, d.H) + row_bytes(d.up_dtype, d.H)) + d.H * row_bytes(d.down_dtype, d.F)
+        b = distinct_experts * per + self.num_experts * d.H * 4
+        if self.has_shared:
+            b += self.n_ff * (row_bytes(d.sh_gate_dtype, d.H) + row_bytes(d.sh_up_dtype, d.H)) \
+                + d.H * row_bytes(d.sh_down_dtype, d.F)
+        return b
+
+    # -- the reference's methods ----------------------------------------------------
+    def forward_with_stats(self, hidden_states: torch.Tensor, out_dtype: Optional[torch.dtype] = None):
+        """MoeBlock::forward_with_stats: ``(out [b,l,H], (router_logits [b,l,E], top_indices [b,l,k]))``.
+        The logits are the unclamped ones; indices are int32 tensors holding the u32 ids."""
+        shape = hidden_states.shape
+        x = self._flat(hidden_states)
+        n = x.shape[0]
+        out_dtype = out_dtype or hidden_states.dtype
+        out = torch.empty((n, self.hidden_dim), dtype=out_dtype, device=self.device)
+        logits = torch.empty((n, self.num_experts), dtype=torch.float32, device=self.device)
+        idx = torch.empty((n, self.num_experts_per_tok), dtype=torch.int32, device=self.device)
+        w = torch.empty((n, self.num_experts_per_tok), dtype=torch.float32, device=self.device)
+        check(lib().pmoe_forward(self._h, x.data_ptr(), _TORCH_TO_PMOE[x.dtype], n, out.data_ptr(),
+                                 _TORCH_TO_PMOE[out_dtype], logits.data_ptr(), idx.data_ptr(), w.data_ptr(),
+                                 _stream_ptr(self.device)))
+        self.last_top_weights = w
+        lead = tuple(shape[:-1])
+        return out.reshape(*lead, self.hidden_dim), (logits.reshape(*lead, self.num_experts),
+                                                     idx.reshape(*lead, self.num_experts_per_tok))
+
+    def forward(self, hidden_states: torch.Tensor) -> torch.Tensor:
+        """MoeBlock::forward."""
+        return self.forward_with_stats(hidden_states)[0]
+
+    def forward_into(self, x: torch.Tensor, out: torch.Tensor):
+        """forward with caller-owned buffers and no stats (nothing is allocated; graph-capturable)."""
+        n = x.shape[0]
+        check(lib().pmoe_forward(self._h, x.data_ptr(), _TORCH_TO_PMOE[x.dtype], n, out.data_ptr(),
+                                 _TORCH_TO_PMOE[out.dtype], None, None, None, _stream_ptr(self.device)))
+
+    def route(self, hidden_states: torch.Tensor):
+        """gate.forward -> clamp -> softmax -> top_k: ``(router_logits, top_weights, top_indices)``."""
+        x = self._flat(hidden_states)
+        n = x.shape[0]
+        logits = torch.empty((n, self.num_experts), dtype=torch.float32, device=self.device)
+        idx = torch.empty((n, self.num_experts_per_tok), dtype=torch.int32, device=self.device)
+        w = torch.empty((n, self.num_experts_per_tok), dtype=torch.float32, device=self.device)
+        check(lib().pmoe_route(self._h, x.data_ptr(), _TORCH_TO_PMOE[x.dtype], n, logits.data_ptr(), idx.data_ptr(),
+                               w.data_ptr(), _stream_ptr(self.device)))
+        return logits, w, idx
+
+    def experts_forward_batched(self, hidden_states: torch.Tensor, expert_indices: torch.Tensor,
+                                expert_weights: torch.Tensor, top_k: Optional[int] = None,
+                                out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+        """MoeExperts::forward_batched(hidden [n,H], indices [n,k] u32, weights [n,k] f32, top_k)."""
+        x = self._flat(hidden_states)
+        n = x.shape[0]
+        top_k = int(top_k or expert_indices.shape[-1])
+        idx = expert_indices.to(self.device, torch.int32).reshape(n, top_k).contiguous()
+        w = expert_weights.to(self.device, torch.float32).reshape(n, top_k).contiguous()
+        out_dtype = out_dtype or hidden_states.dtype
+        out = torch.empty((n, self.hidden_dim), dtype=out_dtype, device=self.device)
+        check(lib().pmoe_experts_forward(self._h, x.data_ptr(), _TORCH_TO_PMOE[x.dtype], idx.data_ptr(), w.data_ptr(),
+                                         n, top_k, out.data_ptr(), _TORCH_TO_PMOE[out_dtype], _stream_ptr(self.device)))
+        return out
+
+    def shared_forward(self, hidden_states: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+        """SharedExpert::forward, sigmoid gate included."""
+        shape = hidden_states.shape
+        x = self._flat(hidden_states)
+        n = x.shape[0]
+        out_dtype = out_dtype or hidden_states.dtype
+        out = torch.empty((n, self.hidden_dim), dtype=out_dtype, device=self.device)
+        check(lib().pmoe_shared_forward(self._h, x.data_ptr(), _TORCH_TO_PMOE[x.dtype], n, out.data_ptr(),
+                                        _TORCH_TO_PMOE[out_dtype], _stream_ptr(self.device)))
+        return out.reshape(shape)
+
+    def forward_host(self, x_host: torch.Tensor, out_host: Optional[torch.Tensor] = None, with_stats: bool = False):
+        """The block with HOST tensors: host->device copy, kernels, device->host copy, synchronised."""
+        if x_host.is_cuda:
+            raise ValueError("forward_host takes host tensors")
+        x = x_host.reshape(-1, self.hidden_dim).contiguous()
+        n = x.shape[0]
+        if out_host is None:
+            out_host = torch.empty((n, self.hidden_dim), dtype=x.dtype)
+        logits = idx = w = None
+        if with_stats:
+            logits = torch.empty((n, self.num_experts), dtype=torch.float32)
+            idx = torch.empty((n, self.num_experts_per_tok), dtype=torch.int32)
+            w = torch.empty((n, self.num_experts_per_tok), dtype=torch.float32)
+        check(lib().pmoe_forward_host(self._h, x.data_ptr(), _TORCH_TO_PMOE[x.dtype], n, out_host.data_ptr(),
+                                      _TORCH_TO_PMOE[out_host.dtype],
+                                      None if logits is None else logits.data_ptr(),
+                                      None if idx is None else idx.data_ptr(),
+                                      None if w is None else w.data_ptr(), _stream_ptr(self.device)))
+        return (out_host, (logits, idx, w)) if with_stats else out_host
+
+    def status(self):
+        """Synchronises and raises PmoeError if a kernel recorded a timeout or a bad index."""
+        check(lib().pmoe_layer_status(self._h, _stream_ptr(self.device)))
