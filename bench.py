@@ -1,0 +1,391 @@
+#!/usr/bin/env python
+"""Benchmark of the quantised MoE FFN block (decode), one JSON line on rank 0.
+
+    python bench.py --gpus N --steps K --warmup W [--impl reference]
+
+Workload (synthetic, seeded): the Qwen3-Next MoE block with Q4_K_M-style mixed quantisation --
+hidden 2048, 512 routed experts (gate/up Q4_K [512x2048], down Q6_K [2048x512]), top-10, one
+Q8_0 shared expert with a sigmoid gate, f32 router -- at decode batch 64 per GPU, bf16 inputs
+~N(0,1), uniform random routing.  A step is one forward of one block; consecutive steps use
+different, independently seeded layers so that the weights of a step are never in L2.
+
+N = 1: the whole block on one GPU.  N > 1: expert parallelism, 512/N experts per GPU, every
+rank home to 64 tokens (weak scaling), dispatch/combine over NCCL.
+
+`value` is tokens/s with the inputs resident in HBM; `e2e` is the same metric through the
+host-buffer entry point (host->device copy of x and device->host copy of the result inside
+the timed region).  `--impl reference` times the CPU restatement of the reference's own CPU
+path (oracle/) on the host cores instead.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "Q4_K MoE layer tokens/s (decode)"
+UNIT = "tokens/s"
+H, F, E, TOPK = 2048, 512, 512, 10
+PRESET = "q4k_m"
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="pmoe", choices=["pmoe", "reference"])
+    ap.add_argument("--batch", type=int, default=64, help="decode tokens per GPU per step")
+    ap.add_argument("--layers", type=int, default=4, help="distinct layers cycled through")
+    ap.add_argument("--no-sweep", action="store_true", help="skip the batch 1/4/16 sweep")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline")
+    ap.add_argument("--cpu-seconds", type=float, default=12.0)
+    ap.add_argument("--ep-mode", default="all_to_all", choices=["all_to_all", "all_gather"])
+    return ap.parse_args()
+
+
+def workload_name(batch, n_gpus):
+    s = (f"qwen3next-moe-block q4k_m (gate/up Q4_K, down Q6_K, shared Q8_0) H{H} F{F} E{E} top{TOPK}, "
+         f"decode batch {batch}/GPU, bf16 x, uniform routing")
+    if n_gpus > 1:
+        s += f", expert-parallel {E // n_gpus} experts/GPU"
+    return s
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.idx = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            f = tempfile.NamedTemporaryFile("w", suffix=".csv", delete=False)
+            self.path = f.name
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.idx)], stdout=f, stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        try:
+            for line in open(self.path):
+                p = [c.strip() for c in line.split(",")]
+                if len(p) < 9:
+                    continue
+                try:
+                    sm.append(float(p[1])); mx.append(float(p[2]))
+                except ValueError:
+                    continue
+                for name, col in (("hw_slowdown", 5), ("hw_thermal_slowdown", 6), ("sw_thermal_slowdown", 7),
+                                  ("sw_power_cap", 8)):
+                    if p[col].lower().startswith("active"):
+                        reasons.add(name)
+            os.unlink(self.path)
+        except Exception:
+            pass
+        if sm:
+            sm.sort()
+            out.update(sm_mhz=sm[len(sm) // 2], sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
+        return out
+
+
+def cpu_threads():
+    try:
+        return len(os.sched_getaffinity(0))
+    except Exception:
+        return os.cpu_count() or 1
+
+
+def run_cpu_baseline(layer_host, batch, seconds, seed=1234):
+    """Times the oracle (the port of the reference's CPU path) on whole-block forwards of `batch` tokens."""
+    import torch
+    from oracle import pmoe_oracle as po
+    from tests.common import oracle_layer
+    ol = oracle_layer(layer_host)
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn((batch, H), generator=g).to(torch.bfloat16).float().numpy()
+    ol.forward(x)  # warm-up (page in the weights)
+    t0 = time.perf_counter()
+    reps = 0
+    while True:
+        ol.forward(x)
+        reps += 1
+        el = time.perf_counter() - t0
+        if el >= seconds or reps >= 50:
+            break
+    return dict(value=batch * reps / el, unit=UNIT, cores=po.max_threads(), kind="port",
+                sample=f"{reps} whole-block forwards of batch {batch} on one layer, {el:.1f} s; "
+                       f"C restatement of the reference CPU path ({po.simd_kind()}), OpenMP over experts and rows",
+                ms_per_step=1e3 * el / reps)
+
+
+def reference_arm(args, rank):
+    """--impl reference: the CPU restatement of the reference's own CPU path on the host cores."""
+    if rank != 0:
+        return
+    import torch
+    from paramecia_b200 import synth
+    layer = synth.make_layer(H, F, E, TOPK, PRESET, seed=0, device="cpu", layer=0)
+    from oracle import pmoe_oracle as po
+    from tests.common import oracle_layer
+    ol = oracle_layer(layer)
+    batch = args.batch * args.gpus
+    g = torch.Generator().manual_seed(99)
+    x = torch.randn((batch, H), generator=g).to(torch.bfloat16).float().numpy()
+    steps = max(1, min(args.steps, 20))
+    warm = max(1, min(args.warmup, 2))
+    for _ in range(warm):
+        ol.forward(x)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        ol.forward(x)
+    el = time.perf_counter() - t0
+    val = batch * steps / el
+    line = dict(metric=METRIC, value=val, unit=UNIT, n_gpus=args.gpus, steps=steps, warmup=warm,
+                ms_per_step=1e3 * el / steps, higher_is_better=True, scaling="weak", vs_baseline=None,
+                dtype="int8 x int4/6/8 block dots, f32 accumulate", data="synthetic", impl="reference",
+                config=dict(workload=workload_name(args.batch, args.gpus), global_batch=batch,
+                            note="the Rust reference cannot be built here (no cargo, candle fork not vendored); "
+                                 "this is the C restatement of its CPU path in oracle/"),
+                cpu_baseline=dict(value=val, unit=UNIT, cores=po.max_threads(), kind="port",
+                                  sample=f"{steps} whole-block forwards of batch {batch}, one layer, all host threads"),
+                e2e=dict(value=val, unit=UNIT, h2d_bytes_per_step=0, d2h_bytes_per_step=0),
+                gpu_launches=0)
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    args = parse()
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.impl == "reference":
+        reference_arm(args, rank)
+        return
+    import torch
+    import torch.distributed as dist
+    import paramecia_b200 as pm
+    from paramecia_b200 import synth
+
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("launch multi-GPU runs with torch.distributed.run (one rank per GPU)")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    N = world
+    batch = args.batch
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except Exception:
+        pass
+    hbm_peak = float(peaks.get("hbm_gbs", 6650.0))
+    peak_kind = "measured (MEASURED_PEAKS.json hbm_gbs)" if "hbm_gbs" in peaks else "fallback 6650 GB/s"
+
+    # ---- layers: every rank builds the same seeded layers and keeps its slice of the experts
+    E_local = E // N
+    max_tok = batch * N if N > 1 else max(batch, 64)
+    blocks, host_layer0 = [], None
+    for li in range(args.layers):
+        t = synth.make_layer(H, F, E, TOPK, PRESET, seed=0, device=dev, layer=li)
+        if li == 0 and rank == 0 and not args.no_cpu:
+            host_layer0 = {k: (v.cpu() if torch.is_tensor(v) else v) for k, v in t.items()}
+            host_layer0["shared"] = {k: (v.cpu() if torch.is_tensor(v) else v) for k, v in t["shared"].items()}
+        blocks.append(synth.make_block(t, dev, max_tokens=max_tok, expert_base=rank * E_local, E_local=E_local))
+        del t
+    torch.cuda.synchronize()
+
+    if N > 1:
+        from paramecia_b200.ep import ExpertParallelMoe
+        eps = [ExpertParallelMoe(b, mode=args.ep_mode) for b in blocks]
+
+    def make_x(n, seed):
+        g = torch.Generator(device=dev).manual_seed(seed + 7919 * rank)
+        return torch.randn((n, H), generator=g, device=dev).to(torch.bfloat16)
+
+    def barrier():
+        if N > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def time_steps(n_tok, steps, warmup):
+        """Device time (ms) of `steps` forwards of n_tok tokens per GPU, layers cycled; max over ranks."""
+        xs = [make_x(n_tok, 100 + i) for i in range(4)]
+        out = torch.empty((n_tok, H), dtype=torch.bfloat16, device=dev)
+
+        def step(i):
+            b = i % len(blocks)
+            if N > 1:
+                eps[b].forward_into(xs[i % 4], out)
+            else:
+                blocks[b].forward_into(xs[i % 4], out)
+        for i in range(warmup):
+            step(i)
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        before = pm.launch_count()
+        e0.record()
+        for i in range(steps):
+            step(warmup + i)
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1)
+        launches = pm.launch_count() - before
+        if N > 1:
+            tms = torch.tensor([ms], device=dev)
+            dist.all_reduce(tms, op=dist.ReduceOp.MAX)
+            ms = float(tms.item())
+        return ms, launches
+
+    def distinct_experts(n_tok):
+        """Average number of distinct local experts a step touches (for the algorithmic bytes)."""
+        tot = 0
+        for i in range(4):
+            x = make_x(n_tok, 100 + i)
+            if N > 1:
+                x = eps[0].gather_tokens(x)
+            _, _, idx = blocks[i % len(blocks)].route(x)
+            idx = idx.to(torch.int64)
+            loc = idx[(idx >= rank * E_local) & (idx < (rank + 1) * E_local)]
+            tot += int(torch.unique(loc).numel())
+        return tot / 4.0
+
+    W = max(args.warmup, 3)
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    ms, launches = time_steps(batch, args.steps, W)
+    clocks = sampler.stop() if rank == 0 else {}
+    ms_per_step = ms / args.steps
+    value = batch * N * args.steps / (ms * 1e-3)
+
+    # ---- roofline of the dominant kernel (gate/up GEMV): traced pass, events around each kernel
+    D = distinct_experts(batch)
+    blk0 = blocks[0]
+    d = blk0._desc
+    gu_bytes = D * F * (pm.row_bytes(d.gate_dtype, H) + pm.row_bytes(d.up_dtype, H))
+    gu_bytes += F * (pm.row_bytes(d.sh_gate_dtype, H) + pm.row_bytes(d.sh_up_dtype, H))
+    step_bytes = blk0.weight_bytes(int(round(D))) + batch * H * 4  # weights + x in + out (bf16 each)
+    phase_ms = {}
+    if N == 1:
+        x = make_x(batch, 5)
+        out = torch.empty((batch, H), dtype=torch.bfloat16, device=dev)
+        for b in blocks:
+            b.trace(True)
+        reps = min(args.steps, 50)
+        for i in range(reps + 3):
+            b = blocks[i % len(blocks)]
+            b.forward_into(x, out)
+            t = b.trace_read()
+            if i >= 3:
+                for k_, v in t.items():
+                    phase_ms[k_] = phase_ms.get(k_, 0.0) + v / reps
+        for b in blocks:
+            b.trace(False)
+    roofline = None
+    if phase_ms.get("gate_up"):
+        ach = gu_bytes / (phase_ms["gate_up"] * 1e-3) / 1e9
+        roofline = dict(bound="hbm", kernel="k_expert_gemv<gate+up>", achieved=ach, peak=hbm_peak, unit="GB/s",
+                        frac=ach / hbm_peak, peak_kind=peak_kind, traffic=None,
+                        algorithmic_bytes_per_launch=gu_bytes, us_per_launch=phase_ms["gate_up"] * 1e3,
+                        phases_us={k_: round(v * 1e3, 2) for k_, v in phase_ms.items()},
+                        layer_gbs=step_bytes / (ms_per_step * 1e-3) / 1e9,
+                        layer_frac=step_bytes / (ms_per_step * 1e-3) / 1e9 / hbm_peak,
+                        layer_bytes_per_step=step_bytes, distinct_experts=D)
+
+    # ---- batch sweep 1/4/16 (tokens/s and whole-layer GB/s)
+    sweep = {}
+    if N == 1 and not args.no_sweep:
+        for nb in (1, 4, 16):
+            s_ms, _ = time_steps(nb, args.steps, W)
+            Dn = distinct_experts(nb)
+            byt = blk0.weight_bytes(int(round(Dn))) + nb * H * 4
+            gbs = byt / (s_ms / args.steps * 1e-3) / 1e9
+            sweep[str(nb)] = dict(tokens_per_s=nb * args.steps / (s_ms * 1e-3), us_per_step=1e3 * s_ms / args.steps,
+                                  layer_gbs=gbs, layer_frac=gbs / hbm_peak, distinct_experts=Dn)
+        sweep[str(batch)] = dict(tokens_per_s=value, us_per_step=1e3 * ms_per_step,
+                                 layer_gbs=roofline["layer_gbs"] if roofline else None,
+                                 layer_frac=roofline["layer_frac"] if roofline else None, distinct_experts=D)
+
+    # ---- end to end: host buffers through the public host entry point
+    e2e = None
+    if N == 1:
+        xh = [make_x(batch, 300 + i).cpu().pin_memory() for i in range(4)]
+        oh = torch.empty((batch, H), dtype=torch.bfloat16).pin_memory()
+        for i in range(W):
+            blocks[i % len(blocks)].forward_host(xh[i % 4], oh)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for i in range(args.steps):
+            blocks[i % len(blocks)].forward_host(xh[i % 4], oh)
+        torch.cuda.synchronize()
+        el = time.perf_counter() - t0
+        e2e = dict(value=batch * args.steps / el, unit=UNIT, h2d_bytes_per_step=batch * H * 2,
+                   d2h_bytes_per_step=batch * H * 2, ms_per_step=1e3 * el / args.steps)
+    else:
+        xh = [make_x(batch, 300 + i).cpu().pin_memory() for i in range(4)]
+        oh = torch.empty((batch, H), dtype=torch.bfloat16).pin_memory()
+        xd = torch.empty((batch, H), dtype=torch.bfloat16, device=dev)
+        od = torch.empty((batch, H), dtype=torch.bfloat16, device=dev)
+
+        def e2e_step(i):
+            xd.copy_(xh[i % 4], non_blocking=True)
+            eps[i % len(blocks)].forward_into(xd, od)
+            oh.copy_(od, non_blocking=True)
+            torch.cuda.synchronize()
+        for i in range(W):
+            e2e_step(i)
+        barrier()
+        t0 = time.perf_counter()
+        for i in range(args.steps):
+            e2e_step(i)
+        barrier()
+        el = torch.tensor([time.perf_counter() - t0], device=dev)
+        dist.all_reduce(el, op=dist.ReduceOp.MAX)
+        el = float(el.item())
+        e2e = dict(value=batch * N * args.steps / el, unit=UNIT, h2d_bytes_per_step=batch * H * 2,
+                   d2h_bytes_per_step=batch * H * 2, ms_per_step=1e3 * el / args.steps)
+
+    cpu = None
+    if rank == 0 and N == 1 and not args.no_cpu and host_layer0 is not None:
+        cpu = run_cpu_baseline(host_layer0, batch, args.cpu_seconds)
+
+    if rank == 0:
+        line = dict(metric=METRIC, value=value, unit=UNIT, n_gpus=N, steps=args.steps, warmup=W,
+                    ms_per_step=ms_per_step, higher_is_better=True, scaling="weak", vs_baseline=None,
+                    dtype="int8 x int4/6/8 block dots, f32 accumulate", data="synthetic",
+                    config=dict(workload=workload_name(batch, N), global_batch=batch * N, layers_cycled=len(blocks),
+                                l2="each step reads a layer not touched for layers-1 steps; per-step weight "
+                                   "traffic exceeds the 126 MB L2", parallelism=f"ep{N}" if N > 1 else "single",
+                                ep_mode=args.ep_mode if N > 1 else None),
+                    roofline=roofline, cpu_baseline=cpu, e2e=e2e, gpu_launches=launches, clocks=clocks,
+                    sweep=sweep or None)
+        print(json.dumps(line), flush=True)
+    if N > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -168,6 +168,18 @@ int pmoe_add_rms_norm(int device, const float *resid_in, const float *delta, con
  * (PMOE_OK, PMOE_ERR_TIMEOUT, PMOE_ERR_BAD_INDEX), clearing it. */
 int pmoe_layer_status(pmoe_layer *layer, void *stream);
 
+/*
+ * Per-phase device timing, the counterpart of the reference's tracing spans ("moe-block",
+ * "moe-experts", "qmatmul"; qwen3_next.rs:1884,1260, models/with_tracing.rs:116).  While
+ * enabled, pmoe_forward brackets each kernel with CUDA events on the caller's stream;
+ * pmoe_layer_trace_read waits for the last call and returns its milliseconds per phase
+ * (ms[PMOE_TRACE_PHASES]; phases a call did not run read 0).
+ */
+#define PMOE_TRACE_PHASES 8
+int pmoe_layer_trace(pmoe_layer *layer, int enable);
+int pmoe_layer_trace_read(pmoe_layer *layer, float *ms);
+const char *pmoe_trace_phase_name(int phase);
+
 /* number of kernels of this library launched by this process so far */
 uint64_t pmoe_launch_count(void);
 

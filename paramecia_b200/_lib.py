@@ -5,6 +5,7 @@ import ctypes as C
 import os
 
 F32, F16, Q8_0, Q4_K, Q6_K, BF16 = 0, 1, 8, 12, 14, 30
+TRACE_PHASES = 8
 
 STATUS_NAMES = {
     0: "PMOE_OK", -1: "PMOE_ERR_INVALID_ARG", -2: "PMOE_ERR_UNSUPPORTED_DTYPE",
@@ -59,6 +60,9 @@ SYMBOLS = [
     ("pmoe_dequantize", _I, [_I, _I, _V, _Z, _V, _V]),
     ("pmoe_add_rms_norm", _I, [_I, _V, _V, _V, _I, _I, C.c_float, _V, _V, _V]),
     ("pmoe_layer_status", _I, [_V, _V]),
+    ("pmoe_layer_trace", _I, [_V, _I]),
+    ("pmoe_layer_trace_read", _I, [_V, _V]),
+    ("pmoe_trace_phase_name", C.c_char_p, [_I]),
     ("pmoe_launch_count", C.c_uint64, []),
     ("pmoe_block_size", _Z, [_I]),
     ("pmoe_type_size", _Z, [_I]),

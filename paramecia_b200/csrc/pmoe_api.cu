@@ -73,6 +73,10 @@ struct pmoe_layer {
     float *st_logits = nullptr;
     uint32_t *st_idx = nullptr;
     float *st_w = nullptr;
+    // per-phase CUDA events of the last traced call (pmoe_layer_trace)
+    bool trace = false;
+    cudaEvent_t ev0[PMOE_TRACE_PHASES] = {}, ev1[PMOE_TRACE_PHASES] = {};
+    bool ev_used[PMOE_TRACE_PHASES] = {};
 };
 
 namespace {
@@ -117,6 +121,7 @@ void carve_workspace(pmoe_layer *L, Carver &c)
     w.groups.pairs = c.take<int>(n * k);
     w.groups.active = c.take<int>(El);
     w.groups.n_active = c.take<int>(1);
+    w.groups.cost_prefix = c.take<int>(El + 1);
     w.act = c.take<float>(rows * F);
     w.act_q8k.qs = c.take<int8_t>(rows * F);
     w.act_q8k.d = c.take<float>(rows * (F / QK_K));
@@ -170,6 +175,29 @@ struct Needs {
     bool q8k, q80;
 };
 
+// Brackets one launch with the layer's events when tracing is on.
+struct PhaseTimer {
+    pmoe_layer *L;
+    int phase;
+    cudaStream_t s;
+    PhaseTimer(pmoe_layer *l, int p, cudaStream_t st) : L(l), phase(p), s(st)
+    {
+        if (L->trace) cudaEventRecord(L->ev0[phase], s);
+    }
+    ~PhaseTimer()
+    {
+        if (L->trace) {
+            cudaEventRecord(L->ev1[phase], s);
+            L->ev_used[phase] = true;
+        }
+    }
+};
+#define PHASE(L, p, s, call)        \
+    do {                            \
+        PhaseTimer _pt(L, p, s);    \
+        CU(call);                   \
+    } while (0)
+
 Needs input_needs(const LayerDev &d, bool routed, bool shared)
 {
     Needs nd{false, false};
@@ -185,13 +213,13 @@ int run_experts(pmoe_layer *L, const void *x, int x_dtype, const uint32_t *idx, 
     const LayerDev &d = L->dev;
     if (!prep_done) {
         Needs nd = input_needs(d, routed, shared);
-        CU(launch_prep(d, L->ws, x, x_dtype, n, nd.q8k, nd.q80, shared, s));
+        PHASE(L, 0, s, launch_prep(d, L->ws, x, x_dtype, n, nd.q8k, nd.q80, shared, s));
     }
-    if (routed) CU(launch_group(d, L->ws, idx, n, top_k, s));
-    CU(launch_gate_up(d, L->ws, n, top_k, routed, shared, s));
-    CU(launch_act_quant(d, L->ws, idx, n, top_k, routed, shared, s));
-    CU(launch_down(d, L->ws, w, n, top_k, routed, shared, s));
-    CU(launch_combine(d, L->ws, idx, n, top_k, routed, shared, out, out_dtype, s));
+    if (routed) PHASE(L, 3, s, launch_group(d, L->ws, idx, n, top_k, s));
+    PHASE(L, 4, s, launch_gate_up(d, L->ws, n, top_k, routed, shared, s));
+    PHASE(L, 5, s, launch_act_quant(d, L->ws, idx, n, top_k, routed, shared, s));
+    PHASE(L, 6, s, launch_down(d, L->ws, w, n, top_k, routed, shared, s));
+    PHASE(L, 7, s, launch_combine(d, L->ws, idx, n, top_k, routed, shared, out, out_dtype, s));
     return PMOE_OK;
 }
 
@@ -314,8 +342,47 @@ int pmoe_layer_destroy(pmoe_layer *L)
     DeviceGuard guard(L->device);
     cudaDeviceSynchronize();
     for (void *p : L->owned) cudaFree(p);
+    for (int i = 0; i < PMOE_TRACE_PHASES; i++) {
+        if (L->ev0[i]) cudaEventDestroy(L->ev0[i]);
+        if (L->ev1[i]) cudaEventDestroy(L->ev1[i]);
+    }
     delete L;
     return PMOE_OK;
+}
+
+int pmoe_layer_trace(pmoe_layer *L, int enable)
+{
+    if (!L) return fail(PMOE_ERR_INVALID_ARG, "layer is NULL");
+    DeviceGuard guard(L->device);
+    if (enable && !L->ev0[0]) {
+        for (int i = 0; i < PMOE_TRACE_PHASES; i++) {
+            CU(cudaEventCreate(&L->ev0[i]));
+            CU(cudaEventCreate(&L->ev1[i]));
+        }
+    }
+    L->trace = enable != 0;
+    for (bool &u : L->ev_used) u = false;
+    return PMOE_OK;
+}
+
+int pmoe_layer_trace_read(pmoe_layer *L, float *ms)
+{
+    if (!L || !ms) return fail(PMOE_ERR_INVALID_ARG, "layer / ms is NULL");
+    DeviceGuard guard(L->device);
+    for (int i = 0; i < PMOE_TRACE_PHASES; i++) {
+        ms[i] = 0.f;
+        if (!L->ev_used[i]) continue;
+        CU(cudaEventSynchronize(L->ev1[i]));
+        CU(cudaEventElapsedTime(&ms[i], L->ev0[i], L->ev1[i]));
+    }
+    return PMOE_OK;
+}
+
+const char *pmoe_trace_phase_name(int phase)
+{
+    static const char *names[PMOE_TRACE_PHASES] = {"prep", "router", "topk", "group",
+                                                   "gate_up", "act_quant", "down", "combine"};
+    return phase >= 0 && phase < PMOE_TRACE_PHASES ? names[phase] : "";
 }
 
 int pmoe_route(pmoe_layer *L, const void *x, int x_dtype, int n, float *logits_out, uint32_t *idx_out, float *w_out,
@@ -346,9 +413,10 @@ int pmoe_forward(pmoe_layer *L, const void *x, int x_dtype, int n, void *out, in
     uint32_t *idx = idx_out ? idx_out : L->ws.topk_idx;
     float *w = w_out ? w_out : L->ws.topk_w;
     Needs nd = input_needs(d, true, d.has_shared);
-    CU(launch_prep(d, L->ws, x, x_dtype, n, nd.q8k, nd.q80, d.has_shared, s));
-    CU(launch_router(d, L->ws, x, x_dtype, n, logits, s));
-    CU(launch_topk(d, L->ws, logits, n, idx, w, s));
+    for (bool &u : L->ev_used) u = false;
+    PHASE(L, 0, s, launch_prep(d, L->ws, x, x_dtype, n, nd.q8k, nd.q80, d.has_shared, s));
+    PHASE(L, 1, s, launch_router(d, L->ws, x, x_dtype, n, logits, s));
+    PHASE(L, 2, s, launch_topk(d, L->ws, logits, n, idx, w, s));
     return run_experts(L, x, x_dtype, idx, w, n, d.k, true, d.has_shared, true, out, out_dtype, s);
 }
 

@@ -84,6 +84,11 @@ __device__ inline void mbar_expect_tx(uint64_t *bar, uint32_t bytes)
                  : "memory");
 }
 
+__device__ inline void mbar_arrive(uint64_t *bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
 __device__ inline void fence_mbar_init()
 {
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -159,7 +164,10 @@ struct Groups {
     int *pairs;       // [n*k] pair ids (t*k + j) sorted by expert
     int *active;      // [E_local] local expert ids with count > 0, ascending
     int *n_active;    // [1]
+    int *cost_prefix; // [E_local + 1] exclusive prefix over active slots of ceil(count / GEMV_TG)
 };
+
+constexpr int GEMV_TG = 2;  // tokens one GEMV pass handles; the unit of the work partition
 
 // Everything a forward call needs, resolved to raw pointers.
 struct LayerDev {

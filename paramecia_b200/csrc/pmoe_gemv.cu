@@ -13,21 +13,25 @@
 // follow the reference CPU path: activations quantised to Q8_K / Q8_0, integer block dot
 // products, f32 scales and accumulation.
 //
-// Each CTA owns a slice of rows of one expert's matrix.  One elected thread streams the
-// slice into shared memory with bulk (TMA) copies -- every weight byte crosses HBM once,
-// in contiguous 16-byte-aligned runs -- while the warps fetch the quantised activations
-// of the expert's tokens into registers.  A lane owns a fixed slice of the reduction
-// dimension, so its activation registers serve every row of the slice; a row's partial
-// sums meet in a shuffle reduction.
+// The expert kernels are persistent: two CTAs per SM, each taking a contiguous range of
+// work items (an item = a few rows of one selected expert's matrix, ~36 KB).  One elected
+// thread streams the items through a three-stage shared-memory ring with bulk (TMA) copies,
+// so every weight byte crosses HBM once in contiguous 16-byte-aligned runs and two stages
+// are always in flight while the warps work on the third.  A lane owns a fixed slice of
+// the reduction dimension: the quantised activations of the expert's tokens stay in its
+// registers across all rows of the expert, and the partial sums of several rows and tokens
+// meet in one transposed shuffle reduction.
 #include "pmoe_common.cuh"
 #include "pmoe_quant.cuh"
 
 namespace pmoe {
 
-constexpr int GEMV_WARPS = 4;
-constexpr int GATE_UP_ROWS = 16;  // rows of gate AND of up per CTA
-constexpr int DOWN_ROWS = 64;
-constexpr int BULK_PIECE = 16384; // bytes per bulk copy
+constexpr int GEMV_WARPS = 8;
+constexpr int GEMV_THREADS = GEMV_WARPS * 32;
+constexpr int NSTAGE = 3;
+constexpr int STAGE_BYTES = 36864;  // one ring slot
+constexpr int BULK_PIECE = 12288;   // bytes per bulk copy
+constexpr int TG = GEMV_TG;         // tokens per pass (activation registers kept per lane)
 
 // ---------------------------------------------------------------- per-dtype lane units
 // A "unit" is the piece of a row one lane handles at a time.
@@ -107,108 +111,156 @@ template <> __device__ inline void load_act<PMOE_Q8_0>(const QAct &q, size_t row
 }
 
 // Decodes unit u of the row at `row` (shared memory) once and adds its dot product with
-// each token's activations to acc[].
-template <int DT, int TG>
-__device__ inline void unit_dot(const uint8_t *row, int u, const typename Tr<DT>::Act (&act)[TG], float (&acc)[TG]);
+// the activations of the first `cnt` tokens to acc[0..cnt).
+template <int DT> struct Dot;
 
-template <int TG> __device__ inline void unit_dot_q4k(const uint8_t *row, int u, const ActQ4K (&act)[TG], float (&acc)[TG])
-{
-    const uint8_t *blk = row + (u >> 2) * Q4_K_BYTES;
-    const int qd = u & 3;
-    const uint4 hdr = *reinterpret_cast<const uint4 *>(blk);
-    const uint4 qa = *reinterpret_cast<const uint4 *>(blk + 16 + 32 * qd);
-    const uint4 qb = *reinterpret_cast<const uint4 *>(blk + 32 + 32 * qd);
-    const float d = half_bits_to_float((uint16_t)(hdr.x & 0xffffu));
-    const float dmin = half_bits_to_float((uint16_t)(hdr.x >> 16));
-    const uint32_t s0 = hdr.y, s1 = hdr.z, s2 = hdr.w;
-    int sc0, sc1, m0, m1;  // 6-bit scale / min of sub-blocks 2*qd and 2*qd+1
-    if (qd < 2) {
-        const int sh = 16 * qd;
-        sc0 = (s0 >> sh) & 63; sc1 = (s0 >> (sh + 8)) & 63;
-        m0 = (s1 >> sh) & 63;  m1 = (s1 >> (sh + 8)) & 63;
-    } else {
-        const int sh = 16 * (qd - 2);
-        sc0 = ((s2 >> sh) & 0xF) | (((s0 >> (sh + 6)) & 3) << 4);
-        sc1 = ((s2 >> (sh + 8)) & 0xF) | (((s0 >> (sh + 14)) & 3) << 4);
-        m0 = ((s2 >> (sh + 4)) & 0xF) | (((s1 >> (sh + 6)) & 3) << 4);
-        m1 = ((s2 >> (sh + 12)) & 0xF) | (((s1 >> (sh + 14)) & 3) << 4);
-    }
-    const uint32_t w[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
-    uint32_t lo[8], hi[8];
-#pragma unroll
-    for (int i = 0; i < 8; i++) {
-        lo[i] = w[i] & 0x0F0F0F0Fu;
-        hi[i] = (w[i] >> 4) & 0x0F0F0F0Fu;
-    }
-#pragma unroll
-    for (int t = 0; t < TG; t++) {
-        int s_lo = 0, s_hi = 0;
-#pragma unroll
-        for (int i = 0; i < 8; i++) {
-            s_lo = __dp4a((int)lo[i], (int)act[t].a[i], s_lo);
-            s_hi = __dp4a((int)hi[i], (int)act[t].a[8 + i], s_hi);
+template <> struct Dot<PMOE_Q4_K> {
+    __device__ static inline void run(const uint8_t *row, int u, const ActQ4K (&act)[TG], int cnt, float *acc)
+    {
+        const uint8_t *blk = row + (u >> 2) * Q4_K_BYTES;
+        const int qd = u & 3;
+        const uint4 hdr = *reinterpret_cast<const uint4 *>(blk);
+        const uint4 qa = *reinterpret_cast<const uint4 *>(blk + 16 + 32 * qd);
+        const uint4 qb = *reinterpret_cast<const uint4 *>(blk + 32 + 32 * qd);
+        const float d = half_bits_to_float((uint16_t)(hdr.x & 0xffffu));
+        const float dmin = half_bits_to_float((uint16_t)(hdr.x >> 16));
+        const uint32_t s0 = hdr.y, s1 = hdr.z, s2 = hdr.w;
+        int sc0, sc1, m0, m1;  // 6-bit scale / min of sub-blocks 2*qd and 2*qd+1
+        if (qd < 2) {
+            const int sh = 16 * qd;
+            sc0 = (s0 >> sh) & 63; sc1 = (s0 >> (sh + 8)) & 63;
+            m0 = (s1 >> sh) & 63;  m1 = (s1 >> (sh + 8)) & 63;
+        } else {
+            const int sh = 16 * (qd - 2);
+            sc0 = ((s2 >> sh) & 0xF) | (((s0 >> (sh + 6)) & 3) << 4);
+            sc1 = ((s2 >> (sh + 8)) & 0xF) | (((s0 >> (sh + 14)) & 3) << 4);
+            m0 = ((s2 >> (sh + 4)) & 0xF) | (((s1 >> (sh + 6)) & 3) << 4);
+            m1 = ((s2 >> (sh + 12)) & 0xF) | (((s1 >> (sh + 14)) & 3) << 4);
         }
-        const int isum = sc0 * s_lo + sc1 * s_hi;
-        const int imin = m0 * act[t].bs_lo + m1 * act[t].bs_hi;
-        acc[t] += act[t].dx * (d * (float)isum - dmin * (float)imin);
+        const uint32_t w[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+#pragma unroll
+        for (int t = 0; t < TG; t++) {
+            if (t < cnt) {
+                int s_lo = 0, s_hi = 0;
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    s_lo = __dp4a((int)(w[i] & 0x0F0F0F0Fu), (int)act[t].a[i], s_lo);
+                    s_hi = __dp4a((int)((w[i] >> 4) & 0x0F0F0F0Fu), (int)act[t].a[8 + i], s_hi);
+                }
+                const int isum = sc0 * s_lo + sc1 * s_hi;
+                const int imin = m0 * act[t].bs_lo + m1 * act[t].bs_hi;
+                acc[t] += act[t].dx * (d * (float)isum - dmin * (float)imin);
+            }
+        }
     }
-}
+};
 
-template <int TG> __device__ inline void unit_dot_q6k(const uint8_t *row, int u, const ActQ16 (&act)[TG], float (&acc)[TG])
+template <> struct Dot<PMOE_Q6_K> {
+    __device__ static inline void run(const uint8_t *row, int u, const ActQ16 (&act)[TG], int cnt, float *acc)
+    {
+        const uint8_t *blk = row + (u >> 4) * Q6_K_BYTES;  // 2-byte aligned
+        const int half = (u >> 3) & 1, j = u & 7;
+        const uint32_t la = lds_u32_a2(blk + 64 * half + 4 * j);
+        const uint32_t lb = lds_u32_a2(blk + 64 * half + 32 + 4 * j);
+        const uint32_t h = lds_u32_a2(blk + 128 + 32 * half + 4 * j);
+        const int8_t *sc = reinterpret_cast<const int8_t *>(blk + 192 + 8 * half + (j >> 2));
+        const int c0 = sc[0], c1 = sc[2], c2 = sc[4], c3 = sc[6];
+        const float d = half_bits_to_float(*reinterpret_cast<const uint16_t *>(blk + 208));
+        const uint32_t w1 = __vsub4((la & 0x0F0F0F0Fu) | ((h << 4) & 0x30303030u), 0x20202020u);
+        const uint32_t w2 = __vsub4((lb & 0x0F0F0F0Fu) | ((h << 2) & 0x30303030u), 0x20202020u);
+        const uint32_t w3 = __vsub4(((la >> 4) & 0x0F0F0F0Fu) | (h & 0x30303030u), 0x20202020u);
+        const uint32_t w4 = __vsub4(((lb >> 4) & 0x0F0F0F0Fu) | ((h >> 2) & 0x30303030u), 0x20202020u);
+#pragma unroll
+        for (int t = 0; t < TG; t++) {
+            if (t < cnt) {
+                const int isum = c0 * __dp4a((int)w1, (int)act[t].a[0], 0) + c1 * __dp4a((int)w2, (int)act[t].a[1], 0) +
+                                 c2 * __dp4a((int)w3, (int)act[t].a[2], 0) + c3 * __dp4a((int)w4, (int)act[t].a[3], 0);
+                acc[t] += (d * act[t].dx) * (float)isum;
+            }
+        }
+    }
+};
+
+template <> struct Dot<PMOE_Q8_0> {
+    __device__ static inline void run(const uint8_t *row, int u, const ActQ16 (&act)[TG], int cnt, float *acc)
+    {
+        const uint8_t *blk = row + (u >> 1) * Q8_0_BYTES;  // 2-byte aligned
+        const int hf = u & 1;
+        const float d = half_bits_to_float(*reinterpret_cast<const uint16_t *>(blk));
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++) w[i] = lds_u32_a2(blk + 2 + 16 * hf + 4 * i);
+#pragma unroll
+        for (int t = 0; t < TG; t++) {
+            if (t < cnt) {
+                int isum = 0;
+#pragma unroll
+                for (int i = 0; i < 4; i++) isum = __dp4a((int)w[i], (int)act[t].a[i], isum);
+                acc[t] += (d * act[t].dx) * (float)isum;
+            }
+        }
+    }
+};
+
+// ---------------------------------------------------------------- compile-time shape of one kernel kind
+constexpr int cmin(int a, int b) { return a < b ? a : b; }
+constexpr int cmax(int a, int b) { return a > b ? a : b; }
+constexpr int floor_pow2(int v) { int p = 1; while (2 * p <= v) p *= 2; return p; }
+
+template <int DT, int NMAT> struct Cfg {
+    static constexpr int K = NMAT == 2 ? 2048 : 512;  // reduction length: H for gate/up, F for down
+    static constexpr int UNIT = Tr<DT>::UNIT;
+    static constexpr int UNITS = K / UNIT;
+    static constexpr int LPR = cmin(32, UNITS);       // lanes that share one row
+    static constexpr int UPL = UNITS / LPR;           // units per lane
+    static constexpr int GROUPS = 32 / LPR;           // rows a warp works on at once
+    static constexpr int ROW_BYTES = K / (DT == PMOE_Q8_0 ? QK8_0 : QK_K) *
+                                     (DT == PMOE_Q8_0 ? Q8_0_BYTES : DT == PMOE_Q4_K ? Q4_K_BYTES : Q6_K_BYTES);
+    static constexpr int ROWS = floor_pow2(STAGE_BYTES / (ROW_BYTES * NMAT));  // rows of each matrix per item
+    static constexpr int ITEM_BYTES = ROWS * ROW_BYTES;                        // per matrix
+    static constexpr int RPW = ROWS / GEMV_WARPS;     // rows per warp per item
+    static constexpr int PASSES = RPW / GROUPS;
+    static constexpr int RB = cmin(cmin(PASSES, 4), cmax(1, LPR / (NMAT * TG)));  // rows reduced together
+    static constexpr int V = NMAT * RB * TG;          // values per transposed reduction (<= LPR)
+    static_assert(RPW >= GROUPS && PASSES % RB == 0 && V <= LPR && ITEM_BYTES % 16 == 0, "bad tiling");
+};
+
+// Sums V per-lane values across the LPR lanes of a row group with LPR-1 shuffles in total:
+// every step halves the number of values a lane still carries.  The lane at in-group position
+// pl ends with the total of value index pl / (LPR / V).  The pairing order (LPR/2, ..., 1) is
+// that of a plain xor butterfly.
+template <int V, int LPR> __device__ inline float transposed_reduce(float (&v)[V], int lane)
 {
-    const uint8_t *blk = row + (u >> 4) * Q6_K_BYTES;  // 2-byte aligned
-    const int half = (u >> 3) & 1, j = u & 7;
-    const uint32_t la = lds_u32_a2(blk + 64 * half + 4 * j);
-    const uint32_t lb = lds_u32_a2(blk + 64 * half + 32 + 4 * j);
-    const uint32_t h = lds_u32_a2(blk + 128 + 32 * half + 4 * j);
-    const int8_t *sc = reinterpret_cast<const int8_t *>(blk + 192 + 8 * half + (j >> 2));
-    const int c0 = sc[0], c1 = sc[2], c2 = sc[4], c3 = sc[6];
-    const float d = half_bits_to_float(*reinterpret_cast<const uint16_t *>(blk + 208));
-    const uint32_t w1 = __vsub4((la & 0x0F0F0F0Fu) | ((h << 4) & 0x30303030u), 0x20202020u);
-    const uint32_t w2 = __vsub4((lb & 0x0F0F0F0Fu) | ((h << 2) & 0x30303030u), 0x20202020u);
-    const uint32_t w3 = __vsub4(((la >> 4) & 0x0F0F0F0Fu) | (h & 0x30303030u), 0x20202020u);
-    const uint32_t w4 = __vsub4(((lb >> 4) & 0x0F0F0F0Fu) | ((h >> 2) & 0x30303030u), 0x20202020u);
+    int cnt = V;
 #pragma unroll
-    for (int t = 0; t < TG; t++) {
-        const int isum = c0 * __dp4a((int)w1, (int)act[t].a[0], 0) + c1 * __dp4a((int)w2, (int)act[t].a[1], 0) +
-                         c2 * __dp4a((int)w3, (int)act[t].a[2], 0) + c3 * __dp4a((int)w4, (int)act[t].a[3], 0);
-        acc[t] += (d * act[t].dx) * (float)isum;
+    for (int step = LPR / 2; step >= 1; step >>= 1) {
+        if (cnt > 1) {
+            const int half = cnt / 2;
+            const bool up = (lane & step) != 0;
+#pragma unroll
+            for (int i = 0; i < V / 2; i++) {
+                if (i < half) {
+                    const float send = up ? v[i] : v[i + half];
+                    const float keep = up ? v[i + half] : v[i];
+                    v[i] = keep + __shfl_xor_sync(0xffffffffu, send, step);
+                }
+            }
+            cnt = half;
+        } else {
+            v[0] += __shfl_xor_sync(0xffffffffu, v[0], step);
+        }
     }
+    return v[0];
 }
-
-template <int TG> __device__ inline void unit_dot_q80(const uint8_t *row, int u, const ActQ16 (&act)[TG], float (&acc)[TG])
-{
-    const uint8_t *blk = row + (u >> 1) * Q8_0_BYTES;  // 2-byte aligned
-    const int hf = u & 1;
-    const float d = half_bits_to_float(*reinterpret_cast<const uint16_t *>(blk));
-    uint32_t w[4];
-#pragma unroll
-    for (int i = 0; i < 4; i++) w[i] = lds_u32_a2(blk + 2 + 16 * hf + 4 * i);
-#pragma unroll
-    for (int t = 0; t < TG; t++) {
-        int isum = 0;
-#pragma unroll
-        for (int i = 0; i < 4; i++) isum = __dp4a((int)w[i], (int)act[t].a[i], isum);
-        acc[t] += (d * act[t].dx) * (float)isum;
-    }
-}
-
-template <> __device__ inline void unit_dot<PMOE_Q4_K, 4>(const uint8_t *r, int u, const ActQ4K (&a)[4], float (&c)[4]) { unit_dot_q4k<4>(r, u, a, c); }
-template <> __device__ inline void unit_dot<PMOE_Q4_K, 8>(const uint8_t *r, int u, const ActQ4K (&a)[8], float (&c)[8]) { unit_dot_q4k<8>(r, u, a, c); }
-template <> __device__ inline void unit_dot<PMOE_Q6_K, 4>(const uint8_t *r, int u, const ActQ16 (&a)[4], float (&c)[4]) { unit_dot_q6k<4>(r, u, a, c); }
-template <> __device__ inline void unit_dot<PMOE_Q6_K, 8>(const uint8_t *r, int u, const ActQ16 (&a)[8], float (&c)[8]) { unit_dot_q6k<8>(r, u, a, c); }
-template <> __device__ inline void unit_dot<PMOE_Q8_0, 4>(const uint8_t *r, int u, const ActQ16 (&a)[4], float (&c)[4]) { unit_dot_q80<4>(r, u, a, c); }
-template <> __device__ inline void unit_dot<PMOE_Q8_0, 8>(const uint8_t *r, int u, const ActQ16 (&a)[8], float (&c)[8]) { unit_dot_q80<8>(r, u, a, c); }
 
 // ---------------------------------------------------------------- kernel arguments
 struct GemvArgs {
     const uint8_t *w0, *w1;    // routed matrices (gate, up) or (down, unused); expert e at + e*expert_bytes
     size_t expert_bytes;
     const uint8_t *sw0, *sw1;  // shared expert matrices
-    int K;                     // reduction length (H for gate/up, F for down)
     int rows_total;            // output length (F for gate/up, H for down)
-    int routed_slots;          // grid.y entries that serve routed experts
-    int has_shared;            // one more grid.y entry serves the shared expert
+    int routed;                // serve the routed experts listed in g
+    int has_shared;            // serve the shared expert
     int n, top_k;
     Groups g;
     QAct in_r, in_s;           // quantised activations matching the routed / shared weight type
@@ -218,158 +270,285 @@ struct GemvArgs {
     DevStatus *status;
 };
 
-// UPL = units per lane (compile-time bound; K <= UPL*32*UNIT), TG = tokens per pass.
-template <int DT, int NMAT, int UPL, int TG, int ROWS>
-__device__ inline void gemv_cta(const GemvArgs &A, uint8_t *smem, uint64_t *bar, bool is_shared, const uint8_t *wsrc0,
-                                const uint8_t *wsrc1, int m, const int *list, const QAct &in)
+
+// Token rows of one pass.
+struct Pass {
+    int cnt;
+    int out_row[TG];
+    float scale[TG];
+};
+
+template <int DT, int NMAT>
+__device__ inline void load_pass(const GemvArgs &A, bool is_shared, const int *list, int m, int t0, const QAct &in,
+                                 int ul, Pass &P, typename Tr<DT>::Act (&act)[Cfg<DT, NMAT>::UPL][TG])
 {
-    using Act = typename Tr<DT>::Act;
-    constexpr int UNIT = Tr<DT>::UNIT;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int K = A.K;
-    const uint32_t rb = (uint32_t)row_bytes(DT, K);
-    const uint32_t slice = rb * ROWS;  // bytes of one matrix slice
-    const int chunk = blockIdx.x;
-
-    // ---- stream the weight slice(s) into shared memory
-    if (threadIdx.x == 0) {
-        mbar_init(bar, 1);
-        fence_mbar_init();
-    }
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        mbar_expect_tx(bar, slice * NMAT);
+    using C = Cfg<DT, NMAT>;
+    P.cnt = m - t0 < TG ? m - t0 : TG;
 #pragma unroll
-        for (int mat = 0; mat < NMAT; mat++) {
-            const uint8_t *src = (mat == 0 ? wsrc0 : wsrc1) + (size_t)chunk * slice;
-            uint8_t *dst = smem + mat * slice;
-            for (uint32_t off = 0; off < slice; off += BULK_PIECE) {
-                uint32_t sz = slice - off < (uint32_t)BULK_PIECE ? slice - off : (uint32_t)BULK_PIECE;
-                bulk_g2s(dst + off, src + off, sz, bar);
+    for (int t = 0; t < TG; t++) {
+        P.out_row[t] = -1;
+        P.scale[t] = 0.f;
+        if (t < P.cnt) {
+            int in_row;
+            if (is_shared) {
+                const int tok = t0 + t;
+                P.out_row[t] = A.n * A.top_k + tok;
+                in_row = NMAT == 2 ? tok : P.out_row[t];
+                if (NMAT == 1) P.scale[t] = A.scale_s[tok];
+            } else {
+                const int p = list[t0 + t];
+                P.out_row[t] = p;
+                in_row = NMAT == 2 ? p / A.top_k : p;
+                if (NMAT == 1) P.scale[t] = A.scale_r[p];
             }
+#pragma unroll
+            for (int i = 0; i < C::UPL; i++) load_act<DT>(in, (size_t)in_row, C::K, i * C::LPR + ul, act[i][t]);
+        } else {
+#pragma unroll
+            for (int i = 0; i < C::UPL; i++) zero_act<DT>(act[i][t]);
         }
     }
-
-    const int units = K / UNIT;
-    const int lpr = units < 32 ? units : 32;      // lanes per row (power of two)
-    const int rpp = 32 / lpr;                     // rows per warp pass
-    const int sub = lane / lpr, ul = lane % lpr;
-    constexpr int ROWS_PER_WARP = ROWS / GEMV_WARPS;
-    bool waited = false;
-
-    for (int t0 = 0; t0 < m; t0 += TG) {
-        // ---- this pass's token rows
-        Act act[UPL][TG];
-        int out_row[TG];
-        float scale[TG];
-#pragma unroll
-        for (int t = 0; t < TG; t++) {
-            const bool valid = t0 + t < m;
-            int in_row = 0;
-            out_row[t] = -1;
-            scale[t] = 0.f;
-            if (valid) {
-                if (is_shared) {
-                    const int tok = t0 + t;
-                    out_row[t] = A.n * A.top_k + tok;
-                    in_row = NMAT == 2 ? tok : out_row[t];
-                    if (NMAT == 1) scale[t] = A.scale_s[tok];
-                } else {
-                    const int p = list[t0 + t];
-                    out_row[t] = p;
-                    in_row = NMAT == 2 ? p / A.top_k : p;
-                    if (NMAT == 1) scale[t] = A.scale_r[p];
-                }
-            }
-#pragma unroll
-            for (int i = 0; i < UPL; i++) {
-                const int u = i * lpr + ul;
-                if (valid && u < units) load_act<DT>(in, (size_t)in_row, K, u, act[i][t]);
-                else zero_act<DT>(act[i][t]);
-            }
-        }
-        if (!waited) {
-            if (!mbar_wait(bar, 0)) {
-                set_status(A.status, PMOE_ERR_TIMEOUT, NMAT, chunk);
-                return;
-            }
-            waited = true;
-        }
-        // ---- rows of this warp
-        for (int r0 = 0; r0 < ROWS_PER_WARP; r0 += rpp) {
-            const int rloc = r0 + sub;
-            const bool row_ok = rloc < ROWS_PER_WARP;
-            const int row = warp * ROWS_PER_WARP + (row_ok ? rloc : 0);
-            float acc[NMAT][TG];
-#pragma unroll
-            for (int mat = 0; mat < NMAT; mat++) {
-#pragma unroll
-                for (int t = 0; t < TG; t++) acc[mat][t] = 0.f;
-                const uint8_t *rp = smem + mat * slice + (size_t)row * rb;
-#pragma unroll
-                for (int i = 0; i < UPL; i++) {
-                    const int u = i * lpr + ul;
-                    if (u < units) unit_dot<DT, TG>(rp, u, act[i], acc[mat]);
-                }
-#pragma unroll
-                for (int t = 0; t < TG; t++) {
-                    float v = acc[mat][t];
-                    for (int s = lpr >> 1; s >= 1; s >>= 1) v += __shfl_xor_sync(0xffffffffu, v, s);
-                    acc[mat][t] = v;
-                }
-            }
-            if (ul == 0 && row_ok) {
-                const int orow = chunk * ROWS + row;
-#pragma unroll
-                for (int t = 0; t < TG; t++) {
-                    if (out_row[t] < 0) continue;
-                    float v;
-                    if (NMAT == 2) {
-                        const float g = acc[0][t];
-                        v = g / (1.f + expf(-g)) * acc[NMAT - 1][t];
-                    } else {
-                        v = acc[0][t] * scale[t];
-                    }
-                    A.out[(size_t)out_row[t] * A.rows_total + orow] = v;
-                }
-            }
-        }
-    }
-    // every issued copy has landed before the CTA may exit
-    if (!waited && !mbar_wait(bar, 0)) set_status(A.status, PMOE_ERR_TIMEOUT, NMAT, chunk);
 }
 
-template <int DT> struct Upl {  // units per lane at the largest supported K for the kernel kind
-    static constexpr int gate_up = (2048 / Tr<DT>::UNIT) / 32;                        // K <= 2048
-    static constexpr int down = (512 / Tr<DT>::UNIT) / 32 > 0 ? (512 / Tr<DT>::UNIT) / 32 : 1;  // K <= 512
+// All rows of one item (in shared memory) against one pass of tokens.
+template <int DT, int NMAT>
+__device__ inline void compute_item(const GemvArgs &A, const uint8_t *stage, int chunk, const Pass &P,
+                                    const typename Tr<DT>::Act (&act)[Cfg<DT, NMAT>::UPL][TG], int warp, int lane)
+{
+    using C = Cfg<DT, NMAT>;
+    const int grp = lane / C::LPR, ul = lane % C::LPR;
+#pragma unroll 1
+    for (int b0 = 0; b0 < C::PASSES; b0 += C::RB) {
+        float acc[C::V];
+#pragma unroll
+        for (int i = 0; i < C::V; i++) acc[i] = 0.f;
+#pragma unroll
+        for (int rb = 0; rb < C::RB; rb++) {
+            const int row = warp * C::RPW + (b0 + rb) * C::GROUPS + grp;
+#pragma unroll
+            for (int mat = 0; mat < NMAT; mat++) {
+                const uint8_t *rp = stage + mat * C::ITEM_BYTES + row * C::ROW_BYTES;
+#pragma unroll
+                for (int i = 0; i < C::UPL; i++) {
+                    Dot<DT>::run(rp, i * C::LPR + ul, act[i], P.cnt, acc + (mat * C::RB + rb) * TG);
+                    // keeps the compiler from hoisting every unit's loads at once (register pressure)
+                    if (C::UPL > 1) asm volatile("" ::: "memory");
+                }
+            }
+        }
+        float v = transposed_reduce<C::V, C::LPR>(acc, lane);
+        constexpr int DUP = C::LPR / C::V;  // lanes holding the same total
+        const int vi = ul / DUP;
+        const int t = vi % TG, rb = (vi / TG) % C::RB, mat = vi / (TG * C::RB);
+        if (NMAT == 2) {
+            const float other = __shfl_xor_sync(0xffffffffu, v, C::LPR / 2);  // up total sits LPR/2 lanes away
+            v = v / (1.f + expf(-v)) * other;                                 // silu(gate) * up
+        }
+        const int row = chunk * C::ROWS + warp * C::RPW + (b0 + rb) * C::GROUPS + grp;
+        // out_row[t] via a small select chain (t is lane-dependent)
+        int orow = -1;
+        float sc = 0.f;
+#pragma unroll
+        for (int q = 0; q < TG; q++)
+            if (q == t) { orow = P.out_row[q]; sc = P.scale[q]; }
+        if (ul % DUP == 0 && mat == 0 && orow >= 0)
+            A.out[(size_t)orow * A.rows_total + row] = NMAT == 2 ? v : v * sc;
+    }
+}
+
+// ---------------------------------------------------------------- work partition
+// Items are ordered (slot 0 chunk 0, slot 0 chunk 1, ..., slot 1 chunk 0, ...); slot n_active is
+// the shared expert.  An item of a slot with m tokens costs ceil(m / TG) passes, and the CTAs
+// split the total cost evenly: a CTA takes the items whose starting cost position falls into
+// its share.  The per-slot cost prefix comes from the grouping kernel.
+struct Cursor {
+    int slot, chunk;
 };
+
+struct Plan {
+    int n_active, has_shared, cpe_r, cpe_s, cost_shared;
+    const int *prefix;  // [n_active + 1] in shared memory
+
+    __device__ inline int cpe(int slot) const { return slot < n_active ? cpe_r : cpe_s; }
+    __device__ inline long routed_cost() const { return (long)cpe_r * prefix[n_active]; }
+    __device__ inline long total_cost() const { return routed_cost() + (has_shared ? (long)cpe_s * cost_shared : 0); }
+    __device__ inline Cursor end() const { return Cursor{n_active + (has_shared ? 1 : 0), 0}; }
+    __device__ inline void advance(Cursor &c) const
+    {
+        if (++c.chunk == cpe(c.slot)) { c.slot++; c.chunk = 0; }
+    }
+    __device__ inline int index(Cursor c) const  // items before c
+    {
+        return c.slot <= n_active ? c.slot * cpe_r + c.chunk : n_active * cpe_r + cpe_s;
+    }
+    // first item whose starting cost position is >= p
+    __device__ inline Cursor find(long p) const
+    {
+        if (p >= total_cost()) return end();
+        const long rc = routed_cost();
+        if (p >= rc) {
+            const int chunk = (int)((p - rc + cost_shared - 1) / cost_shared);
+            return chunk >= cpe_s ? end() : Cursor{n_active, chunk};
+        }
+        int lo = 0, hi = n_active - 1;  // largest slot with cpe_r * prefix[slot] <= p
+        while (lo < hi) {
+            const int mid = (lo + hi + 1) >> 1;
+            if ((long)cpe_r * prefix[mid] <= p) lo = mid; else hi = mid - 1;
+        }
+        const int c = prefix[lo + 1] - prefix[lo];
+        const int chunk = (int)((p - (long)cpe_r * prefix[lo] + c - 1) / c);
+        if (chunk < cpe_r) return Cursor{lo, chunk};
+        return lo + 1 < n_active || has_shared ? Cursor{lo + 1, 0} : end();
+    }
+};
+
+__device__ inline uint8_t *ring_stage(uint8_t *base, int s) { return base + 128 + s * STAGE_BYTES; }
+__device__ inline uint64_t *ring_full(uint8_t *base, int s) { return reinterpret_cast<uint64_t *>(base) + s; }
+__device__ inline uint64_t *ring_empty(uint8_t *base, int s) { return reinterpret_cast<uint64_t *>(base) + NSTAGE + s; }
+
+// Thread 0's side of the ring: issues the bulk copies of its next item once the warps have
+// released the slot's previous contents.
+template <int DT_R, int DT_S1, int NMAT> struct Producer {
+    using CR = Cfg<DT_R, NMAT>;
+    using CS = Cfg<DT_S1, NMAT>;
+    const GemvArgs &A;
+    const Plan &plan;
+    uint8_t *ring;
+    Cursor cur;
+    int issued, n_items;
+
+    __device__ inline bool issue_next()
+    {
+        if (issued >= n_items) return true;
+        const int it = issued++;
+        const int s = it % NSTAGE;
+        const uint32_t use = (uint32_t)(it / NSTAGE);
+        if (use > 0 && !mbar_wait(ring_empty(ring, s), (use - 1) & 1)) {
+            set_status(A.status, PMOE_ERR_TIMEOUT, 20 + NMAT, it);
+            return false;
+        }
+        const uint8_t *src0, *src1;
+        uint32_t bytes;
+        if (cur.slot < plan.n_active) {
+            const size_t off = (size_t)A.g.active[cur.slot] * A.expert_bytes + (size_t)cur.chunk * CR::ITEM_BYTES;
+            src0 = A.w0 + off;
+            src1 = A.w1 + off;
+            bytes = CR::ITEM_BYTES;
+        } else {
+            const size_t off = (size_t)cur.chunk * CS::ITEM_BYTES;
+            src0 = A.sw0 + off;
+            src1 = A.sw1 + off;
+            bytes = CS::ITEM_BYTES;
+        }
+        plan.advance(cur);
+        uint64_t *full = ring_full(ring, s);
+        mbar_expect_tx(full, bytes * NMAT);
+#pragma unroll
+        for (int mat = 0; mat < NMAT; mat++) {
+            const uint8_t *src = mat == 0 ? src0 : src1;
+            uint8_t *dst = ring_stage(ring, s) + mat * bytes;
+            for (uint32_t off = 0; off < bytes; off += BULK_PIECE)
+                bulk_g2s(dst + off, src + off, bytes - off < (uint32_t)BULK_PIECE ? bytes - off : (uint32_t)BULK_PIECE,
+                         full);
+        }
+        return true;
+    }
+};
+
+// The CTA's items of one kind (routed or shared), consumed in order from `cur` while the slot
+// stays below `slot_end`.  Before each item thread 0 tops the ring up, so NSTAGE-1 items stay
+// in flight.  `it` numbers the CTA's items; the ring position follows from it.
+template <int DT, int NMAT, typename Prod>
+__device__ inline bool run_items(const GemvArgs &A, uint8_t *ring, const Plan &plan, Prod &prod, bool is_shared,
+                                 Cursor &cur, int slot_end, int &it, int n_items, const QAct &in, int warp, int lane)
+{
+    using C = Cfg<DT, NMAT>;
+    using Act = typename Tr<DT>::Act;
+    const int ul = lane % C::LPR;
+    int cur_slot = -1, m = 0;
+    const int *list = nullptr;
+    Pass P;
+    Act act[C::UPL][TG];
+    while (it < n_items && cur.slot < slot_end) {
+        if (threadIdx.x == 0 && !prod.issue_next()) return false;
+        __syncwarp();
+        const int s = it % NSTAGE;
+        const uint32_t use = (uint32_t)(it / NSTAGE);
+        if (cur.slot != cur_slot) {
+            cur_slot = cur.slot;
+            if (is_shared) {
+                m = A.n;
+            } else {
+                const int e = A.g.active[cur.slot];
+                m = A.g.count[e];
+                list = A.g.pairs + A.g.offset[e];
+            }
+            if (m <= TG) load_pass<DT, NMAT>(A, is_shared, list, m, 0, in, ul, P, act);
+        }
+        if (!mbar_wait(ring_full(ring, s), use & 1)) {
+            set_status(A.status, PMOE_ERR_TIMEOUT, 10 + NMAT, it);
+            return false;
+        }
+        const uint8_t *stage = ring_stage(ring, s);
+        if (m <= TG) {
+            compute_item<DT, NMAT>(A, stage, cur.chunk, P, act, warp, lane);
+        } else {
+            for (int t0 = 0; t0 < m; t0 += TG) {
+                load_pass<DT, NMAT>(A, is_shared, list, m, t0, in, ul, P, act);
+                compute_item<DT, NMAT>(A, stage, cur.chunk, P, act, warp, lane);
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(ring_empty(ring, s));
+        plan.advance(cur);
+        it++;
+    }
+    return true;
+}
 
 // DT_S == 0 compiles the kernel without a shared-expert branch.
 template <int DT_R, int DT_S, int NMAT>
-__global__ void __launch_bounds__(GEMV_WARPS * 32) k_expert_gemv(const GemvArgs A)
+__global__ void __launch_bounds__(GEMV_THREADS, 2) k_expert_gemv(const GemvArgs A)
 {
-    extern __shared__ __align__(128) uint8_t smem_raw[];
-    uint64_t *bar = reinterpret_cast<uint64_t *>(smem_raw);
-    uint8_t *smem = smem_raw + 128;
-    constexpr int ROWS = NMAT == 2 ? GATE_UP_ROWS : DOWN_ROWS;
-    // tokens per pass: bounded by the activation registers a lane keeps (64 per token group)
-    constexpr int TG_R = (NMAT == 2 || DT_R == PMOE_Q4_K) ? 4 : 8;
-    constexpr int TG_S = (NMAT == 2 || DT_S == PMOE_Q4_K) ? 4 : 8;
-    const int slot = blockIdx.y;
-    if (slot >= A.routed_slots) {
-        if constexpr (DT_S != 0) {
-            constexpr int UPL = NMAT == 2 ? Upl<DT_S>::gate_up : Upl<DT_S>::down;
-            gemv_cta<DT_S, NMAT, UPL, TG_S, ROWS>(A, smem, bar, true, A.sw0, A.sw1, A.n, nullptr, A.in_s);
+    extern __shared__ __align__(128) uint8_t ring[];
+    __shared__ int s_prefix[1025];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    constexpr int DT_S1 = DT_S ? DT_S : DT_R;
+    using CR = Cfg<DT_R, NMAT>;
+    using CS = Cfg<DT_S1, NMAT>;
+    Plan plan;
+    plan.n_active = A.routed ? *A.g.n_active : 0;
+    plan.has_shared = (DT_S != 0 && A.has_shared) ? 1 : 0;
+    plan.cpe_r = A.rows_total / CR::ROWS;
+    plan.cpe_s = A.rows_total / CS::ROWS;
+    plan.cost_shared = (A.n + TG - 1) / TG;
+    plan.prefix = s_prefix;
+    for (int i = threadIdx.x; i <= plan.n_active; i += GEMV_THREADS) s_prefix[i] = plan.n_active ? A.g.cost_prefix[i] : 0;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < NSTAGE; s++) {
+            mbar_init(ring_full(ring, s), 1);
+            mbar_init(ring_empty(ring, s), GEMV_WARPS);
         }
-        return;
+        fence_mbar_init();
     }
-    if (slot >= *A.g.n_active) return;
-    const int e = A.g.active[slot];
-    const int m = A.g.count[e];
-    const int *list = A.g.pairs + A.g.offset[e];
-    constexpr int UPL = NMAT == 2 ? Upl<DT_R>::gate_up : Upl<DT_R>::down;
-    gemv_cta<DT_R, NMAT, UPL, TG_R, ROWS>(A, smem, bar, false, A.w0 + (size_t)e * A.expert_bytes,
-                                        A.w1 + (size_t)e * A.expert_bytes, m, list, A.in_r);
+    __syncthreads();
+
+    const long total = plan.total_cost();
+    Cursor cur = plan.find(total * blockIdx.x / gridDim.x);
+    const Cursor last = plan.find(total * (blockIdx.x + 1) / gridDim.x);
+    const int n_items = plan.index(last) - plan.index(cur);
+    if (n_items <= 0) return;
+
+    Producer<DT_R, DT_S1, NMAT> prod{A, plan, ring, cur, 0, n_items};
+    if (threadIdx.x == 0)
+        for (int i = 0; i < NSTAGE - 1; i++) prod.issue_next();  // run_items tops up one per item
+
+    int it = 0;
+    bool ok = run_items<DT_R, NMAT>(A, ring, plan, prod, false, cur, plan.n_active, it, n_items, A.in_r, warp, lane);
+    if constexpr (DT_S != 0) {
+        if (ok) run_items<DT_S, NMAT>(A, ring, plan, prod, true, cur, plan.n_active + 1, it, n_items, A.in_s, warp, lane);
+    }
 }
 
 // ---------------------------------------------------------------- host-side dispatch
@@ -379,67 +558,58 @@ bool gemv_supported(int dtype, int K, int rows, const char **why)
         *why = "expert weights must be Q4_K, Q6_K or Q8_0";
         return false;
     }
-    if (K < 256 || K > 2048 || (K & (K - 1))) {
-        *why = "reduction length must be a power of two in [256, 2048]";
-        return false;
-    }
-    if (rows % DOWN_ROWS) {
-        *why = "output length must be a multiple of 64";
+    if (!((K == 2048 && rows == 512) || (K == 512 && rows == 2048))) {
+        *why = "this build serves hidden 2048 with expert intermediate 512";
         return false;
     }
     return true;
 }
 
-static size_t gemv_smem(int dt, int K, int nmat)
-{
-    if (!dt) return 0;
-    return row_bytes(dt, K) * (nmat == 2 ? GATE_UP_ROWS * 2 : DOWN_ROWS);
-}
+static int g_sm_count = 0;
 
 template <int DT_R, int DT_S, int NMAT>
-static cudaError_t launch_gemv_t(const GemvArgs &A, int dt_s_rt, dim3 grid, cudaStream_t s)
+static cudaError_t launch_gemv_t(const GemvArgs &A, cudaStream_t s)
 {
-    size_t smem = 128 + (gemv_smem(DT_R, A.K, NMAT) > gemv_smem(dt_s_rt, A.K, NMAT) ? gemv_smem(DT_R, A.K, NMAT)
-                                                                                     : gemv_smem(dt_s_rt, A.K, NMAT));
+    constexpr size_t smem = 128 + (size_t)NSTAGE * STAGE_BYTES;
     auto kern = k_expert_gemv<DT_R, DT_S, NMAT>;
-    static size_t configured = 0;  // per instantiation
-    if (smem > configured) {
+    static bool configured = false;  // per instantiation
+    if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
-        configured = smem;
+        configured = true;
     }
-    kern<<<grid, GEMV_WARPS * 32, smem, s>>>(A);
+    if (!g_sm_count) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev);
+        if (g_sm_count <= 0) g_sm_count = 148;
+    }
+    kern<<<2 * g_sm_count, GEMV_THREADS, smem, s>>>(A);
     count_launch();
     return cudaGetLastError();
 }
 
 template <int DT_R, int NMAT>
-static cudaError_t launch_gemv_s(const GemvArgs &A, int dt_s, dim3 grid, cudaStream_t s)
+static cudaError_t launch_gemv_s(const GemvArgs &A, int dt_s, cudaStream_t s)
 {
     switch (dt_s) {
-    case 0: return launch_gemv_t<DT_R, 0, NMAT>(A, 0, grid, s);
-    case PMOE_Q4_K: return launch_gemv_t<DT_R, PMOE_Q4_K, NMAT>(A, dt_s, grid, s);
-    case PMOE_Q6_K: return launch_gemv_t<DT_R, PMOE_Q6_K, NMAT>(A, dt_s, grid, s);
-    case PMOE_Q8_0: return launch_gemv_t<DT_R, PMOE_Q8_0, NMAT>(A, dt_s, grid, s);
+    case 0: return launch_gemv_t<DT_R, 0, NMAT>(A, s);
+    case PMOE_Q4_K: return launch_gemv_t<DT_R, PMOE_Q4_K, NMAT>(A, s);
+    case PMOE_Q6_K: return launch_gemv_t<DT_R, PMOE_Q6_K, NMAT>(A, s);
+    case PMOE_Q8_0: return launch_gemv_t<DT_R, PMOE_Q8_0, NMAT>(A, s);
     }
     return cudaErrorInvalidValue;
 }
 
 template <int NMAT>
-static cudaError_t launch_gemv(const GemvArgs &A, int dt_r, int dt_s, dim3 grid, cudaStream_t s)
+static cudaError_t launch_gemv(const GemvArgs &A, int dt_r, int dt_s, cudaStream_t s)
 {
     switch (dt_r) {
-    case PMOE_Q4_K: return launch_gemv_s<PMOE_Q4_K, NMAT>(A, dt_s, grid, s);
-    case PMOE_Q6_K: return launch_gemv_s<PMOE_Q6_K, NMAT>(A, dt_s, grid, s);
-    case PMOE_Q8_0: return launch_gemv_s<PMOE_Q8_0, NMAT>(A, dt_s, grid, s);
+    case PMOE_Q4_K: return launch_gemv_s<PMOE_Q4_K, NMAT>(A, dt_s, s);
+    case PMOE_Q6_K: return launch_gemv_s<PMOE_Q6_K, NMAT>(A, dt_s, s);
+    case PMOE_Q8_0: return launch_gemv_s<PMOE_Q8_0, NMAT>(A, dt_s, s);
     }
     return cudaErrorInvalidValue;
-}
-
-static int routed_slots_for(const LayerDev &L, int n, int top_k)
-{
-    long pairs = (long)n * top_k;
-    return (int)(pairs < L.E_local ? pairs : L.E_local);
 }
 
 cudaError_t launch_gate_up(const LayerDev &L, const Workspace &ws, int n, int top_k, bool routed, bool shared,
@@ -450,19 +620,16 @@ cudaError_t launch_gate_up(const LayerDev &L, const Workspace &ws, int n, int to
     A.w0 = L.gate_exps; A.w1 = L.up_exps;
     A.expert_bytes = row_bytes(L.gate_dtype, L.H) * L.F;
     A.sw0 = L.sh_gate; A.sw1 = L.sh_up;
-    A.K = L.H; A.rows_total = L.F;
-    A.routed_slots = routed ? routed_slots_for(L, n, top_k) : 0;
-    A.has_shared = shared;
+    A.rows_total = L.F;
+    A.routed = routed; A.has_shared = shared;
     A.n = n; A.top_k = top_k;
     A.g = ws.groups;
     A.in_r = is_kquant(L.gate_dtype) ? ws.x_q8k : ws.x_q80;
     A.in_s = is_kquant(L.sh_gate_dtype) ? ws.x_q8k : ws.x_q80;
     A.out = ws.act;
     A.status = ws.status;
-    dim3 grid(L.F / GATE_UP_ROWS, A.routed_slots + (shared ? 1 : 0));
-    // a kernel without routed slots still needs a routed type to instantiate; reuse the shared one
-    int dt_r = routed ? L.gate_dtype : L.sh_gate_dtype;
-    return launch_gemv<2>(A, dt_r, shared ? L.sh_gate_dtype : 0, grid, s);
+    // a kernel without routed items still needs a routed type to instantiate; reuse the shared one
+    return launch_gemv<2>(A, routed ? L.gate_dtype : L.sh_gate_dtype, shared ? L.sh_gate_dtype : 0, s);
 }
 
 cudaError_t launch_down(const LayerDev &L, const Workspace &ws, const float *w, int n, int top_k, bool routed,
@@ -473,9 +640,8 @@ cudaError_t launch_down(const LayerDev &L, const Workspace &ws, const float *w, 
     A.w0 = L.down_exps; A.w1 = nullptr;
     A.expert_bytes = row_bytes(L.down_dtype, L.F) * L.H;
     A.sw0 = L.sh_down; A.sw1 = nullptr;
-    A.K = L.F; A.rows_total = L.H;
-    A.routed_slots = routed ? routed_slots_for(L, n, top_k) : 0;
-    A.has_shared = shared;
+    A.rows_total = L.H;
+    A.routed = routed; A.has_shared = shared;
     A.n = n; A.top_k = top_k;
     A.g = ws.groups;
     A.in_r = is_kquant(L.down_dtype) ? ws.act_q8k : ws.act_q80;
@@ -484,9 +650,7 @@ cudaError_t launch_down(const LayerDev &L, const Workspace &ws, const float *w, 
     A.scale_r = w;
     A.scale_s = ws.sh_sigmoid;
     A.status = ws.status;
-    dim3 grid(L.H / DOWN_ROWS, A.routed_slots + (shared ? 1 : 0));
-    int dt_r = routed ? L.down_dtype : L.sh_down_dtype;
-    return launch_gemv<1>(A, dt_r, shared ? L.sh_down_dtype : 0, grid, s);
+    return launch_gemv<1>(A, routed ? L.down_dtype : L.sh_down_dtype, shared ? L.sh_down_dtype : 0, s);
 }
 
 // ---------------------------------------------------------------- re-quantise the activated rows

@@ -297,6 +297,16 @@ class MoeBlock:
                                       None if w is None else w.data_ptr(), _stream_ptr(self.device)))
         return (out_host, (logits, idx, w)) if with_stats else out_host
 
+    def trace(self, enable: bool = True):
+        """Turns per-phase CUDA-event timing of forward calls on or off."""
+        check(lib().pmoe_layer_trace(self._h, 1 if enable else 0))
+
+    def trace_read(self):
+        """Milliseconds per phase of the last traced forward call: {phase name: ms}."""
+        ms = (C.c_float * _lib.TRACE_PHASES)()
+        check(lib().pmoe_layer_trace_read(self._h, ms))
+        return {lib().pmoe_trace_phase_name(i).decode(): float(ms[i]) for i in range(_lib.TRACE_PHASES)}
+
     def status(self):
         """Synchronises and raises PmoeError if a kernel recorded a timeout or a bad index."""
         check(lib().pmoe_layer_status(self._h, _stream_ptr(self.device)))

@@ -49,7 +49,7 @@ def test_dequantize_bit_exact(dtype):
 
 @pytest.mark.parametrize("n,xdtype", [(1, torch.float32), (7, torch.bfloat16), (64, torch.float32), (200, torch.bfloat16)])
 def test_router_bit_exact(n, xdtype):
-    t = synth.make_layer(E=512, k=10, preset="q8_0", seed=3, shared=False, H=2048, F=256)
+    t = synth.make_layer(E=512, k=10, preset="q8_0", seed=3, shared=False, H=2048, F=512)
     blk = synth.make_block(t, DEV, max_tokens=256)
     x = seeded_x(n, 2048, 11, xdtype)
     logits, w, idx = blk.route(x.to(DEV))
@@ -65,7 +65,7 @@ def test_router_bit_exact(n, xdtype):
 
 def test_router_bias_and_ties():
     # identical router rows give exactly equal probabilities: the lower expert id must win
-    t = synth.make_layer(E=64, k=4, preset="q8_0", seed=5, shared=False, F=256, zipf=True)
+    t = synth.make_layer(E=64, k=4, preset="q8_0", seed=5, shared=False, F=512, zipf=True)
     t["router_w"][10] = t["router_w"][3]
     t["router_w"][40] = t["router_w"][3]
     t["router_bias"][10] = t["router_bias"][3]
