@@ -146,6 +146,34 @@ __device__ inline float load_as_float(const __nv_bfloat16 *p, size_t i) { return
 __device__ inline void store_from_float(float *p, size_t i, float v) { p[i] = v; }
 __device__ inline void store_from_float(__nv_bfloat16 *p, size_t i, float v) { p[i] = __float2bfloat16_rn(v); }
 
+// Sums V per-lane values across the LPR lanes of a row group with LPR-1 shuffles in total:
+// every step halves the number of values a lane still carries.  The lane at in-group position
+// pl ends with the total of value index pl / (LPR / V).  The pairing order (LPR/2, ..., 1) is
+// that of a plain xor butterfly.
+template <int V, int LPR> __device__ inline float transposed_reduce(float (&v)[V], int lane)
+{
+    int cnt = V;
+#pragma unroll
+    for (int step = LPR / 2; step >= 1; step >>= 1) {
+        if (cnt > 1) {
+            const int half = cnt / 2;
+            const bool up = (lane & step) != 0;
+#pragma unroll
+            for (int i = 0; i < V / 2; i++) {
+                if (i < half) {
+                    const float send = up ? v[i] : v[i + half];
+                    const float keep = up ? v[i + half] : v[i];
+                    v[i] = keep + __shfl_xor_sync(0xffffffffu, send, step);
+                }
+            }
+            cnt = half;
+        } else {
+            v[0] += __shfl_xor_sync(0xffffffffu, v[0], step);
+        }
+    }
+    return v[0];
+}
+
 // ---------------------------------------------------------------- activation blocks in the workspace
 // Q8_K rows: qs int8 [rows, K], d f32 [rows, K/256], bsums i16 [rows, K/16]
 // Q8_0 rows: qs int8 [rows, K], d f32 [rows, K/32] (the f16-rounded scale, widened)

@@ -21,13 +21,14 @@
 // the reduction dimension: the quantised activations of the expert's tokens stay in its
 // registers across all rows of the expert, and the partial sums of several rows and tokens
 // meet in one transposed shuffle reduction.
+#include <cstdlib>
 #include "pmoe_common.cuh"
 #include "pmoe_quant.cuh"
 
 namespace pmoe {
 
 constexpr int GEMV_WARPS = 8;
-constexpr int GEMV_THREADS = GEMV_WARPS * 32;
+constexpr int GEMV_THREADS = (GEMV_WARPS + 1) * 32;  // compute warps + one producer warp
 constexpr int NSTAGE = 3;
 constexpr int STAGE_BYTES = 36864;  // one ring slot
 constexpr int BULK_PIECE = 12288;   // bytes per bulk copy
@@ -110,94 +111,114 @@ template <> __device__ inline void load_act<PMOE_Q8_0>(const QAct &q, size_t row
     o.dx = q.d[row * (K / QK8_0) + b];
 }
 
-// Decodes unit u of the row at `row` (shared memory) once and adds its dot product with
-// the activations of the first `cnt` tokens to acc[0..cnt).
+// dp4a with unsigned bytes in a and signed bytes in b
+__device__ inline int dp4a_us(uint32_t a, uint32_t b, int c)
+{
+    int d;
+    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+
+// Dot<DT>: the per-lane inner product of one unit of one weight row (in shared memory) with the
+// activations of CNT tokens.  Pre holds what depends only on the lane's unit (byte offsets
+// inside the row, shift amounts) and is computed once per kernel.
 template <int DT> struct Dot;
 
 template <> struct Dot<PMOE_Q4_K> {
-    __device__ static inline void run(const uint8_t *row, int u, const ActQ4K (&act)[TG], int cnt, float *acc)
+    struct Pre {
+        int hdr_off, q_off, sh, hi;
+    };
+    __device__ static inline Pre pre(int u)
     {
-        const uint8_t *blk = row + (u >> 2) * Q4_K_BYTES;
         const int qd = u & 3;
-        const uint4 hdr = *reinterpret_cast<const uint4 *>(blk);
-        const uint4 qa = *reinterpret_cast<const uint4 *>(blk + 16 + 32 * qd);
-        const uint4 qb = *reinterpret_cast<const uint4 *>(blk + 32 + 32 * qd);
-        const float d = half_bits_to_float((uint16_t)(hdr.x & 0xffffu));
+        return Pre{(u >> 2) * Q4_K_BYTES, (u >> 2) * Q4_K_BYTES + 16 + 32 * qd, 16 * (qd & 1), qd >> 1};
+    }
+    template <int CNT>
+    __device__ static inline void run(const uint8_t *row, const Pre &p, const ActQ4K (&act)[TG], float *acc)
+    {
+        const uint4 hdr = *reinterpret_cast<const uint4 *>(row + p.hdr_off);
+        const uint4 qa = *reinterpret_cast<const uint4 *>(row + p.q_off);
+        const uint4 qb = *reinterpret_cast<const uint4 *>(row + p.q_off + 16);
+        // high nibbles stay in place (x16): 1/16 goes into d
+        const float d16 = half_bits_to_float((uint16_t)(hdr.x & 0xffffu)) * 0.0625f;
         const float dmin = half_bits_to_float((uint16_t)(hdr.x >> 16));
-        const uint32_t s0 = hdr.y, s1 = hdr.z, s2 = hdr.w;
-        int sc0, sc1, m0, m1;  // 6-bit scale / min of sub-blocks 2*qd and 2*qd+1
-        if (qd < 2) {
-            const int sh = 16 * qd;
-            sc0 = (s0 >> sh) & 63; sc1 = (s0 >> (sh + 8)) & 63;
-            m0 = (s1 >> sh) & 63;  m1 = (s1 >> (sh + 8)) & 63;
-        } else {
-            const int sh = 16 * (qd - 2);
-            sc0 = ((s2 >> sh) & 0xF) | (((s0 >> (sh + 6)) & 3) << 4);
-            sc1 = ((s2 >> (sh + 8)) & 0xF) | (((s0 >> (sh + 14)) & 3) << 4);
-            m0 = ((s2 >> (sh + 4)) & 0xF) | (((s1 >> (sh + 6)) & 3) << 4);
-            m1 = ((s2 >> (sh + 12)) & 0xF) | (((s1 >> (sh + 14)) & 3) << 4);
-        }
+        // 6-bit scales / mins of sub-blocks 2*qd and 2*qd+1 as byte pairs, without a branch
+        const uint32_t a0 = hdr.y >> p.sh, a1 = hdr.z >> p.sh, a2 = hdr.w >> p.sh;
+        const uint32_t sc_lo = a0 & 0x3F3Fu, m_lo = a1 & 0x3F3Fu;
+        const uint32_t sc_hi = (a2 & 0x0F0Fu) | ((a0 >> 2) & 0x3030u);
+        const uint32_t m_hi = ((a2 >> 4) & 0x0F0Fu) | ((a1 >> 2) & 0x3030u);
+        const uint32_t scp = p.hi ? sc_hi : sc_lo, mp = p.hi ? m_hi : m_lo;
+        const int sc0_16 = (int)(scp & 0xFFu) << 4, sc1 = (int)(scp >> 8) & 0xFF;
+        const int m0 = (int)(mp & 0xFFu), m1 = (int)(mp >> 8) & 0xFF;
         const uint32_t w[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
 #pragma unroll
-        for (int t = 0; t < TG; t++) {
-            if (t < cnt) {
-                int s_lo = 0, s_hi = 0;
+        for (int t = 0; t < CNT; t++) {
+            int s_lo = 0, s_lo2 = 0, s_hi16 = 0, s_hi16b = 0;  // two chains each for ILP
 #pragma unroll
-                for (int i = 0; i < 8; i++) {
-                    s_lo = __dp4a((int)(w[i] & 0x0F0F0F0Fu), (int)act[t].a[i], s_lo);
-                    s_hi = __dp4a((int)((w[i] >> 4) & 0x0F0F0F0Fu), (int)act[t].a[8 + i], s_hi);
-                }
-                const int isum = sc0 * s_lo + sc1 * s_hi;
-                const int imin = m0 * act[t].bs_lo + m1 * act[t].bs_hi;
-                acc[t] += act[t].dx * (d * (float)isum - dmin * (float)imin);
+            for (int i = 0; i < 8; i += 2) {
+                s_lo = dp4a_us(w[i] & 0x0F0F0F0Fu, act[t].a[i], s_lo);
+                s_hi16 = dp4a_us(w[i] & 0xF0F0F0F0u, act[t].a[8 + i], s_hi16);
+                s_lo2 = dp4a_us(w[i + 1] & 0x0F0F0F0Fu, act[t].a[i + 1], s_lo2);
+                s_hi16b = dp4a_us(w[i + 1] & 0xF0F0F0F0u, act[t].a[9 + i], s_hi16b);
             }
+            const int isum16 = sc0_16 * (s_lo + s_lo2) + sc1 * (s_hi16 + s_hi16b);
+            const int imin = m0 * act[t].bs_lo + m1 * act[t].bs_hi;
+            acc[t] += act[t].dx * (d16 * (float)isum16 - dmin * (float)imin);
         }
     }
 };
 
 template <> struct Dot<PMOE_Q6_K> {
-    __device__ static inline void run(const uint8_t *row, int u, const ActQ16 (&act)[TG], int cnt, float *acc)
+    struct Pre {
+        int la_off, h_off, sc_off, d_off;
+    };
+    __device__ static inline Pre pre(int u)
     {
-        const uint8_t *blk = row + (u >> 4) * Q6_K_BYTES;  // 2-byte aligned
-        const int half = (u >> 3) & 1, j = u & 7;
-        const uint32_t la = lds_u32_a2(blk + 64 * half + 4 * j);
-        const uint32_t lb = lds_u32_a2(blk + 64 * half + 32 + 4 * j);
-        const uint32_t h = lds_u32_a2(blk + 128 + 32 * half + 4 * j);
-        const int8_t *sc = reinterpret_cast<const int8_t *>(blk + 192 + 8 * half + (j >> 2));
+        const int blk = (u >> 4) * Q6_K_BYTES, half = (u >> 3) & 1, j = u & 7;
+        return Pre{blk + 64 * half + 4 * j, blk + 128 + 32 * half + 4 * j, blk + 192 + 8 * half + (j >> 2), blk + 208};
+    }
+    template <int CNT>
+    __device__ static inline void run(const uint8_t *row, const Pre &p, const ActQ16 (&act)[TG], float *acc)
+    {
+        const uint32_t la = lds_u32_a2(row + p.la_off);
+        const uint32_t lb = lds_u32_a2(row + p.la_off + 32);
+        const uint32_t h = lds_u32_a2(row + p.h_off);
+        const int8_t *sc = reinterpret_cast<const int8_t *>(row + p.sc_off);
         const int c0 = sc[0], c1 = sc[2], c2 = sc[4], c3 = sc[6];
-        const float d = half_bits_to_float(*reinterpret_cast<const uint16_t *>(blk + 208));
-        const uint32_t w1 = __vsub4((la & 0x0F0F0F0Fu) | ((h << 4) & 0x30303030u), 0x20202020u);
-        const uint32_t w2 = __vsub4((lb & 0x0F0F0F0Fu) | ((h << 2) & 0x30303030u), 0x20202020u);
-        const uint32_t w3 = __vsub4(((la >> 4) & 0x0F0F0F0Fu) | (h & 0x30303030u), 0x20202020u);
-        const uint32_t w4 = __vsub4(((lb >> 4) & 0x0F0F0F0Fu) | ((h >> 2) & 0x30303030u), 0x20202020u);
+        // the 6-bit quant goes to the top of each byte with its top bit flipped: as a signed
+        // byte that is 4*(q-32); the factor 4 is taken out of d
+        const float d4 = half_bits_to_float(*reinterpret_cast<const uint16_t *>(row + p.d_off)) * 0.25f;
+        const uint32_t w1 = (((la << 2) & 0x3C3C3C3Cu) | ((h << 6) & 0xC0C0C0C0u)) ^ 0x80808080u;
+        const uint32_t w2 = (((lb << 2) & 0x3C3C3C3Cu) | ((h << 4) & 0xC0C0C0C0u)) ^ 0x80808080u;
+        const uint32_t w3 = (((la >> 2) & 0x3C3C3C3Cu) | ((h << 2) & 0xC0C0C0C0u)) ^ 0x80808080u;
+        const uint32_t w4 = (((lb >> 2) & 0x3C3C3C3Cu) | (h & 0xC0C0C0C0u)) ^ 0x80808080u;
 #pragma unroll
-        for (int t = 0; t < TG; t++) {
-            if (t < cnt) {
-                const int isum = c0 * __dp4a((int)w1, (int)act[t].a[0], 0) + c1 * __dp4a((int)w2, (int)act[t].a[1], 0) +
-                                 c2 * __dp4a((int)w3, (int)act[t].a[2], 0) + c3 * __dp4a((int)w4, (int)act[t].a[3], 0);
-                acc[t] += (d * act[t].dx) * (float)isum;
-            }
+        for (int t = 0; t < CNT; t++) {
+            const int isum = c0 * __dp4a((int)w1, (int)act[t].a[0], 0) + c1 * __dp4a((int)w2, (int)act[t].a[1], 0) +
+                             c2 * __dp4a((int)w3, (int)act[t].a[2], 0) + c3 * __dp4a((int)w4, (int)act[t].a[3], 0);
+            acc[t] += (d4 * act[t].dx) * (float)isum;
         }
     }
 };
 
 template <> struct Dot<PMOE_Q8_0> {
-    __device__ static inline void run(const uint8_t *row, int u, const ActQ16 (&act)[TG], int cnt, float *acc)
+    struct Pre {
+        int d_off, q_off;
+    };
+    __device__ static inline Pre pre(int u) { return Pre{(u >> 1) * Q8_0_BYTES, (u >> 1) * Q8_0_BYTES + 2 + 16 * (u & 1)}; }
+    template <int CNT>
+    __device__ static inline void run(const uint8_t *row, const Pre &p, const ActQ16 (&act)[TG], float *acc)
     {
-        const uint8_t *blk = row + (u >> 1) * Q8_0_BYTES;  // 2-byte aligned
-        const int hf = u & 1;
-        const float d = half_bits_to_float(*reinterpret_cast<const uint16_t *>(blk));
+        const float d = half_bits_to_float(*reinterpret_cast<const uint16_t *>(row + p.d_off));
         uint32_t w[4];
 #pragma unroll
-        for (int i = 0; i < 4; i++) w[i] = lds_u32_a2(blk + 2 + 16 * hf + 4 * i);
+        for (int i = 0; i < 4; i++) w[i] = lds_u32_a2(row + p.q_off + 4 * i);
 #pragma unroll
-        for (int t = 0; t < TG; t++) {
-            if (t < cnt) {
-                int isum = 0;
+        for (int t = 0; t < CNT; t++) {
+            int isum = 0;
 #pragma unroll
-                for (int i = 0; i < 4; i++) isum = __dp4a((int)w[i], (int)act[t].a[i], isum);
-                acc[t] += (d * act[t].dx) * (float)isum;
-            }
+            for (int i = 0; i < 4; i++) isum = __dp4a((int)w[i], (int)act[t].a[i], isum);
+            acc[t] += (d * act[t].dx) * (float)isum;
         }
     }
 };
@@ -225,34 +246,6 @@ template <int DT, int NMAT> struct Cfg {
     static_assert(RPW >= GROUPS && PASSES % RB == 0 && V <= LPR && ITEM_BYTES % 16 == 0, "bad tiling");
 };
 
-// Sums V per-lane values across the LPR lanes of a row group with LPR-1 shuffles in total:
-// every step halves the number of values a lane still carries.  The lane at in-group position
-// pl ends with the total of value index pl / (LPR / V).  The pairing order (LPR/2, ..., 1) is
-// that of a plain xor butterfly.
-template <int V, int LPR> __device__ inline float transposed_reduce(float (&v)[V], int lane)
-{
-    int cnt = V;
-#pragma unroll
-    for (int step = LPR / 2; step >= 1; step >>= 1) {
-        if (cnt > 1) {
-            const int half = cnt / 2;
-            const bool up = (lane & step) != 0;
-#pragma unroll
-            for (int i = 0; i < V / 2; i++) {
-                if (i < half) {
-                    const float send = up ? v[i] : v[i + half];
-                    const float keep = up ? v[i + half] : v[i];
-                    v[i] = keep + __shfl_xor_sync(0xffffffffu, send, step);
-                }
-            }
-            cnt = half;
-        } else {
-            v[0] += __shfl_xor_sync(0xffffffffu, v[0], step);
-        }
-    }
-    return v[0];
-}
-
 // ---------------------------------------------------------------- kernel arguments
 struct GemvArgs {
     const uint8_t *w0, *w1;    // routed matrices (gate, up) or (down, unused); expert e at + e*expert_bytes
@@ -268,6 +261,7 @@ struct GemvArgs {
     const float *scale_r;      // routing weights [n*top_k]      (down only)
     const float *scale_s;      // shared gate sigmoid [n]        (down only)
     DevStatus *status;
+    int debug;                 // 1: skip the arithmetic, 2: skip the copies (timing experiments)
 };
 
 
@@ -310,10 +304,11 @@ __device__ inline void load_pass(const GemvArgs &A, bool is_shared, const int *l
     }
 }
 
-// All rows of one item (in shared memory) against one pass of tokens.
-template <int DT, int NMAT>
+// All rows of one item (in shared memory) against one pass of CNT tokens.
+template <int DT, int NMAT, int CNT>
 __device__ inline void compute_item(const GemvArgs &A, const uint8_t *stage, int chunk, const Pass &P,
-                                    const typename Tr<DT>::Act (&act)[Cfg<DT, NMAT>::UPL][TG], int warp, int lane)
+                                    const typename Tr<DT>::Act (&act)[Cfg<DT, NMAT>::UPL][TG],
+                                    const typename Dot<DT>::Pre (&pre)[Cfg<DT, NMAT>::UPL], int warp, int lane)
 {
     using C = Cfg<DT, NMAT>;
     const int grp = lane / C::LPR, ul = lane % C::LPR;
@@ -330,7 +325,7 @@ __device__ inline void compute_item(const GemvArgs &A, const uint8_t *stage, int
                 const uint8_t *rp = stage + mat * C::ITEM_BYTES + row * C::ROW_BYTES;
 #pragma unroll
                 for (int i = 0; i < C::UPL; i++) {
-                    Dot<DT>::run(rp, i * C::LPR + ul, act[i], P.cnt, acc + (mat * C::RB + rb) * TG);
+                    Dot<DT>::template run<CNT>(rp, pre[i], act[i], acc + (mat * C::RB + rb) * TG);
                     // keeps the compiler from hoisting every unit's loads at once (register pressure)
                     if (C::UPL > 1) asm volatile("" ::: "memory");
                 }
@@ -345,12 +340,9 @@ __device__ inline void compute_item(const GemvArgs &A, const uint8_t *stage, int
             v = v / (1.f + expf(-v)) * other;                                 // silu(gate) * up
         }
         const int row = chunk * C::ROWS + warp * C::RPW + (b0 + rb) * C::GROUPS + grp;
-        // out_row[t] via a small select chain (t is lane-dependent)
-        int orow = -1;
-        float sc = 0.f;
-#pragma unroll
-        for (int q = 0; q < TG; q++)
-            if (q == t) { orow = P.out_row[q]; sc = P.scale[q]; }
+        static_assert(TG == 2, "select below assumes two tokens per pass");
+        const int orow = t == 0 ? P.out_row[0] : P.out_row[1];
+        const float sc = t == 0 ? P.scale[0] : P.scale[1];
         if (ul % DUP == 0 && mat == 0 && orow >= 0)
             A.out[(size_t)orow * A.rows_total + row] = NMAT == 2 ? v : v * sc;
     }
@@ -406,8 +398,8 @@ __device__ inline uint8_t *ring_stage(uint8_t *base, int s) { return base + 128 
 __device__ inline uint64_t *ring_full(uint8_t *base, int s) { return reinterpret_cast<uint64_t *>(base) + s; }
 __device__ inline uint64_t *ring_empty(uint8_t *base, int s) { return reinterpret_cast<uint64_t *>(base) + NSTAGE + s; }
 
-// Thread 0's side of the ring: issues the bulk copies of its next item once the warps have
-// released the slot's previous contents.
+// The producer's side of the ring: issues the bulk copies of its next item once the compute
+// warps have released the slot's previous contents.
 template <int DT_R, int DT_S1, int NMAT> struct Producer {
     using CR = Cfg<DT_R, NMAT>;
     using CS = Cfg<DT_S1, NMAT>;
@@ -456,11 +448,10 @@ template <int DT_R, int DT_S1, int NMAT> struct Producer {
 };
 
 // The CTA's items of one kind (routed or shared), consumed in order from `cur` while the slot
-// stays below `slot_end`.  Before each item thread 0 tops the ring up, so NSTAGE-1 items stay
-// in flight.  `it` numbers the CTA's items; the ring position follows from it.
-template <int DT, int NMAT, typename Prod>
-__device__ inline bool run_items(const GemvArgs &A, uint8_t *ring, const Plan &plan, Prod &prod, bool is_shared,
-                                 Cursor &cur, int slot_end, int &it, int n_items, const QAct &in, int warp, int lane)
+// stays below `slot_end`.  `it` numbers the CTA's items; the ring position follows from it.
+template <int DT, int NMAT>
+__device__ inline bool run_items(const GemvArgs &A, uint8_t *ring, const Plan &plan, bool is_shared, Cursor &cur,
+                                 int slot_end, int &it, int n_items, const QAct &in, int warp, int lane)
 {
     using C = Cfg<DT, NMAT>;
     using Act = typename Tr<DT>::Act;
@@ -469,9 +460,10 @@ __device__ inline bool run_items(const GemvArgs &A, uint8_t *ring, const Plan &p
     const int *list = nullptr;
     Pass P;
     Act act[C::UPL][TG];
+    typename Dot<DT>::Pre pre[C::UPL];
+#pragma unroll
+    for (int i = 0; i < C::UPL; i++) pre[i] = Dot<DT>::pre(i * C::LPR + ul);
     while (it < n_items && cur.slot < slot_end) {
-        if (threadIdx.x == 0 && !prod.issue_next()) return false;
-        __syncwarp();
         const int s = it % NSTAGE;
         const uint32_t use = (uint32_t)(it / NSTAGE);
         if (cur.slot != cur_slot) {
@@ -485,17 +477,20 @@ __device__ inline bool run_items(const GemvArgs &A, uint8_t *ring, const Plan &p
             }
             if (m <= TG) load_pass<DT, NMAT>(A, is_shared, list, m, 0, in, ul, P, act);
         }
-        if (!mbar_wait(ring_full(ring, s), use & 1)) {
+        if (A.debug != 2 && !mbar_wait(ring_full(ring, s), use & 1)) {
             set_status(A.status, PMOE_ERR_TIMEOUT, 10 + NMAT, it);
             return false;
         }
         const uint8_t *stage = ring_stage(ring, s);
-        if (m <= TG) {
-            compute_item<DT, NMAT>(A, stage, cur.chunk, P, act, warp, lane);
+        if (A.debug == 1) {
+        } else if (m <= TG) {
+            if (P.cnt == TG) compute_item<DT, NMAT, TG>(A, stage, cur.chunk, P, act, pre, warp, lane);
+            else compute_item<DT, NMAT, 1>(A, stage, cur.chunk, P, act, pre, warp, lane);
         } else {
             for (int t0 = 0; t0 < m; t0 += TG) {
                 load_pass<DT, NMAT>(A, is_shared, list, m, t0, in, ul, P, act);
-                compute_item<DT, NMAT>(A, stage, cur.chunk, P, act, warp, lane);
+                if (P.cnt == TG) compute_item<DT, NMAT, TG>(A, stage, cur.chunk, P, act, pre, warp, lane);
+                else compute_item<DT, NMAT, 1>(A, stage, cur.chunk, P, act, pre, warp, lane);
             }
         }
         __syncwarp();
@@ -540,14 +535,18 @@ __global__ void __launch_bounds__(GEMV_THREADS, 2) k_expert_gemv(const GemvArgs 
     const int n_items = plan.index(last) - plan.index(cur);
     if (n_items <= 0) return;
 
-    Producer<DT_R, DT_S1, NMAT> prod{A, plan, ring, cur, 0, n_items};
-    if (threadIdx.x == 0)
-        for (int i = 0; i < NSTAGE - 1; i++) prod.issue_next();  // run_items tops up one per item
-
+    if (warp == GEMV_WARPS) {  // the producer warp: one lane keeps the ring full
+        if (lane == 0 && A.debug != 2) {
+            Producer<DT_R, DT_S1, NMAT> prod{A, plan, ring, cur, 0, n_items};
+            for (int i = 0; i < n_items; i++)
+                if (!prod.issue_next()) break;
+        }
+        return;
+    }
     int it = 0;
-    bool ok = run_items<DT_R, NMAT>(A, ring, plan, prod, false, cur, plan.n_active, it, n_items, A.in_r, warp, lane);
+    bool ok = run_items<DT_R, NMAT>(A, ring, plan, false, cur, plan.n_active, it, n_items, A.in_r, warp, lane);
     if constexpr (DT_S != 0) {
-        if (ok) run_items<DT_S, NMAT>(A, ring, plan, prod, true, cur, plan.n_active + 1, it, n_items, A.in_s, warp, lane);
+        if (ok) run_items<DT_S, NMAT>(A, ring, plan, true, cur, plan.n_active + 1, it, n_items, A.in_s, warp, lane);
     }
 }
 
@@ -628,6 +627,7 @@ cudaError_t launch_gate_up(const LayerDev &L, const Workspace &ws, int n, int to
     A.in_s = is_kquant(L.sh_gate_dtype) ? ws.x_q8k : ws.x_q80;
     A.out = ws.act;
     A.status = ws.status;
+    A.debug = getenv("PMOE_DEBUG") ? atoi(getenv("PMOE_DEBUG")) : 0;
     // a kernel without routed items still needs a routed type to instantiate; reuse the shared one
     return launch_gemv<2>(A, routed ? L.gate_dtype : L.sh_gate_dtype, shared ? L.sh_gate_dtype : 0, s);
 }
@@ -650,6 +650,7 @@ cudaError_t launch_down(const LayerDev &L, const Workspace &ws, const float *w, 
     A.scale_r = w;
     A.scale_s = ws.sh_sigmoid;
     A.status = ws.status;
+    A.debug = getenv("PMOE_DEBUG") ? atoi(getenv("PMOE_DEBUG")) : 0;
     return launch_gemv<1>(A, routed ? L.down_dtype : L.sh_down_dtype, shared ? L.sh_down_dtype : 0, s);
 }
 

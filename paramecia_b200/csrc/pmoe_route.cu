@@ -115,11 +115,88 @@ __global__ void __launch_bounds__(ROUTER_WPB * 32) k_router(const float *__restr
     }
 }
 
+// The same product for more than a handful of tokens.  A CTA stages a tile of RT_TOKENS rows
+// of x in shared memory as f32; each warp keeps its slice of one router row in registers and
+// walks the tile.  The per-lane partial sums are built and folded in exactly the order above
+// (the transposed reduction pairs lanes 16, 8, 4, 2, 1 apart like the butterfly), so the bits
+// do not depend on which kernel ran.  H <= 2048.
+constexpr int RT_TOKENS = 8;
+constexpr int RT_WARPS = 8;
+
+template <typename XT>
+__global__ void __launch_bounds__(RT_WARPS * 32) k_router_tiled(const float *__restrict__ W,
+                                                                const float *__restrict__ bias,
+                                                                const XT *__restrict__ x, int n, int E, int H,
+                                                                int rows_per_cta, float *__restrict__ logits)
+{
+    extern __shared__ __align__(16) float xs[];  // [RT_TOKENS][H]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t0 = blockIdx.y * RT_TOKENS;
+    const int nt = n - t0 < RT_TOKENS ? n - t0 : RT_TOKENS;
+    for (int i = threadIdx.x * 4; i < RT_TOKENS * H; i += RT_WARPS * 32 * 4) {
+        const int tt = i / H;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (tt < nt) v = load_x4(x, (size_t)(t0 + tt) * H + (i - tt * H));
+        *reinterpret_cast<float4 *>(xs + i) = v;
+    }
+    __syncthreads();
+    const int steps = H / 128;  // <= 16
+    const int e_begin = blockIdx.x * rows_per_cta;
+    for (int e = e_begin + warp; e < e_begin + rows_per_cta && e < E; e += RT_WARPS) {
+        float4 wv[16];
+        const float4 *w4 = reinterpret_cast<const float4 *>(W + (size_t)e * H);
+#pragma unroll
+        for (int i = 0; i < 16; i++)
+            if (i < steps) wv[i] = w4[32 * i + lane];
+        float acc[RT_TOKENS];
+#pragma unroll
+        for (int tt = 0; tt < RT_TOKENS; tt++) {
+            float a = 0.f;
+            const float4 *x4 = reinterpret_cast<const float4 *>(xs + tt * H);
+#pragma unroll
+            for (int i = 0; i < 16; i++) {
+                if (i < steps) {
+                    const float4 xv = x4[32 * i + lane];
+                    a = fmaf(xv.x, wv[i].x, a);
+                    a = fmaf(xv.y, wv[i].y, a);
+                    a = fmaf(xv.z, wv[i].z, a);
+                    a = fmaf(xv.w, wv[i].w, a);
+                }
+            }
+            acc[tt] = a;
+        }
+        const float v = transposed_reduce<RT_TOKENS, 32>(acc, lane);
+        const int tt = lane >> 2;  // lanes 4*tt .. 4*tt+3 hold token tt's sum
+        if ((lane & 3) == 0 && tt < nt) logits[(size_t)(t0 + tt) * E + e] = bias ? __fadd_rn(v, bias[e]) : v;
+    }
+}
+
 cudaError_t launch_router(const LayerDev &L, const Workspace &ws, const void *x, int x_dtype, int n, float *logits,
                           cudaStream_t s)
 {
     (void)ws;
     if (n <= 0) return cudaSuccess;
+    if (n > 8 && L.H <= 2048) {
+        static bool configured = false;
+        const size_t smem = (size_t)RT_TOKENS * L.H * sizeof(float);
+        if (!configured) {
+            cudaError_t e1 = cudaFuncSetAttribute(k_router_tiled<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 65536);
+            cudaError_t e2 = cudaFuncSetAttribute(k_router_tiled<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 65536);
+            if (e1 != cudaSuccess) return e1;
+            if (e2 != cudaSuccess) return e2;
+            configured = true;
+        }
+        const int rows_per_cta = n <= 512 ? 8 : 64;
+        dim3 grid((L.E + rows_per_cta - 1) / rows_per_cta, (n + RT_TOKENS - 1) / RT_TOKENS);
+        if (x_dtype == PMOE_F32)
+            k_router_tiled<float><<<grid, RT_WARPS * 32, smem, s>>>(L.router_w, L.router_bias, (const float *)x, n, L.E,
+                                                                    L.H, rows_per_cta, logits);
+        else
+            k_router_tiled<__nv_bfloat16><<<grid, RT_WARPS * 32, smem, s>>>(
+                L.router_w, L.router_bias, (const __nv_bfloat16 *)x, n, L.E, L.H, rows_per_cta, logits);
+        count_launch();
+        return cudaGetLastError();
+    }
     dim3 grid((L.E + ROUTER_WPB - 1) / ROUTER_WPB), block(ROUTER_WPB * 32);
     if (x_dtype == PMOE_F32) {
         if (n == 1)
