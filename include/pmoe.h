@@ -164,6 +164,16 @@ int pmoe_dequantize(int device, int dtype, const void *blocks, size_t n_elems, f
 int pmoe_add_rms_norm(int device, const float *resid_in, const float *delta, const float *weight,
                       int n, int H, float eps, float *resid_out, float *y, void *stream);
 
+/*
+ * Home-rank side of the expert-parallel combine: out[t] = sum_r parts[r][t] (+ extra[t]).
+ * parts [n_parts, n, H] f32 are the per-rank partial sums a token's expert owners returned,
+ * extra [n, H] (F32 or BF16, may be NULL) is the gated shared-expert row.  It continues the
+ * reference's accumulation of expert outputs into one buffer (tokio_experts.rs:133-145) and
+ * the final add (qwen3_next.rs:1932-1937) across GPUs; the reference itself is single-device.
+ */
+int pmoe_reduce_rows(int device, const float *parts, int n_parts, const void *extra, int extra_dtype,
+                     int n, int H, void *out, int out_dtype, void *stream);
+
 /* Synchronises the stream and reports the device-side status word of the layer
  * (PMOE_OK, PMOE_ERR_TIMEOUT, PMOE_ERR_BAD_INDEX), clearing it. */
 int pmoe_layer_status(pmoe_layer *layer, void *stream);

@@ -507,6 +507,20 @@ int pmoe_add_rms_norm(int device, const float *resid_in, const float *delta, con
     return PMOE_OK;
 }
 
+int pmoe_reduce_rows(int device, const float *parts, int n_parts, const void *extra, int extra_dtype, int n, int H,
+                     void *out, int out_dtype, void *stream)
+{
+    if (n < 0 || H <= 0 || H % 4 || n_parts <= 0) return fail(PMOE_ERR_INVALID_ARG, "bad n / H / n_parts");
+    if (n && (!parts || !out)) return fail(PMOE_ERR_INVALID_ARG, "parts / out is NULL");
+    if ((extra && extra_dtype != PMOE_F32 && extra_dtype != PMOE_BF16) || (out_dtype != PMOE_F32 && out_dtype != PMOE_BF16))
+        return fail(PMOE_ERR_UNSUPPORTED_DTYPE, "extra / out must be F32 or BF16");
+    DeviceGuard guard(device);
+    if (!guard.ok) return fail(PMOE_ERR_NO_DEVICE, "cannot select device %d", device);
+    CU(launch_reduce_rows(parts, n_parts, extra, extra ? extra_dtype : PMOE_F32, n, H, out, out_dtype,
+                          (cudaStream_t)stream));
+    return PMOE_OK;
+}
+
 int pmoe_qmatmul(int device, int dtype, const void *w, size_t rows, size_t cols, const float *x, size_t m, float *y,
                  void *stream)
 {

@@ -107,6 +107,50 @@ __global__ void __launch_bounds__(256) k_add_rms_norm(const float *__restrict__ 
     }
 }
 
+// out[t] = sum_r parts[r][t] (+ extra[t]): the home rank's side of the expert-parallel combine.
+// Rank order is fixed, so the result does not depend on message arrival order.
+template <typename ET, typename OT>
+__global__ void __launch_bounds__(256) k_reduce_rows(const float *__restrict__ parts, int R, size_t stride,
+                                                     const ET *__restrict__ extra, size_t total,
+                                                     OT *__restrict__ out)
+{
+    size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (i >= total) return;
+    float4 acc = *reinterpret_cast<const float4 *>(parts + i);
+    for (int r = 1; r < R; r++) {
+        const float4 v = *reinterpret_cast<const float4 *>(parts + (size_t)r * stride + i);
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    if (extra) {
+        acc.x += load_as_float(extra, i); acc.y += load_as_float(extra, i + 1);
+        acc.z += load_as_float(extra, i + 2); acc.w += load_as_float(extra, i + 3);
+    }
+    store_from_float(out, i, acc.x); store_from_float(out, i + 1, acc.y);
+    store_from_float(out, i + 2, acc.z); store_from_float(out, i + 3, acc.w);
+}
+
+cudaError_t launch_reduce_rows(const float *parts, int R, const void *extra, int extra_dtype, int n, int H, void *out,
+                               int out_dtype, cudaStream_t s)
+{
+    if (n <= 0) return cudaSuccess;
+    const size_t total = (size_t)n * H;
+    const unsigned grid = (unsigned)((total / 4 + 255) / 256);
+    const bool ef = extra_dtype == PMOE_F32, of = out_dtype == PMOE_F32;
+    if (ef && of)
+        k_reduce_rows<float, float><<<grid, 256, 0, s>>>(parts, R, total, (const float *)extra, total, (float *)out);
+    else if (ef)
+        k_reduce_rows<float, __nv_bfloat16><<<grid, 256, 0, s>>>(parts, R, total, (const float *)extra, total,
+                                                                 (__nv_bfloat16 *)out);
+    else if (of)
+        k_reduce_rows<__nv_bfloat16, float><<<grid, 256, 0, s>>>(parts, R, total, (const __nv_bfloat16 *)extra, total,
+                                                                 (float *)out);
+    else
+        k_reduce_rows<__nv_bfloat16, __nv_bfloat16><<<grid, 256, 0, s>>>(parts, R, total, (const __nv_bfloat16 *)extra,
+                                                                         total, (__nv_bfloat16 *)out);
+    count_launch();
+    return cudaGetLastError();
+}
+
 cudaError_t launch_add_rms_norm(const float *resid_in, const float *delta, const float *weight, int n, int H,
                                 float eps, float *resid_out, float *y, cudaStream_t s)
 {

@@ -245,6 +245,8 @@ cudaError_t launch_combine(const LayerDev &L, const Workspace &ws, const uint32_
 bool gemv_supported(int dtype, int K, int rows, const char **why);
 // pmoe_codec.cu
 cudaError_t launch_dequantize(int dtype, const void *blocks, size_t n_elems, float *out, cudaStream_t s);
+cudaError_t launch_reduce_rows(const float *parts, int R, const void *extra, int extra_dtype, int n, int H, void *out,
+                               int out_dtype, cudaStream_t s);
 cudaError_t launch_add_rms_norm(const float *resid_in, const float *delta, const float *weight, int n, int H,
                                 float eps, float *resid_out, float *y, cudaStream_t s);
 

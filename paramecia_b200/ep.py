@@ -1,0 +1,146 @@
+"""Expert parallelism for the MoE block: E/N routed experts per GPU, one process per GPU.
+
+The reference is a single-device program (its "expert parallelism" is a rayon loop over
+experts, paramecia-model/src/tokio_experts.rs:116-130); the split across GPUs is this build's.
+Every rank keeps the router and the shared expert (small) and one contiguous slice of the
+routed experts.  One block forward on a rank that is home to n tokens:
+
+1. route the local tokens (router replicated);
+2. dispatch: every rank that owns one of a token's experts receives the token's row once,
+   with the token's top-k ids and weights; ids the destination does not own are replaced by
+   an invalid id so the receiver skips them;
+3. each rank runs its experts over what it received and pre-reduces, per token, the weighted
+   outputs of its own experts (``MoeBlock.experts_forward_batched``);
+4. combine: the per-rank partial rows travel back to the token's home rank, which adds them
+   in rank order together with its shared-expert row (``pmoe_reduce_rows``).
+
+Buffers have a fixed capacity of n rows per (source, destination) pair -- a token is sent to a
+rank at most once -- so neither exchange needs a size handshake or a host synchronisation.
+With top-10 routing over at most 8 ranks nearly every token visits nearly every rank, so the
+padding costs little.  Two transports carry the same rows:
+
+* ``all_to_all``  two ``all_to_all_single`` calls out (rows, routing) and one back;
+* ``all_gather``  ``all_gather_into_tensor`` out and ``reduce_scatter_tensor`` back, which lets
+                  NCCL do the cross-rank sum (in the switch when NVLS is active).
+
+No kernel here reads another GPU's memory: NCCL delivers into local HBM first.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+INVALID_EXPERT = -1  # 0xFFFFFFFF as int32: outside every expert slice
+
+
+class _LibOps:
+    """The device-side pieces of the combine, from libpmoe."""
+
+    @staticmethod
+    def reduce_rows(parts: torch.Tensor, extra: Optional[torch.Tensor], out: torch.Tensor):
+        from ._lib import check, lib
+        from .moe import _TORCH_TO_PMOE, _stream_ptr
+        R, n, H = parts.shape
+        check(lib().pmoe_reduce_rows(parts.device.index or 0, parts.data_ptr(), R,
+                                     None if extra is None else extra.data_ptr(),
+                                     0 if extra is None else _TORCH_TO_PMOE[extra.dtype], n, H, out.data_ptr(),
+                                     _TORCH_TO_PMOE[out.dtype], _stream_ptr(parts.device)))
+
+
+def expert_owner(idx: torch.Tensor, experts_per_rank: int) -> torch.Tensor:
+    """Rank that owns each expert id under the contiguous placement (expert e on rank e // (E/N))."""
+    return torch.div(idx, experts_per_rank, rounding_mode="floor")
+
+
+def mask_for_destinations(idx: torch.Tensor, n_ranks: int, experts_per_rank: int) -> torch.Tensor:
+    """[N, n, k] routing tables, one per destination rank: ids the destination does not own become
+    INVALID_EXPERT, so that a row contributes on a rank only through that rank's experts."""
+    owner = expert_owner(idx, experts_per_rank)                      # [n, k]
+    dest = torch.arange(n_ranks, device=idx.device).view(-1, 1, 1)   # [N, 1, 1]
+    return torch.where(owner.unsqueeze(0) == dest, idx.unsqueeze(0), torch.full_like(idx, INVALID_EXPERT).unsqueeze(0))
+
+
+class ExpertParallelMoe:
+    """One MoE block spread over the ranks of `group`.  `block` is this rank's MoeBlock, built with
+    its expert slice (expert_base = rank * E/N, E_local = E/N) and max_tokens >= N * n."""
+
+    def __init__(self, block, group=None, mode: str = "all_to_all", ops=None):
+        if mode not in ("all_to_all", "all_gather"):
+            raise ValueError("mode must be 'all_to_all' or 'all_gather'")
+        self.block = block
+        self.group = group
+        self.mode = mode
+        self.ops = ops or _LibOps
+        self.rank = dist.get_rank(group)
+        self.N = dist.get_world_size(group)
+        self.E = block.num_experts
+        self.k = block.num_experts_per_tok
+        self.H = block.hidden_dim
+        if self.E % self.N:
+            raise ValueError("the number of experts must be divisible by the number of ranks")
+        self.per_rank = self.E // self.N
+        if block.num_experts_local != self.per_rank or block.expert_base != self.rank * self.per_rank:
+            raise ValueError("block must hold experts [rank*E/N, (rank+1)*E/N)")
+        self._buf_n = -1
+
+    # buffers are sized once per token count and reused (no allocation in the steady state)
+    def _buffers(self, n: int, x: torch.Tensor):
+        if n == self._buf_n and self._x_dtype == x.dtype:
+            return
+        N, H, k, dev = self.N, self.H, self.k, x.device
+        self._buf_n, self._x_dtype = n, x.dtype
+        self.send_x = torch.empty((N, n, H), dtype=x.dtype, device=dev)
+        self.recv_x = torch.empty((N, n, H), dtype=x.dtype, device=dev)
+        self.send_meta = torch.empty((N, n, 2 * k), dtype=torch.int32, device=dev)
+        self.recv_meta = torch.empty((N, n, 2 * k), dtype=torch.int32, device=dev)
+        self.back = torch.empty((N, n, H), dtype=torch.float32, device=dev)
+        self.home = torch.empty((1, n, H), dtype=torch.float32, device=dev)
+
+    def gather_tokens(self, x: torch.Tensor) -> torch.Tensor:
+        """All ranks' token rows, rank-major: [N*n, H]."""
+        out = torch.empty((self.N * x.shape[0], x.shape[1]), dtype=x.dtype, device=x.device)
+        dist.all_gather_into_tensor(out, x.contiguous(), group=self.group)
+        return out
+
+    def forward_into(self, x: torch.Tensor, out: torch.Tensor, stats: Optional[dict] = None):
+        """x [n, H] (this rank's tokens) -> out [n, H]; every rank must call with the same n."""
+        n = x.shape[0]
+        N, k = self.N, self.k
+        self._buffers(n, x)
+        logits, w, idx = self.block.route(x)
+        if stats is not None:
+            stats.update(router_logits=logits, top_indices=idx, top_weights=w)
+        # -- dispatch
+        if self.mode == "all_to_all":
+            self.send_x.copy_(x.unsqueeze(0).expand(N, n, self.H))
+            self.send_meta[:, :, :k] = mask_for_destinations(idx, N, self.per_rank)
+            self.send_meta[:, :, k:] = w.view(torch.int32).unsqueeze(0)
+            dist.all_to_all_single(self.recv_x.view(N * n, self.H), self.send_x.view(N * n, self.H), group=self.group)
+            dist.all_to_all_single(self.recv_meta.view(N * n, 2 * k), self.send_meta.view(N * n, 2 * k),
+                                   group=self.group)
+        else:
+            meta = self.send_meta[0]
+            meta[:, :k] = idx
+            meta[:, k:] = w.view(torch.int32)
+            dist.all_gather_into_tensor(self.recv_x.view(N * n, self.H), x.contiguous(), group=self.group)
+            dist.all_gather_into_tensor(self.recv_meta.view(N * n, 2 * k), meta, group=self.group)
+        rx = self.recv_x.view(N * n, self.H)
+        ridx = self.recv_meta.view(N * n, 2 * k)[:, :k].contiguous()
+        rw = self.recv_meta.view(N * n, 2 * k)[:, k:].contiguous().view(torch.float32)
+        # -- this rank's experts over everything it received, pre-reduced per token
+        part = self.block.experts_forward_batched(rx, ridx, rw, k, out_dtype=torch.float32)
+        # -- combine
+        shared = self.block.shared_forward(x, out_dtype=torch.float32) if self.block.has_shared else None
+        if self.mode == "all_to_all":
+            dist.all_to_all_single(self.back.view(N * n, self.H), part, group=self.group)
+            self.ops.reduce_rows(self.back, shared, out)
+        else:
+            dist.reduce_scatter_tensor(self.home.view(n, self.H), part, group=self.group)
+            self.ops.reduce_rows(self.home, shared, out)
+        return out
+
+    def forward(self, x: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+        out = torch.empty((x.shape[0], self.H), dtype=out_dtype or x.dtype, device=x.device)
+        return self.forward_into(x, out)

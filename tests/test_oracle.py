@@ -1,0 +1,134 @@
+"""CPU tests of the oracle: block codecs against the gguf-py golden vectors, the activation
+quantisers and block dots against straight numpy restatements, routing tie rules, and the
+whole-block oracle against its exact-arithmetic variant."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import pmoe_oracle as po
+from paramecia_b200 import synth
+from tests.common import oracle_layer, rel_l2, seeded_x
+
+G = np.load(os.path.join(os.path.dirname(__file__), "golden", "codec_golden.npz"))
+LG = np.load(os.path.join(os.path.dirname(__file__), "golden", "layer_golden.npz"))
+DT = {"q4_k": po.Q4_K, "q6_k": po.Q6_K, "q8_0": po.Q8_0}
+
+
+@pytest.mark.parametrize("name", ["q4_k", "q6_k", "q8_0"])
+def test_dequantize_matches_gguf_py_bit_exact(name):
+    raw, want = G[name + "_blocks"], G[name + "_dequant"]
+    got = po.dequantize(DT[name], raw.reshape(-1), want.size)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
+def test_q8_0_quantiser_matches_gguf_py():
+    got = po.quantize(po.Q8_0, G["q8_0_quant_in"])
+    assert np.array_equal(got, G["q8_0_quant_blocks"])
+
+
+@pytest.mark.parametrize("dtype,tol", [(po.Q4_K, 0.12), (po.Q6_K, 0.03), (po.Q8_0, 0.01)])
+def test_weight_quantisers_round_trip(dtype, tol):
+    rng = np.random.default_rng(1)
+    w = (rng.standard_normal(256 * 32) * 0.02).astype(np.float32)
+    for q in (po.quantize(dtype, w), synth.quantize(torch.from_numpy(w), dtype).numpy()):
+        back = po.dequantize(dtype, q, w.size)
+        assert rel_l2(back, w) < tol
+    z = po.dequantize(dtype, po.quantize(dtype, np.zeros(256, np.float32)), 256)
+    assert not z.any()
+
+
+def test_q8k_activation_quantiser():
+    rng = np.random.default_rng(2)
+    x = rng.standard_normal(512).astype(np.float32)
+    x[256:] = 0.0                      # an all-zero block gives d = 0
+    x[5] = -7.0                        # the largest magnitude keeps its sign: iscale = -128 / max
+    x[9] = 7.0                         # same magnitude later in the block must not win
+    d, qs, bs = po.quantize_q8k(x)
+    assert d[1] == 0 and not qs[256:].any() and not bs[16:].any()
+    iscale = np.float32(-128.0) / np.float32(-7.0)
+    want = np.minimum(np.sign(iscale * x[:256]) * np.floor(np.abs(iscale * x[:256]) + 0.5), 127).astype(np.int8)
+    assert np.array_equal(qs[:256], want)
+    assert qs[5] == -128 and qs[9] == 127
+    assert d[0] == np.float32(1.0) / iscale
+    assert np.array_equal(bs[:16], want.reshape(16, 16).astype(np.int32).sum(1).astype(np.int16))
+
+
+def test_q8_0_activation_quantiser():
+    rng = np.random.default_rng(3)
+    x = rng.standard_normal(64).astype(np.float32)
+    x[32:] = 0
+    d, qs = po.quantize_q8_0_act(x)
+    amax = np.abs(x[:32]).max()
+    dd = np.float32(amax) / np.float32(127)
+    assert d[0] == np.float16(dd) and d[1] == 0
+    q = x[:32] * (np.float32(1) / dd)
+    assert np.array_equal(qs[:32], (np.sign(q) * np.floor(np.abs(q) + 0.5)).astype(np.int8))
+
+
+@pytest.mark.parametrize("dtype", [po.Q4_K, po.Q6_K, po.Q8_0])
+def test_qmatmul_is_integer_dot_of_quantised_activations(dtype):
+    rng = np.random.default_rng(4)
+    rows, cols, m = 8, 512, 3
+    w = po.quantize(dtype, (rng.standard_normal(rows * cols) * 0.02).astype(np.float32))
+    x = rng.standard_normal((m, cols)).astype(np.float32)
+    got = po.qmatmul(dtype, w, rows, cols, x)
+    wd = po.dequantize(dtype, w, rows * cols).reshape(rows, cols).astype(np.float64)
+    xq = np.empty_like(x, dtype=np.float64)   # the activations as the reference CPU path sees them
+    for r in range(m):
+        if dtype == po.Q8_0:
+            d, qs = po.quantize_q8_0_act(x[r])
+            xq[r] = qs.reshape(-1, 32) .astype(np.float64).reshape(-1) * np.repeat(d.astype(np.float64), 32)
+        else:
+            d, qs, _ = po.quantize_q8k(x[r])
+            xq[r] = qs.astype(np.float64) * np.repeat(d.astype(np.float64), 256)
+    want = xq @ wd.T
+    assert rel_l2(got, want) < 2e-6
+    assert rel_l2(got, x.astype(np.float64) @ wd.T) > 1e-3   # and NOT the unquantised product
+
+
+def test_router_order_and_topk_ties():
+    E, H, k = 16, 256, 4
+    rng = np.random.default_rng(5)
+    W = (rng.standard_normal((E, H)) * 0.02).astype(np.float32)
+    W[7] = W[2]; W[11] = W[2]
+    L = po.Layer(H, 256, E, k, np.zeros(E * 256 * 144 // 256 * H // 1, np.uint8)[:E * 256 * (H // 256) * 144],
+                 np.zeros(E * 256 * (H // 256) * 144, np.uint8), np.zeros(E * H * 144, np.uint8),
+                 po.Q4_K, po.Q4_K, po.Q4_K, W)
+    x = rng.standard_normal((5, H)).astype(np.float32)
+    x[0] = W[2] * 500        # makes experts 2, 7, 11 the (tied) winners of token 0
+    logits = L.router_logits(x)
+    np.testing.assert_allclose(logits, x @ W.T, rtol=0, atol=2e-5)
+    assert np.array_equal(logits[:, 2], logits[:, 7]) and np.array_equal(logits[:, 2], logits[:, 11])
+    idx, w, probs = L.route_topk(logits, with_probs=True)
+    assert list(idx[0][:3]) == [2, 7, 11]            # equal probabilities keep ascending expert order
+    np.testing.assert_allclose(w.sum(1), 1.0, rtol=1e-6)
+    assert (np.diff(w, axis=1) <= 0).all()          # descending weights
+    huge = np.full((1, E), 1000.0, np.float32); huge[0, 3] = -1000.0
+    i2, w2 = L.route_topk(huge)                     # clamp to +-100 keeps softmax finite
+    assert np.isfinite(w2).all() and 3 not in i2[0]
+
+
+@pytest.mark.parametrize("preset", ["q4k", "q4k_m", "q8_0"])
+def test_block_oracle_vs_exact_and_golden(preset):
+    t = synth.make_layer(E=8, k=2, preset=preset, seed=5)
+    ol = oracle_layer(t)
+    x = seeded_x(3, 2048, 9).numpy()
+    out, logits, idx, w = ol.forward(x)
+    assert np.array_equal(idx, LG[preset + "_idx"])
+    np.testing.assert_allclose(out, LG[preset + "_out"], rtol=0, atol=2e-6)
+    exact = ol.forward_exact(x, idx, w)
+    r = rel_l2(out, exact)
+    assert 1e-3 < r < 5e-2    # activation quantisation is visible but small
+    # pieces add up: routed + shared
+    parts = ol.experts_forward(x, idx, w) + ol.shared_forward(x)
+    np.testing.assert_allclose(parts, out, rtol=0, atol=1e-6)
+
+
+def test_rms_norm():
+    x = seeded_x(4, 2048, 3).numpy()
+    wt = np.linspace(0.5, 1.5, 2048).astype(np.float32)
+    y = po.rms_norm(x, wt, 1e-6)
+    want = x / np.sqrt((x.astype(np.float64) ** 2).mean(1, keepdims=True) + 1e-6) * wt
+    np.testing.assert_allclose(y, want, rtol=2e-6)
