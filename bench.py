@@ -44,6 +44,7 @@ def parse():
     ap.add_argument("--layers", type=int, default=4, help="distinct layers cycled through")
     ap.add_argument("--no-sweep", action="store_true", help="skip the batch 1/4/16 sweep")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline")
+    ap.add_argument("--no-graph", action="store_true", help="do not try CUDA-graph replay of the block")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--ep-mode", default="all_to_all", choices=["all_to_all", "all_gather"])
     return ap.parse_args()
@@ -259,6 +260,36 @@ def main():
             ms = float(tms.item())
         return ms, launches
 
+    def time_steps_graph(n_tok, steps, warmup):
+        """Same steps replayed from one CUDA graph that holds one forward per layer (single GPU)."""
+        nb = len(blocks)
+        xs = [make_x(n_tok, 100 + i) for i in range(nb)]
+        out = torch.empty((n_tok, H), dtype=torch.bfloat16, device=dev)
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            for i in range(nb):
+                blocks[i].forward_into(xs[i], out)
+        torch.cuda.current_stream(dev).wait_stream(side)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        before_cap = pm.launch_count()
+        with torch.cuda.graph(g):
+            for i in range(nb):
+                blocks[i].forward_into(xs[i], out)
+        per_replay = pm.launch_count() - before_cap
+        reps = max(1, steps // nb)
+        for _ in range(max(1, warmup // nb)):
+            g.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1), reps * nb, per_replay * reps
+
     def distinct_experts(n_tok):
         """Average number of distinct local experts a step touches (for the algorithmic bytes)."""
         tot = 0
@@ -280,6 +311,15 @@ def main():
     clocks = sampler.stop() if rank == 0 else {}
     ms_per_step = ms / args.steps
     value = batch * N * args.steps / (ms * 1e-3)
+    launch_mode = "direct C-ABI calls"
+    direct = dict(tokens_per_s=value, ms_per_step=ms_per_step)
+    steps_done = args.steps
+    if N == 1 and not args.no_graph:
+        g_ms, g_steps, g_launches = time_steps_graph(batch, args.steps, W)
+        if g_ms / g_steps < ms_per_step:
+            ms, ms_per_step, steps_done, launches = g_ms, g_ms / g_steps, g_steps, g_launches
+            value = batch * g_steps / (g_ms * 1e-3)
+            launch_mode = f"CUDA graph holding one forward per layer ({len(blocks)}), replayed"
 
     # ---- roofline of the dominant kernel (gate/up GEMV): traced pass, events around each kernel
     D = distinct_experts(batch)
@@ -289,12 +329,12 @@ def main():
     gu_bytes += F * (pm.row_bytes(d.sh_gate_dtype, H) + pm.row_bytes(d.sh_up_dtype, H))
     step_bytes = blk0.weight_bytes(int(round(D))) + batch * H * 4  # weights + x in + out (bf16 each)
     phase_ms = {}
+    reps = min(args.steps, 50)
     if N == 1:
         x = make_x(batch, 5)
         out = torch.empty((batch, H), dtype=torch.bfloat16, device=dev)
         for b in blocks:
             b.trace(True)
-        reps = min(args.steps, 50)
         for i in range(reps + 3):
             b = blocks[i % len(blocks)]
             b.forward_into(x, out)
@@ -304,6 +344,27 @@ def main():
                     phase_ms[k_] = phase_ms.get(k_, 0.0) + v / reps
         for b in blocks:
             b.trace(False)
+    else:
+        # expert-parallel: time this rank's expert kernels on the rows the dispatch delivered
+        out = torch.empty((batch, H), dtype=torch.bfloat16, device=dev)
+        for i, e in enumerate(eps):
+            e.forward_into(make_x(batch, 5 + i), out)
+        for b in blocks:
+            b.trace(True)
+        for i in range(reps + 3):
+            e = eps[i % len(eps)]
+            k2 = 2 * TOPK
+            meta = e.recv_meta.view(-1, k2)
+            e.block.experts_forward_batched(e.recv_x.view(-1, H), meta[:, :TOPK].contiguous(),
+                                            meta[:, TOPK:].contiguous().view(torch.float32), TOPK,
+                                            out_dtype=torch.float32)
+            t = e.block.trace_read()
+            if i >= 3:
+                for k_, v in t.items():
+                    phase_ms[k_] = phase_ms.get(k_, 0.0) + v / reps
+        for b in blocks:
+            b.trace(False)
+        gu_bytes = D * F * (pm.row_bytes(d.gate_dtype, H) + pm.row_bytes(d.up_dtype, H))  # no shared expert in this call
     roofline = None
     if phase_ms.get("gate_up"):
         ach = gu_bytes / (phase_ms["gate_up"] * 1e-3) / 1e9
@@ -320,10 +381,15 @@ def main():
     if N == 1 and not args.no_sweep:
         for nb in (1, 4, 16):
             s_ms, _ = time_steps(nb, args.steps, W)
+            us = 1e3 * s_ms / args.steps
+            direct_us = us
+            if not args.no_graph:
+                g_ms, g_steps, _ = time_steps_graph(nb, args.steps, W)
+                us = min(us, 1e3 * g_ms / g_steps)
             Dn = distinct_experts(nb)
             byt = blk0.weight_bytes(int(round(Dn))) + nb * H * 4
-            gbs = byt / (s_ms / args.steps * 1e-3) / 1e9
-            sweep[str(nb)] = dict(tokens_per_s=nb * args.steps / (s_ms * 1e-3), us_per_step=1e3 * s_ms / args.steps,
+            gbs = byt / (us * 1e-6) / 1e9
+            sweep[str(nb)] = dict(tokens_per_s=nb / (us * 1e-6), us_per_step=us, us_per_step_direct=direct_us,
                                   layer_gbs=gbs, layer_frac=gbs / hbm_peak, distinct_experts=Dn)
         sweep[str(batch)] = dict(tokens_per_s=value, us_per_step=1e3 * ms_per_step,
                                  layer_gbs=roofline["layer_gbs"] if roofline else None,
@@ -373,12 +439,12 @@ def main():
         cpu = run_cpu_baseline(host_layer0, batch, args.cpu_seconds)
 
     if rank == 0:
-        line = dict(metric=METRIC, value=value, unit=UNIT, n_gpus=N, steps=args.steps, warmup=W,
+        line = dict(metric=METRIC, value=value, unit=UNIT, n_gpus=N, steps=steps_done, warmup=W,
                     ms_per_step=ms_per_step, higher_is_better=True, scaling="weak", vs_baseline=None,
                     dtype="int8 x int4/6/8 block dots, f32 accumulate", data="synthetic",
                     config=dict(workload=workload_name(batch, N), global_batch=batch * N, layers_cycled=len(blocks),
                                 l2="each step reads a layer not touched for layers-1 steps; per-step weight "
-                                   "traffic exceeds the 126 MB L2", parallelism=f"ep{N}" if N > 1 else "single",
+                                   "traffic exceeds the 126 MB L2", parallelism=f"ep{N}" if N > 1 else "single", launch=launch_mode, direct_calls=direct,
                                 ep_mode=args.ep_mode if N > 1 else None),
                     roofline=roofline, cpu_baseline=cpu, e2e=e2e, gpu_launches=launches, clocks=clocks,
                     sweep=sweep or None)

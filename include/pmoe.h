@@ -148,7 +148,9 @@ int pmoe_shared_forward(pmoe_layer *layer, const void *x, int x_dtype, int n, vo
 /*
  * QMatMul::forward on a quantised tensor (models/with_tracing.rs:324-335):
  * y[m, rows] = x[m, cols] * W[rows, cols]^T, activations quantised to the weight type's
- * dot type as the reference CPU path does.  x, y f32.  m <= 64 per call.
+ * dot type as the reference CPU path does.  x, y f32; w and x 16-byte aligned; cols a multiple
+ * of 256.  Stream-ordered scratch comes from cudaMallocAsync.  Meant for parity checks and
+ * small operands (one warp per output row), not for the block's hot path.
  */
 int pmoe_qmatmul(int device, int dtype, const void *w, size_t rows, size_t cols, const float *x,
                  size_t m, float *y, void *stream);

@@ -524,8 +524,22 @@ int pmoe_reduce_rows(int device, const float *parts, int n_parts, const void *ex
 int pmoe_qmatmul(int device, int dtype, const void *w, size_t rows, size_t cols, const float *x, size_t m, float *y,
                  void *stream)
 {
-    (void)device; (void)dtype; (void)w; (void)rows; (void)cols; (void)x; (void)m; (void)y; (void)stream;
-    return fail(PMOE_ERR_UNSUPPORTED_SHAPE, "pmoe_qmatmul is not available in this build");
+    if (dtype != PMOE_Q4_K && dtype != PMOE_Q6_K && dtype != PMOE_Q8_0)
+        return fail(PMOE_ERR_UNSUPPORTED_DTYPE, "pmoe_qmatmul serves Q4_K, Q6_K and Q8_0 (got %d)", dtype);
+    if (!rows || !cols || cols % 256 || cols > 16384 || rows > (1u << 24) || m > 4096)
+        return fail(PMOE_ERR_UNSUPPORTED_SHAPE, "cols must be a multiple of 256 (<= 16384), m <= 4096");
+    if (!m) return PMOE_OK;
+    if (!w || !x || !y) return fail(PMOE_ERR_INVALID_ARG, "w / x / y is NULL");
+    if (((uintptr_t)w & 15) || ((uintptr_t)x & 15)) return fail(PMOE_ERR_INVALID_ARG, "w and x must be 16-byte aligned");
+    DeviceGuard guard(device);
+    if (!guard.ok) return fail(PMOE_ERR_NO_DEVICE, "cannot select device %d", device);
+    cudaStream_t s = (cudaStream_t)stream;
+    void *scratch = nullptr;
+    CU(cudaMallocAsync(&scratch, qmatmul_scratch_bytes((int)m, (int)cols), s));
+    cudaError_t e = launch_qmatmul(dtype, w, (int)rows, (int)cols, x, (int)m, y, scratch, s);
+    cudaFreeAsync(scratch, s);
+    if (e != cudaSuccess) return fail_cuda(e, "pmoe_qmatmul");
+    return PMOE_OK;
 }
 
 }  // extern "C"

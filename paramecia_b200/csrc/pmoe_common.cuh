@@ -100,17 +100,17 @@ __device__ inline void fence_proxy_async()
 }
 
 // One bounded wait on an mbarrier phase.  Returns false when the limit ran out.
-__device__ inline bool mbar_wait(uint64_t *bar, uint32_t parity, uint32_t max_polls = (1u << 22))
+__device__ inline bool mbar_wait(uint64_t *bar, uint32_t parity, uint32_t max_polls = (1u << 20))
 {
     uint32_t addr = smem_u32(bar);
     for (uint32_t i = 0; i < max_polls; i++) {
         uint32_t done;
         asm volatile(
             "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
             "selp.u32 %0, 1, 0, p;\n\t}"
             : "=r"(done)
-            : "r"(addr), "r"(parity)
+            : "r"(addr), "r"(parity), "r"(20000u)  // may sleep up to ~20 us per try instead of spinning
             : "memory");
         if (done) return true;
     }
@@ -243,6 +243,9 @@ cudaError_t launch_down(const LayerDev &L, const Workspace &ws, const float *w, 
 cudaError_t launch_combine(const LayerDev &L, const Workspace &ws, const uint32_t *idx, int n, int top_k,
                            bool routed, bool shared, void *out, int out_dtype, cudaStream_t s);
 bool gemv_supported(int dtype, int K, int rows, const char **why);
+cudaError_t launch_qmatmul(int dtype, const void *w, int rows, int K, const float *x, int m, float *y, void *scratch,
+                           cudaStream_t s);
+size_t qmatmul_scratch_bytes(int m, int K);
 // pmoe_codec.cu
 cudaError_t launch_dequantize(int dtype, const void *blocks, size_t n_elems, float *out, cudaStream_t s);
 cudaError_t launch_reduce_rows(const float *parts, int R, const void *extra, int extra_dtype, int n, int H, void *out,

@@ -654,6 +654,75 @@ cudaError_t launch_down(const LayerDev &L, const Workspace &ws, const float *w, 
     return launch_gemv<1>(A, routed ? L.down_dtype : L.sh_down_dtype, shared ? L.sh_down_dtype : 0, s);
 }
 
+// ---------------------------------------------------------------- stand-alone quantised mat-mul
+// QMatMul::forward for one quantised matrix: y[m, rows] = x[m, cols] * W[rows, cols]^T with the
+// activations quantised to the weight type's dot type.  One warp per output row, weights read
+// straight from global memory; meant for parity checks and small operands, not for the block.
+__global__ void __launch_bounds__(64) k_quant_rows(const float *__restrict__ x, int K, bool kq, QAct a8k, QAct a80)
+{
+    block_quant_row(x + (size_t)blockIdx.x * K, K, kq, !kq, a8k, a80, (size_t)blockIdx.x, threadIdx.x >> 5, 2,
+                    threadIdx.x & 31);
+}
+
+template <int DT>
+__global__ void __launch_bounds__(128) k_qmatmul(const uint8_t *__restrict__ w, int rows, int K, QAct in, int m,
+                                                 float *__restrict__ y)
+{
+    using Act = typename Tr<DT>::Act;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row = blockIdx.x * 4 + warp;
+    const int t0 = blockIdx.y * TG;
+    if (row >= rows) return;
+    const uint8_t *rp = w + (size_t)row * row_bytes(DT, K);
+    float acc[TG];
+#pragma unroll
+    for (int t = 0; t < TG; t++) acc[t] = 0.f;
+    for (int u = lane; u < K / Tr<DT>::UNIT; u += 32) {
+        Act act[TG];
+#pragma unroll
+        for (int t = 0; t < TG; t++) {
+            if (t0 + t < m) load_act<DT>(in, (size_t)(t0 + t), K, u, act[t]);
+            else zero_act<DT>(act[t]);
+        }
+        const typename Dot<DT>::Pre pre = Dot<DT>::pre(u);
+        Dot<DT>::template run<TG>(rp, pre, act, acc);
+    }
+#pragma unroll
+    for (int t = 0; t < TG; t++) {
+        float v = acc[t];
+#pragma unroll
+        for (int s = 16; s >= 1; s >>= 1) v += __shfl_xor_sync(0xffffffffu, v, s);
+        if (lane == 0 && t0 + t < m) y[(size_t)(t0 + t) * rows + row] = v;
+    }
+}
+
+cudaError_t launch_qmatmul(int dtype, const void *w, int rows, int K, const float *x, int m, float *y, void *scratch,
+                           cudaStream_t s)
+{
+    // scratch layout: qs int8 [m,K] | d f32 [m, K/32] | bsums i16 [m, K/16]
+    QAct a{};
+    uint8_t *p = (uint8_t *)scratch;
+    a.qs = (int8_t *)p;
+    p += ((size_t)m * K + 255) / 256 * 256;
+    a.d = (float *)p;
+    p += ((size_t)m * (K / 32) * 4 + 255) / 256 * 256;
+    a.bsums = (int16_t *)p;
+    const bool kq = is_kquant(dtype);
+    k_quant_rows<<<m, 64, 0, s>>>(x, K, kq, a, a);
+    dim3 grid((rows + 3) / 4, (m + TG - 1) / TG);
+    const uint8_t *wb = (const uint8_t *)w;
+    if (dtype == PMOE_Q4_K) k_qmatmul<PMOE_Q4_K><<<grid, 128, 0, s>>>(wb, rows, K, a, m, y);
+    else if (dtype == PMOE_Q6_K) k_qmatmul<PMOE_Q6_K><<<grid, 128, 0, s>>>(wb, rows, K, a, m, y);
+    else k_qmatmul<PMOE_Q8_0><<<grid, 128, 0, s>>>(wb, rows, K, a, m, y);
+    count_launch(2);
+    return cudaGetLastError();
+}
+
+size_t qmatmul_scratch_bytes(int m, int K)
+{
+    return ((size_t)m * K + 255) / 256 * 256 + ((size_t)m * (K / 32) * 4 + 255) / 256 * 256 + (size_t)m * (K / 16) * 2 + 256;
+}
+
 // ---------------------------------------------------------------- re-quantise the activated rows
 // One CTA per row of act[., F]: routed pair rows that belong to a local expert, then the
 // shared expert's rows.  The block type follows the down matrix that will consume the row.

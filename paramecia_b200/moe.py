@@ -91,6 +91,17 @@ def dequantize(blocks: torch.Tensor, dtype: int, n_elems: int) -> torch.Tensor:
     return out
 
 
+def qmatmul(w: "QTensor", x: torch.Tensor) -> torch.Tensor:
+    """QMatMul::forward for a quantised [rows, cols] tensor: x [m, cols] f32 -> [m, rows] f32."""
+    rows, cols = w.shape
+    x = x.to(torch.float32).reshape(-1, cols).contiguous()
+    data = w.data.to(x.device)
+    y = torch.empty((x.shape[0], rows), dtype=torch.float32, device=x.device)
+    check(lib().pmoe_qmatmul(x.device.index or 0, w.dtype, data.data_ptr(), rows, cols, x.data_ptr(), x.shape[0],
+                             y.data_ptr(), _stream_ptr(x.device)))
+    return y
+
+
 def add_rms_norm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: Optional[torch.Tensor],
                  eps: float) -> Tuple[torch.Tensor, torch.Tensor]:
     """(resid + delta, RmsNorm(resid + delta)): quantized_nn.rs:172-190 with the residual add

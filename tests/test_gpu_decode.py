@@ -188,3 +188,13 @@ def test_add_rms_norm():
     want = po.rms_norm(want_resid, wt.cpu().numpy(), 1e-6)
     assert np.array_equal(resid.cpu().numpy(), want_resid)
     np.testing.assert_allclose(y.cpu().numpy(), want, rtol=2e-6, atol=1e-7)
+
+
+@pytest.mark.parametrize("dtype,rows,cols", [(pm.Q4_K, 64, 2048), (pm.Q6_K, 128, 512), (pm.Q8_0, 32, 1024)])
+def test_qmatmul_entry_point(dtype, rows, cols):
+    rng = np.random.default_rng(11)
+    w = po.quantize(dtype, (rng.standard_normal(rows * cols) * 0.02).astype(np.float32))
+    x = rng.standard_normal((5, cols)).astype(np.float32)
+    want = po.qmatmul(dtype, w, rows, cols, x)
+    got = pm.qmatmul(pm.QTensor(w, dtype, (rows, cols)), torch.from_numpy(x).to(DEV)).cpu().numpy()
+    assert rel_l2(got, want) <= 2e-6
