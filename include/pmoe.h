@@ -155,6 +155,31 @@ int pmoe_shared_forward(pmoe_layer *layer, const void *x, int x_dtype, int n, vo
 int pmoe_qmatmul(int device, int dtype, const void *w, size_t rows, size_t cols, const float *x,
                  size_t m, float *y, void *stream);
 
+/*
+ * pmoe_qmatmul for hosts that must not allocate.  No counterpart in the reference: paramecia
+ * lets candle allocate freely.  It is for embedders that have already handed every byte of
+ * device memory to their own pool (a serving process that sized its KV cache to fill the
+ * card, say) or that forbid allocator calls on the request path because an allocation can
+ * stall every stream of the process.  This entry point calls neither cudaMalloc, cudaFree,
+ * their stream-ordered forms nor any allocating library routine: the quantised activations
+ * go into a 96 KB buffer compiled into the library (held by every GPU that loads it, until
+ * the process exits).
+ *
+ * Limits: the rows must fit that buffer -- roughly m * cols <= 80 000, e.g. 32 rows of 2048
+ * columns or 128 rows of 512 -- otherwise PMOE_ERR_TOO_MANY_TOKENS with the sizes in
+ * pmoe_last_error(); nothing is truncated.  Same arguments, results and other errors as
+ * pmoe_qmatmul.
+ *
+ * The first call on a device looks up the buffer's device address (one runtime query, no
+ * allocation); make that first call during start-up, before any stream capture begins.
+ * All calls on a device share the one buffer: it keeps the previous call's contents, every
+ * byte a call reads is written by that call first (nothing relies on zeros), and two calls
+ * that overlap on the GPU -- different streams, or different threads without ordering --
+ * race on it.  Order them on one stream or with events.
+ */
+int pmoe_qmatmul_noalloc(int device, int dtype, const void *w, size_t rows, size_t cols,
+                         const float *x, size_t m, float *y, void *stream);
+
 /* QTensor::dequantize: blocks -> f32 (the "dequantised weights bit-exact" check). */
 int pmoe_dequantize(int device, int dtype, const void *blocks, size_t n_elems, float *out,
                     void *stream);

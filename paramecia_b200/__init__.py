@@ -10,8 +10,8 @@ import fails if ``libpmoe.so`` has not been built, and constructing a layer fail
 """
 from ._lib import (PmoeError, lib, lib_path, launch_count, F32, F16, BF16, Q8_0, Q4_K, Q6_K,
                    block_size, type_size, row_bytes)
-from .moe import QTensor, MoeBlock, SharedExpertWeights, dequantize, add_rms_norm, qmatmul
+from .moe import QTensor, MoeBlock, SharedExpertWeights, dequantize, add_rms_norm, qmatmul, qmatmul_noalloc
 
 __all__ = ["PmoeError", "lib", "lib_path", "launch_count", "F32", "F16", "BF16", "Q8_0", "Q4_K", "Q6_K",
            "block_size", "type_size", "row_bytes", "QTensor", "MoeBlock", "SharedExpertWeights",
-           "dequantize", "add_rms_norm", "qmatmul"]
+           "dequantize", "add_rms_norm", "qmatmul", "qmatmul_noalloc"]

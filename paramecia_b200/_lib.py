@@ -57,6 +57,7 @@ SYMBOLS = [
     ("pmoe_experts_forward", _I, [_V, _V, _I, _V, _V, _I, _I, _V, _I, _V]),
     ("pmoe_shared_forward", _I, [_V, _V, _I, _I, _V, _I, _V]),
     ("pmoe_qmatmul", _I, [_I, _I, _V, _Z, _Z, _V, _Z, _V, _V]),
+    ("pmoe_qmatmul_noalloc", _I, [_I, _I, _V, _Z, _Z, _V, _Z, _V, _V]),
     ("pmoe_dequantize", _I, [_I, _I, _V, _Z, _V, _V]),
     ("pmoe_reduce_rows", _I, [_I, _V, _I, _V, _I, _I, _I, _V, _I, _V]),
     ("pmoe_add_rms_norm", _I, [_I, _V, _V, _V, _I, _I, C.c_float, _V, _V, _V]),

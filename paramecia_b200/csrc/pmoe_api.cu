@@ -542,4 +542,30 @@ int pmoe_qmatmul(int device, int dtype, const void *w, size_t rows, size_t cols,
     return PMOE_OK;
 }
 
+int pmoe_qmatmul_noalloc(int device, int dtype, const void *w, size_t rows, size_t cols, const float *x, size_t m,
+                         float *y, void *stream)
+{
+    if (dtype != PMOE_Q4_K && dtype != PMOE_Q6_K && dtype != PMOE_Q8_0)
+        return fail(PMOE_ERR_UNSUPPORTED_DTYPE, "pmoe_qmatmul_noalloc serves Q4_K, Q6_K and Q8_0 (got %d)", dtype);
+    if (!rows || !cols || cols % 256 || rows > (1u << 24))
+        return fail(PMOE_ERR_UNSUPPORTED_SHAPE, "cols must be a non-zero multiple of 256");
+    if (!m) return PMOE_OK;
+    if (!w || !x || !y) return fail(PMOE_ERR_INVALID_ARG, "w / x / y is NULL");
+    if (((uintptr_t)w & 15) || ((uintptr_t)x & 15)) return fail(PMOE_ERR_INVALID_ARG, "w and x must be 16-byte aligned");
+    DeviceGuard guard(device);
+    if (!guard.ok) return fail(PMOE_ERR_NO_DEVICE, "cannot select device %d", device);
+    void *scratch = nullptr;
+    size_t cap = 0;
+    cudaError_t e = qmatmul_static_scratch(device, &scratch, &cap);
+    if (e != cudaSuccess) return fail_cuda(e, "cudaGetSymbolAddress(static scratch)");
+    if (m > 4096 || cols > 65536 || qmatmul_scratch_bytes((int)m, (int)cols) > cap)
+        return fail(PMOE_ERR_TOO_MANY_TOKENS,
+                    "m = %zu rows of %zu columns need %zu bytes of scratch; the built-in buffer holds %zu "
+                    "(m * cols <= about 80000, e.g. 32 rows of 2048); use pmoe_qmatmul for larger operands",
+                    m, cols, qmatmul_scratch_bytes((int)(m > 4096 ? 4096 : m), (int)(cols > 65536 ? 65536 : cols)), cap);
+    e = launch_qmatmul(dtype, w, (int)rows, (int)cols, x, (int)m, y, scratch, (cudaStream_t)stream);
+    if (e != cudaSuccess) return fail_cuda(e, "pmoe_qmatmul_noalloc");
+    return PMOE_OK;
+}
+
 }  // extern "C"

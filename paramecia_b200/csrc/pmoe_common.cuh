@@ -246,6 +246,7 @@ bool gemv_supported(int dtype, int K, int rows, const char **why);
 cudaError_t launch_qmatmul(int dtype, const void *w, int rows, int K, const float *x, int m, float *y, void *scratch,
                            cudaStream_t s);
 size_t qmatmul_scratch_bytes(int m, int K);
+cudaError_t qmatmul_static_scratch(int device, void **ptr, size_t *bytes);
 // pmoe_codec.cu
 cudaError_t launch_dequantize(int dtype, const void *blocks, size_t n_elems, float *out, cudaStream_t s);
 cudaError_t launch_reduce_rows(const float *parts, int R, const void *extra, int extra_dtype, int n, int H, void *out,

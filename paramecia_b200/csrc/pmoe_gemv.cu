@@ -723,6 +723,33 @@ size_t qmatmul_scratch_bytes(int m, int K)
     return ((size_t)m * K + 255) / 256 * 256 + ((size_t)m * (K / 32) * 4 + 255) / 256 * 256 + (size_t)m * (K / 16) * 2 + 256;
 }
 
+// ---------------------------------------------------------------- fixed scratch for callers that must not allocate
+// The quantised activations of pmoe_qmatmul_noalloc live here instead of in stream-ordered
+// allocations.  Every GPU that loads the library carries these 96 KB until the process exits.
+// In host code `g_qmm_scratch` is only a handle for the runtime, never a device address:
+// the address a kernel may use comes from cudaGetSymbolAddress, asked once per device with
+// that device current.
+constexpr size_t QMM_STATIC_BYTES = 96 * 1024;
+static __device__ __align__(256) unsigned char g_qmm_scratch[QMM_STATIC_BYTES];
+
+constexpr int QMM_MAX_DEVICES = 64;
+static void *g_qmm_scratch_addr[QMM_MAX_DEVICES];  // device address of g_qmm_scratch, per ordinal
+
+cudaError_t qmatmul_static_scratch(int device, void **ptr, size_t *bytes)
+{
+    *ptr = nullptr;
+    *bytes = QMM_STATIC_BYTES;
+    if (device < 0 || device >= QMM_MAX_DEVICES) return cudaErrorInvalidDevice;
+    if (!g_qmm_scratch_addr[device]) {  // set-up: the calling thread has made `device` current
+        void *p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, g_qmm_scratch);
+        if (e != cudaSuccess) return e;
+        g_qmm_scratch_addr[device] = p;
+    }
+    *ptr = g_qmm_scratch_addr[device];
+    return cudaSuccess;
+}
+
 // ---------------------------------------------------------------- re-quantise the activated rows
 // One CTA per row of act[., F]: routed pair rows that belong to a local expert, then the
 // shared expert's rows.  The block type follows the down matrix that will consume the row.

@@ -102,6 +102,18 @@ def qmatmul(w: "QTensor", x: torch.Tensor) -> torch.Tensor:
     return y
 
 
+def qmatmul_noalloc(w: "QTensor", x: torch.Tensor, y: torch.Tensor) -> torch.Tensor:
+    """`qmatmul` through the entry point that allocates nothing: the caller owns x [m, cols] f32 and
+    y [m, rows] f32 (both CUDA, contiguous) and the quantised activations use the library's built-in
+    96 KB buffer, so m * cols is limited (about 80 000).  Calls on one device must not overlap."""
+    rows, cols = w.shape
+    if not (x.is_cuda and y.is_cuda and x.is_contiguous() and y.is_contiguous() and w.data.is_cuda):
+        raise ValueError("qmatmul_noalloc takes contiguous CUDA tensors it does not have to copy")
+    check(lib().pmoe_qmatmul_noalloc(x.device.index or 0, w.dtype, w.data.data_ptr(), rows, cols, x.data_ptr(),
+                                     x.shape[0], y.data_ptr(), _stream_ptr(x.device)))
+    return y
+
+
 def add_rms_norm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: Optional[torch.Tensor],
                  eps: float) -> Tuple[torch.Tensor, torch.Tensor]:
     """(resid + delta, RmsNorm(resid + delta)): quantized_nn.rs:172-190 with the residual add
