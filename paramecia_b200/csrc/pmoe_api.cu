@@ -3,6 +3,7 @@
 #include <atomic>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <string>
 #include <vector>
@@ -122,6 +123,7 @@ void carve_workspace(pmoe_layer *L, Carver &c)
     w.groups.active = c.take<int>(El);
     w.groups.n_active = c.take<int>(1);
     w.groups.cost_prefix = c.take<int>(El + 1);
+    w.groups.tile_prefix = c.take<int>(El + 1);
     w.act = c.take<float>(rows * F);
     w.act_q8k.qs = c.take<int8_t>(rows * F);
     w.act_q8k.d = c.take<float>(rows * (F / QK_K));
@@ -216,7 +218,14 @@ int run_experts(pmoe_layer *L, const void *x, int x_dtype, const uint32_t *idx, 
         PHASE(L, 0, s, launch_prep(d, L->ws, x, x_dtype, n, nd.q8k, nd.q80, shared, s));
     }
     if (routed) PHASE(L, 3, s, launch_group(d, L->ws, idx, n, top_k, s));
-    PHASE(L, 4, s, launch_gate_up(d, L->ws, n, top_k, routed, shared, s));
+    // prefill: many tokens per expert -> grouped tensor-core GEMM; decode: streaming GEMV
+    const char *force = getenv("PMOE_PREFILL");
+    const bool prefill = prefill_supported(d, routed, shared) &&
+                         (force ? atoi(force) != 0 : (long)n * top_k >= 8L * d.E_local && n >= 512);
+    if (prefill)
+        PHASE(L, 4, s, launch_gate_up_prefill(d, L->ws, n, top_k, routed, shared, s));
+    else
+        PHASE(L, 4, s, launch_gate_up(d, L->ws, n, top_k, routed, shared, s));
     PHASE(L, 5, s, launch_act_quant(d, L->ws, idx, n, top_k, routed, shared, s));
     PHASE(L, 6, s, launch_down(d, L->ws, w, n, top_k, routed, shared, s));
     PHASE(L, 7, s, launch_combine(d, L->ws, idx, n, top_k, routed, shared, out, out_dtype, s));

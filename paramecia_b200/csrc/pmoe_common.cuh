@@ -193,9 +193,11 @@ struct Groups {
     int *active;      // [E_local] local expert ids with count > 0, ascending
     int *n_active;    // [1]
     int *cost_prefix; // [E_local + 1] exclusive prefix over active slots of ceil(count / GEMV_TG)
+    int *tile_prefix; // [E_local + 1] exclusive prefix over active slots of ceil(count / PREFILL_NT)
 };
 
-constexpr int GEMV_TG = 2;  // tokens one GEMV pass handles; the unit of the work partition
+constexpr int GEMV_TG = 2;      // tokens one GEMV pass handles; the unit of the work partition
+constexpr int PREFILL_NT = 64;  // tokens per tile of the prefill GEMMs
 
 // Everything a forward call needs, resolved to raw pointers.
 struct LayerDev {
@@ -247,6 +249,10 @@ cudaError_t launch_qmatmul(int dtype, const void *w, int rows, int K, const floa
                            cudaStream_t s);
 size_t qmatmul_scratch_bytes(int m, int K);
 cudaError_t qmatmul_static_scratch(int device, void **ptr, size_t *bytes);
+// pmoe_prefill.cu
+bool prefill_supported(const LayerDev &L, bool routed, bool shared);
+cudaError_t launch_gate_up_prefill(const LayerDev &L, const Workspace &ws, int n, int top_k, bool routed, bool shared,
+                                   cudaStream_t s);
 // pmoe_codec.cu
 cudaError_t launch_dequantize(int dtype, const void *blocks, size_t n_elems, float *out, cudaStream_t s);
 cudaError_t launch_reduce_rows(const float *parts, int R, const void *extra, int extra_dtype, int n, int H, void *out,

@@ -1,0 +1,395 @@
+// Prefill path of the MoE block: token-sorted grouped GEMMs on the 5th-generation tensor
+// cores (tcgen05.mma, accumulators in tensor memory).
+//
+// Reference semantics are those of the decode kernels (MoeExperts::forward_batched,
+// paramecia-model/src/qwen3_next.rs:1347-1394; the CPU arithmetic of tokio_experts.rs:157-204):
+// activations quantised to Q8_K, integer block dot products, f32 scales.  A tensor-core GEMM
+// over dequantised fp16/bf16 operands does NOT meet the parity bar for gate/up: an error of
+// 3e-4 in silu(gate)*up flips enough int8 roundings of the re-quantised activation to put the
+// block output 3e-3 away from the reference.  The gate/up GEMM therefore stays in integers:
+//
+//   k_gu_prefill   Q4_K gate+up.  For one 256-wide block of the reduction dimension the
+//                  weight sc_j * q (0..945) is split into two byte digits, q*(sc_j & 7) and
+//                  q*(sc_j >> 3), each a byte-wise product of four packed nibbles with a small
+//                  scalar; two kind::i8 MMAs (u8 x s8 -> s32) per 32 weights give the exact
+//                  integer block sums S = D0 + 8*D1.  The minimum term sum_j m_j * bsum_j comes
+//                  from two more small MMAs over the 16 partial sums of a Q8_K block, split
+//                  into digits bsum = 64*h + l.  After every block the epilogue warps read the
+//                  s32 accumulators from tensor memory and add
+//                  d_x * (d_w * S - dmin_w * M) to f32 accumulators in registers -- the same
+//                  f32 expression the decode kernel evaluates.  silu(gate)*up is formed at the
+//                  end (gate rows and up rows share one M = 128 tile) and written as f32.
+//   k_down_prefill down projection over the re-quantised activation (see below).
+//
+// Tiles: M = 128 weight rows (64 gate + 64 up), N = 64 tokens of one expert, operands staged in
+// shared memory in the K-major core-matrix layout (8 rows x 16 bytes, no swizzle).  Every wait
+// is bounded and reports through the status word; tensor memory is freed on every path.
+#include "pmoe_common.cuh"
+
+namespace pmoe {
+
+constexpr int PF_NT = 64;        // tokens per tile (MMA N)
+constexpr int PF_M = 128;        // rows per tile (MMA M): 64 gate + 64 up
+constexpr int PF_THREADS = 128;
+constexpr int PF_TMEM_COLS = 256;  // D0, D1, Dh, Dl: 4 x 64 columns of s32
+
+// ---------------------------------------------------------------- tcgen05 wrappers
+__device__ inline void tmem_alloc(uint32_t *smem_dst, uint32_t cols)
+{
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_dst)), "r"(cols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ inline void tmem_dealloc(uint32_t addr, uint32_t cols)
+{
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+__device__ inline void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ inline void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ inline void tc_commit(uint64_t *bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+                 : "memory");
+}
+// D[tmem] (+)= A[smem] * B[smem], 8-bit integer operands, s32 accumulate
+__device__ inline void mma_i8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ inline void mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// 16 consecutive 32-bit columns of this warp's 32 lanes
+__device__ inline void tmem_ld16(uint32_t taddr, uint32_t (&v)[16])
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ inline void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor, K-major, no swizzle: core matrices of 8 rows x 16 bytes;
+// lbo = bytes between the two 16-byte K chunks of one MMA, sbo = bytes between 8-row groups.
+__device__ inline uint64_t smem_desc(const void *p, uint32_t lbo, uint32_t sbo)
+{
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_u32(p) & 0x3FFFF) >> 4);
+    d |= (uint64_t)(lbo >> 4) << 16;
+    d |= (uint64_t)(sbo >> 4) << 32;
+    d |= (uint64_t)1 << 46;  // descriptor version of this architecture
+    return d;
+}
+// Instruction descriptor: D format (1 = f32, 2 = s32) | A/B formats | N/8 | M/16; K-major A and B.
+__device__ constexpr uint32_t make_idesc(uint32_t cfmt, uint32_t afmt, uint32_t bfmt, uint32_t n, uint32_t m)
+{
+    return (cfmt << 4) | (afmt << 7) | (bfmt << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);
+}
+
+// byte offset of (row, kbyte) inside a K-major core-matrix tile with `rows` rows
+__device__ inline uint32_t core_off(int rows, int row, int kbyte)
+{
+    return (uint32_t)((kbyte >> 4) * (rows * 16) + (row >> 3) * 128 + (row & 7) * 16 + (kbyte & 15));
+}
+
+// ---------------------------------------------------------------- gate/up, Q4_K, exact integer block sums
+struct GuArgs {
+    const uint8_t *gate, *up;      // routed [E_local, F, H] Q4_K
+    size_t expert_bytes;
+    const uint8_t *sgate, *sup;    // shared expert (may be null)
+    int has_shared, routed;
+    int n, top_k, H, F;
+    Groups g;
+    const int *tile_prefix;        // [n_active + 1] exclusive prefix of ceil(count / PF_NT) over active slots
+    QAct xq;                       // Q8_K rows of the input [n, H]
+    float *act;                    // [n*(k+1), F]
+    DevStatus *status;
+};
+
+struct GuSmem {
+    uint8_t a0[PF_M * 256];
+    uint8_t a1[PF_M * 256];
+    uint8_t b[PF_NT * 256];
+    uint8_t am[PF_M * 32];
+    uint8_t bh[PF_NT * 32];
+    uint8_t bl[PF_NT * 32];
+    float dx[PF_NT];
+    int row_in[PF_NT];
+    int row_out[PF_NT];
+    uint64_t bar;
+    uint32_t tmem_base;
+    int slot, tile_in_slot;
+};
+
+__global__ void __launch_bounds__(PF_THREADS, 2) k_gu_prefill(const GuArgs A)
+{
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    GuSmem &S = *reinterpret_cast<GuSmem *>(smem_raw);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+    // ---- which (expert slot, token tile) is this CTA's
+    const int n_active = A.routed ? *A.g.n_active : 0;
+    const int routed_tiles = n_active ? A.tile_prefix[n_active] : 0;
+    const int shared_tiles = A.has_shared ? (A.n + PF_NT - 1) / PF_NT : 0;
+    const int tile = blockIdx.y;
+    if (tile >= routed_tiles + shared_tiles) return;
+    if (tid == 0) {
+        if (tile < routed_tiles) {
+            int lo = 0, hi = n_active - 1;  // largest slot with prefix[slot] <= tile
+            while (lo < hi) {
+                const int mid = (lo + hi + 1) >> 1;
+                if (A.tile_prefix[mid] <= tile) lo = mid; else hi = mid - 1;
+            }
+            S.slot = lo;
+            S.tile_in_slot = tile - A.tile_prefix[lo];
+        } else {
+            S.slot = -1;
+            S.tile_in_slot = tile - routed_tiles;
+        }
+        mbar_init(&S.bar, 1);
+        fence_mbar_init();
+    }
+    if (warp == 0) tmem_alloc(&S.tmem_base, PF_TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = S.tmem_base;
+    const int slot = S.slot, t0 = S.tile_in_slot * PF_NT;
+    const bool is_shared = slot < 0;
+    int m;
+    const int *list = nullptr;
+    const uint8_t *wg, *wu;
+    if (is_shared) {
+        m = A.n;
+        wg = A.sgate; wu = A.sup;
+    } else {
+        const int e = A.g.active[slot];
+        m = A.g.count[e];
+        list = A.g.pairs + A.g.offset[e];
+        wg = A.gate + (size_t)e * A.expert_bytes;
+        wu = A.up + (size_t)e * A.expert_bytes;
+    }
+    const int cnt = m - t0 < PF_NT ? m - t0 : PF_NT;
+    if (tid < PF_NT) {
+        int rin = -1, rout = -1;
+        if (tid < cnt) {
+            if (is_shared) { rin = t0 + tid; rout = A.n * A.top_k + rin; }
+            else { const int p = list[t0 + tid]; rin = p / A.top_k; rout = p; }
+        }
+        S.row_in[tid] = rin;
+        S.row_out[tid] = rout;
+    }
+    __syncthreads();
+
+    // this thread's weight row: threads 0..63 gate rows, 64..127 up rows of the same 64 outputs
+    const int f0 = blockIdx.x * 64;
+    const int nblk = A.H / QK_K;
+    const uint8_t *wrow = (tid < 64 ? wg : wu) + (size_t)(f0 + (tid & 63)) * nblk * Q4_K_BYTES;
+
+    constexpr uint32_t IDESC_UU_S = make_idesc(2, 0, 1, PF_NT, PF_M);  // u8 x s8
+    constexpr uint32_t IDESC_UU_U = make_idesc(2, 0, 0, PF_NT, PF_M);  // u8 x u8
+    float acc[PF_NT];
+#pragma unroll
+    for (int i = 0; i < PF_NT; i++) acc[i] = 0.f;
+    uint32_t phase = 0;
+    bool ok = true;
+
+    for (int b = 0; b < nblk && ok; b++) {
+        // ---- A: two digit tiles and the mins tile for this thread's row
+        const uint4 *blk = reinterpret_cast<const uint4 *>(wrow + (size_t)b * Q4_K_BYTES);
+        const uint4 hdr = blk[0];
+        const float dw = half_bits_to_float((uint16_t)(hdr.x & 0xffffu));
+        const float dmin = half_bits_to_float((uint16_t)(hdr.x >> 16));
+        // 6-bit scales and mins as bytes: sc[0..3] in sca, sc[4..7] in scb, likewise mins
+        const uint32_t u0 = hdr.y, u1 = hdr.z, u2 = hdr.w;
+        const uint32_t sca = u0 & 0x3F3F3F3Fu, mna = u1 & 0x3F3F3F3Fu;
+        const uint32_t scb = (u2 & 0x0F0F0F0Fu) | ((u0 >> 2) & 0x30303030u);
+        const uint32_t mnb = ((u2 >> 4) & 0x0F0F0F0Fu) | ((u1 >> 2) & 0x30303030u);
+#pragma unroll
+        for (int gq = 0; gq < 4; gq++) {
+            const uint4 qa = blk[1 + 2 * gq], qb = blk[2 + 2 * gq];
+            const uint32_t w[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+            const uint32_t scw = gq < 2 ? sca : scb;
+            const uint32_t sc_lo = (scw >> (16 * (gq & 1))) & 0xFFu;        // sub-block 2*gq   (low nibbles)
+            const uint32_t sc_hi = (scw >> (16 * (gq & 1) + 8)) & 0xFFu;    // sub-block 2*gq+1 (high nibbles)
+            uint32_t d0[8], d1[8], e0[8], e1[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const uint32_t lo = w[i] & 0x0F0F0F0Fu, hi = (w[i] >> 4) & 0x0F0F0F0Fu;
+                d0[i] = lo * (sc_lo & 7u); d1[i] = lo * (sc_lo >> 3);
+                e0[i] = hi * (sc_hi & 7u); e1[i] = hi * (sc_hi >> 3);
+            }
+            // sub-block j occupies K bytes 32j .. 32j+31 = chunks 2j, 2j+1
+            const int j0 = 2 * gq, j1 = 2 * gq + 1;
+            *reinterpret_cast<uint4 *>(S.a0 + core_off(PF_M, tid, 32 * j0)) = make_uint4(d0[0], d0[1], d0[2], d0[3]);
+            *reinterpret_cast<uint4 *>(S.a0 + core_off(PF_M, tid, 32 * j0 + 16)) = make_uint4(d0[4], d0[5], d0[6], d0[7]);
+            *reinterpret_cast<uint4 *>(S.a1 + core_off(PF_M, tid, 32 * j0)) = make_uint4(d1[0], d1[1], d1[2], d1[3]);
+            *reinterpret_cast<uint4 *>(S.a1 + core_off(PF_M, tid, 32 * j0 + 16)) = make_uint4(d1[4], d1[5], d1[6], d1[7]);
+            *reinterpret_cast<uint4 *>(S.a0 + core_off(PF_M, tid, 32 * j1)) = make_uint4(e0[0], e0[1], e0[2], e0[3]);
+            *reinterpret_cast<uint4 *>(S.a0 + core_off(PF_M, tid, 32 * j1 + 16)) = make_uint4(e0[4], e0[5], e0[6], e0[7]);
+            *reinterpret_cast<uint4 *>(S.a1 + core_off(PF_M, tid, 32 * j1)) = make_uint4(e1[0], e1[1], e1[2], e1[3]);
+            *reinterpret_cast<uint4 *>(S.a1 + core_off(PF_M, tid, 32 * j1 + 16)) = make_uint4(e1[4], e1[5], e1[6], e1[7]);
+        }
+        {   // mins, each repeated for the two 16-wide halves of its sub-block: m0 m0 m1 m1 ... m7 m7, then zeros
+            const uint32_t w0 = __byte_perm(mna, 0, 0x1100), w1 = __byte_perm(mna, 0, 0x3322);
+            const uint32_t w2 = __byte_perm(mnb, 0, 0x1100), w3 = __byte_perm(mnb, 0, 0x3322);
+            *reinterpret_cast<uint4 *>(S.am + core_off(PF_M, tid, 0)) = make_uint4(w0, w1, w2, w3);
+            *reinterpret_cast<uint4 *>(S.am + core_off(PF_M, tid, 16)) = make_uint4(0, 0, 0, 0);
+        }
+        // ---- B: the tile's quantised activations for this block; token = tid / 2, half = tid & 1
+        {
+            const int tk = tid >> 1, half = tid & 1;
+            const int rin = S.row_in[tk];
+            const uint4 *src = rin >= 0 ? reinterpret_cast<const uint4 *>(A.xq.qs + (size_t)rin * A.H + b * QK_K + 128 * half)
+                                        : nullptr;
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const uint4 v = src ? src[i] : make_uint4(0, 0, 0, 0);
+                *reinterpret_cast<uint4 *>(S.b + core_off(PF_NT, tk, 128 * half + 16 * i)) = v;
+            }
+        }
+        if (tid < PF_NT) {  // partial sums of 16 quants as two digits: bsum = 64*h + l, l in [0,63]
+            const int rin = S.row_in[tid];
+            uint32_t hw[4] = {0, 0, 0, 0}, lw[4] = {0, 0, 0, 0};
+            float dx = 0.f;
+            if (rin >= 0) {
+                const int16_t *bs = A.xq.bsums + (size_t)rin * (A.H / 16) + b * 16;
+#pragma unroll
+                for (int i = 0; i < 16; i++) {
+                    const int v = bs[i];
+                    hw[i >> 2] |= (uint32_t)((v >> 6) & 0xFF) << (8 * (i & 3));
+                    lw[i >> 2] |= (uint32_t)(v & 63) << (8 * (i & 3));
+                }
+                dx = A.xq.d[(size_t)rin * nblk + b];
+            }
+            *reinterpret_cast<uint4 *>(S.bh + core_off(PF_NT, tid, 0)) = make_uint4(hw[0], hw[1], hw[2], hw[3]);
+            *reinterpret_cast<uint4 *>(S.bh + core_off(PF_NT, tid, 16)) = make_uint4(0, 0, 0, 0);
+            *reinterpret_cast<uint4 *>(S.bl + core_off(PF_NT, tid, 0)) = make_uint4(lw[0], lw[1], lw[2], lw[3]);
+            *reinterpret_cast<uint4 *>(S.bl + core_off(PF_NT, tid, 16)) = make_uint4(0, 0, 0, 0);
+            S.dx[tid] = dx;
+        }
+        fence_proxy_async();   // generic-proxy writes above become visible to the tensor core
+        tc_fence_before();
+        __syncthreads();
+        // ---- MMAs of this block, issued by one thread
+        if (tid == 0) {
+            tc_fence_after();
+            for (int ks = 0; ks < 8; ks++) {  // 32 bytes of K per instruction
+                const uint64_t da0 = smem_desc(S.a0 + ks * 2 * (PF_M * 16), PF_M * 16, 128);
+                const uint64_t da1 = smem_desc(S.a1 + ks * 2 * (PF_M * 16), PF_M * 16, 128);
+                const uint64_t db = smem_desc(S.b + ks * 2 * (PF_NT * 16), PF_NT * 16, 128);
+                mma_i8(tmem + 0, da0, db, IDESC_UU_S, ks > 0);
+                mma_i8(tmem + 64, da1, db, IDESC_UU_S, ks > 0);
+            }
+            const uint64_t dam = smem_desc(S.am, PF_M * 16, 128);
+            mma_i8(tmem + 128, dam, smem_desc(S.bh, PF_NT * 16, 128), IDESC_UU_S, 0);
+            mma_i8(tmem + 192, dam, smem_desc(S.bl, PF_NT * 16, 128), IDESC_UU_U, 0);
+            tc_commit(&S.bar);
+        }
+        if (!mbar_wait(&S.bar, phase)) {
+            set_status(A.status, PMOE_ERR_TIMEOUT, 30, b);
+            ok = false;
+        }
+        phase ^= 1;
+        tc_fence_after();
+        // ---- fold the block into the f32 accumulators: row = tid, TMEM lane = tid
+        if (ok) {
+            const uint32_t lane_addr = tmem + ((uint32_t)(warp * 32) << 16);
+#pragma unroll
+            for (int cc = 0; cc < PF_NT / 16; cc++) {
+                uint32_t v0[16], v1[16], vh[16], vl[16];
+                tmem_ld16(lane_addr + 0 + cc * 16, v0);
+                tmem_ld16(lane_addr + 64 + cc * 16, v1);
+                tmem_ld16(lane_addr + 128 + cc * 16, vh);
+                tmem_ld16(lane_addr + 192 + cc * 16, vl);
+                tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 16; j++) {
+                    const int s = (int)v0[j] + 8 * (int)v1[j];
+                    const int mm = 64 * (int)vh[j] + (int)vl[j];
+                    acc[cc * 16 + j] += S.dx[cc * 16 + j] * (dw * (float)s - dmin * (float)mm);
+                }
+            }
+        }
+        tc_fence_before();
+        __syncthreads();  // operands and accumulators are free for the next block
+        tc_fence_after();
+    }
+
+    // ---- silu(gate) * up: up rows (threads 64..127) hand their sums over through shared memory
+    float *xch = reinterpret_cast<float *>(S.a0);  // [64 rows][PF_NT + 1]
+    if (tid >= 64) {
+#pragma unroll
+        for (int j = 0; j < PF_NT; j++) xch[(tid - 64) * (PF_NT + 1) + j] = acc[j];
+    }
+    __syncthreads();
+    if (tid < 64 && ok) {
+#pragma unroll
+        for (int j = 0; j < PF_NT; j++) {
+            const int rout = S.row_out[j];
+            if (rout < 0) continue;
+            const float g = acc[j], u = xch[tid * (PF_NT + 1) + j];
+            A.act[(size_t)rout * A.F + f0 + tid] = g / (1.f + expf(-g)) * u;
+        }
+    }
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem, PF_TMEM_COLS);
+}
+
+// number of token tiles a call can need at most: sum_e ceil(m_e / NT) <= pairs / NT + active experts
+static int max_routed_tiles(const LayerDev &L, int n, int top_k)
+{
+    long pairs = (long)n * top_k;
+    long act = pairs < L.E_local ? pairs : L.E_local;
+    return (int)(pairs / PF_NT + act);
+}
+
+bool prefill_supported(const LayerDev &L, bool routed, bool shared)
+{
+    if (L.H != 2048 || L.F != 512) return false;
+    if (routed && L.gate_dtype != PMOE_Q4_K) return false;
+    if (shared && L.sh_gate_dtype != PMOE_Q4_K) return false;
+    return true;
+}
+
+cudaError_t launch_gate_up_prefill(const LayerDev &L, const Workspace &ws, int n, int top_k, bool routed, bool shared,
+                                   cudaStream_t s)
+{
+    GuArgs A{};
+    A.gate = L.gate_exps; A.up = L.up_exps;
+    A.expert_bytes = row_bytes(L.gate_dtype, L.H) * L.F;
+    A.sgate = L.sh_gate; A.sup = L.sh_up;
+    A.has_shared = shared; A.routed = routed;
+    A.n = n; A.top_k = top_k; A.H = L.H; A.F = L.F;
+    A.g = ws.groups;
+    A.tile_prefix = ws.groups.tile_prefix;
+    A.xq = ws.x_q8k;
+    A.act = ws.act;
+    A.status = ws.status;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(k_gu_prefill, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(GuSmem) + 128);
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    const int tiles = (routed ? max_routed_tiles(L, n, top_k) : 0) + (shared ? (n + PF_NT - 1) / PF_NT : 0);
+    dim3 grid(L.F / 64, tiles);
+    k_gu_prefill<<<grid, PF_THREADS, sizeof(GuSmem) + 128, s>>>(A);
+    count_launch();
+    return cudaGetLastError();
+}
+
+}  // namespace pmoe

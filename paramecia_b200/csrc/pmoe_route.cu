@@ -300,6 +300,7 @@ __global__ void __launch_bounds__(GROUP_THREADS) k_group(const uint32_t *__restr
     __shared__ int scan[1024];
     __shared__ int act_scan[1024];
     __shared__ int cost_scan[1024];
+    __shared__ int tile_scan[1024];
     const int tid = threadIdx.x;
     cnt[tid] = 0;
     __syncthreads();
@@ -315,16 +316,20 @@ __global__ void __launch_bounds__(GROUP_THREADS) k_group(const uint32_t *__restr
     const int cost = (c + GEMV_TG - 1) / GEMV_TG;
     scan[tid] = c;
     act_scan[tid] = flag;
+    const int tiles = (c + PREFILL_NT - 1) / PREFILL_NT;
     cost_scan[tid] = cost;
+    tile_scan[tid] = tiles;
     __syncthreads();
     for (int off = 1; off < GROUP_THREADS; off <<= 1) {  // Hillis-Steele inclusive scans
         int a = tid >= off ? scan[tid - off] : 0;
         int b = tid >= off ? act_scan[tid - off] : 0;
         int d = tid >= off ? cost_scan[tid - off] : 0;
+        int f = tid >= off ? tile_scan[tid - off] : 0;
         __syncthreads();
         scan[tid] += a;
         act_scan[tid] += b;
         cost_scan[tid] += d;
+        tile_scan[tid] += f;
         __syncthreads();
     }
     int excl = scan[tid] - c;
@@ -334,12 +339,14 @@ __global__ void __launch_bounds__(GROUP_THREADS) k_group(const uint32_t *__restr
         if (flag) {
             g.active[act_scan[tid] - 1] = tid;
             g.cost_prefix[act_scan[tid] - 1] = cost_scan[tid] - cost;
+            g.tile_prefix[act_scan[tid] - 1] = tile_scan[tid] - tiles;
         }
     }
     if (tid == GROUP_THREADS - 1) {
         g.offset[E_local] = scan[tid];
         *g.n_active = act_scan[tid];
         g.cost_prefix[act_scan[tid]] = cost_scan[tid];
+        g.tile_prefix[act_scan[tid]] = tile_scan[tid];
     }
     cnt[tid] = excl;  // reuse as the per-expert base
     __syncthreads();
