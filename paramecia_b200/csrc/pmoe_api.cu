@@ -131,6 +131,7 @@ void carve_workspace(pmoe_layer *L, Carver &c)
     w.act_q80.qs = c.take<int8_t>(rows * F);
     w.act_q80.d = c.take<float>(rows * (F / QK8_0));
     w.act_q80.bsums = nullptr;
+    w.act_h = c.take<__half>(rows * F);
     w.partial = c.take<float>(rows * H);
     L->st_x = c.take<float>(n * H);
     L->st_out = c.take<float>(n * H);
@@ -226,8 +227,12 @@ int run_experts(pmoe_layer *L, const void *x, int x_dtype, const uint32_t *idx, 
         PHASE(L, 4, s, launch_gate_up_prefill(d, L->ws, n, top_k, routed, shared, s));
     else
         PHASE(L, 4, s, launch_gate_up(d, L->ws, n, top_k, routed, shared, s));
-    PHASE(L, 5, s, launch_act_quant(d, L->ws, idx, n, top_k, routed, shared, s));
-    PHASE(L, 6, s, launch_down(d, L->ws, w, n, top_k, routed, shared, s));
+    if (prefill && prefill_down_supported(d, routed, shared)) {
+        PHASE(L, 6, s, launch_down_prefill(d, L->ws, w, n, top_k, routed, shared, s));
+    } else {
+        PHASE(L, 5, s, launch_act_quant(d, L->ws, idx, n, top_k, routed, shared, s));
+        PHASE(L, 6, s, launch_down(d, L->ws, w, n, top_k, routed, shared, s));
+    }
     PHASE(L, 7, s, launch_combine(d, L->ws, idx, n, top_k, routed, shared, out, out_dtype, s));
     return PMOE_OK;
 }

@@ -222,6 +222,7 @@ struct Workspace {
     Groups groups;
     float *act;          // [n*(k+1), F]  silu(gate)*up ; routed pair p at row p, shared token t at row n_cap*k + t
     QAct act_q8k, act_q80;
+    __half *act_h;       // [n*(k+1), F]  fake-quantised activation for the fp16 down GEMM
     float *partial;      // [n*(k+1), H]  weighted down-projection rows
 };
 
@@ -253,6 +254,9 @@ cudaError_t qmatmul_static_scratch(int device, void **ptr, size_t *bytes);
 bool prefill_supported(const LayerDev &L, bool routed, bool shared);
 cudaError_t launch_gate_up_prefill(const LayerDev &L, const Workspace &ws, int n, int top_k, bool routed, bool shared,
                                    cudaStream_t s);
+bool prefill_down_supported(const LayerDev &L, bool routed, bool shared);
+cudaError_t launch_down_prefill(const LayerDev &L, const Workspace &ws, const float *w, int n, int top_k, bool routed,
+                                bool shared, cudaStream_t s);
 // pmoe_codec.cu
 cudaError_t launch_dequantize(int dtype, const void *blocks, size_t n_elems, float *out, cudaStream_t s);
 cudaError_t launch_reduce_rows(const float *parts, int R, const void *extra, int extra_dtype, int n, int H, void *out,

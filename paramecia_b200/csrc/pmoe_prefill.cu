@@ -349,6 +349,301 @@ __global__ void __launch_bounds__(PF_THREADS, 2) k_gu_prefill(const GuArgs A)
     if (warp == 0) tmem_dealloc(tmem, PF_TMEM_COLS);
 }
 
+// ---------------------------------------------------------------- down projection, fp16 operands
+// The down GEMM has no re-quantisation after it, so its own rounding lands in the output
+// directly: dequantised fp16 weights times the fake-quantised activation d*q in fp16 with f32
+// accumulation in tensor memory stays near 3e-4 of the integer result, inside the parity bar.
+// Tile: M = 128 output rows, N = 64 tokens, K walked in steps of 128.  The raw GGUF rows of the
+// tile arrive with one bulk (TMA) copy; each thread dequantises its own row straight into the
+// K-major core-matrix layout.
+struct DownArgs {
+    const uint8_t *down;           // routed [E_local, H, F]
+    size_t expert_bytes;
+    const uint8_t *sdown;          // shared
+    int has_shared, routed;
+    int n, top_k, H, F;
+    Groups g;
+    const int *tile_prefix;
+    const __half *act_h;           // [n*(k+1), F] fake-quantised activation
+    const float *scale_r;          // routing weights [n*k]
+    const float *scale_s;          // shared gate [n]
+    float *partial;                // [n*(k+1), H]
+    DevStatus *status;
+};
+
+constexpr int DN_KSTEP = 128;
+
+// 4 unsigned bytes -> 4 halves holding (byte - bias) * s
+__device__ inline void bytes_to_half4(uint32_t v, __half2 bias, __half2 s, uint32_t &o0, uint32_t &o1)
+{
+    // 0x6400 | b is the fp16 number 1024 + b, exactly
+    const uint32_t p0 = __byte_perm(v, 0x64646464u, 0x4140), p1 = __byte_perm(v, 0x64646464u, 0x4342);
+    const __half2 h0 = __hmul2(__hsub2(*reinterpret_cast<const __half2 *>(&p0), bias), s);
+    const __half2 h1 = __hmul2(__hsub2(*reinterpret_cast<const __half2 *>(&p1), bias), s);
+    o0 = *reinterpret_cast<const uint32_t *>(&h0);
+    o1 = *reinterpret_cast<const uint32_t *>(&h1);
+}
+
+template <int DT> struct DownDequant;
+
+// Q6_K: K step s = half `s & 1` of block `s >> 1`
+template <> struct DownDequant<PMOE_Q6_K> {
+    static constexpr int ROW_BYTES = 2 * Q6_K_BYTES;  // F = 512
+    __device__ static inline void step(const uint8_t *row, int s, uint8_t *a_tile, int r)
+    {
+        const uint8_t *blk = row + (s >> 1) * Q6_K_BYTES;
+        const int half = s & 1;
+        const float d = half_bits_to_float(*reinterpret_cast<const uint16_t *>(blk + 208));
+        const int8_t *sc = reinterpret_cast<const int8_t *>(blk + 192 + 8 * half);
+        const __half2 bias = __floats2half2_rn(1056.f, 1056.f);  // 1024 + 32
+#pragma unroll
+        for (int l8 = 0; l8 < 4; l8++) {  // l = 8*l8 .. 8*l8+7
+            const uint32_t la0 = lds_u32_a2(blk + 64 * half + 8 * l8), la1 = lds_u32_a2(blk + 64 * half + 8 * l8 + 4);
+            const uint32_t lb0 = lds_u32_a2(blk + 64 * half + 32 + 8 * l8), lb1 = lds_u32_a2(blk + 64 * half + 32 + 8 * l8 + 4);
+            const uint32_t h0 = lds_u32_a2(blk + 128 + 32 * half + 8 * l8), h1 = lds_u32_a2(blk + 128 + 32 * half + 8 * l8 + 4);
+            const int is = l8 >> 1;  // l / 16
+#pragma unroll
+            for (int quad = 0; quad < 4; quad++) {
+                const float sf = d * (float)sc[is + 2 * quad];
+                const __half2 sh = __floats2half2_rn(sf, sf);
+                uint32_t va, vb;
+                if (quad == 0) { va = (la0 & 0x0F0F0F0Fu) | ((h0 << 4) & 0x30303030u); vb = (la1 & 0x0F0F0F0Fu) | ((h1 << 4) & 0x30303030u); }
+                else if (quad == 1) { va = (lb0 & 0x0F0F0F0Fu) | ((h0 << 2) & 0x30303030u); vb = (lb1 & 0x0F0F0F0Fu) | ((h1 << 2) & 0x30303030u); }
+                else if (quad == 2) { va = ((la0 >> 4) & 0x0F0F0F0Fu) | (h0 & 0x30303030u); vb = ((la1 >> 4) & 0x0F0F0F0Fu) | (h1 & 0x30303030u); }
+                else { va = ((lb0 >> 4) & 0x0F0F0F0Fu) | ((h0 >> 2) & 0x30303030u); vb = ((lb1 >> 4) & 0x0F0F0F0Fu) | ((h1 >> 2) & 0x30303030u); }
+                uint4 o;
+                bytes_to_half4(va, bias, sh, o.x, o.y);
+                bytes_to_half4(vb, bias, sh, o.z, o.w);
+                // weights 32*quad + 8*l8 .. +7 of this half: K element index inside the step
+                const int kel = 32 * quad + 8 * l8;
+                *reinterpret_cast<uint4 *>(a_tile + core_off(PF_M, r, 2 * kel)) = o;
+            }
+        }
+    }
+};
+
+// Q4_K: K step s = sub-blocks 4*(s&1) .. 4*(s&1)+3 of block s >> 1
+template <> struct DownDequant<PMOE_Q4_K> {
+    static constexpr int ROW_BYTES = 2 * Q4_K_BYTES;
+    __device__ static inline void step(const uint8_t *row, int s, uint8_t *a_tile, int r)
+    {
+        const uint8_t *blk = row + (s >> 1) * Q4_K_BYTES;
+        const uint4 hdr = *reinterpret_cast<const uint4 *>(blk);
+        const float d = half_bits_to_float((uint16_t)(hdr.x & 0xffffu));
+        const float dmin = half_bits_to_float((uint16_t)(hdr.x >> 16));
+        const uint32_t u0 = hdr.y, u1 = hdr.z, u2 = hdr.w;
+        const uint32_t sca = u0 & 0x3F3F3F3Fu, mna = u1 & 0x3F3F3F3Fu;
+        const uint32_t scb = (u2 & 0x0F0F0F0Fu) | ((u0 >> 2) & 0x30303030u);
+        const uint32_t mnb = ((u2 >> 4) & 0x0F0F0F0Fu) | ((u1 >> 2) & 0x30303030u);
+        const uint32_t scw = (s & 1) ? scb : sca, mnw = (s & 1) ? mnb : mna;
+#pragma unroll
+        for (int gq = 0; gq < 2; gq++) {  // 32 bytes of nibbles = sub-blocks 2*gq (low), 2*gq+1 (high) of this half
+            const uint4 qa = *reinterpret_cast<const uint4 *>(blk + 16 + 64 * (s & 1) + 32 * gq);
+            const uint4 qb = *reinterpret_cast<const uint4 *>(blk + 32 + 64 * (s & 1) + 32 * gq);
+            const uint32_t w[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+#pragma unroll
+            for (int hi = 0; hi < 2; hi++) {
+                const int j = 2 * gq + hi;  // sub-block inside this half
+                const float sf = d * (float)((scw >> (8 * j)) & 0xFFu);
+                const float mf = dmin * (float)((mnw >> (8 * j)) & 0xFFu);
+#pragma unroll
+                for (int c = 0; c < 4; c++) {  // 8 weights per 16-byte chunk
+                    uint32_t o[4];
+#pragma unroll
+                    for (int i = 0; i < 2; i++) {
+                        const uint32_t v = hi ? (w[2 * c + i] >> 4) & 0x0F0F0F0Fu : w[2 * c + i] & 0x0F0F0F0Fu;
+                        const __half2 a = __floats2half2_rn(fmaf(sf, (float)(v & 0xFF), -mf), fmaf(sf, (float)((v >> 8) & 0xFF), -mf));
+                        const __half2 bq = __floats2half2_rn(fmaf(sf, (float)((v >> 16) & 0xFF), -mf), fmaf(sf, (float)(v >> 24), -mf));
+                        o[2 * i] = *reinterpret_cast<const uint32_t *>(&a);
+                        o[2 * i + 1] = *reinterpret_cast<const uint32_t *>(&bq);
+                    }
+                    const int kel = 32 * j + 8 * c;
+                    *reinterpret_cast<uint4 *>(a_tile + core_off(PF_M, r, 2 * kel)) = make_uint4(o[0], o[1], o[2], o[3]);
+                }
+            }
+        }
+    }
+};
+
+struct DownSmemHdr {
+    float scale[PF_NT];
+    int row_in[PF_NT];
+    uint64_t bar_raw, bar_mma;
+    uint32_t tmem_base;
+    int slot, tile_in_slot;
+};
+
+template <int DT>
+__global__ void __launch_bounds__(PF_THREADS, 2) k_down_prefill(const DownArgs A)
+{
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    using DQ = DownDequant<DT>;
+    constexpr int RAW_BYTES = PF_M * DQ::ROW_BYTES;
+    uint8_t *a_tile = smem_raw;                                  // [128 rows][128 K] fp16, core-matrix layout
+    uint8_t *b_tile = a_tile + PF_M * DN_KSTEP * 2;              // [64 tokens][128 K] fp16
+    uint8_t *raw = b_tile + PF_NT * DN_KSTEP * 2;                // the tile's GGUF rows
+    DownSmemHdr &S = *reinterpret_cast<DownSmemHdr *>(raw + ((RAW_BYTES + 127) / 128) * 128);
+    const int tid = threadIdx.x, warp = tid >> 5;
+
+    const int n_active = A.routed ? *A.g.n_active : 0;
+    const int routed_tiles = n_active ? A.tile_prefix[n_active] : 0;
+    const int shared_tiles = A.has_shared ? (A.n + PF_NT - 1) / PF_NT : 0;
+    const int tile = blockIdx.y;
+    if (tile >= routed_tiles + shared_tiles) return;
+    if (tid == 0) {
+        if (tile < routed_tiles) {
+            int lo = 0, hi = n_active - 1;
+            while (lo < hi) {
+                const int mid = (lo + hi + 1) >> 1;
+                if (A.tile_prefix[mid] <= tile) lo = mid; else hi = mid - 1;
+            }
+            S.slot = lo;
+            S.tile_in_slot = tile - A.tile_prefix[lo];
+        } else {
+            S.slot = -1;
+            S.tile_in_slot = tile - routed_tiles;
+        }
+        mbar_init(&S.bar_raw, 1);
+        mbar_init(&S.bar_mma, 1);
+        fence_mbar_init();
+    }
+    if (warp == 0) tmem_alloc(&S.tmem_base, 64);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = S.tmem_base;
+    const int slot = S.slot, t0 = S.tile_in_slot * PF_NT;
+    const bool is_shared = slot < 0;
+    int m;
+    const int *list = nullptr;
+    const uint8_t *wd;
+    if (is_shared) {
+        m = A.n;
+        wd = A.sdown;
+    } else {
+        const int e = A.g.active[slot];
+        m = A.g.count[e];
+        list = A.g.pairs + A.g.offset[e];
+        wd = A.down + (size_t)e * A.expert_bytes;
+    }
+    const int h0 = blockIdx.x * PF_M;
+    if (tid == 0) {  // the tile's raw rows: one contiguous run
+        mbar_expect_tx(&S.bar_raw, RAW_BYTES);
+        const uint8_t *src = wd + (size_t)h0 * DQ::ROW_BYTES;
+        for (int off = 0; off < RAW_BYTES; off += 16384)
+            bulk_g2s(raw + off, src + off, RAW_BYTES - off < 16384 ? RAW_BYTES - off : 16384, &S.bar_raw);
+    }
+    const int cnt = m - t0 < PF_NT ? m - t0 : PF_NT;
+    if (tid < PF_NT) {
+        int rin = -1;
+        float sc = 0.f;
+        if (tid < cnt) {
+            if (is_shared) { rin = A.n * A.top_k + t0 + tid; sc = A.scale_s[t0 + tid]; }
+            else { rin = list[t0 + tid]; sc = A.scale_r[rin]; }
+        }
+        S.row_in[tid] = rin;
+        S.scale[tid] = sc;
+    }
+    __syncthreads();
+    bool ok = mbar_wait(&S.bar_raw, 0);
+    if (!ok) set_status(A.status, PMOE_ERR_TIMEOUT, 31, tile);
+
+    constexpr uint32_t IDESC = make_idesc(1, 0, 0, PF_NT, PF_M);  // f16 x f16 -> f32
+    const int steps = A.F / DN_KSTEP;
+    uint32_t phase = 0;
+    for (int s = 0; s < steps && ok; s++) {
+        DQ::step(raw + (size_t)tid * DQ::ROW_BYTES, s, a_tile, tid);
+        {   // activations: token = tid / 2, 64 halves each
+            const int tk = tid >> 1, half = tid & 1;
+            const int rin = S.row_in[tk];
+            const uint4 *src = rin >= 0 ? reinterpret_cast<const uint4 *>(A.act_h + (size_t)rin * A.F + s * DN_KSTEP + 64 * half)
+                                        : nullptr;
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const uint4 v = src ? src[i] : make_uint4(0, 0, 0, 0);
+                *reinterpret_cast<uint4 *>(b_tile + core_off(PF_NT, tk, 2 * (64 * half + 8 * i))) = v;
+            }
+        }
+        fence_proxy_async();
+        tc_fence_before();
+        __syncthreads();
+        if (tid == 0) {
+            tc_fence_after();
+            for (int ks = 0; ks < DN_KSTEP / 16; ks++) {  // 16 halves = 32 bytes of K per instruction
+                const uint64_t da = smem_desc(a_tile + ks * 2 * (PF_M * 16), PF_M * 16, 128);
+                const uint64_t db = smem_desc(b_tile + ks * 2 * (PF_NT * 16), PF_NT * 16, 128);
+                mma_f16(tmem, da, db, IDESC, (s > 0 || ks > 0) ? 1u : 0u);
+            }
+            tc_commit(&S.bar_mma);
+        }
+        if (!mbar_wait(&S.bar_mma, phase)) {
+            set_status(A.status, PMOE_ERR_TIMEOUT, 32, s);
+            ok = false;
+        }
+        phase ^= 1;
+        tc_fence_after();
+        __syncthreads();  // operand tiles may be overwritten
+    }
+    if (ok) {
+        const uint32_t lane_addr = tmem + ((uint32_t)(warp * 32) << 16);
+#pragma unroll
+        for (int cc = 0; cc < PF_NT / 16; cc++) {
+            uint32_t v[16];
+            tmem_ld16(lane_addr + cc * 16, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 16; j++) {
+                const int rout = S.row_in[cc * 16 + j];
+                if (rout >= 0) A.partial[(size_t)rout * A.H + h0 + tid] = __uint_as_float(v[j]) * S.scale[cc * 16 + j];
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem, 64);
+}
+
+// Q8_K quantisation of an activated row, written back as fp16 d*q for the fp16 down GEMM
+__global__ void __launch_bounds__(64) k_act_fakequant_h(const float *__restrict__ act, int F, int n_routed_rows,
+                                                        const int *__restrict__ pos, bool routed,
+                                                        __half *__restrict__ out)
+{
+    const int r = blockIdx.x;
+    if (r < n_routed_rows && (!routed || pos[r] < 0)) return;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int b = warp; b < F / QK_K; b += 2) {
+        const float *src = act + (size_t)r * F + b * QK_K;
+        float v[8];
+        const float4 a = reinterpret_cast<const float4 *>(src)[2 * lane], c = reinterpret_cast<const float4 *>(src)[2 * lane + 1];
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = c.x; v[5] = c.y; v[6] = c.z; v[7] = c.w;
+        float amax = 0.f, mx = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; j++)
+            if (amax < fabsf(v[j])) { amax = fabsf(v[j]); mx = v[j]; }
+        int who = lane;
+#pragma unroll
+        for (int s = 16; s >= 1; s >>= 1) {
+            const float oa = __shfl_xor_sync(0xffffffffu, amax, s), om = __shfl_xor_sync(0xffffffffu, mx, s);
+            const int ow = __shfl_xor_sync(0xffffffffu, who, s);
+            if (oa > amax || (oa == amax && ow < who)) { amax = oa; mx = om; who = ow; }
+        }
+        uint4 o = make_uint4(0, 0, 0, 0);
+        if (amax != 0.f) {
+            const float iscale = __fdiv_rn(-128.f, mx), d = __fdiv_rn(1.f, iscale);
+            __half2 h[4];
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const float q0 = fminf(roundf(__fmul_rn(iscale, v[2 * j])), 127.f);
+                const float q1 = fminf(roundf(__fmul_rn(iscale, v[2 * j + 1])), 127.f);
+                h[j] = __floats2half2_rn(q0 * d, q1 * d);
+            }
+            o = make_uint4(*reinterpret_cast<uint32_t *>(&h[0]), *reinterpret_cast<uint32_t *>(&h[1]),
+                           *reinterpret_cast<uint32_t *>(&h[2]), *reinterpret_cast<uint32_t *>(&h[3]));
+        }
+        *reinterpret_cast<uint4 *>(out + (size_t)r * F + b * QK_K + 8 * lane) = o;
+    }
+}
+
 // number of token tiles a call can need at most: sum_e ceil(m_e / NT) <= pairs / NT + active experts
 static int max_routed_tiles(const LayerDev &L, int n, int top_k)
 {
@@ -390,6 +685,58 @@ cudaError_t launch_gate_up_prefill(const LayerDev &L, const Workspace &ws, int n
     k_gu_prefill<<<grid, PF_THREADS, sizeof(GuSmem) + 128, s>>>(A);
     count_launch();
     return cudaGetLastError();
+}
+
+bool prefill_down_supported(const LayerDev &L, bool routed, bool shared)
+{
+    auto ok = [](int dt) { return dt == PMOE_Q6_K || dt == PMOE_Q4_K; };
+    if (L.H != 2048 || L.F != 512) return false;
+    if (routed && !ok(L.down_dtype)) return false;
+    if (shared && !ok(L.sh_down_dtype)) return false;
+    if (routed && shared && L.down_dtype != L.sh_down_dtype) return false;
+    return true;
+}
+
+template <int DT>
+static cudaError_t launch_down_t(const DownArgs &A, dim3 grid, cudaStream_t s)
+{
+    constexpr size_t smem = PF_M * DN_KSTEP * 2 + PF_NT * DN_KSTEP * 2 + ((PF_M * DownDequant<DT>::ROW_BYTES + 127) / 128) * 128 +
+                            sizeof(DownSmemHdr) + 128;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(k_down_prefill<DT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    k_down_prefill<DT><<<grid, PF_THREADS, smem, s>>>(A);
+    count_launch();
+    return cudaGetLastError();
+}
+
+cudaError_t launch_down_prefill(const LayerDev &L, const Workspace &ws, const float *w, int n, int top_k, bool routed,
+                                bool shared, cudaStream_t s)
+{
+    const int rows = n * top_k + (shared ? n : 0);
+    k_act_fakequant_h<<<rows, 64, 0, s>>>(ws.act, L.F, n * top_k, ws.groups.pos, routed, ws.act_h);
+    count_launch();
+    DownArgs A{};
+    A.down = L.down_exps;
+    A.expert_bytes = row_bytes(L.down_dtype, L.F) * L.H;
+    A.sdown = L.sh_down;
+    A.has_shared = shared; A.routed = routed;
+    A.n = n; A.top_k = top_k; A.H = L.H; A.F = L.F;
+    A.g = ws.groups;
+    A.tile_prefix = ws.groups.tile_prefix;
+    A.act_h = ws.act_h;
+    A.scale_r = w;
+    A.scale_s = ws.sh_sigmoid;
+    A.partial = ws.partial;
+    A.status = ws.status;
+    const int tiles = (routed ? max_routed_tiles(L, n, top_k) : 0) + (shared ? (n + PF_NT - 1) / PF_NT : 0);
+    dim3 grid(L.H / PF_M, tiles);
+    const int dt = routed ? L.down_dtype : L.sh_down_dtype;
+    if (dt == PMOE_Q6_K) return launch_down_t<PMOE_Q6_K>(A, grid, s);
+    return launch_down_t<PMOE_Q4_K>(A, grid, s);
 }
 
 }  // namespace pmoe

@@ -21,6 +21,7 @@ PRESETS = {
     "q4k": (Q4_K, Q4_K, Q4_K),          # every matrix Q4_K
     "q4k_m": (Q4_K, Q6_K, Q8_0),        # Q4_K_M-style mix: gate/up Q4_K, down Q6_K, shared Q8_0
     "q4k_q6k": (Q4_K, Q6_K, Q6_K),
+    "q4k_q6k_all": (Q4_K, Q6_K, (Q4_K, Q6_K)),  # shared expert quantised like the routed ones
     "q8_0": (Q8_0, Q8_0, Q8_0),
     "q6k": (Q6_K, Q6_K, Q6_K),
 }
@@ -122,6 +123,7 @@ def make_layer(H=2048, F=512, E=512, k=10, preset="q4k_m", seed=0, device="cpu",
     """One synthetic MoE block as raw tensors.  Returns a dict with the GGUF block bytes
     (uint8 tensors on `device`), dtypes and the float tensors."""
     gu_dt, dn_dt, sh_dt = PRESETS[preset]
+    sh_gu, sh_dn = sh_dt if isinstance(sh_dt, tuple) else (sh_dt, sh_dt)
     dev = torch.device(device)
     gen = torch.Generator(device=dev)
     gen.manual_seed(0x5EED0000 + 1000 * layer + seed)
@@ -134,10 +136,10 @@ def make_layer(H=2048, F=512, E=512, k=10, preset="q4k_m", seed=0, device="cpu",
              router_bias=zipf_router_bias(E, seed + 17, dev) if zipf else None,
              shared=None)
     if shared:
-        t["shared"] = dict(gate_dtype=sh_dt, up_dtype=sh_dt, down_dtype=sh_dt,
-                           gate=random_quantized((1, F * H), sh_dt, gen, dev),
-                           up=random_quantized((1, F * H), sh_dt, gen, dev),
-                           down=random_quantized((1, H * F), sh_dt, gen, dev),
+        t["shared"] = dict(gate_dtype=sh_gu, up_dtype=sh_gu, down_dtype=sh_dn,
+                           gate=random_quantized((1, F * H), sh_gu, gen, dev),
+                           up=random_quantized((1, F * H), sh_gu, gen, dev),
+                           down=random_quantized((1, H * F), sh_dn, gen, dev),
                            gate_inp=torch.randn((H,), generator=gen, device=dev) * 0.02)
     return t
 
