@@ -171,11 +171,88 @@ __global__ void __launch_bounds__(RT_WARPS * 32) k_router_tiled(const float *__r
     }
 }
 
+// Many tokens (prefill): a wider token tile kept in shared memory in its own element type, so
+// that the router matrix is re-read from L2 only once per 32 (bf16) or 16 (f32) tokens.  Same
+// per-lane partial sums and the same fold as above.  H == 2048.
+template <typename XT> struct WideTile { static constexpr int TT = 131072 / (2048 * (int)sizeof(XT)); };
+
+template <typename XT>
+__global__ void __launch_bounds__(RT_WARPS * 32) k_router_wide(const float *__restrict__ W,
+                                                               const float *__restrict__ bias,
+                                                               const XT *__restrict__ x, int n, int E,
+                                                               int rows_per_cta, float *__restrict__ logits)
+{
+    constexpr int TT = WideTile<XT>::TT, H = 2048;
+    extern __shared__ __align__(16) unsigned char xs_raw[];
+    XT *xs = reinterpret_cast<XT *>(xs_raw);  // [TT][H]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t0 = blockIdx.y * TT;
+    const int nt = n - t0 < TT ? n - t0 : TT;
+    constexpr int VEC = 16 / (int)sizeof(XT);  // elements per 16-byte copy
+    for (int i = threadIdx.x * VEC; i < TT * H; i += RT_WARPS * 32 * VEC) {
+        const int tt = i / H;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (tt < nt) v = *reinterpret_cast<const uint4 *>(x + (size_t)(t0 + tt) * H + (i - tt * H));
+        *reinterpret_cast<uint4 *>(xs + i) = v;
+    }
+    __syncthreads();
+    const int e_begin = blockIdx.x * rows_per_cta;
+    for (int e = e_begin + warp; e < e_begin + rows_per_cta && e < E; e += RT_WARPS) {
+        float4 wv[16];
+        const float4 *w4 = reinterpret_cast<const float4 *>(W + (size_t)e * H);
+#pragma unroll
+        for (int i = 0; i < 16; i++) wv[i] = w4[32 * i + lane];
+#pragma unroll 1
+        for (int g0 = 0; g0 < TT; g0 += 8) {  // eight tokens per fold keeps the accumulators in registers
+            float acc[8];
+#pragma unroll
+            for (int tt = 0; tt < 8; tt++) {
+                float a = 0.f;
+#pragma unroll
+                for (int i = 0; i < 16; i++) {
+                    const float4 xv = load_x4(xs, (size_t)(g0 + tt) * H + 128 * i + 4 * lane);
+                    a = fmaf(xv.x, wv[i].x, a);
+                    a = fmaf(xv.y, wv[i].y, a);
+                    a = fmaf(xv.z, wv[i].z, a);
+                    a = fmaf(xv.w, wv[i].w, a);
+                }
+                acc[tt] = a;
+            }
+            const float v = transposed_reduce<8, 32>(acc, lane);
+            const int tt = g0 + (lane >> 2);  // lanes 4*j .. 4*j+3 hold token j's sum
+            if ((lane & 3) == 0 && tt < nt) logits[(size_t)(t0 + tt) * E + e] = bias ? __fadd_rn(v, bias[e]) : v;
+        }
+    }
+}
+
 cudaError_t launch_router(const LayerDev &L, const Workspace &ws, const void *x, int x_dtype, int n, float *logits,
                           cudaStream_t s)
 {
     (void)ws;
     if (n <= 0) return cudaSuccess;
+    if (n > 512 && L.H == 2048) {
+        static bool configured_wide = false;
+        if (!configured_wide) {
+            cudaError_t e1 = cudaFuncSetAttribute(k_router_wide<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 131072);
+            cudaError_t e2 = cudaFuncSetAttribute(k_router_wide<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 131072);
+            if (e1 != cudaSuccess) return e1;
+            if (e2 != cudaSuccess) return e2;
+            configured_wide = true;
+        }
+        const int rows_per_cta = 64;
+        if (x_dtype == PMOE_F32) {
+            dim3 grid((L.E + rows_per_cta - 1) / rows_per_cta, (n + WideTile<float>::TT - 1) / WideTile<float>::TT);
+            k_router_wide<float><<<grid, RT_WARPS * 32, 131072, s>>>(L.router_w, L.router_bias, (const float *)x, n, L.E,
+                                                                     rows_per_cta, logits);
+        } else {
+            using BT = __nv_bfloat16;
+            dim3 grid((L.E + rows_per_cta - 1) / rows_per_cta, (n + WideTile<BT>::TT - 1) / WideTile<BT>::TT);
+            k_router_wide<BT><<<grid, RT_WARPS * 32, 131072, s>>>(L.router_w, L.router_bias, (const BT *)x, n, L.E,
+                                                                  rows_per_cta, logits);
+        }
+        count_launch();
+        return cudaGetLastError();
+    }
     if (n > 8 && L.H <= 2048) {
         static bool configured = false;
         const size_t smem = (size_t)RT_TOKENS * L.H * sizeof(float);

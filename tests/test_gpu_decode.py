@@ -47,10 +47,11 @@ def test_dequantize_bit_exact(dtype):
     assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
 
 
-@pytest.mark.parametrize("n,xdtype", [(1, torch.float32), (7, torch.bfloat16), (64, torch.float32), (200, torch.bfloat16)])
+@pytest.mark.parametrize("n,xdtype", [(1, torch.float32), (7, torch.bfloat16), (64, torch.float32), (200, torch.bfloat16),
+                                      (1000, torch.bfloat16), (530, torch.float32)])
 def test_router_bit_exact(n, xdtype):
     t = synth.make_layer(E=512, k=10, preset="q8_0", seed=3, shared=False, H=2048, F=512)
-    blk = synth.make_block(t, DEV, max_tokens=256)
+    blk = synth.make_block(t, DEV, max_tokens=max(n, 256))
     x = seeded_x(n, 2048, 11, xdtype)
     logits, w, idx = blk.route(x.to(DEV))
     ol = oracle_layer(t)
