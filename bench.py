@@ -47,6 +47,9 @@ def parse():
     ap.add_argument("--no-graph", action="store_true", help="do not try CUDA-graph replay of the block")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--ep-mode", default="all_to_all", choices=["all_to_all", "all_gather"])
+    ap.add_argument("--mode", default="decode", choices=["decode", "prefill"],
+                    help="decode: the headline workload; prefill: 4096 tokens, Zipf-skewed routing, one GPU")
+    ap.add_argument("--tokens", type=int, default=4096, help="tokens per step in prefill mode")
     return ap.parse_args()
 
 
@@ -175,8 +178,91 @@ def reference_arm(args, rank):
     print(json.dumps(line), flush=True)
 
 
+def prefill_main(args):
+    """BASELINE config 3 on one GPU: 4096 bf16 tokens through one Q4_K / Q6_K block whose router carries the
+    bias 2*ln(1/rank_e) (rank = seeded permutation), so a dozen experts take most tokens.  Reports tokens/s and the
+    tensor-core roofline of the gate/up grouped GEMM (tcgen05 kind::i8, two digit MMAs per algorithmic MMA)."""
+    import torch
+    import paramecia_b200 as pm
+    from paramecia_b200 import synth
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except Exception:
+        pass
+    tpeak = float(peaks.get("bf16_tflops", 1590.0))
+    n = args.tokens
+    nl = max(1, min(args.layers, 2))
+    blocks = [synth.make_block(synth.make_layer(H, F, E, TOPK, "q4k_q6k_all", seed=0, device=dev, layer=li, zipf=True),
+                               dev, max_tokens=n) for li in range(nl)]
+    g = torch.Generator(device=dev).manual_seed(11)
+    xs = [torch.randn((n, H), generator=g, device=dev).to(torch.bfloat16) for _ in range(2)]
+    out = torch.empty((n, H), dtype=torch.bfloat16, device=dev)
+    W = max(args.warmup, 3)
+    steps = min(args.steps, 50)
+    for i in range(W):
+        blocks[i % nl].forward_into(xs[i % 2], out)
+    torch.cuda.synchronize()
+    sampler = ClockSampler(0)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    before = pm.launch_count()
+    e0.record()
+    for i in range(steps):
+        blocks[i % nl].forward_into(xs[i % 2], out)
+    e1.record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    ms = e0.elapsed_time(e1) / steps
+    launches = pm.launch_count() - before
+    for b in blocks:
+        b.status()
+    phase = {}
+    reps = min(steps, 10)
+    blocks[0].trace(True)
+    for i in range(reps):
+        blocks[0].forward_into(xs[0], out)
+        for k_, v in blocks[0].trace_read().items():
+            phase[k_] = phase.get(k_, 0.0) + v / reps
+    blocks[0].trace(False)
+    _, _, idx = blocks[0].route(xs[0])
+    counts = torch.bincount(idx.flatten().long(), minlength=E)
+    rows = n * TOPK + n
+    gu_flops = rows * 2 * 2 * H * F
+    ach = gu_flops / (phase["gate_up"] * 1e-3) / 1e12
+    xh = xs[0].cpu().pin_memory()
+    oh = torch.empty((n, H), dtype=torch.bfloat16).pin_memory()
+    for _ in range(2):
+        blocks[0].forward_host(xh, oh)
+    t0 = time.perf_counter()
+    for i in range(steps):
+        blocks[i % nl].forward_host(xh, oh)
+    el = (time.perf_counter() - t0) / steps
+    line = dict(metric="Q4_K MoE layer tokens/s (prefill)", value=n / (ms * 1e-3), unit=UNIT, n_gpus=1, steps=steps,
+                warmup=W, ms_per_step=ms, higher_is_better=True, scaling="weak", vs_baseline=None,
+                dtype="int8 digit MMAs (gate/up, exact) + fp16 MMAs (down), f32 accumulate", data="synthetic",
+                config=dict(workload=f"qwen3next-moe-block gate/up Q4_K, down Q6_K (shared expert alike) H{H} F{F} E{E} "
+                                     f"top{TOPK}, prefill {n} bf16 tokens, Zipf-biased router",
+                            active_experts=int((counts > 0).sum()), max_tokens_per_expert=int(counts.max()),
+                            layers_cycled=nl, block_tflops=n * 71303168 / (ms * 1e-3) / 1e12),
+                roofline=dict(bound="tensor", kernel="k_gu_prefill", achieved=ach, peak=tpeak, unit="TFLOP/s",
+                              frac=ach / tpeak, traffic=None, peak_kind="measured bf16 burst (MEASURED_PEAKS.json)",
+                              algorithmic_flops_per_launch=gu_flops, us_per_launch=phase["gate_up"] * 1e3,
+                              phases_us={k_: round(v * 1e3, 1) for k_, v in phase.items()}),
+                cpu_baseline=None,
+                e2e=dict(value=n / el, unit=UNIT, h2d_bytes_per_step=n * H * 2, d2h_bytes_per_step=n * H * 2,
+                         ms_per_step=el * 1e3),
+                gpu_launches=launches, clocks=clocks)
+    print(json.dumps(line), flush=True)
+
+
 def main():
     args = parse()
+    if args.mode == "prefill" and args.impl != "reference":
+        prefill_main(args)
+        return
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -207,9 +207,31 @@ __global__ void __launch_bounds__(PF_THREADS, 2) k_gu_prefill(const GuArgs A)
     uint32_t phase = 0;
     bool ok = true;
 
+    // the row's current block lives in registers; the next one is fetched while the MMAs run
+    uint4 blk[9];
+#pragma unroll
+    for (int i = 0; i < 9; i++) blk[i] = reinterpret_cast<const uint4 *>(wrow)[i];
+
     for (int b = 0; b < nblk && ok; b++) {
+        // ---- start this block's activation loads first: they fly while the weights are decoded
+        const int tk = tid >> 1, half = tid & 1;
+        const int rin_b = S.row_in[tk];
+        uint4 bv[8];
+        {
+            const uint4 *src = reinterpret_cast<const uint4 *>(A.xq.qs + (size_t)(rin_b >= 0 ? rin_b : 0) * A.H + b * QK_K + 128 * half);
+#pragma unroll
+            for (int i = 0; i < 8; i++) bv[i] = rin_b >= 0 ? src[i] : make_uint4(0, 0, 0, 0);
+        }
+        uint4 bs0 = make_uint4(0, 0, 0, 0), bs1 = make_uint4(0, 0, 0, 0);
+        float dx_reg = 0.f;
+        const int rin_s = tid < PF_NT ? S.row_in[tid] : -1;
+        if (rin_s >= 0) {
+            const uint4 *bsp = reinterpret_cast<const uint4 *>(A.xq.bsums + (size_t)rin_s * (A.H / 16) + b * 16);
+            bs0 = bsp[0];
+            bs1 = bsp[1];
+            dx_reg = A.xq.d[(size_t)rin_s * nblk + b];
+        }
         // ---- A: two digit tiles and the mins tile for this thread's row
-        const uint4 *blk = reinterpret_cast<const uint4 *>(wrow + (size_t)b * Q4_K_BYTES);
         const uint4 hdr = blk[0];
         const float dw = half_bits_to_float((uint16_t)(hdr.x & 0xffffu));
         const float dmin = half_bits_to_float((uint16_t)(hdr.x >> 16));
@@ -250,30 +272,18 @@ __global__ void __launch_bounds__(PF_THREADS, 2) k_gu_prefill(const GuArgs A)
             *reinterpret_cast<uint4 *>(S.am + core_off(PF_M, tid, 16)) = make_uint4(0, 0, 0, 0);
         }
         // ---- B: the tile's quantised activations for this block; token = tid / 2, half = tid & 1
-        {
-            const int tk = tid >> 1, half = tid & 1;
-            const int rin = S.row_in[tk];
-            const uint4 *src = rin >= 0 ? reinterpret_cast<const uint4 *>(A.xq.qs + (size_t)rin * A.H + b * QK_K + 128 * half)
-                                        : nullptr;
 #pragma unroll
-            for (int i = 0; i < 8; i++) {
-                const uint4 v = src ? src[i] : make_uint4(0, 0, 0, 0);
-                *reinterpret_cast<uint4 *>(S.b + core_off(PF_NT, tk, 128 * half + 16 * i)) = v;
-            }
-        }
+        for (int i = 0; i < 8; i++)
+            *reinterpret_cast<uint4 *>(S.b + core_off(PF_NT, tk, 128 * half + 16 * i)) = bv[i];
         if (tid < PF_NT) {  // partial sums of 16 quants as two digits: bsum = 64*h + l, l in [0,63]
-            const int rin = S.row_in[tid];
             uint32_t hw[4] = {0, 0, 0, 0}, lw[4] = {0, 0, 0, 0};
-            float dx = 0.f;
-            if (rin >= 0) {
-                const int16_t *bs = A.xq.bsums + (size_t)rin * (A.H / 16) + b * 16;
+            const float dx = dx_reg;
+            const uint32_t bw[8] = {bs0.x, bs0.y, bs0.z, bs0.w, bs1.x, bs1.y, bs1.z, bs1.w};  // 16 x int16
 #pragma unroll
-                for (int i = 0; i < 16; i++) {
-                    const int v = bs[i];
-                    hw[i >> 2] |= (uint32_t)((v >> 6) & 0xFF) << (8 * (i & 3));
-                    lw[i >> 2] |= (uint32_t)(v & 63) << (8 * (i & 3));
-                }
-                dx = A.xq.d[(size_t)rin * nblk + b];
+            for (int i = 0; i < 16; i++) {
+                const int v = (int)(int16_t)(bw[i >> 1] >> (16 * (i & 1)));
+                hw[i >> 2] |= (uint32_t)((v >> 6) & 0xFF) << (8 * (i & 3));
+                lw[i >> 2] |= (uint32_t)(v & 63) << (8 * (i & 3));
             }
             *reinterpret_cast<uint4 *>(S.bh + core_off(PF_NT, tid, 0)) = make_uint4(hw[0], hw[1], hw[2], hw[3]);
             *reinterpret_cast<uint4 *>(S.bh + core_off(PF_NT, tid, 16)) = make_uint4(0, 0, 0, 0);
@@ -298,6 +308,10 @@ __global__ void __launch_bounds__(PF_THREADS, 2) k_gu_prefill(const GuArgs A)
             mma_i8(tmem + 128, dam, smem_desc(S.bh, PF_NT * 16, 128), IDESC_UU_S, 0);
             mma_i8(tmem + 192, dam, smem_desc(S.bl, PF_NT * 16, 128), IDESC_UU_U, 0);
             tc_commit(&S.bar);
+        }
+        if (b + 1 < nblk) {  // next block of this thread's row, in flight during the MMAs and the fold
+#pragma unroll
+            for (int i = 0; i < 9; i++) blk[i] = reinterpret_cast<const uint4 *>(wrow + (size_t)(b + 1) * Q4_K_BYTES)[i];
         }
         if (!mbar_wait(&S.bar, phase)) {
             set_status(A.status, PMOE_ERR_TIMEOUT, 30, b);
