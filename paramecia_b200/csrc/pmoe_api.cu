@@ -124,6 +124,7 @@ void carve_workspace(pmoe_layer *L, Carver &c)
     w.groups.n_active = c.take<int>(1);
     w.groups.cost_prefix = c.take<int>(El + 1);
     w.groups.tile_prefix = c.take<int>(El + 1);
+    w.groups.tile_table = c.take<int2>(n * k / PREFILL_NT + El + 1);
     w.act = c.take<float>(rows * F);
     w.act_q8k.qs = c.take<int8_t>(rows * F);
     w.act_q8k.d = c.take<float>(rows * (F / QK_K));

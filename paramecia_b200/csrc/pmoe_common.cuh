@@ -117,6 +117,24 @@ __device__ inline bool mbar_wait(uint64_t *bar, uint32_t parity, uint32_t max_po
     return false;
 }
 
+// The same wait without a suspend hint: plain polling, for waits that are expected to be short.
+__device__ inline bool mbar_wait_spin(uint64_t *bar, uint32_t parity, uint32_t max_polls = (1u << 24))
+{
+    uint32_t addr = smem_u32(bar);
+    for (uint32_t i = 0; i < max_polls; i++) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+
 // 1-D bulk copy global -> this CTA's shared memory through the TMA unit (no multicast).
 // Both addresses 16-byte aligned, size a multiple of 16.
 __device__ inline void bulk_g2s(void *smem_dst, const void *gmem_src, uint32_t bytes, uint64_t *bar)
@@ -194,6 +212,7 @@ struct Groups {
     int *n_active;    // [1]
     int *cost_prefix; // [E_local + 1] exclusive prefix over active slots of ceil(count / GEMV_TG)
     int *tile_prefix; // [E_local + 1] exclusive prefix over active slots of ceil(count / PREFILL_NT)
+    int2 *tile_table; // [tile_prefix[n_active]] (local expert id, tile index inside the expert) per prefill tile
 };
 
 constexpr int GEMV_TG = 2;      // tokens one GEMV pass handles; the unit of the work partition

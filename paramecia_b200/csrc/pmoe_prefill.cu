@@ -148,13 +148,9 @@ __global__ void __launch_bounds__(PF_THREADS, 2) k_gu_prefill(const GuArgs A)
     if (tile >= routed_tiles + shared_tiles) return;
     if (tid == 0) {
         if (tile < routed_tiles) {
-            int lo = 0, hi = n_active - 1;  // largest slot with prefix[slot] <= tile
-            while (lo < hi) {
-                const int mid = (lo + hi + 1) >> 1;
-                if (A.tile_prefix[mid] <= tile) lo = mid; else hi = mid - 1;
-            }
-            S.slot = lo;
-            S.tile_in_slot = tile - A.tile_prefix[lo];
+            const int2 ti = A.g.tile_table[tile];  // (local expert, tile inside the expert)
+            S.slot = ti.x;
+            S.tile_in_slot = ti.y;
         } else {
             S.slot = -1;
             S.tile_in_slot = tile - routed_tiles;
@@ -176,7 +172,7 @@ __global__ void __launch_bounds__(PF_THREADS, 2) k_gu_prefill(const GuArgs A)
         m = A.n;
         wg = A.sgate; wu = A.sup;
     } else {
-        const int e = A.g.active[slot];
+        const int e = slot;
         m = A.g.count[e];
         list = A.g.pairs + A.g.offset[e];
         wg = A.gate + (size_t)e * A.expert_bytes;
@@ -313,7 +309,7 @@ __global__ void __launch_bounds__(PF_THREADS, 2) k_gu_prefill(const GuArgs A)
 #pragma unroll
             for (int i = 0; i < 9; i++) blk[i] = reinterpret_cast<const uint4 *>(wrow + (size_t)(b + 1) * Q4_K_BYTES)[i];
         }
-        if (!mbar_wait(&S.bar, phase)) {
+        if (!mbar_wait_spin(&S.bar, phase)) {
             set_status(A.status, PMOE_ERR_TIMEOUT, 30, b);
             ok = false;
         }
@@ -343,20 +339,20 @@ __global__ void __launch_bounds__(PF_THREADS, 2) k_gu_prefill(const GuArgs A)
         tc_fence_after();
     }
 
-    // ---- silu(gate) * up: up rows (threads 64..127) hand their sums over through shared memory
-    float *xch = reinterpret_cast<float *>(S.a0);  // [64 rows][PF_NT + 1]
-    if (tid >= 64) {
+    // ---- silu(gate) * up: all rows hand their sums over through shared memory ([128][PF_NT + 1]
+    // floats over the digit tiles, which no MMA reads any more), then every thread takes a share
+    // of the 64 x PF_NT outputs: output o = (token j, column f), consecutive threads = consecutive f.
+    float *xch = reinterpret_cast<float *>(S.a0);
 #pragma unroll
-        for (int j = 0; j < PF_NT; j++) xch[(tid - 64) * (PF_NT + 1) + j] = acc[j];
-    }
+    for (int j = 0; j < PF_NT; j++) xch[tid * (PF_NT + 1) + j] = acc[j];
     __syncthreads();
-    if (tid < 64 && ok) {
-#pragma unroll
-        for (int j = 0; j < PF_NT; j++) {
+    if (ok) {
+        for (int o = tid; o < 64 * PF_NT; o += PF_THREADS) {
+            const int f = o & 63, j = o >> 6;
             const int rout = S.row_out[j];
             if (rout < 0) continue;
-            const float g = acc[j], u = xch[tid * (PF_NT + 1) + j];
-            A.act[(size_t)rout * A.F + f0 + tid] = g / (1.f + expf(-g)) * u;
+            const float g = xch[f * (PF_NT + 1) + j], u = xch[(64 + f) * (PF_NT + 1) + j];
+            A.act[(size_t)rout * A.F + f0 + f] = g / (1.f + expf(-g)) * u;
         }
     }
     __syncthreads();
@@ -506,13 +502,9 @@ __global__ void __launch_bounds__(PF_THREADS, 2) k_down_prefill(const DownArgs A
     if (tile >= routed_tiles + shared_tiles) return;
     if (tid == 0) {
         if (tile < routed_tiles) {
-            int lo = 0, hi = n_active - 1;
-            while (lo < hi) {
-                const int mid = (lo + hi + 1) >> 1;
-                if (A.tile_prefix[mid] <= tile) lo = mid; else hi = mid - 1;
-            }
-            S.slot = lo;
-            S.tile_in_slot = tile - A.tile_prefix[lo];
+            const int2 ti = A.g.tile_table[tile];
+            S.slot = ti.x;
+            S.tile_in_slot = ti.y;
         } else {
             S.slot = -1;
             S.tile_in_slot = tile - routed_tiles;
@@ -535,7 +527,7 @@ __global__ void __launch_bounds__(PF_THREADS, 2) k_down_prefill(const DownArgs A
         m = A.n;
         wd = A.sdown;
     } else {
-        const int e = A.g.active[slot];
+        const int e = slot;
         m = A.g.count[e];
         list = A.g.pairs + A.g.offset[e];
         wd = A.down + (size_t)e * A.expert_bytes;
@@ -590,7 +582,7 @@ __global__ void __launch_bounds__(PF_THREADS, 2) k_down_prefill(const DownArgs A
             }
             tc_commit(&S.bar_mma);
         }
-        if (!mbar_wait(&S.bar_mma, phase)) {
+        if (!mbar_wait_spin(&S.bar_mma, phase)) {
             set_status(A.status, PMOE_ERR_TIMEOUT, 32, s);
             ok = false;
         }

@@ -417,6 +417,7 @@ __global__ void __launch_bounds__(GROUP_THREADS) k_group(const uint32_t *__restr
             g.active[act_scan[tid] - 1] = tid;
             g.cost_prefix[act_scan[tid] - 1] = cost_scan[tid] - cost;
             g.tile_prefix[act_scan[tid] - 1] = tile_scan[tid] - tiles;
+            for (int i = 0; i < tiles; i++) g.tile_table[tile_scan[tid] - tiles + i] = make_int2(tid, i);
         }
     }
     if (tid == GROUP_THREADS - 1) {
