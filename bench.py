@@ -351,30 +351,36 @@ def main():
         nb = len(blocks)
         xs = [make_x(n_tok, 100 + i) for i in range(nb)]
         out = torch.empty((n_tok, H), dtype=torch.bfloat16, device=dev)
+        fwd = [(eps[i].forward_into if N > 1 else blocks[i].forward_into) for i in range(nb)]
         side = torch.cuda.Stream(device=dev)
         side.wait_stream(torch.cuda.current_stream(dev))
         with torch.cuda.stream(side):
             for i in range(nb):
-                blocks[i].forward_into(xs[i], out)
+                fwd[i](xs[i], out)
         torch.cuda.current_stream(dev).wait_stream(side)
-        torch.cuda.synchronize()
+        barrier()
         g = torch.cuda.CUDAGraph()
         before_cap = pm.launch_count()
         with torch.cuda.graph(g):
             for i in range(nb):
-                blocks[i].forward_into(xs[i], out)
+                fwd[i](xs[i], out)
         per_replay = pm.launch_count() - before_cap
         reps = max(1, steps // nb)
         for _ in range(max(1, warmup // nb)):
             g.replay()
-        torch.cuda.synchronize()
+        barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for _ in range(reps):
             g.replay()
         e1.record()
-        torch.cuda.synchronize()
-        return e0.elapsed_time(e1), reps * nb, per_replay * reps
+        barrier()
+        g_ms = e0.elapsed_time(e1)
+        if N > 1:
+            t_ = torch.tensor([g_ms], device=dev)
+            dist.all_reduce(t_, op=dist.ReduceOp.MAX)
+            g_ms = float(t_.item())
+        return g_ms, reps * nb, per_replay * reps
 
     def distinct_experts(n_tok):
         """Average number of distinct local experts a step touches (for the algorithmic bytes)."""
@@ -400,11 +406,11 @@ def main():
     launch_mode = "direct C-ABI calls"
     direct = dict(tokens_per_s=value, ms_per_step=ms_per_step)
     steps_done = args.steps
-    if N == 1 and not args.no_graph:
+    if not args.no_graph:
         g_ms, g_steps, g_launches = time_steps_graph(batch, args.steps, W)
         if g_ms / g_steps < ms_per_step:
             ms, ms_per_step, steps_done, launches = g_ms, g_ms / g_steps, g_steps, g_launches
-            value = batch * g_steps / (g_ms * 1e-3)
+            value = batch * N * g_steps / (g_ms * 1e-3)
             launch_mode = f"CUDA graph holding one forward per layer ({len(blocks)}), replayed"
 
     # ---- roofline of the dominant kernel (gate/up GEMV): traced pass, events around each kernel
