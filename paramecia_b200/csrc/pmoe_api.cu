@@ -134,6 +134,7 @@ void carve_workspace(pmoe_layer *L, Carver &c)
     w.act_q80.bsums = nullptr;
     w.act_h = c.take<__half>(rows * F);
     w.partial = c.take<float>(rows * H);
+    w.slot_done = c.take<int>(El + 1);
     L->st_x = c.take<float>(n * H);
     L->st_out = c.take<float>(n * H);
     L->st_logits = c.take<float>(n * E);
@@ -231,7 +232,9 @@ int run_experts(pmoe_layer *L, const void *x, int x_dtype, const uint32_t *idx, 
     if (prefill && prefill_down_supported(d, routed, shared)) {
         PHASE(L, 6, s, launch_down_prefill(d, L->ws, w, n, top_k, routed, shared, s));
     } else {
-        PHASE(L, 5, s, launch_act_quant(d, L->ws, idx, n, top_k, routed, shared, s));
+        // the decode gate/up kernel has already re-quantised every expert's activated rows (last-CTA
+        // ticket); after the tensor-core gate/up kernel a separate pass does it
+        if (prefill) PHASE(L, 5, s, launch_act_quant(d, L->ws, idx, n, top_k, routed, shared, s));
         PHASE(L, 6, s, launch_down(d, L->ws, w, n, top_k, routed, shared, s));
     }
     PHASE(L, 7, s, launch_combine(d, L->ws, idx, n, top_k, routed, shared, out, out_dtype, s));
@@ -339,6 +342,7 @@ int pmoe_layer_create(const pmoe_layer_desc *desc, pmoe_layer **out)
             Carver real{(uint8_t *)block};
             carve_workspace(L, real);
             e = cudaMemset(L->ws.status, 0, sizeof(DevStatus));
+            if (e == cudaSuccess) e = cudaMemset(L->ws.slot_done, 0, sizeof(int) * (El + 1));
             if (e != cudaSuccess) rc = fail_cuda(e, "workspace");
         }
     }
@@ -429,8 +433,8 @@ int pmoe_forward(pmoe_layer *L, const void *x, int x_dtype, int n, void *out, in
     float *w = w_out ? w_out : L->ws.topk_w;
     Needs nd = input_needs(d, true, d.has_shared);
     for (bool &u : L->ev_used) u = false;
-    PHASE(L, 0, s, launch_prep(d, L->ws, x, x_dtype, n, nd.q8k, nd.q80, d.has_shared, s));
-    PHASE(L, 1, s, launch_router(d, L->ws, x, x_dtype, n, logits, s));
+    // one launch: router rows plus, in extra CTAs, the per-token preparation
+    PHASE(L, 1, s, launch_router(d, L->ws, x, x_dtype, n, logits, s, true, nd.q8k, nd.q80, d.has_shared));
     PHASE(L, 2, s, launch_topk(d, L->ws, logits, n, idx, w, s));
     return run_experts(L, x, x_dtype, idx, w, n, d.k, true, d.has_shared, true, out, out_dtype, s);
 }

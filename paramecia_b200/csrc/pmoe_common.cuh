@@ -243,6 +243,7 @@ struct Workspace {
     QAct act_q8k, act_q80;
     __half *act_h;       // [n*(k+1), F]  fake-quantised activation for the fp16 down GEMM
     float *partial;      // [n*(k+1), H]  weighted down-projection rows
+    int *slot_done;      // [E_local + 1] per-expert completion counters of the gate/up kernel (zero between calls)
 };
 
 // ---------------------------------------------------------------- launch interface
@@ -250,7 +251,8 @@ struct Workspace {
 cudaError_t launch_prep(const LayerDev &L, const Workspace &ws, const void *x, int x_dtype, int n,
                         bool need_q8k, bool need_q80, bool need_gate, cudaStream_t s);
 cudaError_t launch_router(const LayerDev &L, const Workspace &ws, const void *x, int x_dtype, int n,
-                          float *logits, cudaStream_t s);
+                          float *logits, cudaStream_t s, bool prep = false, bool need_q8k = false,
+                          bool need_q80 = false, bool need_gate = false);
 cudaError_t launch_topk(const LayerDev &L, const Workspace &ws, const float *logits, int n,
                         uint32_t *idx, float *w, cudaStream_t s);
 cudaError_t launch_group(const LayerDev &L, const Workspace &ws, const uint32_t *idx, int n, int top_k,

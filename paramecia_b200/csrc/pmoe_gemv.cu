@@ -262,6 +262,10 @@ struct GemvArgs {
     const float *scale_s;      // shared gate sigmoid [n]        (down only)
     DevStatus *status;
     int debug;                 // 1: skip the arithmetic, 2: skip the copies (timing experiments)
+    // gate/up only: the CTA that completes an expert's last item re-quantises the expert's activated rows
+    int *slot_done;            // [E_local + 1] items finished per slot (shared expert last); returns to zero
+    int quant_dt_r, quant_dt_s; // block types the down matrices will consume (0 = no fused re-quantisation)
+    QAct q8k_out, q80_out;
 };
 
 
@@ -447,6 +451,33 @@ template <int DT_R, int DT_S1, int NMAT> struct Producer {
     }
 };
 
+// Called by the eight compute warps when they leave a slot: adds the items this CTA finished to the slot's
+// counter; the CTA that brings it to `cpe` (all rows of the expert's activation are in memory) quantises those
+// rows for the down projection.  Writers fence before the counter update, the reader after it.
+__device__ inline void finish_slot(const GemvArgs &A, int counter_idx, int items, int cpe, bool is_shared,
+                                   const int *list, int m, int warp, int lane)
+{
+    __shared__ int s_last;
+    if (A.debug == 4) return;
+    asm volatile("bar.sync 2, 256;" ::: "memory");
+    if (warp == 0 && lane == 0) {
+        __threadfence();
+        const int old = atomicAdd(&A.slot_done[counter_idx], items);
+        s_last = old + items == cpe;
+        if (s_last) A.slot_done[counter_idx] = 0;
+    }
+    asm volatile("bar.sync 2, 256;" ::: "memory");
+    if (!s_last || A.debug == 3) return;
+    __threadfence();
+    const int dt = is_shared ? A.quant_dt_s : A.quant_dt_r;
+    const bool kq = is_kquant(dt);
+    for (int i = warp; i < m; i += GEMV_WARPS) {
+        const size_t r = is_shared ? (size_t)A.n * A.top_k + i : (size_t)list[i];
+        if (A.rows_total == 512) warp_quant_row512(A.out + r * 512, kq, A.q8k_out, A.q80_out, r, lane);
+        else block_quant_row(A.out + r * A.rows_total, A.rows_total, kq, !kq, A.q8k_out, A.q80_out, r, 0, 1, lane);
+    }
+}
+
 // The CTA's items of one kind (routed or shared), consumed in order from `cur` while the slot
 // stays below `slot_end`.  `it` numbers the CTA's items; the ring position follows from it.
 template <int DT, int NMAT>
@@ -456,6 +487,7 @@ __device__ inline bool run_items(const GemvArgs &A, uint8_t *ring, const Plan &p
     using C = Cfg<DT, NMAT>;
     using Act = typename Tr<DT>::Act;
     const int ul = lane % C::LPR;
+    const int cpe_of = is_shared ? plan.cpe_s : plan.cpe_r;
     int cur_slot = -1, m = 0;
     const int *list = nullptr;
     Pass P;
@@ -463,10 +495,16 @@ __device__ inline bool run_items(const GemvArgs &A, uint8_t *ring, const Plan &p
     typename Dot<DT>::Pre pre[C::UPL];
 #pragma unroll
     for (int i = 0; i < C::UPL; i++) pre[i] = Dot<DT>::pre(i * C::LPR + ul);
+    const bool fuse_quant = NMAT == 2 && (is_shared ? A.quant_dt_s : A.quant_dt_r) != 0;
+    int items_in_slot = 0;
+    bool failed = false;
     while (it < n_items && cur.slot < slot_end) {
         const int s = it % NSTAGE;
         const uint32_t use = (uint32_t)(it / NSTAGE);
         if (cur.slot != cur_slot) {
+            if (fuse_quant && cur_slot >= 0)
+                finish_slot(A, is_shared ? plan.n_active : cur_slot, items_in_slot, cpe_of, is_shared, list, m, warp, lane);
+            items_in_slot = 0;
             cur_slot = cur.slot;
             if (is_shared) {
                 m = A.n;
@@ -477,12 +515,14 @@ __device__ inline bool run_items(const GemvArgs &A, uint8_t *ring, const Plan &p
             }
             if (m <= TG) load_pass<DT, NMAT>(A, is_shared, list, m, 0, in, ul, P, act);
         }
-        if (A.debug != 2 && !mbar_wait(ring_full(ring, s), use & 1)) {
+        // a wait that runs out is recorded and the warp keeps walking its items without computing,
+        // so that the barriers it shares with the other warps still see it
+        if (!failed && A.debug != 2 && !mbar_wait(ring_full(ring, s), use & 1)) {
             set_status(A.status, PMOE_ERR_TIMEOUT, 10 + NMAT, it);
-            return false;
+            failed = true;
         }
         const uint8_t *stage = ring_stage(ring, s);
-        if (A.debug == 1) {
+        if (A.debug == 1 || failed) {
         } else if (m <= TG) {
             if (P.cnt == TG) compute_item<DT, NMAT, TG>(A, stage, cur.chunk, P, act, pre, warp, lane);
             else compute_item<DT, NMAT, 1>(A, stage, cur.chunk, P, act, pre, warp, lane);
@@ -497,8 +537,11 @@ __device__ inline bool run_items(const GemvArgs &A, uint8_t *ring, const Plan &p
         if (lane == 0) mbar_arrive(ring_empty(ring, s));
         plan.advance(cur);
         it++;
+        items_in_slot++;
     }
-    return true;
+    if (fuse_quant && cur_slot >= 0)
+        finish_slot(A, is_shared ? plan.n_active : cur_slot, items_in_slot, cpe_of, is_shared, list, m, warp, lane);
+    return !failed;
 }
 
 // DT_S == 0 compiles the kernel without a shared-expert branch.
@@ -628,6 +671,11 @@ cudaError_t launch_gate_up(const LayerDev &L, const Workspace &ws, int n, int to
     A.out = ws.act;
     A.status = ws.status;
     A.debug = getenv("PMOE_DEBUG") ? atoi(getenv("PMOE_DEBUG")) : 0;
+    A.slot_done = ws.slot_done;
+    A.quant_dt_r = routed ? L.down_dtype : 0;
+    A.quant_dt_s = shared ? L.sh_down_dtype : 0;
+    A.q8k_out = ws.act_q8k;
+    A.q80_out = ws.act_q80;
     // a kernel without routed items still needs a routed type to instantiate; reuse the shared one
     return launch_gemv<2>(A, routed ? L.gate_dtype : L.sh_gate_dtype, shared ? L.sh_gate_dtype : 0, s);
 }

@@ -14,24 +14,28 @@ namespace pmoe {
 // One CTA per token: widen the row to f32 in shared memory, quantise it for the expert
 // mat-muls and evaluate the shared expert's gate sigmoid(sum_j x_j * w_j)
 // (SharedExpert::forward, qwen3_next.rs:1811-1812).
+// per-token work; any block size up to 8 warps; xrow = H floats of shared memory
+struct PrepArgs {
+    int n;             // tokens to prepare (0 = none)
+    bool q8k, q80;
+    QAct a8k, a80;
+    const float *gate_inp;
+    float *sh_sigmoid;
+};
+
 template <typename XT>
-__global__ void __launch_bounds__(256) k_prep(const XT *__restrict__ x, int H, bool q8k, bool q80, QAct a8k,
-                                              QAct a80, const float *__restrict__ gate_inp,
-                                              float *__restrict__ sh_sigmoid)
+__device__ inline void prep_token(const XT *__restrict__ x, int H, int t, const PrepArgs &P, float *xrow, float *red)
 {
-    extern __shared__ __align__(16) float xrow[];
-    __shared__ float red[8];
-    const int t = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     float part = 0.f;
     for (int h = threadIdx.x; h < H; h += blockDim.x) {
         float v = load_as_float(x, (size_t)t * H + h);
         xrow[h] = v;
-        if (gate_inp) part += v * gate_inp[h];
+        if (P.gate_inp) part += v * P.gate_inp[h];
     }
     __syncthreads();
-    block_quant_row(xrow, H, q8k, q80, a8k, a80, t, warp, blockDim.x >> 5, lane);
-    if (gate_inp) {
+    block_quant_row(xrow, H, P.q8k, P.q80, P.a8k, P.a80, t, warp, blockDim.x >> 5, lane);
+    if (P.gate_inp) {
 #pragma unroll
         for (int s = 16; s >= 1; s >>= 1) part += __shfl_xor_sync(0xffffffffu, part, s);
         if (lane == 0) red[warp] = part;
@@ -39,9 +43,28 @@ __global__ void __launch_bounds__(256) k_prep(const XT *__restrict__ x, int H, b
         if (threadIdx.x == 0) {
             float s = 0.f;
             for (int w = 0; w < (int)(blockDim.x >> 5); w++) s += red[w];
-            sh_sigmoid[t] = 1.f / (1.f + expf(-s));
+            P.sh_sigmoid[t] = 1.f / (1.f + expf(-s));
         }
     }
+}
+
+template <typename XT>
+__global__ void __launch_bounds__(256) k_prep(const XT *__restrict__ x, int H, PrepArgs P)
+{
+    extern __shared__ __align__(16) float xrow[];
+    __shared__ float red[8];
+    prep_token(x, H, blockIdx.x, P, xrow, red);
+}
+
+static PrepArgs make_prep_args(const LayerDev &L, const Workspace &ws, int n, bool need_q8k, bool need_q80, bool need_gate)
+{
+    PrepArgs P{};
+    P.n = n;
+    P.q8k = need_q8k; P.q80 = need_q80;
+    P.a8k = ws.x_q8k; P.a80 = ws.x_q80;
+    P.gate_inp = need_gate ? L.sh_gate_inp : nullptr;
+    P.sh_sigmoid = ws.sh_sigmoid;
+    return P;
 }
 
 cudaError_t launch_prep(const LayerDev &L, const Workspace &ws, const void *x, int x_dtype, int n, bool need_q8k,
@@ -49,13 +72,9 @@ cudaError_t launch_prep(const LayerDev &L, const Workspace &ws, const void *x, i
 {
     if (n <= 0) return cudaSuccess;
     size_t smem = (size_t)L.H * sizeof(float);
-    const float *gi = need_gate ? L.sh_gate_inp : nullptr;
-    if (x_dtype == PMOE_F32)
-        k_prep<float><<<n, 256, smem, s>>>((const float *)x, L.H, need_q8k, need_q80, ws.x_q8k, ws.x_q80, gi,
-                                           ws.sh_sigmoid);
-    else
-        k_prep<__nv_bfloat16><<<n, 256, smem, s>>>((const __nv_bfloat16 *)x, L.H, need_q8k, need_q80, ws.x_q8k,
-                                                   ws.x_q80, gi, ws.sh_sigmoid);
+    const PrepArgs P = make_prep_args(L, ws, n, need_q8k, need_q80, need_gate);
+    if (x_dtype == PMOE_F32) k_prep<float><<<n, 256, smem, s>>>((const float *)x, L.H, P);
+    else k_prep<__nv_bfloat16><<<n, 256, smem, s>>>((const __nv_bfloat16 *)x, L.H, P);
     count_launch();
     return cudaGetLastError();
 }
@@ -80,8 +99,14 @@ template <typename XT, int TT>
 __global__ void __launch_bounds__(ROUTER_WPB * 32) k_router(const float *__restrict__ W,
                                                             const float *__restrict__ bias,
                                                             const XT *__restrict__ x, int n, int E, int H,
-                                                            float *__restrict__ logits)
+                                                            float *__restrict__ logits, int router_ctas, PrepArgs P)
 {
+    extern __shared__ __align__(16) float xrow[];
+    __shared__ float red[8];
+    if ((int)blockIdx.x >= router_ctas) {  // CTAs past the router rows prepare one token each
+        prep_token(x, H, (int)blockIdx.x - router_ctas, P, xrow, red);
+        return;
+    }
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int e = blockIdx.x * ROUTER_WPB + warp;
     if (e >= E) return;
@@ -127,9 +152,16 @@ template <typename XT>
 __global__ void __launch_bounds__(RT_WARPS * 32) k_router_tiled(const float *__restrict__ W,
                                                                 const float *__restrict__ bias,
                                                                 const XT *__restrict__ x, int n, int E, int H,
-                                                                int rows_per_cta, float *__restrict__ logits)
+                                                                int rows_per_cta, float *__restrict__ logits,
+                                                                int token_tiles, PrepArgs P)
 {
     extern __shared__ __align__(16) float xs[];  // [RT_TOKENS][H]
+    __shared__ float red[8];
+    if ((int)blockIdx.y >= token_tiles) {  // grid rows past the token tiles prepare one token per CTA
+        const int t = ((int)blockIdx.y - token_tiles) * gridDim.x + blockIdx.x;
+        if (t < P.n) prep_token(x, H, t, P, xs, red);
+        return;
+    }
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t0 = blockIdx.y * RT_TOKENS;
     const int nt = n - t0 < RT_TOKENS ? n - t0 : RT_TOKENS;
@@ -225,27 +257,33 @@ __global__ void __launch_bounds__(RT_WARPS * 32) k_router_wide(const float *__re
     }
 }
 
+// Router launch.  With `prep` set the same launch also prepares the tokens (quantised rows, shared
+// gate) in extra CTAs, which saves the separate k_prep launch of a decode-sized call.
 cudaError_t launch_router(const LayerDev &L, const Workspace &ws, const void *x, int x_dtype, int n, float *logits,
-                          cudaStream_t s)
+                          cudaStream_t s, bool prep, bool need_q8k, bool need_q80, bool need_gate)
 {
-    (void)ws;
     if (n <= 0) return cudaSuccess;
+    const bool f32 = x_dtype == PMOE_F32;
+    using BT = __nv_bfloat16;
     if (n > 512 && L.H == 2048) {
+        if (prep) {
+            cudaError_t e = launch_prep(L, ws, x, x_dtype, n, need_q8k, need_q80, need_gate, s);
+            if (e != cudaSuccess) return e;
+        }
         static bool configured_wide = false;
         if (!configured_wide) {
             cudaError_t e1 = cudaFuncSetAttribute(k_router_wide<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 131072);
-            cudaError_t e2 = cudaFuncSetAttribute(k_router_wide<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 131072);
+            cudaError_t e2 = cudaFuncSetAttribute(k_router_wide<BT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 131072);
             if (e1 != cudaSuccess) return e1;
             if (e2 != cudaSuccess) return e2;
             configured_wide = true;
         }
         const int rows_per_cta = 64;
-        if (x_dtype == PMOE_F32) {
+        if (f32) {
             dim3 grid((L.E + rows_per_cta - 1) / rows_per_cta, (n + WideTile<float>::TT - 1) / WideTile<float>::TT);
             k_router_wide<float><<<grid, RT_WARPS * 32, 131072, s>>>(L.router_w, L.router_bias, (const float *)x, n, L.E,
                                                                      rows_per_cta, logits);
         } else {
-            using BT = __nv_bfloat16;
             dim3 grid((L.E + rows_per_cta - 1) / rows_per_cta, (n + WideTile<BT>::TT - 1) / WideTile<BT>::TT);
             k_router_wide<BT><<<grid, RT_WARPS * 32, 131072, s>>>(L.router_w, L.router_bias, (const BT *)x, n, L.E,
                                                                   rows_per_cta, logits);
@@ -253,40 +291,47 @@ cudaError_t launch_router(const LayerDev &L, const Workspace &ws, const void *x,
         count_launch();
         return cudaGetLastError();
     }
+    const PrepArgs P = make_prep_args(L, ws, prep ? n : 0, need_q8k, need_q80, need_gate);
     if (n > 8 && L.H <= 2048) {
         static bool configured = false;
         const size_t smem = (size_t)RT_TOKENS * L.H * sizeof(float);
         if (!configured) {
             cudaError_t e1 = cudaFuncSetAttribute(k_router_tiled<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 65536);
-            cudaError_t e2 = cudaFuncSetAttribute(k_router_tiled<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 65536);
+            cudaError_t e2 = cudaFuncSetAttribute(k_router_tiled<BT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 65536);
             if (e1 != cudaSuccess) return e1;
             if (e2 != cudaSuccess) return e2;
             configured = true;
         }
-        const int rows_per_cta = n <= 512 ? 8 : 64;
-        dim3 grid((L.E + rows_per_cta - 1) / rows_per_cta, (n + RT_TOKENS - 1) / RT_TOKENS);
-        if (x_dtype == PMOE_F32)
+        const int rows_per_cta = 8;
+        const int gx = (L.E + rows_per_cta - 1) / rows_per_cta, tiles = (n + RT_TOKENS - 1) / RT_TOKENS;
+        dim3 grid(gx, tiles + (P.n + gx - 1) / gx);
+        if (f32)
             k_router_tiled<float><<<grid, RT_WARPS * 32, smem, s>>>(L.router_w, L.router_bias, (const float *)x, n, L.E,
-                                                                    L.H, rows_per_cta, logits);
+                                                                    L.H, rows_per_cta, logits, tiles, P);
         else
-            k_router_tiled<__nv_bfloat16><<<grid, RT_WARPS * 32, smem, s>>>(
-                L.router_w, L.router_bias, (const __nv_bfloat16 *)x, n, L.E, L.H, rows_per_cta, logits);
+            k_router_tiled<BT><<<grid, RT_WARPS * 32, smem, s>>>(L.router_w, L.router_bias, (const BT *)x, n, L.E, L.H,
+                                                                 rows_per_cta, logits, tiles, P);
         count_launch();
         return cudaGetLastError();
     }
-    dim3 grid((L.E + ROUTER_WPB - 1) / ROUTER_WPB), block(ROUTER_WPB * 32);
-    if (x_dtype == PMOE_F32) {
+    if (L.H > 2048 && prep) {  // the shared-memory row of the fused form is sized for H <= 2048
+        cudaError_t e = launch_prep(L, ws, x, x_dtype, n, need_q8k, need_q80, need_gate, s);
+        if (e != cudaSuccess) return e;
+    }
+    const int rc = (L.E + ROUTER_WPB - 1) / ROUTER_WPB;
+    const int pn = L.H > 2048 ? 0 : P.n;
+    dim3 grid(rc + pn), block(ROUTER_WPB * 32);
+    const size_t smem = pn ? (size_t)L.H * sizeof(float) : 0;
+    if (f32) {
         if (n == 1)
-            k_router<float, 1><<<grid, block, 0, s>>>(L.router_w, L.router_bias, (const float *)x, n, L.E, L.H, logits);
+            k_router<float, 1><<<grid, block, smem, s>>>(L.router_w, L.router_bias, (const float *)x, n, L.E, L.H, logits, rc, P);
         else
-            k_router<float, 8><<<grid, block, 0, s>>>(L.router_w, L.router_bias, (const float *)x, n, L.E, L.H, logits);
+            k_router<float, 8><<<grid, block, smem, s>>>(L.router_w, L.router_bias, (const float *)x, n, L.E, L.H, logits, rc, P);
     } else {
         if (n == 1)
-            k_router<__nv_bfloat16, 1><<<grid, block, 0, s>>>(L.router_w, L.router_bias, (const __nv_bfloat16 *)x, n,
-                                                              L.E, L.H, logits);
+            k_router<BT, 1><<<grid, block, smem, s>>>(L.router_w, L.router_bias, (const BT *)x, n, L.E, L.H, logits, rc, P);
         else
-            k_router<__nv_bfloat16, 8><<<grid, block, 0, s>>>(L.router_w, L.router_bias, (const __nv_bfloat16 *)x, n,
-                                                              L.E, L.H, logits);
+            k_router<BT, 8><<<grid, block, smem, s>>>(L.router_w, L.router_bias, (const BT *)x, n, L.E, L.H, logits, rc, P);
     }
     count_launch();
     return cudaGetLastError();
