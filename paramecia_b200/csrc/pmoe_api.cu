@@ -123,6 +123,7 @@ void carve_workspace(pmoe_layer *L, Carver &c)
     w.groups.active = c.take<int>(El);
     w.groups.n_active = c.take<int>(1);
     w.groups.cost_prefix = c.take<int>(El + 1);
+    w.groups.cost_prefix_wide = c.take<int>(El + 1);
     w.groups.tile_prefix = c.take<int>(El + 1);
     w.groups.tile_table = c.take<int2>(n * k / PREFILL_NT + El + 1);
     w.act = c.take<float>(rows * F);

@@ -211,11 +211,13 @@ struct Groups {
     int *active;      // [E_local] local expert ids with count > 0, ascending
     int *n_active;    // [1]
     int *cost_prefix; // [E_local + 1] exclusive prefix over active slots of ceil(count / GEMV_TG)
+    int *cost_prefix_wide; // same with ceil(count / GEMV_TG_WIDE)
     int *tile_prefix; // [E_local + 1] exclusive prefix over active slots of ceil(count / PREFILL_NT)
     int2 *tile_table; // [tile_prefix[n_active]] (local expert id, tile index inside the expert) per prefill tile
 };
 
 constexpr int GEMV_TG = 2;      // tokens one GEMV pass handles; the unit of the work partition
+constexpr int GEMV_TG_WIDE = 4; // ... for the kernels whose activation registers are small (Q6_K / Q8_0 down)
 constexpr int PREFILL_NT = 64;  // tokens per tile of the prefill GEMMs
 
 // Everything a forward call needs, resolved to raw pointers.

@@ -32,7 +32,8 @@ constexpr int GEMV_THREADS = (GEMV_WARPS + 1) * 32;  // compute warps + one prod
 constexpr int NSTAGE = 3;
 constexpr int STAGE_BYTES = 36864;  // one ring slot
 constexpr int BULK_PIECE = 12288;   // bytes per bulk copy
-constexpr int TG = GEMV_TG;         // tokens per pass (activation registers kept per lane)
+constexpr int TG = GEMV_TG;         // tokens per pass of the gate/up kernels and of Q4_K down
+constexpr int TG_MAX = GEMV_TG_WIDE; // tokens per pass of the Q6_K / Q8_0 down kernels
 
 // ---------------------------------------------------------------- per-dtype lane units
 // A "unit" is the piece of a row one lane handles at a time.
@@ -134,7 +135,7 @@ template <> struct Dot<PMOE_Q4_K> {
         return Pre{(u >> 2) * Q4_K_BYTES, (u >> 2) * Q4_K_BYTES + 16 + 32 * qd, 16 * (qd & 1), qd >> 1};
     }
     template <int CNT>
-    __device__ static inline void run(const uint8_t *row, const Pre &p, const ActQ4K (&act)[TG], float *acc)
+    __device__ static inline void run(const uint8_t *row, const Pre &p, const ActQ4K *act, float *acc)
     {
         const uint4 hdr = *reinterpret_cast<const uint4 *>(row + p.hdr_off);
         const uint4 qa = *reinterpret_cast<const uint4 *>(row + p.q_off);
@@ -178,7 +179,7 @@ template <> struct Dot<PMOE_Q6_K> {
         return Pre{blk + 64 * half + 4 * j, blk + 128 + 32 * half + 4 * j, blk + 192 + 8 * half + (j >> 2), blk + 208};
     }
     template <int CNT>
-    __device__ static inline void run(const uint8_t *row, const Pre &p, const ActQ16 (&act)[TG], float *acc)
+    __device__ static inline void run(const uint8_t *row, const Pre &p, const ActQ16 *act, float *acc)
     {
         const uint32_t la = lds_u32_a2(row + p.la_off);
         const uint32_t lb = lds_u32_a2(row + p.la_off + 32);
@@ -207,7 +208,7 @@ template <> struct Dot<PMOE_Q8_0> {
     };
     __device__ static inline Pre pre(int u) { return Pre{(u >> 1) * Q8_0_BYTES, (u >> 1) * Q8_0_BYTES + 2 + 16 * (u & 1)}; }
     template <int CNT>
-    __device__ static inline void run(const uint8_t *row, const Pre &p, const ActQ16 (&act)[TG], float *acc)
+    __device__ static inline void run(const uint8_t *row, const Pre &p, const ActQ16 *act, float *acc)
     {
         const float d = half_bits_to_float(*reinterpret_cast<const uint16_t *>(row + p.d_off));
         uint32_t w[4];
@@ -239,10 +240,12 @@ template <int DT, int NMAT> struct Cfg {
                                      (DT == PMOE_Q8_0 ? Q8_0_BYTES : DT == PMOE_Q4_K ? Q4_K_BYTES : Q6_K_BYTES);
     static constexpr int ROWS = floor_pow2(STAGE_BYTES / (ROW_BYTES * NMAT));  // rows of each matrix per item
     static constexpr int ITEM_BYTES = ROWS * ROW_BYTES;                        // per matrix
+    // tokens per pass: bounded by the activation registers a lane keeps (16 words per token for Q4_K, 4 otherwise)
+    static constexpr int TGK = (NMAT == 1 && DT != PMOE_Q4_K) ? 4 : 2;
     static constexpr int RPW = ROWS / GEMV_WARPS;     // rows per warp per item
     static constexpr int PASSES = RPW / GROUPS;
-    static constexpr int RB = cmin(cmin(PASSES, 4), cmax(1, LPR / (NMAT * TG)));  // rows reduced together
-    static constexpr int V = NMAT * RB * TG;          // values per transposed reduction (<= LPR)
+    static constexpr int RB = cmin(cmin(PASSES, 4), cmax(1, LPR / (NMAT * TGK)));  // rows reduced together
+    static constexpr int V = NMAT * RB * TGK;         // values per transposed reduction (<= LPR)
     static_assert(RPW >= GROUPS && PASSES % RB == 0 && V <= LPR && ITEM_BYTES % 16 == 0, "bad tiling");
 };
 
@@ -272,18 +275,18 @@ struct GemvArgs {
 // Token rows of one pass.
 struct Pass {
     int cnt;
-    int out_row[TG];
-    float scale[TG];
+    int out_row[TG_MAX];
+    float scale[TG_MAX];
 };
 
 template <int DT, int NMAT>
 __device__ inline void load_pass(const GemvArgs &A, bool is_shared, const int *list, int m, int t0, const QAct &in,
-                                 int ul, Pass &P, typename Tr<DT>::Act (&act)[Cfg<DT, NMAT>::UPL][TG])
+                                 int ul, Pass &P, typename Tr<DT>::Act (&act)[Cfg<DT, NMAT>::UPL][Cfg<DT, NMAT>::TGK])
 {
     using C = Cfg<DT, NMAT>;
-    P.cnt = m - t0 < TG ? m - t0 : TG;
+    P.cnt = m - t0 < C::TGK ? m - t0 : C::TGK;
 #pragma unroll
-    for (int t = 0; t < TG; t++) {
+    for (int t = 0; t < C::TGK; t++) {
         P.out_row[t] = -1;
         P.scale[t] = 0.f;
         if (t < P.cnt) {
@@ -311,7 +314,7 @@ __device__ inline void load_pass(const GemvArgs &A, bool is_shared, const int *l
 // All rows of one item (in shared memory) against one pass of CNT tokens.
 template <int DT, int NMAT, int CNT>
 __device__ inline void compute_item(const GemvArgs &A, const uint8_t *stage, int chunk, const Pass &P,
-                                    const typename Tr<DT>::Act (&act)[Cfg<DT, NMAT>::UPL][TG],
+                                    const typename Tr<DT>::Act (&act)[Cfg<DT, NMAT>::UPL][Cfg<DT, NMAT>::TGK],
                                     const typename Dot<DT>::Pre (&pre)[Cfg<DT, NMAT>::UPL], int warp, int lane)
 {
     using C = Cfg<DT, NMAT>;
@@ -329,7 +332,7 @@ __device__ inline void compute_item(const GemvArgs &A, const uint8_t *stage, int
                 const uint8_t *rp = stage + mat * C::ITEM_BYTES + row * C::ROW_BYTES;
 #pragma unroll
                 for (int i = 0; i < C::UPL; i++) {
-                    Dot<DT>::template run<CNT>(rp, pre[i], act[i], acc + (mat * C::RB + rb) * TG);
+                    Dot<DT>::template run<CNT>(rp, pre[i], act[i], acc + (mat * C::RB + rb) * C::TGK);
                     // keeps the compiler from hoisting every unit's loads at once (register pressure)
                     if (C::UPL > 1) asm volatile("" ::: "memory");
                 }
@@ -338,15 +341,17 @@ __device__ inline void compute_item(const GemvArgs &A, const uint8_t *stage, int
         float v = transposed_reduce<C::V, C::LPR>(acc, lane);
         constexpr int DUP = C::LPR / C::V;  // lanes holding the same total
         const int vi = ul / DUP;
-        const int t = vi % TG, rb = (vi / TG) % C::RB, mat = vi / (TG * C::RB);
+        const int t = vi % C::TGK, rb = (vi / C::TGK) % C::RB, mat = vi / (C::TGK * C::RB);
         if (NMAT == 2) {
             const float other = __shfl_xor_sync(0xffffffffu, v, C::LPR / 2);  // up total sits LPR/2 lanes away
             v = v / (1.f + expf(-v)) * other;                                 // silu(gate) * up
         }
         const int row = chunk * C::ROWS + warp * C::RPW + (b0 + rb) * C::GROUPS + grp;
-        static_assert(TG == 2, "select below assumes two tokens per pass");
-        const int orow = t == 0 ? P.out_row[0] : P.out_row[1];
-        const float sc = t == 0 ? P.scale[0] : P.scale[1];
+        int orow = P.out_row[0];  // t depends on the lane: pick with selects, not an indexed load
+        float sc = P.scale[0];
+#pragma unroll
+        for (int q = 1; q < C::TGK; q++)
+            if (t == q) { orow = P.out_row[q]; sc = P.scale[q]; }
         if (ul % DUP == 0 && mat == 0 && orow >= 0)
             A.out[(size_t)orow * A.rows_total + row] = NMAT == 2 ? v : v * sc;
     }
@@ -451,6 +456,18 @@ template <int DT_R, int DT_S1, int NMAT> struct Producer {
     }
 };
 
+// One pass with the arithmetic compiled for the number of tokens actually present (1, 2 or up to TGK).
+template <int DT, int NMAT>
+__device__ inline void run_pass(const GemvArgs &A, const uint8_t *stage, int chunk, const Pass &P,
+                                const typename Tr<DT>::Act (&act)[Cfg<DT, NMAT>::UPL][Cfg<DT, NMAT>::TGK],
+                                const typename Dot<DT>::Pre (&pre)[Cfg<DT, NMAT>::UPL], int warp, int lane)
+{
+    using C = Cfg<DT, NMAT>;
+    if (P.cnt == 1) compute_item<DT, NMAT, 1>(A, stage, chunk, P, act, pre, warp, lane);
+    else if (P.cnt == 2 || C::TGK == 2) compute_item<DT, NMAT, 2>(A, stage, chunk, P, act, pre, warp, lane);
+    else compute_item<DT, NMAT, C::TGK>(A, stage, chunk, P, act, pre, warp, lane);  // 3 tokens: the 4th slot is zero
+}
+
 // Called by the eight compute warps when they leave a slot: adds the items this CTA finished to the slot's
 // counter; the CTA that brings it to `cpe` (all rows of the expert's activation are in memory) quantises those
 // rows for the down projection.  Writers fence before the counter update, the reader after it.
@@ -491,7 +508,7 @@ __device__ inline bool run_items(const GemvArgs &A, uint8_t *ring, const Plan &p
     int cur_slot = -1, m = 0;
     const int *list = nullptr;
     Pass P;
-    Act act[C::UPL][TG];
+    Act act[C::UPL][C::TGK];
     typename Dot<DT>::Pre pre[C::UPL];
 #pragma unroll
     for (int i = 0; i < C::UPL; i++) pre[i] = Dot<DT>::pre(i * C::LPR + ul);
@@ -513,7 +530,7 @@ __device__ inline bool run_items(const GemvArgs &A, uint8_t *ring, const Plan &p
                 m = A.g.count[e];
                 list = A.g.pairs + A.g.offset[e];
             }
-            if (m <= TG) load_pass<DT, NMAT>(A, is_shared, list, m, 0, in, ul, P, act);
+            if (m <= C::TGK) load_pass<DT, NMAT>(A, is_shared, list, m, 0, in, ul, P, act);
         }
         // a wait that runs out is recorded and the warp keeps walking its items without computing,
         // so that the barriers it shares with the other warps still see it
@@ -523,14 +540,12 @@ __device__ inline bool run_items(const GemvArgs &A, uint8_t *ring, const Plan &p
         }
         const uint8_t *stage = ring_stage(ring, s);
         if (A.debug == 1 || failed) {
-        } else if (m <= TG) {
-            if (P.cnt == TG) compute_item<DT, NMAT, TG>(A, stage, cur.chunk, P, act, pre, warp, lane);
-            else compute_item<DT, NMAT, 1>(A, stage, cur.chunk, P, act, pre, warp, lane);
+        } else if (m <= C::TGK) {
+            run_pass<DT, NMAT>(A, stage, cur.chunk, P, act, pre, warp, lane);
         } else {
-            for (int t0 = 0; t0 < m; t0 += TG) {
+            for (int t0 = 0; t0 < m; t0 += C::TGK) {
                 load_pass<DT, NMAT>(A, is_shared, list, m, t0, in, ul, P, act);
-                if (P.cnt == TG) compute_item<DT, NMAT, TG>(A, stage, cur.chunk, P, act, pre, warp, lane);
-                else compute_item<DT, NMAT, 1>(A, stage, cur.chunk, P, act, pre, warp, lane);
+                run_pass<DT, NMAT>(A, stage, cur.chunk, P, act, pre, warp, lane);
             }
         }
         __syncwarp();
@@ -560,9 +575,9 @@ __global__ void __launch_bounds__(GEMV_THREADS, 2) k_expert_gemv(const GemvArgs 
     plan.has_shared = (DT_S != 0 && A.has_shared) ? 1 : 0;
     plan.cpe_r = A.rows_total / CR::ROWS;
     plan.cpe_s = A.rows_total / CS::ROWS;
-    plan.cost_shared = (A.n + TG - 1) / TG;
+    plan.cost_shared = (A.n + CS::TGK - 1) / CS::TGK;
     plan.prefix = s_prefix;
-    for (int i = threadIdx.x; i <= plan.n_active; i += GEMV_THREADS) s_prefix[i] = plan.n_active ? A.g.cost_prefix[i] : 0;
+    for (int i = threadIdx.x; i <= plan.n_active; i += GEMV_THREADS) s_prefix[i] = plan.n_active ? (CR::TGK == GEMV_TG ? A.g.cost_prefix[i] : A.g.cost_prefix_wide[i]) : 0;
     if (threadIdx.x == 0) {
         for (int s = 0; s < NSTAGE; s++) {
             mbar_init(ring_full(ring, s), 1);

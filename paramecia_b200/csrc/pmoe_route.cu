@@ -423,6 +423,7 @@ __global__ void __launch_bounds__(GROUP_THREADS) k_group(const uint32_t *__restr
     __shared__ int act_scan[1024];
     __shared__ int cost_scan[1024];
     __shared__ int tile_scan[1024];
+    __shared__ int wide_scan[1024];
     const int tid = threadIdx.x;
     cnt[tid] = 0;
     __syncthreads();
@@ -439,19 +440,23 @@ __global__ void __launch_bounds__(GROUP_THREADS) k_group(const uint32_t *__restr
     scan[tid] = c;
     act_scan[tid] = flag;
     const int tiles = (c + PREFILL_NT - 1) / PREFILL_NT;
+    const int wcost = (c + GEMV_TG_WIDE - 1) / GEMV_TG_WIDE;
     cost_scan[tid] = cost;
     tile_scan[tid] = tiles;
+    wide_scan[tid] = wcost;
     __syncthreads();
     for (int off = 1; off < GROUP_THREADS; off <<= 1) {  // Hillis-Steele inclusive scans
         int a = tid >= off ? scan[tid - off] : 0;
         int b = tid >= off ? act_scan[tid - off] : 0;
         int d = tid >= off ? cost_scan[tid - off] : 0;
         int f = tid >= off ? tile_scan[tid - off] : 0;
+        int gw = tid >= off ? wide_scan[tid - off] : 0;
         __syncthreads();
         scan[tid] += a;
         act_scan[tid] += b;
         cost_scan[tid] += d;
         tile_scan[tid] += f;
+        wide_scan[tid] += gw;
         __syncthreads();
     }
     int excl = scan[tid] - c;
@@ -461,6 +466,7 @@ __global__ void __launch_bounds__(GROUP_THREADS) k_group(const uint32_t *__restr
         if (flag) {
             g.active[act_scan[tid] - 1] = tid;
             g.cost_prefix[act_scan[tid] - 1] = cost_scan[tid] - cost;
+            g.cost_prefix_wide[act_scan[tid] - 1] = wide_scan[tid] - wcost;
             g.tile_prefix[act_scan[tid] - 1] = tile_scan[tid] - tiles;
             for (int i = 0; i < tiles; i++) g.tile_table[tile_scan[tid] - tiles + i] = make_int2(tid, i);
         }
@@ -469,6 +475,7 @@ __global__ void __launch_bounds__(GROUP_THREADS) k_group(const uint32_t *__restr
         g.offset[E_local] = scan[tid];
         *g.n_active = act_scan[tid];
         g.cost_prefix[act_scan[tid]] = cost_scan[tid];
+        g.cost_prefix_wide[act_scan[tid]] = wide_scan[tid];
         g.tile_prefix[act_scan[tid]] = tile_scan[tid];
     }
     cnt[tid] = excl;  // reuse as the per-expert base
