@@ -302,7 +302,7 @@ cudaError_t launch_router(const LayerDev &L, const Workspace &ws, const void *x,
             if (e2 != cudaSuccess) return e2;
             configured = true;
         }
-        const int rows_per_cta = 8;
+        const int rows_per_cta = 16;
         const int gx = (L.E + rows_per_cta - 1) / rows_per_cta, tiles = (n + RT_TOKENS - 1) / RT_TOKENS;
         dim3 grid(gx, tiles + (P.n + gx - 1) / gx);
         if (f32)
