@@ -199,3 +199,25 @@ def test_qmatmul_entry_point(dtype, rows, cols):
     want = po.qmatmul(dtype, w, rows, cols, x)
     got = pm.qmatmul(pm.QTensor(w, dtype, (rows, cols)), torch.from_numpy(x).to(DEV)).cpu().numpy()
     assert rel_l2(got, want) <= 2e-6
+
+
+def test_stack_with_residual_and_rms_norm():
+    # BASELINE config 4 in miniature: h <- h + moe(rms_norm(h)) through independently seeded layers
+    # (LayerWeights::forward_with_stats, qwen3_next.rs:4273-4286; eps 1e-6, norm weight 1)
+    layers = [synth.make_layer(E=16, k=2, preset="q4k_m", seed=30, layer=li) for li in range(3)]
+    blocks = [synth.make_block(t, DEV, max_tokens=16) for t in layers]
+    oracles = [oracle_layer(t) for t in layers]
+    h0 = seeded_x(12, 2048, 8)
+    resid = h0.to(DEV)
+    delta = None
+    for blk in blocks:
+        resid, y = pm.add_rms_norm(resid, delta, None, 1e-6)
+        delta = blk.forward(y)
+    resid, _ = pm.add_rms_norm(resid, delta, None, 1e-6)
+    want = h0.numpy().copy()
+    for ol in oracles:
+        want = want + ol.forward(po.rms_norm(want, None, 1e-6))[0]
+    got = resid.cpu().numpy()
+    # compare the MoE contribution, not the residual stream that carries the input unchanged
+    assert rel_l2(got - h0.numpy(), want - h0.numpy()) <= REL_L2_TOL
+    assert max_abs(got, want) <= MAX_ABS_TOL
