@@ -46,7 +46,7 @@ def parse():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline")
     ap.add_argument("--no-graph", action="store_true", help="do not try CUDA-graph replay of the block")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
-    ap.add_argument("--ep-mode", default="all_to_all", choices=["all_to_all", "all_gather"])
+    ap.add_argument("--ep-mode", default="all_gather", choices=["all_to_all", "all_gather"])
     ap.add_argument("--mode", default="decode", choices=["decode", "prefill"],
                     help="decode: the headline workload; prefill: 4096 tokens, Zipf-skewed routing, one GPU")
     ap.add_argument("--tokens", type=int, default=4096, help="tokens per step in prefill mode")
@@ -445,18 +445,14 @@ def main():
             b.trace(True)
         for i in range(reps + 3):
             e = eps[i % len(eps)]
-            k2 = 2 * TOPK
-            meta = e.recv_meta.view(-1, k2)
-            e.block.experts_forward_batched(e.recv_x.view(-1, H), meta[:, :TOPK].contiguous(),
-                                            meta[:, TOPK:].contiguous().view(torch.float32), TOPK,
-                                            out_dtype=torch.float32)
+            e.block.experts_forward_batched(e.recv_x, e.recv_idx, e.recv_w, TOPK, shared_rows=(rank * batch, batch),
+                                            out=e.part)
             t = e.block.trace_read()
             if i >= 3:
                 for k_, v in t.items():
                     phase_ms[k_] = phase_ms.get(k_, 0.0) + v / reps
         for b in blocks:
             b.trace(False)
-        gu_bytes = D * F * (pm.row_bytes(d.gate_dtype, H) + pm.row_bytes(d.up_dtype, H))  # no shared expert in this call
     roofline = None
     if phase_ms.get("gate_up"):
         ach = gu_bytes / (phase_ms["gate_up"] * 1e-3) / 1e9

@@ -141,6 +141,19 @@ int pmoe_route(pmoe_layer *layer, const void *x, int x_dtype, int n, float *logi
 int pmoe_experts_forward(pmoe_layer *layer, const void *x, int x_dtype, const uint32_t *idx,
                          const float *w, int n, int top_k, void *out, int out_dtype, void *stream);
 
+/*
+ * Expert-parallel form of the two calls around this one: the routed experts over all n rows
+ * (MoeExperts::forward_batched, qwen3_next.rs:1347-1394) plus the shared expert
+ * (SharedExpert::forward, qwen3_next.rs:1776-1823) added on rows [shared_begin,
+ * shared_begin + shared_count) only, in the same kernels.  A rank that received n rows from
+ * every rank calls it with the range of its own rows, so that each token's shared expert is
+ * computed exactly once across the ranks.  shared_count = 0, or a layer without a shared
+ * expert, gives pmoe_experts_forward.  The reference has no such call: it runs one process.
+ */
+int pmoe_experts_forward_ep(pmoe_layer *layer, const void *x, int x_dtype, const uint32_t *idx,
+                            const float *w, int n, int top_k, int shared_begin, int shared_count,
+                            void *out, int out_dtype, void *stream);
+
 /* SharedExpert::forward (qwen3_next.rs:1776-1823), sigmoid gate included. */
 int pmoe_shared_forward(pmoe_layer *layer, const void *x, int x_dtype, int n, void *out,
                         int out_dtype, void *stream);

@@ -75,6 +75,8 @@ struct pmoe_layer {
     uint32_t *st_idx = nullptr;
     float *st_w = nullptr;
     // per-phase CUDA events of the last traced call (pmoe_layer_trace)
+    // rows the shared expert serves in the next run_experts call; count < 0 = every row
+    int req_sh_begin = 0, req_sh_count = -1;
     bool trace = false;
     cudaEvent_t ev0[PMOE_TRACE_PHASES] = {}, ev1[PMOE_TRACE_PHASES] = {};
     bool ev_used[PMOE_TRACE_PHASES] = {};
@@ -105,6 +107,8 @@ void carve_workspace(pmoe_layer *L, Carver &c)
     const size_t rows = n * (k + 1);
     Workspace &w = L->ws;
     w.max_tokens = d.max_tokens;
+    w.sh_begin = 0;
+    w.sh_count = -1;
     w.status = c.take<DevStatus>(1);
     w.logits = c.take<float>(n * E);
     w.topk_idx = c.take<uint32_t>(n * k);
@@ -217,6 +221,9 @@ int run_experts(pmoe_layer *L, const void *x, int x_dtype, const uint32_t *idx, 
                 bool routed, bool shared, bool prep_done, void *out, int out_dtype, cudaStream_t s)
 {
     const LayerDev &d = L->dev;
+    L->ws.sh_begin = L->req_sh_count < 0 ? 0 : L->req_sh_begin;
+    L->ws.sh_count = L->req_sh_count < 0 ? n : L->req_sh_count;
+    L->req_sh_count = -1;  // a request holds for one call
     if (!prep_done) {
         Needs nd = input_needs(d, routed, shared);
         PHASE(L, 0, s, launch_prep(d, L->ws, x, x_dtype, n, nd.q8k, nd.q80, shared, s));
@@ -451,6 +458,25 @@ int pmoe_experts_forward(pmoe_layer *L, const void *x, int x_dtype, const uint32
         return fail(PMOE_ERR_INVALID_ARG, "top_k = %d must be in [1, %d]", top_k, L->desc.k);
     DeviceGuard guard(L->device);
     return run_experts(L, x, x_dtype, idx, w, n, top_k, true, false, false, out, out_dtype, (cudaStream_t)stream);
+}
+
+int pmoe_experts_forward_ep(pmoe_layer *L, const void *x, int x_dtype, const uint32_t *idx, const float *w, int n,
+                            int top_k, int shared_begin, int shared_count, void *out, int out_dtype, void *stream)
+{
+    int rc = check_call(L, x, x_dtype, n, out, out_dtype);
+    if (rc) return rc;
+    if (n == 0) return PMOE_OK;
+    if (!idx || !w) return fail(PMOE_ERR_INVALID_ARG, "idx / w is NULL");
+    if (top_k <= 0 || top_k > L->desc.k)
+        return fail(PMOE_ERR_INVALID_ARG, "top_k = %d must be in [1, %d]", top_k, L->desc.k);
+    if (shared_begin < 0 || shared_count < 0 || shared_begin + shared_count > n)
+        return fail(PMOE_ERR_INVALID_ARG, "shared rows [%d, %d) are outside [0, %d)", shared_begin,
+                    shared_begin + shared_count, n);
+    const bool shared = shared_count > 0 && L->dev.has_shared;
+    DeviceGuard guard(L->device);
+    L->req_sh_begin = shared_begin;
+    L->req_sh_count = shared ? shared_count : -1;
+    return run_experts(L, x, x_dtype, idx, w, n, top_k, true, shared, false, out, out_dtype, (cudaStream_t)stream);
 }
 
 int pmoe_shared_forward(pmoe_layer *L, const void *x, int x_dtype, int n, void *out, int out_dtype, void *stream)

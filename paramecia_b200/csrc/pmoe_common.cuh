@@ -234,6 +234,7 @@ struct LayerDev {
 
 struct Workspace {
     int max_tokens;
+    int sh_begin, sh_count;  // tokens of the current call the shared expert serves (set per call)
     DevStatus *status;
     float *logits;       // [n, E]
     uint32_t *topk_idx;  // [n, k]

@@ -258,6 +258,7 @@ struct GemvArgs {
     int routed;                // serve the routed experts listed in g
     int has_shared;            // serve the shared expert
     int n, top_k;
+    int sh_begin, sh_count;    // tokens the shared expert serves: [sh_begin, sh_begin + sh_count)
     Groups g;
     QAct in_r, in_s;           // quantised activations matching the routed / shared weight type
     float *out;                // act [., F] or partial [., H]
@@ -292,7 +293,7 @@ __device__ inline void load_pass(const GemvArgs &A, bool is_shared, const int *l
         if (t < P.cnt) {
             int in_row;
             if (is_shared) {
-                const int tok = t0 + t;
+                const int tok = A.sh_begin + t0 + t;
                 P.out_row[t] = A.n * A.top_k + tok;
                 in_row = NMAT == 2 ? tok : P.out_row[t];
                 if (NMAT == 1) P.scale[t] = A.scale_s[tok];
@@ -489,7 +490,7 @@ __device__ inline void finish_slot(const GemvArgs &A, int counter_idx, int items
     const int dt = is_shared ? A.quant_dt_s : A.quant_dt_r;
     const bool kq = is_kquant(dt);
     for (int i = warp; i < m; i += GEMV_WARPS) {
-        const size_t r = is_shared ? (size_t)A.n * A.top_k + i : (size_t)list[i];
+        const size_t r = is_shared ? (size_t)A.n * A.top_k + A.sh_begin + i : (size_t)list[i];
         if (A.rows_total == 512) warp_quant_row512(A.out + r * 512, kq, A.q8k_out, A.q80_out, r, lane);
         else block_quant_row(A.out + r * A.rows_total, A.rows_total, kq, !kq, A.q8k_out, A.q80_out, r, 0, 1, lane);
     }
@@ -524,7 +525,7 @@ __device__ inline bool run_items(const GemvArgs &A, uint8_t *ring, const Plan &p
             items_in_slot = 0;
             cur_slot = cur.slot;
             if (is_shared) {
-                m = A.n;
+                m = A.sh_count;
             } else {
                 const int e = A.g.active[cur.slot];
                 m = A.g.count[e];
@@ -575,7 +576,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 2) k_expert_gemv(const GemvArgs 
     plan.has_shared = (DT_S != 0 && A.has_shared) ? 1 : 0;
     plan.cpe_r = A.rows_total / CR::ROWS;
     plan.cpe_s = A.rows_total / CS::ROWS;
-    plan.cost_shared = (A.n + CS::TGK - 1) / CS::TGK;
+    plan.cost_shared = (A.sh_count + CS::TGK - 1) / CS::TGK;
     plan.prefix = s_prefix;
     for (int i = threadIdx.x; i <= plan.n_active; i += GEMV_THREADS) s_prefix[i] = plan.n_active ? (CR::TGK == GEMV_TG ? A.g.cost_prefix[i] : A.g.cost_prefix_wide[i]) : 0;
     if (threadIdx.x == 0) {
@@ -680,6 +681,7 @@ cudaError_t launch_gate_up(const LayerDev &L, const Workspace &ws, int n, int to
     A.rows_total = L.F;
     A.routed = routed; A.has_shared = shared;
     A.n = n; A.top_k = top_k;
+    A.sh_begin = ws.sh_begin; A.sh_count = ws.sh_count;
     A.g = ws.groups;
     A.in_r = is_kquant(L.gate_dtype) ? ws.x_q8k : ws.x_q80;
     A.in_s = is_kquant(L.sh_gate_dtype) ? ws.x_q8k : ws.x_q80;
@@ -706,6 +708,7 @@ cudaError_t launch_down(const LayerDev &L, const Workspace &ws, const float *w, 
     A.rows_total = L.H;
     A.routed = routed; A.has_shared = shared;
     A.n = n; A.top_k = top_k;
+    A.sh_begin = ws.sh_begin; A.sh_count = ws.sh_count;
     A.g = ws.groups;
     A.in_r = is_kquant(L.down_dtype) ? ws.act_q8k : ws.act_q80;
     A.in_s = is_kquant(L.sh_down_dtype) ? ws.act_q8k : ws.act_q80;
@@ -850,8 +853,8 @@ cudaError_t launch_act_quant(const LayerDev &L, const Workspace &ws, const uint3
 // final add, 1932-1937).
 template <typename OT>
 __global__ void __launch_bounds__(256) k_combine(const float *__restrict__ partial, const int *__restrict__ pos,
-                                                 int n, int top_k, int H, bool routed, bool shared,
-                                                 OT *__restrict__ out)
+                                                 int n, int top_k, int H, bool routed, bool shared, int sh_begin,
+                                                 int sh_count, OT *__restrict__ out)
 {
     const int t = blockIdx.x;
     for (int h = threadIdx.x * 4; h < H; h += blockDim.x * 4) {
@@ -864,7 +867,7 @@ __global__ void __launch_bounds__(256) k_combine(const float *__restrict__ parti
                 acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
             }
         }
-        if (shared) {
+        if (shared && t >= sh_begin && t < sh_begin + sh_count) {
             const float4 v = *reinterpret_cast<const float4 *>(partial + (size_t)(n * top_k + t) * H + h);
             acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
         }
@@ -881,10 +884,11 @@ cudaError_t launch_combine(const LayerDev &L, const Workspace &ws, const uint32_
     (void)idx;
     if (n <= 0) return cudaSuccess;
     if (out_dtype == PMOE_F32)
-        k_combine<float><<<n, 256, 0, s>>>(ws.partial, ws.groups.pos, n, top_k, L.H, routed, shared, (float *)out);
+        k_combine<float><<<n, 256, 0, s>>>(ws.partial, ws.groups.pos, n, top_k, L.H, routed, shared, ws.sh_begin, ws.sh_count,
+                                           (float *)out);
     else
-        k_combine<__nv_bfloat16><<<n, 256, 0, s>>>(ws.partial, ws.groups.pos, n, top_k, L.H, routed, shared,
-                                                   (__nv_bfloat16 *)out);
+        k_combine<__nv_bfloat16><<<n, 256, 0, s>>>(ws.partial, ws.groups.pos, n, top_k, L.H, routed, shared, ws.sh_begin,
+                                                   ws.sh_count, (__nv_bfloat16 *)out);
     count_launch();
     return cudaGetLastError();
 }

@@ -112,6 +112,7 @@ struct GuArgs {
     const uint8_t *sgate, *sup;    // shared expert (may be null)
     int has_shared, routed;
     int n, top_k, H, F;
+    int sh_begin, sh_count;        // tokens the shared expert serves
     Groups g;
     const int *tile_prefix;        // [n_active + 1] exclusive prefix of ceil(count / PF_NT) over active slots
     QAct xq;                       // Q8_K rows of the input [n, H]
@@ -143,7 +144,7 @@ __global__ void __launch_bounds__(PF_THREADS, 2) k_gu_prefill(const GuArgs A)
     // ---- which (expert slot, token tile) is this CTA's
     const int n_active = A.routed ? *A.g.n_active : 0;
     const int routed_tiles = n_active ? A.tile_prefix[n_active] : 0;
-    const int shared_tiles = A.has_shared ? (A.n + PF_NT - 1) / PF_NT : 0;
+    const int shared_tiles = A.has_shared ? (A.sh_count + PF_NT - 1) / PF_NT : 0;
     const int tile = blockIdx.y;
     if (tile >= routed_tiles + shared_tiles) return;
     if (tid == 0) {
@@ -169,7 +170,7 @@ __global__ void __launch_bounds__(PF_THREADS, 2) k_gu_prefill(const GuArgs A)
     const int *list = nullptr;
     const uint8_t *wg, *wu;
     if (is_shared) {
-        m = A.n;
+        m = A.sh_count;
         wg = A.sgate; wu = A.sup;
     } else {
         const int e = slot;
@@ -182,7 +183,7 @@ __global__ void __launch_bounds__(PF_THREADS, 2) k_gu_prefill(const GuArgs A)
     if (tid < PF_NT) {
         int rin = -1, rout = -1;
         if (tid < cnt) {
-            if (is_shared) { rin = t0 + tid; rout = A.n * A.top_k + rin; }
+            if (is_shared) { rin = A.sh_begin + t0 + tid; rout = A.n * A.top_k + rin; }
             else { const int p = list[t0 + tid]; rin = p / A.top_k; rout = p; }
         }
         S.row_in[tid] = rin;
@@ -372,6 +373,7 @@ struct DownArgs {
     const uint8_t *sdown;          // shared
     int has_shared, routed;
     int n, top_k, H, F;
+    int sh_begin, sh_count;
     Groups g;
     const int *tile_prefix;
     const __half *act_h;           // [n*(k+1), F] fake-quantised activation
@@ -497,7 +499,7 @@ __global__ void __launch_bounds__(PF_THREADS, 2) k_down_prefill(const DownArgs A
 
     const int n_active = A.routed ? *A.g.n_active : 0;
     const int routed_tiles = n_active ? A.tile_prefix[n_active] : 0;
-    const int shared_tiles = A.has_shared ? (A.n + PF_NT - 1) / PF_NT : 0;
+    const int shared_tiles = A.has_shared ? (A.sh_count + PF_NT - 1) / PF_NT : 0;
     const int tile = blockIdx.y;
     if (tile >= routed_tiles + shared_tiles) return;
     if (tid == 0) {
@@ -524,7 +526,7 @@ __global__ void __launch_bounds__(PF_THREADS, 2) k_down_prefill(const DownArgs A
     const int *list = nullptr;
     const uint8_t *wd;
     if (is_shared) {
-        m = A.n;
+        m = A.sh_count;
         wd = A.sdown;
     } else {
         const int e = slot;
@@ -544,7 +546,7 @@ __global__ void __launch_bounds__(PF_THREADS, 2) k_down_prefill(const DownArgs A
         int rin = -1;
         float sc = 0.f;
         if (tid < cnt) {
-            if (is_shared) { rin = A.n * A.top_k + t0 + tid; sc = A.scale_s[t0 + tid]; }
+            if (is_shared) { rin = A.n * A.top_k + A.sh_begin + t0 + tid; sc = A.scale_s[A.sh_begin + t0 + tid]; }
             else { rin = list[t0 + tid]; sc = A.scale_r[rin]; }
         }
         S.row_in[tid] = rin;
@@ -675,6 +677,7 @@ cudaError_t launch_gate_up_prefill(const LayerDev &L, const Workspace &ws, int n
     A.sgate = L.sh_gate; A.sup = L.sh_up;
     A.has_shared = shared; A.routed = routed;
     A.n = n; A.top_k = top_k; A.H = L.H; A.F = L.F;
+    A.sh_begin = ws.sh_begin; A.sh_count = ws.sh_count;
     A.g = ws.groups;
     A.tile_prefix = ws.groups.tile_prefix;
     A.xq = ws.x_q8k;
@@ -686,7 +689,7 @@ cudaError_t launch_gate_up_prefill(const LayerDev &L, const Workspace &ws, int n
         if (e != cudaSuccess) return e;
         configured = true;
     }
-    const int tiles = (routed ? max_routed_tiles(L, n, top_k) : 0) + (shared ? (n + PF_NT - 1) / PF_NT : 0);
+    const int tiles = (routed ? max_routed_tiles(L, n, top_k) : 0) + (shared ? (ws.sh_count + PF_NT - 1) / PF_NT : 0);
     dim3 grid(L.F / 64, tiles);
     k_gu_prefill<<<grid, PF_THREADS, sizeof(GuSmem) + 128, s>>>(A);
     count_launch();
@@ -731,6 +734,7 @@ cudaError_t launch_down_prefill(const LayerDev &L, const Workspace &ws, const fl
     A.sdown = L.sh_down;
     A.has_shared = shared; A.routed = routed;
     A.n = n; A.top_k = top_k; A.H = L.H; A.F = L.F;
+    A.sh_begin = ws.sh_begin; A.sh_count = ws.sh_count;
     A.g = ws.groups;
     A.tile_prefix = ws.groups.tile_prefix;
     A.act_h = ws.act_h;
@@ -738,7 +742,7 @@ cudaError_t launch_down_prefill(const LayerDev &L, const Workspace &ws, const fl
     A.scale_s = ws.sh_sigmoid;
     A.partial = ws.partial;
     A.status = ws.status;
-    const int tiles = (routed ? max_routed_tiles(L, n, top_k) : 0) + (shared ? (n + PF_NT - 1) / PF_NT : 0);
+    const int tiles = (routed ? max_routed_tiles(L, n, top_k) : 0) + (shared ? (ws.sh_count + PF_NT - 1) / PF_NT : 0);
     dim3 grid(L.H / PF_M, tiles);
     const int dt = routed ? L.down_dtype : L.sh_down_dtype;
     if (dt == PMOE_Q6_K) return launch_down_t<PMOE_Q6_K>(A, grid, s);

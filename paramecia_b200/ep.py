@@ -10,23 +10,28 @@ routed experts.  One block forward on a rank that is home to n tokens:
    with the token's top-k ids and weights; ids the destination does not own are replaced by
    an invalid id so the receiver skips them;
 3. each rank runs its experts over what it received and pre-reduces, per token, the weighted
-   outputs of its own experts (``MoeBlock.experts_forward_batched``);
-4. combine: the per-rank partial rows travel back to the token's home rank, which adds them
-   in rank order together with its shared-expert row (``pmoe_reduce_rows``).
+   outputs of its own experts; on its own tokens' rows the same kernels add the shared expert
+   (``MoeBlock.experts_forward_batched(..., shared_rows=...)``, ``pmoe_experts_forward_ep``);
+4. combine: the per-rank partial rows travel back to the token's home rank and are added there
+   (``pmoe_reduce_rows``, rank order) or on the way (reduce-scatter).
 
 Buffers have a fixed capacity of n rows per (source, destination) pair -- a token is sent to a
 rank at most once -- so neither exchange needs a size handshake or a host synchronisation.
 With top-10 routing over at most 8 ranks nearly every token visits nearly every rank, so the
 padding costs little.  Two transports carry the same rows:
 
-* ``all_to_all``  two ``all_to_all_single`` calls out (rows, routing) and one back;
-* ``all_gather``  ``all_gather_into_tensor`` out and ``reduce_scatter_tensor`` back, which lets
-                  NCCL do the cross-rank sum (in the switch when NVLS is active).
+* ``all_to_all``  ``all_to_all_single`` calls out (rows, ids, weights) and one back, the sum done by
+                  ``pmoe_reduce_rows`` on the home rank;
+* ``all_gather``  ``all_gather_into_tensor`` out (the three tensors handed to NCCL as one group, so
+                  one launch) and ``reduce_scatter_tensor`` back, which lets NCCL do the cross-rank
+                  sum (in the switch when NVLS is active).  With a fixed capacity of n rows per pair
+                  both transports move the same bytes; this one needs no send-side packing.
 
 No kernel here reads another GPU's memory: NCCL delivers into local HBM first.
 """
 from __future__ import annotations
 
+import contextlib
 from typing import Optional
 
 import torch
@@ -66,7 +71,7 @@ class ExpertParallelMoe:
     """One MoE block spread over the ranks of `group`.  `block` is this rank's MoeBlock, built with
     its expert slice (expert_base = rank * E/N, E_local = E/N) and max_tokens >= N * n."""
 
-    def __init__(self, block, group=None, mode: str = "all_to_all", ops=None):
+    def __init__(self, block, group=None, mode: str = "all_gather", ops=None):
         if mode not in ("all_to_all", "all_gather"):
             raise ValueError("mode must be 'all_to_all' or 'all_gather'")
         self.block = block
@@ -84,6 +89,8 @@ class ExpertParallelMoe:
         if block.num_experts_local != self.per_rank or block.expert_base != self.rank * self.per_rank:
             raise ValueError("block must hold experts [rank*E/N, (rank+1)*E/N)")
         self._buf_n = -1
+        # NCCL takes several collectives as one group; gloo (CPU tests) runs them one by one
+        self._coalesce = dist.get_backend(group) == "nccl"
 
     # buffers are sized once per token count and reused (no allocation in the steady state)
     def _buffers(self, n: int, x: torch.Tensor):
@@ -91,12 +98,19 @@ class ExpertParallelMoe:
             return
         N, H, k, dev = self.N, self.H, self.k, x.device
         self._buf_n, self._x_dtype = n, x.dtype
-        self.send_x = torch.empty((N, n, H), dtype=x.dtype, device=dev)
-        self.recv_x = torch.empty((N, n, H), dtype=x.dtype, device=dev)
-        self.send_meta = torch.empty((N, n, 2 * k), dtype=torch.int32, device=dev)
-        self.recv_meta = torch.empty((N, n, 2 * k), dtype=torch.int32, device=dev)
-        self.back = torch.empty((N, n, H), dtype=torch.float32, device=dev)
-        self.home = torch.empty((1, n, H), dtype=torch.float32, device=dev)
+        self.logits = torch.empty((n, self.E), dtype=torch.float32, device=dev)
+        self.idx = torch.empty((n, k), dtype=torch.int32, device=dev)
+        self.w = torch.empty((n, k), dtype=torch.float32, device=dev)
+        self.recv_x = torch.empty((N * n, H), dtype=x.dtype, device=dev)
+        self.recv_idx = torch.empty((N * n, k), dtype=torch.int32, device=dev)
+        self.recv_w = torch.empty((N * n, k), dtype=torch.float32, device=dev)
+        self.part = torch.empty((N * n, H), dtype=torch.float32, device=dev)
+        self.home = torch.empty((n, H), dtype=torch.float32, device=dev)
+        if self.mode == "all_to_all":
+            self.send_x = torch.empty((N, n, H), dtype=x.dtype, device=dev)
+            self.send_idx = torch.empty((N, n, k), dtype=torch.int32, device=dev)
+            self.send_w = torch.empty((N, n, k), dtype=torch.float32, device=dev)
+            self.back = torch.empty((N, n, H), dtype=torch.float32, device=dev)
 
     def gather_tokens(self, x: torch.Tensor) -> torch.Tensor:
         """All ranks' token rows, rank-major: [N*n, H]."""
@@ -104,41 +118,50 @@ class ExpertParallelMoe:
         dist.all_gather_into_tensor(out, x.contiguous(), group=self.group)
         return out
 
+    def _batched(self, device):
+        """Context that hands the collectives issued inside it to NCCL as one group (one launch)."""
+        if self._coalesce and device.type == "cuda":
+            from torch.distributed.distributed_c10d import _coalescing_manager
+            return _coalescing_manager(group=self.group, device=device, async_ops=False)
+        return contextlib.nullcontext()
+
     def forward_into(self, x: torch.Tensor, out: torch.Tensor, stats: Optional[dict] = None):
         """x [n, H] (this rank's tokens) -> out [n, H]; every rank must call with the same n."""
         n = x.shape[0]
-        N, k = self.N, self.k
+        N, k, g = self.N, self.k, self.group
+        x = x.contiguous()
         self._buffers(n, x)
-        logits, w, idx = self.block.route(x)
+        self.block.route(x, out=(self.logits, self.w, self.idx))
         if stats is not None:
-            stats.update(router_logits=logits, top_indices=idx, top_weights=w)
-        # -- dispatch
+            stats.update(router_logits=self.logits, top_indices=self.idx, top_weights=self.w)
+        # -- dispatch: rows, ids and weights of every token to every rank that may own one of its experts
         if self.mode == "all_to_all":
             self.send_x.copy_(x.unsqueeze(0).expand(N, n, self.H))
-            self.send_meta[:, :, :k] = mask_for_destinations(idx, N, self.per_rank)
-            self.send_meta[:, :, k:] = w.view(torch.int32).unsqueeze(0)
-            dist.all_to_all_single(self.recv_x.view(N * n, self.H), self.send_x.view(N * n, self.H), group=self.group)
-            dist.all_to_all_single(self.recv_meta.view(N * n, 2 * k), self.send_meta.view(N * n, 2 * k),
-                                   group=self.group)
+            self.send_idx.copy_(mask_for_destinations(self.idx, N, self.per_rank))
+            self.send_w.copy_(self.w.unsqueeze(0).expand(N, n, k))
+            dist.all_to_all_single(self.recv_x, self.send_x.view(N * n, self.H), group=g)
+            dist.all_to_all_single(self.recv_idx, self.send_idx.view(N * n, k), group=g)
+            dist.all_to_all_single(self.recv_w, self.send_w.view(N * n, k), group=g)
         else:
-            meta = self.send_meta[0]
-            meta[:, :k] = idx
-            meta[:, k:] = w.view(torch.int32)
-            dist.all_gather_into_tensor(self.recv_x.view(N * n, self.H), x.contiguous(), group=self.group)
-            dist.all_gather_into_tensor(self.recv_meta.view(N * n, 2 * k), meta, group=self.group)
-        rx = self.recv_x.view(N * n, self.H)
-        ridx = self.recv_meta.view(N * n, 2 * k)[:, :k].contiguous()
-        rw = self.recv_meta.view(N * n, 2 * k)[:, k:].contiguous().view(torch.float32)
-        # -- this rank's experts over everything it received, pre-reduced per token
-        part = self.block.experts_forward_batched(rx, ridx, rw, k, out_dtype=torch.float32)
-        # -- combine
-        shared = self.block.shared_forward(x, out_dtype=torch.float32) if self.block.has_shared else None
+            # ids stay as routed: a rank skips the ids outside its expert slice by itself
+            with self._batched(x.device):
+                dist.all_gather_into_tensor(self.recv_x, x, group=g)
+                dist.all_gather_into_tensor(self.recv_idx, self.idx, group=g)
+                dist.all_gather_into_tensor(self.recv_w, self.w, group=g)
+        # -- this rank's experts over everything it received, pre-reduced per token.  Rows
+        # [rank*n, (rank+1)*n) are this rank's own tokens: the shared expert rides along on those,
+        # so each token's shared row is computed once, on its home rank, in the same kernels.
+        own = (self.rank * n, n) if self.block.has_shared else None
+        self.block.experts_forward_batched(self.recv_x, self.recv_idx, self.recv_w, k, shared_rows=own, out=self.part)
+        # -- combine: the partial rows go back to the token's home rank and are added in rank order
         if self.mode == "all_to_all":
-            dist.all_to_all_single(self.back.view(N * n, self.H), part, group=self.group)
-            self.ops.reduce_rows(self.back, shared, out)
+            dist.all_to_all_single(self.back.view(N * n, self.H), self.part, group=g)
+            self.ops.reduce_rows(self.back, None, out)
+        elif out.dtype == torch.float32 and out.is_contiguous():
+            dist.reduce_scatter_tensor(out, self.part, group=g)
         else:
-            dist.reduce_scatter_tensor(self.home.view(n, self.H), part, group=self.group)
-            self.ops.reduce_rows(self.home, shared, out)
+            dist.reduce_scatter_tensor(self.home, self.part, group=g)
+            out.copy_(self.home)
         return out
 
     def forward(self, x: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:

@@ -263,28 +263,46 @@ class MoeBlock:
         check(lib().pmoe_forward(self._h, x.data_ptr(), _TORCH_TO_PMOE[x.dtype], n, out.data_ptr(),
                                  _TORCH_TO_PMOE[out.dtype], None, None, None, _stream_ptr(self.device)))
 
-    def route(self, hidden_states: torch.Tensor):
-        """gate.forward -> clamp -> softmax -> top_k: ``(router_logits, top_weights, top_indices)``."""
+    def route(self, hidden_states: torch.Tensor, out=None):
+        """gate.forward -> clamp -> softmax -> top_k: ``(router_logits, top_weights, top_indices)``.
+        `out` = the three result tensors to fill (f32 [n,E], f32 [n,k], int32 [n,k], contiguous)."""
         x = self._flat(hidden_states)
         n = x.shape[0]
-        logits = torch.empty((n, self.num_experts), dtype=torch.float32, device=self.device)
-        idx = torch.empty((n, self.num_experts_per_tok), dtype=torch.int32, device=self.device)
-        w = torch.empty((n, self.num_experts_per_tok), dtype=torch.float32, device=self.device)
+        if out is not None:
+            logits, w, idx = out
+        else:
+            logits = torch.empty((n, self.num_experts), dtype=torch.float32, device=self.device)
+            idx = torch.empty((n, self.num_experts_per_tok), dtype=torch.int32, device=self.device)
+            w = torch.empty((n, self.num_experts_per_tok), dtype=torch.float32, device=self.device)
         check(lib().pmoe_route(self._h, x.data_ptr(), _TORCH_TO_PMOE[x.dtype], n, logits.data_ptr(), idx.data_ptr(),
                                w.data_ptr(), _stream_ptr(self.device)))
         return logits, w, idx
 
     def experts_forward_batched(self, hidden_states: torch.Tensor, expert_indices: torch.Tensor,
                                 expert_weights: torch.Tensor, top_k: Optional[int] = None,
-                                out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
-        """MoeExperts::forward_batched(hidden [n,H], indices [n,k] u32, weights [n,k] f32, top_k)."""
+                                out_dtype: Optional[torch.dtype] = None,
+                                shared_rows: Optional[Tuple[int, int]] = None,
+                                out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """MoeExperts::forward_batched(hidden [n,H], indices [n,k] u32, weights [n,k] f32, top_k).
+
+        shared_rows = (begin, count) adds the shared expert on those rows in the same kernels
+        (the expert-parallel form: a rank passes the range of its own tokens); `out` = the
+        contiguous [n, H] tensor to fill."""
         x = self._flat(hidden_states)
         n = x.shape[0]
         top_k = int(top_k or expert_indices.shape[-1])
         idx = expert_indices.to(self.device, torch.int32).reshape(n, top_k).contiguous()
         w = expert_weights.to(self.device, torch.float32).reshape(n, top_k).contiguous()
-        out_dtype = out_dtype or hidden_states.dtype
-        out = torch.empty((n, self.hidden_dim), dtype=out_dtype, device=self.device)
+        if out is None:
+            out_dtype = out_dtype or hidden_states.dtype
+            out = torch.empty((n, self.hidden_dim), dtype=out_dtype, device=self.device)
+        else:
+            out_dtype = out.dtype
+        if shared_rows is not None:
+            check(lib().pmoe_experts_forward_ep(self._h, x.data_ptr(), _TORCH_TO_PMOE[x.dtype], idx.data_ptr(),
+                                                w.data_ptr(), n, top_k, int(shared_rows[0]), int(shared_rows[1]),
+                                                out.data_ptr(), _TORCH_TO_PMOE[out_dtype], _stream_ptr(self.device)))
+            return out
         check(lib().pmoe_experts_forward(self._h, x.data_ptr(), _TORCH_TO_PMOE[x.dtype], idx.data_ptr(), w.data_ptr(),
                                          n, top_k, out.data_ptr(), _TORCH_TO_PMOE[out_dtype], _stream_ptr(self.device)))
         return out

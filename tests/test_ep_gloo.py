@@ -25,16 +25,29 @@ class OracleBlock:
         self.expert_base = rank * self.num_experts_local
         self.has_shared = t["shared"] is not None
 
-    def route(self, x):
+    def route(self, x, out=None):
         logits = self.full.router_logits(x.float().numpy())
         idx, w = self.full.route_topk(logits)
-        return torch.from_numpy(logits), torch.from_numpy(w), torch.from_numpy(idx.astype(np.int32))
+        res = torch.from_numpy(logits), torch.from_numpy(w), torch.from_numpy(idx.astype(np.int32))
+        if out is not None:
+            for dst, src in zip(out, res):
+                dst.copy_(src)
+            return out
+        return res
 
-    def experts_forward_batched(self, x, idx, w, top_k, out_dtype=torch.float32):
+    def experts_forward_batched(self, x, idx, w, top_k, out_dtype=torch.float32, shared_rows=None, out=None):
         ids = idx.numpy().astype(np.int64)
         lo, hi = self.expert_base, self.expert_base + self.num_experts_local
         masked = np.where((ids >= lo) & (ids < hi), ids, 0xFFFFFFFF).astype(np.uint32)  # only this rank's slice
-        return torch.from_numpy(self.full.experts_forward(x.float().numpy(), masked, w.numpy()))
+        res = self.full.experts_forward(x.float().numpy(), masked, w.numpy())
+        if shared_rows is not None:
+            b, c = shared_rows
+            res[b:b + c] += self.full.shared_forward(x[b:b + c].float().numpy())
+        res = torch.from_numpy(res)
+        if out is not None:
+            out.copy_(res)
+            return out
+        return res
 
     def shared_forward(self, x, out_dtype=torch.float32):
         return torch.from_numpy(self.full.shared_forward(x.float().numpy()))

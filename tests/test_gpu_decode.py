@@ -4,6 +4,8 @@ Bars: router logits and top-k indices bit-exact; dequantised weights bit-exact; 
 within max-abs 2e-2 and relative-L2 1e-3 of the oracle (the oracle quantises activations like
 the reference CPU path, and so does the library, so the observed distance is far smaller).
 """
+import os
+
 import numpy as np
 import pytest
 import torch
@@ -135,6 +137,45 @@ def test_experts_and_shared_entry_points():
     want2 = ol.experts_forward(x.numpy(), idx[:, :2].copy(), w[:, :2].copy())
     assert rel_l2(got2.cpu().numpy(), want2) <= 5e-4
     blk.status()
+
+
+@pytest.mark.parametrize("n,begin,count,prefill", [(23, 5, 11, "0"), (23, 0, 23, "0"), (23, 22, 1, "0"), (150, 64, 70, "1"),
+                                                  (9, 3, 0, "0")])
+def test_experts_with_shared_rows(n, begin, count, prefill):
+    # the expert-parallel entry point: routed experts on every row, shared expert on [begin, begin+count)
+    old = os.environ.get("PMOE_PREFILL")
+    os.environ["PMOE_PREFILL"] = prefill
+    try:
+        t = synth.make_layer(E=16, k=3, preset="q4k_q6k_all", seed=21)
+        blk = synth.make_block(t, DEV, max_tokens=n)
+        ol = oracle_layer(t)
+        x = seeded_x(n, 2048, 50 + n)
+        rng = np.random.default_rng(5)
+        idx = np.stack([rng.choice(16, size=3, replace=False) for _ in range(n)]).astype(np.uint32)
+        idx[1, 2] = 0xFFFFFFFF
+        w = rng.random((n, 3)).astype(np.float32)
+        got = blk.experts_forward_batched(x.to(DEV), torch.from_numpy(idx.view(np.int32)), torch.from_numpy(w), 3,
+                                          shared_rows=(begin, count)).cpu().numpy()
+        blk.status()
+        want = ol.experts_forward(x.numpy(), idx, w)
+        if count:
+            want[begin:begin + count] += ol.shared_forward(x.numpy()[begin:begin + count])
+        assert rel_l2(got, want) <= (1e-3 if prefill == "1" else 5e-4)
+        # rows outside the range carry no shared part at all
+        plain = blk.experts_forward_batched(x.to(DEV), torch.from_numpy(idx.view(np.int32)), torch.from_numpy(w), 3)
+        outside = np.ones(n, bool)
+        outside[begin:begin + count] = False
+        assert np.array_equal(got[outside], plain.cpu().numpy()[outside])
+        # and the request does not leak into the next call
+        assert rel_l2(blk.forward(x.to(DEV)).cpu().numpy(), ol.forward(x.numpy())[0]) <= REL_L2_TOL
+        with pytest.raises(pm.PmoeError):
+            blk.experts_forward_batched(x.to(DEV), torch.from_numpy(idx.view(np.int32)), torch.from_numpy(w), 3,
+                                        shared_rows=(n - 1, 2))
+    finally:
+        if old is None:
+            del os.environ["PMOE_PREFILL"]
+        else:
+            os.environ["PMOE_PREFILL"] = old
 
 
 def test_expert_slices_sum_to_whole_block():
