@@ -358,6 +358,22 @@ __device__ inline void compute_item(const GemvArgs &A, const uint8_t *stage, int
     }
 }
 
+// Shared-memory row pitch of a gate/up item of a Q8_0 shared expert that runs as tensor-core tiles
+// (run_items_shared_mma): the rows of a Q8_0 [*, 2048] matrix are
+// 2176 bytes apart, a multiple of 128, so the eight rows of a fragment would meet in the same
+// banks; the producer copies such an item row by row with 32 bytes of padding (a lane reads 8 bytes,
+// so eight rows 32 bytes apart fill the 32 banks twice, the minimum).
+template <int NMAT> struct SharedMma {
+    using C = Cfg<PMOE_Q8_0, NMAT>;
+    static constexpr int KB = C::K / QK8_0;                    // Q8_0 blocks per row
+    static constexpr int MT = NMAT == 2 ? 1 : C::ROWS / 16;    // 16-row tiles per item
+    static constexpr int PITCH = NMAT == 2 ? C::ROW_BYTES + 32 : C::ROW_BYTES;
+    static constexpr bool PER_ROW_COPIES = PITCH != C::ROW_BYTES;
+    static_assert(NMAT == 1 || C::ROWS == 8, "a gate/up item must be 8 + 8 rows");
+    static_assert(NMAT * C::ROWS * PITCH <= STAGE_BYTES, "padded item must fit its ring slot");
+    static_assert(KB % 8 == 0 && PITCH % 16 == 0, "bad shape");
+};
+
 // ---------------------------------------------------------------- work partition
 // Items are ordered (slot 0 chunk 0, slot 0 chunk 1, ..., slot 1 chunk 0, ...); slot n_active is
 // the shared expert.  An item of a slot with m tokens costs ceil(m / TG) passes, and the CTAs
@@ -369,6 +385,7 @@ struct Cursor {
 
 struct Plan {
     int n_active, has_shared, cpe_r, cpe_s, cost_shared;
+    bool shared_mma;     // the shared expert's items run as tensor-core tiles (own shared-memory layout)
     const int *prefix;  // [n_active + 1] in shared memory
 
     __device__ inline int cpe(int slot) const { return slot < n_active ? cpe_r : cpe_s; }
@@ -442,9 +459,19 @@ template <int DT_R, int DT_S1, int NMAT> struct Producer {
             src1 = A.sw1 + off;
             bytes = CS::ITEM_BYTES;
         }
+        const bool padded = cur.slot >= plan.n_active && plan.shared_mma && SharedMma<NMAT>::PER_ROW_COPIES;
         plan.advance(cur);
         uint64_t *full = ring_full(ring, s);
         mbar_expect_tx(full, bytes * NMAT);
+        if (padded) {  // rows land SharedMma::PITCH apart: gate rows first, then the up rows
+            constexpr int RB = Cfg<PMOE_Q8_0, NMAT>::ROW_BYTES, ROWS = Cfg<PMOE_Q8_0, NMAT>::ROWS;
+#pragma unroll
+            for (int mat = 0; mat < NMAT; mat++)
+                for (int r = 0; r < ROWS; r++)
+                    bulk_g2s(ring_stage(ring, s) + (mat * ROWS + r) * SharedMma<NMAT>::PITCH,
+                             (mat == 0 ? src0 : src1) + r * RB, RB, full);
+            return true;
+        }
 #pragma unroll
         for (int mat = 0; mat < NMAT; mat++) {
             const uint8_t *src = mat == 0 ? src0 : src1;
@@ -560,6 +587,175 @@ __device__ inline bool run_items(const GemvArgs &A, uint8_t *ring, const Plan &p
     return !failed;
 }
 
+// ---------------------------------------------------------------- shared expert over many tokens
+// A Q8_0 shared expert that serves SHARED_MMA_MIN tokens or more runs its items as int8 tensor-core
+// tiles instead of per-token dp4a passes: an item's rows are the M side (gate rows 0..7 and up rows
+// 8..15 of one 16-row tile, or ROWS/16 tiles of down rows), eight tokens are the N side and one
+// Q8_0 block (32 weights) is the K of one mma.  The integer block sum is exact, so every block
+// contributes (d_w * d_x) * isum in f32 exactly as in the dp4a path; blocks are added in K order.
+constexpr int SHARED_MMA_MIN = 24;
+
+__device__ inline void mma_s8_16x8x32(int (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2])
+{
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]), "r"(0));
+}
+
+// Cost of one shared item in units of one dp4a pass over an item, for the work partition.
+template <int NMAT> __host__ __device__ inline int shared_mma_cost(int tokens)
+{
+    using C = Cfg<PMOE_Q8_0, NMAT>;
+    constexpr int MT = NMAT == 2 ? 1 : C::ROWS / 16;
+    const int jobs = MT * ((tokens + 7) / 8);
+    const int per_warp = (jobs + GEMV_WARPS - 1) / GEMV_WARPS;
+    // measured at 64 tokens: the 64 blocks a warp walks per item take about as long as eight dp4a
+    // passes (the activation fragments come from L2 under the weight stream's load)
+    const int c = per_warp * (C::K / QK8_0) / 8;
+    return c < 1 ? 1 : c;
+}
+
+// Activations of four consecutive blocks for one lane: its 8 bytes of each block of token column g
+// and the block scales of token columns 2t and 2t+1.
+struct MmaActs {
+    uint2 q[4];
+    float4 x0, x1;
+};
+
+__device__ inline void mma_load_acts(MmaActs &o, const int8_t *xq, const float *dx0, const float *dx1, int kb)
+{
+#pragma unroll
+    for (int i = 0; i < 4; i++) o.q[i] = *reinterpret_cast<const uint2 *>(xq + (kb + i) * QK8_0);
+    o.x0 = *reinterpret_cast<const float4 *>(dx0 + kb);
+    o.x1 = *reinterpret_cast<const float4 *>(dx1 + kb);
+}
+
+// Bytes [8t, 8t+8) of the quants of block kb of one row, as two words.  The quants start 2 bytes
+// into a 34-byte block, so the address is 4-byte aligned for odd kb only; even blocks take three
+// aligned words and two funnel shifts.  ODD is a compile-time fact of the unrolled caller.
+template <bool ODD> __device__ inline void mma_load_row(const uint8_t *q, uint32_t &w0, uint32_t &w1)
+{
+    if (ODD) {
+        w0 = *reinterpret_cast<const uint32_t *>(q);
+        w1 = *reinterpret_cast<const uint32_t *>(q + 4);
+    } else {
+        const uint32_t u0 = *reinterpret_cast<const uint32_t *>(q - 2);
+        const uint32_t u1 = *reinterpret_cast<const uint32_t *>(q + 2);
+        const uint32_t u2 = *reinterpret_cast<const uint32_t *>(q + 6);
+        w0 = __funnelshift_r(u0, u1, 16);
+        w1 = __funnelshift_r(u1, u2, 16);
+    }
+}
+
+template <bool ODD>
+__device__ inline void mma_step(const uint8_t *p0, const uint8_t *p1, int t, const uint2 &bq, float x0, float x1,
+                                float (&acc)[4])
+{
+    uint32_t a[4];
+    // the lane's share of K is bytes 8t..8t+7 of the block, for the weights and the activations alike
+    mma_load_row<ODD>(p0 + 2 + 8 * t, a[0], a[2]);
+    mma_load_row<ODD>(p1 + 2 + 8 * t, a[1], a[3]);
+    const uint32_t b[2] = {bq.x, bq.y};
+    int c[4];
+    mma_s8_16x8x32(c, a, b);
+    const float dw0 = half_bits_to_float(*reinterpret_cast<const uint16_t *>(p0));
+    const float dw1 = half_bits_to_float(*reinterpret_cast<const uint16_t *>(p1));
+    acc[0] += (dw0 * x0) * (float)c[0];
+    acc[1] += (dw0 * x1) * (float)c[1];
+    acc[2] += (dw1 * x0) * (float)c[2];
+    acc[3] += (dw1 * x1) * (float)c[3];
+}
+
+__device__ inline void mma_step4(const uint8_t *r0, const uint8_t *r1, int kb, int t, const MmaActs &v, float (&acc)[4])
+{
+    // kb is a multiple of 4: blocks kb, kb+2 start 4-byte aligned (quants do not), kb+1, kb+3 the other way round
+    mma_step<false>(r0 + (kb + 0) * Q8_0_BYTES, r1 + (kb + 0) * Q8_0_BYTES, t, v.q[0], v.x0.x, v.x1.x, acc);
+    mma_step<true>(r0 + (kb + 1) * Q8_0_BYTES, r1 + (kb + 1) * Q8_0_BYTES, t, v.q[1], v.x0.y, v.x1.y, acc);
+    mma_step<false>(r0 + (kb + 2) * Q8_0_BYTES, r1 + (kb + 2) * Q8_0_BYTES, t, v.q[2], v.x0.z, v.x1.z, acc);
+    mma_step<true>(r0 + (kb + 3) * Q8_0_BYTES, r1 + (kb + 3) * Q8_0_BYTES, t, v.q[3], v.x0.w, v.x1.w, acc);
+}
+
+template <int NMAT>
+__device__ inline bool run_items_shared_mma(const GemvArgs &A, uint8_t *ring, const Plan &plan, Cursor &cur, int &it,
+                                            int n_items, const QAct &in, int warp, int lane)
+{
+    using C = Cfg<PMOE_Q8_0, NMAT>;
+    using SM = SharedMma<NMAT>;
+    constexpr int KB = SM::KB, MT = SM::MT, PITCH = SM::PITCH;
+    const int g = lane >> 2, t = lane & 3;
+    const int m = A.sh_count;
+    const int ntiles = (m + 7) / 8;
+    const size_t row0 = NMAT == 2 ? (size_t)A.sh_begin : (size_t)A.n * A.top_k + A.sh_begin;  // activation row of token 0
+    const size_t out0 = (size_t)A.n * A.top_k + A.sh_begin;                                   // output row of token 0
+    const bool fuse_quant = NMAT == 2 && A.quant_dt_s != 0;
+    int items_in_slot = 0;
+    bool failed = false;
+    while (it < n_items && cur.slot <= plan.n_active) {
+        const int s = it % NSTAGE;
+        const uint32_t use = (uint32_t)(it / NSTAGE);
+        if (!failed && A.debug != 2 && !mbar_wait(ring_full(ring, s), use & 1)) {
+            set_status(A.status, PMOE_ERR_TIMEOUT, 14 + NMAT, it);
+            failed = true;
+        }
+        const uint8_t *stage = ring_stage(ring, s);
+        if (A.debug != 1 && !failed) {
+            for (int job = warp; job < MT * ntiles; job += GEMV_WARPS) {
+                const int mt = job / ntiles, nt = job - mt * ntiles;
+                // fragment rows g and g + 8 of the tile: gate row g and up row g, or two down rows
+                const uint8_t *r0 = stage + (NMAT == 2 ? g : mt * 16 + g) * PITCH;
+                const uint8_t *r1 = r0 + 8 * PITCH;
+                // B column g = token nt*8 + g; C columns 2t, 2t+1 = tokens nt*8 + 2t (+1).  Columns past
+                // the last token read token 0's rows; their sums are never stored.
+                const int tok_b = nt * 8 + g, tok_c = nt * 8 + 2 * t;
+                const bool c0_ok = tok_c < m, c1_ok = tok_c + 1 < m;
+                const int8_t *xq = in.qs + (row0 + (tok_b < m ? tok_b : 0)) * C::K + 8 * t;
+                const float *dx0 = in.d + (row0 + (c0_ok ? tok_c : 0)) * KB;
+                const float *dx1 = in.d + (row0 + (c1_ok ? tok_c + 1 : 0)) * KB;
+                float acc[4] = {0.f, 0.f, 0.f, 0.f};
+                MmaActs va, vb;
+                mma_load_acts(va, xq, dx0, dx1, 0);
+#pragma unroll 1
+                for (int kb = 0; kb < KB; kb += 8) {   // the loads of the next four blocks fly under the current four
+                    mma_load_acts(vb, xq, dx0, dx1, kb + 4);
+                    mma_step4(r0, r1, kb, t, va, acc);
+                    if (kb + 8 < KB) mma_load_acts(va, xq, dx0, dx1, kb + 8);
+                    mma_step4(r0, r1, kb + 4, t, vb, acc);
+                }
+                if (NMAT == 2) {
+                    const int row = cur.chunk * C::ROWS + g;
+                    const float v0 = acc[0] / (1.f + expf(-acc[0])) * acc[2];  // silu(gate) * up
+                    const float v1 = acc[1] / (1.f + expf(-acc[1])) * acc[3];
+                    if (c0_ok) A.out[(out0 + tok_c) * A.rows_total + row] = v0;
+                    if (c1_ok) A.out[(out0 + tok_c + 1) * A.rows_total + row] = v1;
+                } else {
+                    const int row = cur.chunk * C::ROWS + mt * 16 + g;
+                    if (c0_ok) {
+                        const float sc = A.scale_s[A.sh_begin + tok_c];
+                        float *o = A.out + (out0 + tok_c) * A.rows_total + row;
+                        o[0] = acc[0] * sc;
+                        o[8] = acc[2] * sc;
+                    }
+                    if (c1_ok) {
+                        const float sc = A.scale_s[A.sh_begin + tok_c + 1];
+                        float *o = A.out + (out0 + tok_c + 1) * A.rows_total + row;
+                        o[0] = acc[1] * sc;
+                        o[8] = acc[3] * sc;
+                    }
+                }
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(ring_empty(ring, s));
+        plan.advance(cur);
+        it++;
+        items_in_slot++;
+    }
+    if (fuse_quant && items_in_slot > 0)
+        finish_slot(A, plan.n_active, items_in_slot, plan.cpe_s, true, nullptr, m, warp, lane);
+    return !failed;
+}
+
 // DT_S == 0 compiles the kernel without a shared-expert branch.
 template <int DT_R, int DT_S, int NMAT>
 __global__ void __launch_bounds__(GEMV_THREADS, 2) k_expert_gemv(const GemvArgs A)
@@ -576,7 +772,9 @@ __global__ void __launch_bounds__(GEMV_THREADS, 2) k_expert_gemv(const GemvArgs 
     plan.has_shared = (DT_S != 0 && A.has_shared) ? 1 : 0;
     plan.cpe_r = A.rows_total / CR::ROWS;
     plan.cpe_s = A.rows_total / CS::ROWS;
-    plan.cost_shared = (A.sh_count + CS::TGK - 1) / CS::TGK;
+    const bool shared_mma = DT_S == PMOE_Q8_0 && A.sh_count >= SHARED_MMA_MIN;
+    plan.shared_mma = shared_mma;
+    plan.cost_shared = shared_mma ? shared_mma_cost<NMAT>(A.sh_count) : (A.sh_count + CS::TGK - 1) / CS::TGK;
     plan.prefix = s_prefix;
     for (int i = threadIdx.x; i <= plan.n_active; i += GEMV_THREADS) s_prefix[i] = plan.n_active ? (CR::TGK == GEMV_TG ? A.g.cost_prefix[i] : A.g.cost_prefix_wide[i]) : 0;
     if (threadIdx.x == 0) {
@@ -605,7 +803,9 @@ __global__ void __launch_bounds__(GEMV_THREADS, 2) k_expert_gemv(const GemvArgs 
     int it = 0;
     bool ok = run_items<DT_R, NMAT>(A, ring, plan, false, cur, plan.n_active, it, n_items, A.in_r, warp, lane);
     if constexpr (DT_S != 0) {
-        if (ok) run_items<DT_S, NMAT>(A, ring, plan, true, cur, plan.n_active + 1, it, n_items, A.in_s, warp, lane);
+        if (!ok) return;
+        if (DT_S == PMOE_Q8_0 && shared_mma) run_items_shared_mma<NMAT>(A, ring, plan, cur, it, n_items, A.in_s, warp, lane);
+        else run_items<DT_S, NMAT>(A, ring, plan, true, cur, plan.n_active + 1, it, n_items, A.in_s, warp, lane);
     }
 }
 

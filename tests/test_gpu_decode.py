@@ -139,14 +139,17 @@ def test_experts_and_shared_entry_points():
     blk.status()
 
 
-@pytest.mark.parametrize("n,begin,count,prefill", [(23, 5, 11, "0"), (23, 0, 23, "0"), (23, 22, 1, "0"), (150, 64, 70, "1"),
-                                                  (9, 3, 0, "0")])
-def test_experts_with_shared_rows(n, begin, count, prefill):
+@pytest.mark.parametrize("n,begin,count,prefill,preset", [
+    (23, 5, 11, "0", "q4k_q6k_all"), (23, 0, 23, "0", "q4k_q6k_all"), (23, 22, 1, "0", "q4k_q6k_all"),
+    (150, 64, 70, "1", "q4k_q6k_all"), (9, 3, 0, "0", "q4k_q6k_all"),
+    (150, 64, 70, "0", "q4k_m"),    # Q8_0 shared expert over 70 rows: the tensor-core tiles, ragged last tile
+    (40, 7, 29, "0", "q8_0")])
+def test_experts_with_shared_rows(n, begin, count, prefill, preset):
     # the expert-parallel entry point: routed experts on every row, shared expert on [begin, begin+count)
     old = os.environ.get("PMOE_PREFILL")
     os.environ["PMOE_PREFILL"] = prefill
     try:
-        t = synth.make_layer(E=16, k=3, preset="q4k_q6k_all", seed=21)
+        t = synth.make_layer(E=16, k=3, preset=preset, seed=21)
         blk = synth.make_block(t, DEV, max_tokens=n)
         ol = oracle_layer(t)
         x = seeded_x(n, 2048, 50 + n)
