@@ -46,6 +46,16 @@ struct ActQ16 {   // 4 groups of 4 activations
     uint32_t a[4];
     float dx;
 };
+struct ActQ6K {   // 64 activations of a Q8_K block: four runs of 16, one per 6-bit scale of the unit
+    uint32_t a[16];
+    float dx;
+    int bs[4];    // sum of each run (the block's partial sums)
+};
+
+// Internal variant of Q6_K for the down kernels of calls with several tokens per expert: 16-weight
+// lane units, whose four activation words per token let a pass take four tokens.  Same bytes,
+// same arithmetic; only the split of a row over lanes and passes differs.
+constexpr int Q6_K_T4 = 1000 + PMOE_Q6_K;
 
 template <int DT> struct Tr;
 template <> struct Tr<PMOE_Q4_K> {
@@ -54,6 +64,11 @@ template <> struct Tr<PMOE_Q4_K> {
     using Act = ActQ4K;
 };
 template <> struct Tr<PMOE_Q6_K> {
+    static constexpr int UNIT = 64;
+    static constexpr bool KQ = true;
+    using Act = ActQ6K;
+};
+template <> struct Tr<Q6_K_T4> {
     static constexpr int UNIT = 16;
     static constexpr bool KQ = true;
     using Act = ActQ16;
@@ -71,13 +86,21 @@ template <> __device__ inline void zero_act<PMOE_Q4_K>(ActQ4K &o)
     for (int i = 0; i < 16; i++) o.a[i] = 0;
     o.dx = 0.f; o.bs_lo = 0; o.bs_hi = 0;
 }
-template <> __device__ inline void zero_act<PMOE_Q6_K>(ActQ16 &o)
+template <> __device__ inline void zero_act<PMOE_Q6_K>(ActQ6K &o)
+{
+#pragma unroll
+    for (int i = 0; i < 16; i++) o.a[i] = 0;
+    o.dx = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; i++) o.bs[i] = 0;
+}
+template <> __device__ inline void zero_act<PMOE_Q8_0>(ActQ16 &o)
 {
 #pragma unroll
     for (int i = 0; i < 4; i++) o.a[i] = 0;
     o.dx = 0.f;
 }
-template <> __device__ inline void zero_act<PMOE_Q8_0>(ActQ16 &o) { zero_act<PMOE_Q6_K>(o); }
+template <> __device__ inline void zero_act<Q6_K_T4>(ActQ16 &o) { zero_act<PMOE_Q8_0>(o); }
 
 template <int DT> __device__ inline void load_act(const QAct &q, size_t row, int K, int u, typename Tr<DT>::Act &o);
 
@@ -96,7 +119,26 @@ template <> __device__ inline void load_act<PMOE_Q4_K>(const QAct &q, size_t row
     o.bs_hi = (int)bs.z + (int)bs.w;
 }
 
-template <> __device__ inline void load_act<PMOE_Q6_K>(const QAct &q, size_t row, int K, int u, ActQ16 &o)
+// Unit u of a Q6_K row: block u/4, 128-element half (u/2)%2, and inside the half the 16 positions
+// l = 16*jj .. 16*jj+15 (jj = u%2) of each of the four interleaved quant streams, i.e. elements
+// 128*half + 32*g + 16*jj + (0..15) for g = 0..3.  Each run lies under one 6-bit scale.
+template <> __device__ inline void load_act<PMOE_Q6_K>(const QAct &q, size_t row, int K, int u, ActQ6K &o)
+{
+    const int b = u >> 2, half = (u >> 1) & 1, jj = u & 1;
+    const int8_t *p = q.qs + row * K + 256 * b + 128 * half + 16 * jj;
+#pragma unroll
+    for (int g = 0; g < 4; g++) {
+        const uint4 v = *reinterpret_cast<const uint4 *>(p + 32 * g);
+        o.a[4 * g + 0] = v.x; o.a[4 * g + 1] = v.y; o.a[4 * g + 2] = v.z; o.a[4 * g + 3] = v.w;
+    }
+    o.dx = q.d[row * (K / QK_K) + b];
+    const int16_t *bs = q.bsums + row * (K / 16) + 16 * b + 8 * half + jj;
+#pragma unroll
+    for (int g = 0; g < 4; g++) o.bs[g] = bs[2 * g];
+}
+
+// 16-weight unit u: block u/16, half (u/8)%2, positions l = 4j .. 4j+3 (j = u%8) of the four streams
+template <> __device__ inline void load_act<Q6_K_T4>(const QAct &q, size_t row, int K, int u, ActQ16 &o)
 {
     const int b = u >> 4, half = (u >> 3) & 1, j = u & 7;
     const uint32_t *p = reinterpret_cast<const uint32_t *>(q.qs + row * K + 256 * b + 128 * half + 4 * j);
@@ -169,7 +211,70 @@ template <> struct Dot<PMOE_Q4_K> {
     }
 };
 
+// 16 bytes from a 2-byte aligned address: five aligned words and a funnel shift by the lane's own
+// misalignment (0 or 16 bits).  Reads up to 4 bytes past the 16 (inside the block for every caller).
+__device__ inline void load16_a2(const uint8_t *p, uint32_t (&o)[4])
+{
+    const uintptr_t a = reinterpret_cast<uintptr_t>(p);
+    const uint32_t *q = reinterpret_cast<const uint32_t *>(a & ~(uintptr_t)3);
+    const uint32_t sh = (uint32_t)(a & 2) * 8;
+    uint32_t u[5];
+#pragma unroll
+    for (int i = 0; i < 5; i++) u[i] = q[i];
+#pragma unroll
+    for (int i = 0; i < 4; i++) o[i] = __funnelshift_r(u[i], u[i + 1], sh);
+}
+
 template <> struct Dot<PMOE_Q6_K> {
+    struct Pre {
+        int la_off, h_off, sc_off, d_off;
+    };
+    __device__ static inline Pre pre(int u)
+    {
+        const int blk = (u >> 2) * Q6_K_BYTES, half = (u >> 1) & 1, jj = u & 1;
+        return Pre{blk + 64 * half + 16 * jj, blk + 128 + 32 * half + 16 * jj, blk + 192 + 8 * half + jj, blk + 208};
+    }
+    template <int CNT>
+    __device__ static inline void run(const uint8_t *row, const Pre &p, const ActQ6K *act, float *acc)
+    {
+        uint32_t la[4], lb[4], h[4];
+        load16_a2(row + p.la_off, la);
+        load16_a2(row + p.la_off + 32, lb);
+        load16_a2(row + p.h_off, h);
+        const int8_t *sc = reinterpret_cast<const int8_t *>(row + p.sc_off);
+        const int c[4] = {sc[0], sc[2], sc[4], sc[6]};
+        // quants are used as the unsigned bytes 4*q (0..252); the offset -32 comes back through the
+        // activations' partial sums (4*(q-32) = 4*q - 128) and the factor 4 is taken out of d
+        const float d4 = half_bits_to_float(*reinterpret_cast<const uint16_t *>(row + p.d_off)) * 0.25f;
+        int isum[CNT];
+#pragma unroll
+        for (int t = 0; t < CNT; t++)
+            isum[t] = -128 * (c[0] * act[t].bs[0] + c[1] * act[t].bs[1] + c[2] * act[t].bs[2] + c[3] * act[t].bs[3]);
+#pragma unroll
+        for (int g = 0; g < 4; g++) {
+            uint32_t w[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const uint32_t lo = g == 0 ? la[i] << 2 : g == 1 ? lb[i] << 2 : g == 2 ? la[i] >> 2 : lb[i] >> 2;
+                const uint32_t hi = g == 3 ? h[i] : h[i] << (6 - 2 * g);
+                w[i] = (lo & 0x3C3C3C3Cu) | (hi & 0xC0C0C0C0u);
+            }
+#pragma unroll
+            for (int t = 0; t < CNT; t++) {
+                int s = 0, s2 = 0;
+                s = dp4a_us(w[0], act[t].a[4 * g + 0], s);
+                s2 = dp4a_us(w[1], act[t].a[4 * g + 1], s2);
+                s = dp4a_us(w[2], act[t].a[4 * g + 2], s);
+                s2 = dp4a_us(w[3], act[t].a[4 * g + 3], s2);
+                isum[t] += c[g] * (s + s2);
+            }
+        }
+#pragma unroll
+        for (int t = 0; t < CNT; t++) acc[t] += (d4 * act[t].dx) * (float)isum[t];
+    }
+};
+
+template <> struct Dot<Q6_K_T4> {
     struct Pre {
         int la_off, h_off, sc_off, d_off;
     };
@@ -240,8 +345,8 @@ template <int DT, int NMAT> struct Cfg {
                                      (DT == PMOE_Q8_0 ? Q8_0_BYTES : DT == PMOE_Q4_K ? Q4_K_BYTES : Q6_K_BYTES);
     static constexpr int ROWS = floor_pow2(STAGE_BYTES / (ROW_BYTES * NMAT));  // rows of each matrix per item
     static constexpr int ITEM_BYTES = ROWS * ROW_BYTES;                        // per matrix
-    // tokens per pass: bounded by the activation registers a lane keeps (16 words per token for Q4_K, 4 otherwise)
-    static constexpr int TGK = (NMAT == 1 && DT != PMOE_Q4_K) ? 4 : 2;
+    // tokens per pass: bounded by the activation registers a lane keeps (16 words per token for Q4_K and Q6_K, 4 for Q8_0)
+    static constexpr int TGK = (NMAT == 1 && (DT == PMOE_Q8_0 || DT == Q6_K_T4)) ? 4 : 2;
     static constexpr int RPW = ROWS / GEMV_WARPS;     // rows per warp per item
     static constexpr int PASSES = RPW / GROUPS;
     static constexpr int RB = cmin(cmin(PASSES, 4), cmax(1, LPR / (NMAT * TGK)));  // rows reduced together
@@ -255,6 +360,7 @@ struct GemvArgs {
     size_t expert_bytes;
     const uint8_t *sw0, *sw1;  // shared expert matrices
     int rows_total;            // output length (F for gate/up, H for down)
+    int e_local;               // routed experts this layer holds
     int routed;                // serve the routed experts listed in g
     int has_shared;            // serve the shared expert
     int n, top_k;
@@ -853,7 +959,12 @@ static cudaError_t launch_gemv_s(const GemvArgs &A, int dt_s, cudaStream_t s)
     switch (dt_s) {
     case 0: return launch_gemv_t<DT_R, 0, NMAT>(A, s);
     case PMOE_Q4_K: return launch_gemv_t<DT_R, PMOE_Q4_K, NMAT>(A, s);
-    case PMOE_Q6_K: return launch_gemv_t<DT_R, PMOE_Q6_K, NMAT>(A, s);
+    case PMOE_Q6_K:
+        // a down matrix shared by three or more tokens: the four-tokens-per-pass variant
+        if constexpr (NMAT == 1) {
+            if (A.sh_count >= 3) return launch_gemv_t<DT_R, Q6_K_T4, NMAT>(A, s);
+        }
+        return launch_gemv_t<DT_R, PMOE_Q6_K, NMAT>(A, s);
     case PMOE_Q8_0: return launch_gemv_t<DT_R, PMOE_Q8_0, NMAT>(A, s);
     }
     return cudaErrorInvalidValue;
@@ -864,7 +975,13 @@ static cudaError_t launch_gemv(const GemvArgs &A, int dt_r, int dt_s, cudaStream
 {
     switch (dt_r) {
     case PMOE_Q4_K: return launch_gemv_s<PMOE_Q4_K, NMAT>(A, dt_s, s);
-    case PMOE_Q6_K: return launch_gemv_s<PMOE_Q6_K, NMAT>(A, dt_s, s);
+    case PMOE_Q6_K:
+        // down projection of a call with more than about one token per expert: experts with
+        // three or four tokens are common, and the variant that takes four per pass wins
+        if constexpr (NMAT == 1) {
+            if (A.routed && (long)A.n * A.top_k >= A.e_local) return launch_gemv_s<Q6_K_T4, NMAT>(A, dt_s, s);
+        }
+        return launch_gemv_s<PMOE_Q6_K, NMAT>(A, dt_s, s);
     case PMOE_Q8_0: return launch_gemv_s<PMOE_Q8_0, NMAT>(A, dt_s, s);
     }
     return cudaErrorInvalidValue;
@@ -879,6 +996,7 @@ cudaError_t launch_gate_up(const LayerDev &L, const Workspace &ws, int n, int to
     A.expert_bytes = row_bytes(L.gate_dtype, L.H) * L.F;
     A.sw0 = L.sh_gate; A.sw1 = L.sh_up;
     A.rows_total = L.F;
+    A.e_local = L.E_local;
     A.routed = routed; A.has_shared = shared;
     A.n = n; A.top_k = top_k;
     A.sh_begin = ws.sh_begin; A.sh_count = ws.sh_count;
@@ -906,6 +1024,7 @@ cudaError_t launch_down(const LayerDev &L, const Workspace &ws, const float *w, 
     A.expert_bytes = row_bytes(L.down_dtype, L.F) * L.H;
     A.sw0 = L.sh_down; A.sw1 = nullptr;
     A.rows_total = L.H;
+    A.e_local = L.E_local;
     A.routed = routed; A.has_shared = shared;
     A.n = n; A.top_k = top_k;
     A.sh_begin = ws.sh_begin; A.sh_count = ws.sh_count;

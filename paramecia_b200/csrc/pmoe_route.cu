@@ -5,6 +5,7 @@
 // Reference semantics: MoeBlock::forward_with_stats (paramecia-model/src/qwen3_next.rs:1903-1940),
 // ops::topk_moe_routing (paramecia-model/src/ops.rs:28-59), the host-side grouping of
 // apply_experts_sequential (qwen3_next.rs:2037-2050) and ops::group_tokens_by_expert (ops.rs:74-157).
+#include <cstdlib>
 #include "pmoe_common.cuh"
 #include "pmoe_quant.cuh"
 
@@ -140,22 +141,23 @@ __global__ void __launch_bounds__(ROUTER_WPB * 32) k_router(const float *__restr
     }
 }
 
-// The same product for more than a handful of tokens.  A CTA stages a tile of RT_TOKENS rows
-// of x in shared memory as f32; each warp keeps its slice of one router row in registers and
-// walks the tile.  The per-lane partial sums are built and folded in exactly the order above
-// (the transposed reduction pairs lanes 16, 8, 4, 2, 1 apart like the butterfly), so the bits
-// do not depend on which kernel ran.  H <= 2048.
-constexpr int RT_TOKENS = 8;
+// The same product for more than a handful of tokens, register-tiled.  A CTA stages a tile of T
+// rows of x in shared memory as f32; a warp works on R router rows at once against all T tokens,
+// so one shared-memory read of x feeds 4*R multiply-adds and one read of W feeds 4*T.  Each
+// (row, token) partial sum is still built by lane p over elements 128*i + 4*p + j in ascending
+// order and folded 16, 8, 4, 2, 1 lanes apart like the butterfly (the transposed reduction only
+// changes which lane ends up with which total), so the bits do not depend on which kernel ran.
+// H <= 2048, a multiple of 128.  PASSES row groups per warp amortise the tile load.
 constexpr int RT_WARPS = 8;
 
-template <typename XT>
+template <typename XT, int R, int T>
 __global__ void __launch_bounds__(RT_WARPS * 32) k_router_tiled(const float *__restrict__ W,
                                                                 const float *__restrict__ bias,
                                                                 const XT *__restrict__ x, int n, int E, int H,
-                                                                int rows_per_cta, float *__restrict__ logits,
+                                                                int passes, float *__restrict__ logits,
                                                                 int token_tiles, PrepArgs P)
 {
-    extern __shared__ __align__(16) float xs[];  // [RT_TOKENS][H]
+    extern __shared__ __align__(16) float xs[];  // [T][H]
     __shared__ float red[8];
     if ((int)blockIdx.y >= token_tiles) {  // grid rows past the token tiles prepare one token per CTA
         const int t = ((int)blockIdx.y - token_tiles) * gridDim.x + blockIdx.x;
@@ -163,9 +165,9 @@ __global__ void __launch_bounds__(RT_WARPS * 32) k_router_tiled(const float *__r
         return;
     }
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int t0 = blockIdx.y * RT_TOKENS;
-    const int nt = n - t0 < RT_TOKENS ? n - t0 : RT_TOKENS;
-    for (int i = threadIdx.x * 4; i < RT_TOKENS * H; i += RT_WARPS * 32 * 4) {
+    const int t0 = blockIdx.y * T;
+    const int nt = n - t0 < T ? n - t0 : T;
+    for (int i = threadIdx.x * 4; i < T * H; i += RT_WARPS * 32 * 4) {
         const int tt = i / H;
         float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
         if (tt < nt) v = load_x4(x, (size_t)(t0 + tt) * H + (i - tt * H));
@@ -173,88 +175,68 @@ __global__ void __launch_bounds__(RT_WARPS * 32) k_router_tiled(const float *__r
     }
     __syncthreads();
     const int steps = H / 128;  // <= 16
-    const int e_begin = blockIdx.x * rows_per_cta;
-    for (int e = e_begin + warp; e < e_begin + rows_per_cta && e < E; e += RT_WARPS) {
-        float4 wv[16];
-        const float4 *w4 = reinterpret_cast<const float4 *>(W + (size_t)e * H);
+    const int h4 = H / 4;
+    const float4 *xs4 = reinterpret_cast<const float4 *>(xs);
+    for (int pass = 0; pass < passes; pass++) {
+        const int e0 = ((blockIdx.x * passes + pass) * RT_WARPS + warp) * R;
+        if (e0 >= E) break;
+        const float4 *w4[R];
 #pragma unroll
-        for (int i = 0; i < 16; i++)
-            if (i < steps) wv[i] = w4[32 * i + lane];
-        float acc[RT_TOKENS];
+        for (int r = 0; r < R; r++) w4[r] = reinterpret_cast<const float4 *>(W + (size_t)(e0 + r < E ? e0 + r : E - 1) * H) + lane;
+        float acc[R * T];
 #pragma unroll
-        for (int tt = 0; tt < RT_TOKENS; tt++) {
-            float a = 0.f;
-            const float4 *x4 = reinterpret_cast<const float4 *>(xs + tt * H);
+        for (int i = 0; i < R * T; i++) acc[i] = 0.f;
+#pragma unroll 4
+        for (int i = 0; i < steps; i++) {
+            float4 wv[R];
 #pragma unroll
-            for (int i = 0; i < 16; i++) {
-                if (i < steps) {
-                    const float4 xv = x4[32 * i + lane];
-                    a = fmaf(xv.x, wv[i].x, a);
-                    a = fmaf(xv.y, wv[i].y, a);
-                    a = fmaf(xv.z, wv[i].z, a);
-                    a = fmaf(xv.w, wv[i].w, a);
+            for (int r = 0; r < R; r++) wv[r] = w4[r][32 * i];
+#pragma unroll
+            for (int tt = 0; tt < T; tt++) {
+                const float4 xv = xs4[tt * h4 + 32 * i + lane];
+#pragma unroll
+                for (int r = 0; r < R; r++) {
+                    float a = acc[r * T + tt];
+                    a = fmaf(xv.x, wv[r].x, a);
+                    a = fmaf(xv.y, wv[r].y, a);
+                    a = fmaf(xv.z, wv[r].z, a);
+                    a = fmaf(xv.w, wv[r].w, a);
+                    acc[r * T + tt] = a;
                 }
             }
-            acc[tt] = a;
         }
-        const float v = transposed_reduce<RT_TOKENS, 32>(acc, lane);
-        const int tt = lane >> 2;  // lanes 4*tt .. 4*tt+3 hold token tt's sum
-        if ((lane & 3) == 0 && tt < nt) logits[(size_t)(t0 + tt) * E + e] = bias ? __fadd_rn(v, bias[e]) : v;
+        // fold 32 (or fewer) totals at a time: value index = r * T + tt, lane / DUP holds it
+        constexpr int V = R * T < 32 ? R * T : 32;
+        constexpr int DUP = 32 / V;
+#pragma unroll
+        for (int c = 0; c < R * T / V; c++) {
+            const float v = transposed_reduce<V, 32>(*reinterpret_cast<float(*)[V]>(acc + c * V), lane);
+            const int vi = c * V + lane / DUP;
+            const int r = vi / T, tt = vi % T;
+            if (lane % DUP == 0 && tt < nt && e0 + r < E)
+                logits[(size_t)(t0 + tt) * E + e0 + r] = bias ? __fadd_rn(v, bias[e0 + r]) : v;
+        }
     }
 }
 
-// Many tokens (prefill): a wider token tile kept in shared memory in its own element type, so
-// that the router matrix is re-read from L2 only once per 32 (bf16) or 16 (f32) tokens.  Same
-// per-lane partial sums and the same fold as above.  H == 2048.
-template <typename XT> struct WideTile { static constexpr int TT = 131072 / (2048 * (int)sizeof(XT)); };
-
-template <typename XT>
-__global__ void __launch_bounds__(RT_WARPS * 32) k_router_wide(const float *__restrict__ W,
-                                                               const float *__restrict__ bias,
-                                                               const XT *__restrict__ x, int n, int E,
-                                                               int rows_per_cta, float *__restrict__ logits)
+template <typename XT, int R, int T>
+static cudaError_t launch_router_tiled(const LayerDev &L, const void *x, int n, int passes, float *logits, const PrepArgs &P,
+                                       cudaStream_t s)
 {
-    constexpr int TT = WideTile<XT>::TT, H = 2048;
-    extern __shared__ __align__(16) unsigned char xs_raw[];
-    XT *xs = reinterpret_cast<XT *>(xs_raw);  // [TT][H]
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int t0 = blockIdx.y * TT;
-    const int nt = n - t0 < TT ? n - t0 : TT;
-    constexpr int VEC = 16 / (int)sizeof(XT);  // elements per 16-byte copy
-    for (int i = threadIdx.x * VEC; i < TT * H; i += RT_WARPS * 32 * VEC) {
-        const int tt = i / H;
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (tt < nt) v = *reinterpret_cast<const uint4 *>(x + (size_t)(t0 + tt) * H + (i - tt * H));
-        *reinterpret_cast<uint4 *>(xs + i) = v;
+    auto kern = k_router_tiled<XT, R, T>;
+    const size_t smem = (size_t)T * L.H * sizeof(float);
+    static bool configured = false;  // per instantiation
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, T * 2048 * (int)sizeof(float));
+        if (e != cudaSuccess) return e;
+        configured = true;
     }
-    __syncthreads();
-    const int e_begin = blockIdx.x * rows_per_cta;
-    for (int e = e_begin + warp; e < e_begin + rows_per_cta && e < E; e += RT_WARPS) {
-        float4 wv[16];
-        const float4 *w4 = reinterpret_cast<const float4 *>(W + (size_t)e * H);
-#pragma unroll
-        for (int i = 0; i < 16; i++) wv[i] = w4[32 * i + lane];
-#pragma unroll 1
-        for (int g0 = 0; g0 < TT; g0 += 8) {  // eight tokens per fold keeps the accumulators in registers
-            float acc[8];
-#pragma unroll
-            for (int tt = 0; tt < 8; tt++) {
-                float a = 0.f;
-#pragma unroll
-                for (int i = 0; i < 16; i++) {
-                    const float4 xv = load_x4(xs, (size_t)(g0 + tt) * H + 128 * i + 4 * lane);
-                    a = fmaf(xv.x, wv[i].x, a);
-                    a = fmaf(xv.y, wv[i].y, a);
-                    a = fmaf(xv.z, wv[i].z, a);
-                    a = fmaf(xv.w, wv[i].w, a);
-                }
-                acc[tt] = a;
-            }
-            const float v = transposed_reduce<8, 32>(acc, lane);
-            const int tt = g0 + (lane >> 2);  // lanes 4*j .. 4*j+3 hold token j's sum
-            if ((lane & 3) == 0 && tt < nt) logits[(size_t)(t0 + tt) * E + e] = bias ? __fadd_rn(v, bias[e]) : v;
-        }
-    }
+    const int rows_per_cta = RT_WARPS * R * passes;
+    const int gx = (L.E + rows_per_cta - 1) / rows_per_cta, tiles = (n + T - 1) / T;
+    dim3 grid(gx, tiles + (P.n + gx - 1) / gx);
+    kern<<<grid, RT_WARPS * 32, smem, s>>>(L.router_w, L.router_bias, (const XT *)x, n, L.E, L.H, passes, logits, tiles, P);
+    count_launch();
+    return cudaGetLastError();
 }
 
 // Router launch.  With `prep` set the same launch also prepares the tokens (quantised rows, shared
@@ -265,54 +247,25 @@ cudaError_t launch_router(const LayerDev &L, const Workspace &ws, const void *x,
     if (n <= 0) return cudaSuccess;
     const bool f32 = x_dtype == PMOE_F32;
     using BT = __nv_bfloat16;
-    if (n > 512 && L.H == 2048) {
-        if (prep) {
-            cudaError_t e = launch_prep(L, ws, x, x_dtype, n, need_q8k, need_q80, need_gate, s);
-            if (e != cudaSuccess) return e;
-        }
-        static bool configured_wide = false;
-        if (!configured_wide) {
-            cudaError_t e1 = cudaFuncSetAttribute(k_router_wide<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 131072);
-            cudaError_t e2 = cudaFuncSetAttribute(k_router_wide<BT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 131072);
-            if (e1 != cudaSuccess) return e1;
-            if (e2 != cudaSuccess) return e2;
-            configured_wide = true;
-        }
-        const int rows_per_cta = 64;
-        if (f32) {
-            dim3 grid((L.E + rows_per_cta - 1) / rows_per_cta, (n + WideTile<float>::TT - 1) / WideTile<float>::TT);
-            k_router_wide<float><<<grid, RT_WARPS * 32, 131072, s>>>(L.router_w, L.router_bias, (const float *)x, n, L.E,
-                                                                     rows_per_cta, logits);
-        } else {
-            dim3 grid((L.E + rows_per_cta - 1) / rows_per_cta, (n + WideTile<BT>::TT - 1) / WideTile<BT>::TT);
-            k_router_wide<BT><<<grid, RT_WARPS * 32, 131072, s>>>(L.router_w, L.router_bias, (const BT *)x, n, L.E,
-                                                                  rows_per_cta, logits);
-        }
-        count_launch();
-        return cudaGetLastError();
-    }
     const PrepArgs P = make_prep_args(L, ws, prep ? n : 0, need_q8k, need_q80, need_gate);
-    if (n > 8 && L.H <= 2048) {
-        static bool configured = false;
-        const size_t smem = (size_t)RT_TOKENS * L.H * sizeof(float);
-        if (!configured) {
-            cudaError_t e1 = cudaFuncSetAttribute(k_router_tiled<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 65536);
-            cudaError_t e2 = cudaFuncSetAttribute(k_router_tiled<BT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 65536);
-            if (e1 != cudaSuccess) return e1;
-            if (e2 != cudaSuccess) return e2;
-            configured = true;
+    if (n >= 2 && L.H <= 2048 && L.H % 128 == 0) {  // (one token: the row-per-warp kernel below is faster)
+        if (n > 512) {  // prefill sizes: 16-token tiles (128 KB of shared memory), 64 rows per CTA
+            // (token preparation in its own launch: riding along it would hold 128 KB per token)
+            if (prep) {
+                cudaError_t e = launch_prep(L, ws, x, x_dtype, n, need_q8k, need_q80, need_gate, s);
+                if (e != cudaSuccess) return e;
+            }
+            const PrepArgs none = make_prep_args(L, ws, 0, need_q8k, need_q80, need_gate);
+            return f32 ? launch_router_tiled<float, 4, 16>(L, x, n, 8, logits, none, s)
+                       : launch_router_tiled<BT, 4, 16>(L, x, n, 8, logits, none, s);
         }
-        const int rows_per_cta = 16;
-        const int gx = (L.E + rows_per_cta - 1) / rows_per_cta, tiles = (n + RT_TOKENS - 1) / RT_TOKENS;
-        dim3 grid(gx, tiles + (P.n + gx - 1) / gx);
-        if (f32)
-            k_router_tiled<float><<<grid, RT_WARPS * 32, smem, s>>>(L.router_w, L.router_bias, (const float *)x, n, L.E,
-                                                                    L.H, rows_per_cta, logits, tiles, P);
-        else
-            k_router_tiled<BT><<<grid, RT_WARPS * 32, smem, s>>>(L.router_w, L.router_bias, (const BT *)x, n, L.E, L.H,
-                                                                 rows_per_cta, logits, tiles, P);
-        count_launch();
-        return cudaGetLastError();
+        if (n >= 64) {
+            const int tiles = (n + 7) / 8, passes = tiles >= 32 ? tiles / 16 : 1;  // about 256 CTAs
+            return f32 ? launch_router_tiled<float, 4, 8>(L, x, n, passes, logits, P, s)
+                       : launch_router_tiled<BT, 4, 8>(L, x, n, passes, logits, P, s);
+        }
+        return f32 ? launch_router_tiled<float, 2, 8>(L, x, n, 1, logits, P, s)
+                   : launch_router_tiled<BT, 2, 8>(L, x, n, 1, logits, P, s);
     }
     if (L.H > 2048 && prep) {  // the shared-memory row of the fused form is sized for H <= 2048
         cudaError_t e = launch_prep(L, ws, x, x_dtype, n, need_q8k, need_q80, need_gate, s);
