@@ -14,6 +14,11 @@ namespace pmoe {
 
 static std::atomic<uint64_t> g_launches{0};
 void count_launch(int n) { g_launches.fetch_add((uint64_t)n, std::memory_order_relaxed); }
+bool pdl_enabled()
+{
+    static const bool on = !(getenv("PMOE_PDL") && atoi(getenv("PMOE_PDL")) == 0);
+    return on;
+}
 
 static thread_local std::string g_last_error;
 

@@ -146,7 +146,13 @@ __device__ inline void bulk_g2s(void *smem_dst, const void *gmem_src, uint32_t b
         : "memory");
 }
 
-// programmatic dependent launch
+// Programmatic dependent launch.  A kernel started through launch_pdl may begin while its
+// predecessor in the stream still runs: it must call pdl_wait() before it reads anything an
+// earlier kernel wrote or writes anything an earlier kernel may still read (the wait returns
+// once every earlier grid has completed and its writes are visible).  pdl_launch_dependents()
+// lets the next kernel's CTAs become resident early; where a kernel calls it after its own
+// wait, its successor may rely on everything before this kernel being complete.  Both are
+// no-ops in a kernel that was launched the ordinary way.
 __device__ inline void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ inline void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
@@ -289,5 +295,22 @@ cudaError_t launch_add_rms_norm(const float *resid_in, const float *delta, const
                                 float eps, float *resid_out, float *y, cudaStream_t s);
 
 void count_launch(int n = 1);
+bool pdl_enabled();  // PMOE_PDL=0 in the environment turns the overlap off (plain stream order)
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args &&...args)
+{
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+    cfg.attrs = at;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
 
 }  // namespace pmoe

@@ -869,6 +869,12 @@ __global__ void __launch_bounds__(GEMV_THREADS, 2) k_expert_gemv(const GemvArgs 
     extern __shared__ __align__(128) uint8_t ring[];
     __shared__ int s_prefix[1025];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // Gate/up follows the grouping kernel and needs its lists at once.  The down kernel follows
+    // gate/up (or the re-quantisation), which called pdl_launch_dependents() after its own wait:
+    // the lists are complete by then, so the down kernel plans and its producer starts to stream
+    // weights while the predecessor still runs; only the compute warps wait, for the activations.
+    if (NMAT == 2) pdl_wait();
+    pdl_launch_dependents();
 
     constexpr int DT_S1 = DT_S ? DT_S : DT_R;
     using CR = Cfg<DT_R, NMAT>;
@@ -906,6 +912,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 2) k_expert_gemv(const GemvArgs 
         }
         return;
     }
+    if (NMAT == 1) pdl_wait();
     int it = 0;
     bool ok = run_items<DT_R, NMAT>(A, ring, plan, false, cur, plan.n_active, it, n_items, A.in_r, warp, lane);
     if constexpr (DT_S != 0) {
@@ -948,9 +955,9 @@ static cudaError_t launch_gemv_t(const GemvArgs &A, cudaStream_t s)
         cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev);
         if (g_sm_count <= 0) g_sm_count = 148;
     }
-    kern<<<2 * g_sm_count, GEMV_THREADS, smem, s>>>(A);
+    cudaError_t e = launch_pdl(kern, dim3(2 * g_sm_count), dim3(GEMV_THREADS), smem, s, A);
     count_launch();
-    return cudaGetLastError();
+    return e;
 }
 
 template <int DT_R, int NMAT>
@@ -1144,6 +1151,8 @@ __global__ void __launch_bounds__(64) k_act_quant(const float *__restrict__ act,
 {
     const int r = blockIdx.x;
     int dt;
+    pdl_wait();
+    pdl_launch_dependents();
     if (r < n_routed_rows) {
         if (!routed || pos[r] < 0) return;
         dt = dt_r;
@@ -1160,10 +1169,10 @@ cudaError_t launch_act_quant(const LayerDev &L, const Workspace &ws, const uint3
     (void)idx;
     if (n <= 0) return cudaSuccess;
     int rows = n * top_k + (shared ? n : 0);
-    k_act_quant<<<rows, 64, 0, s>>>(ws.act, L.F, n * top_k, ws.groups.pos, routed, L.down_dtype, L.sh_down_dtype,
-                                    ws.act_q8k, ws.act_q80);
+    cudaError_t e = launch_pdl(k_act_quant, dim3(rows), dim3(64), 0, s, (const float *)ws.act, L.F, n * top_k,
+                               (const int *)ws.groups.pos, routed, L.down_dtype, L.sh_down_dtype, ws.act_q8k, ws.act_q80);
     count_launch();
-    return cudaGetLastError();
+    return e;
 }
 
 // ---------------------------------------------------------------- combine
@@ -1176,6 +1185,8 @@ __global__ void __launch_bounds__(256) k_combine(const float *__restrict__ parti
                                                  int sh_count, OT *__restrict__ out)
 {
     const int t = blockIdx.x;
+    pdl_wait();
+    pdl_launch_dependents();
     for (int h = threadIdx.x * 4; h < H; h += blockDim.x * 4) {
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
         if (routed) {
@@ -1202,14 +1213,16 @@ cudaError_t launch_combine(const LayerDev &L, const Workspace &ws, const uint32_
 {
     (void)idx;
     if (n <= 0) return cudaSuccess;
+    cudaError_t e;
     if (out_dtype == PMOE_F32)
-        k_combine<float><<<n, 256, 0, s>>>(ws.partial, ws.groups.pos, n, top_k, L.H, routed, shared, ws.sh_begin, ws.sh_count,
-                                           (float *)out);
+        e = launch_pdl(k_combine<float>, dim3(n), dim3(256), 0, s, (const float *)ws.partial, (const int *)ws.groups.pos, n,
+                       top_k, L.H, routed, shared, ws.sh_begin, ws.sh_count, (float *)out);
     else
-        k_combine<__nv_bfloat16><<<n, 256, 0, s>>>(ws.partial, ws.groups.pos, n, top_k, L.H, routed, shared, ws.sh_begin,
-                                                   ws.sh_count, (__nv_bfloat16 *)out);
+        e = launch_pdl(k_combine<__nv_bfloat16>, dim3(n), dim3(256), 0, s, (const float *)ws.partial,
+                       (const int *)ws.groups.pos, n, top_k, L.H, routed, shared, ws.sh_begin, ws.sh_count,
+                       (__nv_bfloat16 *)out);
     count_launch();
-    return cudaGetLastError();
+    return e;
 }
 
 }  // namespace pmoe

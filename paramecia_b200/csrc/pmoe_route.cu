@@ -54,6 +54,8 @@ __global__ void __launch_bounds__(256) k_prep(const XT *__restrict__ x, int H, P
 {
     extern __shared__ __align__(16) float xrow[];
     __shared__ float red[8];
+    pdl_wait();
+    pdl_launch_dependents();
     prep_token(x, H, blockIdx.x, P, xrow, red);
 }
 
@@ -74,10 +76,11 @@ cudaError_t launch_prep(const LayerDev &L, const Workspace &ws, const void *x, i
     if (n <= 0) return cudaSuccess;
     size_t smem = (size_t)L.H * sizeof(float);
     const PrepArgs P = make_prep_args(L, ws, n, need_q8k, need_q80, need_gate);
-    if (x_dtype == PMOE_F32) k_prep<float><<<n, 256, smem, s>>>((const float *)x, L.H, P);
-    else k_prep<__nv_bfloat16><<<n, 256, smem, s>>>((const __nv_bfloat16 *)x, L.H, P);
+    cudaError_t e;
+    if (x_dtype == PMOE_F32) e = launch_pdl(k_prep<float>, dim3(n), dim3(256), smem, s, (const float *)x, L.H, P);
+    else e = launch_pdl(k_prep<__nv_bfloat16>, dim3(n), dim3(256), smem, s, (const __nv_bfloat16 *)x, L.H, P);
     count_launch();
-    return cudaGetLastError();
+    return e;
 }
 
 // ---------------------------------------------------------------- router logits
@@ -104,6 +107,8 @@ __global__ void __launch_bounds__(ROUTER_WPB * 32) k_router(const float *__restr
 {
     extern __shared__ __align__(16) float xrow[];
     __shared__ float red[8];
+    pdl_wait();
+    pdl_launch_dependents();
     if ((int)blockIdx.x >= router_ctas) {  // CTAs past the router rows prepare one token each
         prep_token(x, H, (int)blockIdx.x - router_ctas, P, xrow, red);
         return;
@@ -159,6 +164,8 @@ __global__ void __launch_bounds__(RT_WARPS * 32) k_router_tiled(const float *__r
 {
     extern __shared__ __align__(16) float xs[];  // [T][H]
     __shared__ float red[8];
+    pdl_wait();
+    pdl_launch_dependents();
     if ((int)blockIdx.y >= token_tiles) {  // grid rows past the token tiles prepare one token per CTA
         const int t = ((int)blockIdx.y - token_tiles) * gridDim.x + blockIdx.x;
         if (t < P.n) prep_token(x, H, t, P, xs, red);
@@ -234,9 +241,10 @@ static cudaError_t launch_router_tiled(const LayerDev &L, const void *x, int n, 
     const int rows_per_cta = RT_WARPS * R * passes;
     const int gx = (L.E + rows_per_cta - 1) / rows_per_cta, tiles = (n + T - 1) / T;
     dim3 grid(gx, tiles + (P.n + gx - 1) / gx);
-    kern<<<grid, RT_WARPS * 32, smem, s>>>(L.router_w, L.router_bias, (const XT *)x, n, L.E, L.H, passes, logits, tiles, P);
+    cudaError_t e = launch_pdl(kern, grid, dim3(RT_WARPS * 32), smem, s, L.router_w, L.router_bias, (const XT *)x, n, L.E,
+                               L.H, passes, logits, tiles, P);
     count_launch();
-    return cudaGetLastError();
+    return e;
 }
 
 // Router launch.  With `prep` set the same launch also prepares the tokens (quantised rows, shared
@@ -275,19 +283,20 @@ cudaError_t launch_router(const LayerDev &L, const Workspace &ws, const void *x,
     const int pn = L.H > 2048 ? 0 : P.n;
     dim3 grid(rc + pn), block(ROUTER_WPB * 32);
     const size_t smem = pn ? (size_t)L.H * sizeof(float) : 0;
+    cudaError_t e;
     if (f32) {
         if (n == 1)
-            k_router<float, 1><<<grid, block, smem, s>>>(L.router_w, L.router_bias, (const float *)x, n, L.E, L.H, logits, rc, P);
+            e = launch_pdl(k_router<float, 1>, grid, block, smem, s, L.router_w, L.router_bias, (const float *)x, n, L.E, L.H, logits, rc, P);
         else
-            k_router<float, 8><<<grid, block, smem, s>>>(L.router_w, L.router_bias, (const float *)x, n, L.E, L.H, logits, rc, P);
+            e = launch_pdl(k_router<float, 8>, grid, block, smem, s, L.router_w, L.router_bias, (const float *)x, n, L.E, L.H, logits, rc, P);
     } else {
         if (n == 1)
-            k_router<BT, 1><<<grid, block, smem, s>>>(L.router_w, L.router_bias, (const BT *)x, n, L.E, L.H, logits, rc, P);
+            e = launch_pdl(k_router<BT, 1>, grid, block, smem, s, L.router_w, L.router_bias, (const BT *)x, n, L.E, L.H, logits, rc, P);
         else
-            k_router<BT, 8><<<grid, block, smem, s>>>(L.router_w, L.router_bias, (const BT *)x, n, L.E, L.H, logits, rc, P);
+            e = launch_pdl(k_router<BT, 8>, grid, block, smem, s, L.router_w, L.router_bias, (const BT *)x, n, L.E, L.H, logits, rc, P);
     }
     count_launch();
-    return cudaGetLastError();
+    return e;
 }
 
 // ---------------------------------------------------------------- softmax + top-k
@@ -302,6 +311,8 @@ __global__ void __launch_bounds__(TOPK_WPB * 32) k_topk(const float *__restrict_
     extern __shared__ float sprob[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.x * TOPK_WPB + warp;
+    pdl_wait();
+    pdl_launch_dependents();
     if (t >= n) return;
     float *p = sprob + (size_t)warp * E;
     float mx = -INFINITY;
@@ -356,9 +367,10 @@ cudaError_t launch_topk(const LayerDev &L, const Workspace &ws, const float *log
     (void)ws;
     if (n <= 0) return cudaSuccess;
     size_t smem = (size_t)TOPK_WPB * L.E * sizeof(float);
-    k_topk<<<(n + TOPK_WPB - 1) / TOPK_WPB, TOPK_WPB * 32, smem, s>>>(logits, n, L.E, L.k, idx, w);
+    cudaError_t e = launch_pdl(k_topk, dim3((n + TOPK_WPB - 1) / TOPK_WPB), dim3(TOPK_WPB * 32), smem, s,
+                               (const float *)logits, n, L.E, L.k, idx, w);
     count_launch();
-    return cudaGetLastError();
+    return e;
 }
 
 // ---------------------------------------------------------------- grouping by expert
@@ -379,6 +391,8 @@ __global__ void __launch_bounds__(GROUP_THREADS) k_group(const uint32_t *__restr
     __shared__ int wide_scan[1024];
     const int tid = threadIdx.x;
     cnt[tid] = 0;
+    pdl_wait();
+    pdl_launch_dependents();
     __syncthreads();
     for (int p = tid; p < npairs; p += GROUP_THREADS) {
         uint32_t e = idx[p] - (uint32_t)base;  // wraps to a large value when below base
@@ -445,9 +459,9 @@ __global__ void __launch_bounds__(GROUP_THREADS) k_group(const uint32_t *__restr
 cudaError_t launch_group(const LayerDev &L, const Workspace &ws, const uint32_t *idx, int n, int top_k,
                          cudaStream_t s)
 {
-    k_group<<<1, GROUP_THREADS, 0, s>>>(idx, n * top_k, L.expert_base, L.E_local, ws.groups);
+    cudaError_t e = launch_pdl(k_group, dim3(1), dim3(GROUP_THREADS), 0, s, idx, n * top_k, L.expert_base, L.E_local, ws.groups);
     count_launch();
-    return cudaGetLastError();
+    return e;
 }
 
 }  // namespace pmoe
