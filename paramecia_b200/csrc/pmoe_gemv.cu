@@ -46,14 +46,18 @@ struct ActQ16 {   // 4 groups of 4 activations
     uint32_t a[4];
     float dx;
 };
+struct ActQ32 {   // 4 runs of 8 activations
+    uint32_t a[8];
+    float dx;
+};
 struct ActQ6K {   // 64 activations of a Q8_K block: four runs of 16, one per 6-bit scale of the unit
     uint32_t a[16];
     float dx;
     int bs[4];    // sum of each run (the block's partial sums)
 };
 
-// Internal variant of Q6_K for the down kernels of calls with several tokens per expert: 16-weight
-// lane units, whose four activation words per token let a pass take four tokens.  Same bytes,
+// Internal variant of Q6_K for the down kernels of calls with several tokens per expert: 32-weight
+// lane units, whose eight activation words per token let a pass take four tokens.  Same bytes,
 // same arithmetic; only the split of a row over lanes and passes differs.
 constexpr int Q6_K_T4 = 1000 + PMOE_Q6_K;
 
@@ -69,9 +73,9 @@ template <> struct Tr<PMOE_Q6_K> {
     using Act = ActQ6K;
 };
 template <> struct Tr<Q6_K_T4> {
-    static constexpr int UNIT = 16;
+    static constexpr int UNIT = 32;
     static constexpr bool KQ = true;
-    using Act = ActQ16;
+    using Act = ActQ32;
 };
 template <> struct Tr<PMOE_Q8_0> {
     static constexpr int UNIT = 16;
@@ -100,7 +104,12 @@ template <> __device__ inline void zero_act<PMOE_Q8_0>(ActQ16 &o)
     for (int i = 0; i < 4; i++) o.a[i] = 0;
     o.dx = 0.f;
 }
-template <> __device__ inline void zero_act<Q6_K_T4>(ActQ16 &o) { zero_act<PMOE_Q8_0>(o); }
+template <> __device__ inline void zero_act<Q6_K_T4>(ActQ32 &o)
+{
+#pragma unroll
+    for (int i = 0; i < 8; i++) o.a[i] = 0;
+    o.dx = 0.f;
+}
 
 template <int DT> __device__ inline void load_act(const QAct &q, size_t row, int K, int u, typename Tr<DT>::Act &o);
 
@@ -137,12 +146,16 @@ template <> __device__ inline void load_act<PMOE_Q6_K>(const QAct &q, size_t row
     for (int g = 0; g < 4; g++) o.bs[g] = bs[2 * g];
 }
 
-// 16-weight unit u: block u/16, half (u/8)%2, positions l = 4j .. 4j+3 (j = u%8) of the four streams
-template <> __device__ inline void load_act<Q6_K_T4>(const QAct &q, size_t row, int K, int u, ActQ16 &o)
+// 32-weight unit u: block u/8, half (u/4)%2, positions l = 8jj .. 8jj+7 (jj = u%4) of the four streams
+template <> __device__ inline void load_act<Q6_K_T4>(const QAct &q, size_t row, int K, int u, ActQ32 &o)
 {
-    const int b = u >> 4, half = (u >> 3) & 1, j = u & 7;
-    const uint32_t *p = reinterpret_cast<const uint32_t *>(q.qs + row * K + 256 * b + 128 * half + 4 * j);
-    o.a[0] = p[0]; o.a[1] = p[8]; o.a[2] = p[16]; o.a[3] = p[24];
+    const int b = u >> 3, half = (u >> 2) & 1, jj = u & 3;
+    const int8_t *p = q.qs + row * K + 256 * b + 128 * half + 8 * jj;
+#pragma unroll
+    for (int g = 0; g < 4; g++) {
+        const uint2 v = *reinterpret_cast<const uint2 *>(p + 32 * g);
+        o.a[2 * g] = v.x; o.a[2 * g + 1] = v.y;
+    }
     o.dx = q.d[row * (K / QK_K) + b];
 }
 
@@ -274,34 +287,52 @@ template <> struct Dot<PMOE_Q6_K> {
     }
 };
 
+// 8 bytes from a 2-byte aligned address: three aligned words and a funnel shift
+__device__ inline void load8_a2(const uint8_t *p, uint32_t &o0, uint32_t &o1)
+{
+    const uintptr_t a = reinterpret_cast<uintptr_t>(p);
+    const uint32_t *q = reinterpret_cast<const uint32_t *>(a & ~(uintptr_t)3);
+    const uint32_t sh = (uint32_t)(a & 2) * 8;
+    const uint32_t u0 = q[0], u1 = q[1], u2 = q[2];
+    o0 = __funnelshift_r(u0, u1, sh);
+    o1 = __funnelshift_r(u1, u2, sh);
+}
+
 template <> struct Dot<Q6_K_T4> {
     struct Pre {
         int la_off, h_off, sc_off, d_off;
     };
     __device__ static inline Pre pre(int u)
     {
-        const int blk = (u >> 4) * Q6_K_BYTES, half = (u >> 3) & 1, j = u & 7;
-        return Pre{blk + 64 * half + 4 * j, blk + 128 + 32 * half + 4 * j, blk + 192 + 8 * half + (j >> 2), blk + 208};
+        const int blk = (u >> 3) * Q6_K_BYTES, half = (u >> 2) & 1, jj = u & 3;
+        return Pre{blk + 64 * half + 8 * jj, blk + 128 + 32 * half + 8 * jj, blk + 192 + 8 * half + (jj >> 1), blk + 208};
     }
     template <int CNT>
-    __device__ static inline void run(const uint8_t *row, const Pre &p, const ActQ16 *act, float *acc)
+    __device__ static inline void run(const uint8_t *row, const Pre &p, const ActQ32 *act, float *acc)
     {
-        const uint32_t la = lds_u32_a2(row + p.la_off);
-        const uint32_t lb = lds_u32_a2(row + p.la_off + 32);
-        const uint32_t h = lds_u32_a2(row + p.h_off);
+        uint32_t la[2], lb[2], h[2];
+        load8_a2(row + p.la_off, la[0], la[1]);
+        load8_a2(row + p.la_off + 32, lb[0], lb[1]);
+        load8_a2(row + p.h_off, h[0], h[1]);
         const int8_t *sc = reinterpret_cast<const int8_t *>(row + p.sc_off);
-        const int c0 = sc[0], c1 = sc[2], c2 = sc[4], c3 = sc[6];
+        const int c[4] = {sc[0], sc[2], sc[4], sc[6]};
         // the 6-bit quant goes to the top of each byte with its top bit flipped: as a signed
         // byte that is 4*(q-32); the factor 4 is taken out of d
         const float d4 = half_bits_to_float(*reinterpret_cast<const uint16_t *>(row + p.d_off)) * 0.25f;
-        const uint32_t w1 = (((la << 2) & 0x3C3C3C3Cu) | ((h << 6) & 0xC0C0C0C0u)) ^ 0x80808080u;
-        const uint32_t w2 = (((lb << 2) & 0x3C3C3C3Cu) | ((h << 4) & 0xC0C0C0C0u)) ^ 0x80808080u;
-        const uint32_t w3 = (((la >> 2) & 0x3C3C3C3Cu) | ((h << 2) & 0xC0C0C0C0u)) ^ 0x80808080u;
-        const uint32_t w4 = (((lb >> 2) & 0x3C3C3C3Cu) | (h & 0xC0C0C0C0u)) ^ 0x80808080u;
+        uint32_t w[4][2];
+#pragma unroll
+        for (int i = 0; i < 2; i++) {
+            w[0][i] = (((la[i] << 2) & 0x3C3C3C3Cu) | ((h[i] << 6) & 0xC0C0C0C0u)) ^ 0x80808080u;
+            w[1][i] = (((lb[i] << 2) & 0x3C3C3C3Cu) | ((h[i] << 4) & 0xC0C0C0C0u)) ^ 0x80808080u;
+            w[2][i] = (((la[i] >> 2) & 0x3C3C3C3Cu) | ((h[i] << 2) & 0xC0C0C0C0u)) ^ 0x80808080u;
+            w[3][i] = (((lb[i] >> 2) & 0x3C3C3C3Cu) | (h[i] & 0xC0C0C0C0u)) ^ 0x80808080u;
+        }
 #pragma unroll
         for (int t = 0; t < CNT; t++) {
-            const int isum = c0 * __dp4a((int)w1, (int)act[t].a[0], 0) + c1 * __dp4a((int)w2, (int)act[t].a[1], 0) +
-                             c2 * __dp4a((int)w3, (int)act[t].a[2], 0) + c3 * __dp4a((int)w4, (int)act[t].a[3], 0);
+            int isum = 0;
+#pragma unroll
+            for (int g = 0; g < 4; g++)
+                isum += c[g] * __dp4a((int)w[g][1], (int)act[t].a[2 * g + 1], __dp4a((int)w[g][0], (int)act[t].a[2 * g], 0));
             acc[t] += (d4 * act[t].dx) * (float)isum;
         }
     }
