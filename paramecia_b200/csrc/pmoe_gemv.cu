@@ -189,7 +189,7 @@ template <> struct Dot<PMOE_Q4_K> {
         const int qd = u & 3;
         return Pre{(u >> 2) * Q4_K_BYTES, (u >> 2) * Q4_K_BYTES + 16 + 32 * qd, 16 * (qd & 1), qd >> 1};
     }
-    template <int CNT>
+    template <int CNT, bool A4 = true>  // A4: the row starts on a 4-byte boundary
     __device__ static inline void run(const uint8_t *row, const Pre &p, const ActQ4K *act, float *acc)
     {
         const uint4 hdr = *reinterpret_cast<const uint4 *>(row + p.hdr_off);
@@ -224,12 +224,14 @@ template <> struct Dot<PMOE_Q4_K> {
     }
 };
 
-// 16 bytes from a 2-byte aligned address: five aligned words and a funnel shift by the lane's own
-// misalignment (0 or 16 bits).  Reads up to 4 bytes past the 16 (inside the block for every caller).
-__device__ inline void load16_a2(const uint8_t *p, uint32_t (&o)[4])
+// 16 bytes at row + off, 2-byte aligned: five aligned words and a funnel shift by the address's own
+// misalignment (0 or 16 bits).  `mis` = (address of row) & 2.  The address is formed from `row` by
+// plain offsets so that loads from a shared-memory row stay shared-memory loads.  Reads up to 4
+// bytes past the 16 (inside the block for every caller).
+__device__ inline void load16_a2(const uint8_t *row, int mis, int off, uint32_t (&o)[4])
 {
-    const uintptr_t a = reinterpret_cast<uintptr_t>(p);
-    const uint32_t *q = reinterpret_cast<const uint32_t *>(a & ~(uintptr_t)3);
+    const int a = off + mis;
+    const uint32_t *q = reinterpret_cast<const uint32_t *>(row - mis + (a & ~3));
     const uint32_t sh = (uint32_t)(a & 2) * 8;
     uint32_t u[5];
 #pragma unroll
@@ -237,6 +239,8 @@ __device__ inline void load16_a2(const uint8_t *p, uint32_t (&o)[4])
 #pragma unroll
     for (int i = 0; i < 4; i++) o[i] = __funnelshift_r(u[i], u[i + 1], sh);
 }
+
+__device__ inline int misalign2(const uint8_t *p) { return (int)(reinterpret_cast<uintptr_t>(p) & 2); }
 
 template <> struct Dot<PMOE_Q6_K> {
     struct Pre {
@@ -247,13 +251,14 @@ template <> struct Dot<PMOE_Q6_K> {
         const int blk = (u >> 2) * Q6_K_BYTES, half = (u >> 1) & 1, jj = u & 1;
         return Pre{blk + 64 * half + 16 * jj, blk + 128 + 32 * half + 16 * jj, blk + 192 + 8 * half + jj, blk + 208};
     }
-    template <int CNT>
+    template <int CNT, bool A4 = true>  // A4: the row starts on a 4-byte boundary
     __device__ static inline void run(const uint8_t *row, const Pre &p, const ActQ6K *act, float *acc)
     {
         uint32_t la[4], lb[4], h[4];
-        load16_a2(row + p.la_off, la);
-        load16_a2(row + p.la_off + 32, lb);
-        load16_a2(row + p.h_off, h);
+        const int mis = A4 ? 0 : misalign2(row);
+        load16_a2(row, mis, p.la_off, la);
+        load16_a2(row, mis, p.la_off + 32, lb);
+        load16_a2(row, mis, p.h_off, h);
         const int8_t *sc = reinterpret_cast<const int8_t *>(row + p.sc_off);
         const int c[4] = {sc[0], sc[2], sc[4], sc[6]};
         // quants are used as the unsigned bytes 4*q (0..252); the offset -32 comes back through the
@@ -287,11 +292,11 @@ template <> struct Dot<PMOE_Q6_K> {
     }
 };
 
-// 8 bytes from a 2-byte aligned address: three aligned words and a funnel shift
-__device__ inline void load8_a2(const uint8_t *p, uint32_t &o0, uint32_t &o1)
+// 8 bytes at row + off, 2-byte aligned: three aligned words and a funnel shift (see load16_a2)
+__device__ inline void load8_a2(const uint8_t *row, int mis, int off, uint32_t &o0, uint32_t &o1)
 {
-    const uintptr_t a = reinterpret_cast<uintptr_t>(p);
-    const uint32_t *q = reinterpret_cast<const uint32_t *>(a & ~(uintptr_t)3);
+    const int a = off + mis;
+    const uint32_t *q = reinterpret_cast<const uint32_t *>(row - mis + (a & ~3));
     const uint32_t sh = (uint32_t)(a & 2) * 8;
     const uint32_t u0 = q[0], u1 = q[1], u2 = q[2];
     o0 = __funnelshift_r(u0, u1, sh);
@@ -307,13 +312,14 @@ template <> struct Dot<Q6_K_T4> {
         const int blk = (u >> 3) * Q6_K_BYTES, half = (u >> 2) & 1, jj = u & 3;
         return Pre{blk + 64 * half + 8 * jj, blk + 128 + 32 * half + 8 * jj, blk + 192 + 8 * half + (jj >> 1), blk + 208};
     }
-    template <int CNT>
+    template <int CNT, bool A4 = true>  // A4: the row starts on a 4-byte boundary
     __device__ static inline void run(const uint8_t *row, const Pre &p, const ActQ32 *act, float *acc)
     {
         uint32_t la[2], lb[2], h[2];
-        load8_a2(row + p.la_off, la[0], la[1]);
-        load8_a2(row + p.la_off + 32, lb[0], lb[1]);
-        load8_a2(row + p.h_off, h[0], h[1]);
+        const int mis = A4 ? 0 : misalign2(row);
+        load8_a2(row, mis, p.la_off, la[0], la[1]);
+        load8_a2(row, mis, p.la_off + 32, lb[0], lb[1]);
+        load8_a2(row, mis, p.h_off, h[0], h[1]);
         const int8_t *sc = reinterpret_cast<const int8_t *>(row + p.sc_off);
         const int c[4] = {sc[0], sc[2], sc[4], sc[6]};
         // the 6-bit quant goes to the top of each byte with its top bit flipped: as a signed
@@ -343,7 +349,7 @@ template <> struct Dot<PMOE_Q8_0> {
         int d_off, q_off;
     };
     __device__ static inline Pre pre(int u) { return Pre{(u >> 1) * Q8_0_BYTES, (u >> 1) * Q8_0_BYTES + 2 + 16 * (u & 1)}; }
-    template <int CNT>
+    template <int CNT, bool A4 = true>  // A4: the row starts on a 4-byte boundary
     __device__ static inline void run(const uint8_t *row, const Pre &p, const ActQ16 *act, float *acc)
     {
         const float d = half_bits_to_float(*reinterpret_cast<const uint16_t *>(row + p.d_off));
@@ -1108,7 +1114,7 @@ __global__ void __launch_bounds__(128) k_qmatmul(const uint8_t *__restrict__ w, 
             else zero_act<DT>(act[t]);
         }
         const typename Dot<DT>::Pre pre = Dot<DT>::pre(u);
-        Dot<DT>::template run<TG>(rp, pre, act, acc);
+        Dot<DT>::template run<TG, false>(rp, pre, act, acc);
     }
 #pragma unroll
     for (int t = 0; t < TG; t++) {

@@ -235,7 +235,8 @@ def test_add_rms_norm():
     np.testing.assert_allclose(y.cpu().numpy(), want, rtol=2e-6, atol=1e-7)
 
 
-@pytest.mark.parametrize("dtype,rows,cols", [(pm.Q4_K, 64, 2048), (pm.Q6_K, 128, 512), (pm.Q8_0, 32, 1024)])
+@pytest.mark.parametrize("dtype,rows,cols", [(pm.Q4_K, 64, 2048), (pm.Q6_K, 128, 512), (pm.Q8_0, 32, 1024),
+                                             (pm.Q6_K, 33, 256)])   # 210-byte rows: every other row starts 2 bytes off a word
 def test_qmatmul_entry_point(dtype, rows, cols):
     rng = np.random.default_rng(11)
     w = po.quantize(dtype, (rng.standard_normal(rows * cols) * 0.02).astype(np.float32))
