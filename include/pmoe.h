@@ -86,7 +86,7 @@ typedef struct {
     const void *sh_gate, *sh_up, *sh_down;
     const float *sh_gate_inp;
 
-    int32_t router_dtype;     /* PMOE_F32 */
+    int32_t router_dtype;     /* PMOE_F32, or PMOE_F16 / PMOE_BF16 (widened to f32 at create) */
     const void *router_w;
     const float *router_bias; /* [E] added to the logits, or NULL (not in the reference;
                                  used to skew synthetic routing) */

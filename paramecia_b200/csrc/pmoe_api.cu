@@ -289,7 +289,8 @@ int pmoe_layer_create(const pmoe_layer_desc *desc, pmoe_layer **out)
     if (d.gate_dtype != d.up_dtype)
         return fail(PMOE_ERR_UNSUPPORTED_DTYPE, "gate and up experts must share one dtype (got %d and %d)", d.gate_dtype,
                     d.up_dtype);
-    if (d.router_dtype != PMOE_F32) return fail(PMOE_ERR_UNSUPPORTED_DTYPE, "router weights must be F32");
+    if (d.router_dtype != PMOE_F32 && d.router_dtype != PMOE_F16 && d.router_dtype != PMOE_BF16)
+        return fail(PMOE_ERR_UNSUPPORTED_DTYPE, "router weights must be F32, F16 or BF16 (got %d)", d.router_dtype);
     const char *why = "";
     if (!gemv_supported(d.gate_dtype, d.H, d.F, &why) || !gemv_supported(d.down_dtype, d.F, d.H, &why))
         return fail(dtype_known(d.gate_dtype) && (block_elems(d.gate_dtype) > 1) && (block_elems(d.down_dtype) > 1)
@@ -336,8 +337,26 @@ int pmoe_layer_create(const pmoe_layer_desc *desc, pmoe_layer **out)
         if (!rc) rc = place_tensor(L, d.sh_gate_inp, (size_t)d.H * 4, loc, &tmp, "sh_gate_inp");
         v.sh_gate_inp = (const float *)tmp;
     }
-    if (!rc) rc = place_tensor(L, d.router_w, (size_t)d.E * d.H * 4, loc, &tmp, "router_w");
-    v.router_w = (const float *)tmp;
+    if (!rc && d.router_dtype == PMOE_F32) {
+        rc = place_tensor(L, d.router_w, (size_t)d.E * d.H * 4, loc, &tmp, "router_w");
+        v.router_w = (const float *)tmp;
+    } else if (!rc) {
+        // 16-bit router weights are widened to f32 once, like the dequantised tensor the reference's
+        // QMatMul holds for an F16/BF16 ffn_gate_inp (models/with_tracing.rs:120-124)
+        rc = place_tensor(L, d.router_w, (size_t)d.E * d.H * 2, loc, &tmp, "router_w");
+        float *wide = nullptr;
+        if (!rc) {
+            cudaError_t e = cudaMalloc(&wide, (size_t)d.E * d.H * 4);
+            if (e != cudaSuccess) rc = fail_cuda(e, "router_w (f32 copy)");
+            else L->owned.push_back(wide);
+        }
+        if (!rc) {
+            cudaError_t e = launch_dequantize(d.router_dtype, tmp, (size_t)d.E * d.H, wide, 0);
+            if (e == cudaSuccess) e = cudaStreamSynchronize(0);
+            if (e != cudaSuccess) rc = fail_cuda(e, "router_w (f32 copy)");
+        }
+        v.router_w = wide;
+    }
     v.router_bias = nullptr;
     if (!rc && d.router_bias) {
         rc = place_tensor(L, d.router_bias, (size_t)d.E * 4, loc, &tmp, "router_bias");

@@ -23,7 +23,7 @@ import numpy as np
 import torch
 
 from . import _lib
-from ._lib import BF16, F32, LayerDesc, PmoeError, check, lib, row_bytes
+from ._lib import BF16, F16, F32, LayerDesc, PmoeError, check, lib, row_bytes
 
 _TORCH_TO_PMOE = {torch.float32: F32, torch.bfloat16: BF16}
 
@@ -166,11 +166,14 @@ class MoeBlock:
             raise ValueError("expert tensor shapes must be [E,F,H], [E,F,H], [E,H,F]")
         if tuple(gate.shape) != (self.num_experts, H):
             raise ValueError("router weight must be [E, H]")
+        # f16 / bf16 router weights go to the library as they are (it widens them once); others as f32
+        router_dt = {torch.float16: F16, torch.bfloat16: BF16}.get(gate.dtype, F32)
+        router = gate.to(self.device).contiguous() if router_dt != F32 else gate.to(self.device, torch.float32).contiguous()
         # the library adopts these device buffers in place (weights_location = 2); keep them alive
         self._keep = dict(
             gate=gate_exps.data.to(self.device), up=up_exps.data.to(self.device),
             down=down_exps.data.to(self.device),
-            router=gate.to(self.device, torch.float32).contiguous(),
+            router=router,
             bias=None if router_bias is None else router_bias.to(self.device, torch.float32).contiguous())
         d = LayerDesc()
         d.struct_size = C.sizeof(LayerDesc)
@@ -190,7 +193,7 @@ class MoeBlock:
             d.sh_gate_dtype, d.sh_up_dtype, d.sh_down_dtype = s.gate_proj.dtype, s.up_proj.dtype, s.down_proj.dtype
             d.sh_gate, d.sh_up, d.sh_down = (self._keep[k].data_ptr() for k in ("sg", "su", "sd"))
             d.sh_gate_inp = self._keep["sgi"].data_ptr()
-        d.router_dtype = F32
+        d.router_dtype = router_dt
         d.router_w = self._keep["router"].data_ptr()
         d.router_bias = None if self._keep["bias"] is None else self._keep["bias"].data_ptr()
         d.weights_location = 2
