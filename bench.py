@@ -50,6 +50,8 @@ def parse():
     ap.add_argument("--mode", default="decode", choices=["decode", "prefill"],
                     help="decode: the headline workload; prefill: 4096 tokens, Zipf-skewed routing, one GPU")
     ap.add_argument("--tokens", type=int, default=4096, help="tokens per step in prefill mode")
+    ap.add_argument("--preset", default="q4k_q6k_all",
+                    help="prefill mode: dtype mix of the layer (paramecia_b200.synth.PRESETS), e.g. q4k_m for a Q8_0 shared expert")
     return ap.parse_args()
 
 
@@ -195,7 +197,7 @@ def prefill_main(args):
     tpeak = float(peaks.get("bf16_tflops", 1590.0))
     n = args.tokens
     nl = max(1, min(args.layers, 2))
-    blocks = [synth.make_block(synth.make_layer(H, F, E, TOPK, "q4k_q6k_all", seed=0, device=dev, layer=li, zipf=True),
+    blocks = [synth.make_block(synth.make_layer(H, F, E, TOPK, args.preset, seed=0, device=dev, layer=li, zipf=True),
                                dev, max_tokens=n) for li in range(nl)]
     g = torch.Generator(device=dev).manual_seed(11)
     xs = [torch.randn((n, H), generator=g, device=dev).to(torch.bfloat16) for _ in range(2)]
@@ -243,7 +245,7 @@ def prefill_main(args):
     line = dict(metric="Q4_K MoE layer tokens/s (prefill)", value=n / (ms * 1e-3), unit=UNIT, n_gpus=1, steps=steps,
                 warmup=W, ms_per_step=ms, higher_is_better=True, scaling="weak", vs_baseline=None,
                 dtype="int8 digit MMAs (gate/up, exact) + fp16 MMAs (down), f32 accumulate", data="synthetic",
-                config=dict(workload=f"qwen3next-moe-block gate/up Q4_K, down Q6_K (shared expert alike) H{H} F{F} E{E} "
+                config=dict(workload=f"qwen3next-moe-block preset {args.preset} (gate/up Q4_K, down Q6_K) H{H} F{F} E{E} "
                                      f"top{TOPK}, prefill {n} bf16 tokens, Zipf-biased router",
                             active_experts=int((counts > 0).sum()), max_tokens_per_expert=int(counts.max()),
                             layers_cycled=nl, block_tflops=n * 71303168 / (ms * 1e-3) / 1e12),

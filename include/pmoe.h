@@ -135,6 +135,20 @@ int pmoe_route(pmoe_layer *layer, const void *x, int x_dtype, int n, float *logi
                uint32_t *idx_out, float *w_out, void *stream);
 
 /*
+ * Router statistics of one block, as the reference's auxiliary training losses use them
+ * (compute_z_loss and compute_load_balance_loss, qwen3_next.rs:5549-5648) -- here per block,
+ * on the device, from the (router_logits, top_indices) pair pmoe_forward / pmoe_route return:
+ *   counts_out [E] f32   number of selections of each expert (ids >= E are skipped),
+ *   losses_out [0]       z    = mean_t logsumexp(logits_t)^2,
+ *   losses_out [1]       lb   = E * sum_e (counts[e] / (n*top_k)) * mean_t softmax(logits_t)[e].
+ * The reference averages both over the blocks and multiplies by its loss weights; that is left
+ * to the caller.  Either output may be NULL.  Uses the handle's workspace: not concurrent with
+ * another call on the same handle.
+ */
+int pmoe_router_stats(pmoe_layer *layer, const float *logits, const uint32_t *idx, int n, int top_k,
+                      float *counts_out, float *losses_out, void *stream);
+
+/*
  * MoeExperts::forward_batched (qwen3_next.rs:1347-1394): routed experts only, with the
  * caller's routing.  idx [n, top_k] u32 (global expert ids), w [n, top_k] f32.
  */

@@ -193,6 +193,22 @@ class Layer:
         lib().pmo_route_topk(_p(logits), n, self.E, self.k, _p(idx), _p(w), _p(probs))
         return (idx, w, probs) if with_probs else (idx, w)
 
+    def router_stats(self, logits, idx):
+        """(expert_counts [E], z, lb) of one block: the per-block terms of compute_z_loss and
+        compute_load_balance_loss (paramecia-model/src/qwen3_next.rs:5549-5648), in float64."""
+        logits = np.asarray(logits, np.float64).reshape(-1, self.E)
+        idx = np.asarray(idx).reshape(logits.shape[0], -1).astype(np.int64)
+        mx = logits.max(-1, keepdims=True)
+        ex = np.exp(logits - mx)
+        lse = mx[:, 0] + np.log(ex.sum(-1))
+        z = float(np.mean(lse * lse))                                   # mean(log_sum_exp^2), 5573
+        probs = ex / ex.sum(-1, keepdims=True)                           # softmax_last_dim, 5617
+        sel = idx[(idx >= 0) & (idx < self.E)]                           # ids past E are skipped, 5624
+        counts = np.bincount(sel, minlength=self.E).astype(np.float64)
+        f = counts / idx.size                                            # / total_selections, 5629-5634
+        lb = float(self.E * np.sum(f * probs.mean(0)))                   # E * sum(f_i * p_i), 5641-5645
+        return counts, z, lb
+
     def experts_forward(self, x, idx, w):
         x = _c(x, np.float32).reshape(-1, self.H)
         idx = _c(idx, np.uint32); w = _c(w, np.float32)

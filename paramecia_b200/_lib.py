@@ -54,6 +54,7 @@ SYMBOLS = [
     ("pmoe_forward", _I, [_V, _V, _I, _I, _V, _I, _V, _V, _V, _V]),
     ("pmoe_forward_host", _I, [_V, _V, _I, _I, _V, _I, _V, _V, _V, _V]),
     ("pmoe_route", _I, [_V, _V, _I, _I, _V, _V, _V, _V]),
+    ("pmoe_router_stats", _I, [_V, _V, _V, _I, _I, _V, _V, _V]),
     ("pmoe_experts_forward", _I, [_V, _V, _I, _V, _V, _I, _I, _V, _I, _V]),
     ("pmoe_experts_forward_ep", _I, [_V, _V, _I, _V, _V, _I, _I, _I, _I, _V, _I, _V]),
     ("pmoe_shared_forward", _I, [_V, _V, _I, _I, _V, _I, _V]),

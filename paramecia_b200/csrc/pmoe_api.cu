@@ -234,10 +234,27 @@ int run_experts(pmoe_layer *L, const void *x, int x_dtype, const uint32_t *idx, 
         PHASE(L, 0, s, launch_prep(d, L->ws, x, x_dtype, n, nd.q8k, nd.q80, shared, s));
     }
     if (routed) PHASE(L, 3, s, launch_group(d, L->ws, idx, n, top_k, s));
-    // prefill: many tokens per expert -> grouped tensor-core GEMM; decode: streaming GEMV
+    // prefill: many tokens per expert -> grouped tensor-core GEMM; decode: streaming GEMV.  The
+    // expected number of tokens per routed expert is n * top_k / E whatever slice this layer holds.
     const char *force = getenv("PMOE_PREFILL");
-    const bool prefill = prefill_supported(d, routed, shared) &&
-                         (force ? atoi(force) != 0 : (long)n * top_k >= 8L * d.E_local && n >= 512);
+    const bool want_prefill = force ? atoi(force) != 0 : (long)n * top_k >= 8L * d.E && n >= 512;
+    bool prefill = want_prefill && prefill_supported(d, routed, shared);
+    // A shared expert the tensor-core kernels do not take (e.g. Q8_0) does not hold the routed experts
+    // back: they go through the tensor-core kernels and the shared expert through the streaming ones.
+    const bool split = want_prefill && !prefill && routed && shared && prefill_supported(d, true, false);
+    if (split) {
+        PHASE(L, 4, s, launch_gate_up_prefill(d, L->ws, n, top_k, true, false, s));
+        if (prefill_down_supported(d, true, false)) {
+            CU(launch_down_prefill(d, L->ws, w, n, top_k, true, false, s));
+        } else {
+            CU(launch_act_quant(d, L->ws, idx, n, top_k, true, false, s));
+            CU(launch_down(d, L->ws, w, n, top_k, true, false, s));
+        }
+        CU(launch_gate_up(d, L->ws, n, top_k, false, true, s));
+        PHASE(L, 6, s, launch_down(d, L->ws, w, n, top_k, false, true, s));
+        PHASE(L, 7, s, launch_combine(d, L->ws, idx, n, top_k, routed, shared, out, out_dtype, s));
+        return PMOE_OK;
+    }
     if (prefill)
         PHASE(L, 4, s, launch_gate_up_prefill(d, L->ws, n, top_k, routed, shared, s));
     else
@@ -469,6 +486,22 @@ int pmoe_forward(pmoe_layer *L, const void *x, int x_dtype, int n, void *out, in
     PHASE(L, 1, s, launch_router(d, L->ws, x, x_dtype, n, logits, s, true, nd.q8k, nd.q80, d.has_shared));
     PHASE(L, 2, s, launch_topk(d, L->ws, logits, n, idx, w, s));
     return run_experts(L, x, x_dtype, idx, w, n, d.k, true, d.has_shared, true, out, out_dtype, s);
+}
+
+int pmoe_router_stats(pmoe_layer *L, const float *logits, const uint32_t *idx, int n, int top_k, float *counts_out,
+                      float *losses_out, void *stream)
+{
+    if (!L) return fail(PMOE_ERR_INVALID_ARG, "layer is NULL");
+    if (n < 0 || n > L->desc.max_tokens) return fail(PMOE_ERR_TOO_MANY_TOKENS, "n = %d, max_tokens = %d", n, L->desc.max_tokens);
+    if (n == 0) return PMOE_OK;
+    if (!logits || !idx) return fail(PMOE_ERR_INVALID_ARG, "logits / idx is NULL");
+    if (top_k <= 0 || top_k > L->desc.k) return fail(PMOE_ERR_INVALID_ARG, "top_k = %d must be in [1, %d]", top_k, L->desc.k);
+    DeviceGuard guard(L->device);
+    // scratch: the workspace's partial-row buffer (rows * H floats), idle outside a forward call
+    const size_t have = (size_t)L->desc.max_tokens * (L->desc.k + 1) * L->desc.H;
+    if (router_stats_scratch_floats(n, L->desc.E) > have) return fail(PMOE_ERR_UNSUPPORTED_SHAPE, "statistics scratch too small");
+    CU(launch_router_stats(logits, idx, n, top_k, L->desc.E, L->ws.partial, counts_out, losses_out, (cudaStream_t)stream));
+    return PMOE_OK;
 }
 
 int pmoe_experts_forward(pmoe_layer *L, const void *x, int x_dtype, const uint32_t *idx, const float *w, int n,

@@ -266,6 +266,9 @@ cudaError_t launch_topk(const LayerDev &L, const Workspace &ws, const float *log
                         uint32_t *idx, float *w, cudaStream_t s);
 cudaError_t launch_group(const LayerDev &L, const Workspace &ws, const uint32_t *idx, int n, int top_k,
                          cudaStream_t s);
+size_t router_stats_scratch_floats(int n, int E);
+cudaError_t launch_router_stats(const float *logits, const uint32_t *idx, int n, int top_k, int E, float *scratch,
+                                float *counts_out, float *losses_out, cudaStream_t s);
 // pmoe_gemv.cu
 cudaError_t launch_gate_up(const LayerDev &L, const Workspace &ws, int n, int top_k, bool routed,
                            bool shared, cudaStream_t s);

@@ -464,4 +464,110 @@ cudaError_t launch_group(const LayerDev &L, const Workspace &ws, const uint32_t 
     return e;
 }
 
+// ---------------------------------------------------------------- router statistics
+// What the reference's auxiliary losses take from (router_logits, selected_experts) of one block
+// (compute_z_loss / compute_load_balance_loss, qwen3_next.rs:5549-5648):
+//   counts[e] = number of selections of expert e (ids >= E are skipped),
+//   z    = mean_t logsumexp(logits_t)^2,
+//   lb   = E * sum_e (counts[e] / (n*k)) * mean_t softmax(logits_t)[e].
+// Every sum runs in a fixed order (no float atomics), so repeated calls give the same bits.
+constexpr int STATS_CHUNK = 256;  // tokens per partial column sum
+
+// one warp per token: max, 1 / sum exp, logsumexp
+__global__ void __launch_bounds__(128) k_stats_tokens(const float *__restrict__ logits, int n, int E,
+                                                      float *__restrict__ mx, float *__restrict__ inv,
+                                                      float *__restrict__ lse)
+{
+    const int t = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (t >= n) return;
+    const float *p = logits + (size_t)t * E;
+    float m = -INFINITY;
+    for (int e = lane; e < E; e += 32) m = fmaxf(m, p[e]);
+#pragma unroll
+    for (int s = 16; s >= 1; s >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, s));
+    float sum = 0.f;
+    for (int e = lane; e < E; e += 32) sum += expf(p[e] - m);
+#pragma unroll
+    for (int s = 16; s >= 1; s >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, s);
+    if (lane == 0) {
+        mx[t] = m;
+        inv[t] = 1.f / sum;
+        lse[t] = m + logf(sum);
+    }
+}
+
+// thread per expert column, one chunk of tokens per grid row: partial[chunk][e] = sum_t softmax(logits_t)[e]
+__global__ void __launch_bounds__(128) k_stats_columns(const float *__restrict__ logits, int n, int E,
+                                                       const float *__restrict__ mx, const float *__restrict__ inv,
+                                                       float *__restrict__ partial)
+{
+    const int e = blockIdx.x * 128 + threadIdx.x;
+    if (e >= E) return;
+    const int t0 = blockIdx.y * STATS_CHUNK, t1 = min(n, t0 + STATS_CHUNK);
+    float acc = 0.f;
+    for (int t = t0; t < t1; t++) acc += expf(logits[(size_t)t * E + e] - mx[t]) * inv[t];
+    partial[(size_t)blockIdx.y * E + e] = acc;
+}
+
+// one CTA: selection counts (integer atomics in shared memory), then the two losses
+__global__ void __launch_bounds__(1024) k_stats_final(const uint32_t *__restrict__ idx, int n, int top_k, int E, int chunks,
+                                                      const float *__restrict__ partial, const float *__restrict__ lse,
+                                                      float *__restrict__ counts_out, float *__restrict__ losses_out)
+{
+    extern __shared__ int cnt[];  // [E]
+    __shared__ float red[32];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    for (int e = tid; e < E; e += 1024) cnt[e] = 0;
+    __syncthreads();
+    for (int p = tid; p < n * top_k; p += 1024) {
+        const uint32_t e = idx[p];
+        if (e < (uint32_t)E) atomicAdd(&cnt[e], 1);
+    }
+    __syncthreads();
+    float lb = 0.f, z = 0.f;
+    const float total = (float)n * (float)top_k;
+    for (int e = tid; e < E; e += 1024) {
+        float p = 0.f;
+        for (int c = 0; c < chunks; c++) p += partial[(size_t)c * E + e];
+        const float f = (float)cnt[e] / total;
+        lb += f * (p / (float)n);
+        if (counts_out) counts_out[e] = (float)cnt[e];
+    }
+    for (int t = tid; t < n; t += 1024) z += lse[t] * lse[t];
+#pragma unroll
+    for (int s = 16; s >= 1; s >>= 1) {
+        lb += __shfl_xor_sync(0xffffffffu, lb, s);
+        z += __shfl_xor_sync(0xffffffffu, z, s);
+    }
+    if (lane == 0) red[warp] = lb;
+    __syncthreads();
+    float lb_all = 0.f;
+    if (tid == 0)
+        for (int w = 0; w < 32; w++) lb_all += red[w];
+    __syncthreads();
+    if (lane == 0) red[warp] = z;
+    __syncthreads();
+    if (tid == 0 && losses_out) {
+        float z_all = 0.f;
+        for (int w = 0; w < 32; w++) z_all += red[w];
+        losses_out[0] = z_all / (float)n;
+        losses_out[1] = lb_all * (float)E;
+    }
+}
+
+size_t router_stats_scratch_floats(int n, int E) { return 3 * (size_t)n + (size_t)((n + STATS_CHUNK - 1) / STATS_CHUNK) * E; }
+
+cudaError_t launch_router_stats(const float *logits, const uint32_t *idx, int n, int top_k, int E, float *scratch,
+                                float *counts_out, float *losses_out, cudaStream_t s)
+{
+    if (n <= 0) return cudaSuccess;
+    float *mx = scratch, *inv = scratch + n, *lse = scratch + 2 * (size_t)n, *partial = scratch + 3 * (size_t)n;
+    const int chunks = (n + STATS_CHUNK - 1) / STATS_CHUNK;
+    k_stats_tokens<<<(n + 3) / 4, 128, 0, s>>>(logits, n, E, mx, inv, lse);
+    k_stats_columns<<<dim3((E + 127) / 128, chunks), 128, 0, s>>>(logits, n, E, mx, inv, partial);
+    k_stats_final<<<1, 1024, (size_t)E * sizeof(int), s>>>(idx, n, top_k, E, chunks, partial, lse, counts_out, losses_out);
+    count_launch(3);
+    return cudaGetLastError();
+}
+
 }  // namespace pmoe

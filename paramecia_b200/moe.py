@@ -281,6 +281,19 @@ class MoeBlock:
                                w.data_ptr(), _stream_ptr(self.device)))
         return logits, w, idx
 
+    def router_stats(self, router_logits: torch.Tensor, top_indices: torch.Tensor):
+        """Per-block pieces of compute_z_loss / compute_load_balance_loss (qwen3_next.rs:5549-5648):
+        ``(expert_counts [E] f32, z_loss, load_balance_loss)`` as device tensors, unweighted."""
+        E = self.num_experts
+        logits = router_logits.to(self.device, torch.float32).reshape(-1, E).contiguous()
+        n = logits.shape[0]
+        idx = top_indices.to(self.device, torch.int32).reshape(n, -1).contiguous()
+        counts = torch.zeros(E, dtype=torch.float32, device=self.device)
+        losses = torch.zeros(2, dtype=torch.float32, device=self.device)
+        check(lib().pmoe_router_stats(self._h, logits.data_ptr(), idx.data_ptr(), n, idx.shape[1], counts.data_ptr(),
+                                      losses.data_ptr(), _stream_ptr(self.device)))
+        return counts, losses[0], losses[1]
+
     def experts_forward_batched(self, hidden_states: torch.Tensor, expert_indices: torch.Tensor,
                                 expert_weights: torch.Tensor, top_k: Optional[int] = None,
                                 out_dtype: Optional[torch.dtype] = None,

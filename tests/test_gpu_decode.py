@@ -181,6 +181,24 @@ def test_experts_with_shared_rows(n, begin, count, prefill, preset):
             os.environ["PMOE_PREFILL"] = old
 
 
+@pytest.mark.parametrize("n", [1, 37, 700])
+def test_router_stats(n):
+    t = synth.make_layer(E=64, k=4, preset="q8_0", seed=6, shared=False, zipf=True)
+    blk = synth.make_block(t, DEV, max_tokens=n)
+    x = seeded_x(n, 2048, 90 + n).to(DEV)
+    logits, w, idx = blk.route(x)
+    idx = idx.clone()
+    if n > 1:
+        idx[1, 2] = 64        # an id past E does not count, but stays in the denominator
+    counts, z, lb = blk.router_stats(logits, idx)
+    want_counts, want_z, want_lb = oracle_layer(t).router_stats(logits.cpu().numpy(), idx.cpu().numpy())
+    assert np.array_equal(counts.cpu().numpy(), want_counts.astype(np.float32))
+    assert abs(float(z) - want_z) <= 1e-5 * abs(want_z)
+    assert abs(float(lb) - want_lb) <= 1e-5 * abs(want_lb)
+    again = blk.router_stats(logits, idx)
+    assert float(again[1]) == float(z) and float(again[2]) == float(lb)   # fixed summation order
+
+
 def test_expert_slices_sum_to_whole_block():
     # two expert-parallel halves of one layer give the whole layer's routed output
     t = synth.make_layer(E=64, k=6, preset="q4k_m", seed=9)

@@ -132,3 +132,23 @@ def test_rms_norm():
     y = po.rms_norm(x, wt, 1e-6)
     want = x / np.sqrt((x.astype(np.float64) ** 2).mean(1, keepdims=True) + 1e-6) * wt
     np.testing.assert_allclose(y, want, rtol=2e-6)
+
+
+def test_router_stats_formulas():
+    # the oracle's statistics against the formulas written with torch ops, as the reference writes them
+    import torch
+    from paramecia_b200 import synth
+    from tests.common import oracle_layer
+    t = synth.make_layer(E=16, k=3, preset="q8_0", seed=2, shared=False)
+    ol = oracle_layer(t)
+    rng = np.random.default_rng(4)
+    logits = rng.standard_normal((25, 16)).astype(np.float32) * 3
+    idx = np.stack([rng.choice(16, size=3, replace=False) for _ in range(25)]).astype(np.uint32)
+    counts, z, lb = ol.router_stats(logits, idx)
+    L = torch.from_numpy(logits).double()
+    lse = torch.logsumexp(L, -1)
+    assert abs(z - float((lse * lse).mean())) < 1e-12
+    f = torch.bincount(torch.from_numpy(idx.astype(np.int64)).flatten(), minlength=16).double() / idx.size
+    p = torch.softmax(L, -1).mean(0)
+    assert abs(lb - float(16 * (f * p).sum())) < 1e-12
+    assert counts.sum() == idx.size
