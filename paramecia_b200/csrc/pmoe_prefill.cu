@@ -31,6 +31,7 @@ namespace pmoe {
 constexpr int PF_NT = 64;        // tokens per tile (MMA N)
 constexpr int PF_M = 128;        // rows per tile (MMA M): 64 gate + 64 up
 constexpr int PF_THREADS = 128;
+constexpr int GU_THREADS = 256;   // gate/up kernel: two threads per weight row (one per half of a 256-wide block)
 constexpr int PF_TMEM_COLS = 256;  // D0, D1, Dh, Dl: 4 x 64 columns of s32
 
 // ---------------------------------------------------------------- tcgen05 wrappers
@@ -135,7 +136,7 @@ struct GuSmem {
     int slot, tile_in_slot;
 };
 
-__global__ void __launch_bounds__(PF_THREADS, 2) k_gu_prefill(const GuArgs A)
+__global__ void __launch_bounds__(GU_THREADS, 2) k_gu_prefill(const GuArgs A)
 {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     GuSmem &S = *reinterpret_cast<GuSmem *>(smem_raw);
@@ -191,33 +192,39 @@ __global__ void __launch_bounds__(PF_THREADS, 2) k_gu_prefill(const GuArgs A)
     }
     __syncthreads();
 
-    // this thread's weight row: threads 0..63 gate rows, 64..127 up rows of the same 64 outputs
+    // this thread's weight row r: rows 0..63 are gate rows, 64..127 the up rows of the same 64 outputs.
+    // Threads r and r + 128 share a row: kh = 0 decodes sub-blocks 0..3 of each block and drains
+    // token columns 0..31, kh = 1 sub-blocks 4..7 and columns 32..63.
+    const int r = tid & (PF_M - 1), kh = tid >> 7;
     const int f0 = blockIdx.x * 64;
     const int nblk = A.H / QK_K;
-    const uint8_t *wrow = (tid < 64 ? wg : wu) + (size_t)(f0 + (tid & 63)) * nblk * Q4_K_BYTES;
+    const uint8_t *wrow = (r < 64 ? wg : wu) + (size_t)(f0 + (r & 63)) * nblk * Q4_K_BYTES;
 
     constexpr uint32_t IDESC_UU_S = make_idesc(2, 0, 1, PF_NT, PF_M);  // u8 x s8
     constexpr uint32_t IDESC_UU_U = make_idesc(2, 0, 0, PF_NT, PF_M);  // u8 x u8
-    float acc[PF_NT];
+    constexpr int NC = PF_NT / 2;  // token columns this thread drains
+    float acc[NC];
 #pragma unroll
-    for (int i = 0; i < PF_NT; i++) acc[i] = 0.f;
+    for (int i = 0; i < NC; i++) acc[i] = 0.f;
     uint32_t phase = 0;
     bool ok = true;
 
-    // the row's current block lives in registers; the next one is fetched while the MMAs run
-    uint4 blk[9];
+    // the thread's half of the row's current block lives in registers (header + 64 bytes of quants);
+    // the next one is fetched while the MMAs run
+    uint4 blk[5];
+    blk[0] = reinterpret_cast<const uint4 *>(wrow)[0];
 #pragma unroll
-    for (int i = 0; i < 9; i++) blk[i] = reinterpret_cast<const uint4 *>(wrow)[i];
+    for (int i = 0; i < 4; i++) blk[1 + i] = reinterpret_cast<const uint4 *>(wrow)[1 + 4 * kh + i];
 
     for (int b = 0; b < nblk && ok; b++) {
         // ---- start this block's activation loads first: they fly while the weights are decoded
-        const int tk = tid >> 1, half = tid & 1;
+        const int tk = tid >> 2, quarter = tid & 3;   // 64 bytes of one token's block per thread
         const int rin_b = S.row_in[tk];
-        uint4 bv[8];
+        uint4 bv[4];
         {
-            const uint4 *src = reinterpret_cast<const uint4 *>(A.xq.qs + (size_t)(rin_b >= 0 ? rin_b : 0) * A.H + b * QK_K + 128 * half);
+            const uint4 *src = reinterpret_cast<const uint4 *>(A.xq.qs + (size_t)(rin_b >= 0 ? rin_b : 0) * A.H + b * QK_K + 64 * quarter);
 #pragma unroll
-            for (int i = 0; i < 8; i++) bv[i] = rin_b >= 0 ? src[i] : make_uint4(0, 0, 0, 0);
+            for (int i = 0; i < 4; i++) bv[i] = rin_b >= 0 ? src[i] : make_uint4(0, 0, 0, 0);
         }
         uint4 bs0 = make_uint4(0, 0, 0, 0), bs1 = make_uint4(0, 0, 0, 0);
         float dx_reg = 0.f;
@@ -237,13 +244,14 @@ __global__ void __launch_bounds__(PF_THREADS, 2) k_gu_prefill(const GuArgs A)
         const uint32_t sca = u0 & 0x3F3F3F3Fu, mna = u1 & 0x3F3F3F3Fu;
         const uint32_t scb = (u2 & 0x0F0F0F0Fu) | ((u0 >> 2) & 0x30303030u);
         const uint32_t mnb = ((u2 >> 4) & 0x0F0F0F0Fu) | ((u1 >> 2) & 0x30303030u);
+        const uint32_t scw = kh == 0 ? sca : scb;   // the four scales of this thread's half
 #pragma unroll
-        for (int gq = 0; gq < 4; gq++) {
-            const uint4 qa = blk[1 + 2 * gq], qb = blk[2 + 2 * gq];
+        for (int gl = 0; gl < 2; gl++) {
+            const int gq = 2 * kh + gl;                // 64-weight group of the block
+            const uint4 qa = blk[1 + 2 * gl], qb = blk[2 + 2 * gl];
             const uint32_t w[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
-            const uint32_t scw = gq < 2 ? sca : scb;
-            const uint32_t sc_lo = (scw >> (16 * (gq & 1))) & 0xFFu;        // sub-block 2*gq   (low nibbles)
-            const uint32_t sc_hi = (scw >> (16 * (gq & 1) + 8)) & 0xFFu;    // sub-block 2*gq+1 (high nibbles)
+            const uint32_t sc_lo = (scw >> (16 * gl)) & 0xFFu;        // sub-block 2*gq   (low nibbles)
+            const uint32_t sc_hi = (scw >> (16 * gl + 8)) & 0xFFu;    // sub-block 2*gq+1 (high nibbles)
             uint32_t d0[8], d1[8], e0[8], e1[8];
 #pragma unroll
             for (int i = 0; i < 8; i++) {
@@ -253,25 +261,25 @@ __global__ void __launch_bounds__(PF_THREADS, 2) k_gu_prefill(const GuArgs A)
             }
             // sub-block j occupies K bytes 32j .. 32j+31 = chunks 2j, 2j+1
             const int j0 = 2 * gq, j1 = 2 * gq + 1;
-            *reinterpret_cast<uint4 *>(S.a0 + core_off(PF_M, tid, 32 * j0)) = make_uint4(d0[0], d0[1], d0[2], d0[3]);
-            *reinterpret_cast<uint4 *>(S.a0 + core_off(PF_M, tid, 32 * j0 + 16)) = make_uint4(d0[4], d0[5], d0[6], d0[7]);
-            *reinterpret_cast<uint4 *>(S.a1 + core_off(PF_M, tid, 32 * j0)) = make_uint4(d1[0], d1[1], d1[2], d1[3]);
-            *reinterpret_cast<uint4 *>(S.a1 + core_off(PF_M, tid, 32 * j0 + 16)) = make_uint4(d1[4], d1[5], d1[6], d1[7]);
-            *reinterpret_cast<uint4 *>(S.a0 + core_off(PF_M, tid, 32 * j1)) = make_uint4(e0[0], e0[1], e0[2], e0[3]);
-            *reinterpret_cast<uint4 *>(S.a0 + core_off(PF_M, tid, 32 * j1 + 16)) = make_uint4(e0[4], e0[5], e0[6], e0[7]);
-            *reinterpret_cast<uint4 *>(S.a1 + core_off(PF_M, tid, 32 * j1)) = make_uint4(e1[0], e1[1], e1[2], e1[3]);
-            *reinterpret_cast<uint4 *>(S.a1 + core_off(PF_M, tid, 32 * j1 + 16)) = make_uint4(e1[4], e1[5], e1[6], e1[7]);
+            *reinterpret_cast<uint4 *>(S.a0 + core_off(PF_M, r, 32 * j0)) = make_uint4(d0[0], d0[1], d0[2], d0[3]);
+            *reinterpret_cast<uint4 *>(S.a0 + core_off(PF_M, r, 32 * j0 + 16)) = make_uint4(d0[4], d0[5], d0[6], d0[7]);
+            *reinterpret_cast<uint4 *>(S.a1 + core_off(PF_M, r, 32 * j0)) = make_uint4(d1[0], d1[1], d1[2], d1[3]);
+            *reinterpret_cast<uint4 *>(S.a1 + core_off(PF_M, r, 32 * j0 + 16)) = make_uint4(d1[4], d1[5], d1[6], d1[7]);
+            *reinterpret_cast<uint4 *>(S.a0 + core_off(PF_M, r, 32 * j1)) = make_uint4(e0[0], e0[1], e0[2], e0[3]);
+            *reinterpret_cast<uint4 *>(S.a0 + core_off(PF_M, r, 32 * j1 + 16)) = make_uint4(e0[4], e0[5], e0[6], e0[7]);
+            *reinterpret_cast<uint4 *>(S.a1 + core_off(PF_M, r, 32 * j1)) = make_uint4(e1[0], e1[1], e1[2], e1[3]);
+            *reinterpret_cast<uint4 *>(S.a1 + core_off(PF_M, r, 32 * j1 + 16)) = make_uint4(e1[4], e1[5], e1[6], e1[7]);
         }
-        {   // mins, each repeated for the two 16-wide halves of its sub-block: m0 m0 m1 m1 ... m7 m7, then zeros
+        if (kh == 0) {   // mins, each repeated for the two 16-wide halves of its sub-block: m0 m0 m1 m1 ... m7 m7, then zeros
             const uint32_t w0 = __byte_perm(mna, 0, 0x1100), w1 = __byte_perm(mna, 0, 0x3322);
             const uint32_t w2 = __byte_perm(mnb, 0, 0x1100), w3 = __byte_perm(mnb, 0, 0x3322);
-            *reinterpret_cast<uint4 *>(S.am + core_off(PF_M, tid, 0)) = make_uint4(w0, w1, w2, w3);
-            *reinterpret_cast<uint4 *>(S.am + core_off(PF_M, tid, 16)) = make_uint4(0, 0, 0, 0);
+            *reinterpret_cast<uint4 *>(S.am + core_off(PF_M, r, 0)) = make_uint4(w0, w1, w2, w3);
+            *reinterpret_cast<uint4 *>(S.am + core_off(PF_M, r, 16)) = make_uint4(0, 0, 0, 0);
         }
-        // ---- B: the tile's quantised activations for this block; token = tid / 2, half = tid & 1
+        // ---- B: the tile's quantised activations for this block; token = tid / 4, 64 bytes each
 #pragma unroll
-        for (int i = 0; i < 8; i++)
-            *reinterpret_cast<uint4 *>(S.b + core_off(PF_NT, tk, 128 * half + 16 * i)) = bv[i];
+        for (int i = 0; i < 4; i++)
+            *reinterpret_cast<uint4 *>(S.b + core_off(PF_NT, tk, 64 * quarter + 16 * i)) = bv[i];
         if (tid < PF_NT) {  // partial sums of 16 quants as two digits: bsum = 64*h + l, l in [0,63]
             uint32_t hw[4] = {0, 0, 0, 0}, lw[4] = {0, 0, 0, 0};
             const float dx = dx_reg;
@@ -307,8 +315,10 @@ __global__ void __launch_bounds__(PF_THREADS, 2) k_gu_prefill(const GuArgs A)
             tc_commit(&S.bar);
         }
         if (b + 1 < nblk) {  // next block of this thread's row, in flight during the MMAs and the fold
+            const uint4 *nx = reinterpret_cast<const uint4 *>(wrow + (size_t)(b + 1) * Q4_K_BYTES);
+            blk[0] = nx[0];
 #pragma unroll
-            for (int i = 0; i < 9; i++) blk[i] = reinterpret_cast<const uint4 *>(wrow + (size_t)(b + 1) * Q4_K_BYTES)[i];
+            for (int i = 0; i < 4; i++) blk[1 + i] = nx[1 + 4 * kh + i];
         }
         if (!mbar_wait_spin(&S.bar, phase)) {
             set_status(A.status, PMOE_ERR_TIMEOUT, 30, b);
@@ -316,11 +326,12 @@ __global__ void __launch_bounds__(PF_THREADS, 2) k_gu_prefill(const GuArgs A)
         }
         phase ^= 1;
         tc_fence_after();
-        // ---- fold the block into the f32 accumulators: row = tid, TMEM lane = tid
+        // ---- fold the block into the f32 accumulators: row r = TMEM lane r (a warp reaches the 32
+        // lanes of its quarter, warp % 4), this thread's half of the token columns
         if (ok) {
-            const uint32_t lane_addr = tmem + ((uint32_t)(warp * 32) << 16);
+            const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16) + kh * NC;
 #pragma unroll
-            for (int cc = 0; cc < PF_NT / 16; cc++) {
+            for (int cc = 0; cc < NC / 16; cc++) {
                 uint32_t v0[16], v1[16], vh[16], vl[16];
                 tmem_ld16(lane_addr + 0 + cc * 16, v0);
                 tmem_ld16(lane_addr + 64 + cc * 16, v1);
@@ -331,7 +342,7 @@ __global__ void __launch_bounds__(PF_THREADS, 2) k_gu_prefill(const GuArgs A)
                 for (int j = 0; j < 16; j++) {
                     const int s = (int)v0[j] + 8 * (int)v1[j];
                     const int mm = 64 * (int)vh[j] + (int)vl[j];
-                    acc[cc * 16 + j] += S.dx[cc * 16 + j] * (dw * (float)s - dmin * (float)mm);
+                    acc[cc * 16 + j] += S.dx[kh * NC + cc * 16 + j] * (dw * (float)s - dmin * (float)mm);
                 }
             }
         }
@@ -345,10 +356,10 @@ __global__ void __launch_bounds__(PF_THREADS, 2) k_gu_prefill(const GuArgs A)
     // of the 64 x PF_NT outputs: output o = (token j, column f), consecutive threads = consecutive f.
     float *xch = reinterpret_cast<float *>(S.a0);
 #pragma unroll
-    for (int j = 0; j < PF_NT; j++) xch[tid * (PF_NT + 1) + j] = acc[j];
+    for (int j = 0; j < NC; j++) xch[r * (PF_NT + 1) + kh * NC + j] = acc[j];
     __syncthreads();
     if (ok) {
-        for (int o = tid; o < 64 * PF_NT; o += PF_THREADS) {
+        for (int o = tid; o < 64 * PF_NT; o += GU_THREADS) {
             const int f = o & 63, j = o >> 6;
             const int rout = S.row_out[j];
             if (rout < 0) continue;
@@ -691,7 +702,7 @@ cudaError_t launch_gate_up_prefill(const LayerDev &L, const Workspace &ws, int n
     }
     const int tiles = (routed ? max_routed_tiles(L, n, top_k) : 0) + (shared ? (ws.sh_count + PF_NT - 1) / PF_NT : 0);
     dim3 grid(L.F / 64, tiles);
-    k_gu_prefill<<<grid, PF_THREADS, sizeof(GuSmem) + 128, s>>>(A);
+    k_gu_prefill<<<grid, GU_THREADS, sizeof(GuSmem) + 128, s>>>(A);
     count_launch();
     return cudaGetLastError();
 }
