@@ -34,6 +34,7 @@ typedef enum {
     PMOE_F16 = 1,
     PMOE_Q8_0 = 8,
     PMOE_Q4_K = 12,
+    PMOE_Q5_K = 13,
     PMOE_Q6_K = 14,
     PMOE_BF16 = 30
 } pmoe_dtype;

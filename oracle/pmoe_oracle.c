@@ -88,6 +88,7 @@ static inline uint16_t f32_to_f16(float f)
 #pragma pack(push, 1)
 typedef struct { uint16_t d; int8_t qs[QK8_0]; } block_q8_0;                      /* 34 B  */
 typedef struct { uint16_t d, dmin; uint8_t scales[12]; uint8_t qs[QK_K / 2]; } block_q4_K; /* 144 B */
+typedef struct { uint16_t d, dmin; uint8_t scales[12]; uint8_t qh[QK_K / 8]; uint8_t qs[QK_K / 2]; } block_q5_K; /* 176 B */
 typedef struct { uint8_t ql[QK_K / 2]; uint8_t qh[QK_K / 4]; int8_t scales[QK_K / 16]; uint16_t d; } block_q6_K; /* 210 B */
 #pragma pack(pop)
 typedef struct { float d; int8_t qs[QK_K]; int16_t bsums[QK_K / 16]; } block_q8_K; /* activation block */
@@ -97,7 +98,7 @@ size_t pmo_block_size(int dtype)
     switch (dtype) {
     case PMO_F32: case PMO_F16: return 1;
     case PMO_Q8_0: return QK8_0;
-    case PMO_Q4_K: case PMO_Q6_K: return QK_K;
+    case PMO_Q4_K: case PMO_Q5_K: case PMO_Q6_K: return QK_K;
     default: return 0;
     }
 }
@@ -109,6 +110,7 @@ size_t pmo_type_size(int dtype)
     case PMO_F16: return 2;
     case PMO_Q8_0: return sizeof(block_q8_0);
     case PMO_Q4_K: return sizeof(block_q4_K);
+    case PMO_Q5_K: return sizeof(block_q5_K);
     case PMO_Q6_K: return sizeof(block_q6_K);
     default: return 0;
     }
@@ -166,6 +168,33 @@ static void dequant_q4_K(const block_q4_K *b, size_t nb, float *y)
     }
 }
 
+/* BlockQ5K::to_float (ggml dequantize_row_q5_K): the fifth bit of the two sub-blocks of 64-group
+ * j sits in bits 2j and 2j+1 of qh[l] */
+static void dequant_q5_K(const block_q5_K *b, size_t nb, float *y)
+{
+    for (size_t i = 0; i < nb; i++) {
+        const uint8_t *ql = b[i].qs;
+        const uint8_t *qh = b[i].qh;
+        float d = f16_to_f32(b[i].d);
+        float min = f16_to_f32(b[i].dmin);
+        int is = 0;
+        uint8_t u1 = 1, u2 = 2;
+        for (int j = 0; j < QK_K; j += 64) {
+            uint8_t sc, m;
+            q4k_scale_min(is, b[i].scales, &sc, &m);
+            float d1 = d * sc, m1 = min * m;
+            q4k_scale_min(is + 1, b[i].scales, &sc, &m);
+            float d2 = d * sc, m2 = min * m;
+            for (int l = 0; l < 32; l++) *y++ = d1 * (float)((ql[l] & 0xF) + ((qh[l] & u1) ? 16 : 0)) - m1;
+            for (int l = 0; l < 32; l++) *y++ = d2 * (float)((ql[l] >> 4) + ((qh[l] & u2) ? 16 : 0)) - m2;
+            ql += 32;
+            is += 2;
+            u1 = (uint8_t)(u1 << 2);
+            u2 = (uint8_t)(u2 << 2);
+        }
+    }
+}
+
 static void dequant_q6_K(const block_q6_K *b, size_t nb, float *y)
 {
     for (size_t i = 0; i < nb; i++) {
@@ -202,6 +231,7 @@ int pmo_dequantize(int dtype, const void *blocks, size_t n, float *out)
     case PMO_F16: for (size_t i = 0; i < n; i++) out[i] = f16_to_f32(((const uint16_t *)blocks)[i]); return 0;
     case PMO_Q8_0: dequant_q8_0((const block_q8_0 *)blocks, n / bs, out); return 0;
     case PMO_Q4_K: dequant_q4_K((const block_q4_K *)blocks, n / bs, out); return 0;
+    case PMO_Q5_K: dequant_q5_K((const block_q5_K *)blocks, n / bs, out); return 0;
     case PMO_Q6_K: dequant_q6_K((const block_q6_K *)blocks, n / bs, out); return 0;
     }
     return -1;
@@ -209,7 +239,7 @@ int pmo_dequantize(int dtype, const void *blocks, size_t n, float *out)
 
 /* ------------------------------------------------------------------ weight quantisers
  * Used only to make synthetic GGUF blocks from seeded normal weights.  Q8_0 is
- * the ggml/candle reference quantiser.  The Q4_K and Q6_K quantisers are plain
+ * the ggml/candle reference quantiser.  The Q4_K, Q5_K and Q6_K quantisers are plain
  * min/max quantisers of this build (not ggml's error-minimising search): any
  * valid quantiser serves, since oracle and library consume the same bytes. */
 
@@ -278,6 +308,64 @@ static void quant_q4_K(const float *x, size_t nb, block_q4_K *y)
     }
 }
 
+/* the Q4_K min/max quantiser with 32 levels */
+static void quant_q5_K(const float *x, size_t nb, block_q5_K *y)
+{
+    for (size_t i = 0; i < nb; i++) {
+        const float *xb = x + i * QK_K;
+        float scales[8], mins[8];
+        float max_scale = 0.f, max_min = 0.f;
+        for (int j = 0; j < 8; j++) {
+            float mn = 0.f, mx = 0.f;
+            for (int l = 0; l < 32; l++) {
+                mn = fminf(mn, xb[32 * j + l]);
+                mx = fmaxf(mx, xb[32 * j + l]);
+            }
+            scales[j] = (mx - mn) / 31.f;
+            mins[j] = -mn;
+            max_scale = fmaxf(max_scale, scales[j]);
+            max_min = fmaxf(max_min, mins[j]);
+        }
+        float inv_scale = max_scale > 0.f ? 63.f / max_scale : 0.f;
+        float inv_min = max_min > 0.f ? 63.f / max_min : 0.f;
+        uint8_t ls[8], lm[8];
+        for (int j = 0; j < 8; j++) {
+            int a = (int)roundf(inv_scale * scales[j]);
+            int b = (int)roundf(inv_min * mins[j]);
+            ls[j] = (uint8_t)(a > 63 ? 63 : a);
+            lm[j] = (uint8_t)(b > 63 ? 63 : b);
+        }
+        y[i].d = f32_to_f16(max_scale / 63.f);
+        y[i].dmin = f32_to_f16(max_min / 63.f);
+        for (int j = 0; j < 4; j++) {
+            y[i].scales[j] = (uint8_t)(ls[j] | ((ls[j + 4] >> 4) << 6));
+            y[i].scales[j + 4] = (uint8_t)(lm[j] | ((lm[j + 4] >> 4) << 6));
+            y[i].scales[j + 8] = (uint8_t)((ls[j + 4] & 0xF) | ((lm[j + 4] & 0xF) << 4));
+        }
+        float d = f16_to_f32(y[i].d), dmin = f16_to_f32(y[i].dmin);
+        uint8_t L[QK_K];
+        for (int j = 0; j < 8; j++) {
+            float dq = d * (float)ls[j];
+            float mq = dmin * (float)lm[j];
+            for (int l = 0; l < 32; l++) {
+                int q = 0;
+                if (dq > 0.f) {
+                    q = (int)roundf((xb[32 * j + l] + mq) / dq);
+                    q = q < 0 ? 0 : (q > 31 ? 31 : q);
+                }
+                L[32 * j + l] = (uint8_t)q;
+            }
+        }
+        memset(y[i].qh, 0, sizeof(y[i].qh));
+        for (int g = 0; g < 4; g++)
+            for (int l = 0; l < 32; l++) {
+                uint8_t a = L[64 * g + l], b = L[64 * g + 32 + l];
+                y[i].qs[32 * g + l] = (uint8_t)((a & 0xF) | ((b & 0xF) << 4));
+                y[i].qh[l] = (uint8_t)(y[i].qh[l] | ((a >> 4) << (2 * g)) | ((b >> 4) << (2 * g + 1)));
+            }
+    }
+}
+
 static void quant_q6_K(const float *x, size_t nb, block_q6_K *y)
 {
     for (size_t i = 0; i < nb; i++) {
@@ -328,12 +416,13 @@ int pmo_quantize(int dtype, const float *x, size_t n, void *blocks)
     size_t chunk = 4096;
     if (dtype == PMO_F32) { memcpy(blocks, x, n * 4); return 0; }
     if (dtype == PMO_F16) { for (size_t i = 0; i < n; i++) ((uint16_t *)blocks)[i] = f32_to_f16(x[i]); return 0; }
-    if (dtype != PMO_Q8_0 && dtype != PMO_Q4_K && dtype != PMO_Q6_K) return -1;
+    if (dtype != PMO_Q8_0 && dtype != PMO_Q4_K && dtype != PMO_Q5_K && dtype != PMO_Q6_K) return -1;
 #pragma omp parallel for schedule(static)
     for (size_t b0 = 0; b0 < nb; b0 += chunk) {
         size_t cnt = nb - b0 < chunk ? nb - b0 : chunk;
         if (dtype == PMO_Q8_0) quant_q8_0(x + b0 * bs, cnt, (block_q8_0 *)blocks + b0);
         else if (dtype == PMO_Q4_K) quant_q4_K(x + b0 * bs, cnt, (block_q4_K *)blocks + b0);
+        else if (dtype == PMO_Q5_K) quant_q5_K(x + b0 * bs, cnt, (block_q5_K *)blocks + b0);
         else quant_q6_K(x + b0 * bs, cnt, (block_q6_K *)blocks + b0);
     }
     return 0;
@@ -443,6 +532,51 @@ static float vec_dot_q4_K_q8_K(size_t n, const block_q4_K *x, const block_q8_K *
     return sumf + s;
 }
 
+/* BlockQ5K::vec_dot against Q8_K (portable path): as Q4_K with the fifth bit added to each quant */
+static float vec_dot_q5_K_q8_K(size_t n, const block_q5_K *x, const block_q8_K *y)
+{
+    float sums[8] = {0};
+    float sumf = 0.f;
+    int8_t aux8[QK_K];
+    for (size_t i = 0; i < n / QK_K; i++) {
+        const uint8_t *q4 = x[i].qs;
+        const uint8_t *hm = x[i].qh;
+        int8_t *a = aux8;
+        uint8_t m = 1;
+        for (int j = 0; j < QK_K / 64; j++) {
+            for (int l = 0; l < 32; l++) a[l] = (int8_t)((q4[l] & 0xF) + ((hm[l] & m) ? 16 : 0));
+            a += 32;
+            m = (uint8_t)(m << 1);
+            for (int l = 0; l < 32; l++) a[l] = (int8_t)((q4[l] >> 4) + ((hm[l] & m) ? 16 : 0));
+            a += 32;
+            m = (uint8_t)(m << 1);
+            q4 += 32;
+        }
+        uint8_t sc[8], mn[8];
+        for (int j = 0; j < 8; j++) q4k_scale_min(j, x[i].scales, &sc[j], &mn[j]);
+        int32_t sumi = 0;
+        for (int j = 0; j < QK_K / 16; j++) sumi += (int32_t)y[i].bsums[j] * (int32_t)mn[j / 2];
+        int32_t aux32[8] = {0};
+        const int8_t *q8 = y[i].qs;
+        a = aux8;
+        for (int j = 0; j < 8; j++) {
+            int32_t scale = sc[j];
+            for (int r = 0; r < 4; r++) {
+                for (int l = 0; l < 8; l++) aux32[l] += scale * ((int32_t)q8[l] * (int32_t)a[l]);
+                q8 += 8;
+                a += 8;
+            }
+        }
+        float d = f16_to_f32(x[i].d) * y[i].d;
+        for (int l = 0; l < 8; l++) sums[l] += d * (float)aux32[l];
+        float dmin = f16_to_f32(x[i].dmin) * y[i].d;
+        sumf -= dmin * (float)sumi;
+    }
+    float s = 0.f;
+    for (int l = 0; l < 8; l++) s += sums[l];
+    return sumf + s;
+}
+
 static float vec_dot_q6_K_q8_K(size_t n, const block_q6_K *x, const block_q8_K *y)
 {
     float sums[8] = {0};
@@ -512,7 +646,7 @@ static int qact_make(qact *a, int wdtype, const float *x, size_t m, size_t cols)
     a->dtype = wdtype;
     a->cols = cols;
     a->m = m;
-    if (wdtype == PMO_Q4_K || wdtype == PMO_Q6_K) {
+    if (wdtype == PMO_Q4_K || wdtype == PMO_Q5_K || wdtype == PMO_Q6_K) {
         if (cols % QK_K) return -1;
         block_q8_K *b = (block_q8_K *)malloc(sizeof(block_q8_K) * m * (cols / QK_K));
         for (size_t r = 0; r < m; r++) quantize_row_q8_K(x + r * cols, cols, b + r * (cols / QK_K));
@@ -536,6 +670,9 @@ static inline float qdot(int dtype, const void *w, size_t row, size_t cols, cons
     switch (dtype) {
     case PMO_Q4_K:
         return vec_dot_q4_K_q8_K(cols, (const block_q4_K *)w + row * (cols / QK_K),
+                                 (const block_q8_K *)a->blocks + r * (cols / QK_K));
+    case PMO_Q5_K:
+        return vec_dot_q5_K_q8_K(cols, (const block_q5_K *)w + row * (cols / QK_K),
                                  (const block_q8_K *)a->blocks + r * (cols / QK_K));
     case PMO_Q6_K:
         return vec_dot_q6_K_q8_K(cols, (const block_q6_K *)w + row * (cols / QK_K),

@@ -61,7 +61,7 @@ struct DeviceGuard {
 
 static bool dtype_known(int dt)
 {
-    return dt == PMOE_F32 || dt == PMOE_F16 || dt == PMOE_BF16 || dt == PMOE_Q8_0 || dt == PMOE_Q4_K || dt == PMOE_Q6_K;
+    return dt == PMOE_F32 || dt == PMOE_F16 || dt == PMOE_BF16 || dt == PMOE_Q8_0 || dt == PMOE_Q4_K || dt == PMOE_Q5_K || dt == PMOE_Q6_K;
 }
 
 }  // namespace pmoe
@@ -627,8 +627,8 @@ int pmoe_reduce_rows(int device, const float *parts, int n_parts, const void *ex
 int pmoe_qmatmul(int device, int dtype, const void *w, size_t rows, size_t cols, const float *x, size_t m, float *y,
                  void *stream)
 {
-    if (dtype != PMOE_Q4_K && dtype != PMOE_Q6_K && dtype != PMOE_Q8_0)
-        return fail(PMOE_ERR_UNSUPPORTED_DTYPE, "pmoe_qmatmul serves Q4_K, Q6_K and Q8_0 (got %d)", dtype);
+    if (dtype != PMOE_Q4_K && dtype != PMOE_Q5_K && dtype != PMOE_Q6_K && dtype != PMOE_Q8_0)
+        return fail(PMOE_ERR_UNSUPPORTED_DTYPE, "pmoe_qmatmul serves Q4_K, Q5_K, Q6_K and Q8_0 (got %d)", dtype);
     if (!rows || !cols || cols % 256 || cols > 16384 || rows > (1u << 24) || m > 4096)
         return fail(PMOE_ERR_UNSUPPORTED_SHAPE, "cols must be a multiple of 256 (<= 16384), m <= 4096");
     if (!m) return PMOE_OK;
@@ -648,8 +648,8 @@ int pmoe_qmatmul(int device, int dtype, const void *w, size_t rows, size_t cols,
 int pmoe_qmatmul_noalloc(int device, int dtype, const void *w, size_t rows, size_t cols, const float *x, size_t m,
                          float *y, void *stream)
 {
-    if (dtype != PMOE_Q4_K && dtype != PMOE_Q6_K && dtype != PMOE_Q8_0)
-        return fail(PMOE_ERR_UNSUPPORTED_DTYPE, "pmoe_qmatmul_noalloc serves Q4_K, Q6_K and Q8_0 (got %d)", dtype);
+    if (dtype != PMOE_Q4_K && dtype != PMOE_Q5_K && dtype != PMOE_Q6_K && dtype != PMOE_Q8_0)
+        return fail(PMOE_ERR_UNSUPPORTED_DTYPE, "pmoe_qmatmul_noalloc serves Q4_K, Q5_K, Q6_K and Q8_0 (got %d)", dtype);
     if (!rows || !cols || cols % 256 || rows > (1u << 24))
         return fail(PMOE_ERR_UNSUPPORTED_SHAPE, "cols must be a non-zero multiple of 256");
     if (!m) return PMOE_OK;

@@ -1,6 +1,6 @@
 // Block codecs and the small f32 kernels around the MoE block.
 //
-// k_dequantize restates candle's GgmlType::to_float for BlockQ8_0 / BlockQ4K / BlockQ6K (the
+// k_dequantize restates candle's GgmlType::to_float for BlockQ8_0 / BlockQ4K / BlockQ5K / BlockQ6K (the
 // QTensor::dequantize the reference calls, e.g. paramecia-model/src/qwen3_next.rs:1758-1762);
 // products are rounded one by one so the f32 bits equal the host codec's.
 // k_add_rms_norm is RmsNorm::forward (paramecia-model/src/quantized_nn.rs:172-190) fused with
@@ -41,6 +41,17 @@ __global__ void __launch_bounds__(256) k_dequantize(int dtype, const uint8_t *__
         q4k_scale_min(sub, b + 4, sc, m);
         uint8_t q = b[16 + 32 * grp + l];
         int v = (sub & 1) ? (q >> 4) : (q & 0xF);
+        out[i] = __fsub_rn(__fmul_rn(__fmul_rn(d, (float)sc), (float)v), __fmul_rn(dmin, (float)m));
+    } else if (dtype == PMOE_Q5_K) {
+        const uint8_t *b = blocks + (i / QK_K) * Q5_K_BYTES;
+        int w = (int)(i % QK_K);
+        int sub = w / 32, l = w % 32, grp = w / 64;
+        float d = half_bits_to_float((uint16_t)(b[0] | (b[1] << 8)));
+        float dmin = half_bits_to_float((uint16_t)(b[2] | (b[3] << 8)));
+        int sc, m;
+        q4k_scale_min(sub, b + 4, sc, m);
+        uint8_t q = b[48 + 32 * grp + l];
+        int v = ((sub & 1) ? (q >> 4) : (q & 0xF)) + (((b[16 + l] >> sub) & 1) << 4);
         out[i] = __fsub_rn(__fmul_rn(__fmul_rn(d, (float)sc), (float)v), __fmul_rn(dmin, (float)m));
     } else if (dtype == PMOE_Q6_K) {
         const uint8_t *b = blocks + (i / QK_K) * Q6_K_BYTES;

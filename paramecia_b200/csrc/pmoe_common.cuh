@@ -17,9 +17,11 @@ namespace pmoe {
 // ---------------------------------------------------------------- GGUF block layouts
 // Q8_0:  34 B = f16 d, int8 qs[32]
 // Q4_K: 144 B = f16 d, f16 dmin, u8 scales[12] (8x 6-bit scale + 8x 6-bit min), u8 qs[128]
+// Q5_K: 176 B = the Q4_K header, u8 qh[32] (fifth bits: bit j of qh[l] belongs to sub-block j), u8 qs[128]
 // Q6_K: 210 B = u8 ql[128], u8 qh[64], i8 scales[16], f16 d
 constexpr int Q8_0_BYTES = 34;
 constexpr int Q4_K_BYTES = 144;
+constexpr int Q5_K_BYTES = 176;
 constexpr int Q6_K_BYTES = 210;
 
 __host__ __device__ inline int block_elems(int dtype)
@@ -27,7 +29,7 @@ __host__ __device__ inline int block_elems(int dtype)
     switch (dtype) {
     case PMOE_F32: case PMOE_F16: case PMOE_BF16: return 1;
     case PMOE_Q8_0: return QK8_0;
-    case PMOE_Q4_K: case PMOE_Q6_K: return QK_K;
+    case PMOE_Q4_K: case PMOE_Q5_K: case PMOE_Q6_K: return QK_K;
     default: return 0;
     }
 }
@@ -39,6 +41,7 @@ __host__ __device__ inline int block_bytes(int dtype)
     case PMOE_F16: case PMOE_BF16: return 2;
     case PMOE_Q8_0: return Q8_0_BYTES;
     case PMOE_Q4_K: return Q4_K_BYTES;
+    case PMOE_Q5_K: return Q5_K_BYTES;
     case PMOE_Q6_K: return Q6_K_BYTES;
     default: return 0;
     }
@@ -51,8 +54,8 @@ __host__ __device__ inline size_t row_bytes(int dtype, size_t cols)
 }
 
 // Activation blocks follow the weight type's dot type on the reference CPU path:
-// Q4_K, Q6_K -> Q8_K (256 values, f32 scale, 16 sums of 16); Q8_0 -> Q8_0 (32 values, f16 scale).
-__host__ __device__ inline bool is_kquant(int dtype) { return dtype == PMOE_Q4_K || dtype == PMOE_Q6_K; }
+// Q4_K, Q5_K, Q6_K -> Q8_K (256 values, f32 scale, 16 sums of 16); Q8_0 -> Q8_0 (32 values, f16 scale).
+__host__ __device__ inline bool is_kquant(int dtype) { return dtype == PMOE_Q4_K || dtype == PMOE_Q5_K || dtype == PMOE_Q6_K; }
 
 // ---------------------------------------------------------------- status word
 // Kernels never trap: a failed range check or an expired wait records a code here.

@@ -67,6 +67,11 @@ template <> struct Tr<PMOE_Q4_K> {
     static constexpr bool KQ = true;
     using Act = ActQ4K;
 };
+template <> struct Tr<PMOE_Q5_K> {   // same split of a block over lanes as Q4_K
+    static constexpr int UNIT = 64;
+    static constexpr bool KQ = true;
+    using Act = ActQ4K;
+};
 template <> struct Tr<PMOE_Q6_K> {
     static constexpr int UNIT = 64;
     static constexpr bool KQ = true;
@@ -90,6 +95,7 @@ template <> __device__ inline void zero_act<PMOE_Q4_K>(ActQ4K &o)
     for (int i = 0; i < 16; i++) o.a[i] = 0;
     o.dx = 0.f; o.bs_lo = 0; o.bs_hi = 0;
 }
+template <> __device__ inline void zero_act<PMOE_Q5_K>(ActQ4K &o) { zero_act<PMOE_Q4_K>(o); }
 template <> __device__ inline void zero_act<PMOE_Q6_K>(ActQ6K &o)
 {
 #pragma unroll
@@ -126,6 +132,11 @@ template <> __device__ inline void load_act<PMOE_Q4_K>(const QAct &q, size_t row
     const short4 bs = *reinterpret_cast<const short4 *>(q.bsums + row * (K / 16) + 16 * b + 4 * qd);
     o.bs_lo = (int)bs.x + (int)bs.y;
     o.bs_hi = (int)bs.z + (int)bs.w;
+}
+
+template <> __device__ inline void load_act<PMOE_Q5_K>(const QAct &q, size_t row, int K, int u, ActQ4K &o)
+{
+    load_act<PMOE_Q4_K>(q, row, K, u, o);
 }
 
 // Unit u of a Q6_K row: block u/4, 128-element half (u/2)%2, and inside the half the 16 positions
@@ -220,6 +231,61 @@ template <> struct Dot<PMOE_Q4_K> {
             const int isum16 = sc0_16 * (s_lo + s_lo2) + sc1 * (s_hi16 + s_hi16b);
             const int imin = m0 * act[t].bs_lo + m1 * act[t].bs_hi;
             acc[t] += act[t].dx * (d16 * (float)isum16 - dmin * (float)imin);
+        }
+    }
+};
+
+// Q5_K: the Q4_K unit with the fifth bit of each quant taken from qh (bit 2*qd for the low-nibble
+// sub-block, 2*qd+1 for the high-nibble one).  With five bits the high quants no longer fit a byte
+// in place, so they are shifted down.
+template <> struct Dot<PMOE_Q5_K> {
+    struct Pre {
+        int hdr_off, q_off, sh, hi, hsh;
+    };
+    __device__ static inline Pre pre(int u)
+    {
+        const int qd = u & 3, blk = (u >> 2) * Q5_K_BYTES;
+        return Pre{blk, blk + 48 + 32 * qd, 16 * (qd & 1), qd >> 1, 2 * qd};
+    }
+    template <int CNT, bool A4 = true>
+    __device__ static inline void run(const uint8_t *row, const Pre &p, const ActQ4K *act, float *acc)
+    {
+        const uint4 hdr = *reinterpret_cast<const uint4 *>(row + p.hdr_off);
+        const uint4 ha = *reinterpret_cast<const uint4 *>(row + p.hdr_off + 16);
+        const uint4 hb = *reinterpret_cast<const uint4 *>(row + p.hdr_off + 32);
+        const uint4 qa = *reinterpret_cast<const uint4 *>(row + p.q_off);
+        const uint4 qb = *reinterpret_cast<const uint4 *>(row + p.q_off + 16);
+        const float d = half_bits_to_float((uint16_t)(hdr.x & 0xffffu));
+        const float dmin = half_bits_to_float((uint16_t)(hdr.x >> 16));
+        const uint32_t a0 = hdr.y >> p.sh, a1 = hdr.z >> p.sh, a2 = hdr.w >> p.sh;
+        const uint32_t sc_lo = a0 & 0x3F3Fu, m_lo = a1 & 0x3F3Fu;
+        const uint32_t sc_hi = (a2 & 0x0F0Fu) | ((a0 >> 2) & 0x3030u);
+        const uint32_t m_hi = ((a2 >> 4) & 0x0F0Fu) | ((a1 >> 2) & 0x3030u);
+        const uint32_t scp = p.hi ? sc_hi : sc_lo, mp = p.hi ? m_hi : m_lo;
+        const int sc0 = (int)(scp & 0xFFu), sc1 = (int)(scp >> 8) & 0xFF;
+        const int m0 = (int)(mp & 0xFFu), m1 = (int)(mp >> 8) & 0xFF;
+        const uint32_t w[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+        const uint32_t h[8] = {ha.x, ha.y, ha.z, ha.w, hb.x, hb.y, hb.z, hb.w};
+        uint32_t lo[8], hi[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const uint32_t t = h[i] >> p.hsh;   // bit 0 of each byte: low sub-block, bit 1: high sub-block
+            lo[i] = (w[i] & 0x0F0F0F0Fu) | ((t << 4) & 0x10101010u);
+            hi[i] = ((w[i] >> 4) & 0x0F0F0F0Fu) | ((t << 3) & 0x10101010u);
+        }
+#pragma unroll
+        for (int t = 0; t < CNT; t++) {
+            int s_lo = 0, s_lo2 = 0, s_hi = 0, s_hi2 = 0;
+#pragma unroll
+            for (int i = 0; i < 8; i += 2) {
+                s_lo = dp4a_us(lo[i], act[t].a[i], s_lo);
+                s_hi = dp4a_us(hi[i], act[t].a[8 + i], s_hi);
+                s_lo2 = dp4a_us(lo[i + 1], act[t].a[i + 1], s_lo2);
+                s_hi2 = dp4a_us(hi[i + 1], act[t].a[9 + i], s_hi2);
+            }
+            const int isum = sc0 * (s_lo + s_lo2) + sc1 * (s_hi + s_hi2);
+            const int imin = m0 * act[t].bs_lo + m1 * act[t].bs_hi;
+            acc[t] += act[t].dx * (d * (float)isum - dmin * (float)imin);
         }
     }
 };
@@ -379,7 +445,8 @@ template <int DT, int NMAT> struct Cfg {
     static constexpr int UPL = UNITS / LPR;           // units per lane
     static constexpr int GROUPS = 32 / LPR;           // rows a warp works on at once
     static constexpr int ROW_BYTES = K / (DT == PMOE_Q8_0 ? QK8_0 : QK_K) *
-                                     (DT == PMOE_Q8_0 ? Q8_0_BYTES : DT == PMOE_Q4_K ? Q4_K_BYTES : Q6_K_BYTES);
+                                     (DT == PMOE_Q8_0 ? Q8_0_BYTES : DT == PMOE_Q4_K ? Q4_K_BYTES
+                                      : DT == PMOE_Q5_K ? Q5_K_BYTES : Q6_K_BYTES);
     static constexpr int ROWS = floor_pow2(STAGE_BYTES / (ROW_BYTES * NMAT));  // rows of each matrix per item
     static constexpr int ITEM_BYTES = ROWS * ROW_BYTES;                        // per matrix
     // tokens per pass: bounded by the activation registers a lane keeps (16 words per token for Q4_K and Q6_K, 4 for Q8_0)
@@ -962,8 +1029,8 @@ __global__ void __launch_bounds__(GEMV_THREADS, 2) k_expert_gemv(const GemvArgs 
 // ---------------------------------------------------------------- host-side dispatch
 bool gemv_supported(int dtype, int K, int rows, const char **why)
 {
-    if (dtype != PMOE_Q4_K && dtype != PMOE_Q6_K && dtype != PMOE_Q8_0) {
-        *why = "expert weights must be Q4_K, Q6_K or Q8_0";
+    if (dtype != PMOE_Q4_K && dtype != PMOE_Q5_K && dtype != PMOE_Q6_K && dtype != PMOE_Q8_0) {
+        *why = "expert weights must be Q4_K, Q5_K, Q6_K or Q8_0";
         return false;
     }
     if (!((K == 2048 && rows == 512) || (K == 512 && rows == 2048))) {
@@ -1003,6 +1070,7 @@ static cudaError_t launch_gemv_s(const GemvArgs &A, int dt_s, cudaStream_t s)
     switch (dt_s) {
     case 0: return launch_gemv_t<DT_R, 0, NMAT>(A, s);
     case PMOE_Q4_K: return launch_gemv_t<DT_R, PMOE_Q4_K, NMAT>(A, s);
+    case PMOE_Q5_K: return launch_gemv_t<DT_R, PMOE_Q5_K, NMAT>(A, s);
     case PMOE_Q6_K:
         // a down matrix shared by three or more tokens: the four-tokens-per-pass variant
         if constexpr (NMAT == 1) {
@@ -1019,6 +1087,7 @@ static cudaError_t launch_gemv(const GemvArgs &A, int dt_r, int dt_s, cudaStream
 {
     switch (dt_r) {
     case PMOE_Q4_K: return launch_gemv_s<PMOE_Q4_K, NMAT>(A, dt_s, s);
+    case PMOE_Q5_K: return launch_gemv_s<PMOE_Q5_K, NMAT>(A, dt_s, s);
     case PMOE_Q6_K:
         // down projection of a call with more than about one token per expert: experts with
         // three or four tokens are common, and the variant that takes four per pass wins
@@ -1141,6 +1210,7 @@ cudaError_t launch_qmatmul(int dtype, const void *w, int rows, int K, const floa
     dim3 grid((rows + 3) / 4, (m + TG - 1) / TG);
     const uint8_t *wb = (const uint8_t *)w;
     if (dtype == PMOE_Q4_K) k_qmatmul<PMOE_Q4_K><<<grid, 128, 0, s>>>(wb, rows, K, a, m, y);
+    else if (dtype == PMOE_Q5_K) k_qmatmul<PMOE_Q5_K><<<grid, 128, 0, s>>>(wb, rows, K, a, m, y);
     else if (dtype == PMOE_Q6_K) k_qmatmul<PMOE_Q6_K><<<grid, 128, 0, s>>>(wb, rows, K, a, m, y);
     else k_qmatmul<PMOE_Q8_0><<<grid, 128, 0, s>>>(wb, rows, K, a, m, y);
     count_launch(2);

@@ -1,11 +1,11 @@
 """Seeded synthetic MoE layers in GGUF block formats.
 
 The reference publishes no benchmark data for this path, so the workloads are synthetic:
-normal weights N(0, 0.02) quantised to Q4_K / Q6_K / Q8_0 blocks, a float router and normal
+normal weights N(0, 0.02) quantised to Q4_K / Q5_K / Q6_K / Q8_0 blocks, a float router and normal
 inputs.  The quantisers here are plain torch tensor code (CPU or CUDA) used only to
 manufacture valid blocks; the library and the CPU oracle both consume the resulting bytes,
 so their quality does not enter any comparison.  Q8_0 follows the ggml reference quantiser;
-Q4_K and Q6_K are simple min/max quantisers.
+Q4_K, Q5_K and Q6_K are simple min/max quantisers.
 """
 from __future__ import annotations
 
@@ -14,7 +14,7 @@ from typing import Dict, Optional
 
 import torch
 
-from ._lib import Q4_K, Q6_K, Q8_0
+from ._lib import Q4_K, Q5_K, Q6_K, Q8_0
 
 PRESETS = {
     # name: (gate/up dtype, down dtype, shared dtype)
@@ -24,6 +24,8 @@ PRESETS = {
     "q4k_q6k_all": (Q4_K, Q6_K, (Q4_K, Q6_K)),  # shared expert quantised like the routed ones
     "q8_0": (Q8_0, Q8_0, Q8_0),
     "q6k": (Q6_K, Q6_K, Q6_K),
+    "q5k": (Q5_K, Q5_K, Q5_K),
+    "q5k_m": (Q5_K, Q6_K, Q8_0),        # Q5_K_M-style mix
 }
 
 
@@ -68,6 +70,38 @@ def quantize_q4_k(x: torch.Tensor) -> torch.Tensor:
     return torch.cat([_half_bytes(d16), _half_bytes(m16), sb.to(torch.uint8), qs], dim=1).reshape(-1)
 
 
+def quantize_q5_k(x: torch.Tensor) -> torch.Tensor:
+    xb = x.reshape(-1, 8, 32).float()
+    nb = xb.shape[0]
+    mn = xb.amin(-1).clamp(max=0)
+    mx = xb.amax(-1).clamp(min=0)
+    scales = (mx - mn) / 31.0
+    mins = -mn
+    max_scale = scales.amax(-1)
+    max_min = mins.amax(-1)
+    inv_s = torch.where(max_scale > 0, 63.0 / max_scale, torch.zeros_like(max_scale))
+    inv_m = torch.where(max_min > 0, 63.0 / max_min, torch.zeros_like(max_min))
+    ls = torch.round(inv_s[:, None] * scales).clamp(0, 63).to(torch.int32)
+    lm = torch.round(inv_m[:, None] * mins).clamp(0, 63).to(torch.int32)
+    d16 = (max_scale / 63.0).to(torch.float16)
+    m16 = (max_min / 63.0).to(torch.float16)
+    dq = d16.float()[:, None] * ls.float()
+    mq = m16.float()[:, None] * lm.float()
+    q = torch.where(dq[..., None] > 0, torch.round((xb + mq[..., None]) / dq[..., None].clamp(min=1e-30)),
+                    torch.zeros_like(xb)).clamp(0, 31).to(torch.uint8)
+    q = q.reshape(nb, 4, 2, 32)   # [block, 64-group, low/high sub-block, l]
+    qs = ((q[:, :, 0, :] & 0xF) | ((q[:, :, 1, :] & 0xF) << 4)).reshape(nb, 128)
+    qh = torch.zeros((nb, 32), dtype=torch.uint8, device=x.device)
+    for g in range(4):   # bit 2g: low sub-block of group g, bit 2g+1: its high sub-block
+        qh |= (q[:, g, 0, :] >> 4) << (2 * g)
+        qh |= (q[:, g, 1, :] >> 4) << (2 * g + 1)
+    sb = torch.empty((nb, 12), dtype=torch.int32, device=x.device)
+    sb[:, 0:4] = ls[:, 0:4] | ((ls[:, 4:8] >> 4) << 6)
+    sb[:, 4:8] = lm[:, 0:4] | ((lm[:, 4:8] >> 4) << 6)
+    sb[:, 8:12] = (ls[:, 4:8] & 0xF) | ((lm[:, 4:8] & 0xF) << 4)
+    return torch.cat([_half_bytes(d16), _half_bytes(m16), sb.to(torch.uint8), qh, qs], dim=1).reshape(-1)
+
+
 def quantize_q6_k(x: torch.Tensor) -> torch.Tensor:
     xb = x.reshape(-1, 16, 16).float()
     nb = xb.shape[0]
@@ -85,7 +119,7 @@ def quantize_q6_k(x: torch.Tensor) -> torch.Tensor:
     return torch.cat([ql, qh, s.to(torch.int8).view(torch.uint8), _half_bytes(d16)], dim=1).reshape(-1)
 
 
-_QUANT = {Q8_0: quantize_q8_0, Q4_K: quantize_q4_k, Q6_K: quantize_q6_k}
+_QUANT = {Q8_0: quantize_q8_0, Q4_K: quantize_q4_k, Q5_K: quantize_q5_k, Q6_K: quantize_q6_k}
 
 
 def quantize(x: torch.Tensor, dtype: int, chunk_elems: int = 1 << 26) -> torch.Tensor:

@@ -3,7 +3,7 @@
 The Rust reference cannot be built or run here (no cargo; its candle fork is not vendored) and
 holds no golden vectors for this path, so the block codecs are pinned against an independent
 implementation instead: the `gguf` Python package (gguf-py 0.19, the GGUF project's own
-reader).  For seeded random Q4_K / Q6_K / Q8_0 blocks (plus edge blocks: zero scales, largest
+reader).  For seeded random Q4_K / Q5_K / Q6_K / Q8_0 blocks (plus edge blocks: zero scales, largest
 and negative f16 scales, all-ones payload) the file stores the raw block bytes and gguf-py's
 dequantised f32 output, and for Q8_0 also gguf-py's quantisation of a seeded normal vector.
 
@@ -45,6 +45,11 @@ def main():
     w = (rng.standard_normal(32 * 64) * 0.02).astype(np.float32)
     out["q8_0_quant_in"] = w
     out["q8_0_quant_blocks"] = quants.quantize(w, T.Q8_0).reshape(-1)
+    # Q5_K joined later: its own generator, so that the entries above keep their values
+    rng5 = np.random.default_rng(20240608)
+    raw = blocks(rng5, 48, 176, (0, 2))
+    out["q5_k_blocks"] = raw
+    out["q5_k_dequant"] = quants.dequantize(raw.reshape(-1), T.Q5_K).astype(np.float32).reshape(-1)
     np.savez_compressed(OUT, **out)
     print("wrote", OUT, {k: v.shape for k, v in out.items()})
 

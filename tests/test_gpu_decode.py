@@ -24,12 +24,12 @@ from oracle import pmoe_oracle as po
 DEV = "cuda:0"
 
 
-@pytest.mark.parametrize("dtype", [pm.Q4_K, pm.Q6_K, pm.Q8_0])
+@pytest.mark.parametrize("dtype", [pm.Q4_K, pm.Q5_K, pm.Q6_K, pm.Q8_0])
 def test_dequantize_bit_exact(dtype):
     rng = np.random.default_rng(7)
     nb, ts, bs = 512, pm.type_size(dtype), pm.block_size(dtype)
     raw = rng.integers(0, 256, size=(nb, ts), dtype=np.uint8)
-    offs = {pm.Q4_K: (0, 2), pm.Q6_K: (208,), pm.Q8_0: (0,)}[dtype]
+    offs = {pm.Q4_K: (0, 2), pm.Q5_K: (0, 2), pm.Q6_K: (208,), pm.Q8_0: (0,)}[dtype]
     for off in offs:  # keep the f16 scales finite; include zero, negative and large ones
         v = raw[:, off:off + 2].copy().view(np.float16)
         v[~np.isfinite(v)] = np.float16(-0.75)
@@ -38,7 +38,7 @@ def test_dequantize_bit_exact(dtype):
         raw[:, off:off + 2] = v.view(np.uint8)
     raw[2] = 0
     raw[3, :] = 255
-    if dtype == pm.Q4_K:
+    if dtype in (pm.Q4_K, pm.Q5_K):
         raw[3, 0:4] = np.array([1.0, 1.0], np.float16).view(np.uint8)
     elif dtype == pm.Q6_K:
         raw[3, 208:210] = np.array([1.0], np.float16).view(np.uint8)
@@ -92,6 +92,8 @@ CASES = [
     ("q6k", 16, 2, 3, torch.float32),
     ("q4k_q6k", 4, 1, 2, torch.float32),
     ("q4k_m", 32, 4, 130, torch.float32),     # many tokens per expert: several token passes
+    ("q5k", 16, 3, 5, torch.float32),
+    ("q5k_m", 64, 6, 40, torch.bfloat16),
 ]
 
 
@@ -254,6 +256,7 @@ def test_add_rms_norm():
 
 
 @pytest.mark.parametrize("dtype,rows,cols", [(pm.Q4_K, 64, 2048), (pm.Q6_K, 128, 512), (pm.Q8_0, 32, 1024),
+                                             (pm.Q5_K, 48, 1024),
                                              (pm.Q6_K, 33, 256)])   # 210-byte rows: every other row starts 2 bytes off a word
 def test_qmatmul_entry_point(dtype, rows, cols):
     rng = np.random.default_rng(11)
