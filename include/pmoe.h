@@ -123,6 +123,9 @@ int pmoe_forward(pmoe_layer *layer, const void *x, int x_dtype, int n, void *out
  * The same call with HOST buffers: copies x to the device, runs the block, copies the
  * results back and synchronises the stream.  This is the shape of the reference's own
  * offload paths (Tensor::to_device around the expert computation, ops.rs:188-198,291-293).
+ * From the third call with the same n and dtypes on, the kernels between the two copies are
+ * replayed from a CUDA graph the handle recorded (PMOE_HOST_GRAPH=0 in the environment keeps
+ * direct launches).
  */
 int pmoe_forward_host(pmoe_layer *layer, const void *x_host, int x_dtype, int n, void *out_host,
                       int out_dtype, float *logits_host, uint32_t *idx_host, float *w_host,

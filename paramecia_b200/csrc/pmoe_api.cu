@@ -80,6 +80,14 @@ struct pmoe_layer {
     uint32_t *st_idx = nullptr;
     float *st_w = nullptr;
     // per-phase CUDA events of the last traced call (pmoe_layer_trace)
+    // pmoe_forward_host replays the kernel chain of its last shape as a CUDA graph (the chain works on
+    // the handle's own staging buffers, so its arguments do not change from call to call)
+    cudaStream_t cap_stream = nullptr;
+    cudaGraphExec_t hg_exec = nullptr;
+    int hg_n = -1, hg_x_dtype = 0, hg_out_dtype = 0, hg_flags = 0, hg_launches = 0;
+    int hg_seen_n = -1, hg_seen_x = 0, hg_seen_out = 0, hg_seen_flags = 0;
+    void *hg_out = nullptr, *hg_seen_out_ptr = nullptr;   // where the chain writes the block output
+    bool hg_off = false;
     // rows the shared expert serves in the next run_experts call; count < 0 = every row
     int req_sh_begin = 0, req_sh_count = -1;
     bool trace = false;
@@ -410,6 +418,8 @@ int pmoe_layer_destroy(pmoe_layer *L)
     DeviceGuard guard(L->device);
     cudaDeviceSynchronize();
     for (void *p : L->owned) cudaFree(p);
+    if (L->hg_exec) cudaGraphExecDestroy(L->hg_exec);
+    if (L->cap_stream) cudaStreamDestroy(L->cap_stream);
     for (int i = 0; i < PMOE_TRACE_PHASES; i++) {
         if (L->ev0[i]) cudaEventDestroy(L->ev0[i]);
         if (L->ev1[i]) cudaEventDestroy(L->ev1[i]);
@@ -559,10 +569,73 @@ int pmoe_forward_host(pmoe_layer *L, const void *x_host, int x_dtype, int n, voi
     const size_t xin = (size_t)n * d.H * (x_dtype == PMOE_F32 ? 4 : 2);
     const size_t xout = (size_t)n * d.H * (out_dtype == PMOE_F32 ? 4 : 2);
     CU(cudaMemcpyAsync(L->st_x, x_host, xin, cudaMemcpyHostToDevice, s));
-    rc = pmoe_forward(L, L->st_x, x_dtype, n, L->st_out, out_dtype, logits_host ? L->st_logits : nullptr,
-                      idx_host ? L->st_idx : nullptr, w_host ? L->st_w : nullptr, stream);
-    if (rc) return rc;
-    CU(cudaMemcpyAsync(out_host, L->st_out, xout, cudaMemcpyDeviceToHost, s));
+    float *lg = logits_host ? L->st_logits : nullptr;
+    uint32_t *ix = idx_host ? L->st_idx : nullptr;
+    float *wt = w_host ? L->st_w : nullptr;
+    // Pinned (mapped) output memory is written by the combine kernel itself, without a copy afterwards.
+    // (looked up on every call: an address can change hands between pinned and pageable memory)
+    void *out_dev = L->st_out;
+    {
+        cudaPointerAttributes pa{};
+        if (cudaPointerGetAttributes(&pa, out_host) == cudaSuccess && pa.type == cudaMemoryTypeHost && pa.devicePointer &&
+            !((uintptr_t)pa.devicePointer & 15))
+            out_dev = pa.devicePointer;
+        cudaGetLastError();
+    }
+    // The chain between the two copies: first call of a shape runs directly, the second records it
+    // into a graph, later ones replay the graph (PMOE_HOST_GRAPH=0 keeps direct launches).
+    const int flags = (lg ? 1 : 0) | (ix ? 2 : 0) | (wt ? 4 : 0);
+    static const bool graphs_on = !(getenv("PMOE_HOST_GRAPH") && atoi(getenv("PMOE_HOST_GRAPH")) == 0);
+    bool done = false;
+    if (graphs_on && !L->hg_off && !L->trace) {
+        const bool cached = L->hg_exec && L->hg_n == n && L->hg_x_dtype == x_dtype && L->hg_out_dtype == out_dtype &&
+                            L->hg_flags == flags && L->hg_out == out_dev;
+        const bool seen = L->hg_seen_n == n && L->hg_seen_x == x_dtype && L->hg_seen_out == out_dtype &&
+                          L->hg_seen_flags == flags && L->hg_seen_out_ptr == out_dev;
+        if (!cached && seen) {
+            if (!L->cap_stream && cudaStreamCreateWithFlags(&L->cap_stream, cudaStreamNonBlocking) != cudaSuccess) {
+                cudaGetLastError();
+                L->hg_off = true;
+            }
+            if (!L->hg_off) {
+                cudaGraph_t graph = nullptr;
+                cudaGraphExec_t exec = nullptr;
+                const unsigned long long before = pmoe_launch_count();
+                bool ok = cudaStreamBeginCapture(L->cap_stream, cudaStreamCaptureModeThreadLocal) == cudaSuccess;
+                if (ok) {
+                    const int frc = pmoe_forward(L, L->st_x, x_dtype, n, out_dev, out_dtype, lg, ix, wt, L->cap_stream);
+                    const cudaError_t ee = cudaStreamEndCapture(L->cap_stream, &graph);
+                    ok = frc == PMOE_OK && ee == cudaSuccess && graph != nullptr;
+                }
+                if (ok) ok = cudaGraphInstantiate(&exec, graph, 0) == cudaSuccess;
+                if (graph) cudaGraphDestroy(graph);
+                if (ok) {
+                    if (L->hg_exec) cudaGraphExecDestroy(L->hg_exec);
+                    L->hg_exec = exec;
+                    L->hg_n = n; L->hg_x_dtype = x_dtype; L->hg_out_dtype = out_dtype; L->hg_flags = flags;
+                    L->hg_out = out_dev;
+                    L->hg_launches = (int)(pmoe_launch_count() - before);
+                    count_launch(-L->hg_launches);   // recorded, not run
+                } else {
+                    cudaGetLastError();
+                    L->hg_off = true;   // this handle keeps direct launches
+                }
+            }
+        }
+        if (!L->hg_off && L->hg_exec && L->hg_n == n && L->hg_x_dtype == x_dtype && L->hg_out_dtype == out_dtype &&
+            L->hg_flags == flags && L->hg_out == out_dev) {
+            CU(cudaGraphLaunch(L->hg_exec, s));
+            count_launch(L->hg_launches);
+            done = true;
+        }
+        L->hg_seen_n = n; L->hg_seen_x = x_dtype; L->hg_seen_out = out_dtype; L->hg_seen_flags = flags;
+        L->hg_seen_out_ptr = out_dev;
+    }
+    if (!done) {
+        rc = pmoe_forward(L, L->st_x, x_dtype, n, out_dev, out_dtype, lg, ix, wt, stream);
+        if (rc) return rc;
+    }
+    if (out_dev == L->st_out) CU(cudaMemcpyAsync(out_host, L->st_out, xout, cudaMemcpyDeviceToHost, s));
     if (logits_host) CU(cudaMemcpyAsync(logits_host, L->st_logits, (size_t)n * d.E * 4, cudaMemcpyDeviceToHost, s));
     if (idx_host) CU(cudaMemcpyAsync(idx_host, L->st_idx, (size_t)n * d.k * 4, cudaMemcpyDeviceToHost, s));
     if (w_host) CU(cudaMemcpyAsync(w_host, L->st_w, (size_t)n * d.k * 4, cudaMemcpyDeviceToHost, s));

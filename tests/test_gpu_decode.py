@@ -226,6 +226,23 @@ def test_deterministic_and_host_entry_point():
     ol = oracle_layer(t)
     _, want_logits, want_idx, _ = ol.forward(x.float().numpy())
     assert np.array_equal(idx.numpy().astype(np.uint32), want_idx)
+    # repeated calls of one shape go through the recorded graph; another shape in between drops back
+    # to direct launches; every result is the same
+    x2 = seeded_x(48, 2048, 5, torch.bfloat16)
+    a2 = blk.forward(x2.to(DEV)).float().cpu().numpy()
+    for i in range(5):
+        xi, ai = (x, a) if i % 2 == 0 else (x2, a2)
+        assert np.array_equal(blk.forward_host(xi).float().numpy().view(np.uint32), ai.view(np.uint32))
+    short = blk.forward_host(x[:7])
+    assert np.array_equal(short.float().numpy().view(np.uint32), blk.forward(x[:7].to(DEV)).float().cpu().numpy().view(np.uint32))
+    assert np.array_equal(blk.forward_host(x).float().numpy().view(np.uint32), a.view(np.uint32))
+    pinned = torch.empty((48, 2048), dtype=torch.bfloat16).pin_memory()   # written by the kernel, no copy back
+    for _ in range(3):
+        pinned.zero_()
+        blk.forward_host(x, out_host=pinned)
+        assert np.array_equal(pinned.float().numpy().view(np.uint32), a.view(np.uint32))
+    out_h2, (lg2, idx2, w2) = blk.forward_host(x, with_stats=True)
+    assert np.array_equal(idx2.numpy(), idx.numpy()) and np.array_equal(lg2.numpy(), lg.numpy())
     blk.status()
 
 
