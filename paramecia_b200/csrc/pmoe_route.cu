@@ -375,20 +375,61 @@ cudaError_t launch_topk(const LayerDev &L, const Workspace &ws, const float *log
 
 // ---------------------------------------------------------------- grouping by expert
 // Counting sort of the n*k (token, slot) pairs by local expert id in one CTA:
-// counts through shared-memory atomics, an exclusive scan, then the scatter.  The order of
+// counts through shared-memory atomics, a scan, then the scatter.  The order of
 // pairs inside one expert's list depends on atomic arrival order; no result depends on it
 // (every pair's rows are computed on their own and combined in slot order).
 constexpr int GROUP_THREADS = 1024;
+
+// inclusive scan of five integers per thread across the CTA: shuffles inside a warp, one pass
+// over the 32 warp totals, three barriers in all
+struct Scan5 {
+    int v[5];
+};
+
+__device__ inline Scan5 block_scan5(Scan5 x, int (*warp_tot)[5], int tid)
+{
+    const int lane = tid & 31, warp = tid >> 5;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+#pragma unroll
+        for (int i = 0; i < 5; i++) {
+            const int y = __shfl_up_sync(0xffffffffu, x.v[i], off);
+            if (lane >= off) x.v[i] += y;
+        }
+    }
+    if (lane == 31) {
+#pragma unroll
+        for (int i = 0; i < 5; i++) warp_tot[warp][i] = x.v[i];
+    }
+    __syncthreads();
+    if (warp == 0) {
+        Scan5 t;
+#pragma unroll
+        for (int i = 0; i < 5; i++) t.v[i] = warp_tot[lane][i];
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+#pragma unroll
+            for (int i = 0; i < 5; i++) {
+                const int y = __shfl_up_sync(0xffffffffu, t.v[i], off);
+                if (lane >= off) t.v[i] += y;
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 5; i++) warp_tot[lane][i] = t.v[i];   // inclusive totals up to and including warp `lane`
+    }
+    __syncthreads();
+    if (warp > 0) {
+#pragma unroll
+        for (int i = 0; i < 5; i++) x.v[i] += warp_tot[warp - 1][i];
+    }
+    return x;
+}
 
 __global__ void __launch_bounds__(GROUP_THREADS) k_group(const uint32_t *__restrict__ idx, int npairs, int base,
                                                          int E_local, Groups g)
 {
     __shared__ int cnt[1024];
-    __shared__ int scan[1024];
-    __shared__ int act_scan[1024];
-    __shared__ int cost_scan[1024];
-    __shared__ int tile_scan[1024];
-    __shared__ int wide_scan[1024];
+    __shared__ int warp_tot[32][5];
     const int tid = threadIdx.x;
     cnt[tid] = 0;
     pdl_wait();
@@ -401,51 +442,36 @@ __global__ void __launch_bounds__(GROUP_THREADS) k_group(const uint32_t *__restr
         g.pos[p] = pos;
     }
     __syncthreads();
-    int c = tid < E_local ? cnt[tid] : 0;
-    int flag = c > 0 ? 1 : 0;
+    const int c = tid < E_local ? cnt[tid] : 0;
+    const int flag = c > 0 ? 1 : 0;
     const int cost = (c + GEMV_TG - 1) / GEMV_TG;
-    scan[tid] = c;
-    act_scan[tid] = flag;
     const int tiles = (c + PREFILL_NT - 1) / PREFILL_NT;
     const int wcost = (c + GEMV_TG_WIDE - 1) / GEMV_TG_WIDE;
-    cost_scan[tid] = cost;
-    tile_scan[tid] = tiles;
-    wide_scan[tid] = wcost;
-    __syncthreads();
-    for (int off = 1; off < GROUP_THREADS; off <<= 1) {  // Hillis-Steele inclusive scans
-        int a = tid >= off ? scan[tid - off] : 0;
-        int b = tid >= off ? act_scan[tid - off] : 0;
-        int d = tid >= off ? cost_scan[tid - off] : 0;
-        int f = tid >= off ? tile_scan[tid - off] : 0;
-        int gw = tid >= off ? wide_scan[tid - off] : 0;
-        __syncthreads();
-        scan[tid] += a;
-        act_scan[tid] += b;
-        cost_scan[tid] += d;
-        tile_scan[tid] += f;
-        wide_scan[tid] += gw;
-        __syncthreads();
-    }
-    int excl = scan[tid] - c;
+    Scan5 in;
+    in.v[0] = c; in.v[1] = flag; in.v[2] = cost; in.v[3] = tiles; in.v[4] = wcost;
+    const Scan5 sc = block_scan5(in, warp_tot, tid);   // inclusive
+    const int excl = sc.v[0] - c;
     if (tid < E_local) {
         g.count[tid] = c;
         g.offset[tid] = excl;
         if (flag) {
-            g.active[act_scan[tid] - 1] = tid;
-            g.cost_prefix[act_scan[tid] - 1] = cost_scan[tid] - cost;
-            g.cost_prefix_wide[act_scan[tid] - 1] = wide_scan[tid] - wcost;
-            g.tile_prefix[act_scan[tid] - 1] = tile_scan[tid] - tiles;
-            for (int i = 0; i < tiles; i++) g.tile_table[tile_scan[tid] - tiles + i] = make_int2(tid, i);
+            const int slot = sc.v[1] - 1;
+            g.active[slot] = tid;
+            g.cost_prefix[slot] = sc.v[2] - cost;
+            g.cost_prefix_wide[slot] = sc.v[4] - wcost;
+            g.tile_prefix[slot] = sc.v[3] - tiles;
+            for (int i = 0; i < tiles; i++) g.tile_table[sc.v[3] - tiles + i] = make_int2(tid, i);
         }
     }
     if (tid == GROUP_THREADS - 1) {
-        g.offset[E_local] = scan[tid];
-        *g.n_active = act_scan[tid];
-        g.cost_prefix[act_scan[tid]] = cost_scan[tid];
-        g.cost_prefix_wide[act_scan[tid]] = wide_scan[tid];
-        g.tile_prefix[act_scan[tid]] = tile_scan[tid];
+        g.offset[E_local] = sc.v[0];
+        *g.n_active = sc.v[1];
+        g.cost_prefix[sc.v[1]] = sc.v[2];
+        g.cost_prefix_wide[sc.v[1]] = sc.v[4];
+        g.tile_prefix[sc.v[1]] = sc.v[3];
     }
-    cnt[tid] = excl;  // reuse as the per-expert base
+    __syncthreads();   // every thread has read its count
+    cnt[tid] = excl;   // reuse as the per-expert base
     __syncthreads();
     for (int p = tid; p < npairs; p += GROUP_THREADS) {
         int pos = g.pos[p];
