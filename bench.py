@@ -180,6 +180,9 @@ def reference_arm(args, rank):
     print(json.dumps(line), flush=True)
 
 
+NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 439.356672 / 429.555712   # gate/up launch, batch 64 (see profiles/)
+
+
 def prefill_main(args):
     """BASELINE config 3 on one GPU: 4096 bf16 tokens through one Q4_K / Q6_K block whose router carries the
     bias 2*ln(1/rank_e) (rank = seeded permutation), so a dozen experts take most tokens.  Reports tokens/s and the
@@ -458,8 +461,12 @@ def main():
     roofline = None
     if phase_ms.get("gate_up"):
         ach = gu_bytes / (phase_ms["gate_up"] * 1e-3) / 1e9
+        # DRAM traffic of this launch: the ncu capture of the same workload (profiles/
+        # k_expert_gemv_decode_batch64_ncu_full.md: 439.4 MB read + written against 429.6 MB algorithmic,
+        # growing in proportion to the experts hit) scaled to this run's algorithmic bytes
         roofline = dict(bound="hbm", kernel="k_expert_gemv<gate+up>", achieved=ach, peak=hbm_peak, unit="GB/s",
-                        frac=ach / hbm_peak, peak_kind=peak_kind, traffic=None,
+                        frac=ach / hbm_peak, peak_kind=peak_kind, traffic=gu_bytes * NCU_TRAFFIC_PER_ALGORITHMIC_BYTE,
+                        traffic_kind="ncu dram__bytes_read+write of a captured launch, scaled by algorithmic bytes",
                         algorithmic_bytes_per_launch=gu_bytes, us_per_launch=phase_ms["gate_up"] * 1e3,
                         phases_us={k_: round(v * 1e3, 2) for k_, v in phase_ms.items()},
                         layer_gbs=step_bytes / (ms_per_step * 1e-3) / 1e9,
