@@ -1294,17 +1294,31 @@ __global__ void __launch_bounds__(256) k_combine(const float *__restrict__ parti
     const int t = blockIdx.x;
     pdl_wait();
     pdl_launch_dependents();
-    for (int h = threadIdx.x * 4; h < H; h += blockDim.x * 4) {
+    // which of the token's slots belong to a local expert: read once, so that the row loads below do
+    // not each wait for their own flag
+    uint32_t valid = 0;
+    if (routed)
+        for (int j = 0; j < top_k; j++) valid |= (pos[t * top_k + j] >= 0 ? 1u : 0u) << j;
+    const bool with_shared = shared && t >= sh_begin && t < sh_begin + sh_count;
+    // grid.y splits the row; the sum still runs in slot order
+    for (int h = (blockIdx.y * blockDim.x + threadIdx.x) * 4; h < H; h += gridDim.y * blockDim.x * 4) {
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (routed) {
-            for (int j = 0; j < top_k; j++) {
-                const int p = t * top_k + j;
-                if (pos[p] < 0) continue;
-                const float4 v = *reinterpret_cast<const float4 *>(partial + (size_t)p * H + h);
-                acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        for (int j0 = 0; j0 < top_k; j0 += 4) {
+            float4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; u++) {   // four independent loads in flight
+                const int j = j0 + u;
+                v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (j < top_k && ((valid >> j) & 1u))
+                    v[u] = *reinterpret_cast<const float4 *>(partial + (size_t)(t * top_k + j) * H + h);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                const int j = j0 + u;
+                if (j < top_k && ((valid >> j) & 1u)) { acc.x += v[u].x; acc.y += v[u].y; acc.z += v[u].z; acc.w += v[u].w; }
             }
         }
-        if (shared && t >= sh_begin && t < sh_begin + sh_count) {
+        if (with_shared) {
             const float4 v = *reinterpret_cast<const float4 *>(partial + (size_t)(n * top_k + t) * H + h);
             acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
         }
@@ -1321,11 +1335,14 @@ cudaError_t launch_combine(const LayerDev &L, const Workspace &ws, const uint32_
     (void)idx;
     if (n <= 0) return cudaSuccess;
     cudaError_t e;
+    // few tokens: split each row over several CTAs so that the machine has enough loads in flight
+    const int parts = n >= 512 ? 1 : (L.H + 1023) / 1024;
+    const dim3 grid(n, parts);
     if (out_dtype == PMOE_F32)
-        e = launch_pdl(k_combine<float>, dim3(n), dim3(256), 0, s, (const float *)ws.partial, (const int *)ws.groups.pos, n,
+        e = launch_pdl(k_combine<float>, grid, dim3(256), 0, s, (const float *)ws.partial, (const int *)ws.groups.pos, n,
                        top_k, L.H, routed, shared, ws.sh_begin, ws.sh_count, (float *)out);
     else
-        e = launch_pdl(k_combine<__nv_bfloat16>, dim3(n), dim3(256), 0, s, (const float *)ws.partial,
+        e = launch_pdl(k_combine<__nv_bfloat16>, grid, dim3(256), 0, s, (const float *)ws.partial,
                        (const int *)ws.groups.pos, n, top_k, L.H, routed, shared, ws.sh_begin, ws.sh_count,
                        (__nv_bfloat16 *)out);
     count_launch();
