@@ -33,6 +33,8 @@ typedef enum {
     PMOE_F32 = 0,
     PMOE_F16 = 1,
     PMOE_Q8_0 = 8,
+    PMOE_Q2_K = 10,
+    PMOE_Q3_K = 11,
     PMOE_Q4_K = 12,
     PMOE_Q5_K = 13,
     PMOE_Q6_K = 14,

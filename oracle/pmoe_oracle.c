@@ -87,6 +87,8 @@ static inline uint16_t f32_to_f16(float f)
 
 #pragma pack(push, 1)
 typedef struct { uint16_t d; int8_t qs[QK8_0]; } block_q8_0;                      /* 34 B  */
+typedef struct { uint8_t scales[QK_K / 16]; uint8_t qs[QK_K / 4]; uint16_t d, dmin; } block_q2_K;       /* 84 B  */
+typedef struct { uint8_t hmask[QK_K / 8]; uint8_t qs[QK_K / 4]; uint8_t scales[12]; uint16_t d; } block_q3_K; /* 110 B */
 typedef struct { uint16_t d, dmin; uint8_t scales[12]; uint8_t qs[QK_K / 2]; } block_q4_K; /* 144 B */
 typedef struct { uint16_t d, dmin; uint8_t scales[12]; uint8_t qh[QK_K / 8]; uint8_t qs[QK_K / 2]; } block_q5_K; /* 176 B */
 typedef struct { uint8_t ql[QK_K / 2]; uint8_t qh[QK_K / 4]; int8_t scales[QK_K / 16]; uint16_t d; } block_q6_K; /* 210 B */
@@ -98,7 +100,7 @@ size_t pmo_block_size(int dtype)
     switch (dtype) {
     case PMO_F32: case PMO_F16: return 1;
     case PMO_Q8_0: return QK8_0;
-    case PMO_Q4_K: case PMO_Q5_K: case PMO_Q6_K: return QK_K;
+    case PMO_Q2_K: case PMO_Q3_K: case PMO_Q4_K: case PMO_Q5_K: case PMO_Q6_K: return QK_K;
     default: return 0;
     }
 }
@@ -109,6 +111,8 @@ size_t pmo_type_size(int dtype)
     case PMO_F32: return 4;
     case PMO_F16: return 2;
     case PMO_Q8_0: return sizeof(block_q8_0);
+    case PMO_Q2_K: return sizeof(block_q2_K);
+    case PMO_Q3_K: return sizeof(block_q3_K);
     case PMO_Q4_K: return sizeof(block_q4_K);
     case PMO_Q5_K: return sizeof(block_q5_K);
     case PMO_Q6_K: return sizeof(block_q6_K);
@@ -144,6 +148,73 @@ static void dequant_q8_0(const block_q8_0 *b, size_t nb, float *y)
     for (size_t i = 0; i < nb; i++) {
         float d = f16_to_f32(b[i].d);
         for (int j = 0; j < QK8_0; j++) y[i * QK8_0 + j] = (float)b[i].qs[j] * d;
+    }
+}
+
+/* BlockQ2K::to_float (ggml dequantize_row_q2_K): 16 sub-blocks of 16, 4-bit scale and 4-bit min each */
+static void dequant_q2_K(const block_q2_K *b, size_t nb, float *y)
+{
+    for (size_t i = 0; i < nb; i++) {
+        float d = f16_to_f32(b[i].d);
+        float min = f16_to_f32(b[i].dmin);
+        const uint8_t *q = b[i].qs;
+        int is = 0;
+        for (int n = 0; n < QK_K; n += 128) {
+            int shift = 0;
+            for (int j = 0; j < 4; j++) {
+                uint8_t sc = b[i].scales[is++];
+                float dl = d * (float)(sc & 0xF), ml = min * (float)(sc >> 4);
+                for (int l = 0; l < 16; l++) *y++ = dl * (float)((int8_t)((q[l] >> shift) & 3)) - ml;
+                sc = b[i].scales[is++];
+                dl = d * (float)(sc & 0xF);
+                ml = min * (float)(sc >> 4);
+                for (int l = 0; l < 16; l++) *y++ = dl * (float)((int8_t)((q[l + 16] >> shift) & 3)) - ml;
+                shift += 2;
+            }
+            q += 32;
+        }
+    }
+}
+
+/* the 16 six-bit scales of a Q3_K block (ggml's kmask unpacking), still offset by 32 */
+static void q3k_scales(const uint8_t *packed, int8_t *out)
+{
+    const uint32_t kmask1 = 0x03030303u, kmask2 = 0x0f0f0f0fu;
+    uint32_t aux[4];
+    memcpy(aux, packed, 12);
+    uint32_t tmp = aux[2];
+    aux[2] = ((aux[0] >> 4) & kmask2) | (((tmp >> 4) & kmask1) << 4);
+    aux[3] = ((aux[1] >> 4) & kmask2) | (((tmp >> 6) & kmask1) << 4);
+    aux[0] = (aux[0] & kmask2) | (((tmp >> 0) & kmask1) << 4);
+    aux[1] = (aux[1] & kmask2) | (((tmp >> 2) & kmask1) << 4);
+    memcpy(out, aux, 16);
+}
+
+/* BlockQ3K::to_float (ggml dequantize_row_q3_K): 2 low bits in qs, the third in hmask (clear = -4) */
+static void dequant_q3_K(const block_q3_K *b, size_t nb, float *y)
+{
+    for (size_t i = 0; i < nb; i++) {
+        float d_all = f16_to_f32(b[i].d);
+        const uint8_t *q = b[i].qs;
+        const uint8_t *hm = b[i].hmask;
+        uint8_t m = 1;
+        int8_t scales[16];
+        q3k_scales(b[i].scales, scales);
+        int is = 0;
+        for (int n = 0; n < QK_K; n += 128) {
+            int shift = 0;
+            for (int j = 0; j < 4; j++) {
+                float dl = d_all * (float)(scales[is++] - 32);
+                for (int l = 0; l < 16; l++)
+                    *y++ = dl * (float)((int8_t)((q[l] >> shift) & 3) - ((hm[l] & m) ? 0 : 4));
+                dl = d_all * (float)(scales[is++] - 32);
+                for (int l = 0; l < 16; l++)
+                    *y++ = dl * (float)((int8_t)((q[l + 16] >> shift) & 3) - ((hm[l + 16] & m) ? 0 : 4));
+                shift += 2;
+                m = (uint8_t)(m << 1);
+            }
+            q += 32;
+        }
     }
 }
 
@@ -230,6 +301,8 @@ int pmo_dequantize(int dtype, const void *blocks, size_t n, float *out)
     case PMO_F32: memcpy(out, blocks, n * 4); return 0;
     case PMO_F16: for (size_t i = 0; i < n; i++) out[i] = f16_to_f32(((const uint16_t *)blocks)[i]); return 0;
     case PMO_Q8_0: dequant_q8_0((const block_q8_0 *)blocks, n / bs, out); return 0;
+    case PMO_Q2_K: dequant_q2_K((const block_q2_K *)blocks, n / bs, out); return 0;
+    case PMO_Q3_K: dequant_q3_K((const block_q3_K *)blocks, n / bs, out); return 0;
     case PMO_Q4_K: dequant_q4_K((const block_q4_K *)blocks, n / bs, out); return 0;
     case PMO_Q5_K: dequant_q5_K((const block_q5_K *)blocks, n / bs, out); return 0;
     case PMO_Q6_K: dequant_q6_K((const block_q6_K *)blocks, n / bs, out); return 0;
@@ -239,7 +312,7 @@ int pmo_dequantize(int dtype, const void *blocks, size_t n, float *out)
 
 /* ------------------------------------------------------------------ weight quantisers
  * Used only to make synthetic GGUF blocks from seeded normal weights.  Q8_0 is
- * the ggml/candle reference quantiser.  The Q4_K, Q5_K and Q6_K quantisers are plain
+ * the ggml/candle reference quantiser.  The K-quant quantisers (Q2_K ... Q6_K) are plain
  * min/max quantisers of this build (not ggml's error-minimising search): any
  * valid quantiser serves, since oracle and library consume the same bytes. */
 
@@ -252,6 +325,95 @@ static void quant_q8_0(const float *x, size_t nb, block_q8_0 *y)
         float id = d != 0.f ? 1.f / d : 0.f;
         y[i].d = f32_to_f16(d);
         for (int j = 0; j < QK8_0; j++) y[i].qs[j] = (int8_t)roundf(x[i * QK8_0 + j] * id);
+    }
+}
+
+/* element e of a Q2_K / Q3_K block lives in byte 32*(e/128) + e%32 of qs at bit 2*((e%128)/32) */
+static inline void q23_set(uint8_t *qs, int e, int q2)
+{
+    qs[32 * (e / 128) + (e % 32)] |= (uint8_t)((q2 & 3) << (2 * ((e % 128) / 32)));
+}
+
+/* min/max quantiser: 16 sub-blocks of 16, scale = range/3 and min on 4 bits each */
+static void quant_q2_K(const float *x, size_t nb, block_q2_K *y)
+{
+    for (size_t i = 0; i < nb; i++) {
+        const float *xb = x + i * QK_K;
+        float scales[16], mins[16], max_scale = 0.f, max_min = 0.f;
+        for (int j = 0; j < 16; j++) {
+            float mn = 0.f, mx = 0.f;
+            for (int l = 0; l < 16; l++) {
+                mn = fminf(mn, xb[16 * j + l]);
+                mx = fmaxf(mx, xb[16 * j + l]);
+            }
+            scales[j] = (mx - mn) / 3.f;
+            mins[j] = -mn;
+            max_scale = fmaxf(max_scale, scales[j]);
+            max_min = fmaxf(max_min, mins[j]);
+        }
+        float inv_scale = max_scale > 0.f ? 15.f / max_scale : 0.f;
+        float inv_min = max_min > 0.f ? 15.f / max_min : 0.f;
+        y[i].d = f32_to_f16(max_scale / 15.f);
+        y[i].dmin = f32_to_f16(max_min / 15.f);
+        float d = f16_to_f32(y[i].d), dmin = f16_to_f32(y[i].dmin);
+        memset(y[i].qs, 0, sizeof y[i].qs);
+        for (int j = 0; j < 16; j++) {
+            int ls = (int)roundf(inv_scale * scales[j]), lm = (int)roundf(inv_min * mins[j]);
+            ls = ls > 15 ? 15 : ls;
+            lm = lm > 15 ? 15 : lm;
+            y[i].scales[j] = (uint8_t)(ls | (lm << 4));
+            float dq = d * (float)ls, mq = dmin * (float)lm;
+            for (int l = 0; l < 16; l++) {
+                int q = 0;
+                if (dq > 0.f) {
+                    q = (int)roundf((xb[16 * j + l] + mq) / dq);
+                    q = q < 0 ? 0 : (q > 3 ? 3 : q);
+                }
+                q23_set(y[i].qs, 16 * j + l, q);
+            }
+        }
+    }
+}
+
+/* symmetric quantiser: 16 sub-blocks of 16, signed 6-bit scale, quants in [-4, 3] */
+static void quant_q3_K(const float *x, size_t nb, block_q3_K *y)
+{
+    for (size_t i = 0; i < nb; i++) {
+        const float *xb = x + i * QK_K;
+        float scales[16], max_scale = 0.f;
+        for (int j = 0; j < 16; j++) {
+            float amax = 0.f;
+            for (int l = 0; l < 16; l++) amax = fmaxf(amax, fabsf(xb[16 * j + l]));
+            scales[j] = amax / 4.f;
+            max_scale = fmaxf(max_scale, scales[j]);
+        }
+        float inv = max_scale > 0.f ? 31.f / max_scale : 0.f;
+        y[i].d = f32_to_f16(max_scale / 31.f);
+        float d = f16_to_f32(y[i].d);
+        memset(y[i].qs, 0, sizeof y[i].qs);
+        memset(y[i].hmask, 0, sizeof y[i].hmask);
+        memset(y[i].scales, 0, sizeof y[i].scales);
+        for (int j = 0; j < 16; j++) {
+            int s = (int)roundf(inv * scales[j]);
+            s = s > 31 ? 31 : s;
+            int l6 = s + 32; /* stored with an offset of 32 */
+            /* low 4 bits: nibble j%8 half j/8 of scales[0..7]; high 2 bits: scales[8 + j%4] at bit 2*(j/4) */
+            if (j < 8) y[i].scales[j] |= (uint8_t)(l6 & 0xF);
+            else y[i].scales[j - 8] |= (uint8_t)((l6 & 0xF) << 4);
+            y[i].scales[8 + j % 4] |= (uint8_t)((l6 >> 4) << (2 * (j / 4)));
+            float dq = d * (float)s;
+            for (int l = 0; l < 16; l++) {
+                int e = 16 * j + l;
+                int q = 0;
+                if (dq > 0.f) {
+                    q = (int)roundf(xb[e] / dq);
+                    q = q < -4 ? -4 : (q > 3 ? 3 : q);
+                }
+                int u = q + 4; /* 0..7: two low bits in qs, the third in hmask */
+                q23_set(y[i].qs, e, u & 3);
+                if (u & 4) y[i].hmask[e % 32] |= (uint8_t)(1 << (4 * (e / 128) + (e % 128) / 32));
+            }
+        }
     }
 }
 
@@ -416,11 +578,15 @@ int pmo_quantize(int dtype, const float *x, size_t n, void *blocks)
     size_t chunk = 4096;
     if (dtype == PMO_F32) { memcpy(blocks, x, n * 4); return 0; }
     if (dtype == PMO_F16) { for (size_t i = 0; i < n; i++) ((uint16_t *)blocks)[i] = f32_to_f16(x[i]); return 0; }
-    if (dtype != PMO_Q8_0 && dtype != PMO_Q4_K && dtype != PMO_Q5_K && dtype != PMO_Q6_K) return -1;
+    if (dtype != PMO_Q8_0 && dtype != PMO_Q2_K && dtype != PMO_Q3_K && dtype != PMO_Q4_K && dtype != PMO_Q5_K &&
+        dtype != PMO_Q6_K)
+        return -1;
 #pragma omp parallel for schedule(static)
     for (size_t b0 = 0; b0 < nb; b0 += chunk) {
         size_t cnt = nb - b0 < chunk ? nb - b0 : chunk;
         if (dtype == PMO_Q8_0) quant_q8_0(x + b0 * bs, cnt, (block_q8_0 *)blocks + b0);
+        else if (dtype == PMO_Q2_K) quant_q2_K(x + b0 * bs, cnt, (block_q2_K *)blocks + b0);
+        else if (dtype == PMO_Q3_K) quant_q3_K(x + b0 * bs, cnt, (block_q3_K *)blocks + b0);
         else if (dtype == PMO_Q4_K) quant_q4_K(x + b0 * bs, cnt, (block_q4_K *)blocks + b0);
         else if (dtype == PMO_Q5_K) quant_q5_K(x + b0 * bs, cnt, (block_q5_K *)blocks + b0);
         else quant_q6_K(x + b0 * bs, cnt, (block_q6_K *)blocks + b0);
@@ -491,6 +657,80 @@ void pmo_quantize_q8_0_act(const float *x, size_t n, uint16_t *d_f16, int8_t *qs
  * candle's portable vec_dot (GgmlType::vec_dot_unopt).  The integer sums are
  * exact; the f32 steps keep the reference's association: eight running f32
  * lanes per row, summed at the end. */
+
+/* BlockQ2K::vec_dot against Q8_K (portable path, ggml_vec_dot_q2_K_q8_K generic) */
+static float vec_dot_q2_K_q8_K(size_t n, const block_q2_K *x, const block_q8_K *y)
+{
+    float sumf = 0.f;
+    for (size_t i = 0; i < n / QK_K; i++) {
+        const uint8_t *q2 = x[i].qs;
+        const int8_t *q8 = y[i].qs;
+        const uint8_t *sc = x[i].scales;
+        int summs = 0;
+        for (int j = 0; j < 16; j++) summs += y[i].bsums[j] * (sc[j] >> 4);
+        float dall = y[i].d * f16_to_f32(x[i].d);
+        float dmin = y[i].d * f16_to_f32(x[i].dmin);
+        int isum = 0, is = 0;
+        for (int k = 0; k < QK_K / 128; k++) {
+            int shift = 0;
+            for (int j = 0; j < 4; j++) {
+                int d = sc[is++] & 0xF;
+                int isuml = 0;
+                for (int l = 0; l < 16; l++) isuml += q8[l] * ((q2[l] >> shift) & 3);
+                isum += d * isuml;
+                d = sc[is++] & 0xF;
+                isuml = 0;
+                for (int l = 16; l < 32; l++) isuml += q8[l] * ((q2[l] >> shift) & 3);
+                isum += d * isuml;
+                shift += 2;
+                q8 += 32;
+            }
+            q2 += 32;
+        }
+        sumf += dall * (float)isum - dmin * (float)summs;
+    }
+    return sumf;
+}
+
+/* BlockQ3K::vec_dot against Q8_K (portable path): the quants as signed values -4..3, eight f32 lanes */
+static float vec_dot_q3_K_q8_K(size_t n, const block_q3_K *x, const block_q8_K *y)
+{
+    float sums[8] = {0};
+    int8_t aux8[QK_K];
+    for (size_t i = 0; i < n / QK_K; i++) {
+        const uint8_t *q3 = x[i].qs;
+        const uint8_t *hm = x[i].hmask;
+        int8_t *a = aux8;
+        uint8_t m = 1;
+        for (int j = 0; j < QK_K; j += 128) {
+            for (int sh = 0; sh < 8; sh += 2) {
+                for (int l = 0; l < 32; l++) a[l] = (int8_t)((q3[l] >> sh) & 3);
+                for (int l = 0; l < 32; l++) a[l] = (int8_t)(a[l] - ((hm[l] & m) ? 0 : 4));
+                a += 32;
+                m = (uint8_t)(m << 1);
+            }
+            q3 += 32;
+        }
+        int8_t scales[16];
+        q3k_scales(x[i].scales, scales);
+        int32_t aux32[8] = {0};
+        const int8_t *q8 = y[i].qs;
+        a = aux8;
+        for (int j = 0; j < QK_K / 16; j++) {
+            int32_t scale = scales[j] - 32;
+            for (int r = 0; r < 2; r++) {
+                for (int l = 0; l < 8; l++) aux32[l] += scale * ((int32_t)q8[l] * (int32_t)a[l]);
+                q8 += 8;
+                a += 8;
+            }
+        }
+        float d = f16_to_f32(x[i].d) * y[i].d;
+        for (int l = 0; l < 8; l++) sums[l] += d * (float)aux32[l];
+    }
+    float s = 0.f;
+    for (int l = 0; l < 8; l++) s += sums[l];
+    return s;
+}
 
 static float vec_dot_q4_K_q8_K(size_t n, const block_q4_K *x, const block_q8_K *y)
 {
@@ -646,7 +886,7 @@ static int qact_make(qact *a, int wdtype, const float *x, size_t m, size_t cols)
     a->dtype = wdtype;
     a->cols = cols;
     a->m = m;
-    if (wdtype == PMO_Q4_K || wdtype == PMO_Q5_K || wdtype == PMO_Q6_K) {
+    if (wdtype == PMO_Q2_K || wdtype == PMO_Q3_K || wdtype == PMO_Q4_K || wdtype == PMO_Q5_K || wdtype == PMO_Q6_K) {
         if (cols % QK_K) return -1;
         block_q8_K *b = (block_q8_K *)malloc(sizeof(block_q8_K) * m * (cols / QK_K));
         for (size_t r = 0; r < m; r++) quantize_row_q8_K(x + r * cols, cols, b + r * (cols / QK_K));
@@ -670,6 +910,12 @@ static inline float qdot(int dtype, const void *w, size_t row, size_t cols, cons
     switch (dtype) {
     case PMO_Q4_K:
         return vec_dot_q4_K_q8_K(cols, (const block_q4_K *)w + row * (cols / QK_K),
+                                 (const block_q8_K *)a->blocks + r * (cols / QK_K));
+    case PMO_Q2_K:
+        return vec_dot_q2_K_q8_K(cols, (const block_q2_K *)w + row * (cols / QK_K),
+                                 (const block_q8_K *)a->blocks + r * (cols / QK_K));
+    case PMO_Q3_K:
+        return vec_dot_q3_K_q8_K(cols, (const block_q3_K *)w + row * (cols / QK_K),
                                  (const block_q8_K *)a->blocks + r * (cols / QK_K));
     case PMO_Q5_K:
         return vec_dot_q5_K_q8_K(cols, (const block_q5_K *)w + row * (cols / QK_K),

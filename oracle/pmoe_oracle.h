@@ -27,7 +27,7 @@ extern "C" {
 #endif
 
 /* GGML dtype numbering (the ids candle's GgmlDType uses). */
-enum { PMO_F32 = 0, PMO_F16 = 1, PMO_Q8_0 = 8, PMO_Q4_K = 12, PMO_Q5_K = 13, PMO_Q6_K = 14 };
+enum { PMO_F32 = 0, PMO_F16 = 1, PMO_Q8_0 = 8, PMO_Q2_K = 10, PMO_Q3_K = 11, PMO_Q4_K = 12, PMO_Q5_K = 13, PMO_Q6_K = 14 };
 
 typedef struct {
     int32_t H, F, E, k;           /* hidden, expert intermediate, experts, experts per token */

@@ -17,8 +17,8 @@ import numpy as np
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _LIB_PATH = os.path.join(_HERE, "libpmoe_oracle.so")
 
-F32, F16, Q8_0, Q4_K, Q5_K, Q6_K = 0, 1, 8, 12, 13, 14
-DTYPE_NAMES = {F32: "F32", F16: "F16", Q8_0: "Q8_0", Q4_K: "Q4_K", Q5_K: "Q5_K", Q6_K: "Q6_K"}
+F32, F16, Q8_0, Q2_K, Q3_K, Q4_K, Q5_K, Q6_K = 0, 1, 8, 10, 11, 12, 13, 14
+DTYPE_NAMES = {F32: "F32", F16: "F16", Q8_0: "Q8_0", Q2_K: "Q2_K", Q3_K: "Q3_K", Q4_K: "Q4_K", Q5_K: "Q5_K", Q6_K: "Q6_K"}
 
 
 def build(force: bool = False) -> str:

@@ -4,7 +4,7 @@ from __future__ import annotations
 import ctypes as C
 import os
 
-F32, F16, Q8_0, Q4_K, Q5_K, Q6_K, BF16 = 0, 1, 8, 12, 13, 14, 30
+F32, F16, Q8_0, Q2_K, Q3_K, Q4_K, Q5_K, Q6_K, BF16 = 0, 1, 8, 10, 11, 12, 13, 14, 30
 TRACE_PHASES = 8
 
 STATUS_NAMES = {

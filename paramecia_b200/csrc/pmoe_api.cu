@@ -61,7 +61,7 @@ struct DeviceGuard {
 
 static bool dtype_known(int dt)
 {
-    return dt == PMOE_F32 || dt == PMOE_F16 || dt == PMOE_BF16 || dt == PMOE_Q8_0 || dt == PMOE_Q4_K || dt == PMOE_Q5_K || dt == PMOE_Q6_K;
+    return dt == PMOE_F32 || dt == PMOE_F16 || dt == PMOE_BF16 || dt == PMOE_Q8_0 || (dt >= PMOE_Q2_K && dt <= PMOE_Q6_K);
 }
 
 }  // namespace pmoe
@@ -328,6 +328,19 @@ int pmoe_layer_create(const pmoe_layer_desc *desc, pmoe_layer **out)
             return fail(PMOE_ERR_UNSUPPORTED_DTYPE, "shared gate and up must share one dtype");
         if (!gemv_supported(d.sh_gate_dtype, d.H, d.F, &why) || !gemv_supported(d.sh_down_dtype, d.F, d.H, &why))
             return fail(PMOE_ERR_UNSUPPORTED_DTYPE, "shared expert: %s", why);
+        // Q2_K / Q3_K / Q5_K shared matrices only beside routed matrices of the same type (kernel variants
+        // exist for those pairings and for Q4_K / Q6_K / Q8_0 shared experts)
+        auto low = [](int t) { return t == PMOE_Q2_K || t == PMOE_Q3_K; };
+        auto pair_ok = [&](int routed_t, int shared_t) {
+            if (low(shared_t)) return shared_t == routed_t;
+            if (low(routed_t) && shared_t == PMOE_Q5_K) return false;
+            return true;
+        };
+        if (!pair_ok(d.gate_dtype, d.sh_gate_dtype) || !pair_ok(d.down_dtype, d.sh_down_dtype))
+            return fail(PMOE_ERR_UNSUPPORTED_DTYPE,
+                        "shared expert types (%d, %d) beside routed types (%d, %d): Q2_K / Q3_K shared matrices need routed "
+                        "matrices of the same type, and Q2_K / Q3_K routed matrices a shared expert of their own type, "
+                        "Q4_K, Q6_K or Q8_0", d.sh_gate_dtype, d.sh_down_dtype, d.gate_dtype, d.down_dtype);
     }
     int ndev = 0;
     if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev == 0) {
@@ -700,8 +713,8 @@ int pmoe_reduce_rows(int device, const float *parts, int n_parts, const void *ex
 int pmoe_qmatmul(int device, int dtype, const void *w, size_t rows, size_t cols, const float *x, size_t m, float *y,
                  void *stream)
 {
-    if (dtype != PMOE_Q4_K && dtype != PMOE_Q5_K && dtype != PMOE_Q6_K && dtype != PMOE_Q8_0)
-        return fail(PMOE_ERR_UNSUPPORTED_DTYPE, "pmoe_qmatmul serves Q4_K, Q5_K, Q6_K and Q8_0 (got %d)", dtype);
+    if (!(dtype >= PMOE_Q2_K && dtype <= PMOE_Q6_K) && dtype != PMOE_Q8_0)
+        return fail(PMOE_ERR_UNSUPPORTED_DTYPE, "pmoe_qmatmul serves Q2_K ... Q6_K and Q8_0 (got %d)", dtype);
     if (!rows || !cols || cols % 256 || cols > 16384 || rows > (1u << 24) || m > 4096)
         return fail(PMOE_ERR_UNSUPPORTED_SHAPE, "cols must be a multiple of 256 (<= 16384), m <= 4096");
     if (!m) return PMOE_OK;
@@ -721,8 +734,8 @@ int pmoe_qmatmul(int device, int dtype, const void *w, size_t rows, size_t cols,
 int pmoe_qmatmul_noalloc(int device, int dtype, const void *w, size_t rows, size_t cols, const float *x, size_t m,
                          float *y, void *stream)
 {
-    if (dtype != PMOE_Q4_K && dtype != PMOE_Q5_K && dtype != PMOE_Q6_K && dtype != PMOE_Q8_0)
-        return fail(PMOE_ERR_UNSUPPORTED_DTYPE, "pmoe_qmatmul_noalloc serves Q4_K, Q5_K, Q6_K and Q8_0 (got %d)", dtype);
+    if (!(dtype >= PMOE_Q2_K && dtype <= PMOE_Q6_K) && dtype != PMOE_Q8_0)
+        return fail(PMOE_ERR_UNSUPPORTED_DTYPE, "pmoe_qmatmul_noalloc serves Q2_K ... Q6_K and Q8_0 (got %d)", dtype);
     if (!rows || !cols || cols % 256 || rows > (1u << 24))
         return fail(PMOE_ERR_UNSUPPORTED_SHAPE, "cols must be a non-zero multiple of 256");
     if (!m) return PMOE_OK;

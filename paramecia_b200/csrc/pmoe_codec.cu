@@ -1,6 +1,6 @@
 // Block codecs and the small f32 kernels around the MoE block.
 //
-// k_dequantize restates candle's GgmlType::to_float for BlockQ8_0 / BlockQ4K / BlockQ5K / BlockQ6K (the
+// k_dequantize restates candle's GgmlType::to_float for BlockQ8_0 and BlockQ2K ... BlockQ6K (the
 // QTensor::dequantize the reference calls, e.g. paramecia-model/src/qwen3_next.rs:1758-1762);
 // products are rounded one by one so the f32 bits equal the host codec's.
 // k_add_rms_norm is RmsNorm::forward (paramecia-model/src/quantized_nn.rs:172-190) fused with
@@ -31,6 +31,25 @@ __global__ void __launch_bounds__(256) k_dequantize(int dtype, const uint8_t *__
         const uint8_t *b = blocks + (i / QK8_0) * Q8_0_BYTES;
         float d = half_bits_to_float((uint16_t)(b[0] | (b[1] << 8)));
         out[i] = __fmul_rn((float)(int8_t)b[2 + i % QK8_0], d);
+    } else if (dtype == PMOE_Q2_K) {
+        const uint8_t *b = blocks + (i / QK_K) * Q2_K_BYTES;
+        int w = (int)(i % QK_K);
+        int half = w / 128, j = (w % 128) / 32, l = w % 32;
+        float d = half_bits_to_float((uint16_t)(b[80] | (b[81] << 8)));
+        float dmin = half_bits_to_float((uint16_t)(b[82] | (b[83] << 8)));
+        uint8_t sc = b[8 * half + 2 * j + l / 16];
+        int q = (b[16 + 32 * half + l] >> (2 * j)) & 3;
+        out[i] = __fsub_rn(__fmul_rn(__fmul_rn(d, (float)(sc & 0xF)), (float)q), __fmul_rn(dmin, (float)(sc >> 4)));
+    } else if (dtype == PMOE_Q3_K) {
+        const uint8_t *b = blocks + (i / QK_K) * Q3_K_BYTES;
+        int w = (int)(i % QK_K);
+        int half = w / 128, j = (w % 128) / 32, l = w % 32;
+        float d = half_bits_to_float((uint16_t)(b[108] | (b[109] << 8)));
+        int is = 8 * half + 2 * j + l / 16;   // 6-bit scale: low nibble in scales[is % 8], high 2 bits in scales[8 + is % 4]
+        int low = is < 8 ? (b[96 + is] & 0xF) : (b[96 + is - 8] >> 4);
+        int sc = (low | (((b[104 + (is & 3)] >> (2 * (is >> 2))) & 3) << 4)) - 32;
+        int q = ((b[32 + 32 * half + l] >> (2 * j)) & 3) - (((b[l] >> (4 * half + j)) & 1) ? 0 : 4);
+        out[i] = __fmul_rn(__fmul_rn(d, (float)sc), (float)q);
     } else if (dtype == PMOE_Q4_K) {
         const uint8_t *b = blocks + (i / QK_K) * Q4_K_BYTES;
         int w = (int)(i % QK_K);

@@ -16,10 +16,14 @@ namespace pmoe {
 
 // ---------------------------------------------------------------- GGUF block layouts
 // Q8_0:  34 B = f16 d, int8 qs[32]
+// Q2_K:  84 B = u8 scales[16] (4-bit scale | 4-bit min << 4 per 16 weights), u8 qs[64] (2 bits), f16 d, f16 dmin
+// Q3_K: 110 B = u8 hmask[32] (third bits), u8 qs[64] (2 bits), u8 scales[12] (16 x 6 bits, offset 32), f16 d
 // Q4_K: 144 B = f16 d, f16 dmin, u8 scales[12] (8x 6-bit scale + 8x 6-bit min), u8 qs[128]
 // Q5_K: 176 B = the Q4_K header, u8 qh[32] (fifth bits: bit j of qh[l] belongs to sub-block j), u8 qs[128]
 // Q6_K: 210 B = u8 ql[128], u8 qh[64], i8 scales[16], f16 d
 constexpr int Q8_0_BYTES = 34;
+constexpr int Q2_K_BYTES = 84;
+constexpr int Q3_K_BYTES = 110;
 constexpr int Q4_K_BYTES = 144;
 constexpr int Q5_K_BYTES = 176;
 constexpr int Q6_K_BYTES = 210;
@@ -29,7 +33,7 @@ __host__ __device__ inline int block_elems(int dtype)
     switch (dtype) {
     case PMOE_F32: case PMOE_F16: case PMOE_BF16: return 1;
     case PMOE_Q8_0: return QK8_0;
-    case PMOE_Q4_K: case PMOE_Q5_K: case PMOE_Q6_K: return QK_K;
+    case PMOE_Q2_K: case PMOE_Q3_K: case PMOE_Q4_K: case PMOE_Q5_K: case PMOE_Q6_K: return QK_K;
     default: return 0;
     }
 }
@@ -40,6 +44,8 @@ __host__ __device__ inline int block_bytes(int dtype)
     case PMOE_F32: return 4;
     case PMOE_F16: case PMOE_BF16: return 2;
     case PMOE_Q8_0: return Q8_0_BYTES;
+    case PMOE_Q2_K: return Q2_K_BYTES;
+    case PMOE_Q3_K: return Q3_K_BYTES;
     case PMOE_Q4_K: return Q4_K_BYTES;
     case PMOE_Q5_K: return Q5_K_BYTES;
     case PMOE_Q6_K: return Q6_K_BYTES;
@@ -54,8 +60,8 @@ __host__ __device__ inline size_t row_bytes(int dtype, size_t cols)
 }
 
 // Activation blocks follow the weight type's dot type on the reference CPU path:
-// Q4_K, Q5_K, Q6_K -> Q8_K (256 values, f32 scale, 16 sums of 16); Q8_0 -> Q8_0 (32 values, f16 scale).
-__host__ __device__ inline bool is_kquant(int dtype) { return dtype == PMOE_Q4_K || dtype == PMOE_Q5_K || dtype == PMOE_Q6_K; }
+// Q2_K ... Q6_K -> Q8_K (256 values, f32 scale, 16 sums of 16); Q8_0 -> Q8_0 (32 values, f16 scale).
+__host__ __device__ inline bool is_kquant(int dtype) { return dtype >= PMOE_Q2_K && dtype <= PMOE_Q6_K; }
 
 // ---------------------------------------------------------------- status word
 // Kernels never trap: a failed range check or an expired wait records a code here.

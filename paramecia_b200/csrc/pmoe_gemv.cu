@@ -67,6 +67,18 @@ template <> struct Tr<PMOE_Q4_K> {
     static constexpr bool KQ = true;
     using Act = ActQ4K;
 };
+// Q2_K and Q3_K interleave their 2-bit quants like Q6_K (element 128*half + 32*stream + l sits in byte
+// 32*half + l at bits 2*stream), so a lane takes the same 64 weights: 16 positions of four streams.
+template <> struct Tr<PMOE_Q2_K> {
+    static constexpr int UNIT = 64;
+    static constexpr bool KQ = true;
+    using Act = ActQ6K;
+};
+template <> struct Tr<PMOE_Q3_K> {
+    static constexpr int UNIT = 64;
+    static constexpr bool KQ = true;
+    using Act = ActQ6K;
+};
 template <> struct Tr<PMOE_Q5_K> {   // same split of a block over lanes as Q4_K
     static constexpr int UNIT = 64;
     static constexpr bool KQ = true;
@@ -104,6 +116,8 @@ template <> __device__ inline void zero_act<PMOE_Q6_K>(ActQ6K &o)
 #pragma unroll
     for (int i = 0; i < 4; i++) o.bs[i] = 0;
 }
+template <> __device__ inline void zero_act<PMOE_Q2_K>(ActQ6K &o) { zero_act<PMOE_Q6_K>(o); }
+template <> __device__ inline void zero_act<PMOE_Q3_K>(ActQ6K &o) { zero_act<PMOE_Q6_K>(o); }
 template <> __device__ inline void zero_act<PMOE_Q8_0>(ActQ16 &o)
 {
 #pragma unroll
@@ -155,6 +169,15 @@ template <> __device__ inline void load_act<PMOE_Q6_K>(const QAct &q, size_t row
     const int16_t *bs = q.bsums + row * (K / 16) + 16 * b + 8 * half + jj;
 #pragma unroll
     for (int g = 0; g < 4; g++) o.bs[g] = bs[2 * g];
+}
+
+template <> __device__ inline void load_act<PMOE_Q2_K>(const QAct &q, size_t row, int K, int u, ActQ6K &o)
+{
+    load_act<PMOE_Q6_K>(q, row, K, u, o);
+}
+template <> __device__ inline void load_act<PMOE_Q3_K>(const QAct &q, size_t row, int K, int u, ActQ6K &o)
+{
+    load_act<PMOE_Q6_K>(q, row, K, u, o);
 }
 
 // 32-weight unit u: block u/8, half (u/4)%2, positions l = 8jj .. 8jj+7 (jj = u%4) of the four streams
@@ -308,6 +331,125 @@ __device__ inline void load16_a2(const uint8_t *row, int mis, int off, uint32_t 
 
 __device__ inline int misalign2(const uint8_t *p) { return (int)(reinterpret_cast<uintptr_t>(p) & 2); }
 
+// 12 bytes at row + off, 2-byte aligned: four aligned words and a funnel shift; reads nothing past
+// the 14th byte from the aligned base
+__device__ inline void load12_a2(const uint8_t *row, int mis, int off, uint32_t (&o)[3])
+{
+    const int a = off + mis;
+    const uint32_t *q = reinterpret_cast<const uint32_t *>(row - mis + (a & ~3));
+    const uint32_t sh = (uint32_t)(a & 2) * 8;
+    const uint32_t u0 = q[0], u1 = q[1], u2 = q[2];
+    const uint32_t u3 = sh ? q[3] : 0u;
+    o[0] = __funnelshift_r(u0, u1, sh);
+    o[1] = __funnelshift_r(u1, u2, sh);
+    o[2] = __funnelshift_r(u2, u3, sh);
+}
+
+// Q2_K: unit u = block u/4, half (u/2)%2, positions 16*s .. 16*s+15 (s = u%2) of the four 2-bit streams.
+// Blocks are 84 bytes, so every field is 4-byte aligned.
+template <> struct Dot<PMOE_Q2_K> {
+    struct Pre {
+        int q_off, sc_off, d_off;
+    };
+    __device__ static inline Pre pre(int u)
+    {
+        const int blk = (u >> 2) * Q2_K_BYTES, half = (u >> 1) & 1, s = u & 1;
+        return Pre{blk + 16 + 32 * half + 16 * s, blk + 8 * half + s, blk + 80};
+    }
+    template <int CNT, bool A4 = true>
+    __device__ static inline void run(const uint8_t *row, const Pre &p, const ActQ6K *act, float *acc)
+    {
+        const uint32_t *qp = reinterpret_cast<const uint32_t *>(row + p.q_off);
+        const uint32_t w[4] = {qp[0], qp[1], qp[2], qp[3]};
+        const uint8_t *sc = row + p.sc_off;
+        const uint32_t c[4] = {sc[0], sc[2], sc[4], sc[6]};   // 4-bit scale | 4-bit min << 4
+        const uint32_t dd = *reinterpret_cast<const uint32_t *>(row + p.d_off);
+        const float d = half_bits_to_float((uint16_t)(dd & 0xffffu));
+        const float dmin = half_bits_to_float((uint16_t)(dd >> 16));
+        int isum[CNT];
+#pragma unroll
+        for (int t = 0; t < CNT; t++) isum[t] = 0;
+#pragma unroll
+        for (int g = 0; g < 4; g++) {
+            uint32_t v[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) v[i] = (w[i] >> (2 * g)) & 0x03030303u;
+#pragma unroll
+            for (int t = 0; t < CNT; t++) {
+                int s = 0, s2 = 0;
+                s = dp4a_us(v[0], act[t].a[4 * g + 0], s);
+                s2 = dp4a_us(v[1], act[t].a[4 * g + 1], s2);
+                s = dp4a_us(v[2], act[t].a[4 * g + 2], s);
+                s2 = dp4a_us(v[3], act[t].a[4 * g + 3], s2);
+                isum[t] += (int)(c[g] & 0xFu) * (s + s2);
+            }
+        }
+#pragma unroll
+        for (int t = 0; t < CNT; t++) {
+            const int imin = (int)(c[0] >> 4) * act[t].bs[0] + (int)(c[1] >> 4) * act[t].bs[1] +
+                             (int)(c[2] >> 4) * act[t].bs[2] + (int)(c[3] >> 4) * act[t].bs[3];
+            acc[t] += act[t].dx * (d * (float)isum[t] - dmin * (float)imin);
+        }
+    }
+};
+
+// Q3_K: the same unit; the third bit of stream g's quants is bit 4*half + g of hmask[16*s + l], and a clear
+// bit means -4: with u = q2 | bit << 2 (0..7) the signed quant is u - 4, and the -4 comes back through the
+// activations' partial sums.  Blocks are 110 bytes: fields of odd blocks start 2 bytes off a word.
+template <> struct Dot<PMOE_Q3_K> {
+    struct Pre {
+        int q_off, hm_off, sc_off, d_off, hbit, is0;
+    };
+    __device__ static inline Pre pre(int u)
+    {
+        const int blk = (u >> 2) * Q3_K_BYTES, half = (u >> 1) & 1, s = u & 1;
+        return Pre{blk + 32 + 32 * half + 16 * s, blk + 16 * s, blk + 96, blk + 108, 4 * half, 8 * half + s};
+    }
+    template <int CNT, bool A4 = true>
+    __device__ static inline void run(const uint8_t *row, const Pre &p, const ActQ6K *act, float *acc)
+    {
+        const int mis = A4 ? 0 : misalign2(row);
+        uint32_t w[4], hm[4], sw[3];
+        load16_a2(row, mis, p.q_off, w);
+        load16_a2(row, mis, p.hm_off, hm);
+        load12_a2(row, mis, p.sc_off, sw);   // scales[0..3], scales[4..7], scales[8..11]
+        const float d = half_bits_to_float(*reinterpret_cast<const uint16_t *>(row + p.d_off));
+        int c[4];
+#pragma unroll
+        for (int g = 0; g < 4; g++) {
+            // six-bit scale `is`: low nibble in byte is%8 (upper nibbles for is >= 8), high two bits in
+            // byte 8 + is%4 at bit 2*(is/4); stored with an offset of 32
+            const int is = p.is0 + 2 * g;
+            const uint32_t src = ((is >> 2) & 1) ? sw[1] : sw[0];
+            const uint32_t nib = (is >= 8 ? src >> 4 : src) >> (8 * (is & 3));
+            const uint32_t hi2 = sw[2] >> (8 * (is & 3) + 2 * (is >> 2));
+            c[g] = (int)((nib & 0xFu) | ((hi2 & 3u) << 4)) - 32;
+        }
+        int isum[CNT];
+#pragma unroll
+        for (int t = 0; t < CNT; t++)
+            isum[t] = -4 * (c[0] * act[t].bs[0] + c[1] * act[t].bs[1] + c[2] * act[t].bs[2] + c[3] * act[t].bs[3]);
+#pragma unroll
+        for (int g = 0; g < 4; g++) {
+            uint32_t v[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+                v[i] = ((w[i] >> (2 * g)) & 0x03030303u) | (((hm[i] >> (p.hbit + g)) & 0x01010101u) << 2);
+#pragma unroll
+            for (int t = 0; t < CNT; t++) {
+                int s = 0, s2 = 0;
+                s = dp4a_us(v[0], act[t].a[4 * g + 0], s);
+                s2 = dp4a_us(v[1], act[t].a[4 * g + 1], s2);
+                s = dp4a_us(v[2], act[t].a[4 * g + 2], s);
+                s2 = dp4a_us(v[3], act[t].a[4 * g + 3], s2);
+                isum[t] += c[g] * (s + s2);
+            }
+        }
+#pragma unroll
+        for (int t = 0; t < CNT; t++) acc[t] += (d * act[t].dx) * (float)isum[t];
+    }
+};
+
 template <> struct Dot<PMOE_Q6_K> {
     struct Pre {
         int la_off, h_off, sc_off, d_off;
@@ -445,8 +587,8 @@ template <int DT, int NMAT> struct Cfg {
     static constexpr int UPL = UNITS / LPR;           // units per lane
     static constexpr int GROUPS = 32 / LPR;           // rows a warp works on at once
     static constexpr int ROW_BYTES = K / (DT == PMOE_Q8_0 ? QK8_0 : QK_K) *
-                                     (DT == PMOE_Q8_0 ? Q8_0_BYTES : DT == PMOE_Q4_K ? Q4_K_BYTES
-                                      : DT == PMOE_Q5_K ? Q5_K_BYTES : Q6_K_BYTES);
+                                     (DT == PMOE_Q8_0 ? Q8_0_BYTES : DT == PMOE_Q2_K ? Q2_K_BYTES : DT == PMOE_Q3_K ? Q3_K_BYTES
+                                      : DT == PMOE_Q4_K ? Q4_K_BYTES : DT == PMOE_Q5_K ? Q5_K_BYTES : Q6_K_BYTES);
     static constexpr int ROWS = floor_pow2(STAGE_BYTES / (ROW_BYTES * NMAT));  // rows of each matrix per item
     static constexpr int ITEM_BYTES = ROWS * ROW_BYTES;                        // per matrix
     // tokens per pass: bounded by the activation registers a lane keeps (16 words per token for Q4_K and Q6_K, 4 for Q8_0)
@@ -1029,8 +1171,8 @@ __global__ void __launch_bounds__(GEMV_THREADS, 2) k_expert_gemv(const GemvArgs 
 // ---------------------------------------------------------------- host-side dispatch
 bool gemv_supported(int dtype, int K, int rows, const char **why)
 {
-    if (dtype != PMOE_Q4_K && dtype != PMOE_Q5_K && dtype != PMOE_Q6_K && dtype != PMOE_Q8_0) {
-        *why = "expert weights must be Q4_K, Q5_K, Q6_K or Q8_0";
+    if (!(dtype >= PMOE_Q2_K && dtype <= PMOE_Q6_K) && dtype != PMOE_Q8_0) {
+        *why = "expert weights must be Q2_K ... Q6_K or Q8_0";
         return false;
     }
     if (!((K == 2048 && rows == 512) || (K == 512 && rows == 2048))) {
@@ -1082,10 +1224,31 @@ static cudaError_t launch_gemv_s(const GemvArgs &A, int dt_s, cudaStream_t s)
     return cudaErrorInvalidValue;
 }
 
+// Q2_K / Q3_K routed experts: the shared expert may be absent, of the same type, or Q4_K / Q6_K / Q8_0
+// (pmoe_layer_create refuses the other pairings; this keeps the number of kernel variants bounded)
+template <int DT_R, int NMAT>
+static cudaError_t launch_gemv_s_low(const GemvArgs &A, int dt_s, cudaStream_t s)
+{
+    if (dt_s == DT_R) return launch_gemv_t<DT_R, DT_R, NMAT>(A, s);
+    switch (dt_s) {
+    case 0: return launch_gemv_t<DT_R, 0, NMAT>(A, s);
+    case PMOE_Q4_K: return launch_gemv_t<DT_R, PMOE_Q4_K, NMAT>(A, s);
+    case PMOE_Q6_K:
+        if constexpr (NMAT == 1) {
+            if (A.sh_count >= 3) return launch_gemv_t<DT_R, Q6_K_T4, NMAT>(A, s);
+        }
+        return launch_gemv_t<DT_R, PMOE_Q6_K, NMAT>(A, s);
+    case PMOE_Q8_0: return launch_gemv_t<DT_R, PMOE_Q8_0, NMAT>(A, s);
+    }
+    return cudaErrorInvalidValue;
+}
+
 template <int NMAT>
 static cudaError_t launch_gemv(const GemvArgs &A, int dt_r, int dt_s, cudaStream_t s)
 {
     switch (dt_r) {
+    case PMOE_Q2_K: return launch_gemv_s_low<PMOE_Q2_K, NMAT>(A, dt_s, s);
+    case PMOE_Q3_K: return launch_gemv_s_low<PMOE_Q3_K, NMAT>(A, dt_s, s);
     case PMOE_Q4_K: return launch_gemv_s<PMOE_Q4_K, NMAT>(A, dt_s, s);
     case PMOE_Q5_K: return launch_gemv_s<PMOE_Q5_K, NMAT>(A, dt_s, s);
     case PMOE_Q6_K:
@@ -1210,6 +1373,8 @@ cudaError_t launch_qmatmul(int dtype, const void *w, int rows, int K, const floa
     dim3 grid((rows + 3) / 4, (m + TG - 1) / TG);
     const uint8_t *wb = (const uint8_t *)w;
     if (dtype == PMOE_Q4_K) k_qmatmul<PMOE_Q4_K><<<grid, 128, 0, s>>>(wb, rows, K, a, m, y);
+    else if (dtype == PMOE_Q2_K) k_qmatmul<PMOE_Q2_K><<<grid, 128, 0, s>>>(wb, rows, K, a, m, y);
+    else if (dtype == PMOE_Q3_K) k_qmatmul<PMOE_Q3_K><<<grid, 128, 0, s>>>(wb, rows, K, a, m, y);
     else if (dtype == PMOE_Q5_K) k_qmatmul<PMOE_Q5_K><<<grid, 128, 0, s>>>(wb, rows, K, a, m, y);
     else if (dtype == PMOE_Q6_K) k_qmatmul<PMOE_Q6_K><<<grid, 128, 0, s>>>(wb, rows, K, a, m, y);
     else k_qmatmul<PMOE_Q8_0><<<grid, 128, 0, s>>>(wb, rows, K, a, m, y);

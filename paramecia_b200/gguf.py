@@ -23,7 +23,7 @@ from typing import Dict, Optional, Tuple
 import numpy as np
 import torch
 
-from ._lib import BF16, F16, F32, Q4_K, Q5_K, Q6_K, Q8_0, row_bytes
+from ._lib import BF16, F16, F32, Q2_K, Q3_K, Q4_K, Q5_K, Q6_K, Q8_0, row_bytes
 
 GGUF_MAGIC = 0x46554747  # "GGUF"
 DEFAULT_ALIGNMENT = 32
@@ -182,7 +182,7 @@ def _float_tensor(f: GGUFFile, name: str, device, keep_16bit: bool = False) -> t
     if t.dtype in (F16, BF16):
         v = raw.view(torch.float16 if t.dtype == F16 else torch.bfloat16).reshape(t.shape).to(device)
         return v if keep_16bit else v.float()
-    if t.dtype in (Q8_0, Q4_K, Q5_K, Q6_K):
+    if t.dtype in (Q8_0, Q2_K, Q3_K, Q4_K, Q5_K, Q6_K):
         from .moe import dequantize
         n = int(np.prod(t.shape))
         return dequantize(raw.to(device), t.dtype, n).reshape(t.shape)

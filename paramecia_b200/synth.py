@@ -1,11 +1,11 @@
 """Seeded synthetic MoE layers in GGUF block formats.
 
 The reference publishes no benchmark data for this path, so the workloads are synthetic:
-normal weights N(0, 0.02) quantised to Q4_K / Q5_K / Q6_K / Q8_0 blocks, a float router and normal
+normal weights N(0, 0.02) quantised to Q2_K ... Q6_K / Q8_0 blocks, a float router and normal
 inputs.  The quantisers here are plain torch tensor code (CPU or CUDA) used only to
 manufacture valid blocks; the library and the CPU oracle both consume the resulting bytes,
 so their quality does not enter any comparison.  Q8_0 follows the ggml reference quantiser;
-Q4_K, Q5_K and Q6_K are simple min/max quantisers.
+the K-quants are simple min/max quantisers.
 """
 from __future__ import annotations
 
@@ -14,7 +14,7 @@ from typing import Dict, Optional
 
 import torch
 
-from ._lib import Q4_K, Q5_K, Q6_K, Q8_0
+from ._lib import Q2_K, Q3_K, Q4_K, Q5_K, Q6_K, Q8_0
 
 PRESETS = {
     # name: (gate/up dtype, down dtype, shared dtype)
@@ -26,6 +26,10 @@ PRESETS = {
     "q6k": (Q6_K, Q6_K, Q6_K),
     "q5k": (Q5_K, Q5_K, Q5_K),
     "q5k_m": (Q5_K, Q6_K, Q8_0),        # Q5_K_M-style mix
+    "q2k": (Q2_K, Q2_K, Q2_K),
+    "q3k": (Q3_K, Q3_K, Q3_K),
+    "q3k_m": (Q3_K, Q4_K, Q8_0),        # Q3_K_M-style mix
+    "q2k_q3k": (Q2_K, Q3_K, Q4_K),
 }
 
 
@@ -68,6 +72,59 @@ def quantize_q4_k(x: torch.Tensor) -> torch.Tensor:
     sb[:, 4:8] = lm[:, 0:4] | ((lm[:, 4:8] >> 4) << 6)
     sb[:, 8:12] = (ls[:, 4:8] & 0xF) | ((lm[:, 4:8] & 0xF) << 4)
     return torch.cat([_half_bytes(d16), _half_bytes(m16), sb.to(torch.uint8), qs], dim=1).reshape(-1)
+
+
+def _pack_2bit(q: torch.Tensor) -> torch.Tensor:
+    """[nb, 256] values 0..3 -> [nb, 64] bytes: element 128*half + 32*stream + l in byte 32*half + l at bits 2*stream."""
+    q = q.reshape(-1, 2, 4, 32).to(torch.uint8)
+    out = q[:, :, 0] | (q[:, :, 1] << 2) | (q[:, :, 2] << 4) | (q[:, :, 3] << 6)
+    return out.reshape(-1, 64)
+
+
+def quantize_q2_k(x: torch.Tensor) -> torch.Tensor:
+    xb = x.reshape(-1, 16, 16).float()
+    mn = xb.amin(-1).clamp(max=0)
+    mx = xb.amax(-1).clamp(min=0)
+    scales = (mx - mn) / 3.0
+    mins = -mn
+    max_scale = scales.amax(-1)
+    max_min = mins.amax(-1)
+    inv_s = torch.where(max_scale > 0, 15.0 / max_scale, torch.zeros_like(max_scale))
+    inv_m = torch.where(max_min > 0, 15.0 / max_min, torch.zeros_like(max_min))
+    ls = torch.round(inv_s[:, None] * scales).clamp(0, 15).to(torch.int32)
+    lm = torch.round(inv_m[:, None] * mins).clamp(0, 15).to(torch.int32)
+    d16 = (max_scale / 15.0).to(torch.float16)
+    m16 = (max_min / 15.0).to(torch.float16)
+    dq = d16.float()[:, None] * ls.float()
+    mq = m16.float()[:, None] * lm.float()
+    q = torch.where(dq[..., None] > 0, torch.round((xb + mq[..., None]) / dq[..., None].clamp(min=1e-30)),
+                    torch.zeros_like(xb)).clamp(0, 3)
+    sc = (ls | (lm << 4)).to(torch.uint8)
+    return torch.cat([sc, _pack_2bit(q.reshape(-1, 256)), _half_bytes(d16), _half_bytes(m16)], dim=1).reshape(-1)
+
+
+def quantize_q3_k(x: torch.Tensor) -> torch.Tensor:
+    xb = x.reshape(-1, 16, 16).float()
+    nb = xb.shape[0]
+    scales = xb.abs().amax(-1) / 4.0
+    max_scale = scales.amax(-1)
+    inv = torch.where(max_scale > 0, 31.0 / max_scale, torch.zeros_like(max_scale))
+    d16 = (max_scale / 31.0).to(torch.float16)
+    s = torch.round(inv[:, None] * scales).clamp(0, 31).to(torch.int32)
+    dq = d16.float()[:, None] * s.float()
+    q = torch.where(dq[..., None] > 0, torch.round(xb / dq[..., None].clamp(min=1e-30)), torch.zeros_like(xb)).clamp(-4, 3)
+    u = (q + 4).to(torch.uint8).reshape(nb, 256)            # 0..7: low two bits in qs, the third in hmask
+    hb = (u >> 2).reshape(nb, 2, 4, 32)                      # [block, half, stream, l]
+    hmask = torch.zeros((nb, 32), dtype=torch.uint8, device=x.device)
+    for h in range(2):
+        for g in range(4):
+            hmask |= hb[:, h, g] << (4 * h + g)
+    l6 = s + 32                                              # stored with an offset of 32
+    sb = torch.zeros((nb, 12), dtype=torch.int32, device=x.device)
+    sb[:, 0:8] = (l6[:, 0:8] & 0xF) | ((l6[:, 8:16] & 0xF) << 4)
+    for j in range(16):
+        sb[:, 8 + j % 4] |= (l6[:, j] >> 4) << (2 * (j // 4))
+    return torch.cat([hmask, _pack_2bit(u & 3), sb.to(torch.uint8), _half_bytes(d16)], dim=1).reshape(-1)
 
 
 def quantize_q5_k(x: torch.Tensor) -> torch.Tensor:
@@ -119,7 +176,8 @@ def quantize_q6_k(x: torch.Tensor) -> torch.Tensor:
     return torch.cat([ql, qh, s.to(torch.int8).view(torch.uint8), _half_bytes(d16)], dim=1).reshape(-1)
 
 
-_QUANT = {Q8_0: quantize_q8_0, Q4_K: quantize_q4_k, Q5_K: quantize_q5_k, Q6_K: quantize_q6_k}
+_QUANT = {Q8_0: quantize_q8_0, Q2_K: quantize_q2_k, Q3_K: quantize_q3_k, Q4_K: quantize_q4_k, Q5_K: quantize_q5_k,
+          Q6_K: quantize_q6_k}
 
 
 def quantize(x: torch.Tensor, dtype: int, chunk_elems: int = 1 << 26) -> torch.Tensor:

@@ -3,7 +3,7 @@
 The Rust reference cannot be built or run here (no cargo; its candle fork is not vendored) and
 holds no golden vectors for this path, so the block codecs are pinned against an independent
 implementation instead: the `gguf` Python package (gguf-py 0.19, the GGUF project's own
-reader).  For seeded random Q4_K / Q5_K / Q6_K / Q8_0 blocks (plus edge blocks: zero scales, largest
+reader).  For seeded random Q2_K ... Q6_K / Q8_0 blocks (plus edge blocks: zero scales, largest
 and negative f16 scales, all-ones payload) the file stores the raw block bytes and gguf-py's
 dequantised f32 output, and for Q8_0 also gguf-py's quantisation of a seeded normal vector.
 
@@ -50,6 +50,10 @@ def main():
     raw = blocks(rng5, 48, 176, (0, 2))
     out["q5_k_blocks"] = raw
     out["q5_k_dequant"] = quants.dequantize(raw.reshape(-1), T.Q5_K).astype(np.float32).reshape(-1)
+    for seed, name, gt, ts, offs in ((20240609, "q2_k", T.Q2_K, 84, (80, 82)), (20240610, "q3_k", T.Q3_K, 110, (108,))):
+        raw = blocks(np.random.default_rng(seed), 48, ts, offs)
+        out[name + "_blocks"] = raw
+        out[name + "_dequant"] = quants.dequantize(raw.reshape(-1), gt).astype(np.float32).reshape(-1)
     np.savez_compressed(OUT, **out)
     print("wrote", OUT, {k: v.shape for k, v in out.items()})
 

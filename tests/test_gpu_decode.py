@@ -24,12 +24,12 @@ from oracle import pmoe_oracle as po
 DEV = "cuda:0"
 
 
-@pytest.mark.parametrize("dtype", [pm.Q4_K, pm.Q5_K, pm.Q6_K, pm.Q8_0])
+@pytest.mark.parametrize("dtype", [pm.Q2_K, pm.Q3_K, pm.Q4_K, pm.Q5_K, pm.Q6_K, pm.Q8_0])
 def test_dequantize_bit_exact(dtype):
     rng = np.random.default_rng(7)
     nb, ts, bs = 512, pm.type_size(dtype), pm.block_size(dtype)
     raw = rng.integers(0, 256, size=(nb, ts), dtype=np.uint8)
-    offs = {pm.Q4_K: (0, 2), pm.Q5_K: (0, 2), pm.Q6_K: (208,), pm.Q8_0: (0,)}[dtype]
+    offs = {pm.Q2_K: (80, 82), pm.Q3_K: (108,), pm.Q4_K: (0, 2), pm.Q5_K: (0, 2), pm.Q6_K: (208,), pm.Q8_0: (0,)}[dtype]
     for off in offs:  # keep the f16 scales finite; include zero, negative and large ones
         v = raw[:, off:off + 2].copy().view(np.float16)
         v[~np.isfinite(v)] = np.float16(-0.75)
@@ -40,6 +40,10 @@ def test_dequantize_bit_exact(dtype):
     raw[3, :] = 255
     if dtype in (pm.Q4_K, pm.Q5_K):
         raw[3, 0:4] = np.array([1.0, 1.0], np.float16).view(np.uint8)
+    elif dtype == pm.Q2_K:
+        raw[3, 80:84] = np.array([1.0, 1.0], np.float16).view(np.uint8)
+    elif dtype == pm.Q3_K:
+        raw[3, 108:110] = np.array([1.0], np.float16).view(np.uint8)
     elif dtype == pm.Q6_K:
         raw[3, 208:210] = np.array([1.0], np.float16).view(np.uint8)
     else:
@@ -94,6 +98,10 @@ CASES = [
     ("q4k_m", 32, 4, 130, torch.float32),     # many tokens per expert: several token passes
     ("q5k", 16, 3, 5, torch.float32),
     ("q5k_m", 64, 6, 40, torch.bfloat16),
+    ("q2k", 16, 3, 5, torch.float32),
+    ("q3k", 16, 3, 7, torch.float32),
+    ("q3k_m", 64, 6, 40, torch.bfloat16),
+    ("q2k_q3k", 32, 4, 70, torch.bfloat16),
 ]
 
 
@@ -259,6 +267,13 @@ def test_error_behaviour():
         tr.forward(seeded_x(2, 2048, 1).to(DEV))
     assert e.value.code == -6
     assert blk.forward(seeded_x(0, 2048, 1).to(DEV)).shape == (0, 2048)
+    # a Q3_K shared expert beside Q4_K routed experts is a pairing without kernels: refused at create
+    bad = synth.make_layer(E=4, k=1, preset="q4k", seed=2)
+    sh = synth.make_layer(E=4, k=1, preset="q3k", seed=2)["shared"]
+    bad["shared"] = sh
+    with pytest.raises(pm.PmoeError) as e:
+        synth.make_block(bad, DEV, max_tokens=4)
+    assert e.value.code == -2
 
 
 def test_add_rms_norm():
@@ -273,7 +288,7 @@ def test_add_rms_norm():
 
 
 @pytest.mark.parametrize("dtype,rows,cols", [(pm.Q4_K, 64, 2048), (pm.Q6_K, 128, 512), (pm.Q8_0, 32, 1024),
-                                             (pm.Q5_K, 48, 1024),
+                                             (pm.Q5_K, 48, 1024), (pm.Q2_K, 40, 768), (pm.Q3_K, 35, 256),
                                              (pm.Q6_K, 33, 256)])   # 210-byte rows: every other row starts 2 bytes off a word
 def test_qmatmul_entry_point(dtype, rows, cols):
     rng = np.random.default_rng(11)

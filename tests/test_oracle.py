@@ -13,10 +13,10 @@ from tests.common import oracle_layer, rel_l2, seeded_x
 
 G = np.load(os.path.join(os.path.dirname(__file__), "golden", "codec_golden.npz"))
 LG = np.load(os.path.join(os.path.dirname(__file__), "golden", "layer_golden.npz"))
-DT = {"q4_k": po.Q4_K, "q5_k": po.Q5_K, "q6_k": po.Q6_K, "q8_0": po.Q8_0}
+DT = {"q2_k": po.Q2_K, "q3_k": po.Q3_K, "q4_k": po.Q4_K, "q5_k": po.Q5_K, "q6_k": po.Q6_K, "q8_0": po.Q8_0}
 
 
-@pytest.mark.parametrize("name", ["q4_k", "q5_k", "q6_k", "q8_0"])
+@pytest.mark.parametrize("name", ["q2_k", "q3_k", "q4_k", "q5_k", "q6_k", "q8_0"])
 def test_dequantize_matches_gguf_py_bit_exact(name):
     raw, want = G[name + "_blocks"], G[name + "_dequant"]
     got = po.dequantize(DT[name], raw.reshape(-1), want.size)
@@ -28,7 +28,8 @@ def test_q8_0_quantiser_matches_gguf_py():
     assert np.array_equal(got, G["q8_0_quant_blocks"])
 
 
-@pytest.mark.parametrize("dtype,tol", [(po.Q4_K, 0.12), (po.Q5_K, 0.06), (po.Q6_K, 0.03), (po.Q8_0, 0.01)])
+@pytest.mark.parametrize("dtype,tol", [(po.Q2_K, 0.4), (po.Q3_K, 0.25), (po.Q4_K, 0.12), (po.Q5_K, 0.06), (po.Q6_K, 0.03),
+                                       (po.Q8_0, 0.01)])
 def test_weight_quantisers_round_trip(dtype, tol):
     rng = np.random.default_rng(1)
     w = (rng.standard_normal(256 * 32) * 0.02).astype(np.float32)
@@ -67,7 +68,7 @@ def test_q8_0_activation_quantiser():
     assert np.array_equal(qs[:32], (np.sign(q) * np.floor(np.abs(q) + 0.5)).astype(np.int8))
 
 
-@pytest.mark.parametrize("dtype", [po.Q4_K, po.Q5_K, po.Q6_K, po.Q8_0])
+@pytest.mark.parametrize("dtype", [po.Q2_K, po.Q3_K, po.Q4_K, po.Q5_K, po.Q6_K, po.Q8_0])
 def test_qmatmul_is_integer_dot_of_quantised_activations(dtype):
     rng = np.random.default_rng(4)
     rows, cols, m = 8, 512, 3
