@@ -99,6 +99,15 @@ __device__ inline float4 load_x4(const __nv_bfloat16 *x, size_t off)
 
 constexpr int ROUTER_WPB = 2;
 
+// The router matrix is static: a kernel pulls its own rows towards L2 before it waits for the
+// previous kernel (whose output, x, it may not touch yet), so the cold read of W overlaps that
+// kernel's tail instead of following it.
+__device__ inline void prefetch_l2(const void *p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
+__device__ inline void prefetch_row_l2(const float *row, int H, int lane)
+{
+    for (int j = lane * 32; j < H; j += 32 * 32) prefetch_l2(row + j);   // one 128-byte line per lane and step
+}
+
 template <typename XT, int TT>
 __global__ void __launch_bounds__(ROUTER_WPB * 32) k_router(const float *__restrict__ W,
                                                             const float *__restrict__ bias,
@@ -107,6 +116,10 @@ __global__ void __launch_bounds__(ROUTER_WPB * 32) k_router(const float *__restr
 {
     extern __shared__ __align__(16) float xrow[];
     __shared__ float red[8];
+    {
+        const int e_pf = blockIdx.x * ROUTER_WPB + (threadIdx.x >> 5);
+        if ((int)blockIdx.x < router_ctas && e_pf < E) prefetch_row_l2(W + (size_t)e_pf * H, H, threadIdx.x & 31);
+    }
     pdl_wait();
     pdl_launch_dependents();
     if ((int)blockIdx.x >= router_ctas) {  // CTAs past the router rows prepare one token each
@@ -164,6 +177,14 @@ __global__ void __launch_bounds__(RT_WARPS * 32) k_router_tiled(const float *__r
 {
     extern __shared__ __align__(16) float xs[];  // [T][H]
     __shared__ float red[8];
+    if ((int)blockIdx.y == 0) {   // the CTAs of the first token tile cover every row once
+        for (int pass = 0; pass < passes; pass++) {
+            const int e0 = ((blockIdx.x * passes + pass) * RT_WARPS + (threadIdx.x >> 5)) * R;
+#pragma unroll
+            for (int r_ = 0; r_ < R; r_++)
+                if (e0 + r_ < E) prefetch_row_l2(W + (size_t)(e0 + r_) * H, H, threadIdx.x & 31);
+        }
+    }
     pdl_wait();
     pdl_launch_dependents();
     if ((int)blockIdx.y >= token_tiles) {  // grid rows past the token tiles prepare one token per CTA
