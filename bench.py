@@ -73,13 +73,21 @@ class ClockSampler:
         self.idx = gpu_index
         self.proc = None
         self.path = None
+        self.skip = 0
+
+    def mark(self):
+        """Samples taken so far (while the layers were being built, the GPU idle) do not count."""
+        try:
+            self.skip = sum(1 for _ in open(self.path))
+        except Exception:
+            self.skip = 0
 
     def start(self):
         try:
             f = tempfile.NamedTemporaryFile("w", suffix=".csv", delete=False)
             self.path = f.name
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-lms", "100", "-i", str(self.idx)], stdout=f, stderr=subprocess.DEVNULL)
+                                          "-lms", "20", "-i", str(self.idx)], stdout=f, stderr=subprocess.DEVNULL)
         except Exception:
             self.proc = None
 
@@ -94,7 +102,12 @@ class ClockSampler:
             self.proc.kill()
         sm, mx, reasons = [], [], set()
         try:
-            for line in open(self.path):
+            lines = open(self.path).read().splitlines()
+            window = lines[self.skip:]
+            if not any(len(l.split(",")) >= 9 for l in window):
+                window = lines   # a run shorter than the sampling period: fall back to every sample of the process
+                out["window"] = "whole process (the marked region held no sample)"
+            for line in window:
                 p = [c.strip() for c in line.split(",")]
                 if len(p) < 9:
                     continue
@@ -207,11 +220,15 @@ def prefill_main(args):
     out = torch.empty((n, H), dtype=torch.bfloat16, device=dev)
     W = max(args.warmup, 3)
     steps = min(args.steps, 50)
+    sampler = ClockSampler(0)
+    sampler.start()
+    for i in range(2):   # (first touches; nvidia-smi comes up meanwhile)
+        blocks[i % nl].forward_into(xs[i % 2], out)
+    torch.cuda.synchronize()
+    sampler.mark()       # window: warm-up and timed steps, the same load
     for i in range(W):
         blocks[i % nl].forward_into(xs[i % 2], out)
     torch.cuda.synchronize()
-    sampler = ClockSampler(0)
-    sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     before = pm.launch_count()
     e0.record()
@@ -284,6 +301,9 @@ def main():
             raise SystemExit("launch multi-GPU runs with torch.distributed.run (one rank per GPU)")
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()   # early: nvidia-smi takes a moment to come up; idle samples are dropped by mark()
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     N = world
@@ -410,11 +430,9 @@ def main():
         return tot / 4.0
 
     W = max(args.warmup, 3)
-    sampler = ClockSampler(local_rank)
     if rank == 0:
-        sampler.start()
+        sampler.mark()   # window: warm-up, the timed steps and their graph replay (all the same load)
     ms, launches = time_steps(batch, args.steps, W)
-    clocks = sampler.stop() if rank == 0 else {}
     ms_per_step = ms / args.steps
     value = batch * N * args.steps / (ms * 1e-3)
     launch_mode = "direct C-ABI calls"
@@ -426,6 +444,7 @@ def main():
             ms, ms_per_step, steps_done, launches = g_ms, g_ms / g_steps, g_steps, g_launches
             value = batch * N * g_steps / (g_ms * 1e-3)
             launch_mode = f"CUDA graph holding one forward per layer ({len(blocks)}), replayed"
+    clocks = sampler.stop() if rank == 0 else {}
 
     # ---- roofline of the dominant kernel (gate/up GEMV): traced pass, events around each kernel
     D = distinct_experts(batch)
