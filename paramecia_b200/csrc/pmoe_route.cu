@@ -382,11 +382,78 @@ __global__ void __launch_bounds__(TOPK_WPB * 32) k_topk(const float *__restrict_
     }
 }
 
+// The same selection with a token's probabilities in registers (E = 32 * NV): lane l owns experts
+// l, l + 32, ...  Same operations on the same values as k_topk, so the same bits come out; it only
+// drops the shared-memory round trips of the k arg-max rounds.
+template <int NV>
+__global__ void __launch_bounds__(TOPK_WPB * 32) k_topk_reg(const float *__restrict__ logits, int n, int k,
+                                                            uint32_t *__restrict__ idx_out, float *__restrict__ w_out)
+{
+    constexpr int E = 32 * NV;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * TOPK_WPB + warp;
+    pdl_wait();
+    pdl_launch_dependents();
+    if (t >= n) return;
+    float p[NV];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < NV; i++) {
+        float v = logits[(size_t)t * E + lane + 32 * i];
+        v = fminf(fmaxf(v, -100.f), 100.f);
+        p[i] = v;
+        mx = fmaxf(mx, v);
+    }
+#pragma unroll
+    for (int s = 16; s >= 1; s >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, s));
+    float sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; i++) {
+        p[i] = expf(p[i] - mx);
+        sum += p[i];
+    }
+#pragma unroll
+    for (int s = 16; s >= 1; s >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, s);
+#pragma unroll
+    for (int i = 0; i < NV; i++) p[i] = __fdiv_rn(p[i], sum);
+    float my_w = 0.f;      // lane j keeps the j-th selection
+    uint32_t my_i = 0;
+    for (int j = 0; j < k; j++) {
+        float bv = -1.f;
+        int bi = 0x7fffffff;
+#pragma unroll
+        for (int i = 0; i < NV; i++)
+            if (p[i] > bv) { bv = p[i]; bi = lane + 32 * i; }
+#pragma unroll
+        for (int s = 16; s >= 1; s >>= 1) {
+            float ov = __shfl_xor_sync(0xffffffffu, bv, s);
+            int oi = __shfl_xor_sync(0xffffffffu, bi, s);
+            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+        }
+        if (lane == j) { my_w = bv; my_i = (uint32_t)bi; }
+#pragma unroll
+        for (int i = 0; i < NV; i++)
+            if (bi == lane + 32 * i) p[i] = -2.f;   // taken
+    }
+    float wsum = 0.f;
+    for (int j = 0; j < k; j++) wsum += __shfl_sync(0xffffffffu, my_w, j);
+    if (lane < k) {
+        if (idx_out) idx_out[(size_t)t * k + lane] = my_i;
+        if (w_out) w_out[(size_t)t * k + lane] = __fdiv_rn(my_w, wsum);
+    }
+}
+
 cudaError_t launch_topk(const LayerDev &L, const Workspace &ws, const float *logits, int n, uint32_t *idx, float *w,
                         cudaStream_t s)
 {
     (void)ws;
     if (n <= 0) return cudaSuccess;
+    if (L.E == 512) {
+        cudaError_t e = launch_pdl(k_topk_reg<16>, dim3((n + TOPK_WPB - 1) / TOPK_WPB), dim3(TOPK_WPB * 32), 0, s,
+                                   (const float *)logits, n, L.k, idx, w);
+        count_launch();
+        return e;
+    }
     size_t smem = (size_t)TOPK_WPB * L.E * sizeof(float);
     cudaError_t e = launch_pdl(k_topk, dim3((n + TOPK_WPB - 1) / TOPK_WPB), dim3(TOPK_WPB * 32), smem, s,
                                (const float *)logits, n, L.E, L.k, idx, w);

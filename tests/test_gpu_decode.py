@@ -70,9 +70,10 @@ def test_router_bit_exact(n, xdtype):
     blk.status()
 
 
-def test_router_bias_and_ties():
+@pytest.mark.parametrize("E", [64, 512])   # 512: the register-resident top-k kernel
+def test_router_bias_and_ties(E):
     # identical router rows give exactly equal probabilities: the lower expert id must win
-    t = synth.make_layer(E=64, k=4, preset="q8_0", seed=5, shared=False, F=512, zipf=True)
+    t = synth.make_layer(E=E, k=4, preset="q8_0", seed=5, shared=False, F=512, zipf=True)
     t["router_w"][10] = t["router_w"][3]
     t["router_w"][40] = t["router_w"][3]
     t["router_bias"][10] = t["router_bias"][3]
