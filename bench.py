@@ -197,7 +197,7 @@ NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 439.356672 / 429.555712   # gate/up launch, b
 
 
 def prefill_main(args):
-    """BASELINE config 3 on one GPU: 4096 bf16 tokens through one Q4_K / Q6_K block whose router carries the
+    """Benchmark configuration 3 (prefill) on one GPU: 4096 bf16 tokens through one Q4_K / Q6_K block whose router carries the
     bias 2*ln(1/rank_e) (rank = seeded permutation), so a dozen experts take most tokens.  Reports tokens/s and the
     tensor-core roofline of the gate/up grouped GEMM (tcgen05 kind::i8, two digit MMAs per algorithmic MMA)."""
     import torch

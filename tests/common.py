@@ -29,7 +29,7 @@ def max_abs(a, b):
     return float(np.max(np.abs(np.asarray(a, np.float64) - np.asarray(b, np.float64))))
 
 
-# BASELINE tolerance for layer outputs in fp32 accumulation
+# required tolerance for layer outputs in fp32 accumulation
 MAX_ABS_TOL = 2e-2
 REL_L2_TOL = 1e-3
 

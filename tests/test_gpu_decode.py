@@ -90,8 +90,8 @@ def test_router_bias_and_ties(E):
 
 CASES = [
     # preset, E, k, n, x dtype
-    ("q4k", 512, 10, 1, torch.float32),       # BASELINE config 1
-    ("q4k_m", 512, 10, 4, torch.bfloat16),    # BASELINE config 2 shapes
+    ("q4k", 512, 10, 1, torch.float32),       # benchmark configuration 1 (one f32 token, all Q4_K)
+    ("q4k_m", 512, 10, 4, torch.bfloat16),    # benchmark configuration 2 shapes
     ("q4k_m", 512, 10, 64, torch.bfloat16),
     ("q8_0", 64, 6, 17, torch.bfloat16),
     ("q6k", 16, 2, 3, torch.float32),
@@ -301,7 +301,7 @@ def test_qmatmul_entry_point(dtype, rows, cols):
 
 
 def test_stack_with_residual_and_rms_norm():
-    # BASELINE config 4 in miniature: h <- h + moe(rms_norm(h)) through independently seeded layers
+    # benchmark configuration 4 (layer stack) in miniature: h <- h + moe(rms_norm(h)) through independently seeded layers
     # (LayerWeights::forward_with_stats, qwen3_next.rs:4273-4286; eps 1e-6, norm weight 1)
     layers = [synth.make_layer(E=16, k=2, preset="q4k_m", seed=30, layer=li) for li in range(3)]
     blocks = [synth.make_block(t, DEV, max_tokens=16) for t in layers]
