@@ -78,3 +78,21 @@ def test_prefill_equals_decode_kernels_on_gate_up(force_prefill):
     b = blk.forward(x).float().cpu().numpy()
     os.environ["PMOE_PREFILL"] = "1"
     assert rel_l2(a, b) <= 2e-3   # bf16 output rounding dominates here
+
+
+@pytest.mark.parametrize("preset", ["q8_0", "q4k_m"])
+def test_prefill_sized_call_with_a_q8_0_shared_expert(preset):
+    # benchmark configuration 5 in miniature (all-Q8_0 block, Zipf routing, hundreds of tokens): no tensor-core
+    # kernel serves Q8_0 gate/up, so the streaming kernels take every pass and the shared expert's 600 tokens run
+    # as 75 eight-token tensor-core tiles per item; with Q4_K routed experts (q4k_m) the routed part takes the
+    # tensor-core kernels and the shared expert the streaming ones
+    n = 600
+    t = synth.make_layer(E=32, k=4, preset=preset, seed=16, zipf=True)
+    blk = synth.make_block(t, DEV, max_tokens=n)
+    x = seeded_x(n, 2048, 21, torch.bfloat16)
+    out, (logits, idx) = blk.forward_with_stats(x.to(DEV), out_dtype=torch.float32)
+    blk.status()
+    want, _, want_idx, _ = oracle_layer(t).forward(x.float().numpy())
+    assert np.array_equal(idx.cpu().numpy().astype(np.uint32), want_idx)
+    got = out.cpu().numpy()
+    assert max_abs(got, want) <= MAX_ABS_TOL and rel_l2(got, want) <= REL_L2_TOL
