@@ -277,7 +277,9 @@ cudaError_t launch_router(const LayerDev &L, const Workspace &ws, const void *x,
     const bool f32 = x_dtype == PMOE_F32;
     using BT = __nv_bfloat16;
     const PrepArgs P = make_prep_args(L, ws, prep ? n : 0, need_q8k, need_q80, need_gate);
-    if (n >= 2 && L.H <= 2048 && L.H % 128 == 0) {  // (one token: the row-per-warp kernel below is faster)
+    // (also for one token: with W cold in HBM, as it is when a model's layers take turns, the tiled kernel's
+    // eight loads in flight per lane beat the row-per-warp kernel below: 27 -> 16 us)
+    if (L.H <= 2048 && L.H % 128 == 0) {
         if (n > 512) {  // prefill sizes: 16-token tiles (128 KB of shared memory), 64 rows per CTA
             // (token preparation in its own launch: riding along it would hold 128 KB per token)
             if (prep) {
