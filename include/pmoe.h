@@ -26,7 +26,7 @@
 extern "C" {
 #endif
 
-#define PMOE_VERSION 1
+#define PMOE_VERSION 2
 
 /* GGML tensor-type ids, the numbering of candle's GgmlDType / GGUF files. */
 typedef enum {
@@ -75,10 +75,14 @@ typedef struct {
     int32_t H, F, E, k;    /* hidden, expert intermediate, experts (global), experts per token */
     int32_t max_tokens;    /* workspace is sized for this many tokens per call */
 
-    /* Routed experts held by this handle: global ids [expert_base, expert_base+E_local).
-       E_local == 0 means all E.  Indices outside the range are skipped, the way the
+    /* Routed experts held by this handle.  ep_placement 0 (contiguous): global ids
+       [expert_base, expert_base+E_local), local expert i = global expert_base + i;
+       E_local == 0 means all E.  ep_placement 1 (round-robin over ep_size ranks): the
+       E_local = E / ep_size experts ep_rank, ep_rank + ep_size, ... in that order
+       (expert_base is ignored); under a skewed router neighbouring hot experts then land
+       on different ranks.  Indices the handle does not hold are skipped, the way the
        reference skips indices >= num_experts (qwen3_next.rs:2045); expert parallelism
-       gives every rank one slice. */
+       gives every rank one share.  The reference runs one process and has no such table. */
     int32_t expert_base, E_local;
 
     int32_t gate_dtype, up_dtype, down_dtype;
@@ -103,6 +107,10 @@ typedef struct {
     /* non-zero when custom block multipliers are installed (MoeExperts::set_block_multipliers,
        qwen3_next.rs:1705-1720): every forward then returns PMOE_ERR_TRAINING_MODE */
     int32_t training_mode;
+
+    /* expert -> rank table of an expert-parallel group (see expert_base above) */
+    int32_t ep_placement; /* 0 contiguous, 1 round-robin */
+    int32_t ep_rank, ep_size; /* used by ep_placement 1 and by pmoe_ep_forward; 0, 0 = a single GPU */
 } pmoe_layer_desc;
 
 /* MoeBlock::new (qwen3_next.rs:1864-1895) */

@@ -37,6 +37,7 @@ class LayerDesc(C.Structure):
         ("sh_gate_inp", C.c_void_p),
         ("router_dtype", C.c_int32), ("router_w", C.c_void_p), ("router_bias", C.c_void_p),
         ("weights_location", C.c_int32), ("training_mode", C.c_int32),
+        ("ep_placement", C.c_int32), ("ep_rank", C.c_int32), ("ep_size", C.c_int32),
     ]
 
 

@@ -141,6 +141,7 @@ void carve_workspace(pmoe_layer *L, Carver &c)
     w.groups.n_active = c.take<int>(1);
     w.groups.cost_prefix = c.take<int>(El + 1);
     w.groups.cost_prefix_wide = c.take<int>(El + 1);
+    w.groups.cost_prefix_mma = c.take<int>(El + 1);
     w.groups.tile_prefix = c.take<int>(El + 1);
     w.groups.tile_table = c.take<int2>(n * k / PREFILL_NT + El + 1);
     w.act = c.take<float>(rows * F);
@@ -303,7 +304,14 @@ int pmoe_layer_create(const pmoe_layer_desc *desc, pmoe_layer **out)
     if (d.E > 1024) return fail(PMOE_ERR_UNSUPPORTED_SHAPE, "E must be <= 1024");
     if (d.H % 128) return fail(PMOE_ERR_UNSUPPORTED_SHAPE, "H must be a multiple of 128");
     int E_local = d.E_local > 0 ? d.E_local : d.E;
-    if (d.expert_base < 0 || d.expert_base + E_local > d.E)
+    if (d.ep_placement != 0 && d.ep_placement != 1) return fail(PMOE_ERR_INVALID_ARG, "ep_placement must be 0 or 1");
+    if (d.ep_size < 0 || d.ep_rank < 0 || (d.ep_size > 0 && d.ep_rank >= d.ep_size))
+        return fail(PMOE_ERR_INVALID_ARG, "ep_rank %d / ep_size %d", d.ep_rank, d.ep_size);
+    if (d.ep_placement == 1) {
+        if (d.ep_size < 1 || d.E % d.ep_size || E_local != d.E / d.ep_size)
+            return fail(PMOE_ERR_INVALID_ARG, "round-robin placement: E = %d must divide by ep_size = %d and E_local be E / ep_size",
+                        d.E, d.ep_size);
+    } else if (d.expert_base < 0 || d.expert_base + E_local > d.E)
         return fail(PMOE_ERR_INVALID_ARG, "expert slice [%d, %d) is outside [0, %d)", d.expert_base,
                     d.expert_base + E_local, d.E);
     if (d.weights_location < 0 || d.weights_location > 2)
@@ -358,6 +366,8 @@ int pmoe_layer_create(const pmoe_layer_desc *desc, pmoe_layer **out)
     LayerDev &v = L->dev;
     v.H = d.H; v.F = d.F; v.E = d.E; v.k = d.k;
     v.expert_base = d.expert_base; v.E_local = E_local;
+    v.ep_stride = d.ep_placement == 1 ? d.ep_size : 0;
+    v.ep_rem = d.ep_placement == 1 ? d.ep_rank : 0;
     v.gate_dtype = d.gate_dtype; v.up_dtype = d.up_dtype; v.down_dtype = d.down_dtype;
     v.has_shared = d.has_shared ? 1 : 0;
     v.sh_gate_dtype = d.sh_gate_dtype; v.sh_up_dtype = d.sh_up_dtype; v.sh_down_dtype = d.sh_down_dtype;

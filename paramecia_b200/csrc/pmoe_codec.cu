@@ -102,10 +102,10 @@ cudaError_t launch_dequantize(int dtype, const void *blocks, size_t n_elems, flo
 }
 
 // resid_out = resid_in + delta; y = resid_out / sqrt(mean(resid_out^2) + eps) * weight
-__global__ void __launch_bounds__(256) k_add_rms_norm(const float *__restrict__ resid_in,
-                                                      const float *__restrict__ delta,
+// (resid_out may be resid_in: a thread reads and later writes the same elements)
+__global__ void __launch_bounds__(256) k_add_rms_norm(const float *resid_in, const float *__restrict__ delta,
                                                       const float *__restrict__ weight, int H, float eps,
-                                                      float *__restrict__ resid_out, float *__restrict__ y)
+                                                      float *resid_out, float *__restrict__ y)
 {
     extern __shared__ float row[];
     __shared__ float red[8];

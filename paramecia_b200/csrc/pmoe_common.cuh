@@ -227,18 +227,32 @@ struct Groups {
     int *n_active;    // [1]
     int *cost_prefix; // [E_local + 1] exclusive prefix over active slots of ceil(count / GEMV_TG)
     int *cost_prefix_wide; // same with ceil(count / GEMV_TG_WIDE)
+    int *cost_prefix_mma;  // same with ceil(count / GEMV_TG_MMA): 8-token groups of the tensor-core GEMV
     int *tile_prefix; // [E_local + 1] exclusive prefix over active slots of ceil(count / PREFILL_NT)
     int2 *tile_table; // [tile_prefix[n_active]] (local expert id, tile index inside the expert) per prefill tile
 };
 
+// Local index of global expert id `g` on this handle, or -1 when another rank holds it (or the id is out of range).
+__host__ __device__ inline int local_expert(uint32_t g, int base, int E_local, int stride, int rem)
+{
+    if (stride > 1) {
+        const uint32_t q = g / (uint32_t)stride;
+        return (g % (uint32_t)stride == (uint32_t)rem && q < (uint32_t)E_local) ? (int)q : -1;
+    }
+    const uint32_t e = g - (uint32_t)base;   // wraps to a large value when below base
+    return e < (uint32_t)E_local ? (int)e : -1;
+}
+
 constexpr int GEMV_TG = 2;      // tokens one GEMV pass handles; the unit of the work partition
 constexpr int GEMV_TG_WIDE = 4; // ... for the kernels whose activation registers are small (Q6_K / Q8_0 down)
+constexpr int GEMV_TG_MMA = 8;  // tokens one pass of the tensor-core GEMV takes (the N of mma.m16n8k32)
 constexpr int PREFILL_NT = 64;  // tokens per tile of the prefill GEMMs
 
 // Everything a forward call needs, resolved to raw pointers.
 struct LayerDev {
     int H, F, E, k;
     int expert_base, E_local;
+    int ep_stride, ep_rem;   // round-robin placement: this handle holds the experts e with e % ep_stride == ep_rem (0: contiguous)
     int gate_dtype, up_dtype, down_dtype;
     const uint8_t *gate_exps, *up_exps, *down_exps;
     int has_shared, sh_gate_dtype, sh_up_dtype, sh_down_dtype;

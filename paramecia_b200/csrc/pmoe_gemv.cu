@@ -618,6 +618,7 @@ struct GemvArgs {
     const float *scale_s;      // shared gate sigmoid [n]        (down only)
     DevStatus *status;
     int debug;                 // 1: skip the arithmetic, 2: skip the copies (timing experiments)
+    int stage_bytes;           // bytes between the slots of the shared-memory ring
     // gate/up only: the CTA that completes an expert's last item re-quantises the expert's activated rows
     int *slot_done;            // [E_local + 1] items finished per slot (shared expert last); returns to zero
     int quant_dt_r, quant_dt_s; // block types the down matrices will consume (0 = no fused re-quantisation)
@@ -773,9 +774,17 @@ struct Plan {
     }
 };
 
-__device__ inline uint8_t *ring_stage(uint8_t *base, int s) { return base + 128 + s * STAGE_BYTES; }
+__device__ inline uint8_t *ring_stage(uint8_t *base, int s, int stride) { return base + 128 + s * stride; }
 __device__ inline uint64_t *ring_full(uint8_t *base, int s) { return reinterpret_cast<uint64_t *>(base) + s; }
 __device__ inline uint64_t *ring_empty(uint8_t *base, int s) { return reinterpret_cast<uint64_t *>(base) + NSTAGE + s; }
+
+// After its last copy a producer waits (bounded) until the copies still in flight have landed, so
+// that no asynchronous write can reach shared memory after the CTA has left.
+__device__ inline void drain_ring(uint8_t *ring, int issued)
+{
+    for (int it = issued > NSTAGE ? issued - NSTAGE : 0; it < issued; it++)
+        mbar_wait(ring_full(ring, it % NSTAGE), (uint32_t)(it / NSTAGE) & 1);
+}
 
 // The producer's side of the ring: issues the bulk copies of its next item once the compute
 // warps have released the slot's previous contents.
@@ -820,14 +829,14 @@ template <int DT_R, int DT_S1, int NMAT> struct Producer {
 #pragma unroll
             for (int mat = 0; mat < NMAT; mat++)
                 for (int r = 0; r < ROWS; r++)
-                    bulk_g2s(ring_stage(ring, s) + (mat * ROWS + r) * SharedMma<NMAT>::PITCH,
+                    bulk_g2s(ring_stage(ring, s, A.stage_bytes) + (mat * ROWS + r) * SharedMma<NMAT>::PITCH,
                              (mat == 0 ? src0 : src1) + r * RB, RB, full);
             return true;
         }
 #pragma unroll
         for (int mat = 0; mat < NMAT; mat++) {
             const uint8_t *src = mat == 0 ? src0 : src1;
-            uint8_t *dst = ring_stage(ring, s) + mat * bytes;
+            uint8_t *dst = ring_stage(ring, s, A.stage_bytes) + mat * bytes;
             for (uint32_t off = 0; off < bytes; off += BULK_PIECE)
                 bulk_g2s(dst + off, src + off, bytes - off < (uint32_t)BULK_PIECE ? bytes - off : (uint32_t)BULK_PIECE,
                          full);
@@ -918,7 +927,7 @@ __device__ inline bool run_items(const GemvArgs &A, uint8_t *ring, const Plan &p
             set_status(A.status, PMOE_ERR_TIMEOUT, 10 + NMAT, it);
             failed = true;
         }
-        const uint8_t *stage = ring_stage(ring, s);
+        const uint8_t *stage = ring_stage(ring, s, A.stage_bytes);
         if (A.debug == 1 || failed) {
         } else if (m <= C::TGK) {
             run_pass<DT, NMAT>(A, stage, cur.chunk, P, act, pre, warp, lane);
@@ -1050,7 +1059,7 @@ __device__ inline bool run_items_shared_mma(const GemvArgs &A, uint8_t *ring, co
             set_status(A.status, PMOE_ERR_TIMEOUT, 14 + NMAT, it);
             failed = true;
         }
-        const uint8_t *stage = ring_stage(ring, s);
+        const uint8_t *stage = ring_stage(ring, s, A.stage_bytes);
         if (A.debug != 1 && !failed) {
             for (int job = warp; job < MT * ntiles; job += GEMV_WARPS) {
                 const int mt = job / ntiles, nt = job - mt * ntiles;
@@ -1154,7 +1163,8 @@ __global__ void __launch_bounds__(GEMV_THREADS, 2) k_expert_gemv(const GemvArgs 
         if (lane == 0 && A.debug != 2) {
             Producer<DT_R, DT_S1, NMAT> prod{A, plan, ring, cur, 0, n_items};
             for (int i = 0; i < n_items; i++)
-                if (!prod.issue_next()) break;
+                if (!prod.issue_next()) { prod.issued--; break; }   // the item whose slot never came free was not issued
+            drain_ring(ring, prod.issued);
         }
         return;
     }
@@ -1165,6 +1175,362 @@ __global__ void __launch_bounds__(GEMV_THREADS, 2) k_expert_gemv(const GemvArgs 
         if (!ok) return;
         if (DT_S == PMOE_Q8_0 && shared_mma) run_items_shared_mma<NMAT>(A, ring, plan, cur, it, n_items, A.in_s, warp, lane);
         else run_items<DT_S, NMAT>(A, ring, plan, true, cur, plan.n_active + 1, it, n_items, A.in_s, warp, lane);
+    }
+}
+
+// ---------------------------------------------------------------- Q4_K gate/up on the tensor cores
+// The same gate/up step for Q4_K routed experts with the dot products on the tensor cores
+// (mma.sync.m16n8k32, u8 weights x s8 activations -> s32): sixteen weight rows are the M side, up to
+// eight tokens of the expert the N side, and one 32-weight sub-block -- the span of one 6-bit
+// scale -- the K of one instruction, so the integer sub-block sums are exact and meet their scales
+// as integers exactly like the dp4a path.  One instruction replaces 16 x tokens dp4a, and no
+// shuffle reduction over the reduction dimension is left.
+//
+// An item is still 16 gate + 16 up rows of one expert, but a slot with more than eight tokens is
+// walked once per group of eight (the ring delivers its items again, from L2).  Warp w of the eight
+// compute warps owns block column w of all 32 rows (K = 2048 = 8 blocks), so the eight tokens'
+// quantised activations of that column stay in 16 registers per lane for the whole expert.  The
+// mins term sum_j m_j * bsum_j goes through two more instructions over the partial sums split into
+// signed byte digits (bsum = 64 h + l).  The eight warps' partial sums meet in shared memory, in
+// the part of the ring slot the warp itself has finished reading, and are added in warp order.
+//
+// Rows land in shared memory 1168 bytes apart (1152 + 16): with rows 0,2,4,6 / 1,3,5,7 on the
+// eight row positions of a fragment the 8-byte loads of a half-warp fall into 32 different banks.
+constexpr int Q4K_ROW = 8 * Q4_K_BYTES;                 // 1152: one row of K = 2048
+constexpr int Q4K_MMA_PITCH = Q4K_ROW + 16;
+constexpr int MMA_STAGE_BYTES = 32 * Q4K_MMA_PITCH;     // 37 376
+static_assert(MMA_STAGE_BYTES % 128 == 0 && MMA_STAGE_BYTES >= STAGE_BYTES, "ring slot of the tensor-core GEMV");
+
+__device__ inline void mma_u8s8_k32(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                    uint32_t b1)
+{
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
+
+// Items of the tensor-core kernel, in order: (slot, token group, chunk), chunk fastest.  Every item
+// costs the same, so a CTA takes an equal share of the item count.
+struct MmaCursor {
+    int slot, group, chunk, groups;   // groups = token groups of `slot`
+};
+
+struct MmaWork {
+    int n_active, cpe, groups_sh;   // groups_sh = 0 when the shared expert is not served by these items
+    const int *prefix;              // [n_active + 1] exclusive prefix of ceil(count / 8) over the active slots (global)
+
+    __device__ inline int routed_groups() const { return n_active ? prefix[n_active] : 0; }
+    __device__ inline long total() const { return (long)cpe * (routed_groups() + groups_sh); }
+    __device__ inline MmaCursor at(long q) const
+    {
+        const int G = (int)(q / cpe), chunk = (int)(q % cpe);
+        const int rg = routed_groups();
+        if (G >= rg) return MmaCursor{n_active, G - rg, chunk, groups_sh};
+        int lo = 0, hi = n_active - 1;   // largest slot with prefix[slot] <= G
+        while (lo < hi) {
+            const int mid = (lo + hi + 1) >> 1;
+            if (prefix[mid] <= G) lo = mid; else hi = mid - 1;
+        }
+        return MmaCursor{lo, G - prefix[lo], chunk, prefix[lo + 1] - prefix[lo]};
+    }
+    __device__ inline void advance(MmaCursor &c) const
+    {
+        if (++c.chunk < cpe) return;
+        c.chunk = 0;
+        if (++c.group < c.groups) return;
+        c.group = 0;
+        c.slot++;
+        c.groups = c.slot < n_active ? prefix[c.slot + 1] - prefix[c.slot] : groups_sh;
+    }
+};
+
+struct Q4Hdr {
+    float d16, dmin;              // d / 16 (high nibbles stay in place) and dmin
+    uint32_t sca, scb, mna, mnb;  // 6-bit scales 0..3 / 4..7 and mins 0..3 / 4..7 as bytes
+};
+
+__device__ inline Q4Hdr q4k_hdr(const uint4 h)
+{
+    Q4Hdr o;
+    o.d16 = half_bits_to_float((uint16_t)(h.x & 0xffffu)) * 0.0625f;
+    o.dmin = half_bits_to_float((uint16_t)(h.x >> 16));
+    o.sca = h.y & 0x3F3F3F3Fu;
+    o.mna = h.z & 0x3F3F3F3Fu;
+    o.scb = (h.w & 0x0F0F0F0Fu) | ((h.y >> 2) & 0x30303030u);
+    o.mnb = ((h.w >> 4) & 0x0F0F0F0Fu) | ((h.z >> 2) & 0x30303030u);
+    return o;
+}
+
+// byte `i` (compile-time) of w, zero-extended
+template <int I> __device__ inline int byte_of(uint32_t w) { return (int)__byte_perm(w, 0u, 0x4440u + I); }
+
+// The compute warps' side: items [it, n_items) of this CTA starting at `cur`.
+__device__ inline bool run_items_q4k_mma(const GemvArgs &A, uint8_t *ring, const MmaWork &work, MmaCursor cur, int n_items,
+                                         int &it, int warp, int lane)
+{
+    const int g = lane >> 2, t = lane & 3;
+    const int r0 = ((g & 3) << 1) | (g >> 2);   // tile row under fragment row g (fragment row g + 8: tile row r0 + 8)
+    // this thread's share of the cross-warp sum: value (matrix rmt, fragment lane rsrc, register ri)
+    const int rq = warp * 16 + (lane & 15), rmt = lane >> 4;
+    const int rsrc = rq >> 2, ri = rq & 3;
+    const int rg = rsrc >> 2, rt = rsrc & 3;
+    const int r_row = (((rg & 3) << 1) | (rg >> 2)) + ((ri & 2) ? 8 : 0);
+    const int r_tok = 2 * rt + (ri & 1);
+    const uint32_t part_wr = (uint32_t)((lane >> 3) * Q4K_MMA_PITCH + Q4_K_BYTES * warp + (lane & 7) * 16);
+    const uint32_t part_rd = (uint32_t)((rmt * 4 + (rsrc >> 3)) * Q4K_MMA_PITCH + (rsrc & 7) * 16 + 4 * ri);
+
+    uint32_t bq[8][2];   // token g: its 8 bytes of each sub-block of block column `warp`
+    uint32_t bh = 0, bl = 0;
+    float dx0 = 0.f, dx1 = 0.f;
+    int r_orow = -1;
+#pragma unroll
+    for (int j = 0; j < 8; j++) bq[j][0] = bq[j][1] = 0;
+
+    int cur_slot = -1, cur_group = -1, m = 0, items_in_slot = 0, slot_groups = 0;
+    const int *list = nullptr;
+    bool is_sh = false, failed = false;
+    for (; it < n_items; it++) {
+        const int s = it % NSTAGE;
+        const uint32_t use = (uint32_t)(it / NSTAGE);
+        if (cur.slot != cur_slot) {
+            if (cur_slot >= 0 && (is_sh ? A.quant_dt_s : A.quant_dt_r) != 0)
+                finish_slot(A, is_sh ? work.n_active : cur_slot, items_in_slot, work.cpe * slot_groups, is_sh, list, m, warp,
+                            lane);
+            items_in_slot = 0;
+            cur_slot = cur.slot;
+            cur_group = -1;
+            slot_groups = cur.groups;
+            is_sh = cur.slot >= work.n_active;
+            if (is_sh) {
+                m = A.sh_count;
+                list = nullptr;
+            } else {
+                const int e = A.g.active[cur.slot];
+                m = A.g.count[e];
+                list = A.g.pairs + A.g.offset[e];
+            }
+        }
+        if (cur.group != cur_group) {   // the group's tokens: fragments of their quantised rows
+            cur_group = cur.group;
+            const int t0 = 8 * cur.group;
+            const int cnt = m - t0 < 8 ? m - t0 : 8;
+            const QAct &in = is_sh ? A.in_s : A.in_r;
+            bh = bl = 0;
+            if (g < cnt) {
+                const size_t row = is_sh ? (size_t)(A.sh_begin + t0 + g) : (size_t)(list[t0 + g] / A.top_k);
+                const int8_t *xp = in.qs + row * 2048 + 256 * warp + 8 * t;
+#pragma unroll
+                for (int c = 0; c < 4; c++) {
+                    const uint2 lo = *reinterpret_cast<const uint2 *>(xp + 64 * c);
+                    const uint2 hi = *reinterpret_cast<const uint2 *>(xp + 64 * c + 32);
+                    bq[2 * c][0] = lo.x; bq[2 * c][1] = lo.y;
+                    bq[2 * c + 1][0] = hi.x; bq[2 * c + 1][1] = hi.y;
+                }
+                if (t < 2) {   // sums of the quants under sub-blocks 4t .. 4t+3, as two signed byte digits
+                    const uint4 bs = *reinterpret_cast<const uint4 *>(in.bsums + row * 128 + 16 * warp + 8 * t);
+                    const uint32_t w4[4] = {bs.x, bs.y, bs.z, bs.w};
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        const int v = (int)(int16_t)(w4[i] & 0xffffu) + (int)(int16_t)(w4[i] >> 16);
+                        bh |= (uint32_t)((v >> 6) & 0xFF) << (8 * i);
+                        bl |= (uint32_t)(v & 63) << (8 * i);
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 8; j++) bq[j][0] = bq[j][1] = 0;
+            }
+            dx0 = dx1 = 0.f;
+            if (2 * t < cnt) {
+                const size_t row = is_sh ? (size_t)(A.sh_begin + t0 + 2 * t) : (size_t)(list[t0 + 2 * t] / A.top_k);
+                dx0 = in.d[row * 8 + warp];
+            }
+            if (2 * t + 1 < cnt) {
+                const size_t row = is_sh ? (size_t)(A.sh_begin + t0 + 2 * t + 1) : (size_t)(list[t0 + 2 * t + 1] / A.top_k);
+                dx1 = in.d[row * 8 + warp];
+            }
+            r_orow = -1;
+            if (r_tok < cnt) r_orow = is_sh ? A.n * A.top_k + A.sh_begin + t0 + r_tok : list[t0 + r_tok];
+        }
+        // a wait that runs out is recorded; the warp keeps walking its items (and meeting the barriers
+        // it shares with the other warps) without computing
+        if (!failed && A.debug != 2 && !mbar_wait(ring_full(ring, s), use & 1)) {
+            set_status(A.status, PMOE_ERR_TIMEOUT, 18, it);
+            failed = true;
+        }
+        uint8_t *stage = ring_stage(ring, s, A.stage_bytes);
+        const bool compute = !failed && A.debug != 1;
+        float acc[2][4];
+#pragma unroll
+        for (int mt = 0; mt < 2; mt++) {
+#pragma unroll
+            for (int i = 0; i < 4; i++) acc[mt][i] = 0.f;
+            if (!compute) continue;
+            const uint8_t *p0 = stage + (mt * 16 + r0) * Q4K_MMA_PITCH + Q4_K_BYTES * warp;
+            const uint8_t *p1 = p0 + 8 * Q4K_MMA_PITCH;
+            const Q4Hdr h0 = q4k_hdr(*reinterpret_cast<const uint4 *>(p0));
+            const Q4Hdr h1 = q4k_hdr(*reinterpret_cast<const uint4 *>(p1));
+            int ie[4] = {0, 0, 0, 0}, io[4] = {0, 0, 0, 0};   // even (low-nibble) and odd (high-nibble, x16) sub-blocks
+#pragma unroll
+            for (int c = 0; c < 4; c++) {
+                const uint2 q0 = *reinterpret_cast<const uint2 *>(p0 + 16 + 32 * c + 8 * t);
+                const uint2 q1 = *reinterpret_cast<const uint2 *>(p1 + 16 + 32 * c + 8 * t);
+                const uint32_t sw0 = c < 2 ? h0.sca : h0.scb, sw1 = c < 2 ? h1.sca : h1.scb;
+                int cc[4];
+                mma_u8s8_k32(cc, q0.x & 0x0F0F0F0Fu, q1.x & 0x0F0F0F0Fu, q0.y & 0x0F0F0F0Fu, q1.y & 0x0F0F0F0Fu, bq[2 * c][0],
+                             bq[2 * c][1]);
+                {
+                    const int s0 = (c & 1) ? byte_of<2>(sw0) : byte_of<0>(sw0);
+                    const int s1 = (c & 1) ? byte_of<2>(sw1) : byte_of<0>(sw1);
+                    ie[0] += cc[0] * s0; ie[1] += cc[1] * s0; ie[2] += cc[2] * s1; ie[3] += cc[3] * s1;
+                }
+                mma_u8s8_k32(cc, q0.x & 0xF0F0F0F0u, q1.x & 0xF0F0F0F0u, q0.y & 0xF0F0F0F0u, q1.y & 0xF0F0F0F0u,
+                             bq[2 * c + 1][0], bq[2 * c + 1][1]);
+                {
+                    const int s0 = (c & 1) ? byte_of<3>(sw0) : byte_of<1>(sw0);
+                    const int s1 = (c & 1) ? byte_of<3>(sw1) : byte_of<1>(sw1);
+                    io[0] += cc[0] * s0; io[1] += cc[1] * s0; io[2] += cc[2] * s1; io[3] += cc[3] * s1;
+                }
+            }
+            // mins: K positions 0..7 carry m_0..m_7 (lanes t = 0, 1), the rest is zero
+            const uint32_t am0 = t == 0 ? h0.mna : (t == 1 ? h0.mnb : 0u);
+            const uint32_t am1 = t == 0 ? h1.mna : (t == 1 ? h1.mnb : 0u);
+            int ch[4], cl[4];
+            mma_u8s8_k32(ch, am0, am1, 0u, 0u, bh, 0u);
+            mma_u8s8_k32(cl, am0, am1, 0u, 0u, bl, 0u);
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const Q4Hdr &h = i < 2 ? h0 : h1;
+                const float dx = (i & 1) ? dx1 : dx0;
+                acc[mt][i] = dx * (h.d16 * (float)(16 * ie[i] + io[i]) - h.dmin * (float)(64 * ch[i] + cl[i]));
+            }
+        }
+        // partial sums of this warp's block column into its own part of rows 0..7 of the slot
+        __syncwarp();
+#pragma unroll
+        for (int mt = 0; mt < 2; mt++)
+            *reinterpret_cast<float4 *>(stage + part_wr + mt * 4 * Q4K_MMA_PITCH) =
+                make_float4(acc[mt][0], acc[mt][1], acc[mt][2], acc[mt][3]);
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        float v = 0.f;
+#pragma unroll
+        for (int w = 0; w < GEMV_WARPS; w++) v += *reinterpret_cast<const float *>(stage + part_rd + Q4_K_BYTES * w);
+        const float up = __shfl_xor_sync(0xffffffffu, v, 16);
+        if (lane < 16 && r_orow >= 0 && compute)
+            A.out[(size_t)r_orow * A.rows_total + cur.chunk * 16 + r_row] = v / (1.f + expf(-v)) * up;   // silu(gate) * up
+        __syncwarp();
+        if (lane == 0) mbar_arrive(ring_empty(ring, s));
+        work.advance(cur);
+        items_in_slot++;
+    }
+    if (cur_slot >= 0 && (is_sh ? A.quant_dt_s : A.quant_dt_r) != 0)
+        finish_slot(A, is_sh ? work.n_active : cur_slot, items_in_slot, work.cpe * slot_groups, is_sh, list, m, warp, lane);
+    return !failed;
+}
+
+// DT_S: type of the shared expert's gate/up matrices served by this launch (0 = none).  A Q4_K shared
+// expert is one more slot of the tensor-core items; other types follow as items of the streaming kind.
+template <int DT_S>
+__global__ void __launch_bounds__(GEMV_THREADS, 2) k_gate_up_q4k_mma(const GemvArgs A)
+{
+    extern __shared__ __align__(128) uint8_t ring[];
+    __shared__ int s_prefix1[2];
+    __shared__ MmaCursor s_first;
+    __shared__ int s_items;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    pdl_wait();
+    pdl_launch_dependents();
+
+    MmaWork work;
+    work.n_active = A.routed ? *A.g.n_active : 0;
+    work.cpe = A.rows_total / 16;
+    work.groups_sh = (DT_S == PMOE_Q4_K && A.has_shared) ? (A.sh_count + GEMV_TG_MMA - 1) / GEMV_TG_MMA : 0;
+    work.prefix = A.g.cost_prefix_mma;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < NSTAGE; s++) {
+            mbar_init(ring_full(ring, s), 1);
+            mbar_init(ring_empty(ring, s), GEMV_WARPS);
+        }
+        fence_mbar_init();
+        const long total = work.total();
+        const long q0 = total * blockIdx.x / gridDim.x, q1 = total * (blockIdx.x + 1) / gridDim.x;
+        s_items = (int)(q1 - q0);
+        s_first = q1 > q0 ? work.at(q0) : MmaCursor{0, 0, 0, 0};
+        s_prefix1[0] = s_prefix1[1] = 0;
+    }
+    __syncthreads();
+    const int n_mma = s_items;
+    const MmaCursor first = s_first;
+
+    // items of the streaming kind for a shared expert of another type: an equal share of their cost
+    constexpr bool STREAM_SH = DT_S != 0 && DT_S != PMOE_Q4_K;
+    constexpr int DT_S1 = STREAM_SH ? DT_S : PMOE_Q8_0;
+    using CS = Cfg<DT_S1, 2>;
+    Plan plan;
+    Cursor scur{0, 0};
+    int n_sh = 0;
+    if (STREAM_SH && A.has_shared) {
+        plan.n_active = 0;
+        plan.has_shared = 1;
+        plan.cpe_r = plan.cpe_s = A.rows_total / CS::ROWS;
+        plan.shared_mma = DT_S == PMOE_Q8_0 && A.sh_count >= SHARED_MMA_MIN;
+        plan.cost_shared = plan.shared_mma ? shared_mma_cost<2>(A.sh_count) : (A.sh_count + CS::TGK - 1) / CS::TGK;
+        plan.prefix = s_prefix1;
+        const long total = plan.total_cost();
+        scur = plan.find(total * blockIdx.x / gridDim.x);
+        const Cursor last = plan.find(total * (blockIdx.x + 1) / gridDim.x);
+        n_sh = plan.index(last) - plan.index(scur);
+    }
+    if (n_mma + n_sh <= 0) return;
+
+    if (warp == GEMV_WARPS) {   // the producer warp: every lane copies one row of an item
+        if (A.debug == 2) return;
+        MmaCursor pc = first;
+        int issued = 0;
+        bool ok = true;
+        for (; issued < n_mma; issued++) {
+            const int s = issued % NSTAGE;
+            const uint32_t use = (uint32_t)(issued / NSTAGE);
+            if (use > 0) {
+                int w = 1;
+                if (lane == 0) w = mbar_wait(ring_empty(ring, s), (use - 1) & 1) ? 1 : 0;
+                w = __shfl_sync(0xffffffffu, w, 0);
+                if (!w) {
+                    if (lane == 0) set_status(A.status, PMOE_ERR_TIMEOUT, 23, issued);
+                    ok = false;
+                    break;
+                }
+            }
+            const uint8_t *base;
+            if (pc.slot < work.n_active) base = (lane < 16 ? A.w0 : A.w1) + (size_t)A.g.active[pc.slot] * A.expert_bytes;
+            else base = lane < 16 ? A.sw0 : A.sw1;
+            uint64_t *full = ring_full(ring, s);
+            if (lane == 0) mbar_expect_tx(full, 32 * Q4K_ROW);
+            __syncwarp();
+            bulk_g2s(ring_stage(ring, s, A.stage_bytes) + lane * Q4K_MMA_PITCH,
+                     base + (size_t)(pc.chunk * 16 + (lane & 15)) * Q4K_ROW, Q4K_ROW, full);
+            work.advance(pc);
+        }
+        if (lane == 0) {
+            if (STREAM_SH && ok && n_sh > 0) {
+                Producer<DT_S1, DT_S1, 2> prod{A, plan, ring, scur, issued, n_mma + n_sh};
+                for (int i = 0; i < n_sh; i++)
+                    if (!prod.issue_next()) { prod.issued--; break; }
+                issued = prod.issued;
+            }
+            drain_ring(ring, issued);
+        }
+        return;
+    }
+    int it = 0;
+    bool ok = run_items_q4k_mma(A, ring, work, first, n_mma, it, warp, lane);
+    if constexpr (STREAM_SH) {
+        if (ok && n_sh > 0) {
+            if (DT_S == PMOE_Q8_0 && plan.shared_mma)
+                run_items_shared_mma<2>(A, ring, plan, scur, it, n_mma + n_sh, A.in_s, warp, lane);
+            else
+                run_items<DT_S1, 2>(A, ring, plan, true, scur, 1, it, n_mma + n_sh, A.in_s, warp, lane);
+        }
     }
 }
 
@@ -1184,6 +1550,17 @@ bool gemv_supported(int dtype, int K, int rows, const char **why)
 
 static int g_sm_count = 0;
 
+static int sm_count()
+{
+    if (!g_sm_count) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev);
+        if (g_sm_count <= 0) g_sm_count = 148;
+    }
+    return g_sm_count;
+}
+
 template <int DT_R, int DT_S, int NMAT>
 static cudaError_t launch_gemv_t(const GemvArgs &A, cudaStream_t s)
 {
@@ -1195,13 +1572,7 @@ static cudaError_t launch_gemv_t(const GemvArgs &A, cudaStream_t s)
         if (e != cudaSuccess) return e;
         configured = true;
     }
-    if (!g_sm_count) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev);
-        if (g_sm_count <= 0) g_sm_count = 148;
-    }
-    cudaError_t e = launch_pdl(kern, dim3(2 * g_sm_count), dim3(GEMV_THREADS), smem, s, A);
+    cudaError_t e = launch_pdl(kern, dim3(2 * sm_count()), dim3(GEMV_THREADS), smem, s, A);
     count_launch();
     return e;
 }
@@ -1263,6 +1634,28 @@ static cudaError_t launch_gemv(const GemvArgs &A, int dt_r, int dt_s, cudaStream
     return cudaErrorInvalidValue;
 }
 
+template <int DT_S> static cudaError_t launch_q4k_mma_t(const GemvArgs &A, cudaStream_t s)
+{
+    constexpr size_t smem = 128 + (size_t)NSTAGE * MMA_STAGE_BYTES;
+    auto kern = k_gate_up_q4k_mma<DT_S>;
+    static bool configured = false;  // per instantiation
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    cudaError_t e = launch_pdl(kern, dim3(2 * sm_count()), dim3(GEMV_THREADS), smem, s, A);
+    count_launch();
+    return e;
+}
+
+// PMOE_MMA=0 in the environment keeps the dp4a kernels for Q4_K gate/up (comparison runs)
+static bool mma_enabled()
+{
+    static const bool on = !(getenv("PMOE_MMA") && atoi(getenv("PMOE_MMA")) == 0);
+    return on;
+}
+
 cudaError_t launch_gate_up(const LayerDev &L, const Workspace &ws, int n, int top_k, bool routed, bool shared,
                            cudaStream_t s)
 {
@@ -1282,11 +1675,23 @@ cudaError_t launch_gate_up(const LayerDev &L, const Workspace &ws, int n, int to
     A.out = ws.act;
     A.status = ws.status;
     A.debug = getenv("PMOE_DEBUG") ? atoi(getenv("PMOE_DEBUG")) : 0;
+    A.stage_bytes = STAGE_BYTES;
     A.slot_done = ws.slot_done;
     A.quant_dt_r = routed ? L.down_dtype : 0;
     A.quant_dt_s = shared ? L.sh_down_dtype : 0;
     A.q8k_out = ws.act_q8k;
     A.q80_out = ws.act_q80;
+    if (routed && L.gate_dtype == PMOE_Q4_K && L.H == 2048 && L.F == 512 && mma_enabled()) {
+        A.stage_bytes = MMA_STAGE_BYTES;
+        switch (shared ? L.sh_gate_dtype : 0) {
+        case 0: return launch_q4k_mma_t<0>(A, s);
+        case PMOE_Q4_K: return launch_q4k_mma_t<PMOE_Q4_K>(A, s);
+        case PMOE_Q5_K: return launch_q4k_mma_t<PMOE_Q5_K>(A, s);
+        case PMOE_Q6_K: return launch_q4k_mma_t<PMOE_Q6_K>(A, s);
+        case PMOE_Q8_0: return launch_q4k_mma_t<PMOE_Q8_0>(A, s);
+        }
+        A.stage_bytes = STAGE_BYTES;
+    }
     // a kernel without routed items still needs a routed type to instantiate; reuse the shared one
     return launch_gemv<2>(A, routed ? L.gate_dtype : L.sh_gate_dtype, shared ? L.sh_gate_dtype : 0, s);
 }
@@ -1312,6 +1717,7 @@ cudaError_t launch_down(const LayerDev &L, const Workspace &ws, const float *w, 
     A.scale_s = ws.sh_sigmoid;
     A.status = ws.status;
     A.debug = getenv("PMOE_DEBUG") ? atoi(getenv("PMOE_DEBUG")) : 0;
+    A.stage_bytes = STAGE_BYTES;
     return launch_gemv<1>(A, routed ? L.down_dtype : L.sh_down_dtype, shared ? L.sh_down_dtype : 0, s);
 }
 

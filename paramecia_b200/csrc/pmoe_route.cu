@@ -470,65 +470,66 @@ cudaError_t launch_topk(const LayerDev &L, const Workspace &ws, const float *log
 // (every pair's rows are computed on their own and combined in slot order).
 constexpr int GROUP_THREADS = 1024;
 
-// inclusive scan of five integers per thread across the CTA: shuffles inside a warp, one pass
+// inclusive scan of six integers per thread across the CTA: shuffles inside a warp, one pass
 // over the 32 warp totals, three barriers in all
+constexpr int NSCAN = 6;
 struct Scan5 {
-    int v[5];
+    int v[NSCAN];
 };
 
-__device__ inline Scan5 block_scan5(Scan5 x, int (*warp_tot)[5], int tid)
+__device__ inline Scan5 block_scan5(Scan5 x, int (*warp_tot)[NSCAN], int tid)
 {
     const int lane = tid & 31, warp = tid >> 5;
 #pragma unroll
     for (int off = 1; off < 32; off <<= 1) {
 #pragma unroll
-        for (int i = 0; i < 5; i++) {
+        for (int i = 0; i < NSCAN; i++) {
             const int y = __shfl_up_sync(0xffffffffu, x.v[i], off);
             if (lane >= off) x.v[i] += y;
         }
     }
     if (lane == 31) {
 #pragma unroll
-        for (int i = 0; i < 5; i++) warp_tot[warp][i] = x.v[i];
+        for (int i = 0; i < NSCAN; i++) warp_tot[warp][i] = x.v[i];
     }
     __syncthreads();
     if (warp == 0) {
         Scan5 t;
 #pragma unroll
-        for (int i = 0; i < 5; i++) t.v[i] = warp_tot[lane][i];
+        for (int i = 0; i < NSCAN; i++) t.v[i] = warp_tot[lane][i];
 #pragma unroll
         for (int off = 1; off < 32; off <<= 1) {
 #pragma unroll
-            for (int i = 0; i < 5; i++) {
+            for (int i = 0; i < NSCAN; i++) {
                 const int y = __shfl_up_sync(0xffffffffu, t.v[i], off);
                 if (lane >= off) t.v[i] += y;
             }
         }
 #pragma unroll
-        for (int i = 0; i < 5; i++) warp_tot[lane][i] = t.v[i];   // inclusive totals up to and including warp `lane`
+        for (int i = 0; i < NSCAN; i++) warp_tot[lane][i] = t.v[i];   // inclusive totals up to and including warp `lane`
     }
     __syncthreads();
     if (warp > 0) {
 #pragma unroll
-        for (int i = 0; i < 5; i++) x.v[i] += warp_tot[warp - 1][i];
+        for (int i = 0; i < NSCAN; i++) x.v[i] += warp_tot[warp - 1][i];
     }
     return x;
 }
 
 __global__ void __launch_bounds__(GROUP_THREADS) k_group(const uint32_t *__restrict__ idx, int npairs, int base,
-                                                         int E_local, Groups g)
+                                                         int E_local, int stride, int rem, Groups g)
 {
     __shared__ int cnt[1024];
-    __shared__ int warp_tot[32][5];
+    __shared__ int warp_tot[32][NSCAN];
     const int tid = threadIdx.x;
     cnt[tid] = 0;
     pdl_wait();
     pdl_launch_dependents();
     __syncthreads();
     for (int p = tid; p < npairs; p += GROUP_THREADS) {
-        uint32_t e = idx[p] - (uint32_t)base;  // wraps to a large value when below base
+        const int e = local_expert(idx[p], base, E_local, stride, rem);
         int pos = -1;
-        if (e < (uint32_t)E_local) pos = atomicAdd(&cnt[e], 1);
+        if (e >= 0) pos = atomicAdd(&cnt[e], 1);
         g.pos[p] = pos;
     }
     __syncthreads();
@@ -537,8 +538,9 @@ __global__ void __launch_bounds__(GROUP_THREADS) k_group(const uint32_t *__restr
     const int cost = (c + GEMV_TG - 1) / GEMV_TG;
     const int tiles = (c + PREFILL_NT - 1) / PREFILL_NT;
     const int wcost = (c + GEMV_TG_WIDE - 1) / GEMV_TG_WIDE;
+    const int mcost = (c + GEMV_TG_MMA - 1) / GEMV_TG_MMA;
     Scan5 in;
-    in.v[0] = c; in.v[1] = flag; in.v[2] = cost; in.v[3] = tiles; in.v[4] = wcost;
+    in.v[0] = c; in.v[1] = flag; in.v[2] = cost; in.v[3] = tiles; in.v[4] = wcost; in.v[5] = mcost;
     const Scan5 sc = block_scan5(in, warp_tot, tid);   // inclusive
     const int excl = sc.v[0] - c;
     if (tid < E_local) {
@@ -549,6 +551,7 @@ __global__ void __launch_bounds__(GROUP_THREADS) k_group(const uint32_t *__restr
             g.active[slot] = tid;
             g.cost_prefix[slot] = sc.v[2] - cost;
             g.cost_prefix_wide[slot] = sc.v[4] - wcost;
+            g.cost_prefix_mma[slot] = sc.v[5] - mcost;
             g.tile_prefix[slot] = sc.v[3] - tiles;
             for (int i = 0; i < tiles; i++) g.tile_table[sc.v[3] - tiles + i] = make_int2(tid, i);
         }
@@ -558,6 +561,7 @@ __global__ void __launch_bounds__(GROUP_THREADS) k_group(const uint32_t *__restr
         *g.n_active = sc.v[1];
         g.cost_prefix[sc.v[1]] = sc.v[2];
         g.cost_prefix_wide[sc.v[1]] = sc.v[4];
+        g.cost_prefix_mma[sc.v[1]] = sc.v[5];
         g.tile_prefix[sc.v[1]] = sc.v[3];
     }
     __syncthreads();   // every thread has read its count
@@ -566,7 +570,7 @@ __global__ void __launch_bounds__(GROUP_THREADS) k_group(const uint32_t *__restr
     for (int p = tid; p < npairs; p += GROUP_THREADS) {
         int pos = g.pos[p];
         if (pos >= 0) {
-            uint32_t e = idx[p] - (uint32_t)base;
+            const int e = local_expert(idx[p], base, E_local, stride, rem);
             g.pairs[cnt[e] + pos] = p;
         }
     }
@@ -575,7 +579,8 @@ __global__ void __launch_bounds__(GROUP_THREADS) k_group(const uint32_t *__restr
 cudaError_t launch_group(const LayerDev &L, const Workspace &ws, const uint32_t *idx, int n, int top_k,
                          cudaStream_t s)
 {
-    cudaError_t e = launch_pdl(k_group, dim3(1), dim3(GROUP_THREADS), 0, s, idx, n * top_k, L.expert_base, L.E_local, ws.groups);
+    cudaError_t e = launch_pdl(k_group, dim3(1), dim3(GROUP_THREADS), 0, s, idx, n * top_k, L.expert_base, L.E_local, L.ep_stride, L.ep_rem,
+                               ws.groups);
     count_launch();
     return e;
 }

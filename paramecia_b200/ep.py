@@ -54,15 +54,17 @@ class _LibOps:
                                      _TORCH_TO_PMOE[out.dtype], _stream_ptr(parts.device)))
 
 
-def expert_owner(idx: torch.Tensor, experts_per_rank: int) -> torch.Tensor:
-    """Rank that owns each expert id under the contiguous placement (expert e on rank e // (E/N))."""
+def expert_owner(idx: torch.Tensor, experts_per_rank: int, n_ranks: int = 0, round_robin: bool = False) -> torch.Tensor:
+    """Rank that owns each expert id: e // (E/N) under the contiguous placement, e % N under round-robin."""
+    if round_robin:
+        return torch.remainder(idx, n_ranks)
     return torch.div(idx, experts_per_rank, rounding_mode="floor")
 
 
-def mask_for_destinations(idx: torch.Tensor, n_ranks: int, experts_per_rank: int) -> torch.Tensor:
+def mask_for_destinations(idx: torch.Tensor, n_ranks: int, experts_per_rank: int, round_robin: bool = False) -> torch.Tensor:
     """[N, n, k] routing tables, one per destination rank: ids the destination does not own become
     INVALID_EXPERT, so that a row contributes on a rank only through that rank's experts."""
-    owner = expert_owner(idx, experts_per_rank)                      # [n, k]
+    owner = expert_owner(idx, experts_per_rank, n_ranks, round_robin)  # [n, k]
     dest = torch.arange(n_ranks, device=idx.device).view(-1, 1, 1)   # [N, 1, 1]
     return torch.where(owner.unsqueeze(0) == dest, idx.unsqueeze(0), torch.full_like(idx, INVALID_EXPERT).unsqueeze(0))
 
@@ -86,8 +88,9 @@ class ExpertParallelMoe:
         if self.E % self.N:
             raise ValueError("the number of experts must be divisible by the number of ranks")
         self.per_rank = self.E // self.N
-        if block.num_experts_local != self.per_rank or block.expert_base != self.rank * self.per_rank:
-            raise ValueError("block must hold experts [rank*E/N, (rank+1)*E/N)")
+        self.round_robin = getattr(block, "ep_placement", 0) == 1
+        if block.num_experts_local != self.per_rank or (not self.round_robin and block.expert_base != self.rank * self.per_rank):
+            raise ValueError("block must hold experts [rank*E/N, (rank+1)*E/N), or rank, rank+N, ... (round-robin)")
         self._buf_n = -1
         # NCCL takes several collectives as one group; gloo (CPU tests) runs them one by one
         self._coalesce = dist.get_backend(group) == "nccl"
@@ -125,19 +128,51 @@ class ExpertParallelMoe:
             return _coalescing_manager(group=self.group, device=device, async_ops=False)
         return contextlib.nullcontext()
 
-    def forward_into(self, x: torch.Tensor, out: torch.Tensor, stats: Optional[dict] = None):
-        """x [n, H] (this rank's tokens) -> out [n, H]; every rank must call with the same n."""
+    @staticmethod
+    def default_mode() -> str:
+        return "all_gather"
+
+    def _mark(self, profile, name):
+        if profile:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            self._events[name] = ev
+
+    def trace_experts(self, x: torch.Tensor, reps: int) -> dict:
+        """Milliseconds per phase of this rank's expert kernels on the rows a dispatch of `x` delivers."""
+        out = torch.empty((x.shape[0], self.H), dtype=torch.bfloat16, device=x.device)
+        self.forward_into(x, out)
+        n = x.shape[0]
+        own = (self.rank * n, n) if self.block.has_shared else None
+        acc = {}
+        self.block.trace(True)
+        for i in range(reps + 3):
+            self.block.experts_forward_batched(self.recv_x, self.recv_idx, self.recv_w, self.k, shared_rows=own, out=self.part)
+            t = self.block.trace_read()
+            if i >= 3:
+                for k_, v in t.items():
+                    acc[k_] = acc.get(k_, 0.0) + v / reps
+        self.block.trace(False)
+        return acc
+
+    def forward_into(self, x: torch.Tensor, out: torch.Tensor, stats: Optional[dict] = None, profile: bool = False):
+        """x [n, H] (this rank's tokens) -> out [n, H]; every rank must call with the same n.  With `profile` the call
+        brackets the dispatch and the combine with CUDA events on the launching stream, waits for them and returns
+        {"dispatch", "combine", "total"} in milliseconds."""
         n = x.shape[0]
         N, k, g = self.N, self.k, self.group
         x = x.contiguous()
         self._buffers(n, x)
+        self._events = {}
+        self._mark(profile, "t0")
         self.block.route(x, out=(self.logits, self.w, self.idx))
+        self._mark(profile, "d0")
         if stats is not None:
             stats.update(router_logits=self.logits, top_indices=self.idx, top_weights=self.w)
         # -- dispatch: rows, ids and weights of every token to every rank that may own one of its experts
         if self.mode == "all_to_all":
             self.send_x.copy_(x.unsqueeze(0).expand(N, n, self.H))
-            self.send_idx.copy_(mask_for_destinations(self.idx, N, self.per_rank))
+            self.send_idx.copy_(mask_for_destinations(self.idx, N, self.per_rank, self.round_robin))
             self.send_w.copy_(self.w.unsqueeze(0).expand(N, n, k))
             dist.all_to_all_single(self.recv_x, self.send_x.view(N * n, self.H), group=g)
             dist.all_to_all_single(self.recv_idx, self.send_idx.view(N * n, k), group=g)
@@ -151,8 +186,10 @@ class ExpertParallelMoe:
         # -- this rank's experts over everything it received, pre-reduced per token.  Rows
         # [rank*n, (rank+1)*n) are this rank's own tokens: the shared expert rides along on those,
         # so each token's shared row is computed once, on its home rank, in the same kernels.
+        self._mark(profile, "d1")
         own = (self.rank * n, n) if self.block.has_shared else None
         self.block.experts_forward_batched(self.recv_x, self.recv_idx, self.recv_w, k, shared_rows=own, out=self.part)
+        self._mark(profile, "c0")
         # -- combine: the partial rows go back to the token's home rank and are added in rank order
         if self.mode == "all_to_all":
             dist.all_to_all_single(self.back.view(N * n, self.H), self.part, group=g)
@@ -162,6 +199,12 @@ class ExpertParallelMoe:
         else:
             dist.reduce_scatter_tensor(self.home, self.part, group=g)
             out.copy_(self.home)
+        if profile:
+            self._mark(True, "c1")
+            torch.cuda.synchronize()
+            e = self._events
+            return dict(dispatch=e["d0"].elapsed_time(e["d1"]), combine=e["c0"].elapsed_time(e["c1"]),
+                        total=e["t0"].elapsed_time(e["c1"]))
         return out
 
     def forward(self, x: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:

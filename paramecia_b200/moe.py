@@ -107,8 +107,12 @@ def qmatmul_noalloc(w: "QTensor", x: torch.Tensor, y: torch.Tensor) -> torch.Ten
     y [m, rows] f32 (both CUDA, contiguous) and the quantised activations use the library's built-in
     96 KB buffer, so m * cols is limited (about 80 000).  Calls on one device must not overlap."""
     rows, cols = w.shape
-    if not (x.is_cuda and y.is_cuda and x.is_contiguous() and y.is_contiguous() and w.data.is_cuda):
-        raise ValueError("qmatmul_noalloc takes contiguous CUDA tensors it does not have to copy")
+    if not w.data.is_cuda:
+        raise ValueError("qmatmul_noalloc takes CUDA tensors it does not have to copy")
+    if x.dim() != 2:
+        raise ValueError("x must be [m, cols]")
+    _check_buffer("x", x, (x.shape[0], cols), torch.float32, w.data.device)
+    _check_buffer("y", y, (x.shape[0], rows), torch.float32, w.data.device)
     check(lib().pmoe_qmatmul_noalloc(x.device.index or 0, w.dtype, w.data.data_ptr(), rows, cols, x.data_ptr(),
                                      x.shape[0], y.data_ptr(), _stream_ptr(x.device)))
     return y
@@ -127,6 +131,36 @@ def add_rms_norm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: Opt
                                   None if weight is None else weight.contiguous().data_ptr(),
                                   n, H, float(eps), new_resid.data_ptr(), y.data_ptr(), _stream_ptr(resid.device)))
     return new_resid, y
+
+
+def add_rms_norm_into(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: Optional[torch.Tensor], eps: float,
+                      resid_out: torch.Tensor, y: torch.Tensor) -> None:
+    """`add_rms_norm` into caller-owned f32 [n, H] buffers (nothing is allocated); `resid_out` may be `resid`."""
+    n, H = resid.shape
+    for name, t in (("resid", resid), ("resid_out", resid_out), ("y", y)) + ((("delta", delta),) if delta is not None else ()):
+        _check_buffer(name, t, (n, H), torch.float32, resid.device)
+    if weight is not None:
+        _check_buffer("weight", weight, (H,), torch.float32, resid.device)
+    check(lib().pmoe_add_rms_norm(resid.device.index or 0, resid.data_ptr(),
+                                  None if delta is None else delta.data_ptr(),
+                                  None if weight is None else weight.data_ptr(),
+                                  n, H, float(eps), resid_out.data_ptr(), y.data_ptr(), _stream_ptr(resid.device)))
+
+
+def _check_buffer(name: str, t: torch.Tensor, shape, dtype, device) -> None:
+    """A caller-owned buffer whose raw pointer goes to the C ABI: the library cannot see its size or type, so a wrong
+    one would be read or written out of bounds on the device.  Refuse it here."""
+    if not isinstance(t, torch.Tensor):
+        raise ValueError(f"{name} must be a torch tensor")
+    if t.device != torch.device(device):
+        raise ValueError(f"{name} must live on {device} (got {t.device})")
+    dtypes = dtype if isinstance(dtype, (tuple, list)) else (dtype,)
+    if t.dtype not in dtypes:
+        raise ValueError(f"{name} must be {' or '.join(str(d) for d in dtypes)} (got {t.dtype})")
+    if tuple(t.shape) != tuple(shape):
+        raise ValueError(f"{name} must have shape {tuple(shape)} (got {tuple(t.shape)})")
+    if not t.is_contiguous():
+        raise ValueError(f"{name} must be contiguous")
 
 
 @dataclass
@@ -149,7 +183,8 @@ class MoeBlock:
     def __init__(self, gate_exps: QTensor, up_exps: QTensor, down_exps: QTensor, gate: torch.Tensor,
                  num_experts_per_tok: int, shared_expert: Optional[SharedExpertWeights] = None,
                  device="cuda:0", max_tokens: int = 256, router_bias: Optional[torch.Tensor] = None,
-                 num_experts: Optional[int] = None, expert_base: int = 0, training_mode: bool = False):
+                 num_experts: Optional[int] = None, expert_base: int = 0, training_mode: bool = False,
+                 ep_rank: int = 0, ep_size: int = 0, ep_placement: str = "contiguous"):
         self.device = torch.device(device)
         if self.device.type != "cuda":
             raise PmoeError(-9, "MoeBlock needs a CUDA device; libpmoe has no CPU path")
@@ -160,6 +195,10 @@ class MoeBlock:
         self.num_experts = int(num_experts) if num_experts is not None else int(gate.shape[0])
         self.num_experts_local = E_local
         self.expert_base = int(expert_base)
+        if ep_placement not in ("contiguous", "round_robin"):
+            raise ValueError("ep_placement must be 'contiguous' or 'round_robin'")
+        self.ep_placement = 1 if ep_placement == "round_robin" else 0
+        self.ep_rank, self.ep_size = int(ep_rank), int(ep_size)
         self.num_experts_per_tok = int(num_experts_per_tok)
         self.max_tokens = int(max_tokens)
         if tuple(up_exps.shape) != (E_local, F, H) or tuple(down_exps.shape) != (E_local, H, F):
@@ -198,6 +237,7 @@ class MoeBlock:
         d.router_bias = None if self._keep["bias"] is None else self._keep["bias"].data_ptr()
         d.weights_location = 2
         d.training_mode = 1 if training_mode else 0
+        d.ep_placement, d.ep_rank, d.ep_size = self.ep_placement, self.ep_rank, self.ep_size
         self.has_shared = shared_expert is not None
         self._desc = d
         self._h = C.c_void_p()
@@ -225,6 +265,17 @@ class MoeBlock:
         if hidden_states.shape[-1] != self.hidden_dim:
             raise ValueError(f"last dim must be {self.hidden_dim}")
         return hidden_states.reshape(-1, self.hidden_dim).contiguous()
+
+    def local_mask(self, idx: torch.Tensor) -> torch.Tensor:
+        """Which entries of a routing table name an expert this handle holds."""
+        idx = idx.to(torch.int64)
+        if self.ep_placement == 1:
+            return (idx >= 0) & (idx < self.num_experts) & (idx % self.ep_size == self.ep_rank)
+        return (idx >= self.expert_base) & (idx < self.expert_base + self.num_experts_local)
+
+    def resident_bytes(self) -> int:
+        """Bytes of weights this handle keeps in HBM."""
+        return int(sum(v.numel() * v.element_size() for v in self._keep.values() if v is not None))
 
     def weight_bytes(self, distinct_experts: int) -> int:
         """Algorithmic weight bytes one decode call streams when `distinct_experts` experts are hit."""
@@ -262,7 +313,11 @@ class MoeBlock:
 
     def forward_into(self, x: torch.Tensor, out: torch.Tensor):
         """forward with caller-owned buffers and no stats (nothing is allocated; graph-capturable)."""
+        if x.dim() != 2 or x.shape[1] != self.hidden_dim:
+            raise ValueError(f"x must be [n, {self.hidden_dim}]")
         n = x.shape[0]
+        _check_buffer("x", x, (n, self.hidden_dim), tuple(_TORCH_TO_PMOE), self.device)
+        _check_buffer("out", out, (n, self.hidden_dim), tuple(_TORCH_TO_PMOE), self.device)
         check(lib().pmoe_forward(self._h, x.data_ptr(), _TORCH_TO_PMOE[x.dtype], n, out.data_ptr(),
                                  _TORCH_TO_PMOE[out.dtype], None, None, None, _stream_ptr(self.device)))
 
@@ -273,6 +328,9 @@ class MoeBlock:
         n = x.shape[0]
         if out is not None:
             logits, w, idx = out
+            _check_buffer("router_logits", logits, (n, self.num_experts), torch.float32, self.device)
+            _check_buffer("top_weights", w, (n, self.num_experts_per_tok), torch.float32, self.device)
+            _check_buffer("top_indices", idx, (n, self.num_experts_per_tok), torch.int32, self.device)
         else:
             logits = torch.empty((n, self.num_experts), dtype=torch.float32, device=self.device)
             idx = torch.empty((n, self.num_experts_per_tok), dtype=torch.int32, device=self.device)
@@ -313,6 +371,7 @@ class MoeBlock:
             out_dtype = out_dtype or hidden_states.dtype
             out = torch.empty((n, self.hidden_dim), dtype=out_dtype, device=self.device)
         else:
+            _check_buffer("out", out, (n, self.hidden_dim), tuple(_TORCH_TO_PMOE), self.device)
             out_dtype = out.dtype
         if shared_rows is not None:
             check(lib().pmoe_experts_forward_ep(self._h, x.data_ptr(), _TORCH_TO_PMOE[x.dtype], idx.data_ptr(),

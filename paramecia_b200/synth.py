@@ -237,7 +237,7 @@ def make_layer(H=2048, F=512, E=512, k=10, preset="q4k_m", seed=0, device="cpu",
 
 
 def make_block(t: Dict[str, object], device="cuda:0", max_tokens=256, expert_base=0, E_local: Optional[int] = None,
-               training_mode=False):
+               training_mode=False, ep_rank=0, ep_size=0):
     """Builds a MoeBlock from make_layer() output; an expert slice gives one expert-parallel rank."""
     from .moe import MoeBlock, QTensor, SharedExpertWeights
     H, F, E, k = t["H"], t["F"], t["E"], t["k"]
@@ -256,7 +256,33 @@ def make_block(t: Dict[str, object], device="cuda:0", max_tokens=256, expert_bas
     return MoeBlock(sl("gate", t["gate_dtype"], F, H), sl("up", t["up_dtype"], F, H), sl("down", t["down_dtype"], H, F),
                     t["router_w"], k, shared_expert=sh, device=device, max_tokens=max_tokens,
                     router_bias=t["router_bias"], num_experts=E, expert_base=expert_base,
-                    training_mode=training_mode)
+                    training_mode=training_mode, ep_rank=ep_rank, ep_size=ep_size)
+
+
+def make_rank_block(t: Dict[str, object], device, max_tokens: int, rank: int, world: int, placement: str = "contiguous"):
+    """The MoeBlock of rank `rank` of `world` expert-parallel ranks: E / world routed experts, contiguous
+    (rank * E/world ...) or round-robin (rank, rank + world, ...), router and shared expert whole."""
+    from .moe import MoeBlock, QTensor, SharedExpertWeights
+    from ._lib import row_bytes
+    H, F, E, k = t["H"], t["F"], t["E"], t["k"]
+    if world <= 1:
+        return make_block(t, device, max_tokens=max_tokens)
+    El = E // world
+    if placement == "contiguous":
+        return make_block(t, device, max_tokens=max_tokens, expert_base=rank * El, E_local=El, ep_rank=rank, ep_size=world)
+
+    def pick(name, dtype, rows, cols):   # experts rank, rank + world, ... gathered into one tensor
+        per = rows * row_bytes(dtype, cols)
+        return QTensor(t[name].reshape(E, per)[rank::world].contiguous().reshape(-1), dtype, (El, rows, cols))
+
+    sh = None
+    if t["shared"] is not None:
+        s = t["shared"]
+        sh = SharedExpertWeights(QTensor(s["gate"], s["gate_dtype"], (F, H)), QTensor(s["up"], s["up_dtype"], (F, H)),
+                                 QTensor(s["down"], s["down_dtype"], (H, F)), s["gate_inp"])
+    return MoeBlock(pick("gate", t["gate_dtype"], F, H), pick("up", t["up_dtype"], F, H), pick("down", t["down_dtype"], H, F),
+                    t["router_w"], k, shared_expert=sh, device=device, max_tokens=max_tokens,
+                    router_bias=t["router_bias"], num_experts=E, ep_rank=rank, ep_size=world, ep_placement="round_robin")
 
 
 def layer_bytes(t: Dict[str, object]) -> int:

@@ -91,7 +91,9 @@ def test_router_bias_and_ties(E):
 CASES = [
     # preset, E, k, n, x dtype
     ("q4k", 512, 10, 1, torch.float32),       # benchmark configuration 1 (one f32 token, all Q4_K)
-    ("q4k_m", 512, 10, 4, torch.bfloat16),    # benchmark configuration 2 shapes
+    ("q4k_m", 512, 10, 1, torch.bfloat16),    # benchmark configuration 2: the whole batch sweep 1 / 4 / 16 / 64
+    ("q4k_m", 512, 10, 4, torch.bfloat16),
+    ("q4k_m", 512, 10, 16, torch.bfloat16),
     ("q4k_m", 512, 10, 64, torch.bfloat16),
     ("q8_0", 64, 6, 17, torch.bfloat16),
     ("q6k", 16, 2, 3, torch.float32),
@@ -108,7 +110,7 @@ CASES = [
 
 @pytest.mark.parametrize("preset,E,k,n,xdtype", CASES)
 def test_block_matches_oracle(preset, E, k, n, xdtype):
-    t = synth.make_layer(E=E, k=k, preset=preset, seed=21)
+    t = synth.make_layer(E=E, k=k, preset=preset, seed=21, device=DEV if E >= 256 else "cpu")   # big layers are made on the GPU
     blk = synth.make_block(t, DEV, max_tokens=max(n, 8))
     x = seeded_x(n, 2048, 100 + n, xdtype)
     out, (logits, idx) = blk.forward_with_stats(x.to(DEV), out_dtype=torch.float32)
