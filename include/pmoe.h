@@ -26,7 +26,7 @@
 extern "C" {
 #endif
 
-#define PMOE_VERSION 2
+#define PMOE_VERSION 3
 
 /* GGML tensor-type ids, the numbering of candle's GgmlDType / GGUF files. */
 typedef enum {
@@ -104,8 +104,11 @@ typedef struct {
           16-byte aligned.  This is how a candle QTensor already on the GPU is used. */
     int32_t weights_location;
 
-    /* non-zero when custom block multipliers are installed (MoeExperts::set_block_multipliers,
-       qwen3_next.rs:1705-1720): every forward then returns PMOE_ERR_TRAINING_MODE */
+    /* non-zero when the host holds custom block multipliers (MoeExperts::set_block_multipliers,
+       qwen3_next.rs:1705-1720) that it has NOT handed to pmoe_layer_set_block_multipliers: every
+       forward then returns PMOE_ERR_TRAINING_MODE, the way the reference bypasses its own fast
+       paths (qwen3_next.rs:1977,1989).  A host that installs the multipliers in the handle
+       leaves this 0 and keeps the fast path. */
     int32_t training_mode;
 
     /* expert -> rank table of an expert-parallel group (see expert_base above) */
@@ -182,6 +185,37 @@ int pmoe_experts_forward_ep(pmoe_layer *layer, const void *x, int x_dtype, const
                             const float *w, int n, int top_k, int shared_begin, int shared_count,
                             void *out, int out_dtype, void *stream);
 
+/*
+ * MoeExperts::set_block_multipliers / clear_block_multipliers (qwen3_next.rs:1705-1732): the
+ * per-block scale multipliers of the EGGROLL / QZO training mode.  Each array is DEVICE f32 with
+ * one value per quantisation block of this handle's tensor in storage order -- [E_local, F, H/blk],
+ * [E_local, F, H/blk], [E_local, H, F/blk]; expert e owns blocks [e*B, (e+1)*B) as in
+ * extract_expert_scales (1688-1703).  The three come together; all NULL removes them.
+ *
+ * The reference builds, per expert and per use, QTensor::modify_block_scales copies of the three
+ * matrices (build_scaled_mats, 1554-1621) and multiplies through those.  Here the handle keeps one
+ * scaled copy of each tensor (device memory of the tensor's own size, allocated by this call) and
+ * every entry point reads the copies, tensor-core paths included, until the multipliers are
+ * removed.  The scaling runs on `stream`; use the stream the forwards use.  Not concurrent with
+ * another call on the handle.
+ */
+int pmoe_layer_set_block_multipliers(pmoe_layer *layer, const float *gate_mults, const float *up_mults,
+                                     const float *down_mults, void *stream);
+
+/* SharedExpert's custom_gate_scales / custom_up_scales / custom_down_scales (qwen3_next.rs:1743-1745,
+ * used through QMatMul::forward_with_scales at 1780-1799): independent of one another, NULL = none.
+ * Same layout rule and lifetime as above for the [F, H/blk], [F, H/blk], [H, F/blk] tensors. */
+int pmoe_layer_set_shared_scales(pmoe_layer *layer, const float *gate_scales, const float *up_scales,
+                                 const float *down_scales, void *stream);
+
+/* QTensor::modify_block_scales as QMatMul::forward_with_scales calls it (models/with_tracing.rs:217-248):
+ * out = blocks with block i's f16 scale d -- and dmin for Q2_K / Q4_K / Q5_K -- multiplied by mults[i]
+ * and rounded back to f16; quants and packed sub-scales unchanged.  out may be blocks.  All device
+ * pointers.  (The routine itself is in the candle fork the reference depends on, which is not part of
+ * its tree: this restates "every value of the block times m".) */
+int pmoe_modify_block_scales(int device, int dtype, const void *blocks, size_t n_blocks, const float *mults,
+                             void *out, void *stream);
+
 /* SharedExpert::forward (qwen3_next.rs:1776-1823), sigmoid gate included. */
 int pmoe_shared_forward(pmoe_layer *layer, const void *x, int x_dtype, int n, void *out,
                         int out_dtype, void *stream);
@@ -206,10 +240,10 @@ int pmoe_qmatmul(int device, int dtype, const void *w, size_t rows, size_t cols,
  * go into a 96 KB buffer compiled into the library (held by every GPU that loads it, until
  * the process exits).
  *
- * Limits: the rows must fit that buffer -- roughly m * cols <= 80 000, e.g. 32 rows of 2048
- * columns or 128 rows of 512 -- otherwise PMOE_ERR_TOO_MANY_TOKENS with the sizes in
- * pmoe_last_error(); nothing is truncated.  Same arguments, results and other errors as
- * pmoe_qmatmul.
+ * Limits: the quantised rows must fit that buffer: 1.25 * m * cols + 768 <= 98 304 bytes, so
+ * every m * cols <= 78 028 fits -- 38 rows of 2048 columns, 152 rows of 512 -- otherwise
+ * PMOE_ERR_TOO_MANY_TOKENS with the sizes in pmoe_last_error(); nothing is truncated.  Same
+ * arguments (cols a multiple of 256, at most 16 384), results and other errors as pmoe_qmatmul.
  *
  * The first call on a device looks up the buffer's device address (one runtime query, no
  * allocation); make that first call during start-up, before any stream capture begins.

@@ -16,6 +16,7 @@
 
 #include <math.h>
 #include <stdlib.h>
+#include <stddef.h>
 #include <string.h>
 #ifdef _OPENMP
 #include <omp.h>
@@ -568,6 +569,45 @@ static void quant_q6_K(const float *x, size_t nb, block_q6_K *y)
             }
         }
     }
+}
+
+/* ------------------------------------------------------------------ block-scale multipliers
+ * QTensor::modify_block_scales as the reference's training mode calls it
+ * (paramecia-model/src/qwen3_next.rs:1604-1606 for the routed experts, one f32 multiplier per
+ * block of the [E, rows, cols] tensor, expert e taking blocks [e*B, (e+1)*B) -- extract_expert_scales,
+ * 1688-1703; models/with_tracing.rs:217-248 for a single QMatMul).  The routine itself lives in the
+ * candle fork, which is not part of the reference tree [UNVERIFIED]: restated here as "the block's
+ * dequantised values are multiplied by m", i.e. every f16 super-scale of the block (d, and dmin
+ * where the type has one) becomes f16(f32(scale) * m), rounded to nearest even like half::f16::from_f32;
+ * quants and the packed 6-bit / 4-bit sub-scales are copied unchanged. */
+int pmo_modify_block_scales(int dtype, const void *blocks, size_t n_blocks, const float *mults, void *out)
+{
+    const size_t ts = pmo_type_size(dtype);
+    if (dtype != PMO_Q8_0 && !(dtype >= PMO_Q2_K && dtype <= PMO_Q6_K)) return -1;
+    if (out != blocks) memcpy(out, blocks, n_blocks * ts);
+    for (size_t i = 0; i < n_blocks; i++) {
+        uint8_t *b = (uint8_t *)out + i * ts;
+        const float m = mults[i];
+        size_t d_off = 0, dmin_off = (size_t)-1;
+        switch (dtype) {
+        case PMO_Q8_0: d_off = offsetof(block_q8_0, d); break;
+        case PMO_Q2_K: d_off = offsetof(block_q2_K, d); dmin_off = offsetof(block_q2_K, dmin); break;
+        case PMO_Q3_K: d_off = offsetof(block_q3_K, d); break;
+        case PMO_Q4_K: d_off = offsetof(block_q4_K, d); dmin_off = offsetof(block_q4_K, dmin); break;
+        case PMO_Q5_K: d_off = offsetof(block_q5_K, d); dmin_off = offsetof(block_q5_K, dmin); break;
+        case PMO_Q6_K: d_off = offsetof(block_q6_K, d); break;
+        }
+        uint16_t h;
+        memcpy(&h, b + d_off, 2);
+        h = f32_to_f16(f16_to_f32(h) * m);
+        memcpy(b + d_off, &h, 2);
+        if (dmin_off != (size_t)-1) {
+            memcpy(&h, b + dmin_off, 2);
+            h = f32_to_f16(f16_to_f32(h) * m);
+            memcpy(b + dmin_off, &h, 2);
+        }
+    }
+    return 0;
 }
 
 int pmo_quantize(int dtype, const float *x, size_t n, void *blocks)

@@ -53,6 +53,10 @@ size_t pmo_row_bytes(int dtype, size_t cols);
 int pmo_dequantize(int dtype, const void *blocks, size_t n_elems, float *out);
 int pmo_quantize(int dtype, const float *x, size_t n_elems, void *blocks);   /* weight quantisers */
 
+/* QTensor::modify_block_scales (training mode, qwen3_next.rs:1604-1606): block i's f16 scale(s) times mults[i];
+   out may equal blocks.  [UNVERIFIED: the routine lives in the candle fork] */
+int pmo_modify_block_scales(int dtype, const void *blocks, size_t n_blocks, const float *mults, void *out);
+
 /* activation quantisers (candle BlockQ8K / BlockQ8_0 from_float) */
 void pmo_quantize_q8k(const float *x, size_t n, float *d, int8_t *qs, int16_t *bsums);
 void pmo_quantize_q8_0_act(const float *x, size_t n, uint16_t *d_f16, int8_t *qs);

@@ -59,6 +59,7 @@ def lib():
         L.pmo_row_bytes.argtypes = [C.c_int, C.c_size_t]
         L.pmo_dequantize.argtypes = [C.c_int, C.c_void_p, C.c_size_t, C.c_void_p]
         L.pmo_quantize.argtypes = [C.c_int, C.c_void_p, C.c_size_t, C.c_void_p]
+        L.pmo_modify_block_scales.argtypes = [C.c_int, C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p]
         L.pmo_quantize_q8k.argtypes = [C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p, C.c_void_p]
         L.pmo_quantize_q8k.restype = None
         L.pmo_quantize_q8_0_act.argtypes = [C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p]
@@ -111,6 +112,18 @@ def quantize(dtype: int, x: np.ndarray) -> np.ndarray:
     out = np.empty(nbytes, np.uint8)
     if lib().pmo_quantize(dtype, _p(x), x.size, _p(out)):
         raise ValueError("pmo_quantize failed")
+    return out
+
+
+def modify_block_scales(dtype: int, blocks: np.ndarray, mults: np.ndarray) -> np.ndarray:
+    """QTensor::modify_block_scales: a copy of `blocks` whose block i has its f16 scale(s) times mults[i]."""
+    blocks = _c(blocks, np.uint8).ravel()
+    mults = _c(mults, np.float32).ravel()
+    if blocks.size != mults.size * type_size(dtype):
+        raise ValueError("one multiplier per block")
+    out = np.empty_like(blocks)
+    if lib().pmo_modify_block_scales(dtype, _p(blocks), mults.size, _p(mults), _p(out)):
+        raise ValueError("pmo_modify_block_scales failed")
     return out
 
 

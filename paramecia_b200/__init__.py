@@ -10,10 +10,10 @@ import fails if ``libpmoe.so`` has not been built, and constructing a layer fail
 """
 from ._lib import (PmoeError, lib, lib_path, launch_count, F32, F16, BF16, Q8_0, Q2_K, Q3_K, Q4_K, Q5_K, Q6_K,
                    block_size, type_size, row_bytes)
-from .moe import QTensor, MoeBlock, SharedExpertWeights, dequantize, add_rms_norm, add_rms_norm_into, qmatmul, qmatmul_noalloc
+from .moe import QTensor, MoeBlock, SharedExpertWeights, dequantize, add_rms_norm, add_rms_norm_into, qmatmul, qmatmul_noalloc, modify_block_scales
 from .gguf import GGUFFile, GGUFError, load_moe_block, moe_layers
 
 __all__ = ["PmoeError", "lib", "lib_path", "launch_count", "F32", "F16", "BF16", "Q8_0", "Q2_K", "Q3_K", "Q4_K", "Q5_K", "Q6_K",
            "block_size", "type_size", "row_bytes", "QTensor", "MoeBlock", "SharedExpertWeights",
-           "dequantize", "add_rms_norm", "add_rms_norm_into", "qmatmul", "qmatmul_noalloc", "GGUFFile", "GGUFError", "load_moe_block",
+           "dequantize", "add_rms_norm", "add_rms_norm_into", "qmatmul", "qmatmul_noalloc", "modify_block_scales", "GGUFFile", "GGUFError", "load_moe_block",
            "moe_layers"]

@@ -58,6 +58,9 @@ SYMBOLS = [
     ("pmoe_router_stats", _I, [_V, _V, _V, _I, _I, _V, _V, _V]),
     ("pmoe_experts_forward", _I, [_V, _V, _I, _V, _V, _I, _I, _V, _I, _V]),
     ("pmoe_experts_forward_ep", _I, [_V, _V, _I, _V, _V, _I, _I, _I, _I, _V, _I, _V]),
+    ("pmoe_layer_set_block_multipliers", _I, [_V, _V, _V, _V, _V]),
+    ("pmoe_layer_set_shared_scales", _I, [_V, _V, _V, _V, _V]),
+    ("pmoe_modify_block_scales", _I, [_I, _I, _V, _Z, _V, _V, _V]),
     ("pmoe_shared_forward", _I, [_V, _V, _I, _I, _V, _I, _V]),
     ("pmoe_qmatmul", _I, [_I, _I, _V, _Z, _Z, _V, _Z, _V, _V]),
     ("pmoe_qmatmul_noalloc", _I, [_I, _I, _V, _Z, _Z, _V, _Z, _V, _V]),

@@ -90,6 +90,10 @@ struct pmoe_layer {
     bool hg_off = false;
     // rows the shared expert serves in the next run_experts call; count < 0 = every row
     int req_sh_begin = 0, req_sh_count = -1;
+    // block-scale multipliers (training mode): the tensors as created, and the scaled copies the kernels read
+    // while multipliers are installed (index: 0 gate_exps, 1 up_exps, 2 down_exps, 3 sh_gate, 4 sh_up, 5 sh_down)
+    const uint8_t *orig[6] = {};
+    void *scaled[6] = {};
     bool trace = false;
     cudaEvent_t ev0[PMOE_TRACE_PHASES] = {}, ev1[PMOE_TRACE_PHASES] = {};
     bool ev_used[PMOE_TRACE_PHASES] = {};
@@ -431,6 +435,8 @@ int pmoe_layer_create(const pmoe_layer_desc *desc, pmoe_layer **out)
         delete L;
         return rc;
     }
+    L->orig[0] = v.gate_exps; L->orig[1] = v.up_exps; L->orig[2] = v.down_exps;
+    L->orig[3] = v.sh_gate; L->orig[4] = v.sh_up; L->orig[5] = v.sh_down;
     *out = L;
     return PMOE_OK;
 }
@@ -441,6 +447,8 @@ int pmoe_layer_destroy(pmoe_layer *L)
     DeviceGuard guard(L->device);
     cudaDeviceSynchronize();
     for (void *p : L->owned) cudaFree(p);
+    for (void *p : L->scaled)
+        if (p) cudaFree(p);
     if (L->hg_exec) cudaGraphExecDestroy(L->hg_exec);
     if (L->cap_stream) cudaStreamDestroy(L->cap_stream);
     for (int i = 0; i < PMOE_TRACE_PHASES; i++) {
@@ -746,8 +754,8 @@ int pmoe_qmatmul_noalloc(int device, int dtype, const void *w, size_t rows, size
 {
     if (!(dtype >= PMOE_Q2_K && dtype <= PMOE_Q6_K) && dtype != PMOE_Q8_0)
         return fail(PMOE_ERR_UNSUPPORTED_DTYPE, "pmoe_qmatmul_noalloc serves Q2_K ... Q6_K and Q8_0 (got %d)", dtype);
-    if (!rows || !cols || cols % 256 || rows > (1u << 24))
-        return fail(PMOE_ERR_UNSUPPORTED_SHAPE, "cols must be a non-zero multiple of 256");
+    if (!rows || !cols || cols % 256 || cols > 16384 || rows > (1u << 24))
+        return fail(PMOE_ERR_UNSUPPORTED_SHAPE, "cols must be a multiple of 256 (<= 16384)");
     if (!m) return PMOE_OK;
     if (!w || !x || !y) return fail(PMOE_ERR_INVALID_ARG, "w / x / y is NULL");
     if (((uintptr_t)w & 15) || ((uintptr_t)x & 15)) return fail(PMOE_ERR_INVALID_ARG, "w and x must be 16-byte aligned");
@@ -757,13 +765,119 @@ int pmoe_qmatmul_noalloc(int device, int dtype, const void *w, size_t rows, size
     size_t cap = 0;
     cudaError_t e = qmatmul_static_scratch(device, &scratch, &cap);
     if (e != cudaSuccess) return fail_cuda(e, "cudaGetSymbolAddress(static scratch)");
-    if (m > 4096 || cols > 65536 || qmatmul_scratch_bytes((int)m, (int)cols) > cap)
+    if (m > 4096 || qmatmul_scratch_bytes((int)m, (int)cols) > cap)
         return fail(PMOE_ERR_TOO_MANY_TOKENS,
                     "m = %zu rows of %zu columns need %zu bytes of scratch; the built-in buffer holds %zu "
-                    "(m * cols <= about 80000, e.g. 32 rows of 2048); use pmoe_qmatmul for larger operands",
-                    m, cols, qmatmul_scratch_bytes((int)(m > 4096 ? 4096 : m), (int)(cols > 65536 ? 65536 : cols)), cap);
+                    "(1.25 * m * cols + 768 <= 98304, i.e. m * cols <= 78028: 32 rows of 2048 fit, 39 do not); use "
+                    "pmoe_qmatmul for larger operands",
+                    m, cols, qmatmul_scratch_bytes((int)(m > 4096 ? 4096 : m), (int)cols), cap);
     e = launch_qmatmul(dtype, w, (int)rows, (int)cols, x, (int)m, y, scratch, (cudaStream_t)stream);
     if (e != cudaSuccess) return fail_cuda(e, "pmoe_qmatmul_noalloc");
+    return PMOE_OK;
+}
+
+}  // extern "C"
+
+// ---------------------------------------------------------------- block-scale multipliers
+namespace {
+
+struct TensorSlot {
+    int dtype;
+    size_t blocks;
+    const uint8_t **live;   // the pointer the kernels read
+};
+
+TensorSlot tensor_slot(pmoe_layer *L, int which)
+{
+    LayerDev &v = L->dev;
+    const size_t El = (size_t)v.E_local, H = v.H, F = v.F;
+    switch (which) {
+    case 0: return {v.gate_dtype, El * F * (H / block_elems(v.gate_dtype)), &v.gate_exps};
+    case 1: return {v.up_dtype, El * F * (H / block_elems(v.up_dtype)), &v.up_exps};
+    case 2: return {v.down_dtype, El * H * (F / block_elems(v.down_dtype)), &v.down_exps};
+    case 3: return {v.sh_gate_dtype, F * (H / block_elems(v.sh_gate_dtype)), &v.sh_gate};
+    case 4: return {v.sh_up_dtype, F * (H / block_elems(v.sh_up_dtype)), &v.sh_up};
+    default: return {v.sh_down_dtype, H * (F / block_elems(v.sh_down_dtype)), &v.sh_down};
+    }
+}
+
+// Installs (mults != NULL) or removes (NULL) the multipliers of one tensor of the handle.
+int set_tensor_multipliers(pmoe_layer *L, int which, const float *mults, cudaStream_t s)
+{
+    TensorSlot t = tensor_slot(L, which);
+    if (!mults) {
+        if (L->scaled[which]) {
+            CU(cudaStreamSynchronize(s));   // a forward still reading the copy must finish first
+            CU(cudaFree(L->scaled[which]));
+            L->scaled[which] = nullptr;
+        }
+        *t.live = L->orig[which];
+        return PMOE_OK;
+    }
+    const size_t bytes = t.blocks * (size_t)block_bytes(t.dtype);
+    if (!L->scaled[which]) CU(cudaMalloc(&L->scaled[which], bytes));
+    CU(launch_modify_block_scales(t.dtype, L->orig[which], t.blocks, mults, L->scaled[which], s));
+    *t.live = (const uint8_t *)L->scaled[which];
+    return PMOE_OK;
+}
+
+// the host-buffer entry point replays a recorded kernel chain that holds the old weight pointers
+void drop_host_graph(pmoe_layer *L)
+{
+    if (L->hg_exec) cudaGraphExecDestroy(L->hg_exec);
+    L->hg_exec = nullptr;
+    L->hg_n = L->hg_seen_n = -1;
+}
+
+}  // namespace
+
+extern "C" {
+
+int pmoe_layer_set_block_multipliers(pmoe_layer *L, const float *gate_mults, const float *up_mults,
+                                     const float *down_mults, void *stream)
+{
+    if (!L) return fail(PMOE_ERR_INVALID_ARG, "layer is NULL");
+    const int given = (gate_mults ? 1 : 0) + (up_mults ? 1 : 0) + (down_mults ? 1 : 0);
+    if (given != 0 && given != 3)
+        return fail(PMOE_ERR_INVALID_ARG, "gate, up and down multipliers are installed together (or all NULL to clear)");
+    DeviceGuard guard(L->device);
+    drop_host_graph(L);
+    const float *m[3] = {gate_mults, up_mults, down_mults};
+    for (int i = 0; i < 3; i++) {
+        int rc = set_tensor_multipliers(L, i, m[i], (cudaStream_t)stream);
+        if (rc) return rc;
+    }
+    return PMOE_OK;
+}
+
+int pmoe_layer_set_shared_scales(pmoe_layer *L, const float *gate_scales, const float *up_scales,
+                                 const float *down_scales, void *stream)
+{
+    if (!L) return fail(PMOE_ERR_INVALID_ARG, "layer is NULL");
+    if (!L->dev.has_shared) {
+        if (gate_scales || up_scales || down_scales) return fail(PMOE_ERR_INVALID_ARG, "the layer has no shared expert");
+        return PMOE_OK;
+    }
+    DeviceGuard guard(L->device);
+    drop_host_graph(L);
+    const float *m[3] = {gate_scales, up_scales, down_scales};
+    for (int i = 0; i < 3; i++) {
+        int rc = set_tensor_multipliers(L, 3 + i, m[i], (cudaStream_t)stream);
+        if (rc) return rc;
+    }
+    return PMOE_OK;
+}
+
+int pmoe_modify_block_scales(int device, int dtype, const void *blocks, size_t n_blocks, const float *mults, void *out,
+                             void *stream)
+{
+    if (!(dtype >= PMOE_Q2_K && dtype <= PMOE_Q6_K) && dtype != PMOE_Q8_0)
+        return fail(PMOE_ERR_UNSUPPORTED_DTYPE, "pmoe_modify_block_scales serves Q2_K ... Q6_K and Q8_0 (got %d)", dtype);
+    if (n_blocks && (!blocks || !mults || !out)) return fail(PMOE_ERR_INVALID_ARG, "blocks / mults / out is NULL");
+    if (((uintptr_t)blocks & 1) || ((uintptr_t)out & 1)) return fail(PMOE_ERR_INVALID_ARG, "blocks and out must be 2-byte aligned");
+    DeviceGuard guard(device);
+    if (!guard.ok) return fail(PMOE_ERR_NO_DEVICE, "cannot select device %d", device);
+    CU(launch_modify_block_scales(dtype, blocks, n_blocks, mults, out, (cudaStream_t)stream));
     return PMOE_OK;
 }
 

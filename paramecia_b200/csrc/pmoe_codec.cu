@@ -101,6 +101,49 @@ cudaError_t launch_dequantize(int dtype, const void *blocks, size_t n_elems, flo
     return cudaGetLastError();
 }
 
+// QTensor::modify_block_scales as the reference's training mode uses it (qwen3_next.rs:1604-1606,
+// models/with_tracing.rs:230): out = blocks with block i's f16 super-scale d (and dmin where the type
+// has one) replaced by f16(f32(scale) * mults[i]), round to nearest even; quants and packed sub-scales
+// are copied.  Blocks are 2-byte aligned only (34, 110, 210 bytes), so the copy runs in 16-bit units:
+// one warp per block, lanes stride over its halfwords.
+__global__ void __launch_bounds__(256) k_modify_block_scales(int type_bytes, int d_off, int dmin_off,
+                                                             const uint16_t *__restrict__ blocks, size_t n_blocks,
+                                                             const float *__restrict__ mults, uint16_t *__restrict__ out)
+{
+    const size_t b = (size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (b >= n_blocks) return;
+    const int lane = threadIdx.x & 31;
+    const int hw = type_bytes / 2;
+    const uint16_t *src = blocks + b * hw;
+    uint16_t *dst = out + b * hw;
+    const float m = mults[b];
+    for (int i = lane; i < hw; i += 32) {
+        uint16_t v = src[i];
+        if (2 * i == d_off || 2 * i == dmin_off) v = __half_as_ushort(__float2half_rn(__fmul_rn(half_bits_to_float(v), m)));
+        dst[i] = v;
+    }
+}
+
+cudaError_t launch_modify_block_scales(int dtype, const void *blocks, size_t n_blocks, const float *mults, void *out,
+                                       cudaStream_t s)
+{
+    if (!n_blocks) return cudaSuccess;
+    int d_off = 0, dmin_off = -1;
+    switch (dtype) {
+    case PMOE_Q8_0: d_off = 0; break;
+    case PMOE_Q2_K: d_off = 80; dmin_off = 82; break;
+    case PMOE_Q3_K: d_off = 108; break;
+    case PMOE_Q4_K: case PMOE_Q5_K: d_off = 0; dmin_off = 2; break;
+    case PMOE_Q6_K: d_off = 208; break;
+    default: return cudaErrorInvalidValue;
+    }
+    const size_t grid = (n_blocks + 7) / 8;
+    k_modify_block_scales<<<(unsigned)grid, 256, 0, s>>>(block_bytes(dtype), d_off, dmin_off, (const uint16_t *)blocks,
+                                                         n_blocks, mults, (uint16_t *)out);
+    count_launch();
+    return cudaGetLastError();
+}
+
 // resid_out = resid_in + delta; y = resid_out / sqrt(mean(resid_out^2) + eps) * weight
 // (resid_out may be resid_in: a thread reads and later writes the same elements)
 __global__ void __launch_bounds__(256) k_add_rms_norm(const float *resid_in, const float *__restrict__ delta,

@@ -315,6 +315,8 @@ cudaError_t launch_down_prefill(const LayerDev &L, const Workspace &ws, const fl
                                 bool shared, cudaStream_t s);
 // pmoe_codec.cu
 cudaError_t launch_dequantize(int dtype, const void *blocks, size_t n_elems, float *out, cudaStream_t s);
+cudaError_t launch_modify_block_scales(int dtype, const void *blocks, size_t n_blocks, const float *mults, void *out,
+                                       cudaStream_t s);
 cudaError_t launch_reduce_rows(const float *parts, int R, const void *extra, int extra_dtype, int n, int H, void *out,
                                int out_dtype, cudaStream_t s);
 cudaError_t launch_add_rms_norm(const float *resid_in, const float *delta, const float *weight, int n, int H,

@@ -21,6 +21,7 @@
 // the reduction dimension: the quantised activations of the expert's tokens stay in its
 // registers across all rows of the expert, and the partial sums of several rows and tokens
 // meet in one transposed shuffle reduction.
+#include <atomic>
 #include <cstdlib>
 #include "pmoe_common.cuh"
 #include "pmoe_quant.cuh"
@@ -1803,20 +1804,20 @@ constexpr size_t QMM_STATIC_BYTES = 96 * 1024;
 static __device__ __align__(256) unsigned char g_qmm_scratch[QMM_STATIC_BYTES];
 
 constexpr int QMM_MAX_DEVICES = 64;
-static void *g_qmm_scratch_addr[QMM_MAX_DEVICES];  // device address of g_qmm_scratch, per ordinal
+static std::atomic<void *> g_qmm_scratch_addr[QMM_MAX_DEVICES];  // device address of g_qmm_scratch, per ordinal
 
 cudaError_t qmatmul_static_scratch(int device, void **ptr, size_t *bytes)
 {
     *ptr = nullptr;
     *bytes = QMM_STATIC_BYTES;
     if (device < 0 || device >= QMM_MAX_DEVICES) return cudaErrorInvalidDevice;
-    if (!g_qmm_scratch_addr[device]) {  // set-up: the calling thread has made `device` current
-        void *p = nullptr;
+    void *p = g_qmm_scratch_addr[device].load(std::memory_order_acquire);
+    if (!p) {  // set-up: the calling thread has made `device` current; two threads racing here store the same address
         cudaError_t e = cudaGetSymbolAddress(&p, g_qmm_scratch);
         if (e != cudaSuccess) return e;
-        g_qmm_scratch_addr[device] = p;
+        g_qmm_scratch_addr[device].store(p, std::memory_order_release);
     }
-    *ptr = g_qmm_scratch_addr[device];
+    *ptr = p;
     return cudaSuccess;
 }
 

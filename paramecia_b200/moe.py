@@ -102,10 +102,24 @@ def qmatmul(w: "QTensor", x: torch.Tensor) -> torch.Tensor:
     return y
 
 
+def modify_block_scales(w: "QTensor", mults: torch.Tensor) -> "QTensor":
+    """QTensor::modify_block_scales: a new QTensor whose block i carries its f16 scale(s) times mults[i]."""
+    if not w.data.is_cuda:
+        raise PmoeError(-9, "modify_block_scales needs CUDA tensors; libpmoe has no CPU path")
+    n_blocks = w.numel() // _lib.block_size(w.dtype)
+    m = mults.to(w.data.device, torch.float32).reshape(-1).contiguous()
+    if m.numel() != n_blocks:
+        raise ValueError(f"{m.numel()} multipliers given, the tensor has {n_blocks} blocks")
+    out = torch.empty_like(w.data)
+    check(lib().pmoe_modify_block_scales(w.data.device.index or 0, w.dtype, w.data.data_ptr(), n_blocks, m.data_ptr(),
+                                         out.data_ptr(), _stream_ptr(w.data.device)))
+    return QTensor(out, w.dtype, w.shape)
+
+
 def qmatmul_noalloc(w: "QTensor", x: torch.Tensor, y: torch.Tensor) -> torch.Tensor:
     """`qmatmul` through the entry point that allocates nothing: the caller owns x [m, cols] f32 and
     y [m, rows] f32 (both CUDA, contiguous) and the quantised activations use the library's built-in
-    96 KB buffer, so m * cols is limited (about 80 000).  Calls on one device must not overlap."""
+    96 KB buffer, so m * cols <= 78 028 (38 rows of 2048 columns).  Calls on one device must not overlap."""
     rows, cols = w.shape
     if not w.data.is_cuda:
         raise ValueError("qmatmul_noalloc takes CUDA tensors it does not have to copy")
@@ -381,6 +395,43 @@ class MoeBlock:
         check(lib().pmoe_experts_forward(self._h, x.data_ptr(), _TORCH_TO_PMOE[x.dtype], idx.data_ptr(), w.data_ptr(),
                                          n, top_k, out.data_ptr(), _TORCH_TO_PMOE[out_dtype], _stream_ptr(self.device)))
         return out
+
+    def _blocks_of(self, which: str) -> int:
+        d = self._desc
+        El, F, H = self.num_experts_local, self.n_ff, self.hidden_dim
+        return {"gate": El * F * (H // _lib.block_size(d.gate_dtype)), "up": El * F * (H // _lib.block_size(d.up_dtype)),
+                "down": El * H * (F // _lib.block_size(d.down_dtype)),
+                "sh_gate": F * (H // max(1, _lib.block_size(d.sh_gate_dtype))), "sh_up": F * (H // max(1, _lib.block_size(d.sh_up_dtype))),
+                "sh_down": H * (F // max(1, _lib.block_size(d.sh_down_dtype)))}[which]
+
+    def _mults(self, name: str, which: str, m: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+        if m is None:
+            return None
+        m = m.to(self.device, torch.float32).reshape(-1).contiguous()
+        if m.numel() != self._blocks_of(which):
+            raise ValueError(f"{name}: {m.numel()} multipliers given, the tensor has {self._blocks_of(which)} blocks")
+        return m
+
+    def set_block_multipliers(self, gate_mults: torch.Tensor, up_mults: torch.Tensor, down_mults: torch.Tensor) -> None:
+        """MoeExperts::set_block_multipliers (qwen3_next.rs:1705-1720): one f32 multiplier per quantisation block
+        of this handle's gate / up / down expert tensors, in storage order.  Every later forward uses the scaled
+        weights (QTensor::modify_block_scales, build_scaled_mats 1554-1621) on the fast paths."""
+        g, u, d = (self._mults(n, w, m) for n, w, m in (("gate_mults", "gate", gate_mults), ("up_mults", "up", up_mults),
+                                                          ("down_mults", "down", down_mults)))
+        check(lib().pmoe_layer_set_block_multipliers(self._h, g.data_ptr(), u.data_ptr(), d.data_ptr(), _stream_ptr(self.device)))
+
+    def clear_block_multipliers(self) -> None:
+        """MoeExperts::clear_block_multipliers (qwen3_next.rs:1722-1732)."""
+        check(lib().pmoe_layer_set_block_multipliers(self._h, None, None, None, _stream_ptr(self.device)))
+
+    def set_shared_scales(self, gate_scales: Optional[torch.Tensor] = None, up_scales: Optional[torch.Tensor] = None,
+                          down_scales: Optional[torch.Tensor] = None) -> None:
+        """SharedExpert's custom_gate_scales / custom_up_scales / custom_down_scales (qwen3_next.rs:1743-1745,
+        1780-1799); None leaves that matrix unscaled."""
+        g, u, d = (self._mults(n, w, m) for n, w, m in (("gate_scales", "sh_gate", gate_scales), ("up_scales", "sh_up", up_scales),
+                                                          ("down_scales", "sh_down", down_scales)))
+        check(lib().pmoe_layer_set_shared_scales(self._h, *(None if t is None else t.data_ptr() for t in (g, u, d)),
+                                                 _stream_ptr(self.device)))
 
     def shared_forward(self, hidden_states: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
         """SharedExpert::forward, sigmoid gate included."""

@@ -153,3 +153,33 @@ def test_router_stats_formulas():
     p = torch.softmax(L, -1).mean(0)
     assert abs(lb - float(16 * (f * p).sum())) < 1e-12
     assert counts.sum() == idx.size
+
+
+@pytest.mark.parametrize("dtype", [po.Q2_K, po.Q3_K, po.Q4_K, po.Q5_K, po.Q6_K, po.Q8_0])
+def test_modify_block_scales(dtype):
+    """Block-scale multipliers (QTensor::modify_block_scales, qwen3_next.rs:1604-1606): the block's values times m,
+    with the f16 scales re-rounded; quants untouched."""
+    rng = np.random.default_rng(11)
+    bs, ts, nb = po.block_size(dtype), po.type_size(dtype), 24
+    w = po.quantize(dtype, (rng.standard_normal(nb * bs) * 0.02).astype(np.float32))
+    ones = po.modify_block_scales(dtype, w, np.ones(nb, np.float32))
+    assert np.array_equal(ones, w)                                        # m = 1 changes no byte
+    m = np.array([2.0, 4.0, -1.0, 0.0] * (nb // 4), np.float32)           # exact in f16 (no subnormal is halved)
+    got = po.dequantize(dtype, po.modify_block_scales(dtype, w, m), nb * bs)
+    want = po.dequantize(dtype, w, nb * bs) * np.repeat(m, bs)
+    assert np.array_equal(got, want)
+    m = rng.uniform(0.5, 1.5, nb).astype(np.float32)                      # general: within f16 rounding of the scales
+    mod = po.modify_block_scales(dtype, w, m)
+    got = po.dequantize(dtype, mod, nb * bs)
+    want = po.dequantize(dtype, w, nb * bs).astype(np.float64) * np.repeat(m.astype(np.float64), bs)
+    assert np.max(np.abs(got - want)) <= 2.0 ** -10 * np.max(np.abs(want)) * 2
+    # only the scale fields differ
+    offs = {po.Q2_K: (80, 82), po.Q3_K: (108,), po.Q4_K: (0, 2), po.Q5_K: (0, 2), po.Q6_K: (208,), po.Q8_0: (0,)}[dtype]
+    keep = np.ones(ts, bool)
+    for o in offs:
+        keep[o:o + 2] = False
+    assert np.array_equal(mod.reshape(nb, ts)[:, keep], w.reshape(nb, ts)[:, keep])
+    for o in offs:                                                         # and they are f16(f32(d) * m)
+        d0 = w.reshape(nb, ts)[:, o:o + 2].copy().view(np.float16).astype(np.float32)[:, 0]
+        d1 = mod.reshape(nb, ts)[:, o:o + 2].copy().view(np.float16)[:, 0]
+        assert np.array_equal(d1, (d0 * m).astype(np.float16))

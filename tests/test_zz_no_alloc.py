@@ -37,9 +37,14 @@ def test_two_calls_match_the_allocating_entry_point():
     b_w, b_x = _case(pm.Q8_0, 64, 512, 7, 2)
     a_y = torch.full((24, 96), float("nan"), device=DEV)
     b_y = torch.full((7, 64), float("nan"), device=DEV)
+    pm.qmatmul_noalloc(a_w, a_x, a_y)      # the first call on the device also looks up the buffer's address
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
     pm.qmatmul_noalloc(a_w, a_x, a_y)
     pm.qmatmul_noalloc(b_w, b_x, b_y)
     torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before       # the calls took no device memory (the driver's own count)
     want_a = pm.qmatmul(a_w, a_x)
     want_b = pm.qmatmul(b_w, b_x)
     # same kernels, same arithmetic, only the scratch differs: bit-identical (tolerance 0)
@@ -60,3 +65,12 @@ def test_oversized_operands_are_refused():
     with pytest.raises(pm.PmoeError) as e:
         pm.qmatmul_noalloc(w, x, y)
     assert e.value.code == -5 and "built-in buffer" in e.value.message
+    # the largest operands that fit, and the first that do not
+    w, x = _case(pm.Q8_0, 16, 2048, 39, 4)
+    pm.qmatmul_noalloc(w, x[:38].contiguous(), torch.empty((38, 16), device=DEV))
+    with pytest.raises(pm.PmoeError):
+        pm.qmatmul_noalloc(w, x, torch.empty((39, 16), device=DEV))
+    # the column limit of pmoe_qmatmul holds here too
+    lib = pm.lib()
+    rc = lib.pmoe_qmatmul_noalloc(0, pm.Q8_0, w.data.data_ptr(), 1, 32768, x.data_ptr(), 1, x.data_ptr(), None)
+    assert rc == -3
