@@ -212,7 +212,7 @@ cudaError_t launch_gate_up(const LayerDev &L, const Workspace &ws, int n, int to
     A.quant_dt_s = shared ? L.sh_down_dtype : 0;
     A.q8k_out = ws.act_q8k;
     A.q80_out = ws.act_q80;
-    if (routed && L.gate_dtype == PMOE_Q4_K && L.H == 2048 && L.F == 512 && mma_enabled())
+    if (routed && L.gate_dtype == PMOE_Q4_K && L.H == 2048 && L.F == 512 && mma_enabled(1))
         return launch_gate_up_q4k_mma(A, shared ? L.sh_gate_dtype : 0, s);
     // a kernel without routed items still needs a routed type to instantiate; reuse the shared one
     return launch_gemv<2>(A, routed ? L.gate_dtype : L.sh_gate_dtype, shared ? L.sh_gate_dtype : 0, s);
@@ -241,7 +241,7 @@ cudaError_t launch_down(const LayerDev &L, const Workspace &ws, const float *w, 
     A.debug = getenv("PMOE_DEBUG") ? atoi(getenv("PMOE_DEBUG")) : 0;
     A.stage_bytes = STAGE_BYTES;
     // Q2_K / Q3_K shared matrices only come beside routed matrices of their own type, never beside Q6_K
-    if (routed && L.down_dtype == PMOE_Q6_K && L.H == 2048 && L.F == 512 && mma_enabled())
+    if (routed && L.down_dtype == PMOE_Q6_K && L.H == 2048 && L.F == 512 && mma_enabled(2))
         return launch_down_q6k_mma(A, shared ? L.sh_down_dtype : 0, s);
     return launch_gemv<1>(A, routed ? L.down_dtype : L.sh_down_dtype, shared ? L.sh_down_dtype : 0, s);
 }

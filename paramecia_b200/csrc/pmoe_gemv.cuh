@@ -1119,7 +1119,7 @@ __device__ inline bool run_items_shared_mma(const GemvArgs &A, uint8_t *ring, co
 // pmoe_gemv_mma.cu
 cudaError_t launch_gate_up_q4k_mma(GemvArgs &A, int dt_s, cudaStream_t s);
 cudaError_t launch_down_q6k_mma(GemvArgs &A, int dt_s, cudaStream_t s);
-bool mma_enabled();
+bool mma_enabled(int kernel);   // 1: Q4_K gate/up, 2: Q6_K down
 int sm_count();
 
 }  // namespace pmoe

@@ -87,170 +87,398 @@ __device__ inline Q4Hdr q4k_hdr(const uint4 h)
     return o;
 }
 
-// byte `i` (compile-time) of w, zero-extended
-template <int I> __device__ inline int byte_of(uint32_t w) { return (int)__byte_perm(w, 0u, 0x4440u + I); }
+// The lists of the token group that follows the current one, fetched one dependent load per item while the
+// current group's items are computed (a warp issues in order: a chain of dependent loads would stall it for
+// the whole chain, and under the weight stream a single access to L2 or HBM already takes microseconds).
+struct LookAhead {
+    int slot, group, step, e, m, off, row;   // row: pair id of token (lane & 7) of that group, -1 if none
+    __device__ inline void start(const MmaCursor &cur)
+    {
+        slot = cur.slot; group = cur.group + 1;
+        if (group >= cur.groups) { slot++; group = 0; }
+        step = 0; row = -1; m = 0; e = 0; off = 0;
+    }
+    __device__ inline void advance(const GemvArgs &A, const MmaWork &work, int lane)
+    {
+        if (slot >= work.n_active || step > 2) return;   // the shared expert (or nothing) follows: no lists to read
+        if (step == 0) {
+            e = A.g.active[slot];
+        } else if (step == 1) {
+            m = A.g.count[e];
+            off = A.g.offset[e];
+        } else {
+            const int i = GEMV_TG_MMA * group + (lane & 7);
+            row = i < m ? A.g.pairs[off + i] : -1;
+        }
+        step++;
+    }
+    __device__ inline bool ready(const MmaWork &work, int s, int g) const
+    {
+        return s == slot && g == group && s < work.n_active && step > 2;
+    }
+};
 
-// The compute warps' side: items [it, n_items) of this CTA starting at `cur`.
-__device__ inline bool run_items_q4k_mma(const GemvArgs &A, uint8_t *ring, const MmaWork &work, MmaCursor cur, int n_items,
-                                         int &it, int warp, int lane)
+__device__ inline void mma_u8s8_k32_acc(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                        uint32_t b1)
+{
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// Sums of the quants under the four sub-blocks 4t .. 4t+3 (pairs of the Q8_K partial sums of 16) as four bytes:
+// their high digits (v >> 6) or low digits (v & 63), v = 64 h + l.
+__device__ inline uint32_t q4_bsum_digits(uint4 bs, bool low)
+{
+    const uint32_t w4[4] = {bs.x, bs.y, bs.z, bs.w};
+    uint32_t o = 0;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const int v = (int)(int16_t)(w4[i] & 0xffffu) + (int)(int16_t)(w4[i] >> 16);
+        o |= (uint32_t)((low ? (v & 63) : (v >> 6)) & 0xFF) << (8 * i);
+    }
+    return o;
+}
+
+// How many tokens a group is laid out for decides what the eight accumulator columns mean:
+//   TP 2: (sub-block slot 0..3) x (token 0..1) -- the four even sub-blocks of a block share one accumulator (a token's
+//         activations are non-zero only in the columns of the slot the instruction covers), the four odd ones another;
+//   TP 4: (slot 0..1) x (token 0..3), two accumulators per parity;
+//   TP 8: the columns are the tokens, one accumulator per sub-block.
+// Fewer accumulators mean fewer integer multiplies by the 6-bit scales afterwards.
+template <int TP> struct GuGroup {
+    static constexpr int NF = TP == 2 ? 1 : 2;   // tokens of the lane's final values
+    uint32_t bq[8][2];   // B operand per sub-block of block column `warp` (zero where the lane's column belongs to another slot)
+    uint32_t bm[2];      // partial-sum digits for the mins products (TP 2: one register, the digit follows the column)
+    float dx[NF];        // activation scale of the lane's final tokens in this block column
+    int r_orow, r_row;   // cross-warp sum: output row and row inside the item of the value this thread finishes (-1: none)
+};
+
+// my_row = pair id of token (lane & 7) of the group (routed experts).  Called by all lanes; shuffles come first.
+template <int TP>
+__device__ inline void gu_load_group(const GemvArgs &A, bool is_sh, int my_row, int t0, int cnt, int warp, int lane, GuGroup<TP> &G)
+{
+    const int g = lane >> 2, t = lane & 3;
+    const QAct &in = is_sh ? A.in_s : A.in_r;
+    const int my_act = my_row >= 0 ? my_row / A.top_k : 0;
+    auto act_row = [&](int i) -> size_t {   // row of the quantised input of token i
+        const int r = __shfl_sync(0xffffffffu, my_act, i & 7);
+        return is_sh ? (size_t)(A.sh_begin + t0 + i) : (size_t)r;
+    };
+    const int tok_b = TP == 2 ? (g & 1) : TP == 4 ? (g & 3) : g;
+    const int tok_m = TP == 2 ? ((g >> 1) & 1) : tok_b;
+    const size_t row_b = act_row(tok_b), row_m = act_row(tok_m);
+    size_t row_f[GuGroup<TP>::NF];
+    int tok_f[GuGroup<TP>::NF];
+#pragma unroll
+    for (int j = 0; j < GuGroup<TP>::NF; j++) {
+        tok_f[j] = TP == 2 ? (t & 1) : TP == 4 ? 2 * (t & 1) + j : 2 * t + j;
+        row_f[j] = act_row(tok_f[j]);
+    }
+    // the value this thread finishes in the cross-warp sum: (row r_row of the item, token r_tok)
+    constexpr int TPV = 8 / TP;   // threads per value
+    const int vi = warp * (16 / TPV) + (lane & 15) / TPV;
+    const int r_tok = vi % TP;
+    const int r_pair = __shfl_sync(0xffffffffu, my_row, r_tok & 7);
+    G.r_row = vi / TP;
+    G.r_orow = r_tok < cnt ? (is_sh ? A.n * A.top_k + A.sh_begin + t0 + r_tok : r_pair) : -1;
+
+#pragma unroll
+    for (int j = 0; j < 8; j++) G.bq[j][0] = G.bq[j][1] = 0;
+    if (tok_b < cnt) {
+        const int8_t *xp = in.qs + row_b * 2048 + 256 * warp + 8 * t;
+        if (TP == 2) {          // the lane's column belongs to slot g >> 1 = chunk c: sub-blocks 2c (low nibbles), 2c + 1
+            const int c_own = g >> 1;
+            const uint2 lo = *reinterpret_cast<const uint2 *>(xp + 64 * c_own);
+            const uint2 hi = *reinterpret_cast<const uint2 *>(xp + 64 * c_own + 32);
+#pragma unroll
+            for (int c = 0; c < 4; c++)
+                if (c == c_own) { G.bq[2 * c][0] = lo.x; G.bq[2 * c][1] = lo.y; G.bq[2 * c + 1][0] = hi.x; G.bq[2 * c + 1][1] = hi.y; }
+        } else if (TP == 4) {   // slot g >> 2: chunks c with (c & 1) == slot
+            const int s_own = g >> 2;
+#pragma unroll
+            for (int a = 0; a < 2; a++) {
+                const uint2 lo = *reinterpret_cast<const uint2 *>(xp + 64 * (2 * a + s_own));
+                const uint2 hi = *reinterpret_cast<const uint2 *>(xp + 64 * (2 * a + s_own) + 32);
+#pragma unroll
+                for (int sl = 0; sl < 2; sl++)
+                    if (sl == s_own) {
+                        G.bq[2 * (2 * a + sl)][0] = lo.x; G.bq[2 * (2 * a + sl)][1] = lo.y;
+                        G.bq[2 * (2 * a + sl) + 1][0] = hi.x; G.bq[2 * (2 * a + sl) + 1][1] = hi.y;
+                    }
+            }
+        } else {
+#pragma unroll
+            for (int c = 0; c < 4; c++) {
+                const uint2 lo = *reinterpret_cast<const uint2 *>(xp + 64 * c);
+                const uint2 hi = *reinterpret_cast<const uint2 *>(xp + 64 * c + 32);
+                G.bq[2 * c][0] = lo.x; G.bq[2 * c][1] = lo.y;
+                G.bq[2 * c + 1][0] = hi.x; G.bq[2 * c + 1][1] = hi.y;
+            }
+        }
+    }
+    // mins products: K positions 0..7 carry the eight sub-block sums; lanes t = 0, 1 hold them
+    G.bm[0] = G.bm[1] = 0;
+    if (t < 2 && tok_m < cnt) {
+        const uint4 bs = *reinterpret_cast<const uint4 *>(in.bsums + row_m * 128 + 16 * warp + 8 * t);
+        if (TP == 2) {
+            G.bm[0] = q4_bsum_digits(bs, (g & 1) != 0);   // column g = (.., token (g>>1)&1, digit g&1)
+        } else {
+            G.bm[0] = q4_bsum_digits(bs, false);
+            G.bm[1] = q4_bsum_digits(bs, true);
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < GuGroup<TP>::NF; j++) G.dx[j] = tok_f[j] < cnt ? in.d[row_f[j] * 8 + warp] : 0.f;
+}
+
+// One item (16 gate + 16 up rows in `stage`) against the group: this warp's block column, then the sum over the
+// eight warps in shared memory, silu(gate) * up and the store.
+template <int TP>
+__device__ inline void gu_item(const GemvArgs &A, uint8_t *stage, const GuGroup<TP> &G, int chunk, bool compute, int warp,
+                               int lane)
 {
     const int g = lane >> 2, t = lane & 3;
     const int r0 = ((g & 3) << 1) | (g >> 2);   // tile row under fragment row g (fragment row g + 8: tile row r0 + 8)
-    // this thread's share of the cross-warp sum: value (matrix rmt, fragment lane rsrc, register ri)
-    const int rq = warp * 16 + (lane & 15), rmt = lane >> 4;
-    const int rsrc = rq >> 2, ri = rq & 3;
-    const int rg = rsrc >> 2, rt = rsrc & 3;
-    const int r_row = (((rg & 3) << 1) | (rg >> 2)) + ((ri & 2) ? 8 : 0);
-    const int r_tok = 2 * rt + (ri & 1);
-    const uint32_t part_wr = (uint32_t)((lane >> 3) * Q4K_MMA_PITCH + Q4_K_BYTES * warp + (lane & 7) * 16);
-    const uint32_t part_rd = (uint32_t)((rmt * 4 + (rsrc >> 3)) * Q4K_MMA_PITCH + (rsrc & 7) * 16 + 4 * ri);
-
-    uint32_t bq[8][2];   // token g: its 8 bytes of each sub-block of block column `warp`
-    uint32_t bh = 0, bl = 0;
-    float dx0 = 0.f, dx1 = 0.f;
-    int r_orow = -1;
+    constexpr int NV = TP == 2 ? 1 : TP == 4 ? 2 : 4;
+    float acc[2][NV];
 #pragma unroll
-    for (int j = 0; j < 8; j++) bq[j][0] = bq[j][1] = 0;
+    for (int mt = 0; mt < 2; mt++) {
+#pragma unroll
+        for (int i = 0; i < NV; i++) acc[mt][i] = 0.f;
+        if (!compute) continue;
+        const uint8_t *p0 = stage + (mt * 16 + r0) * Q4K_MMA_PITCH + Q4_K_BYTES * warp;
+        const uint8_t *p1 = p0 + 8 * Q4K_MMA_PITCH;
+        const uint4 h0 = *reinterpret_cast<const uint4 *>(p0);
+        const uint4 h1 = *reinterpret_cast<const uint4 *>(p1);
+        // mins of both rows as the A operand of the mins products: lane t = 0 carries m_0..3, t = 1 m_4..7
+        const uint32_t am0 = t == 0 ? (h0.z & 0x3F3F3F3Fu) : t == 1 ? (((h0.w >> 4) & 0x0F0F0F0Fu) | ((h0.z >> 2) & 0x30303030u)) : 0u;
+        const uint32_t am1 = t == 0 ? (h1.z & 0x3F3F3F3Fu) : t == 1 ? (((h1.w >> 4) & 0x0F0F0F0Fu) | ((h1.z >> 2) & 0x30303030u)) : 0u;
+        if (TP == 8) {
+            const Q4Hdr k0 = q4k_hdr(h0), k1 = q4k_hdr(h1);
+            int ie[4] = {0, 0, 0, 0}, io[4] = {0, 0, 0, 0};   // even (low-nibble) and odd (high-nibble, x16) sub-blocks
+#pragma unroll
+            for (int c = 0; c < 4; c++) {
+                const uint2 q0 = *reinterpret_cast<const uint2 *>(p0 + 16 + 32 * c + 8 * t);
+                const uint2 q1 = *reinterpret_cast<const uint2 *>(p1 + 16 + 32 * c + 8 * t);
+                const uint32_t sw0 = c < 2 ? k0.sca : k0.scb, sw1 = c < 2 ? k1.sca : k1.scb;
+                int cc[4];
+                mma_u8s8_k32(cc, q0.x & 0x0F0F0F0Fu, q1.x & 0x0F0F0F0Fu, q0.y & 0x0F0F0F0Fu, q1.y & 0x0F0F0F0Fu, G.bq[2 * c][0],
+                             G.bq[2 * c][1]);
+                {
+                    const int s0 = (int)__byte_perm(sw0, 0u, 0x4440u + 2 * (c & 1)), s1 = (int)__byte_perm(sw1, 0u, 0x4440u + 2 * (c & 1));
+                    ie[0] += cc[0] * s0; ie[1] += cc[1] * s0; ie[2] += cc[2] * s1; ie[3] += cc[3] * s1;
+                }
+                mma_u8s8_k32(cc, q0.x & 0xF0F0F0F0u, q1.x & 0xF0F0F0F0u, q0.y & 0xF0F0F0F0u, q1.y & 0xF0F0F0F0u,
+                             G.bq[2 * c + 1][0], G.bq[2 * c + 1][1]);
+                {
+                    const int s0 = (int)__byte_perm(sw0, 0u, 0x4441u + 2 * (c & 1)), s1 = (int)__byte_perm(sw1, 0u, 0x4441u + 2 * (c & 1));
+                    io[0] += cc[0] * s0; io[1] += cc[1] * s0; io[2] += cc[2] * s1; io[3] += cc[3] * s1;
+                }
+            }
+            int ch[4], cl[4];
+            mma_u8s8_k32(ch, am0, am1, 0u, 0u, G.bm[0], 0u);
+            mma_u8s8_k32(cl, am0, am1, 0u, 0u, G.bm[1], 0u);
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const Q4Hdr &k = i < 2 ? k0 : k1;
+                acc[mt][i] = G.dx[i & 1] * (k.d16 * (float)(16 * ie[i] + io[i]) - k.dmin * (float)(64 * ch[i] + cl[i]));
+            }
+        } else {
+            // accumulators: TP 2: [0] even, [1] odd sub-blocks; TP 4: [2a + parity] for chunks 2a, 2a + 1
+            constexpr int NA = TP == 2 ? 2 : 4;
+            int cs[NA][4];
+#pragma unroll
+            for (int c = 0; c < 4; c++) {
+                const uint2 q0 = *reinterpret_cast<const uint2 *>(p0 + 16 + 32 * c + 8 * t);
+                const uint2 q1 = *reinterpret_cast<const uint2 *>(p1 + 16 + 32 * c + 8 * t);
+                const int ae = TP == 2 ? 0 : 2 * (c >> 1), ao = ae + 1;
+                const bool first = TP == 2 ? c == 0 : (c & 1) == 0;
+                if (first) {
+                    mma_u8s8_k32(cs[ae], q0.x & 0x0F0F0F0Fu, q1.x & 0x0F0F0F0Fu, q0.y & 0x0F0F0F0Fu, q1.y & 0x0F0F0F0Fu,
+                                 G.bq[2 * c][0], G.bq[2 * c][1]);
+                    mma_u8s8_k32(cs[ao], q0.x & 0xF0F0F0F0u, q1.x & 0xF0F0F0F0u, q0.y & 0xF0F0F0F0u, q1.y & 0xF0F0F0F0u,
+                                 G.bq[2 * c + 1][0], G.bq[2 * c + 1][1]);
+                } else {
+                    mma_u8s8_k32_acc(cs[ae], q0.x & 0x0F0F0F0Fu, q1.x & 0x0F0F0F0Fu, q0.y & 0x0F0F0F0Fu, q1.y & 0x0F0F0F0Fu,
+                                     G.bq[2 * c][0], G.bq[2 * c][1]);
+                    mma_u8s8_k32_acc(cs[ao], q0.x & 0xF0F0F0F0u, q1.x & 0xF0F0F0F0u, q0.y & 0xF0F0F0F0u, q1.y & 0xF0F0F0F0u,
+                                     G.bq[2 * c + 1][0], G.bq[2 * c + 1][1]);
+                }
+            }
+            // the lane's columns 2t, 2t+1 belong to one slot: TP 2: chunk t; TP 4: chunk t >> 1 (first pair), 2 + (t >> 1)
+            int v[4];
+            if (TP == 2) {
+                // scales of sub-blocks 2t, 2t+1 as a byte pair, without a branch
+                const uint32_t sh = 16 * (t & 1);
+                const uint32_t y0 = h0.y >> sh, y1 = h1.y >> sh;
+                const uint32_t lo0 = y0 & 0x3F3Fu, lo1 = y1 & 0x3F3Fu;
+                const uint32_t hi0 = ((h0.w >> sh) & 0x0F0Fu) | ((y0 >> 2) & 0x3030u), hi1 = ((h1.w >> sh) & 0x0F0Fu) | ((y1 >> 2) & 0x3030u);
+                const uint32_t sp0 = t < 2 ? lo0 : hi0, sp1 = t < 2 ? lo1 : hi1;
+                const int se0 = (int)(sp0 & 0xFFu) << 4, so0 = (int)(sp0 >> 8), se1 = (int)(sp1 & 0xFFu) << 4, so1 = (int)(sp1 >> 8);
+                v[0] = se0 * cs[0][0] + so0 * cs[1][0];
+                v[1] = se0 * cs[0][1] + so0 * cs[1][1];
+                v[2] = se1 * cs[0][2] + so1 * cs[1][2];
+                v[3] = se1 * cs[0][3] + so1 * cs[1][3];
+            } else {
+                const uint32_t sh = 16 * (t >> 1);
+                const uint32_t y0 = h0.y >> sh, y1 = h1.y >> sh;
+                const uint32_t a0 = y0 & 0x3F3Fu, a1 = y1 & 0x3F3Fu;   // chunk t >> 1
+                const uint32_t b0 = ((h0.w >> sh) & 0x0F0Fu) | ((y0 >> 2) & 0x3030u), b1 = ((h1.w >> sh) & 0x0F0Fu) | ((y1 >> 2) & 0x3030u);
+                const int ae0 = (int)(a0 & 0xFFu) << 4, ao0 = (int)(a0 >> 8), ae1 = (int)(a1 & 0xFFu) << 4, ao1 = (int)(a1 >> 8);
+                const int be0 = (int)(b0 & 0xFFu) << 4, bo0 = (int)(b0 >> 8), be1 = (int)(b1 & 0xFFu) << 4, bo1 = (int)(b1 >> 8);
+                v[0] = ae0 * cs[0][0] + ao0 * cs[1][0] + be0 * cs[2][0] + bo0 * cs[3][0];
+                v[1] = ae0 * cs[0][1] + ao0 * cs[1][1] + be0 * cs[2][1] + bo0 * cs[3][1];
+                v[2] = ae1 * cs[0][2] + ao1 * cs[1][2] + be1 * cs[2][2] + bo1 * cs[3][2];
+                v[3] = ae1 * cs[0][3] + ao1 * cs[1][3] + be1 * cs[2][3] + bo1 * cs[3][3];
+            }
+            const bool up2 = (t & 2) != 0;   // row g + 8 ends in the lanes with t >= 2
+            const uint32_t hx = up2 ? h1.x : h0.x;
+            const float d16 = half_bits_to_float((uint16_t)(hx & 0xffffu)) * 0.0625f;
+            const float dmin = half_bits_to_float((uint16_t)(hx >> 16));
+            if (TP == 2) {
+                // sum over the four slots (lanes t = 0..3); lane t ends with (row g + 8 (t>>1), token t & 1)
+                const int ka = (up2 ? v[2] : v[0]) + __shfl_xor_sync(0xffffffffu, up2 ? v[0] : v[2], 2);
+                const int kb = (up2 ? v[3] : v[1]) + __shfl_xor_sync(0xffffffffu, up2 ? v[1] : v[3], 2);
+                const bool up1 = (t & 1) != 0;
+                const int k = (up1 ? kb : ka) + __shfl_xor_sync(0xffffffffu, up1 ? ka : kb, 1);
+                // columns 2t, 2t+1 of the mins product: high and low digit of token t & 1
+                int cm[4];
+                mma_u8s8_k32(cm, am0, am1, 0u, 0u, G.bm[0], 0u);
+                const int imin = up2 ? 64 * cm[2] + cm[3] : 64 * cm[0] + cm[1];
+                acc[mt][0] = G.dx[0] * (d16 * (float)k - dmin * (float)imin);
+            } else {
+                // sum over the two slots (lanes t, t ^ 2); the lane keeps (row g + 8 (t>>1), tokens 2 (t&1), 2 (t&1) + 1)
+                const int k0 = (up2 ? v[2] : v[0]) + __shfl_xor_sync(0xffffffffu, up2 ? v[0] : v[2], 2);
+                const int k1 = (up2 ? v[3] : v[1]) + __shfl_xor_sync(0xffffffffu, up2 ? v[1] : v[3], 2);
+                int ch[4], cl[4];   // columns = tokens (n & 3): 2t, 2t+1 -> tokens 2 (t&1), 2 (t&1) + 1
+                mma_u8s8_k32(ch, am0, am1, 0u, 0u, G.bm[0], 0u);
+                mma_u8s8_k32(cl, am0, am1, 0u, 0u, G.bm[1], 0u);
+                const int m0 = up2 ? 64 * ch[2] + cl[2] : 64 * ch[0] + cl[0];
+                const int m1 = up2 ? 64 * ch[3] + cl[3] : 64 * ch[1] + cl[1];
+                acc[mt][0] = G.dx[0] * (d16 * (float)k0 - dmin * (float)m0);
+                acc[mt][1] = G.dx[1] * (d16 * (float)k1 - dmin * (float)m1);
+            }
+        }
+    }
+    // partial sums of this warp's block column into its own bytes of rows 0..7 of the slot: value idx of
+    // matrix mt = 16 TP mt + TP (row in the item) + token, at row idx >> 5, word idx & 31 of the warp's 144 bytes
+    __syncwarp();
+    {
+        uint8_t *mine = stage + Q4_K_BYTES * warp;
+        auto at = [&](int idx) -> uint8_t * { return mine + (idx >> 5) * Q4K_MMA_PITCH + (idx & 31) * 4; };
+#pragma unroll
+        for (int mt = 0; mt < 2; mt++) {
+            if (TP == 2) {
+                *reinterpret_cast<float *>(at(mt * 32 + (r0 + 8 * (t >> 1)) * 2 + (t & 1))) = acc[mt][0];
+            } else if (TP == 4) {
+                *reinterpret_cast<float2 *>(at(mt * 64 + (r0 + 8 * (t >> 1)) * 4 + 2 * (t & 1))) = make_float2(acc[mt][0], acc[mt][1]);
+            } else {
+                *reinterpret_cast<float2 *>(at(mt * 128 + r0 * 8 + 2 * t)) = make_float2(acc[mt][0], acc[mt][1]);
+                *reinterpret_cast<float2 *>(at(mt * 128 + (r0 + 8) * 8 + 2 * t)) = make_float2(acc[mt][2], acc[mt][3]);
+            }
+        }
+    }
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    {
+        constexpr int TPV = 8 / TP;   // threads per value, each adding TP of the eight partial sums
+        const int mt = lane >> 4, part = lane % TPV;
+        const int idx = mt * 16 * TP + warp * (16 / TPV) + (lane & 15) / TPV;
+        const uint8_t *src = stage + (idx >> 5) * Q4K_MMA_PITCH + (idx & 31) * 4 + Q4_K_BYTES * TP * part;
+        // the eight partial sums are added as one balanced tree whatever TP is, so that a token's result does not
+        // depend on how many tokens shared its group (the order of an expert's token list is not fixed between runs)
+        float pv[TP];
+#pragma unroll
+        for (int w = 0; w < TP; w++) pv[w] = *reinterpret_cast<const float *>(src + Q4_K_BYTES * w);
+#pragma unroll
+        for (int st = 1; st < TP; st *= 2)
+#pragma unroll
+            for (int w = 0; w < TP; w += 2 * st) pv[w] += pv[w + st];
+        float v = pv[0];
+        if (TPV >= 2) v += __shfl_xor_sync(0xffffffffu, v, 1);
+        if (TPV >= 4) v += __shfl_xor_sync(0xffffffffu, v, 2);
+        const float up = __shfl_xor_sync(0xffffffffu, v, 16);
+        if (lane < 16 && part == 0 && G.r_orow >= 0 && compute)
+            A.out[(size_t)G.r_orow * A.rows_total + chunk * 16 + G.r_row] = v / (1.f + expf(-v)) * up;   // silu(gate) * up
+    }
+}
 
-    int cur_slot = -1, cur_group = -1, m = 0, items_in_slot = 0, slot_groups = 0;
-    const int *list = nullptr;
-    bool is_sh = false, failed = false;
-    for (; it < n_items; it++) {
+// The items of one (expert, token group) starting at `cur` (item `it` of the CTA).
+template <int TP>
+__device__ inline void gu_run_group(const GemvArgs &A, uint8_t *ring, const MmaWork &work, MmaCursor &cur, int &it, int n_items,
+                                    bool is_sh, int my_row, int t0, int cnt, int warp, int lane, bool &failed, LookAhead &la,
+                                    int &items_in_slot)
+{
+    GuGroup<TP> G;
+    gu_load_group<TP>(A, is_sh, my_row, t0, cnt, warp, lane, G);
+    const int slot = cur.slot, group = cur.group;
+    while (it < n_items && cur.slot == slot && cur.group == group) {
         const int s = it % NSTAGE;
         const uint32_t use = (uint32_t)(it / NSTAGE);
-        if (cur.slot != cur_slot) {
-            if (cur_slot >= 0 && (is_sh ? A.quant_dt_s : A.quant_dt_r) != 0)
-                finish_slot(A, is_sh ? work.n_active : cur_slot, items_in_slot, work.cpe * slot_groups, is_sh, list, m, warp,
-                            lane);
-            items_in_slot = 0;
-            cur_slot = cur.slot;
-            cur_group = -1;
-            slot_groups = cur.groups;
-            is_sh = cur.slot >= work.n_active;
-            if (is_sh) {
-                m = A.sh_count;
-                list = nullptr;
-            } else {
-                const int e = A.g.active[cur.slot];
-                m = A.g.count[e];
-                list = A.g.pairs + A.g.offset[e];
-            }
-        }
-        if (cur.group != cur_group) {   // the group's tokens: fragments of their quantised rows
-            cur_group = cur.group;
-            const int t0 = 8 * cur.group;
-            const int cnt = m - t0 < 8 ? m - t0 : 8;
-            const QAct &in = is_sh ? A.in_s : A.in_r;
-            bh = bl = 0;
-            if (g < cnt) {
-                const size_t row = is_sh ? (size_t)(A.sh_begin + t0 + g) : (size_t)(list[t0 + g] / A.top_k);
-                const int8_t *xp = in.qs + row * 2048 + 256 * warp + 8 * t;
-#pragma unroll
-                for (int c = 0; c < 4; c++) {
-                    const uint2 lo = *reinterpret_cast<const uint2 *>(xp + 64 * c);
-                    const uint2 hi = *reinterpret_cast<const uint2 *>(xp + 64 * c + 32);
-                    bq[2 * c][0] = lo.x; bq[2 * c][1] = lo.y;
-                    bq[2 * c + 1][0] = hi.x; bq[2 * c + 1][1] = hi.y;
-                }
-                if (t < 2) {   // sums of the quants under sub-blocks 4t .. 4t+3, as two signed byte digits
-                    const uint4 bs = *reinterpret_cast<const uint4 *>(in.bsums + row * 128 + 16 * warp + 8 * t);
-                    const uint32_t w4[4] = {bs.x, bs.y, bs.z, bs.w};
-#pragma unroll
-                    for (int i = 0; i < 4; i++) {
-                        const int v = (int)(int16_t)(w4[i] & 0xffffu) + (int)(int16_t)(w4[i] >> 16);
-                        bh |= (uint32_t)((v >> 6) & 0xFF) << (8 * i);
-                        bl |= (uint32_t)(v & 63) << (8 * i);
-                    }
-                }
-            } else {
-#pragma unroll
-                for (int j = 0; j < 8; j++) bq[j][0] = bq[j][1] = 0;
-            }
-            dx0 = dx1 = 0.f;
-            if (2 * t < cnt) {
-                const size_t row = is_sh ? (size_t)(A.sh_begin + t0 + 2 * t) : (size_t)(list[t0 + 2 * t] / A.top_k);
-                dx0 = in.d[row * 8 + warp];
-            }
-            if (2 * t + 1 < cnt) {
-                const size_t row = is_sh ? (size_t)(A.sh_begin + t0 + 2 * t + 1) : (size_t)(list[t0 + 2 * t + 1] / A.top_k);
-                dx1 = in.d[row * 8 + warp];
-            }
-            r_orow = -1;
-            if (r_tok < cnt) r_orow = is_sh ? A.n * A.top_k + A.sh_begin + t0 + r_tok : list[t0 + r_tok];
-        }
         // a wait that runs out is recorded; the warp keeps walking its items (and meeting the barriers
         // it shares with the other warps) without computing
         if (!failed && A.debug != 2 && !mbar_wait(ring_full(ring, s), use & 1)) {
             set_status(A.status, PMOE_ERR_TIMEOUT, 18, it);
             failed = true;
         }
-        uint8_t *stage = ring_stage(ring, s, A.stage_bytes);
-        const bool compute = !failed && A.debug != 1;
-        float acc[2][4];
-#pragma unroll
-        for (int mt = 0; mt < 2; mt++) {
-#pragma unroll
-            for (int i = 0; i < 4; i++) acc[mt][i] = 0.f;
-            if (!compute) continue;
-            const uint8_t *p0 = stage + (mt * 16 + r0) * Q4K_MMA_PITCH + Q4_K_BYTES * warp;
-            const uint8_t *p1 = p0 + 8 * Q4K_MMA_PITCH;
-            const Q4Hdr h0 = q4k_hdr(*reinterpret_cast<const uint4 *>(p0));
-            const Q4Hdr h1 = q4k_hdr(*reinterpret_cast<const uint4 *>(p1));
-            int ie[4] = {0, 0, 0, 0}, io[4] = {0, 0, 0, 0};   // even (low-nibble) and odd (high-nibble, x16) sub-blocks
-#pragma unroll
-            for (int c = 0; c < 4; c++) {
-                const uint2 q0 = *reinterpret_cast<const uint2 *>(p0 + 16 + 32 * c + 8 * t);
-                const uint2 q1 = *reinterpret_cast<const uint2 *>(p1 + 16 + 32 * c + 8 * t);
-                const uint32_t sw0 = c < 2 ? h0.sca : h0.scb, sw1 = c < 2 ? h1.sca : h1.scb;
-                int cc[4];
-                mma_u8s8_k32(cc, q0.x & 0x0F0F0F0Fu, q1.x & 0x0F0F0F0Fu, q0.y & 0x0F0F0F0Fu, q1.y & 0x0F0F0F0Fu, bq[2 * c][0],
-                             bq[2 * c][1]);
-                {
-                    const int s0 = (c & 1) ? byte_of<2>(sw0) : byte_of<0>(sw0);
-                    const int s1 = (c & 1) ? byte_of<2>(sw1) : byte_of<0>(sw1);
-                    ie[0] += cc[0] * s0; ie[1] += cc[1] * s0; ie[2] += cc[2] * s1; ie[3] += cc[3] * s1;
-                }
-                mma_u8s8_k32(cc, q0.x & 0xF0F0F0F0u, q1.x & 0xF0F0F0F0u, q0.y & 0xF0F0F0F0u, q1.y & 0xF0F0F0F0u,
-                             bq[2 * c + 1][0], bq[2 * c + 1][1]);
-                {
-                    const int s0 = (c & 1) ? byte_of<3>(sw0) : byte_of<1>(sw0);
-                    const int s1 = (c & 1) ? byte_of<3>(sw1) : byte_of<1>(sw1);
-                    io[0] += cc[0] * s0; io[1] += cc[1] * s0; io[2] += cc[2] * s1; io[3] += cc[3] * s1;
-                }
-            }
-            // mins: K positions 0..7 carry m_0..m_7 (lanes t = 0, 1), the rest is zero
-            const uint32_t am0 = t == 0 ? h0.mna : (t == 1 ? h0.mnb : 0u);
-            const uint32_t am1 = t == 0 ? h1.mna : (t == 1 ? h1.mnb : 0u);
-            int ch[4], cl[4];
-            mma_u8s8_k32(ch, am0, am1, 0u, 0u, bh, 0u);
-            mma_u8s8_k32(cl, am0, am1, 0u, 0u, bl, 0u);
-#pragma unroll
-            for (int i = 0; i < 4; i++) {
-                const Q4Hdr &h = i < 2 ? h0 : h1;
-                const float dx = (i & 1) ? dx1 : dx0;
-                acc[mt][i] = dx * (h.d16 * (float)(16 * ie[i] + io[i]) - h.dmin * (float)(64 * ch[i] + cl[i]));
-            }
-        }
-        // partial sums of this warp's block column into its own part of rows 0..7 of the slot
-        __syncwarp();
-#pragma unroll
-        for (int mt = 0; mt < 2; mt++)
-            *reinterpret_cast<float4 *>(stage + part_wr + mt * 4 * Q4K_MMA_PITCH) =
-                make_float4(acc[mt][0], acc[mt][1], acc[mt][2], acc[mt][3]);
-        asm volatile("bar.sync 1, 256;" ::: "memory");
-        float v = 0.f;
-#pragma unroll
-        for (int w = 0; w < GEMV_WARPS; w++) v += *reinterpret_cast<const float *>(stage + part_rd + Q4_K_BYTES * w);
-        const float up = __shfl_xor_sync(0xffffffffu, v, 16);
-        if (lane < 16 && r_orow >= 0 && compute)
-            A.out[(size_t)r_orow * A.rows_total + cur.chunk * 16 + r_row] = v / (1.f + expf(-v)) * up;   // silu(gate) * up
+        gu_item<TP>(A, ring_stage(ring, s, A.stage_bytes), G, cur.chunk, !failed && A.debug != 1, warp, lane);
         __syncwarp();
         if (lane == 0) mbar_arrive(ring_empty(ring, s));
+        la.advance(A, work, lane);
         work.advance(cur);
+        it++;
         items_in_slot++;
     }
-    if (cur_slot >= 0 && (is_sh ? A.quant_dt_s : A.quant_dt_r) != 0)
-        finish_slot(A, is_sh ? work.n_active : cur_slot, items_in_slot, work.cpe * slot_groups, is_sh, list, m, warp, lane);
+}
+
+// The compute warps' side: items [it, n_items) of this CTA starting at `cur`.
+__device__ inline bool run_items_q4k_mma(const GemvArgs &A, uint8_t *ring, const MmaWork &work, MmaCursor cur, int n_items,
+                                         int &it, int warp, int lane)
+{
+    LookAhead la;
+    la.slot = la.group = -1;
+    la.step = 3;
+    bool failed = false;
+    int cur_slot = -1, items_in_slot = 0, slot_groups = 0, slot_m = 0, slot_off = 0;
+    bool slot_sh = false;
+    while (it < n_items) {
+        const bool is_sh = cur.slot >= work.n_active;
+        const int t0 = GEMV_TG_MMA * cur.group;
+        int m, off = 0, my_row = -1;
+        if (is_sh) {
+            m = A.sh_count;
+        } else if (la.ready(work, cur.slot, cur.group)) {
+            m = la.m;
+            off = la.off;
+            my_row = la.row;
+        } else {
+            const int e = A.g.active[cur.slot];
+            m = A.g.count[e];
+            off = A.g.offset[e];
+            const int i = t0 + (lane & 7);
+            if (i < m) my_row = A.g.pairs[off + i];
+        }
+        if (cur.slot != cur_slot) {
+            // leaving a slot: the CTA that completes its last item re-quantises the expert's activated rows
+            if (cur_slot >= 0 && (slot_sh ? A.quant_dt_s : A.quant_dt_r) != 0)
+                finish_slot(A, slot_sh ? work.n_active : cur_slot, items_in_slot, work.cpe * slot_groups, slot_sh,
+                            A.g.pairs + slot_off, slot_m, warp, lane);
+            items_in_slot = 0;
+            cur_slot = cur.slot;
+            slot_groups = cur.groups;
+            slot_sh = is_sh;
+            slot_m = m;
+            slot_off = off;
+        }
+        la.start(cur);
+        const int cnt = m - t0 < GEMV_TG_MMA ? m - t0 : GEMV_TG_MMA;
+        if (cnt <= 2) gu_run_group<2>(A, ring, work, cur, it, n_items, is_sh, my_row, t0, cnt, warp, lane, failed, la, items_in_slot);
+        else if (cnt <= 4) gu_run_group<4>(A, ring, work, cur, it, n_items, is_sh, my_row, t0, cnt, warp, lane, failed, la, items_in_slot);
+        else gu_run_group<8>(A, ring, work, cur, it, n_items, is_sh, my_row, t0, cnt, warp, lane, failed, la, items_in_slot);
+    }
+    if (cur_slot >= 0 && (slot_sh ? A.quant_dt_s : A.quant_dt_r) != 0)
+        finish_slot(A, slot_sh ? work.n_active : cur_slot, items_in_slot, work.cpe * slot_groups, slot_sh, A.g.pairs + slot_off,
+                    slot_m, warp, lane);
     return !failed;
 }
 
@@ -414,14 +642,6 @@ __device__ inline uint64_t *dm_full(uint8_t *smem, int s) { return reinterpret_c
 __device__ inline uint64_t *dm_empty(uint8_t *smem, int s) { return reinterpret_cast<uint64_t *>(smem) + DM_NSTAGE + s; }
 __device__ inline uint8_t *dm_stage(uint8_t *smem, int s) { return smem + DM_HDR + s * DM_ITEM; }
 
-__device__ inline void mma_u8s8_k32_acc(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
-                                        uint32_t b1)
-{
-    asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-
 __device__ inline void mma_s8s8_k32(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                     uint32_t b1)
 {
@@ -478,37 +698,6 @@ template <int SA> __device__ inline void q6_unpack(uint32_t ql, uint32_t qh, uin
     lo = (ql & 0x0F0F0F0Fu) | ((qh << (4 - 2 * SA)) & 0x30303030u);
     hi = ((ql >> 4) & 0x0F0F0F0Fu) | ((SA == 0 ? qh : qh >> 2) & 0x30303030u);
 }
-
-// The lists of the token group that follows the current one, fetched one dependent load per item while the
-// current group's items are computed (the warp issues in order: a chain of dependent loads would stall it for
-// the whole chain, and under the weight stream a single L2 access already takes microseconds).
-struct LookAhead {
-    int slot, group, step, e, m, off, row;   // row: pair id of token (lane & 7) of that group, -1 if none
-    __device__ inline void start(const MmaCursor &cur)
-    {
-        slot = cur.slot; group = cur.group + 1;
-        if (group >= cur.groups) { slot++; group = 0; }
-        step = 0; row = -1; m = 0; e = 0; off = 0;
-    }
-    __device__ inline void advance(const GemvArgs &A, const MmaWork &work, int lane)
-    {
-        if (slot >= work.n_active || step > 2) return;   // the shared expert (or nothing) follows: no lists to read
-        if (step == 0) {
-            e = A.g.active[slot];
-        } else if (step == 1) {
-            m = A.g.count[e];
-            off = A.g.offset[e];
-        } else {
-            const int i = GEMV_TG_MMA * group + (lane & 7);
-            row = i < m ? A.g.pairs[off + i] : -1;
-        }
-        step++;
-    }
-    __device__ inline bool ready(const MmaWork &work, int s, int g) const
-    {
-        return s == slot && g == group && s < work.n_active && step > 2;
-    }
-};
 
 // What a group of up to TP tokens of one expert leaves in a lane's registers.
 template <int TP> struct DmGroup {
@@ -1046,11 +1235,12 @@ cudaError_t launch_gate_up_q4k_mma(GemvArgs &A, int dt_s, cudaStream_t s)
     return cudaErrorInvalidValue;
 }
 
-// PMOE_MMA=0 in the environment keeps the dp4a kernels for Q4_K gate/up (comparison runs)
-bool mma_enabled()
+// PMOE_MMA in the environment (comparison runs): 0 keeps the dp4a kernels everywhere, 2 takes the tensor-core
+// kernel for Q4_K gate/up only, 3 for Q6_K down only; unset or 1: both
+bool mma_enabled(int kernel)
 {
-    static const bool on = !(getenv("PMOE_MMA") && atoi(getenv("PMOE_MMA")) == 0);
-    return on;
+    static const int mode = getenv("PMOE_MMA") ? atoi(getenv("PMOE_MMA")) : 1;
+    return mode == 1 || (mode == 2 && kernel == 1) || (mode == 3 && kernel == 2);
 }
 
 
