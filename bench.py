@@ -456,7 +456,7 @@ def stack_record(ctx):
     torch, args, N = ctx.torch, ctx.args, ctx.N
     nl, gb = args.stack_layers, args.stack_batch
     n_home = gb // N
-    blocks = build_rank_blocks(ctx, nl, "q4k_q6k", max_tokens=gb if N > 1 else max(gb, 64), seed=3)
+    blocks = build_rank_blocks(ctx, nl, "q4k_q6k_all", max_tokens=gb if N > 1 else max(gb, 64), seed=3)
     eps = [make_ep(ctx, b) for b in blocks] if N > 1 else None
     h0 = ctx.x(n_home, 500).float()
     resid = torch.empty_like(h0)
@@ -496,7 +496,7 @@ def stack_record(ctx):
     rec = dict(metric="48-layer MoE FFN stack tokens/s (decode)", value=gb / (ms_step * 1e-3), unit=UNIT,
                ms_per_step=ms_step, us_per_layer=1e3 * ms_step / nl, steps=steps, repeats=R,
                spread_ms_per_step=[min(ms) / steps, max(ms) / steps], scaling="strong",
-               config=dict(workload=f"{nl} stacked qwen3next-moe blocks (gate/up Q4_K, down Q6_K, shared Q6_K/Q4_K like the "
+               config=dict(workload=f"{nl} stacked qwen3next-moe blocks (gate/up Q4_K, down Q6_K, shared expert quantised like the "
                                     f"routed ones), residual add + RMSNorm(eps 1e-6, weight 1) between layers, global decode "
                                     f"batch {gb}, f32 residual stream", global_batch=gb, tokens_per_gpu=n_home,
                            parallelism=f"ep{N}" if N > 1 else "single", launch=mode,

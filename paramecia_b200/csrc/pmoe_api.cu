@@ -157,7 +157,7 @@ void carve_workspace(pmoe_layer *L, Carver &c)
     w.act_q80.bsums = nullptr;
     w.act_h = c.take<__half>(rows * F);
     w.partial = c.take<float>(rows * H);
-    w.slot_done = c.take<int>(El + 1);
+    w.slot_done = c.take<int>(El + 1 + (n + 7) / 8);   // per expert, the shared expert, and its 8-token tiles
     L->st_x = c.take<float>(n * H);
     L->st_out = c.take<float>(n * H);
     L->st_logits = c.take<float>(n * E);
@@ -426,7 +426,7 @@ int pmoe_layer_create(const pmoe_layer_desc *desc, pmoe_layer **out)
             Carver real{(uint8_t *)block};
             carve_workspace(L, real);
             e = cudaMemset(L->ws.status, 0, sizeof(DevStatus));
-            if (e == cudaSuccess) e = cudaMemset(L->ws.slot_done, 0, sizeof(int) * (El + 1));
+            if (e == cudaSuccess) e = cudaMemset(L->ws.slot_done, 0, sizeof(int) * (El + 1 + ((size_t)d.max_tokens + 7) / 8));
             if (e != cudaSuccess) rc = fail_cuda(e, "workspace");
         }
     }

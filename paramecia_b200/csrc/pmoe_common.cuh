@@ -275,7 +275,8 @@ struct Workspace {
     QAct act_q8k, act_q80;
     __half *act_h;       // [n*(k+1), F]  fake-quantised activation for the fp16 down GEMM
     float *partial;      // [n*(k+1), H]  weighted down-projection rows
-    int *slot_done;      // [E_local + 1] per-expert completion counters of the gate/up kernel (zero between calls)
+    int *slot_done;      // [E_local + 1 + max_tokens/8] completion counters of the gate/up kernel: per expert, the shared
+                         // expert, and the shared expert's 8-token tiles (zero between calls)
 };
 
 // ---------------------------------------------------------------- launch interface

@@ -842,8 +842,9 @@ __device__ inline void run_pass(const GemvArgs &A, const uint8_t *stage, int chu
 // Called by the eight compute warps when they leave a slot: adds the items this CTA finished to the slot's
 // counter; the CTA that brings it to `cpe` (all rows of the expert's activation are in memory) quantises those
 // rows for the down projection.  Writers fence before the counter update, the reader after it.
+// The shared expert's rows may be finished tile by tile: `first` is the first of the m tokens then.
 __device__ inline void finish_slot(const GemvArgs &A, int counter_idx, int items, int cpe, bool is_shared,
-                                   const int *list, int m, int warp, int lane)
+                                   const int *list, int m, int warp, int lane, int first = 0)
 {
     __shared__ int s_last;
     if (A.debug == 4) return;
@@ -860,7 +861,7 @@ __device__ inline void finish_slot(const GemvArgs &A, int counter_idx, int items
     const int dt = is_shared ? A.quant_dt_s : A.quant_dt_r;
     const bool kq = is_kquant(dt);
     for (int i = warp; i < m; i += GEMV_WARPS) {
-        const size_t r = is_shared ? (size_t)A.n * A.top_k + A.sh_begin + i : (size_t)list[i];
+        const size_t r = is_shared ? (size_t)A.n * A.top_k + A.sh_begin + first + i : (size_t)list[i];
         if (A.rows_total == 512) warp_quant_row512(A.out + r * 512, kq, A.q8k_out, A.q80_out, r, lane);
         else block_quant_row(A.out + r * A.rows_total, A.rows_total, kq, !kq, A.q8k_out, A.q80_out, r, 0, 1, lane);
     }
@@ -1098,20 +1099,25 @@ __device__ inline bool run_items_shared_mma(const GemvArgs &A, uint8_t *ring, co
                 }
             }
         }
-        if (job_hi >= 0) {   // progress is counted in jobs
-            const long base = (long)cur.chunk * (MT * ntiles);
-            const long lo = job_lo > base ? job_lo : base, hi = job_hi < base + MT * ntiles ? job_hi : base + MT * ntiles;
-            items_in_slot += hi > lo ? (int)(hi - lo) - 1 : -1;
-        }
         __syncwarp();
         if (lane == 0) mbar_arrive(ring_empty(ring, s));
         plan.advance(cur);
         it++;
         items_in_slot++;
     }
-    if (fuse_quant && items_in_slot > 0)
-        finish_slot(A, plan.n_active, items_in_slot, job_hi >= 0 ? plan.cpe_s * MT * ntiles : plan.cpe_s, true, nullptr, m,
-                    warp, lane);
+    if (fuse_quant && job_hi >= 0) {
+        // split by jobs: every 8-token tile has its own counter (behind the per-expert ones), and the CTA that
+        // completes a tile's last chunk re-quantises those eight rows -- no CTA is left with all the rows at the end
+        for (int nt = 0; nt < ntiles; nt++) {
+            const long cmin = job_lo > nt ? (job_lo - nt + ntiles - 1) / ntiles : 0;
+            const long cmax = job_hi - 1 >= nt ? (job_hi - 1 - nt) / ntiles : -1;
+            if (cmax < cmin) continue;
+            const int rows = m - 8 * nt < 8 ? m - 8 * nt : 8;
+            finish_slot(A, A.e_local + 1 + nt, (int)(cmax - cmin + 1), plan.cpe_s, true, nullptr, rows, warp, lane, 8 * nt);
+        }
+    } else if (fuse_quant && items_in_slot > 0) {
+        finish_slot(A, plan.n_active, items_in_slot, plan.cpe_s, true, nullptr, m, warp, lane);
+    }
     return !failed;
 }
 

@@ -439,8 +439,20 @@ __device__ inline bool run_items_q4k_mma(const GemvArgs &A, uint8_t *ring, const
     la.slot = la.group = -1;
     la.step = 3;
     bool failed = false;
-    int cur_slot = -1, items_in_slot = 0, slot_groups = 0, slot_m = 0, slot_off = 0;
+    // progress bookkeeping for the fused re-quantisation: a routed expert is finished as a whole (all its groups),
+    // the shared expert group by group (its eight rows are quantised by whoever completes the group)
+    int cur_slot = -1, cur_group = -1, items_in_slot = 0, slot_groups = 0, slot_m = 0, slot_off = 0;
     bool slot_sh = false;
+    auto leave = [&]() {
+        if (cur_slot < 0 || (slot_sh ? A.quant_dt_s : A.quant_dt_r) == 0) return;
+        if (slot_sh) {
+            const int first = GEMV_TG_MMA * cur_group;
+            finish_slot(A, A.e_local + 1 + cur_group, items_in_slot, work.cpe, true, nullptr,
+                        slot_m - first < GEMV_TG_MMA ? slot_m - first : GEMV_TG_MMA, warp, lane, first);
+        } else {
+            finish_slot(A, cur_slot, items_in_slot, work.cpe * slot_groups, false, A.g.pairs + slot_off, slot_m, warp, lane);
+        }
+    };
     while (it < n_items) {
         const bool is_sh = cur.slot >= work.n_active;
         const int t0 = GEMV_TG_MMA * cur.group;
@@ -458,11 +470,8 @@ __device__ inline bool run_items_q4k_mma(const GemvArgs &A, uint8_t *ring, const
             const int i = t0 + (lane & 7);
             if (i < m) my_row = A.g.pairs[off + i];
         }
-        if (cur.slot != cur_slot) {
-            // leaving a slot: the CTA that completes its last item re-quantises the expert's activated rows
-            if (cur_slot >= 0 && (slot_sh ? A.quant_dt_s : A.quant_dt_r) != 0)
-                finish_slot(A, slot_sh ? work.n_active : cur_slot, items_in_slot, work.cpe * slot_groups, slot_sh,
-                            A.g.pairs + slot_off, slot_m, warp, lane);
+        if (cur.slot != cur_slot || is_sh) {
+            leave();
             items_in_slot = 0;
             cur_slot = cur.slot;
             slot_groups = cur.groups;
@@ -470,22 +479,112 @@ __device__ inline bool run_items_q4k_mma(const GemvArgs &A, uint8_t *ring, const
             slot_m = m;
             slot_off = off;
         }
+        cur_group = cur.group;
         la.start(cur);
         const int cnt = m - t0 < GEMV_TG_MMA ? m - t0 : GEMV_TG_MMA;
         if (cnt <= 2) gu_run_group<2>(A, ring, work, cur, it, n_items, is_sh, my_row, t0, cnt, warp, lane, failed, la, items_in_slot);
         else if (cnt <= 4) gu_run_group<4>(A, ring, work, cur, it, n_items, is_sh, my_row, t0, cnt, warp, lane, failed, la, items_in_slot);
         else gu_run_group<8>(A, ring, work, cur, it, n_items, is_sh, my_row, t0, cnt, warp, lane, failed, la, items_in_slot);
     }
-    if (cur_slot >= 0 && (slot_sh ? A.quant_dt_s : A.quant_dt_r) != 0)
-        finish_slot(A, slot_sh ? work.n_active : cur_slot, items_in_slot, work.cpe * slot_groups, slot_sh, A.g.pairs + slot_off,
-                    slot_m, warp, lane);
+    leave();
     return !failed;
+}
+
+// ---------------------------------------------------------------- a Q8_0 shared expert beside the tensor-core items
+// A Q8_0 shared expert over SHARED_MMA_MIN tokens or more is served by a tenth warp of every CTA, in the shadow
+// of the routed experts' stream: the shared expert is small (it stays in L2), but a job -- 16 rows x 8 tokens over
+// the whole K, one block per mma.m16n8k32 -- is a chain of L2 round trips, so it belongs beside the memory-bound
+// work, not after it.  The jobs are numbered (16-row tile, 8-token tile), token tile fastest, and every CTA's warp
+// takes an equal share; weights and activations are read straight from global memory.  For gate/up each token
+// tile has a completion counter (behind the per-expert ones): the warp that finishes a tile's last job
+// re-quantises those eight activated rows for the down projection.
+constexpr int SHW_WARP = GEMV_WARPS + 1;
+constexpr int SHW_THREADS = GEMV_THREADS + 32;
+
+template <int NMAT> __device__ inline void q80_shared_warp(const GemvArgs &A, int lane)
+{
+    using C = Cfg<PMOE_Q8_0, NMAT>;
+    constexpr int KB = C::K / QK8_0;
+    const int g = lane >> 2, t = lane & 3;
+    const int m = A.sh_count, ntiles = (m + 7) / 8;
+    const int tiles16 = NMAT == 2 ? A.rows_total / 8 : A.rows_total / 16;   // gate/up: 8 gate + 8 up rows per tile
+    const long total = (long)tiles16 * ntiles;
+    const long lo = total * blockIdx.x / gridDim.x, hi = total * (blockIdx.x + 1) / gridDim.x;
+    const QAct &in = A.in_s;
+    const size_t row0 = NMAT == 2 ? (size_t)A.sh_begin : (size_t)A.n * A.top_k + A.sh_begin;  // activation row of token 0
+    const size_t out0 = (size_t)A.n * A.top_k + A.sh_begin;                                   // output row of token 0
+    const bool fuse_quant = NMAT == 2 && A.quant_dt_s != 0;
+    if (A.debug == 1) return;
+    for (long j = lo; j < hi; j++) {
+        const int tile = (int)(j / ntiles), nt = (int)(j - (long)tile * ntiles);
+        // fragment rows g and g + 8: gate row and up row 8*tile + g, or down rows 16*tile + g, + 8
+        const uint8_t *r0 = A.sw0 + (size_t)(NMAT == 2 ? 8 * tile + g : 16 * tile + g) * C::ROW_BYTES;
+        const uint8_t *r1 = NMAT == 2 ? A.sw1 + (size_t)(8 * tile + g) * C::ROW_BYTES : r0 + 8 * C::ROW_BYTES;
+        // B column g = token 8 nt + g; C columns 2t, 2t+1 = tokens 8 nt + 2t (+1).  Columns past the last token
+        // read token 0's rows; their sums are never stored.
+        const int tok_b = nt * 8 + g, tok_c = nt * 8 + 2 * t;
+        const bool c0_ok = tok_c < m, c1_ok = tok_c + 1 < m;
+        const int8_t *xq = in.qs + (row0 + (tok_b < m ? tok_b : 0)) * C::K + 8 * t;
+        const float *dx0 = in.d + (row0 + (c0_ok ? tok_c : 0)) * KB;
+        const float *dx1 = in.d + (row0 + (c1_ok ? tok_c + 1 : 0)) * KB;
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+        MmaActs va, vb;
+        mma_load_acts(va, xq, dx0, dx1, 0);
+#pragma unroll 1
+        for (int kb = 0; kb < KB; kb += 8) {   // the loads of the next four blocks fly under the current four
+            mma_load_acts(vb, xq, dx0, dx1, kb + 4);
+            mma_step4(r0, r1, kb, t, va, acc);
+            if (kb + 8 < KB) mma_load_acts(va, xq, dx0, dx1, kb + 8);
+            mma_step4(r0, r1, kb + 4, t, vb, acc);
+        }
+        if (NMAT == 2) {
+            const int row = 8 * tile + g;
+            const float v0 = acc[0] / (1.f + expf(-acc[0])) * acc[2];  // silu(gate) * up
+            const float v1 = acc[1] / (1.f + expf(-acc[1])) * acc[3];
+            if (c0_ok) A.out[(out0 + tok_c) * A.rows_total + row] = v0;
+            if (c1_ok) A.out[(out0 + tok_c + 1) * A.rows_total + row] = v1;
+        } else {
+            const int row = 16 * tile + g;
+            if (c0_ok) {
+                const float sc = A.scale_s[A.sh_begin + tok_c];
+                float *o = A.out + (out0 + tok_c) * A.rows_total + row;
+                o[0] = acc[0] * sc;
+                o[8] = acc[2] * sc;
+            }
+            if (c1_ok) {
+                const float sc = A.scale_s[A.sh_begin + tok_c + 1];
+                float *o = A.out + (out0 + tok_c + 1) * A.rows_total + row;
+                o[0] = acc[1] * sc;
+                o[8] = acc[3] * sc;
+            }
+        }
+        if (fuse_quant) {
+            __threadfence();   // every lane's rows before the counter update, the reader's fence after it
+            __syncwarp();
+            int last = 0;
+            if (lane == 0) {
+                const int old = atomicAdd(&A.slot_done[A.e_local + 1 + nt], 1);
+                last = old + 1 == tiles16;
+                if (last) A.slot_done[A.e_local + 1 + nt] = 0;
+            }
+            last = __shfl_sync(0xffffffffu, last, 0);
+            if (last && A.debug != 3) {
+                __threadfence();
+                const bool kq = is_kquant(A.quant_dt_s);
+                const int rows = m - 8 * nt < 8 ? m - 8 * nt : 8;
+                for (int i = 0; i < rows; i++) {
+                    const size_t r = out0 + 8 * nt + i;
+                    warp_quant_row512(A.out + r * 512, kq, A.q8k_out, A.q80_out, r, lane);
+                }
+            }
+        }
+    }
 }
 
 // DT_S: type of the shared expert's gate/up matrices served by this launch (0 = none).  A Q4_K shared
 // expert is one more slot of the tensor-core items; other types follow as items of the streaming kind.
 template <int DT_S>
-__global__ void __launch_bounds__(GEMV_THREADS, 2) k_gate_up_q4k_mma(const GemvArgs A)
+__global__ void __launch_bounds__(DT_S == PMOE_Q8_0 ? SHW_THREADS : GEMV_THREADS, 2) k_gate_up_q4k_mma(const GemvArgs A)
 {
     extern __shared__ __align__(128) uint8_t ring[];
     __shared__ int s_prefix1[2];
@@ -523,17 +622,25 @@ __global__ void __launch_bounds__(GEMV_THREADS, 2) k_gate_up_q4k_mma(const GemvA
     Plan plan;
     Cursor scur{0, 0};
     int n_sh = 0;
+    // a Q8_0 shared expert over many tokens has a warp of its own; over few tokens it follows as streaming items
+    const bool shared_warp = DT_S == PMOE_Q8_0 && A.has_shared && A.sh_count >= SHARED_MMA_MIN;
     if (STREAM_SH && A.has_shared) {
         plan.n_active = 0;
         plan.has_shared = 1;
         plan.cpe_r = plan.cpe_s = A.rows_total / CS::ROWS;
-        plan.shared_mma = DT_S == PMOE_Q8_0 && A.sh_count >= SHARED_MMA_MIN;
-        plan.cost_shared = plan.shared_mma ? shared_mma_cost<2>(A.sh_count) : (A.sh_count + CS::TGK - 1) / CS::TGK;
+        plan.shared_mma = false;
+        plan.cost_shared = (A.sh_count + CS::TGK - 1) / CS::TGK;
         plan.prefix = s_prefix1;
-        const long total = plan.total_cost();
-        scur = plan.find(total * blockIdx.x / gridDim.x);
-        const Cursor last = plan.find(total * (blockIdx.x + 1) / gridDim.x);
-        n_sh = plan.index(last) - plan.index(scur);
+        if (!shared_warp) {
+            const long total = plan.total_cost();
+            scur = plan.find(total * blockIdx.x / gridDim.x);
+            const Cursor last = plan.find(total * (blockIdx.x + 1) / gridDim.x);
+            n_sh = plan.index(last) - plan.index(scur);
+        }
+    }
+    if (DT_S == PMOE_Q8_0 && warp == SHW_WARP) {   // the shared expert's warp
+        if (shared_warp) q80_shared_warp<2>(A, lane);
+        return;
     }
     if (n_mma + n_sh <= 0) return;
 
@@ -579,12 +686,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 2) k_gate_up_q4k_mma(const GemvA
     int it = 0;
     bool ok = run_items_q4k_mma(A, ring, work, first, n_mma, it, warp, lane);
     if constexpr (STREAM_SH) {
-        if (ok && n_sh > 0) {
-            if (DT_S == PMOE_Q8_0 && plan.shared_mma)
-                run_items_shared_mma<2>(A, ring, plan, scur, it, n_mma + n_sh, A.in_s, warp, lane);
-            else
-                run_items<DT_S1, 2>(A, ring, plan, true, scur, 1, it, n_mma + n_sh, A.in_s, warp, lane);
-        }
+        if (ok && n_sh > 0) run_items<DT_S1, 2>(A, ring, plan, true, scur, 1, it, n_mma + n_sh, A.in_s, warp, lane);
     }
 }
 
@@ -598,7 +700,7 @@ template <int DT_S> static cudaError_t launch_q4k_mma_t(const GemvArgs &A, cudaS
         if (e != cudaSuccess) return e;
         configured = true;
     }
-    cudaError_t e = launch_pdl(kern, dim3(2 * sm_count()), dim3(GEMV_THREADS), smem, s, A);
+    cudaError_t e = launch_pdl(kern, dim3(2 * sm_count()), dim3(DT_S == PMOE_Q8_0 ? SHW_THREADS : GEMV_THREADS), smem, s, A);
     count_launch();
     return e;
 }
@@ -1037,7 +1139,7 @@ __device__ inline void dm_run_group(const GemvArgs &A, uint8_t *smem, const MmaW
 // DT_S: type of the shared expert's down matrix served by this launch (0 = none).  A Q6_K shared expert is
 // one more slot of the tensor-core items; other types follow as items of the streaming kind.
 template <int DT_S>
-__global__ void __launch_bounds__(GEMV_THREADS, 2) k_down_q6k_mma(const GemvArgs A)
+__global__ void __launch_bounds__(DT_S == PMOE_Q8_0 ? SHW_THREADS : GEMV_THREADS, 2) k_down_q6k_mma(const GemvArgs A)
 {
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ int s_prefix1[2];
@@ -1082,29 +1184,26 @@ __global__ void __launch_bounds__(GEMV_THREADS, 2) k_down_q6k_mma(const GemvArgs
     Plan plan;
     Cursor scur{0, 0};
     int n_sh = 0;
-    long job_lo = 0, job_hi = -1;
-    if (STREAM_SH && A.has_shared) {
+    // a Q8_0 shared expert over many tokens has a warp of its own; over few tokens it follows as streaming items
+    const bool shared_warp = DT_S == PMOE_Q8_0 && A.has_shared && A.sh_count >= SHARED_MMA_MIN;
+    if (STREAM_SH && A.has_shared && !shared_warp) {
         plan.n_active = 0;
         plan.has_shared = 1;
         plan.cpe_r = plan.cpe_s = A.rows_total / CS::ROWS;
-        plan.shared_mma = DT_S == PMOE_Q8_0 && A.sh_count >= SHARED_MMA_MIN;
-        plan.cost_shared = plan.shared_mma ? shared_mma_cost<1>(A.sh_count) : (A.sh_count + CS::TGK - 1) / CS::TGK;
+        plan.shared_mma = false;
+        plan.cost_shared = (A.sh_count + CS::TGK - 1) / CS::TGK;
         plan.prefix = s_prefix1;
-        if (plan.shared_mma) {
-            // split by jobs (16 rows x 8 tokens), not by items: an item over many tokens is too coarse a unit
-            const long jpc = (long)SharedMma<1>::MT * ((A.sh_count + 7) / 8), total = jpc * plan.cpe_s;
-            job_lo = total * blockIdx.x / gridDim.x;
-            job_hi = total * (blockIdx.x + 1) / gridDim.x;
-            if (job_hi > job_lo) {
-                scur = Cursor{0, (int)(job_lo / jpc)};
-                n_sh = (int)((job_hi - 1) / jpc) - scur.chunk + 1;
-            }
-        } else {
-            const long total = plan.total_cost();
-            scur = plan.find(total * blockIdx.x / gridDim.x);
-            const Cursor last = plan.find(total * (blockIdx.x + 1) / gridDim.x);
-            n_sh = plan.index(last) - plan.index(scur);
+        const long total = plan.total_cost();
+        scur = plan.find(total * blockIdx.x / gridDim.x);
+        const Cursor last = plan.find(total * (blockIdx.x + 1) / gridDim.x);
+        n_sh = plan.index(last) - plan.index(scur);
+    }
+    if (DT_S == PMOE_Q8_0 && warp == SHW_WARP) {   // the shared expert's warp
+        if (shared_warp) {
+            pdl_wait();
+            q80_shared_warp<1>(A, lane);
         }
+        return;
     }
     if (n_mma + n_sh <= 0) return;
 
@@ -1187,10 +1286,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 2) k_down_q6k_mma(const GemvArgs
     if constexpr (STREAM_SH) {
         if (!failed && n_sh > 0) {
             int it = 0;
-            if (DT_S == PMOE_Q8_0 && plan.shared_mma)
-                run_items_shared_mma<1>(A, ring2, plan, scur, it, n_sh, A.in_s, warp, lane, job_lo, job_hi);
-            else
-                run_items<DT_S1, 1>(A, ring2, plan, true, scur, 1, it, n_sh, A.in_s, warp, lane);
+            run_items<DT_S1, 1>(A, ring2, plan, true, scur, 1, it, n_sh, A.in_s, warp, lane);
         }
     }
 }
@@ -1204,7 +1300,7 @@ template <int DT_S> static cudaError_t launch_q6k_mma_t(const GemvArgs &A, cudaS
         if (e != cudaSuccess) return e;
         configured = true;
     }
-    cudaError_t e = launch_pdl(kern, dim3(2 * sm_count()), dim3(GEMV_THREADS), DM_SMEM, s, A);
+    cudaError_t e = launch_pdl(kern, dim3(2 * sm_count()), dim3(DT_S == PMOE_Q8_0 ? SHW_THREADS : GEMV_THREADS), DM_SMEM, s, A);
     count_launch();
     return e;
 }
