@@ -601,6 +601,7 @@ struct GemvArgs {
     DevStatus *status;
     int debug;                 // 1: skip the arithmetic, 2: skip the copies (timing experiments)
     int stage_bytes;           // bytes between the slots of the shared-memory ring
+    int shw_min;               // tensor-core kernels: a Q8_0 shared expert over this many tokens or more gets its own warp
     // gate/up only: the CTA that completes an expert's last item re-quantises the expert's activated rows
     int *slot_done;            // [E_local + 1] items finished per slot (shared expert last); returns to zero
     int quant_dt_r, quant_dt_s; // block types the down matrices will consume (0 = no fused re-quantisation)

@@ -528,14 +528,48 @@ template <int NMAT> __device__ inline void q80_shared_warp(const GemvArgs &A, in
         const float *dx0 = in.d + (row0 + (c0_ok ? tok_c : 0)) * KB;
         const float *dx1 = in.d + (row0 + (c1_ok ? tok_c + 1 : 0)) * KB;
         float acc[4] = {0.f, 0.f, 0.f, 0.f};
-        MmaActs va, vb;
-        mma_load_acts(va, xq, dx0, dx1, 0);
 #pragma unroll 1
-        for (int kb = 0; kb < KB; kb += 8) {   // the loads of the next four blocks fly under the current four
-            mma_load_acts(vb, xq, dx0, dx1, kb + 4);
-            mma_step4(r0, r1, kb, t, va, acc);
-            if (kb + 8 < KB) mma_load_acts(va, xq, dx0, dx1, kb + 8);
-            mma_step4(r0, r1, kb + 4, t, vb, acc);
+        for (int kb = 0; kb < KB; kb += 8) {
+            // every load of eight blocks is in flight before the first product: one round trip to L2 per step
+            uint32_t a[8][4];
+            uint2 bq[8];
+            uint16_t dw[8][2];
+            float4 x0[2], x1[2];
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const uint8_t *p0 = r0 + (kb + i) * Q8_0_BYTES, *p1 = r1 + (kb + i) * Q8_0_BYTES;
+                // the lane's share of K is bytes 8t..8t+7 of the block, for the weights and the activations alike;
+                // kb is a multiple of 8: even blocks start on a word boundary (their quants do not), odd ones 2 bytes off
+                if (i & 1) {
+                    mma_load_row<true>(p0 + 2 + 8 * t, a[i][0], a[i][2]);
+                    mma_load_row<true>(p1 + 2 + 8 * t, a[i][1], a[i][3]);
+                } else {
+                    mma_load_row<false>(p0 + 2 + 8 * t, a[i][0], a[i][2]);
+                    mma_load_row<false>(p1 + 2 + 8 * t, a[i][1], a[i][3]);
+                }
+                dw[i][0] = *reinterpret_cast<const uint16_t *>(p0);
+                dw[i][1] = *reinterpret_cast<const uint16_t *>(p1);
+                bq[i] = *reinterpret_cast<const uint2 *>(xq + (kb + i) * QK8_0);
+            }
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                x0[h] = *reinterpret_cast<const float4 *>(dx0 + kb + 4 * h);
+                x1[h] = *reinterpret_cast<const float4 *>(dx1 + kb + 4 * h);
+            }
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const uint32_t b[2] = {bq[i].x, bq[i].y};
+                int c[4];
+                mma_s8_16x8x32(c, a[i], b);
+                const float dw0 = half_bits_to_float(dw[i][0]), dw1 = half_bits_to_float(dw[i][1]);
+                const float4 &xa = x0[i >> 2], &xb = x1[i >> 2];
+                const float xs0 = (i & 3) == 0 ? xa.x : (i & 3) == 1 ? xa.y : (i & 3) == 2 ? xa.z : xa.w;
+                const float xs1 = (i & 3) == 0 ? xb.x : (i & 3) == 1 ? xb.y : (i & 3) == 2 ? xb.z : xb.w;
+                acc[0] += (dw0 * xs0) * (float)c[0];
+                acc[1] += (dw0 * xs1) * (float)c[1];
+                acc[2] += (dw1 * xs0) * (float)c[2];
+                acc[3] += (dw1 * xs1) * (float)c[3];
+            }
         }
         if (NMAT == 2) {
             const int row = 8 * tile + g;
@@ -622,8 +656,8 @@ __global__ void __launch_bounds__(DT_S == PMOE_Q8_0 ? SHW_THREADS : GEMV_THREADS
     Plan plan;
     Cursor scur{0, 0};
     int n_sh = 0;
-    // a Q8_0 shared expert over many tokens has a warp of its own; over few tokens it follows as streaming items
-    const bool shared_warp = DT_S == PMOE_Q8_0 && A.has_shared && A.sh_count >= SHARED_MMA_MIN;
+    // a Q8_0 shared expert has a warp of its own (PMOE_SHW_MIN: from that many tokens on; below, streaming items follow)
+    const bool shared_warp = DT_S == PMOE_Q8_0 && A.has_shared && A.sh_count >= A.shw_min;
     if (STREAM_SH && A.has_shared) {
         plan.n_active = 0;
         plan.has_shared = 1;
@@ -1184,8 +1218,8 @@ __global__ void __launch_bounds__(DT_S == PMOE_Q8_0 ? SHW_THREADS : GEMV_THREADS
     Plan plan;
     Cursor scur{0, 0};
     int n_sh = 0;
-    // a Q8_0 shared expert over many tokens has a warp of its own; over few tokens it follows as streaming items
-    const bool shared_warp = DT_S == PMOE_Q8_0 && A.has_shared && A.sh_count >= SHARED_MMA_MIN;
+    // a Q8_0 shared expert has a warp of its own (PMOE_SHW_MIN: from that many tokens on; below, streaming items follow)
+    const bool shared_warp = DT_S == PMOE_Q8_0 && A.has_shared && A.sh_count >= A.shw_min;
     if (STREAM_SH && A.has_shared && !shared_warp) {
         plan.n_active = 0;
         plan.has_shared = 1;
@@ -1305,8 +1339,15 @@ template <int DT_S> static cudaError_t launch_q6k_mma_t(const GemvArgs &A, cudaS
     return e;
 }
 
+static int shw_min_tokens()
+{
+    static const int v = getenv("PMOE_SHW_MIN") ? atoi(getenv("PMOE_SHW_MIN")) : 1;
+    return v;
+}
+
 cudaError_t launch_down_q6k_mma(GemvArgs &A, int dt_s, cudaStream_t s)
 {
+    A.shw_min = shw_min_tokens();
     A.stage_bytes = STAGE_BYTES;   // the streaming-kind items of a shared expert of another type
     switch (dt_s) {
     case 0: return launch_q6k_mma_t<0>(A, s);
@@ -1320,6 +1361,7 @@ cudaError_t launch_down_q6k_mma(GemvArgs &A, int dt_s, cudaStream_t s)
 
 cudaError_t launch_gate_up_q4k_mma(GemvArgs &A, int dt_s, cudaStream_t s)
 {
+    A.shw_min = shw_min_tokens();
     A.stage_bytes = MMA_STAGE_BYTES;
     switch (dt_s) {
     case 0: return launch_q4k_mma_t<0>(A, s);
