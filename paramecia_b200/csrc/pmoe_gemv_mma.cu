@@ -20,12 +20,17 @@ namespace pmoe {
 // signed byte digits (bsum = 64 h + l).  The eight warps' partial sums meet in shared memory, in
 // the part of the ring slot the warp itself has finished reading, and are added in warp order.
 //
-// Rows land in shared memory 1168 bytes apart (1152 + 16): with rows 0,2,4,6 / 1,3,5,7 on the
-// eight row positions of a fragment the 8-byte loads of a half-warp fall into 32 different banks.
+// An item arrives as eight bulk copies of four consecutive rows (4608 bytes); the quads of a matrix sit
+// 4640 bytes apart, so that with one row of every quad on the row positions of a half-warp's fragment
+// the 8-byte loads fall into 32 different banks (rows 1152 bytes apart would all meet in the same ones).
 constexpr int Q4K_ROW = 8 * Q4_K_BYTES;                 // 1152: one row of K = 2048
-constexpr int Q4K_MMA_PITCH = Q4K_ROW + 16;
-constexpr int MMA_STAGE_BYTES = 32 * Q4K_MMA_PITCH;     // 37 376
-static_assert(MMA_STAGE_BYTES % 128 == 0 && MMA_STAGE_BYTES >= STAGE_BYTES, "ring slot of the tensor-core GEMV");
+constexpr int Q4K_QUAD = 4 * Q4K_ROW + 32;              // 4640: four consecutive rows (one bulk copy) and 32 bytes of padding
+constexpr int Q4K_TILE = 4 * Q4K_QUAD;                  // 18 560: the 16 rows of one matrix
+constexpr int MMA_STAGE_BYTES = 37376;                  // 2 x 18 560 rounded up to a multiple of 128
+static_assert(MMA_STAGE_BYTES % 128 == 0 && MMA_STAGE_BYTES >= STAGE_BYTES && MMA_STAGE_BYTES >= 2 * Q4K_TILE,
+              "ring slot of the tensor-core GEMV");
+// byte offset of row r (0..15) of a matrix inside its tile
+__device__ inline int q4k_row_off(int r) { return (r >> 2) * Q4K_QUAD + (r & 3) * Q4K_ROW; }
 
 __device__ inline void mma_u8s8_k32(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                     uint32_t b1)
@@ -239,7 +244,9 @@ __device__ inline void gu_item(const GemvArgs &A, uint8_t *stage, const GuGroup<
                                int lane)
 {
     const int g = lane >> 2, t = lane & 3;
-    const int r0 = ((g & 3) << 1) | (g >> 2);   // tile row under fragment row g (fragment row g + 8: tile row r0 + 8)
+    // tile rows under fragment rows g and g + 8: a half-warp (g = 0..3 or 4..7) meets one row of every quad, whose
+    // starts are 32 bytes apart modulo 128, so its 8-byte loads fall into 32 different banks
+    const int ra = 4 * (g & 3) + (g >> 2), rb = ra + 2;
     constexpr int NV = TP == 2 ? 1 : TP == 4 ? 2 : 4;
     float acc[2][NV];
 #pragma unroll
@@ -247,8 +254,8 @@ __device__ inline void gu_item(const GemvArgs &A, uint8_t *stage, const GuGroup<
 #pragma unroll
         for (int i = 0; i < NV; i++) acc[mt][i] = 0.f;
         if (!compute) continue;
-        const uint8_t *p0 = stage + (mt * 16 + r0) * Q4K_MMA_PITCH + Q4_K_BYTES * warp;
-        const uint8_t *p1 = p0 + 8 * Q4K_MMA_PITCH;
+        const uint8_t *p0 = stage + mt * Q4K_TILE + q4k_row_off(ra) + Q4_K_BYTES * warp;
+        const uint8_t *p1 = p0 + 2 * Q4K_ROW;
         const uint4 h0 = *reinterpret_cast<const uint4 *>(p0);
         const uint4 h1 = *reinterpret_cast<const uint4 *>(p1);
         // mins of both rows as the A operand of the mins products: lane t = 0 carries m_0..3, t = 1 m_4..7
@@ -361,21 +368,21 @@ __device__ inline void gu_item(const GemvArgs &A, uint8_t *stage, const GuGroup<
             }
         }
     }
-    // partial sums of this warp's block column into its own bytes of rows 0..7 of the slot: value idx of
-    // matrix mt = 16 TP mt + TP (row in the item) + token, at row idx >> 5, word idx & 31 of the warp's 144 bytes
+    // partial sums of this warp's block column into its own bytes of the first eight gate rows of the slot: value
+    // idx of matrix mt = 16 TP mt + TP (row in the item) + token, at row idx >> 5, word idx & 31 of the warp's 144 bytes
     __syncwarp();
     {
         uint8_t *mine = stage + Q4_K_BYTES * warp;
-        auto at = [&](int idx) -> uint8_t * { return mine + (idx >> 5) * Q4K_MMA_PITCH + (idx & 31) * 4; };
+        auto at = [&](int idx) -> uint8_t * { return mine + q4k_row_off(idx >> 5) + (idx & 31) * 4; };
 #pragma unroll
         for (int mt = 0; mt < 2; mt++) {
             if (TP == 2) {
-                *reinterpret_cast<float *>(at(mt * 32 + (r0 + 8 * (t >> 1)) * 2 + (t & 1))) = acc[mt][0];
+                *reinterpret_cast<float *>(at(mt * 32 + (ra + 2 * (t >> 1)) * 2 + (t & 1))) = acc[mt][0];
             } else if (TP == 4) {
-                *reinterpret_cast<float2 *>(at(mt * 64 + (r0 + 8 * (t >> 1)) * 4 + 2 * (t & 1))) = make_float2(acc[mt][0], acc[mt][1]);
+                *reinterpret_cast<float2 *>(at(mt * 64 + (ra + 2 * (t >> 1)) * 4 + 2 * (t & 1))) = make_float2(acc[mt][0], acc[mt][1]);
             } else {
-                *reinterpret_cast<float2 *>(at(mt * 128 + r0 * 8 + 2 * t)) = make_float2(acc[mt][0], acc[mt][1]);
-                *reinterpret_cast<float2 *>(at(mt * 128 + (r0 + 8) * 8 + 2 * t)) = make_float2(acc[mt][2], acc[mt][3]);
+                *reinterpret_cast<float2 *>(at(mt * 128 + ra * 8 + 2 * t)) = make_float2(acc[mt][0], acc[mt][1]);
+                *reinterpret_cast<float2 *>(at(mt * 128 + rb * 8 + 2 * t)) = make_float2(acc[mt][2], acc[mt][3]);
             }
         }
     }
@@ -384,7 +391,7 @@ __device__ inline void gu_item(const GemvArgs &A, uint8_t *stage, const GuGroup<
         constexpr int TPV = 8 / TP;   // threads per value, each adding TP of the eight partial sums
         const int mt = lane >> 4, part = lane % TPV;
         const int idx = mt * 16 * TP + warp * (16 / TPV) + (lane & 15) / TPV;
-        const uint8_t *src = stage + (idx >> 5) * Q4K_MMA_PITCH + (idx & 31) * 4 + Q4_K_BYTES * TP * part;
+        const uint8_t *src = stage + q4k_row_off(idx >> 5) + (idx & 31) * 4 + Q4_K_BYTES * TP * part;
         // the eight partial sums are added as one balanced tree whatever TP is, so that a token's result does not
         // depend on how many tokens shared its group (the order of an expert's token list is not fixed between runs)
         float pv[TP];
@@ -678,7 +685,7 @@ __global__ void __launch_bounds__(DT_S == PMOE_Q8_0 ? SHW_THREADS : GEMV_THREADS
     }
     if (n_mma + n_sh <= 0) return;
 
-    if (warp == GEMV_WARPS) {   // the producer warp: every lane copies one row of an item
+    if (warp == GEMV_WARPS) {   // the producer warp: eight lanes copy four rows of an item each
         if (A.debug == 2) return;
         MmaCursor pc = first;
         int issued = 0;
@@ -696,14 +703,16 @@ __global__ void __launch_bounds__(DT_S == PMOE_Q8_0 ? SHW_THREADS : GEMV_THREADS
                     break;
                 }
             }
+            // lanes 0..7 copy four consecutive rows each: lane = 4 * matrix + quad
             const uint8_t *base;
-            if (pc.slot < work.n_active) base = (lane < 16 ? A.w0 : A.w1) + (size_t)A.g.active[pc.slot] * A.expert_bytes;
-            else base = lane < 16 ? A.sw0 : A.sw1;
+            if (pc.slot < work.n_active) base = (lane < 4 ? A.w0 : A.w1) + (size_t)A.g.active[pc.slot] * A.expert_bytes;
+            else base = lane < 4 ? A.sw0 : A.sw1;
             uint64_t *full = ring_full(ring, s);
             if (lane == 0) mbar_expect_tx(full, 32 * Q4K_ROW);
             __syncwarp();
-            bulk_g2s(ring_stage(ring, s, A.stage_bytes) + lane * Q4K_MMA_PITCH,
-                     base + (size_t)(pc.chunk * 16 + (lane & 15)) * Q4K_ROW, Q4K_ROW, full);
+            if (lane < 8)
+                bulk_g2s(ring_stage(ring, s, A.stage_bytes) + (lane >> 2) * Q4K_TILE + (lane & 3) * Q4K_QUAD,
+                         base + (size_t)(pc.chunk * 16 + 4 * (lane & 3)) * Q4K_ROW, 4 * Q4K_ROW, full);
             work.advance(pc);
         }
         if (lane == 0) {
