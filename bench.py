@@ -684,7 +684,7 @@ def pmoe_arm(args):
     roofline = None
     if phase_ms.get("gate_up"):
         ach = gu_bytes / (phase_ms["gate_up"] * 1e-3) / 1e9
-        roofline = dict(bound="hbm", kernel="k_expert_gemv<gate+up>", achieved=ach, peak=ctx.hbm_peak, unit="GB/s",
+        roofline = dict(bound="hbm", kernel="k_gate_up_q4k_mma (gate + up + SiLU, Q4_K experts)", achieved=ach, peak=ctx.hbm_peak, unit="GB/s",
                         frac=ach / ctx.hbm_peak, peak_kind=ctx.hbm_kind,
                         # DRAM bytes of one captured launch of this kernel on this workload (ncu dram__bytes_read.sum +
                         # dram__bytes_write.sum) divided by that launch's algorithmic bytes; regenerate the constant
@@ -698,7 +698,7 @@ def pmoe_arm(args):
                         layer_bytes_per_step=step_bytes, distinct_experts=D)
         if phase_ms.get("down"):
             a2 = dn_bytes / (phase_ms["down"] * 1e-3) / 1e9
-            roofline["down"] = dict(kernel="k_expert_gemv<down>", achieved=a2, frac=a2 / ctx.hbm_peak,
+            roofline["down"] = dict(kernel="k_down_q6k_mma (down x routing weight, Q6_K experts)", achieved=a2, frac=a2 / ctx.hbm_peak,
                                     algorithmic_bytes_per_launch=dn_bytes, us_per_launch=phase_ms["down"] * 1e3)
 
     # ---- batch sweep 1/4/16: cold (layers and inputs rotate) and L2-hot (one layer, one input)
@@ -798,7 +798,7 @@ def pmoe_arm(args):
         dist.destroy_process_group()
 
 
-NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 439.356672 / 429.555712   # gate/up launch at batch 64, 362 experts hit
+NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = (435.576064 + 6.948864) / 429.555712   # gate/up launch at batch 64, 362 experts hit
 
 
 def main():

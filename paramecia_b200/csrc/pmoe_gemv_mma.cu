@@ -75,6 +75,40 @@ struct MmaWork {
     }
 };
 
+// The CTA's share of the items: its first item and its item count, found by all threads together.  Every thread
+// fetches the prefix entries of its candidate slots before anything depends on them, so the search costs two
+// round trips to memory (the number of active slots, then the total) instead of a binary search's chain of them.
+__device__ inline void mma_plan(MmaWork &work, const GemvArgs &A, MmaCursor *s_first, int *s_items)
+{
+    constexpr int CAND = 4;   // candidate slots per thread: covers E_local <= 4 * 288
+    int lo[CAND], hi[CAND];
+#pragma unroll
+    for (int i = 0; i < CAND; i++) {
+        const int sl = threadIdx.x + i * blockDim.x;
+        lo[i] = hi[i] = 0;
+        if (sl < A.e_local) { lo[i] = work.prefix[sl]; hi[i] = work.prefix[sl + 1]; }
+    }
+    work.n_active = A.routed ? *A.g.n_active : 0;
+    const long total = work.total();
+    const long q0 = total * blockIdx.x / gridDim.x, q1 = total * (blockIdx.x + 1) / gridDim.x;
+    if (threadIdx.x == 0) *s_items = (int)(q1 - q0);
+    if (q1 <= q0) {
+        if (threadIdx.x == 0) *s_first = MmaCursor{0, 0, 0, 0};
+        return;
+    }
+    const int G = (int)(q0 / work.cpe), chunk = (int)(q0 % work.cpe);
+    const int rg = work.routed_groups();
+    if (G >= rg) {
+        if (threadIdx.x == 0) *s_first = MmaCursor{work.n_active, G - rg, chunk, work.groups_sh};
+        return;
+    }
+#pragma unroll
+    for (int i = 0; i < CAND; i++) {
+        const int sl = threadIdx.x + i * blockDim.x;
+        if (sl < work.n_active && lo[i] <= G && G < hi[i]) *s_first = MmaCursor{sl, G - lo[i], chunk, hi[i] - lo[i]};
+    }
+}
+
 struct Q4Hdr {
     float d16, dmin;              // d / 16 (high nibbles stay in place) and dmin
     uint32_t sca, scb, mna, mnb;  // 6-bit scales 0..3 / 4..7 and mins 0..3 / 4..7 as bytes
@@ -636,7 +670,7 @@ __global__ void __launch_bounds__(DT_S == PMOE_Q8_0 ? SHW_THREADS : GEMV_THREADS
     pdl_launch_dependents();
 
     MmaWork work;
-    work.n_active = A.routed ? *A.g.n_active : 0;
+    work.n_active = 0;
     work.cpe = A.rows_total / 16;
     work.groups_sh = (DT_S == PMOE_Q4_K && A.has_shared) ? (A.sh_count + GEMV_TG_MMA - 1) / GEMV_TG_MMA : 0;
     work.prefix = A.g.cost_prefix_mma;
@@ -646,12 +680,9 @@ __global__ void __launch_bounds__(DT_S == PMOE_Q8_0 ? SHW_THREADS : GEMV_THREADS
             mbar_init(ring_empty(ring, s), GEMV_WARPS);
         }
         fence_mbar_init();
-        const long total = work.total();
-        const long q0 = total * blockIdx.x / gridDim.x, q1 = total * (blockIdx.x + 1) / gridDim.x;
-        s_items = (int)(q1 - q0);
-        s_first = q1 > q0 ? work.at(q0) : MmaCursor{0, 0, 0, 0};
         s_prefix1[0] = s_prefix1[1] = 0;
     }
+    mma_plan(work, A, &s_first, &s_items);
     __syncthreads();
     const int n_mma = s_items;
     const MmaCursor first = s_first;
@@ -1196,7 +1227,7 @@ __global__ void __launch_bounds__(DT_S == PMOE_Q8_0 ? SHW_THREADS : GEMV_THREADS
 
     uint8_t *ring2 = smem + DM_RING2;
     MmaWork work;
-    work.n_active = A.routed ? *A.g.n_active : 0;
+    work.n_active = 0;
     work.cpe = A.rows_total / DM_ROWS;
     work.groups_sh = (DT_S == PMOE_Q6_K && A.has_shared) ? (A.sh_count + GEMV_TG_MMA - 1) / GEMV_TG_MMA : 0;
     work.prefix = A.g.cost_prefix_mma;
@@ -1210,12 +1241,9 @@ __global__ void __launch_bounds__(DT_S == PMOE_Q8_0 ? SHW_THREADS : GEMV_THREADS
             mbar_init(ring_empty(ring2, s), GEMV_WARPS);
         }
         fence_mbar_init();
-        const long total = work.total();
-        const long q0 = total * blockIdx.x / gridDim.x, q1 = total * (blockIdx.x + 1) / gridDim.x;
-        s_items = (int)(q1 - q0);
-        s_first = q1 > q0 ? work.at(q0) : MmaCursor{0, 0, 0, 0};
         s_prefix1[0] = s_prefix1[1] = 0;
     }
+    mma_plan(work, A, &s_first, &s_items);
     __syncthreads();
     const int n_mma = s_items;
     const MmaCursor first = s_first;
