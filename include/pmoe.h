@@ -26,7 +26,7 @@
 extern "C" {
 #endif
 
-#define PMOE_VERSION 3
+#define PMOE_VERSION 4
 
 /* GGML tensor-type ids, the numbering of candle's GgmlDType / GGUF files. */
 typedef enum {
@@ -215,6 +215,41 @@ int pmoe_layer_set_shared_scales(pmoe_layer *layer, const float *gate_scales, co
  * its tree: this restates "every value of the block times m".) */
 int pmoe_modify_block_scales(int device, int dtype, const void *blocks, size_t n_blocks, const float *mults,
                              void *out, void *stream);
+
+/*
+ * Expert-parallel form of pmoe_forward: MoeBlock::forward_with_stats (qwen3_next.rs:1903-1940) for a block whose
+ * routed experts are spread over the ranks of a communicator, one process per GPU.  The reference has no
+ * counterpart: it runs one process on one device (its expert loop is a rayon loop, tokio_experts.rs:116-130).
+ *
+ * Every rank creates its layer with ep_rank / ep_size, E_local = E / ep_size experts (ep_placement says which) and
+ * max_tokens >= ep_size * n, and calls pmoe_ep_forward with its own n tokens (the same n on every rank).  A
+ * token's quantised row travels once to every rank that holds one of its top-k experts (grouped ncclSend /
+ * ncclRecv, an all-to-all-v), that rank returns one pre-reduced f32 row, and the home rank adds the returned rows
+ * in rank order; the shared expert runs on the home rank.  x, out, logits_out, idx_out, w_out as in pmoe_forward,
+ * for the rank's own tokens.
+ *
+ * mode 1 (padded counts): every pair of ranks exchanges n records; no host synchronisation.  mode 2 (exact
+ * counts): the ranks all-gather their counts first and the host reads them (one stream synchronisation per call);
+ * only the rows that are needed travel.  mode 0: padded below 2048 rows in flight, exact from there on.
+ *
+ * The communicator: rank 0 calls pmoe_ep_unique_id and hands the bytes to the others over any channel the host
+ * has, then every rank calls pmoe_ep_comm_create (ncclCommInitRank; collective).  A host that already owns an
+ * ncclComm_t for exactly these ranks passes it to pmoe_ep_comm_adopt instead.  NCCL (libnccl.so.2) is loaded on
+ * first use.  At most 64 ranks.
+ */
+typedef struct pmoe_ep_comm pmoe_ep_comm; /* opaque */
+#define PMOE_EP_ID_BYTES 128
+int pmoe_ep_unique_id(void *id_out, size_t id_bytes);
+int pmoe_ep_comm_create(const void *id, size_t id_bytes, int rank, int size, int device, pmoe_ep_comm **out);
+int pmoe_ep_comm_adopt(void *nccl_comm, int rank, int size, int device, pmoe_ep_comm **out);
+int pmoe_ep_comm_destroy(pmoe_ep_comm *comm);
+int pmoe_ep_forward(pmoe_layer *layer, pmoe_ep_comm *comm, const void *x, int x_dtype, int n, void *out,
+                    int out_dtype, float *logits_out, uint32_t *idx_out, float *w_out, int mode, void *stream);
+/* Device time the two exchanges of the last pmoe_ep_forward took on its stream (dispatch: plan, pack, counts,
+ * exchange; combine: return exchange and the sum), in milliseconds; either pointer may be NULL.  enable 1 / 0
+ * switches the event records on / off for the following calls, -1 leaves the setting.  Valid after the layer's
+ * first pmoe_ep_forward. */
+int pmoe_ep_profile(pmoe_layer *layer, int enable, float *dispatch_ms, float *combine_ms);
 
 /* SharedExpert::forward (qwen3_next.rs:1776-1823), sigmoid gate included. */
 int pmoe_shared_forward(pmoe_layer *layer, const void *x, int x_dtype, int n, void *out,

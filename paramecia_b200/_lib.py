@@ -61,6 +61,12 @@ SYMBOLS = [
     ("pmoe_layer_set_block_multipliers", _I, [_V, _V, _V, _V, _V]),
     ("pmoe_layer_set_shared_scales", _I, [_V, _V, _V, _V, _V]),
     ("pmoe_modify_block_scales", _I, [_I, _I, _V, _Z, _V, _V, _V]),
+    ("pmoe_ep_unique_id", _I, [_V, _Z]),
+    ("pmoe_ep_comm_create", _I, [_V, _Z, _I, _I, _I, C.POINTER(_V)]),
+    ("pmoe_ep_comm_adopt", _I, [_V, _I, _I, _I, C.POINTER(_V)]),
+    ("pmoe_ep_comm_destroy", _I, [_V]),
+    ("pmoe_ep_forward", _I, [_V, _V, _V, _I, _I, _V, _I, _V, _V, _V, _I, _V]),
+    ("pmoe_ep_profile", _I, [_V, _I, _V, _V]),
     ("pmoe_shared_forward", _I, [_V, _V, _I, _I, _V, _I, _V]),
     ("pmoe_qmatmul", _I, [_I, _I, _V, _Z, _Z, _V, _Z, _V, _V]),
     ("pmoe_qmatmul_noalloc", _I, [_I, _I, _V, _Z, _Z, _V, _Z, _V, _V]),

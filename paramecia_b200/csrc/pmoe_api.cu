@@ -8,7 +8,7 @@
 #include <string>
 #include <vector>
 
-#include "pmoe_common.cuh"
+#include "pmoe_internal.h"
 
 namespace pmoe {
 
@@ -22,7 +22,7 @@ bool pdl_enabled()
 
 static thread_local std::string g_last_error;
 
-static int fail(int code, const char *fmt, ...)
+int fail(int code, const char *fmt, ...)
 {
     char buf[512];
     va_list ap;
@@ -33,31 +33,10 @@ static int fail(int code, const char *fmt, ...)
     return code;
 }
 
-static int fail_cuda(cudaError_t e, const char *what)
+int fail_cuda(cudaError_t e, const char *what)
 {
     return fail(PMOE_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
 }
-
-#define CU(call)                                                  \
-    do {                                                          \
-        cudaError_t _e = (call);                                  \
-        if (_e != cudaSuccess) return fail_cuda(_e, #call);       \
-    } while (0)
-
-// Makes `device` current for the calling thread and restores the previous one on exit.
-struct DeviceGuard {
-    int prev = -1;
-    bool ok = false;
-    explicit DeviceGuard(int device)
-    {
-        if (cudaGetDevice(&prev) != cudaSuccess) prev = -1;
-        ok = cudaSetDevice(device) == cudaSuccess;
-    }
-    ~DeviceGuard()
-    {
-        if (prev >= 0) cudaSetDevice(prev);
-    }
-};
 
 static bool dtype_known(int dt)
 {
@@ -67,37 +46,6 @@ static bool dtype_known(int dt)
 }  // namespace pmoe
 
 using namespace pmoe;
-
-struct pmoe_layer {
-    pmoe_layer_desc desc;
-    LayerDev dev;
-    Workspace ws;
-    int device;
-    std::vector<void *> owned;  // device allocations freed at destroy
-    // device staging for the host-buffer entry point
-    void *st_x = nullptr, *st_out = nullptr;
-    float *st_logits = nullptr;
-    uint32_t *st_idx = nullptr;
-    float *st_w = nullptr;
-    // per-phase CUDA events of the last traced call (pmoe_layer_trace)
-    // pmoe_forward_host replays the kernel chain of its last shape as a CUDA graph (the chain works on
-    // the handle's own staging buffers, so its arguments do not change from call to call)
-    cudaStream_t cap_stream = nullptr;
-    cudaGraphExec_t hg_exec = nullptr;
-    int hg_n = -1, hg_x_dtype = 0, hg_out_dtype = 0, hg_flags = 0, hg_launches = 0;
-    int hg_seen_n = -1, hg_seen_x = 0, hg_seen_out = 0, hg_seen_flags = 0;
-    void *hg_out = nullptr, *hg_seen_out_ptr = nullptr;   // where the chain writes the block output
-    bool hg_off = false;
-    // rows the shared expert serves in the next run_experts call; count < 0 = every row
-    int req_sh_begin = 0, req_sh_count = -1;
-    // block-scale multipliers (training mode): the tensors as created, and the scaled copies the kernels read
-    // while multipliers are installed (index: 0 gate_exps, 1 up_exps, 2 down_exps, 3 sh_gate, 4 sh_up, 5 sh_down)
-    const uint8_t *orig[6] = {};
-    void *scaled[6] = {};
-    bool trace = false;
-    cudaEvent_t ev0[PMOE_TRACE_PHASES] = {}, ev1[PMOE_TRACE_PHASES] = {};
-    bool ev_used[PMOE_TRACE_PHASES] = {};
-};
 
 namespace {
 
@@ -183,7 +131,9 @@ int place_tensor(pmoe_layer *L, const void *src, size_t bytes, int location, con
     return PMOE_OK;
 }
 
-int check_call(pmoe_layer *L, const void *x, int x_dtype, int n, const void *out, int out_dtype)
+}  // namespace
+
+int pmoe::check_call(pmoe_layer *L, const void *x, int x_dtype, int n, const void *out, int out_dtype)
 {
     if (!L) return fail(PMOE_ERR_INVALID_ARG, "layer is NULL");
     if (L->desc.training_mode)
@@ -198,6 +148,8 @@ int check_call(pmoe_layer *L, const void *x, int x_dtype, int n, const void *out
         return fail(PMOE_ERR_UNSUPPORTED_DTYPE, "outputs must be F32 or BF16 (got %d)", out_dtype);
     return PMOE_OK;
 }
+
+namespace {
 
 struct Needs {
     bool q8k, q80;
@@ -234,19 +186,21 @@ Needs input_needs(const LayerDev &d, bool routed, bool shared)
     return nd;
 }
 
+}  // namespace
+
 // experts (+ shared) given routing already in device memory
-int run_experts(pmoe_layer *L, const void *x, int x_dtype, const uint32_t *idx, const float *w, int n, int top_k,
-                bool routed, bool shared, bool prep_done, void *out, int out_dtype, cudaStream_t s)
+int pmoe::run_experts(pmoe_layer *L, Workspace &ws, const void *x, int x_dtype, const uint32_t *idx, const float *w, int n,
+                      int top_k, bool routed, bool shared, bool prep_done, void *out, int out_dtype, cudaStream_t s)
 {
     const LayerDev &d = L->dev;
-    L->ws.sh_begin = L->req_sh_count < 0 ? 0 : L->req_sh_begin;
-    L->ws.sh_count = L->req_sh_count < 0 ? n : L->req_sh_count;
+    ws.sh_begin = L->req_sh_count < 0 ? 0 : L->req_sh_begin;
+    ws.sh_count = L->req_sh_count < 0 ? n : L->req_sh_count;
     L->req_sh_count = -1;  // a request holds for one call
     if (!prep_done) {
         Needs nd = input_needs(d, routed, shared);
-        PHASE(L, 0, s, launch_prep(d, L->ws, x, x_dtype, n, nd.q8k, nd.q80, shared, s));
+        PHASE(L, 0, s, launch_prep(d, ws, x, x_dtype, n, nd.q8k, nd.q80, shared, s));
     }
-    if (routed) PHASE(L, 3, s, launch_group(d, L->ws, idx, n, top_k, s));
+    if (routed) PHASE(L, 3, s, launch_group(d, ws, idx, n, top_k, s));
     // prefill: many tokens per expert -> grouped tensor-core GEMM; decode: streaming GEMV.  The
     // expected number of tokens per routed expert is n * top_k / E whatever slice this layer holds.
     const char *force = getenv("PMOE_PREFILL");
@@ -256,35 +210,33 @@ int run_experts(pmoe_layer *L, const void *x, int x_dtype, const uint32_t *idx, 
     // back: they go through the tensor-core kernels and the shared expert through the streaming ones.
     const bool split = want_prefill && !prefill && routed && shared && prefill_supported(d, true, false);
     if (split) {
-        PHASE(L, 4, s, launch_gate_up_prefill(d, L->ws, n, top_k, true, false, s));
+        PHASE(L, 4, s, launch_gate_up_prefill(d, ws, n, top_k, true, false, s));
         if (prefill_down_supported(d, true, false)) {
-            CU(launch_down_prefill(d, L->ws, w, n, top_k, true, false, s));
+            CU(launch_down_prefill(d, ws, w, n, top_k, true, false, s));
         } else {
-            CU(launch_act_quant(d, L->ws, idx, n, top_k, true, false, s));
-            CU(launch_down(d, L->ws, w, n, top_k, true, false, s));
+            CU(launch_act_quant(d, ws, idx, n, top_k, true, false, s));
+            CU(launch_down(d, ws, w, n, top_k, true, false, s));
         }
-        CU(launch_gate_up(d, L->ws, n, top_k, false, true, s));
-        PHASE(L, 6, s, launch_down(d, L->ws, w, n, top_k, false, true, s));
-        PHASE(L, 7, s, launch_combine(d, L->ws, idx, n, top_k, routed, shared, out, out_dtype, s));
+        CU(launch_gate_up(d, ws, n, top_k, false, true, s));
+        PHASE(L, 6, s, launch_down(d, ws, w, n, top_k, false, true, s));
+        PHASE(L, 7, s, launch_combine(d, ws, idx, n, top_k, routed, shared, out, out_dtype, s));
         return PMOE_OK;
     }
     if (prefill)
-        PHASE(L, 4, s, launch_gate_up_prefill(d, L->ws, n, top_k, routed, shared, s));
+        PHASE(L, 4, s, launch_gate_up_prefill(d, ws, n, top_k, routed, shared, s));
     else
-        PHASE(L, 4, s, launch_gate_up(d, L->ws, n, top_k, routed, shared, s));
+        PHASE(L, 4, s, launch_gate_up(d, ws, n, top_k, routed, shared, s));
     if (prefill && prefill_down_supported(d, routed, shared)) {
-        PHASE(L, 6, s, launch_down_prefill(d, L->ws, w, n, top_k, routed, shared, s));
+        PHASE(L, 6, s, launch_down_prefill(d, ws, w, n, top_k, routed, shared, s));
     } else {
         // the decode gate/up kernel has already re-quantised every expert's activated rows (last-CTA
         // ticket); after the tensor-core gate/up kernel a separate pass does it
-        if (prefill) PHASE(L, 5, s, launch_act_quant(d, L->ws, idx, n, top_k, routed, shared, s));
-        PHASE(L, 6, s, launch_down(d, L->ws, w, n, top_k, routed, shared, s));
+        if (prefill) PHASE(L, 5, s, launch_act_quant(d, ws, idx, n, top_k, routed, shared, s));
+        PHASE(L, 6, s, launch_down(d, ws, w, n, top_k, routed, shared, s));
     }
-    PHASE(L, 7, s, launch_combine(d, L->ws, idx, n, top_k, routed, shared, out, out_dtype, s));
+    PHASE(L, 7, s, launch_combine(d, ws, idx, n, top_k, routed, shared, out, out_dtype, s));
     return PMOE_OK;
 }
-
-}  // namespace
 
 extern "C" {
 
@@ -449,6 +401,7 @@ int pmoe_layer_destroy(pmoe_layer *L)
     for (void *p : L->owned) cudaFree(p);
     for (void *p : L->scaled)
         if (p) cudaFree(p);
+    if (L->ep) ep_state_destroy(L->ep);
     if (L->hg_exec) cudaGraphExecDestroy(L->hg_exec);
     if (L->cap_stream) cudaStreamDestroy(L->cap_stream);
     for (int i = 0; i < PMOE_TRACE_PHASES; i++) {
@@ -526,7 +479,7 @@ int pmoe_forward(pmoe_layer *L, const void *x, int x_dtype, int n, void *out, in
     // one launch: router rows plus, in extra CTAs, the per-token preparation
     PHASE(L, 1, s, launch_router(d, L->ws, x, x_dtype, n, logits, s, true, nd.q8k, nd.q80, d.has_shared));
     PHASE(L, 2, s, launch_topk(d, L->ws, logits, n, idx, w, s));
-    return run_experts(L, x, x_dtype, idx, w, n, d.k, true, d.has_shared, true, out, out_dtype, s);
+    return run_experts(L, L->ws, x, x_dtype, idx, w, n, d.k, true, d.has_shared, true, out, out_dtype, s);
 }
 
 int pmoe_router_stats(pmoe_layer *L, const float *logits, const uint32_t *idx, int n, int top_k, float *counts_out,
@@ -555,7 +508,7 @@ int pmoe_experts_forward(pmoe_layer *L, const void *x, int x_dtype, const uint32
     if (top_k <= 0 || top_k > L->desc.k)
         return fail(PMOE_ERR_INVALID_ARG, "top_k = %d must be in [1, %d]", top_k, L->desc.k);
     DeviceGuard guard(L->device);
-    return run_experts(L, x, x_dtype, idx, w, n, top_k, true, false, false, out, out_dtype, (cudaStream_t)stream);
+    return run_experts(L, L->ws, x, x_dtype, idx, w, n, top_k, true, false, false, out, out_dtype, (cudaStream_t)stream);
 }
 
 int pmoe_experts_forward_ep(pmoe_layer *L, const void *x, int x_dtype, const uint32_t *idx, const float *w, int n,
@@ -574,7 +527,7 @@ int pmoe_experts_forward_ep(pmoe_layer *L, const void *x, int x_dtype, const uin
     DeviceGuard guard(L->device);
     L->req_sh_begin = shared_begin;
     L->req_sh_count = shared ? shared_count : -1;
-    return run_experts(L, x, x_dtype, idx, w, n, top_k, true, shared, false, out, out_dtype, (cudaStream_t)stream);
+    return run_experts(L, L->ws, x, x_dtype, idx, w, n, top_k, true, shared, false, out, out_dtype, (cudaStream_t)stream);
 }
 
 int pmoe_shared_forward(pmoe_layer *L, const void *x, int x_dtype, int n, void *out, int out_dtype, void *stream)
@@ -584,7 +537,7 @@ int pmoe_shared_forward(pmoe_layer *L, const void *x, int x_dtype, int n, void *
     if (n == 0) return PMOE_OK;
     if (!L->dev.has_shared) return fail(PMOE_ERR_INVALID_ARG, "the layer has no shared expert");
     DeviceGuard guard(L->device);
-    return run_experts(L, x, x_dtype, nullptr, nullptr, n, L->desc.k, false, true, false, out, out_dtype,
+    return run_experts(L, L->ws, x, x_dtype, nullptr, nullptr, n, L->desc.k, false, true, false, out, out_dtype,
                        (cudaStream_t)stream);
 }
 

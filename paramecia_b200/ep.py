@@ -27,6 +27,16 @@ padding costs little.  Two transports carry the same rows:
                   sum (in the switch when NVLS is active).  With a fixed capacity of n rows per pair
                   both transports move the same bytes; this one needs no send-side packing.
 
+* ``native``      (default on GPUs) the whole forward behind the C ABI, ``pmoe_ep_forward``: the dispatch is an
+                  all-to-all-v of QUANTISED rows over grouped ncclSend / ncclRecv -- a row travels only to the ranks
+                  that hold one of its experts (exact counts, from 2048 rows in flight) or to every rank with the
+                  foreign ids masked (padded counts, no host synchronisation) -- and each rank returns one
+                  pre-reduced f32 row per record; ``native_exact`` / ``native_padded`` force one of the two.  The
+                  library opens its own NCCL communicator from an id this module broadcasts over ``torch.distributed``.
+
+``plan_dispatch`` / ``A2avReference`` restate the native path's index arithmetic (which token goes where, at which
+position, and how the returned rows are added) in torch, so that it can be checked on CPU ranks.
+
 No kernel here reads another GPU's memory: NCCL delivers into local HBM first.
 """
 from __future__ import annotations
@@ -69,13 +79,55 @@ def mask_for_destinations(idx: torch.Tensor, n_ranks: int, experts_per_rank: int
     return torch.where(owner.unsqueeze(0) == dest, idx.unsqueeze(0), torch.full_like(idx, INVALID_EXPERT).unsqueeze(0))
 
 
+_NATIVE_MODES = {"native": 0, "native_padded": 1, "native_exact": 2}
+_native_comms = {}
+
+
+def native_comm(group, device: torch.device):
+    """The library's own NCCL communicator over the ranks of `group` (one per group and device, created on first use:
+    rank 0 makes the id, torch.distributed carries it to the others, every rank joins)."""
+    import ctypes as C
+    from ._lib import check, lib
+    key = (id(group), device.index)
+    if key in _native_comms:
+        return _native_comms[key]
+    rank, size = dist.get_rank(group), dist.get_world_size(group)
+    buf = (C.c_ubyte * 128)()
+    if rank == 0:
+        check(lib().pmoe_ep_unique_id(buf, 128))
+    t = torch.tensor(list(buf), dtype=torch.uint8, device=device if dist.get_backend(group) == "nccl" else "cpu")
+    dist.broadcast(t, src=dist.get_global_rank(group, 0) if group is not None else 0, group=group)
+    raw = bytes(t.cpu().tolist())
+    comm = C.c_void_p()
+    with torch.cuda.device(device):
+        check(lib().pmoe_ep_comm_create(raw, 128, rank, size, device.index, C.byref(comm)))
+    _native_comms[key] = comm
+    return comm
+
+
+def plan_dispatch(idx: torch.Tensor, n_ranks: int, experts_per_rank: int, self_rank: int, round_robin: bool = False,
+                  self_takes_all: bool = True):
+    """The dispatch plan of the native path for one rank's routing table idx [n, k]: ``pos`` [n, N] = position of token
+    t among the records for rank r (token order), -1 when t does not travel there; ``cnt`` [N] records per rank.  The
+    home rank takes all its tokens (the shared expert runs there)."""
+    owner = expert_owner(idx.long(), experts_per_rank, n_ranks, round_robin)             # [n, k]
+    valid = (idx.long() >= 0) & (idx.long() < n_ranks * experts_per_rank)
+    dest = torch.arange(n_ranks, device=idx.device).view(1, -1, 1)                         # [1, N, 1]
+    flag = ((owner.unsqueeze(1) == dest) & valid.unsqueeze(1)).any(-1)                     # [n, N]
+    if self_takes_all:
+        flag[:, self_rank] = True
+    pos = torch.cumsum(flag.long(), 0) - 1
+    pos = torch.where(flag, pos, torch.full_like(pos, -1))
+    return pos, flag.sum(0)
+
+
 class ExpertParallelMoe:
     """One MoE block spread over the ranks of `group`.  `block` is this rank's MoeBlock, built with
     its expert slice (expert_base = rank * E/N, E_local = E/N) and max_tokens >= N * n."""
 
     def __init__(self, block, group=None, mode: str = "all_gather", ops=None):
-        if mode not in ("all_to_all", "all_gather"):
-            raise ValueError("mode must be 'all_to_all' or 'all_gather'")
+        if mode not in ("all_to_all", "all_gather", "a2av") and mode not in _NATIVE_MODES:
+            raise ValueError("mode must be 'native', 'native_padded', 'native_exact', 'all_to_all', 'all_gather' or 'a2av'")
         self.block = block
         self.group = group
         self.mode = mode
@@ -130,7 +182,16 @@ class ExpertParallelMoe:
 
     @staticmethod
     def default_mode() -> str:
-        return "all_gather"
+        return "native"
+
+    def _routed_everywhere(self, x: torch.Tensor):
+        """Every rank's rows, ids and weights on this rank (what the all-gather transport delivers)."""
+        n = x.shape[0]
+        self.block.route(x, out=(self.logits, self.w, self.idx))
+        with self._batched(x.device):
+            dist.all_gather_into_tensor(self.recv_x, x, group=self.group)
+            dist.all_gather_into_tensor(self.recv_idx, self.idx, group=self.group)
+            dist.all_gather_into_tensor(self.recv_w, self.w, group=self.group)
 
     def _mark(self, profile, name):
         if profile:
@@ -143,6 +204,8 @@ class ExpertParallelMoe:
         out = torch.empty((x.shape[0], self.H), dtype=torch.bfloat16, device=x.device)
         self.forward_into(x, out)
         n = x.shape[0]
+        if self.mode in _NATIVE_MODES or self.mode == "a2av":
+            self._routed_everywhere(x.contiguous())
         own = (self.rank * n, n) if self.block.has_shared else None
         acc = {}
         self.block.trace(True)
@@ -164,6 +227,10 @@ class ExpertParallelMoe:
         x = x.contiguous()
         self._buffers(n, x)
         self._events = {}
+        if self.mode in _NATIVE_MODES:
+            return self._native(x, out, stats, profile)
+        if self.mode == "a2av":
+            return A2avReference.forward_into(self, x, out, stats)
         self._mark(profile, "t0")
         self.block.route(x, out=(self.logits, self.w, self.idx))
         self._mark(profile, "d0")
@@ -207,6 +274,85 @@ class ExpertParallelMoe:
                         total=e["t0"].elapsed_time(e["c1"]))
         return out
 
+    def _native(self, x, out, stats, profile):
+        """pmoe_ep_forward: route, dispatch, experts, combine behind the C ABI."""
+        import ctypes as C
+        from ._lib import check, lib
+        from .moe import _TORCH_TO_PMOE, _check_buffer, _stream_ptr
+        n, dev = x.shape[0], x.device
+        _check_buffer("x", x, (n, self.H), tuple(_TORCH_TO_PMOE), dev)
+        _check_buffer("out", out, (n, self.H), tuple(_TORCH_TO_PMOE), dev)
+        comm = native_comm(self.group, dev)
+        h = self.block._h
+        if profile and not getattr(self, "_prof_on", False):
+            self._call_native(h, comm, x, out, n)   # the buffers exist after the first call
+            check(lib().pmoe_ep_profile(h, 1, None, None))
+            self._prof_on = True
+        self._mark(profile, "t0")
+        self._call_native(h, comm, x, out, n)
+        if stats is not None:
+            stats.update(router_logits=self.logits, top_indices=self.idx, top_weights=self.w)
+        if profile:
+            self._mark(True, "c1")
+            torch.cuda.synchronize()
+            a, b = C.c_float(), C.c_float()
+            check(lib().pmoe_ep_profile(h, -1, C.byref(a), C.byref(b)))
+            return dict(dispatch=a.value, combine=b.value, total=self._events["t0"].elapsed_time(self._events["c1"]))
+        return out
+
+    def _call_native(self, h, comm, x, out, n):
+        from ._lib import check, lib
+        from .moe import _TORCH_TO_PMOE, _stream_ptr
+        check(lib().pmoe_ep_forward(h, comm, x.data_ptr(), _TORCH_TO_PMOE[x.dtype], n, out.data_ptr(), _TORCH_TO_PMOE[out.dtype],
+                                    self.logits.data_ptr(), self.idx.data_ptr(), self.w.data_ptr(), _NATIVE_MODES[self.mode],
+                                    _stream_ptr(x.device)))
+
     def forward(self, x: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
         out = torch.empty((x.shape[0], self.H), dtype=out_dtype or x.dtype, device=x.device)
         return self.forward_into(x, out)
+
+
+class A2avReference:
+    """The native path's exchange restated with torch collectives (mode ``a2av``): the same plan, the same record order,
+    the same rank-order sum -- with unquantised rows, and `block` doing the expert arithmetic.  It is what the CPU
+    (gloo) test drives; on GPUs the native path is the product."""
+
+    @staticmethod
+    def forward_into(ep: "ExpertParallelMoe", x: torch.Tensor, out: torch.Tensor, stats: Optional[dict] = None):
+        n, N, k, g, H = x.shape[0], ep.N, ep.k, ep.group, ep.H
+        ep.block.route(x, out=(ep.logits, ep.w, ep.idx))
+        if stats is not None:
+            stats.update(router_logits=ep.logits, top_indices=ep.idx, top_weights=ep.w)
+        pos, cnt = plan_dispatch(ep.idx, N, ep.per_rank, ep.rank, ep.round_robin, True)
+        # everybody's counts: cnt_all[s][r] = records rank s sends to rank r
+        cnt_all = [torch.zeros_like(cnt) for _ in range(N)]
+        dist.all_gather(cnt_all, cnt, group=g)
+        cnt_all = torch.stack(cnt_all)
+        send_cnt = cnt_all[ep.rank].tolist()
+        recv_cnt = cnt_all[:, ep.rank].tolist()
+        # pack: records for rank r are the tokens with pos[:, r] >= 0, in token order; foreign ids masked
+        masked = mask_for_destinations(ep.idx, N, ep.per_rank, ep.round_robin)          # [N, n, k]
+        sel = [torch.nonzero(pos[:, r] >= 0).flatten() for r in range(N)]
+        send_x = torch.cat([x[s] for s in sel])
+        send_idx = torch.cat([masked[r][s] for r, s in enumerate(sel)])
+        send_w = torch.cat([ep.w[s] for s in sel])
+        rows = sum(recv_cnt)
+        recv_x = torch.empty((rows, H), dtype=x.dtype, device=x.device)
+        recv_idx = torch.empty((rows, k), dtype=torch.int32, device=x.device)
+        recv_w = torch.empty((rows, k), dtype=torch.float32, device=x.device)
+        dist.all_to_all_single(recv_x, send_x, recv_cnt, send_cnt, group=g)
+        dist.all_to_all_single(recv_idx, send_idx, recv_cnt, send_cnt, group=g)
+        dist.all_to_all_single(recv_w, send_w, recv_cnt, send_cnt, group=g)
+        own_begin = sum(recv_cnt[:ep.rank])
+        own = (own_begin, recv_cnt[ep.rank]) if ep.block.has_shared else None
+        part = ep.block.experts_forward_batched(recv_x, recv_idx, recv_w, k, out_dtype=torch.float32, shared_rows=own)
+        back = torch.empty((sum(send_cnt), H), dtype=torch.float32, device=x.device)
+        dist.all_to_all_single(back, part.contiguous(), send_cnt, recv_cnt, group=g)
+        # combine: rank order
+        acc = torch.zeros((n, H), dtype=torch.float32, device=x.device)
+        off = 0
+        for r in range(N):
+            acc[sel[r]] += back[off:off + send_cnt[r]]
+            off += send_cnt[r]
+        out.copy_(acc)
+        return out

@@ -13,7 +13,9 @@ sys.path.insert(0, ROOT)
 
 
 def main():
-    mode = sys.argv[1] if len(sys.argv) > 1 else "all_to_all"
+    mode = sys.argv[1] if len(sys.argv) > 1 else "native"
+    placement = sys.argv[2] if len(sys.argv) > 2 else "contiguous"
+    preset = sys.argv[3] if len(sys.argv) > 3 else "q4k_m"
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
@@ -22,9 +24,9 @@ def main():
     from paramecia_b200.ep import ExpertParallelMoe
     from tests.common import seeded_x
     E, k, n = 64, 6, 24
-    t = synth.make_layer(E=E, k=k, preset="q4k_m", seed=4)
+    t = synth.make_layer(E=E, k=k, preset=preset, seed=4)
     whole = synth.make_block(t, dev, max_tokens=world * n)
-    mine = synth.make_block(t, dev, max_tokens=world * n, expert_base=rank * (E // world), E_local=E // world)
+    mine = synth.make_rank_block(t, dev, world * n, rank, world, placement)
     x_all = seeded_x(world * n, 2048, 77, torch.bfloat16).to(dev)
     x = x_all[rank * n:(rank + 1) * n].contiguous()
     ep = ExpertParallelMoe(mine, mode=mode)
@@ -41,7 +43,8 @@ def main():
     flag = torch.tensor([1.0 if (err < 1e-5 and ok_idx) else 0.0], device=dev)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     if rank == 0:
-        print(f"EP_RESULT mode={mode} world={world} max_rel_err={err:.3e} idx_equal={ok_idx} all_ok={int(flag.item())}")
+        print(f"EP_RESULT mode={mode} placement={placement} preset={preset} world={world} max_rel_err={err:.3e} "
+              f"idx_equal={ok_idx} all_ok={int(flag.item())}")
     dist.destroy_process_group()
     sys.exit(0 if flag.item() == 1.0 else 1)
 

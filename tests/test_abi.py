@@ -31,7 +31,7 @@ def test_every_declared_symbol_is_exported_and_bound():
 
 
 def test_sizes_and_version():
-    assert pm.lib().pmoe_version() == 3
+    assert pm.lib().pmoe_version() == 4
     assert (pm.block_size(pm.Q4_K), pm.type_size(pm.Q4_K)) == (256, 144)
     assert (pm.block_size(pm.Q6_K), pm.type_size(pm.Q6_K)) == (256, 210)
     assert (pm.block_size(pm.Q8_0), pm.type_size(pm.Q8_0)) == (32, 34)

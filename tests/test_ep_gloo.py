@@ -64,7 +64,7 @@ class NumpyOps:
         out.copy_(acc)
 
 
-def _worker(rank, world, port, mode, ret):
+def _worker(rank, world, port, mode, ret, k=3):
     sys.path.insert(0, ROOT)
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -72,7 +72,7 @@ def _worker(rank, world, port, mode, ret):
         from paramecia_b200 import synth
         from paramecia_b200.ep import ExpertParallelMoe
         from tests.common import oracle_layer, seeded_x
-        t = synth.make_layer(E=8, k=3, preset="q4k_m", seed=2)
+        t = synth.make_layer(E=8, k=k, preset="q4k_m", seed=2)
         n = 5
         x_all = seeded_x(world * n, 2048, 31)
         x = x_all[rank * n:(rank + 1) * n].contiguous()
@@ -89,12 +89,13 @@ def _worker(rank, world, port, mode, ret):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("mode", ["all_to_all", "all_gather"])
-def test_two_ranks_equal_one(mode):
+@pytest.mark.parametrize("mode,k", [("all_to_all", 3), ("all_gather", 3), ("a2av", 3), ("a2av", 1)])
+def test_two_ranks_equal_one(mode, k):
+    # a2av: the exchange of the native path (exact counts; with k = 1 most tokens stay on one rank)
     s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
     mgr = mp.Manager()
     ret = mgr.dict()
-    mp.spawn(_worker, args=(2, port, mode, ret), nprocs=2, join=True)
+    mp.spawn(_worker, args=(2, port, mode, ret, k), nprocs=2, join=True)
     assert len(ret) == 2
     for rank in range(2):
         err, same_idx = ret[rank]
@@ -109,3 +110,17 @@ def test_destination_masks():
     m = mask_for_destinations(idx, 2, 4)
     assert m[0].tolist() == [[0, INVALID_EXPERT, INVALID_EXPERT], [3, INVALID_EXPERT, INVALID_EXPERT]]
     assert m[1].tolist() == [[INVALID_EXPERT, 5, 7], [INVALID_EXPERT, 4, 6]]
+
+
+def test_dispatch_plan():
+    from paramecia_b200.ep import plan_dispatch
+    # 4 experts per rank, 2 ranks; rank 0 is home
+    idx = torch.tensor([[0, 1], [4, 5], [3, 6], [7, 4], [-1, 2]], dtype=torch.int32)
+    pos, cnt = plan_dispatch(idx, 2, 4, self_rank=0)
+    assert pos[:, 0].tolist() == [0, 1, 2, 3, 4]            # the home rank takes every token (shared expert)
+    assert pos[:, 1].tolist() == [-1, 0, 1, 2, -1]          # rank 1 only the tokens with an expert 4..7
+    assert cnt.tolist() == [5, 3]
+    pos, cnt = plan_dispatch(idx, 2, 4, self_rank=0, round_robin=True)   # expert e on rank e % 2
+    assert pos[:, 1].tolist() == [0, 1, 2, 3, -1] and cnt.tolist() == [5, 4]
+    pos, cnt = plan_dispatch(idx, 2, 4, self_rank=1, self_takes_all=False)
+    assert pos[:, 0].tolist() == [0, -1, 1, -1, 2] and cnt.tolist() == [3, 3]
