@@ -371,6 +371,205 @@ __global__ void __launch_bounds__(GU_THREADS, 2) k_gu_prefill(const GuArgs A)
     if (warp == 0) tmem_dealloc(tmem, PF_TMEM_COLS);
 }
 
+// ---------------------------------------------------------------- gate/up, Q8_0, exact integer block sums
+// Q8_0 weights against Q8_0 activations (what the reference CPU path does for this type): one block of 32 is the
+// K of one kind::i8 MMA (s8 x s8 -> s32), and every block has its own accumulator -- four blocks (K = 128) per
+// step fill 4 x 64 columns of tensor memory -- because the scales d_w (per row and block) and d_x (per token and
+// block) meet the integer sum only afterwards: acc += (d_w * d_x) * S, exactly the f32 expression of the decode
+// kernels, block after block in K order.  The weights need no decoding: a thread copies its row's quants into the
+// K-major core-matrix layout (the 34-byte blocks put every second block's quants 2 bytes off a word: funnel shifts).
+struct Gu80Ops {
+    uint8_t a[PF_M * 128];
+    uint8_t b[PF_NT * 128];
+    float dw[4][PF_M];
+    float dx[4][PF_NT];
+};
+struct Gu80Smem {
+    union {
+        Gu80Ops o;                           // operands and scales of one step
+        float xch[PF_M * (PF_NT + 1)];       // the accumulators' way to silu(gate) * up at the end
+    };
+    int row_in[PF_NT];
+    int row_out[PF_NT];
+    uint64_t bar;
+    uint32_t tmem_base;
+    int slot, tile_in_slot;
+};
+
+__global__ void __launch_bounds__(GU_THREADS, 2) k_gu_prefill_q80(const GuArgs A)
+{
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    Gu80Smem &S = *reinterpret_cast<Gu80Smem *>(smem_raw);
+    const int tid = threadIdx.x, warp = tid >> 5;
+
+    const int n_active = A.routed ? *A.g.n_active : 0;
+    const int routed_tiles = n_active ? A.tile_prefix[n_active] : 0;
+    const int shared_tiles = A.has_shared ? (A.sh_count + PF_NT - 1) / PF_NT : 0;
+    const int tile = blockIdx.y;
+    if (tile >= routed_tiles + shared_tiles) return;
+    if (tid == 0) {
+        if (tile < routed_tiles) {
+            const int2 ti = A.g.tile_table[tile];
+            S.slot = ti.x;
+            S.tile_in_slot = ti.y;
+        } else {
+            S.slot = -1;
+            S.tile_in_slot = tile - routed_tiles;
+        }
+        mbar_init(&S.bar, 1);
+        fence_mbar_init();
+    }
+    if (warp == 0) tmem_alloc(&S.tmem_base, PF_TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = S.tmem_base;
+    const int slot = S.slot, t0 = S.tile_in_slot * PF_NT;
+    const bool is_shared = slot < 0;
+    int m;
+    const int *list = nullptr;
+    const uint8_t *wg, *wu;
+    if (is_shared) {
+        m = A.sh_count;
+        wg = A.sgate; wu = A.sup;
+    } else {
+        m = A.g.count[slot];
+        list = A.g.pairs + A.g.offset[slot];
+        wg = A.gate + (size_t)slot * A.expert_bytes;
+        wu = A.up + (size_t)slot * A.expert_bytes;
+    }
+    const int cnt = m - t0 < PF_NT ? m - t0 : PF_NT;
+    if (tid < PF_NT) {
+        int rin = -1, rout = -1;
+        if (tid < cnt) {
+            if (is_shared) { rin = A.sh_begin + t0 + tid; rout = A.n * A.top_k + rin; }
+            else { const int p = list[t0 + tid]; rin = p / A.top_k; rout = p; }
+        }
+        S.row_in[tid] = rin;
+        S.row_out[tid] = rout;
+    }
+    __syncthreads();
+
+    // thread (r, kh): weight row r (0..63 gate, 64..127 up), blocks 2 kh and 2 kh + 1 of every 128-wide step;
+    // afterwards it drains token columns 32 kh .. 32 kh + 31 of row r
+    const int r = tid & (PF_M - 1), kh = tid >> 7;
+    const int f0 = blockIdx.x * 64;
+    const int nkb = A.H / QK8_0;   // blocks per row
+    const uint8_t *wrow = (r < 64 ? wg : wu) + (size_t)(f0 + (r & 63)) * nkb * Q8_0_BYTES;
+    const int steps = A.H / 128;
+    const int tk = tid >> 2, quarter = tid & 3;   // B side: one block of one token per thread
+    const int rin_b = S.row_in[tk];
+
+    constexpr uint32_t IDESC_SS = make_idesc(2, 1, 1, PF_NT, PF_M);  // s8 x s8 -> s32
+    constexpr int NC = PF_NT / 2;
+    float acc[NC];
+#pragma unroll
+    for (int i = 0; i < NC; i++) acc[i] = 0.f;
+    uint32_t phase = 0;
+    bool ok = true;
+
+    // the thread's two blocks of the current step: 68 bytes from a 4-byte boundary
+    //   [0,2) d of block 0 | [2,34) its quants | [34,36) d of block 1 | [36,68) its quants
+    uint32_t raw[17];
+    {
+        const uint32_t *src = reinterpret_cast<const uint32_t *>(wrow + 68 * kh);
+#pragma unroll
+        for (int i = 0; i < 17; i++) raw[i] = src[i];
+    }
+    for (int s = 0; s < steps && ok; s++) {
+        // ---- this step's activations first: they fly while the weights are laid out
+        uint4 bv[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
+        float dxv = 0.f;
+        if (rin_b >= 0) {
+            const uint4 *src = reinterpret_cast<const uint4 *>(A.xq.qs + (size_t)rin_b * A.H + 128 * s + 32 * quarter);
+            bv[0] = src[0];
+            bv[1] = src[1];
+            dxv = A.xq.d[(size_t)rin_b * nkb + 4 * s + quarter];
+        }
+        // ---- A: the row's two blocks of quants
+        {
+            uint32_t q0[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) q0[i] = __funnelshift_r(raw[i], raw[i + 1], 16);
+            const int kb0 = 64 * kh;   // K byte of block 2 kh inside the step
+            *reinterpret_cast<uint4 *>(S.o.a + core_off(PF_M, r, kb0)) = make_uint4(q0[0], q0[1], q0[2], q0[3]);
+            *reinterpret_cast<uint4 *>(S.o.a + core_off(PF_M, r, kb0 + 16)) = make_uint4(q0[4], q0[5], q0[6], q0[7]);
+            *reinterpret_cast<uint4 *>(S.o.a + core_off(PF_M, r, kb0 + 32)) = make_uint4(raw[9], raw[10], raw[11], raw[12]);
+            *reinterpret_cast<uint4 *>(S.o.a + core_off(PF_M, r, kb0 + 48)) = make_uint4(raw[13], raw[14], raw[15], raw[16]);
+            S.o.dw[2 * kh][r] = half_bits_to_float((uint16_t)(raw[0] & 0xffffu));
+            S.o.dw[2 * kh + 1][r] = half_bits_to_float((uint16_t)(raw[8] >> 16));
+        }
+        // ---- B: block `quarter` of token tk
+        *reinterpret_cast<uint4 *>(S.o.b + core_off(PF_NT, tk, 32 * quarter)) = bv[0];
+        *reinterpret_cast<uint4 *>(S.o.b + core_off(PF_NT, tk, 32 * quarter + 16)) = bv[1];
+        S.o.dx[quarter][tk] = dxv;
+        fence_proxy_async();   // generic-proxy writes above become visible to the tensor core
+        tc_fence_before();
+        __syncthreads();
+        if (tid == 0) {
+            tc_fence_after();
+#pragma unroll
+            for (int j = 0; j < 4; j++)   // one block = 32 bytes of K = one instruction, its own 64 columns
+                mma_i8(tmem + 64 * j, smem_desc(S.o.a + j * 2 * (PF_M * 16), PF_M * 16, 128),
+                       smem_desc(S.o.b + j * 2 * (PF_NT * 16), PF_NT * 16, 128), IDESC_SS, 0);
+            tc_commit(&S.bar);
+        }
+        if (s + 1 < steps) {   // the next step's blocks, in flight during the MMAs and the fold
+            const uint32_t *src = reinterpret_cast<const uint32_t *>(wrow + (size_t)(s + 1) * 136 + 68 * kh);
+#pragma unroll
+            for (int i = 0; i < 17; i++) raw[i] = src[i];
+        }
+        if (!mbar_wait_spin(&S.bar, phase)) {
+            set_status(A.status, PMOE_ERR_TIMEOUT, 35, s);
+            ok = false;
+        }
+        phase ^= 1;
+        tc_fence_after();
+        if (ok) {
+            const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16) + kh * NC;
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const float dw = S.o.dw[j][r];
+#pragma unroll
+                for (int cc = 0; cc < NC / 16; cc++) {
+                    uint32_t v[16];
+                    tmem_ld16(lane_addr + 64 * j + cc * 16, v);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int q = 0; q < 4; q++) {
+                        const float4 dx = *reinterpret_cast<const float4 *>(&S.o.dx[j][kh * NC + cc * 16 + 4 * q]);
+                        acc[cc * 16 + 4 * q + 0] += (dw * dx.x) * (float)(int)v[4 * q + 0];
+                        acc[cc * 16 + 4 * q + 1] += (dw * dx.y) * (float)(int)v[4 * q + 1];
+                        acc[cc * 16 + 4 * q + 2] += (dw * dx.z) * (float)(int)v[4 * q + 2];
+                        acc[cc * 16 + 4 * q + 3] += (dw * dx.w) * (float)(int)v[4 * q + 3];
+                    }
+                }
+            }
+        }
+        tc_fence_before();
+        __syncthreads();  // operands, scales and accumulators are free for the next step
+        tc_fence_after();
+    }
+
+    // ---- silu(gate) * up through shared memory ([128][PF_NT + 1] floats, over the operand tiles and the scale
+    // arrays, which nothing reads any more)
+    float *xch = S.xch;
+#pragma unroll
+    for (int j = 0; j < NC; j++) xch[r * (PF_NT + 1) + kh * NC + j] = acc[j];
+    __syncthreads();
+    if (ok) {
+        for (int o = tid; o < 64 * PF_NT; o += GU_THREADS) {
+            const int f = o & 63, j = o >> 6;
+            const int rout = S.row_out[j];
+            if (rout < 0) continue;
+            const float g = xch[f * (PF_NT + 1) + j], u = xch[(64 + f) * (PF_NT + 1) + j];
+            A.act[(size_t)rout * A.F + f0 + f] = g / (1.f + expf(-g)) * u;
+        }
+    }
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem, PF_TMEM_COLS);
+}
+
 // ---------------------------------------------------------------- down projection, fp16 operands
 // The down GEMM has no re-quantisation after it, so its own rounding lands in the output
 // directly: dequantised fp16 weights times the fake-quantised activation d*q in fp16 with f32
@@ -483,6 +682,38 @@ template <> struct DownDequant<PMOE_Q4_K> {
                     const int kel = 32 * j + 8 * c;
                     *reinterpret_cast<uint4 *>(a_tile + core_off(PF_M, r, 2 * kel)) = make_uint4(o[0], o[1], o[2], o[3]);
                 }
+            }
+        }
+    }
+};
+
+// Q8_0: K step s = blocks 4 s .. 4 s + 3 of the row (F = 512: 16 blocks of 34 bytes)
+template <> struct DownDequant<PMOE_Q8_0> {
+    static constexpr int ROW_BYTES = 16 * Q8_0_BYTES;
+    __device__ static inline void step(const uint8_t *row, int s, uint8_t *a_tile, int r)
+    {
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const uint8_t *blk = row + (4 * s + j) * Q8_0_BYTES;   // 2-byte aligned
+            const __half d = __ushort_as_half(*reinterpret_cast<const uint16_t *>(blk));
+            const __half2 d2 = __halves2half2(d, d);
+#pragma unroll
+            for (int c = 0; c < 4; c++) {   // 8 weights per 16-byte chunk
+                uint32_t o[4];
+#pragma unroll
+                for (int i = 0; i < 2; i++) {
+                    const uint32_t v = lds_u32_a2(blk + 2 + 8 * c + 4 * i);
+                    // 0x6400 | (b ^ 0x80) is the fp16 number 1024 + 128 + q for the signed byte q
+                    const uint32_t u = v ^ 0x80808080u;
+                    const uint32_t p0 = __byte_perm(u, 0x64646464u, 0x4140), p1 = __byte_perm(u, 0x64646464u, 0x4342);
+                    const __half2 bias = __floats2half2_rn(1152.f, 1152.f);
+                    const __half2 h0 = __hmul2(__hsub2(*reinterpret_cast<const __half2 *>(&p0), bias), d2);
+                    const __half2 h1 = __hmul2(__hsub2(*reinterpret_cast<const __half2 *>(&p1), bias), d2);
+                    o[2 * i] = *reinterpret_cast<const uint32_t *>(&h0);
+                    o[2 * i + 1] = *reinterpret_cast<const uint32_t *>(&h1);
+                }
+                const int kel = 32 * j + 8 * c;
+                *reinterpret_cast<uint4 *>(a_tile + core_off(PF_M, r, 2 * kel)) = make_uint4(o[0], o[1], o[2], o[3]);
             }
         }
     }
@@ -622,14 +853,31 @@ __global__ void __launch_bounds__(PF_THREADS, 2) k_down_prefill(const DownArgs A
     if (warp == 0) tmem_dealloc(tmem, 64);
 }
 
-// Q8_K quantisation of an activated row, written back as fp16 d*q for the fp16 down GEMM
+// Quantisation of an activated row the way the row's down matrix wants it (Q8_K for K-quants, Q8_0 for Q8_0:
+// BlockQ8K / BlockQ8_0::from_float, bit-exact), written back as fp16 d*q for the fp16 down GEMM
 __global__ void __launch_bounds__(64) k_act_fakequant_h(const float *__restrict__ act, int F, int n_routed_rows,
-                                                        const int *__restrict__ pos, bool routed,
-                                                        __half *__restrict__ out)
+                                                        const int *__restrict__ pos, bool routed, bool kq_routed,
+                                                        bool kq_shared, __half *__restrict__ out)
 {
     const int r = blockIdx.x;
     if (r < n_routed_rows && (!routed || pos[r] < 0)) return;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const bool kq = r < n_routed_rows ? kq_routed : kq_shared;
+    if (!kq) {
+        // Q8_0: blocks of 32, d = amax / 127 kept as f16, q = round_half_away(x * (1 / d))
+        for (int b = warp; b < F / QK8_0; b += 2) {
+            const float x = act[(size_t)r * F + b * QK8_0 + lane];
+            float amax = fabsf(x);
+#pragma unroll
+            for (int s = 16; s >= 1; s >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, s));
+            const float d = __fdiv_rn(amax, 127.f);
+            const float id = d != 0.f ? __fdiv_rn(1.f, d) : 0.f;
+            const float q = roundf(__fmul_rn(x, id));
+            const float df = __half2float(__float2half_rn(d));
+            out[(size_t)r * F + b * QK8_0 + lane] = __float2half_rn(q * df);
+        }
+        return;
+    }
     for (int b = warp; b < F / QK_K; b += 2) {
         const float *src = act + (size_t)r * F + b * QK_K;
         float v[8];
@@ -671,17 +919,26 @@ static int max_routed_tiles(const LayerDev &L, int n, int top_k)
     return (int)(pairs / PF_NT + act);
 }
 
+static bool pf_gu_ok(int dt) { return dt == PMOE_Q4_K || dt == PMOE_Q8_0; }
+static bool pf_dn_ok(int dt) { return dt == PMOE_Q6_K || dt == PMOE_Q4_K || dt == PMOE_Q8_0; }
+
 bool prefill_supported(const LayerDev &L, bool routed, bool shared)
 {
     if (L.H != 2048 || L.F != 512) return false;
-    if (routed && L.gate_dtype != PMOE_Q4_K) return false;
-    if (shared && L.sh_gate_dtype != PMOE_Q4_K) return false;
+    if (routed && !pf_gu_ok(L.gate_dtype)) return false;
+    if (shared && !pf_gu_ok(L.sh_gate_dtype)) return false;
     return true;
 }
 
 cudaError_t launch_gate_up_prefill(const LayerDev &L, const Workspace &ws, int n, int top_k, bool routed, bool shared,
                                    cudaStream_t s)
 {
+    if (routed && shared && L.gate_dtype != L.sh_gate_dtype) {   // two types: one launch each
+        cudaError_t e = launch_gate_up_prefill(L, ws, n, top_k, true, false, s);
+        if (e != cudaSuccess) return e;
+        return launch_gate_up_prefill(L, ws, n, top_k, false, true, s);
+    }
+    const int dt = routed ? L.gate_dtype : L.sh_gate_dtype;
     GuArgs A{};
     A.gate = L.gate_exps; A.up = L.up_exps;
     A.expert_bytes = row_bytes(L.gate_dtype, L.H) * L.F;
@@ -691,29 +948,30 @@ cudaError_t launch_gate_up_prefill(const LayerDev &L, const Workspace &ws, int n
     A.sh_begin = ws.sh_begin; A.sh_count = ws.sh_count;
     A.g = ws.groups;
     A.tile_prefix = ws.groups.tile_prefix;
-    A.xq = ws.x_q8k;
+    A.xq = dt == PMOE_Q8_0 ? ws.x_q80 : ws.x_q8k;
     A.act = ws.act;
     A.status = ws.status;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(k_gu_prefill, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(GuSmem) + 128);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(k_gu_prefill_q80, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Gu80Smem) + 128);
         if (e != cudaSuccess) return e;
         configured = true;
     }
     const int tiles = (routed ? max_routed_tiles(L, n, top_k) : 0) + (shared ? (ws.sh_count + PF_NT - 1) / PF_NT : 0);
     dim3 grid(L.F / 64, tiles);
-    k_gu_prefill<<<grid, GU_THREADS, sizeof(GuSmem) + 128, s>>>(A);
+    if (dt == PMOE_Q8_0) k_gu_prefill_q80<<<grid, GU_THREADS, sizeof(Gu80Smem) + 128, s>>>(A);
+    else k_gu_prefill<<<grid, GU_THREADS, sizeof(GuSmem) + 128, s>>>(A);
     count_launch();
     return cudaGetLastError();
 }
 
 bool prefill_down_supported(const LayerDev &L, bool routed, bool shared)
 {
-    auto ok = [](int dt) { return dt == PMOE_Q6_K || dt == PMOE_Q4_K; };
     if (L.H != 2048 || L.F != 512) return false;
-    if (routed && !ok(L.down_dtype)) return false;
-    if (shared && !ok(L.sh_down_dtype)) return false;
-    if (routed && shared && L.down_dtype != L.sh_down_dtype) return false;
+    if (routed && !pf_dn_ok(L.down_dtype)) return false;
+    if (shared && !pf_dn_ok(L.sh_down_dtype)) return false;
     return true;
 }
 
@@ -733,12 +991,9 @@ static cudaError_t launch_down_t(const DownArgs &A, dim3 grid, cudaStream_t s)
     return cudaGetLastError();
 }
 
-cudaError_t launch_down_prefill(const LayerDev &L, const Workspace &ws, const float *w, int n, int top_k, bool routed,
-                                bool shared, cudaStream_t s)
+static cudaError_t launch_down_gemm(const LayerDev &L, const Workspace &ws, const float *w, int n, int top_k, bool routed,
+                                    bool shared, cudaStream_t s)
 {
-    const int rows = n * top_k + (shared ? n : 0);
-    k_act_fakequant_h<<<rows, 64, 0, s>>>(ws.act, L.F, n * top_k, ws.groups.pos, routed, ws.act_h);
-    count_launch();
     DownArgs A{};
     A.down = L.down_exps;
     A.expert_bytes = row_bytes(L.down_dtype, L.F) * L.H;
@@ -757,7 +1012,23 @@ cudaError_t launch_down_prefill(const LayerDev &L, const Workspace &ws, const fl
     dim3 grid(L.H / PF_M, tiles);
     const int dt = routed ? L.down_dtype : L.sh_down_dtype;
     if (dt == PMOE_Q6_K) return launch_down_t<PMOE_Q6_K>(A, grid, s);
+    if (dt == PMOE_Q8_0) return launch_down_t<PMOE_Q8_0>(A, grid, s);
     return launch_down_t<PMOE_Q4_K>(A, grid, s);
+}
+
+cudaError_t launch_down_prefill(const LayerDev &L, const Workspace &ws, const float *w, int n, int top_k, bool routed,
+                                bool shared, cudaStream_t s)
+{
+    const int rows = n * top_k + (shared ? n : 0);
+    k_act_fakequant_h<<<rows, 64, 0, s>>>(ws.act, L.F, n * top_k, ws.groups.pos, routed, is_kquant(L.down_dtype),
+                                          is_kquant(L.sh_down_dtype), ws.act_h);
+    count_launch();
+    if (routed && shared && L.down_dtype != L.sh_down_dtype) {   // two types: one launch each
+        cudaError_t e = launch_down_gemm(L, ws, w, n, top_k, true, false, s);
+        if (e != cudaSuccess) return e;
+        return launch_down_gemm(L, ws, w, n, top_k, false, true, s);
+    }
+    return launch_down_gemm(L, ws, w, n, top_k, routed, shared, s);
 }
 
 }  // namespace pmoe

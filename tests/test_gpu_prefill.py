@@ -33,7 +33,8 @@ def force_prefill():
         os.environ["PMOE_PREFILL"] = old
 
 
-@pytest.mark.parametrize("preset,E,k,n", [("q4k", 8, 2, 200), ("q4k_q6k_all", 16, 3, 333), ("q4k_q6k_all", 4, 1, 65)])
+@pytest.mark.parametrize("preset,E,k,n", [("q4k", 8, 2, 200), ("q4k_q6k_all", 16, 3, 333), ("q4k_q6k_all", 4, 1, 65),
+                                          ("q8_0", 8, 2, 200), ("q8_0", 4, 1, 65), ("q4k_m", 16, 3, 333)])
 def test_forced_prefill_matches_oracle(force_prefill, preset, E, k, n):
     t = synth.make_layer(E=E, k=k, preset=preset, seed=13)
     blk = synth.make_block(t, DEV, max_tokens=n)
@@ -67,10 +68,11 @@ def test_skewed_routing_takes_the_prefill_path_by_itself():
     assert max_abs(got, want) <= MAX_ABS_TOL and rel_l2(got, want) <= REL_L2_TOL
 
 
-def test_prefill_equals_decode_kernels_on_gate_up(force_prefill):
+@pytest.mark.parametrize("preset", ["q4k", "q8_0"])
+def test_prefill_equals_decode_kernels_on_gate_up(force_prefill, preset):
     # same layer through both paths: the activated rows are integer-exact in both, so the
     # outputs differ only by the fp16 down GEMM
-    t = synth.make_layer(E=8, k=2, preset="q4k", seed=15)
+    t = synth.make_layer(E=8, k=2, preset=preset, seed=15)
     blk = synth.make_block(t, DEV, max_tokens=128)
     x = seeded_x(128, 2048, 3, torch.bfloat16).to(DEV)
     a = blk.forward(x).float().cpu().numpy()
@@ -82,10 +84,9 @@ def test_prefill_equals_decode_kernels_on_gate_up(force_prefill):
 
 @pytest.mark.parametrize("preset", ["q8_0", "q4k_m"])
 def test_prefill_sized_call_with_a_q8_0_shared_expert(preset):
-    # benchmark configuration 5 in miniature (all-Q8_0 block, Zipf routing, hundreds of tokens): no tensor-core
-    # kernel serves Q8_0 gate/up, so the streaming kernels take every pass and the shared expert's 600 tokens run
-    # as 75 eight-token tensor-core tiles per item; with Q4_K routed experts (q4k_m) the routed part takes the
-    # tensor-core kernels and the shared expert the streaming ones
+    # benchmark configuration 5 in miniature (all-Q8_0 block, Zipf routing, hundreds of tokens): Q8_0 gate/up and
+    # down have tensor-core kernels of their own (one block of 32 per MMA, scales applied per block); with Q4_K
+    # routed experts (q4k_m) the routed part and the Q8_0 shared expert take one launch each
     n = 600
     t = synth.make_layer(E=32, k=4, preset=preset, seed=16, zipf=True)
     blk = synth.make_block(t, DEV, max_tokens=n)
