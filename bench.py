@@ -771,8 +771,9 @@ def pmoe_arm(args):
         want = lambda name: (not only) or name in only
         if N == 1 and want("prefill"):
             extra["prefill"] = prefill_record(ctx)
-            extra["prefill_q8_0_shared"] = {k_: v for k_, v in prefill_record(ctx, "q4k_m").items()
-                                            if k_ in ("value", "ms_per_step", "phases_us", "config", "block_tflops")}
+            keep = ("value", "ms_per_step", "phases_us", "config", "block_tflops", "roofline", "roofline_down")
+            extra["prefill_q8_0_shared"] = {k_: v for k_, v in prefill_record(ctx, "q4k_m").items() if k_ in keep}
+            extra["prefill_q8_0"] = {k_: v for k_, v in prefill_record(ctx, "q8_0").items() if k_ in keep}
         if want("stack48"):
             extra["stack48"] = stack_record(ctx)
         if N > 1 and want("ep_prefill"):

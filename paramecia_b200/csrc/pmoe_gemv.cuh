@@ -601,6 +601,7 @@ struct GemvArgs {
     DevStatus *status;
     int debug;                 // 1: skip the arithmetic, 2: skip the copies (timing experiments)
     int stage_bytes;           // bytes between the slots of the shared-memory ring
+    uint32_t max_polls;        // tensor-core kernels: limit of every bounded wait (try_wait calls, each up to ~20 us)
     int shw_min;               // tensor-core kernels: a Q8_0 shared expert over this many tokens or more gets its own warp
     // gate/up only: the CTA that completes an expert's last item re-quantises the expert's activated rows
     int *slot_done;            // [E_local + 1] items finished per slot (shared expert last); returns to zero
@@ -763,10 +764,10 @@ __device__ inline uint64_t *ring_empty(uint8_t *base, int s) { return reinterpre
 
 // After its last copy a producer waits (bounded) until the copies still in flight have landed, so
 // that no asynchronous write can reach shared memory after the CTA has left.
-__device__ inline void drain_ring(uint8_t *ring, int issued)
+__device__ inline void drain_ring(uint8_t *ring, int issued, uint32_t max_polls = (1u << 20))
 {
     for (int it = issued > NSTAGE ? issued - NSTAGE : 0; it < issued; it++)
-        mbar_wait(ring_full(ring, it % NSTAGE), (uint32_t)(it / NSTAGE) & 1);
+        mbar_wait(ring_full(ring, it % NSTAGE), (uint32_t)(it / NSTAGE) & 1, max_polls);
 }
 
 // The producer's side of the ring: issues the bulk copies of its next item once the compute
@@ -786,7 +787,9 @@ template <int DT_R, int DT_S1, int NMAT> struct Producer {
         const int it = issued++;
         const int s = it % NSTAGE;
         const uint32_t use = (uint32_t)(it / NSTAGE);
-        if (use > 0 && !mbar_wait(ring_empty(ring, s), (use - 1) & 1)) {
+        // the slot must have been released, and its previous copy must have landed: warps that gave up waiting
+        // release slots early, and a barrier must not be armed twice in one phase
+        if (use > 0 && !(mbar_wait(ring_empty(ring, s), (use - 1) & 1) && mbar_wait(ring_full(ring, s), (use - 1) & 1))) {
             set_status(A.status, PMOE_ERR_TIMEOUT, 20 + NMAT, it);
             return false;
         }

@@ -458,7 +458,7 @@ __device__ inline void gu_run_group(const GemvArgs &A, uint8_t *ring, const MmaW
         const uint32_t use = (uint32_t)(it / NSTAGE);
         // a wait that runs out is recorded; the warp keeps walking its items (and meeting the barriers
         // it shares with the other warps) without computing
-        if (!failed && A.debug != 2 && !mbar_wait(ring_full(ring, s), use & 1)) {
+        if (!failed && A.debug != 2 && !mbar_wait(ring_full(ring, s), use & 1, A.max_polls)) {
             set_status(A.status, PMOE_ERR_TIMEOUT, 18, it);
             failed = true;
         }
@@ -480,6 +480,13 @@ __device__ inline bool run_items_q4k_mma(const GemvArgs &A, uint8_t *ring, const
     la.slot = la.group = -1;
     la.step = 3;
     bool failed = false;
+    // PMOE_DEBUG=6 (test of the bounded waits): CTA 0 first waits on a barrier nothing ever arrives at; the wait runs
+    // out, the status word gets PMOE_ERR_TIMEOUT and the warps walk their items without computing, as after any
+    // expired wait
+    if (A.debug == 6 && blockIdx.x == 0 && !mbar_wait(ring_full(ring, 2 * NSTAGE), 0, A.max_polls)) {
+        set_status(A.status, PMOE_ERR_TIMEOUT, 19, 0);
+        failed = true;
+    }
     // progress bookkeeping for the fused re-quantisation: a routed expert is finished as a whole (all its groups),
     // the shared expert group by group (its eight rows are quantised by whoever completes the group)
     int cur_slot = -1, cur_group = -1, items_in_slot = 0, slot_groups = 0, slot_m = 0, slot_off = 0;
@@ -679,6 +686,7 @@ __global__ void __launch_bounds__(DT_S == PMOE_Q8_0 ? SHW_THREADS : GEMV_THREADS
             mbar_init(ring_full(ring, s), 1);
             mbar_init(ring_empty(ring, s), GEMV_WARPS);
         }
+        mbar_init(ring_full(ring, 2 * NSTAGE), 1);   // never arrived at: the timeout test waits on it
         fence_mbar_init();
         s_prefix1[0] = s_prefix1[1] = 0;
     }
@@ -725,8 +733,13 @@ __global__ void __launch_bounds__(DT_S == PMOE_Q8_0 ? SHW_THREADS : GEMV_THREADS
             const int s = issued % NSTAGE;
             const uint32_t use = (uint32_t)(issued / NSTAGE);
             if (use > 0) {
+                // the slot must have been released, and its previous copy must have landed: warps that gave up
+                // waiting release slots early, and a barrier must not be armed twice in one phase
                 int w = 1;
-                if (lane == 0) w = mbar_wait(ring_empty(ring, s), (use - 1) & 1) ? 1 : 0;
+                if (lane == 0)
+                    w = mbar_wait(ring_empty(ring, s), (use - 1) & 1, A.max_polls) &&
+                                mbar_wait(ring_full(ring, s), (use - 1) & 1, A.max_polls)
+                            ? 1 : 0;
                 w = __shfl_sync(0xffffffffu, w, 0);
                 if (!w) {
                     if (lane == 0) set_status(A.status, PMOE_ERR_TIMEOUT, 23, issued);
@@ -753,7 +766,7 @@ __global__ void __launch_bounds__(DT_S == PMOE_Q8_0 ? SHW_THREADS : GEMV_THREADS
                     if (!prod.issue_next()) { prod.issued--; break; }
                 issued = prod.issued;
             }
-            drain_ring(ring, issued);
+            drain_ring(ring, issued, A.max_polls);
         }
         return;
     }
@@ -1193,7 +1206,7 @@ __device__ inline void dm_run_group(const GemvArgs &A, uint8_t *smem, const MmaW
         const uint32_t use = (uint32_t)(it / DM_NSTAGE);
         // a wait that runs out is recorded; the warp keeps walking its items without computing, so that
         // the producer still sees its stages released
-        if (!failed && A.debug != 2 && !mbar_wait(dm_full(smem, s), use & 1)) {
+        if (!failed && A.debug != 2 && !mbar_wait(dm_full(smem, s), use & 1, A.max_polls)) {
             set_status(A.status, PMOE_ERR_TIMEOUT, 31, it);
             failed = true;
         }
@@ -1286,7 +1299,10 @@ __global__ void __launch_bounds__(DT_S == PMOE_Q8_0 ? SHW_THREADS : GEMV_THREADS
         for (; issued < n_mma; issued++) {
             const int s = issued % DM_NSTAGE;
             const uint32_t use = (uint32_t)(issued / DM_NSTAGE);
-            if (use > 0 && !mbar_wait(dm_empty(smem, s), (use - 1) & 1)) {
+            // the slot must have been released, and its previous copy must have landed: warps that gave up waiting
+            // release slots early, and a barrier must not be armed twice in one phase
+            if (use > 0 && !(mbar_wait(dm_empty(smem, s), (use - 1) & 1, A.max_polls) &&
+                             mbar_wait(dm_full(smem, s), (use - 1) & 1, A.max_polls))) {
                 set_status(A.status, PMOE_ERR_TIMEOUT, 33, issued);
                 ok = false;
                 break;
@@ -1304,7 +1320,7 @@ __global__ void __launch_bounds__(DT_S == PMOE_Q8_0 ? SHW_THREADS : GEMV_THREADS
             // the streaming items reuse the same shared memory: every tensor-core stage must have been
             // released first (which also means its copy has landed)
             for (int it = issued > DM_NSTAGE ? issued - DM_NSTAGE : 0; it < issued && ok; it++)
-                if (!mbar_wait(dm_empty(smem, it % DM_NSTAGE), (uint32_t)(it / DM_NSTAGE) & 1)) {
+                if (!mbar_wait(dm_empty(smem, it % DM_NSTAGE), (uint32_t)(it / DM_NSTAGE) & 1, A.max_polls)) {
                     set_status(A.status, PMOE_ERR_TIMEOUT, 34, it);
                     ok = false;
                 }
@@ -1312,13 +1328,13 @@ __global__ void __launch_bounds__(DT_S == PMOE_Q8_0 ? SHW_THREADS : GEMV_THREADS
                 Producer<DT_S1, DT_S1, 1> prod{A, plan, ring2, scur, 0, n_sh};
                 for (int i = 0; i < n_sh; i++)
                     if (!prod.issue_next()) { prod.issued--; break; }
-                drain_ring(ring2, prod.issued);
+                drain_ring(ring2, prod.issued, A.max_polls);
                 return;
             }
         }
         // no asynchronous write may reach shared memory after the CTA has left
         for (int it = issued > DM_NSTAGE ? issued - DM_NSTAGE : 0; it < issued; it++)
-            mbar_wait(dm_full(smem, it % DM_NSTAGE), (uint32_t)(it / DM_NSTAGE) & 1);
+            mbar_wait(dm_full(smem, it % DM_NSTAGE), (uint32_t)(it / DM_NSTAGE) & 1, A.max_polls);
         return;
     }
 
@@ -1376,6 +1392,15 @@ template <int DT_S> static cudaError_t launch_q6k_mma_t(const GemvArgs &A, cudaS
     return e;
 }
 
+// PMOE_MAX_POLLS in the environment shortens every bounded device-side wait (read at each launch; tests of the
+// timeout path use it)
+static uint32_t max_polls_env()
+{
+    const char *e = getenv("PMOE_MAX_POLLS");
+    const long v = e ? atol(e) : 0;
+    return v > 0 ? (uint32_t)v : (1u << 20);
+}
+
 static int shw_min_tokens()
 {
     static const int v = getenv("PMOE_SHW_MIN") ? atoi(getenv("PMOE_SHW_MIN")) : 1;
@@ -1385,6 +1410,7 @@ static int shw_min_tokens()
 cudaError_t launch_down_q6k_mma(GemvArgs &A, int dt_s, cudaStream_t s)
 {
     A.shw_min = shw_min_tokens();
+    A.max_polls = max_polls_env();
     A.stage_bytes = STAGE_BYTES;   // the streaming-kind items of a shared expert of another type
     switch (dt_s) {
     case 0: return launch_q6k_mma_t<0>(A, s);
@@ -1399,6 +1425,7 @@ cudaError_t launch_down_q6k_mma(GemvArgs &A, int dt_s, cudaStream_t s)
 cudaError_t launch_gate_up_q4k_mma(GemvArgs &A, int dt_s, cudaStream_t s)
 {
     A.shw_min = shw_min_tokens();
+    A.max_polls = max_polls_env();
     A.stage_bytes = MMA_STAGE_BYTES;
     switch (dt_s) {
     case 0: return launch_q4k_mma_t<0>(A, s);

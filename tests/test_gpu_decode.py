@@ -322,3 +322,31 @@ def test_stack_with_residual_and_rms_norm():
     # compare the MoE contribution, not the residual stream that carries the input unchanged
     assert rel_l2(got - h0.numpy(), want - h0.numpy()) <= REL_L2_TOL
     assert max_abs(got, want) <= MAX_ABS_TOL
+
+
+def test_bounded_wait_reports_timeout_and_the_layer_recovers():
+    """A device-side wait that runs out: one CTA of the gate/up kernel never receives its first item (the producer
+    skips that copy on request), its bounded wait expires after a few polls, the kernel records PMOE_ERR_TIMEOUT in
+    the layer's status word and every CTA still leaves normally.  Nothing traps or hangs; the next call is fine."""
+    t = synth.make_layer(E=64, k=6, preset="q4k_m", seed=23)
+    blk = synth.make_block(t, DEV, max_tokens=64)
+    x = seeded_x(64, 2048, 5, torch.bfloat16).to(DEV)
+    good = blk.forward(x).float().cpu()
+    blk.status()
+    old = {k: os.environ.get(k) for k in ("PMOE_DEBUG", "PMOE_MAX_POLLS")}
+    os.environ["PMOE_DEBUG"], os.environ["PMOE_MAX_POLLS"] = "6", "64"
+    try:
+        blk.forward(x)
+        with pytest.raises(pm.PmoeError) as e:
+            blk.status()
+        assert e.value.code == -7                      # PMOE_ERR_TIMEOUT
+    finally:
+        for k, v in old.items():
+            if v is None:
+                os.environ.pop(k, None)
+            else:
+                os.environ[k] = v
+    blk.status()                                       # the status word was cleared by the read above
+    again = blk.forward(x).float().cpu()
+    blk.status()
+    assert torch.equal(again, good)
