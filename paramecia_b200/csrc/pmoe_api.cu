@@ -104,6 +104,7 @@ void carve_workspace(pmoe_layer *L, Carver &c)
     w.act_q80.d = c.take<float>(rows * (F / QK8_0));
     w.act_q80.bsums = nullptr;
     w.act_h = c.take<__half>(rows * F);
+    w.act_h_scale = c.take<float>(rows);
     w.partial = c.take<float>(rows * H);
     w.slot_done = c.take<int>(El + 1 + (n + 7) / 8);   // per expert, the shared expert, and its 8-token tiles
     L->st_x = c.take<float>(n * H);

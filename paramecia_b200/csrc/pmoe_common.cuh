@@ -274,6 +274,7 @@ struct Workspace {
     float *act;          // [n*(k+1), F]  silu(gate)*up ; routed pair p at row p, shared token t at row n_cap*k + t
     QAct act_q8k, act_q80;
     __half *act_h;       // [n*(k+1), F]  fake-quantised activation for the fp16 down GEMM
+    float *act_h_scale;  // [n*(k+1)]     power of two a row of act_h was divided by (1 unless it would leave the fp16 range)
     float *partial;      // [n*(k+1), H]  weighted down-projection rows
     int *slot_done;      // [E_local + 1 + max_tokens/8] completion counters of the gate/up kernel: per expert, the shared
                          // expert, and the shared expert's 8-token tiles (zero between calls)

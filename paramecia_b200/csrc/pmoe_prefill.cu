@@ -587,6 +587,7 @@ struct DownArgs {
     Groups g;
     const int *tile_prefix;
     const __half *act_h;           // [n*(k+1), F] fake-quantised activation
+    const float *act_h_scale;      // [n*(k+1)] power of two each row of act_h was divided by
     const float *scale_r;          // routing weights [n*k]
     const float *scale_s;          // shared gate [n]
     float *partial;                // [n*(k+1), H]
@@ -790,6 +791,7 @@ __global__ void __launch_bounds__(PF_THREADS, 2) k_down_prefill(const DownArgs A
         if (tid < cnt) {
             if (is_shared) { rin = A.n * A.top_k + A.sh_begin + t0 + tid; sc = A.scale_s[A.sh_begin + t0 + tid]; }
             else { rin = list[t0 + tid]; sc = A.scale_r[rin]; }
+            sc *= A.act_h_scale[rin];
         }
         S.row_in[tid] = rin;
         S.scale[tid] = sc;
@@ -855,14 +857,32 @@ __global__ void __launch_bounds__(PF_THREADS, 2) k_down_prefill(const DownArgs A
 
 // Quantisation of an activated row the way the row's down matrix wants it (Q8_K for K-quants, Q8_0 for Q8_0:
 // BlockQ8K / BlockQ8_0::from_float, bit-exact), written back as fp16 d*q for the fp16 down GEMM
+// A row whose largest magnitude would leave the fp16 range is written times a power of two 2^-e (exact), and
+// row_scale[r] = 2^e goes back in when the down GEMM's accumulators are drained; other rows have scale 1.
 __global__ void __launch_bounds__(64) k_act_fakequant_h(const float *__restrict__ act, int F, int n_routed_rows,
                                                         const int *__restrict__ pos, bool routed, bool kq_routed,
-                                                        bool kq_shared, __half *__restrict__ out)
+                                                        bool kq_shared, __half *__restrict__ out,
+                                                        float *__restrict__ row_scale)
 {
+    __shared__ float s_amax[2];
     const int r = blockIdx.x;
     if (r < n_routed_rows && (!routed || pos[r] < 0)) return;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const bool kq = r < n_routed_rows ? kq_routed : kq_shared;
+    float down = 1.f;   // 2^-e
+    {
+        float am = 0.f;
+        for (int i = threadIdx.x; i < F; i += 64) am = fmaxf(am, fabsf(act[(size_t)r * F + i]));
+#pragma unroll
+        for (int s = 16; s >= 1; s >>= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, s));
+        if (lane == 0) s_amax[warp] = am;
+        __syncthreads();
+        am = fmaxf(s_amax[0], s_amax[1]);
+        // quantised values stay below 1.01 * amax; keep them under 32768
+        float up = 1.f;
+        while (am * down > 32768.f) { down *= 0.5f; up *= 2.f; }
+        if (threadIdx.x == 0) row_scale[r] = up;
+    }
     if (!kq) {
         // Q8_0: blocks of 32, d = amax / 127 kept as f16, q = round_half_away(x * (1 / d))
         for (int b = warp; b < F / QK8_0; b += 2) {
@@ -874,7 +894,7 @@ __global__ void __launch_bounds__(64) k_act_fakequant_h(const float *__restrict_
             const float id = d != 0.f ? __fdiv_rn(1.f, d) : 0.f;
             const float q = roundf(__fmul_rn(x, id));
             const float df = __half2float(__float2half_rn(d));
-            out[(size_t)r * F + b * QK8_0 + lane] = __float2half_rn(q * df);
+            out[(size_t)r * F + b * QK8_0 + lane] = __float2half_rn((q * df) * down);
         }
         return;
     }
@@ -902,7 +922,7 @@ __global__ void __launch_bounds__(64) k_act_fakequant_h(const float *__restrict_
             for (int j = 0; j < 4; j++) {
                 const float q0 = fminf(roundf(__fmul_rn(iscale, v[2 * j])), 127.f);
                 const float q1 = fminf(roundf(__fmul_rn(iscale, v[2 * j + 1])), 127.f);
-                h[j] = __floats2half2_rn(q0 * d, q1 * d);
+                h[j] = __floats2half2_rn((q0 * d) * down, (q1 * d) * down);
             }
             o = make_uint4(*reinterpret_cast<uint32_t *>(&h[0]), *reinterpret_cast<uint32_t *>(&h[1]),
                            *reinterpret_cast<uint32_t *>(&h[2]), *reinterpret_cast<uint32_t *>(&h[3]));
@@ -1004,6 +1024,7 @@ static cudaError_t launch_down_gemm(const LayerDev &L, const Workspace &ws, cons
     A.g = ws.groups;
     A.tile_prefix = ws.groups.tile_prefix;
     A.act_h = ws.act_h;
+    A.act_h_scale = ws.act_h_scale;
     A.scale_r = w;
     A.scale_s = ws.sh_sigmoid;
     A.partial = ws.partial;
@@ -1021,7 +1042,7 @@ cudaError_t launch_down_prefill(const LayerDev &L, const Workspace &ws, const fl
 {
     const int rows = n * top_k + (shared ? n : 0);
     k_act_fakequant_h<<<rows, 64, 0, s>>>(ws.act, L.F, n * top_k, ws.groups.pos, routed, is_kquant(L.down_dtype),
-                                          is_kquant(L.sh_down_dtype), ws.act_h);
+                                          is_kquant(L.sh_down_dtype), ws.act_h, ws.act_h_scale);
     count_launch();
     if (routed && shared && L.down_dtype != L.sh_down_dtype) {   // two types: one launch each
         cudaError_t e = launch_down_gemm(L, ws, w, n, top_k, true, false, s);

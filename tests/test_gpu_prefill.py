@@ -97,3 +97,21 @@ def test_prefill_sized_call_with_a_q8_0_shared_expert(preset):
     assert np.array_equal(idx.cpu().numpy().astype(np.uint32), want_idx)
     got = out.cpu().numpy()
     assert max_abs(got, want) <= MAX_ABS_TOL and rel_l2(got, want) <= REL_L2_TOL
+
+
+@pytest.mark.parametrize("preset,mult", [("q4k_q6k_all", 3000.0), ("q8_0", 800.0)])
+def test_activations_beyond_the_fp16_range(force_prefill, preset, mult):
+    # silu(gate) * up far above 65504: the fp16 down GEMM sees such a row divided by a power of two and the factor
+    # comes back when the accumulators are drained, so the result stays finite and within the relative bar
+    n = 130
+    t = synth.make_layer(E=8, k=2, preset=preset, seed=19)
+    blk = synth.make_block(t, DEV, max_tokens=n)
+    # (Q8_0 keeps its block scales as f16, so the reference itself overflows a little further up: smaller factor)
+    x = seeded_x(n, 2048, 77) * mult
+    out, (_, idx) = blk.forward_with_stats(x.to(DEV), out_dtype=torch.float32)
+    blk.status()
+    want, _, want_idx, _ = oracle_layer(t).forward(x.numpy())
+    assert np.array_equal(idx.cpu().numpy().astype(np.uint32), want_idx)
+    got = out.cpu().numpy()
+    assert np.isfinite(got).all() and np.abs(want).max() > 65504.0
+    assert rel_l2(got, want) <= REL_L2_TOL
