@@ -909,6 +909,121 @@ static float vec_dot_q8_0_q8_0(size_t n, const block_q8_0 *x, const block_q8_0 *
     return sumf;
 }
 
+/* ------------------------------------------------------------------ the same block dots with AVX2
+ * What candle does on x86 hosts: SIMD integer dots.  These restate the three hot ones (Q4_K, Q6_K and Q8_0
+ * weights) so that the CPU baseline is not a scalar loop, with THE SAME eight f32 lanes as the portable
+ * routines above: lane l collects the elements l, l + 8, l + 16, ... of a block, which is what the byte
+ * shuffle below arranges before the pairwise multiply-add.  Integer sums are exact in any order, the f32 steps
+ * are the portable ones in the same order: results are bit-identical (tests/test_oracle.py checks it). */
+#if defined(__AVX2__)
+#include <immintrin.h>
+static int g_use_simd = 1;
+
+/* bytes (b0..b15) of each 128-bit half -> (b0,b8,b1,b9,...,b7,b15): neighbours become the pair (l, l + 8) */
+static inline __m256i pair_mod8(__m256i v)
+{
+    const __m256i m = _mm256_setr_epi8(0, 8, 1, 9, 2, 10, 3, 11, 4, 12, 5, 13, 6, 14, 7, 15,
+                                       0, 8, 1, 9, 2, 10, 3, 11, 4, 12, 5, 13, 6, 14, 7, 15);
+    return _mm256_shuffle_epi8(v, m);
+}
+
+/* 32 unsigned bytes a (0..63) times 32 signed bytes y, both already paired: eight int32 lanes, lane l = sum of
+ * a[i] * y[i] over i = l mod 8 */
+static inline __m256i dot32_mod8(__m256i a, __m256i y)
+{
+    const __m256i p = _mm256_maddubs_epi16(a, y);                            /* 16 x int16: half h, lane l = groups 2h, 2h+1 */
+    const __m128i s = _mm_add_epi16(_mm256_castsi256_si128(p), _mm256_extracti128_si256(p, 1));
+    return _mm256_cvtepi16_epi32(s);
+}
+
+static float vec_dot_q4_K_q8_K_avx2(size_t n, const block_q4_K *x, const block_q8_K *y)
+{
+    float sums[8] = {0};
+    float sumf = 0.f;
+    for (size_t i = 0; i < n / QK_K; i++) {
+        uint8_t sc[8], mn[8];
+        for (int j = 0; j < 8; j++) q4k_scale_min(j, x[i].scales, &sc[j], &mn[j]);
+        int32_t sumi = 0;
+        for (int j = 0; j < QK_K / 16; j++) sumi += (int32_t)y[i].bsums[j] * (int32_t)mn[j / 2];
+        __m256i acc = _mm256_setzero_si256();
+        const __m256i lowmask = _mm256_set1_epi8(0xF);
+        for (int j = 0; j < QK_K / 64; j++) {
+            const __m256i q = pair_mod8(_mm256_loadu_si256((const __m256i *)(x[i].qs + 32 * j)));
+            const __m256i y0 = pair_mod8(_mm256_loadu_si256((const __m256i *)(y[i].qs + 64 * j)));
+            const __m256i y1 = pair_mod8(_mm256_loadu_si256((const __m256i *)(y[i].qs + 64 * j + 32)));
+            const __m256i lo = _mm256_and_si256(q, lowmask), hi = _mm256_and_si256(_mm256_srli_epi16(q, 4), lowmask);
+            acc = _mm256_add_epi32(acc, _mm256_mullo_epi32(dot32_mod8(lo, y0), _mm256_set1_epi32(sc[2 * j])));
+            acc = _mm256_add_epi32(acc, _mm256_mullo_epi32(dot32_mod8(hi, y1), _mm256_set1_epi32(sc[2 * j + 1])));
+        }
+        int32_t aux32[8];
+        _mm256_storeu_si256((__m256i *)aux32, acc);
+        float d = f16_to_f32(x[i].d) * y[i].d;
+        for (int l = 0; l < 8; l++) sums[l] += d * (float)aux32[l];
+        float dmin = f16_to_f32(x[i].dmin) * y[i].d;
+        sumf -= dmin * (float)sumi;
+    }
+    float s = 0.f;
+    for (int l = 0; l < 8; l++) s += sums[l];
+    return sumf + s;
+}
+
+static float vec_dot_q6_K_q8_K_avx2(size_t n, const block_q6_K *x, const block_q8_K *y)
+{
+    float sums[8] = {0};
+    for (size_t i = 0; i < n / QK_K; i++) {
+        __m256i acc = _mm256_setzero_si256();
+        const __m256i m4 = _mm256_set1_epi8(0xF), m2 = _mm256_set1_epi8(3), off = _mm256_set1_epi8(32);
+        for (int h = 0; h < 2; h++) {   /* 128 weights: four streams of 32 over ql[64], qh[32] */
+            const __m256i la = _mm256_loadu_si256((const __m256i *)(x[i].ql + 64 * h));
+            const __m256i lb = _mm256_loadu_si256((const __m256i *)(x[i].ql + 64 * h + 32));
+            const __m256i qh = _mm256_loadu_si256((const __m256i *)(x[i].qh + 32 * h));
+            __m256i q[4];
+            q[0] = _mm256_or_si256(_mm256_and_si256(la, m4), _mm256_slli_epi16(_mm256_and_si256(qh, m2), 4));
+            q[1] = _mm256_or_si256(_mm256_and_si256(lb, m4), _mm256_slli_epi16(_mm256_and_si256(_mm256_srli_epi16(qh, 2), m2), 4));
+            q[2] = _mm256_or_si256(_mm256_and_si256(_mm256_srli_epi16(la, 4), m4), _mm256_slli_epi16(_mm256_and_si256(_mm256_srli_epi16(qh, 4), m2), 4));
+            q[3] = _mm256_or_si256(_mm256_and_si256(_mm256_srli_epi16(lb, 4), m4), _mm256_slli_epi16(_mm256_and_si256(_mm256_srli_epi16(qh, 6), m2), 4));
+            for (int st = 0; st < 4; st++) {
+                /* 32 weights = two sub-blocks of 16 (one 128-bit half each).  (q - 32) * y as q * y - 32 * y: the
+                 * quants stay unsigned bytes (a Q8_K block always holds a -128, which no sign trick may negate) */
+                const __m256i a = pair_mod8(q[st]);
+                const __m256i yy = pair_mod8(_mm256_loadu_si256((const __m256i *)(y[i].qs + 128 * h + 32 * st)));
+                const __m256i p = _mm256_sub_epi16(_mm256_maddubs_epi16(a, yy), _mm256_maddubs_epi16(off, yy));
+                const int s0 = x[i].scales[8 * h + 2 * st], s1 = x[i].scales[8 * h + 2 * st + 1];
+                const __m256i p0 = _mm256_cvtepi16_epi32(_mm256_castsi256_si128(p));
+                const __m256i p1 = _mm256_cvtepi16_epi32(_mm256_extracti128_si256(p, 1));
+                acc = _mm256_add_epi32(acc, _mm256_mullo_epi32(p0, _mm256_set1_epi32(s0)));
+                acc = _mm256_add_epi32(acc, _mm256_mullo_epi32(p1, _mm256_set1_epi32(s1)));
+            }
+        }
+        int32_t aux32[8];
+        _mm256_storeu_si256((__m256i *)aux32, acc);
+        float d = f16_to_f32(x[i].d) * y[i].d;
+        for (int l = 0; l < 8; l++) sums[l] += (float)aux32[l] * d;
+    }
+    float s = 0.f;
+    for (int l = 0; l < 8; l++) s += sums[l];
+    return s;
+}
+
+static float vec_dot_q8_0_q8_0_avx2(size_t n, const block_q8_0 *x, const block_q8_0 *y)
+{
+    float sumf = 0.f;
+    const __m256i ones = _mm256_set1_epi16(1);
+    for (size_t i = 0; i < n / QK8_0; i++) {
+        const __m256i a = _mm256_loadu_si256((const __m256i *)x[i].qs), b = _mm256_loadu_si256((const __m256i *)y[i].qs);
+        const __m256i p = _mm256_madd_epi16(_mm256_maddubs_epi16(_mm256_abs_epi8(a), _mm256_sign_epi8(b, a)), ones);
+        __m128i s = _mm_add_epi32(_mm256_castsi256_si128(p), _mm256_extracti128_si256(p, 1));
+        s = _mm_add_epi32(s, _mm_shuffle_epi32(s, 0x4E));
+        s = _mm_add_epi32(s, _mm_shuffle_epi32(s, 0xB1));
+        const int32_t sumi = _mm_cvtsi128_si32(s);
+        sumf += (float)sumi * f16_to_f32(x[i].d) * f16_to_f32(y[i].d);
+    }
+    return sumf;
+}
+#else
+static int g_use_simd = 0;
+#endif
+
 /* ------------------------------------------------------------------ quantised mat-mul */
 
 /* candle k_quants::matmul: each activation row is quantised to the weight type's
@@ -947,6 +1062,19 @@ static void qact_free(qact *a) { free(a->blocks); a->blocks = NULL; }
 
 static inline float qdot(int dtype, const void *w, size_t row, size_t cols, const qact *a, size_t r)
 {
+#if defined(__AVX2__)
+    if (g_use_simd) {
+        if (dtype == PMO_Q4_K)
+            return vec_dot_q4_K_q8_K_avx2(cols, (const block_q4_K *)w + row * (cols / QK_K),
+                                          (const block_q8_K *)a->blocks + r * (cols / QK_K));
+        if (dtype == PMO_Q6_K)
+            return vec_dot_q6_K_q8_K_avx2(cols, (const block_q6_K *)w + row * (cols / QK_K),
+                                          (const block_q8_K *)a->blocks + r * (cols / QK_K));
+        if (dtype == PMO_Q8_0)
+            return vec_dot_q8_0_q8_0_avx2(cols, (const block_q8_0 *)w + row * (cols / QK8_0),
+                                          (const block_q8_0 *)a->blocks + r * (cols / QK8_0));
+    }
+#endif
     switch (dtype) {
     case PMO_Q4_K:
         return vec_dot_q4_K_q8_K(cols, (const block_q4_K *)w + row * (cols / QK_K),
@@ -1313,4 +1441,18 @@ void pmo_set_threads(int n)
 #endif
 }
 
-const char *pmo_simd_kind(void) { return "scalar (compiler-vectorised, portable vec_dot)"; }
+/* 1: AVX2 block dots for Q4_K / Q6_K / Q8_0 weights (the default where the build has AVX2), 0: the portable ones */
+void pmo_set_simd(int on)
+{
+#if defined(__AVX2__)
+    g_use_simd = on ? 1 : 0;
+#else
+    (void)on;
+#endif
+}
+
+const char *pmo_simd_kind(void)
+{
+    return g_use_simd ? "AVX2 integer block dots for Q4_K / Q6_K / Q8_0 (portable for the other types)"
+                      : "portable vec_dot (compiler-vectorised)";
+}

@@ -87,6 +87,7 @@ void pmo_rms_norm(const float *x, const float *weight, int n, int H, float eps, 
 
 int pmo_max_threads(void);
 void pmo_set_threads(int n);
+void pmo_set_simd(int on);   /* 0: the portable block dots everywhere (same bits, slower) */
 const char *pmo_simd_kind(void);
 
 #ifdef __cplusplus

@@ -78,6 +78,8 @@ def lib():
         L.pmo_set_threads.argtypes = [C.c_int]
         L.pmo_set_threads.restype = None
         L.pmo_simd_kind.restype = C.c_char_p
+        L.pmo_set_simd.argtypes = [C.c_int]
+        L.pmo_set_simd.restype = None
         _lib = L
     return _lib
 
@@ -96,6 +98,7 @@ def row_bytes(dtype, cols): return lib().pmo_row_bytes(dtype, cols)
 def max_threads(): return lib().pmo_max_threads()
 def set_threads(n): lib().pmo_set_threads(int(n))
 def simd_kind(): return lib().pmo_simd_kind().decode()
+def set_simd(on): lib().pmo_set_simd(1 if on else 0)
 
 
 def dequantize(dtype: int, blocks: np.ndarray, n_elems: int) -> np.ndarray:

@@ -183,3 +183,28 @@ def test_modify_block_scales(dtype):
         d0 = w.reshape(nb, ts)[:, o:o + 2].copy().view(np.float16).astype(np.float32)[:, 0]
         d1 = mod.reshape(nb, ts)[:, o:o + 2].copy().view(np.float16)[:, 0]
         assert np.array_equal(d1, (d0 * m).astype(np.float16))
+
+
+@pytest.mark.parametrize("dtype", [po.Q4_K, po.Q6_K, po.Q8_0])
+def test_simd_block_dots_equal_the_portable_ones_bit_for_bit(dtype):
+    rng = np.random.default_rng(17)
+    rows, cols, m = 48, 2048, 5
+    w = po.quantize(dtype, (rng.standard_normal(rows * cols) * 0.02).astype(np.float32))
+    raw = w.reshape(-1, po.type_size(dtype)).copy()
+    raw[3] = rng.integers(0, 256, raw.shape[1], dtype=np.uint8)     # arbitrary quants and sub-scales too
+    off = {po.Q4_K: (0, 2), po.Q6_K: (208,), po.Q8_0: (0,)}[dtype]
+    for o in off:
+        raw[3, o:o + 2] = np.array([0.01], np.float16).view(np.uint8)
+    w = raw.ravel()
+    x = (rng.standard_normal((m, cols)) * 3).astype(np.float32)
+    x[1, :300] = 0
+    try:
+        po.set_simd(True)
+        a = po.qmatmul(dtype, w, rows, cols, x)
+        assert "AVX2" in po.simd_kind()
+        po.set_simd(False)
+        b = po.qmatmul(dtype, w, rows, cols, x)
+        assert "portable" in po.simd_kind()
+    finally:
+        po.set_simd(True)
+    assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
