@@ -83,6 +83,14 @@ __device__ inline void tmem_ld16(uint32_t taddr, uint32_t (&v)[16])
 }
 __device__ inline void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
+// 16 bytes global -> shared without passing through registers; src_bytes = 0 writes zeros
+__device__ inline void cp_async16(void *smem_dst, const void *gmem_src, uint32_t src_bytes)
+{
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(smem_dst)), "l"(gmem_src), "r"(src_bytes) : "memory");
+}
+__device__ inline void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ inline void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
 // Shared-memory matrix descriptor, K-major, no swizzle: core matrices of 8 rows x 16 bytes;
 // lbo = bytes between the two 16-byte K chunks of one MMA, sbo = bytes between 8-row groups.
 __device__ inline uint64_t smem_desc(const void *p, uint32_t lbo, uint32_t sbo)
@@ -202,6 +210,10 @@ __global__ void __launch_bounds__(GU_THREADS, 2) k_gu_prefill(const GuArgs A)
 
     constexpr uint32_t IDESC_UU_S = make_idesc(2, 0, 1, PF_NT, PF_M);  // u8 x s8
     constexpr uint32_t IDESC_UU_U = make_idesc(2, 0, 0, PF_NT, PF_M);  // u8 x u8
+    // shared-memory descriptors of the operand tiles (the tiles do not move; a K slice is an address offset)
+    const uint64_t desc_a0 = smem_desc(S.a0, PF_M * 16, 128), desc_a1 = smem_desc(S.a1, PF_M * 16, 128);
+    const uint64_t desc_b = smem_desc(S.b, PF_NT * 16, 128), desc_am = smem_desc(S.am, PF_M * 16, 128);
+    const uint64_t desc_bh = smem_desc(S.bh, PF_NT * 16, 128), desc_bl = smem_desc(S.bl, PF_NT * 16, 128);
     constexpr int NC = PF_NT / 2;  // token columns this thread drains
     float acc[NC];
 #pragma unroll
@@ -302,16 +314,14 @@ __global__ void __launch_bounds__(GU_THREADS, 2) k_gu_prefill(const GuArgs A)
         // ---- MMAs of this block, issued by one thread
         if (tid == 0) {
             tc_fence_after();
-            for (int ks = 0; ks < 8; ks++) {  // 32 bytes of K per instruction
-                const uint64_t da0 = smem_desc(S.a0 + ks * 2 * (PF_M * 16), PF_M * 16, 128);
-                const uint64_t da1 = smem_desc(S.a1 + ks * 2 * (PF_M * 16), PF_M * 16, 128);
-                const uint64_t db = smem_desc(S.b + ks * 2 * (PF_NT * 16), PF_NT * 16, 128);
-                mma_i8(tmem + 0, da0, db, IDESC_UU_S, ks > 0);
-                mma_i8(tmem + 64, da1, db, IDESC_UU_S, ks > 0);
+#pragma unroll
+            for (int ks = 0; ks < 8; ks++) {  // 32 bytes of K per instruction: two 16-byte chunks further on per step
+                const uint64_t ka = (uint64_t)(ks * ((2 * PF_M * 16) >> 4)), kb = (uint64_t)(ks * ((2 * PF_NT * 16) >> 4));
+                mma_i8(tmem + 0, desc_a0 + ka, desc_b + kb, IDESC_UU_S, ks > 0);
+                mma_i8(tmem + 64, desc_a1 + ka, desc_b + kb, IDESC_UU_S, ks > 0);
             }
-            const uint64_t dam = smem_desc(S.am, PF_M * 16, 128);
-            mma_i8(tmem + 128, dam, smem_desc(S.bh, PF_NT * 16, 128), IDESC_UU_S, 0);
-            mma_i8(tmem + 192, dam, smem_desc(S.bl, PF_NT * 16, 128), IDESC_UU_U, 0);
+            mma_i8(tmem + 128, desc_am, desc_bh, IDESC_UU_S, 0);
+            mma_i8(tmem + 192, desc_am, desc_bl, IDESC_UU_U, 0);
             tc_commit(&S.bar);
         }
         if (b + 1 < nblk) {  // next block of this thread's row, in flight during the MMAs and the fold
@@ -461,6 +471,7 @@ __global__ void __launch_bounds__(GU_THREADS, 2) k_gu_prefill_q80(const GuArgs A
     const int rin_b = S.row_in[tk];
 
     constexpr uint32_t IDESC_SS = make_idesc(2, 1, 1, PF_NT, PF_M);  // s8 x s8 -> s32
+    const uint64_t desc_a = smem_desc(S.o.a, PF_M * 16, 128), desc_b = smem_desc(S.o.b, PF_NT * 16, 128);
     constexpr int NC = PF_NT / 2;
     float acc[NC];
 #pragma unroll
@@ -510,8 +521,8 @@ __global__ void __launch_bounds__(GU_THREADS, 2) k_gu_prefill_q80(const GuArgs A
             tc_fence_after();
 #pragma unroll
             for (int j = 0; j < 4; j++)   // one block = 32 bytes of K = one instruction, its own 64 columns
-                mma_i8(tmem + 64 * j, smem_desc(S.o.a + j * 2 * (PF_M * 16), PF_M * 16, 128),
-                       smem_desc(S.o.b + j * 2 * (PF_NT * 16), PF_NT * 16, 128), IDESC_SS, 0);
+                mma_i8(tmem + 64 * j, desc_a + (uint64_t)(j * ((2 * PF_M * 16) >> 4)), desc_b + (uint64_t)(j * ((2 * PF_NT * 16) >> 4)),
+                       IDESC_SS, 0);
             tc_commit(&S.bar);
         }
         if (s + 1 < steps) {   // the next step's blocks, in flight during the MMAs and the fold
@@ -594,7 +605,7 @@ struct DownArgs {
     DevStatus *status;
 };
 
-constexpr int DN_KSTEP = 128;
+constexpr int DN_KSTEP = 64;
 
 // 4 unsigned bytes -> 4 halves holding (byte - bias) * s
 __device__ inline void bytes_to_half4(uint32_t v, __half2 bias, __half2 s, uint32_t &o0, uint32_t &o1)
@@ -607,252 +618,303 @@ __device__ inline void bytes_to_half4(uint32_t v, __half2 bias, __half2 s, uint3
     o1 = *reinterpret_cast<const uint32_t *>(&h1);
 }
 
+// step(row, s, a_tile, r, part): weights 64 s .. 64 s + 63 of raw row `row` as fp16 into row r of the A tile
+// (core-matrix layout, K index inside the step); two threads share a row, `part` says which half of the work
 template <int DT> struct DownDequant;
 
-// Q6_K: K step s = half `s & 1` of block `s >> 1`
+// Q6_K: step s = quads 2 (s & 1), 2 (s & 1) + 1 of half (s >> 1) & 1 of block s >> 2.  In a half, quad q's weight l
+// (0..31) has its low nibble in ql[l + 32 (q & 1)] (the high nibble for q >= 2) and bits 2q, 2q+1 of qh[l].
 template <> struct DownDequant<PMOE_Q6_K> {
     static constexpr int ROW_BYTES = 2 * Q6_K_BYTES;  // F = 512
-    __device__ static inline void step(const uint8_t *row, int s, uint8_t *a_tile, int r)
+    __device__ static inline void step(const uint8_t *row, int s, uint8_t *a_tile, int r, int part)
     {
-        const uint8_t *blk = row + (s >> 1) * Q6_K_BYTES;
-        const int half = s & 1;
+        const uint8_t *blk = row + (s >> 2) * Q6_K_BYTES;
+        const int half = (s >> 1) & 1, qp = s & 1;
         const float d = half_bits_to_float(*reinterpret_cast<const uint16_t *>(blk + 208));
-        const int8_t *sc = reinterpret_cast<const int8_t *>(blk + 192 + 8 * half);
+        const int8_t *sc = reinterpret_cast<const int8_t *>(blk + 192 + 8 * half + 4 * qp);
         const __half2 bias = __floats2half2_rn(1056.f, 1056.f);  // 1024 + 32
 #pragma unroll
-        for (int l8 = 0; l8 < 4; l8++) {  // l = 8*l8 .. 8*l8+7
-            const uint32_t la0 = lds_u32_a2(blk + 64 * half + 8 * l8), la1 = lds_u32_a2(blk + 64 * half + 8 * l8 + 4);
-            const uint32_t lb0 = lds_u32_a2(blk + 64 * half + 32 + 8 * l8), lb1 = lds_u32_a2(blk + 64 * half + 32 + 8 * l8 + 4);
-            const uint32_t h0 = lds_u32_a2(blk + 128 + 32 * half + 8 * l8), h1 = lds_u32_a2(blk + 128 + 32 * half + 8 * l8 + 4);
+        for (int l8i = 0; l8i < 2; l8i++) {  // l = 8*l8 .. 8*l8+7
+            const int l8 = 2 * part + l8i;
+            const uint8_t *ql = blk + 64 * half + 8 * l8, *qh = blk + 128 + 32 * half + 8 * l8;
+            uint32_t la0 = lds_u32_a2(ql), la1 = lds_u32_a2(ql + 4), lb0 = lds_u32_a2(ql + 32), lb1 = lds_u32_a2(ql + 36);
+            uint32_t h0 = lds_u32_a2(qh), h1 = lds_u32_a2(qh + 4);
+            if (qp) { la0 >>= 4; la1 >>= 4; lb0 >>= 4; lb1 >>= 4; h0 >>= 2; h1 >>= 2; }
+            else { h0 <<= 2; h1 <<= 2; }
+            // now: quad 2qp+1 has its two high bits at bits 4,5 of h; quad 2qp two places lower
             const int is = l8 >> 1;  // l / 16
 #pragma unroll
-            for (int quad = 0; quad < 4; quad++) {
-                const float sf = d * (float)sc[is + 2 * quad];
+            for (int qq = 0; qq < 2; qq++) {
+                const float sf = d * (float)sc[is + 2 * qq];
                 const __half2 sh = __floats2half2_rn(sf, sf);
-                uint32_t va, vb;
-                if (quad == 0) { va = (la0 & 0x0F0F0F0Fu) | ((h0 << 4) & 0x30303030u); vb = (la1 & 0x0F0F0F0Fu) | ((h1 << 4) & 0x30303030u); }
-                else if (quad == 1) { va = (lb0 & 0x0F0F0F0Fu) | ((h0 << 2) & 0x30303030u); vb = (lb1 & 0x0F0F0F0Fu) | ((h1 << 2) & 0x30303030u); }
-                else if (quad == 2) { va = ((la0 >> 4) & 0x0F0F0F0Fu) | (h0 & 0x30303030u); vb = ((la1 >> 4) & 0x0F0F0F0Fu) | (h1 & 0x30303030u); }
-                else { va = ((lb0 >> 4) & 0x0F0F0F0Fu) | ((h0 >> 2) & 0x30303030u); vb = ((lb1 >> 4) & 0x0F0F0F0Fu) | ((h1 >> 2) & 0x30303030u); }
+                const uint32_t va = ((qq ? lb0 : la0) & 0x0F0F0F0Fu) | ((qq ? h0 : h0 << 2) & 0x30303030u);
+                const uint32_t vb = ((qq ? lb1 : la1) & 0x0F0F0F0Fu) | ((qq ? h1 : h1 << 2) & 0x30303030u);
                 uint4 o;
                 bytes_to_half4(va, bias, sh, o.x, o.y);
                 bytes_to_half4(vb, bias, sh, o.z, o.w);
-                // weights 32*quad + 8*l8 .. +7 of this half: K element index inside the step
-                const int kel = 32 * quad + 8 * l8;
-                *reinterpret_cast<uint4 *>(a_tile + core_off(PF_M, r, 2 * kel)) = o;
+                *reinterpret_cast<uint4 *>(a_tile + core_off(PF_M, r, 2 * (32 * qq + 8 * l8))) = o;
             }
         }
     }
 };
 
-// Q4_K: K step s = sub-blocks 4*(s&1) .. 4*(s&1)+3 of block s >> 1
+// Q4_K: step s = sub-blocks 2 (s & 3), 2 (s & 3) + 1 of block s >> 2: the low and the high nibbles of 32 bytes
 template <> struct DownDequant<PMOE_Q4_K> {
     static constexpr int ROW_BYTES = 2 * Q4_K_BYTES;
-    __device__ static inline void step(const uint8_t *row, int s, uint8_t *a_tile, int r)
+    __device__ static inline void step(const uint8_t *row, int s, uint8_t *a_tile, int r, int part)
     {
-        const uint8_t *blk = row + (s >> 1) * Q4_K_BYTES;
+        const uint8_t *blk = row + (s >> 2) * Q4_K_BYTES;
         const uint4 hdr = *reinterpret_cast<const uint4 *>(blk);
         const float d = half_bits_to_float((uint16_t)(hdr.x & 0xffffu));
         const float dmin = half_bits_to_float((uint16_t)(hdr.x >> 16));
         const uint32_t u0 = hdr.y, u1 = hdr.z, u2 = hdr.w;
-        const uint32_t sca = u0 & 0x3F3F3F3Fu, mna = u1 & 0x3F3F3F3Fu;
-        const uint32_t scb = (u2 & 0x0F0F0F0Fu) | ((u0 >> 2) & 0x30303030u);
-        const uint32_t mnb = ((u2 >> 4) & 0x0F0F0F0Fu) | ((u1 >> 2) & 0x30303030u);
-        const uint32_t scw = (s & 1) ? scb : sca, mnw = (s & 1) ? mnb : mna;
+        const int upper = (s >> 1) & 1, gq = s & 1;   // sub-blocks 4..7 keep their scales in the packed form
+        const uint32_t scw = upper ? (u2 & 0x0F0F0F0Fu) | ((u0 >> 2) & 0x30303030u) : u0 & 0x3F3F3F3Fu;
+        const uint32_t mnw = upper ? ((u2 >> 4) & 0x0F0F0F0Fu) | ((u1 >> 2) & 0x30303030u) : u1 & 0x3F3F3F3Fu;
+        // this thread: bytes 16 part .. 16 part + 15 of the 32 = weights 16 part .. + 15 of both sub-blocks
+        const uint4 q = *reinterpret_cast<const uint4 *>(blk + 16 + 64 * upper + 32 * gq + 16 * part);
+        const uint32_t w[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
-        for (int gq = 0; gq < 2; gq++) {  // 32 bytes of nibbles = sub-blocks 2*gq (low), 2*gq+1 (high) of this half
-            const uint4 qa = *reinterpret_cast<const uint4 *>(blk + 16 + 64 * (s & 1) + 32 * gq);
-            const uint4 qb = *reinterpret_cast<const uint4 *>(blk + 32 + 64 * (s & 1) + 32 * gq);
-            const uint32_t w[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+        for (int hi = 0; hi < 2; hi++) {
+            const int j = 2 * gq + hi;  // sub-block inside its group of four
+            const float sf = d * (float)((scw >> (8 * j)) & 0xFFu);
+            const float mf = dmin * (float)((mnw >> (8 * j)) & 0xFFu);
 #pragma unroll
-            for (int hi = 0; hi < 2; hi++) {
-                const int j = 2 * gq + hi;  // sub-block inside this half
-                const float sf = d * (float)((scw >> (8 * j)) & 0xFFu);
-                const float mf = dmin * (float)((mnw >> (8 * j)) & 0xFFu);
-#pragma unroll
-                for (int c = 0; c < 4; c++) {  // 8 weights per 16-byte chunk
-                    uint32_t o[4];
-#pragma unroll
-                    for (int i = 0; i < 2; i++) {
-                        const uint32_t v = hi ? (w[2 * c + i] >> 4) & 0x0F0F0F0Fu : w[2 * c + i] & 0x0F0F0F0Fu;
-                        const __half2 a = __floats2half2_rn(fmaf(sf, (float)(v & 0xFF), -mf), fmaf(sf, (float)((v >> 8) & 0xFF), -mf));
-                        const __half2 bq = __floats2half2_rn(fmaf(sf, (float)((v >> 16) & 0xFF), -mf), fmaf(sf, (float)(v >> 24), -mf));
-                        o[2 * i] = *reinterpret_cast<const uint32_t *>(&a);
-                        o[2 * i + 1] = *reinterpret_cast<const uint32_t *>(&bq);
-                    }
-                    const int kel = 32 * j + 8 * c;
-                    *reinterpret_cast<uint4 *>(a_tile + core_off(PF_M, r, 2 * kel)) = make_uint4(o[0], o[1], o[2], o[3]);
-                }
-            }
-        }
-    }
-};
-
-// Q8_0: K step s = blocks 4 s .. 4 s + 3 of the row (F = 512: 16 blocks of 34 bytes)
-template <> struct DownDequant<PMOE_Q8_0> {
-    static constexpr int ROW_BYTES = 16 * Q8_0_BYTES;
-    __device__ static inline void step(const uint8_t *row, int s, uint8_t *a_tile, int r)
-    {
-#pragma unroll
-        for (int j = 0; j < 4; j++) {
-            const uint8_t *blk = row + (4 * s + j) * Q8_0_BYTES;   // 2-byte aligned
-            const __half d = __ushort_as_half(*reinterpret_cast<const uint16_t *>(blk));
-            const __half2 d2 = __halves2half2(d, d);
-#pragma unroll
-            for (int c = 0; c < 4; c++) {   // 8 weights per 16-byte chunk
+            for (int ci = 0; ci < 2; ci++) {  // 8 weights per 16-byte chunk
                 uint32_t o[4];
 #pragma unroll
                 for (int i = 0; i < 2; i++) {
-                    const uint32_t v = lds_u32_a2(blk + 2 + 8 * c + 4 * i);
-                    // 0x6400 | (b ^ 0x80) is the fp16 number 1024 + 128 + q for the signed byte q
-                    const uint32_t u = v ^ 0x80808080u;
-                    const uint32_t p0 = __byte_perm(u, 0x64646464u, 0x4140), p1 = __byte_perm(u, 0x64646464u, 0x4342);
-                    const __half2 bias = __floats2half2_rn(1152.f, 1152.f);
-                    const __half2 h0 = __hmul2(__hsub2(*reinterpret_cast<const __half2 *>(&p0), bias), d2);
-                    const __half2 h1 = __hmul2(__hsub2(*reinterpret_cast<const __half2 *>(&p1), bias), d2);
-                    o[2 * i] = *reinterpret_cast<const uint32_t *>(&h0);
-                    o[2 * i + 1] = *reinterpret_cast<const uint32_t *>(&h1);
+                    const uint32_t v = hi ? (w[2 * ci + i] >> 4) & 0x0F0F0F0Fu : w[2 * ci + i] & 0x0F0F0F0Fu;
+                    const __half2 a = __floats2half2_rn(fmaf(sf, (float)(v & 0xFF), -mf), fmaf(sf, (float)((v >> 8) & 0xFF), -mf));
+                    const __half2 bq = __floats2half2_rn(fmaf(sf, (float)((v >> 16) & 0xFF), -mf), fmaf(sf, (float)(v >> 24), -mf));
+                    o[2 * i] = *reinterpret_cast<const uint32_t *>(&a);
+                    o[2 * i + 1] = *reinterpret_cast<const uint32_t *>(&bq);
                 }
-                const int kel = 32 * j + 8 * c;
+                const int kel = 32 * hi + 16 * part + 8 * ci;
                 *reinterpret_cast<uint4 *>(a_tile + core_off(PF_M, r, 2 * kel)) = make_uint4(o[0], o[1], o[2], o[3]);
             }
         }
     }
 };
 
+// Q8_0: step s = blocks 2 s, 2 s + 1 of the row (F = 512: 16 blocks of 34 bytes), one per thread of the pair
+template <> struct DownDequant<PMOE_Q8_0> {
+    static constexpr int ROW_BYTES = 16 * Q8_0_BYTES;
+    __device__ static inline void step(const uint8_t *row, int s, uint8_t *a_tile, int r, int part)
+    {
+        const uint8_t *blk = row + (2 * s + part) * Q8_0_BYTES;   // 2-byte aligned
+        const __half d = __ushort_as_half(*reinterpret_cast<const uint16_t *>(blk));
+        const __half2 d2 = __halves2half2(d, d);
+        const __half2 bias = __floats2half2_rn(1152.f, 1152.f);
+#pragma unroll
+        for (int c = 0; c < 4; c++) {   // 8 weights per 16-byte chunk
+            uint4 o;
+            // 0x6400 | (b ^ 0x80) is the fp16 number 1024 + 128 + q for the signed byte q
+            bytes_to_half4(lds_u32_a2(blk + 2 + 8 * c) ^ 0x80808080u, bias, d2, o.x, o.y);
+            bytes_to_half4(lds_u32_a2(blk + 6 + 8 * c) ^ 0x80808080u, bias, d2, o.z, o.w);
+            *reinterpret_cast<uint4 *>(a_tile + core_off(PF_M, r, 2 * (32 * part + 8 * c))) = o;
+        }
+    }
+};
+
+// A CTA takes one block of 128 output rows and up to DN_TILES consecutive entries of the tile table (token tiles of
+// 64).  Entries of the same expert form a run: the run's raw GGUF rows arrive with one bulk copy, every K step
+// dequantises them ONCE (two threads per row) and feeds all the run's token tiles, each with its own 64 columns of
+// f32 in tensor memory -- a hot expert's weights are not decoded once per token tile.  The B tiles go through a ring
+// of buffers filled by cp.async ahead of their use, straight into the core-matrix layout.  Two CTAs share an SM
+// (half of tensor memory and of shared memory each), so that one's copies, dequantisation and drain overlap the
+// other's MMAs.
+constexpr int DN_THREADS = 256;
+constexpr int DN_TILES = 4;      // 4 x 64 columns = half of tensor memory
+constexpr int DN_COLS = 64 * DN_TILES;
+
+template <int DT> struct DownCfg {
+    // Q8_0 rows are the widest: three B buffers filled one piece ahead; the others take four, two ahead
+    static constexpr int NB = DT == PMOE_Q8_0 ? 3 : 4;
+    static constexpr int AHEAD = NB - 2;
+};
+
 struct DownSmemHdr {
-    float scale[PF_NT];
-    int row_in[PF_NT];
-    uint64_t bar_raw, bar_mma;
+    float scale[DN_TILES][PF_NT];
+    int row_in[DN_TILES][PF_NT];
+    int2 entry[DN_TILES];          // (slot or -1 for the shared expert, tile inside the expert)
+    uint64_t bar_raw, bar_b[4];
     uint32_t tmem_base;
-    int slot, tile_in_slot;
+    int n_entries;
 };
 
 template <int DT>
-__global__ void __launch_bounds__(PF_THREADS, 2) k_down_prefill(const DownArgs A)
+__global__ void __launch_bounds__(DN_THREADS, 2) k_down_prefill(const DownArgs A)
 {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     using DQ = DownDequant<DT>;
+    constexpr int NB = DownCfg<DT>::NB, AHEAD = DownCfg<DT>::AHEAD;
     constexpr int RAW_BYTES = PF_M * DQ::ROW_BYTES;
-    uint8_t *a_tile = smem_raw;                                  // [128 rows][128 K] fp16, core-matrix layout
-    uint8_t *b_tile = a_tile + PF_M * DN_KSTEP * 2;              // [64 tokens][128 K] fp16
-    uint8_t *raw = b_tile + PF_NT * DN_KSTEP * 2;                // the tile's GGUF rows
+    constexpr int B_BYTES = PF_NT * DN_KSTEP * 2;
+    uint8_t *a_tile = smem_raw;                                  // [128 rows][64 K] fp16, core-matrix layout
+    uint8_t *b_tile = a_tile + PF_M * DN_KSTEP * 2;              // NB x [64 tokens][64 K] fp16
+    uint8_t *raw = b_tile + NB * B_BYTES;                        // the run's GGUF rows
     DownSmemHdr &S = *reinterpret_cast<DownSmemHdr *>(raw + ((RAW_BYTES + 127) / 128) * 128);
-    const int tid = threadIdx.x, warp = tid >> 5;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
     const int n_active = A.routed ? *A.g.n_active : 0;
     const int routed_tiles = n_active ? A.tile_prefix[n_active] : 0;
     const int shared_tiles = A.has_shared ? (A.sh_count + PF_NT - 1) / PF_NT : 0;
-    const int tile = blockIdx.y;
-    if (tile >= routed_tiles + shared_tiles) return;
+    const int first = blockIdx.y * DN_TILES;
+    if (first >= routed_tiles + shared_tiles) return;
+    if (tid < DN_TILES) {
+        const int tile = first + tid;
+        int2 e = make_int2(-2, 0);
+        if (tile < routed_tiles) e = A.g.tile_table[tile];
+        else if (tile < routed_tiles + shared_tiles) e = make_int2(-1, tile - routed_tiles);
+        S.entry[tid] = e;
+    }
     if (tid == 0) {
-        if (tile < routed_tiles) {
-            const int2 ti = A.g.tile_table[tile];
-            S.slot = ti.x;
-            S.tile_in_slot = ti.y;
-        } else {
-            S.slot = -1;
-            S.tile_in_slot = tile - routed_tiles;
-        }
+        const int left = routed_tiles + shared_tiles - first;
+        S.n_entries = left < DN_TILES ? left : DN_TILES;
         mbar_init(&S.bar_raw, 1);
-        mbar_init(&S.bar_mma, 1);
+        for (int i = 0; i < NB; i++) mbar_init(&S.bar_b[i], 1);
         fence_mbar_init();
     }
-    if (warp == 0) tmem_alloc(&S.tmem_base, 64);
+    if (warp == 0) tmem_alloc(&S.tmem_base, DN_COLS);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = S.tmem_base;
-    const int slot = S.slot, t0 = S.tile_in_slot * PF_NT;
-    const bool is_shared = slot < 0;
-    int m;
-    const int *list = nullptr;
-    const uint8_t *wd;
-    if (is_shared) {
-        m = A.sh_count;
-        wd = A.sdown;
-    } else {
-        const int e = slot;
-        m = A.g.count[e];
-        list = A.g.pairs + A.g.offset[e];
-        wd = A.down + (size_t)e * A.expert_bytes;
-    }
+    const int n_entries = S.n_entries;
     const int h0 = blockIdx.x * PF_M;
-    if (tid == 0) {  // the tile's raw rows: one contiguous run
-        mbar_expect_tx(&S.bar_raw, RAW_BYTES);
-        const uint8_t *src = wd + (size_t)h0 * DQ::ROW_BYTES;
-        for (int off = 0; off < RAW_BYTES; off += 16384)
-            bulk_g2s(raw + off, src + off, RAW_BYTES - off < 16384 ? RAW_BYTES - off : 16384, &S.bar_raw);
-    }
-    const int cnt = m - t0 < PF_NT ? m - t0 : PF_NT;
-    if (tid < PF_NT) {
-        int rin = -1;
-        float sc = 0.f;
-        if (tid < cnt) {
-            if (is_shared) { rin = A.n * A.top_k + A.sh_begin + t0 + tid; sc = A.scale_s[A.sh_begin + t0 + tid]; }
-            else { rin = list[t0 + tid]; sc = A.scale_r[rin]; }
-            sc *= A.act_h_scale[rin];
-        }
-        S.row_in[tid] = rin;
-        S.scale[tid] = sc;
-    }
-    __syncthreads();
-    bool ok = mbar_wait(&S.bar_raw, 0);
-    if (!ok) set_status(A.status, PMOE_ERR_TIMEOUT, 31, tile);
-
     constexpr uint32_t IDESC = make_idesc(1, 0, 0, PF_NT, PF_M);  // f16 x f16 -> f32
     const int steps = A.F / DN_KSTEP;
-    uint32_t phase = 0;
-    for (int s = 0; s < steps && ok; s++) {
-        DQ::step(raw + (size_t)tid * DQ::ROW_BYTES, s, a_tile, tid);
-        {   // activations: token = tid / 2, 64 halves each
-            const int tk = tid >> 1, half = tid & 1;
-            const int rin = S.row_in[tk];
-            const uint4 *src = rin >= 0 ? reinterpret_cast<const uint4 *>(A.act_h + (size_t)rin * A.F + s * DN_KSTEP + 64 * half)
-                                        : nullptr;
-#pragma unroll
-            for (int i = 0; i < 8; i++) {
-                const uint4 v = src ? src[i] : make_uint4(0, 0, 0, 0);
-                *reinterpret_cast<uint4 *>(b_tile + core_off(PF_NT, tk, 2 * (64 * half + 8 * i))) = v;
+    const int r = tid & (PF_M - 1), part = tid >> 7;               // dequantisation: row and half of the step
+    const int tk = tid >> 2, quarter = tid & 3;                    // B side: 16 halves of one token per thread
+    const uint64_t desc_a0 = smem_desc(a_tile, PF_M * 16, 128), desc_b0 = smem_desc(b_tile, PF_NT * 16, 128);
+
+    // MMA commits are counted over the CTA's life: commit c lands on barrier c % NB as its (c / NB)-th completion
+    int committed = 0, seen = 0;
+    uint32_t ph_raw = 0;
+    bool ok = true;
+    // waits until the first `upto` commits (the MMAs they cover and everything issued before) have finished
+    auto wait_mma = [&](int upto) {
+        for (; seen < upto; seen++)
+            if (ok && !mbar_wait_spin(&S.bar_b[seen % NB], (uint32_t)((seen / NB) & 1))) {
+                set_status(A.status, PMOE_ERR_TIMEOUT, 32, seen);
+                ok = false;
             }
+    };
+
+    for (int e0 = 0; e0 < n_entries && ok;) {
+        const int slot = S.entry[e0].x;
+        int e1 = e0 + 1;
+        while (e1 < n_entries && S.entry[e1].x == slot) e1++;
+        const int T = e1 - e0;                                     // token tiles of this run
+        const bool is_shared = slot < 0;
+        int m;
+        const int *list = nullptr;
+        const uint8_t *wd;
+        if (is_shared) {
+            m = A.sh_count;
+            wd = A.sdown;
+        } else {
+            m = A.g.count[slot];
+            list = A.g.pairs + A.g.offset[slot];
+            wd = A.down + (size_t)slot * A.expert_bytes;
         }
-        fence_proxy_async();
-        tc_fence_before();
+        if (tid == 0) {   // the run's raw rows: one contiguous range
+            mbar_expect_tx(&S.bar_raw, RAW_BYTES);
+            const uint8_t *src = wd + (size_t)h0 * DQ::ROW_BYTES;
+            for (int off = 0; off < RAW_BYTES; off += 16384)
+                bulk_g2s(raw + off, src + off, RAW_BYTES - off < 16384 ? RAW_BYTES - off : 16384, &S.bar_raw);
+        }
+        for (int i = tid; i < T * PF_NT; i += DN_THREADS) {
+            const int t = i / PF_NT, j = i % PF_NT;
+            const int tok = S.entry[e0 + t].y * PF_NT + j;
+            int rin = -1;
+            float sc = 0.f;
+            if (tok < m) {
+                if (is_shared) { rin = A.n * A.top_k + A.sh_begin + tok; sc = A.scale_s[A.sh_begin + tok]; }
+                else { rin = list[tok]; sc = A.scale_r[rin]; }
+                sc *= A.act_h_scale[rin];
+            }
+            S.row_in[t][j] = rin;
+            S.scale[t][j] = sc;
+        }
         __syncthreads();
-        if (tid == 0) {
-            tc_fence_after();
-            for (int ks = 0; ks < DN_KSTEP / 16; ks++) {  // 16 halves = 32 bytes of K per instruction
-                const uint64_t da = smem_desc(a_tile + ks * 2 * (PF_M * 16), PF_M * 16, 128);
-                const uint64_t db = smem_desc(b_tile + ks * 2 * (PF_NT * 16), PF_NT * 16, 128);
-                mma_f16(tmem, da, db, IDESC, (s > 0 || ks > 0) ? 1u : 0u);
+
+        // B pieces are numbered i = s * T + t; piece i is the CTA's commit base + i and sits in that commit's buffer
+        const int pieces = steps * T, base = committed;
+        auto fetch_b = [&](int i) {
+            if (i < pieces) {
+                const int s = i / T, t = i - s * T;
+                wait_mma(base + i - NB + 1);   // the MMAs that read this buffer NB pieces ago
+                const int rin = S.row_in[t][tk];
+                const __half *src = A.act_h + (size_t)(rin >= 0 ? rin : 0) * A.F + s * DN_KSTEP + 16 * quarter;
+                uint8_t *bt = b_tile + ((base + i) % NB) * B_BYTES;
+#pragma unroll
+                for (int c = 0; c < 2; c++)
+                    cp_async16(bt + core_off(PF_NT, tk, 2 * (16 * quarter + 8 * c)), src + 8 * c, rin >= 0 ? 16u : 0u);
             }
-            tc_commit(&S.bar_mma);
-        }
-        if (!mbar_wait_spin(&S.bar_mma, phase)) {
-            set_status(A.status, PMOE_ERR_TIMEOUT, 32, s);
+            cp_async_commit();   // one group per piece, empty past the end, so that the counts below stay fixed
+        };
+#pragma unroll
+        for (int i = 0; i < AHEAD; i++) fetch_b(i);
+        if (!mbar_wait(&S.bar_raw, ph_raw)) {
+            set_status(A.status, PMOE_ERR_TIMEOUT, 31, e0);
             ok = false;
         }
-        phase ^= 1;
-        tc_fence_after();
-        __syncthreads();  // operand tiles may be overwritten
-    }
-    if (ok) {
-        const uint32_t lane_addr = tmem + ((uint32_t)(warp * 32) << 16);
+        ph_raw ^= 1;
+        for (int s = 0, i = 0; s < steps && ok; s++) {
+            wait_mma(base + i);   // the previous step's MMAs still read the A tile
+            tc_fence_after();
+            DQ::step(raw + (size_t)r * DQ::ROW_BYTES, s, a_tile, r, part);
+            for (int t = 0; t < T && ok; t++, i++) {
+                fetch_b(i + AHEAD);
+                cp_async_wait<AHEAD>();   // this thread's copies of piece i have landed
+                const int buf = (base + i) % NB;
+                fence_proxy_async();
+                tc_fence_before();
+                __syncthreads();
+                if (tid == 0) {
+                    tc_fence_after();
+                    // a K slice of 16 halves is two 16-byte chunks further on: the descriptor's address field moves with it
+                    const uint64_t db0 = desc_b0 + (uint64_t)((buf * B_BYTES) >> 4);
 #pragma unroll
-        for (int cc = 0; cc < PF_NT / 16; cc++) {
-            uint32_t v[16];
-            tmem_ld16(lane_addr + cc * 16, v);
-            tmem_ld_wait();
-#pragma unroll
-            for (int j = 0; j < 16; j++) {
-                const int rout = S.row_in[cc * 16 + j];
-                if (rout >= 0) A.partial[(size_t)rout * A.H + h0 + tid] = __uint_as_float(v[j]) * S.scale[cc * 16 + j];
+                    for (int ks = 0; ks < DN_KSTEP / 16; ks++)   // 16 halves = 32 bytes of K per instruction
+                        mma_f16(tmem + 64 * t, desc_a0 + (uint64_t)(ks * ((2 * PF_M * 16) >> 4)),
+                                db0 + (uint64_t)(ks * ((2 * PF_NT * 16) >> 4)), IDESC, (s > 0 || ks > 0) ? 1u : 0u);
+                    tc_commit(&S.bar_b[buf]);
+                }
+                committed++;
             }
         }
+        cp_async_wait<0>();
+        wait_mma(committed);
+        tc_fence_after();
+        if (ok) {
+            // row (32 * (warp & 3) + lane) of the block: a warp reaches the 32 lanes of its quarter; the two warps
+            // of a quarter split the run's tiles
+            const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16);
+            const int row = h0 + (warp & 3) * 32 + lane;
+            for (int t = warp >> 2; t < T; t += 2) {
+#pragma unroll
+                for (int cc = 0; cc < PF_NT / 16; cc++) {
+                    uint32_t v[16];
+                    tmem_ld16(lane_addr + 64 * t + cc * 16, v);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 16; j++) {
+                        const int rout = S.row_in[t][cc * 16 + j];
+                        if (rout >= 0) A.partial[(size_t)rout * A.H + row] = __uint_as_float(v[j]) * S.scale[t][cc * 16 + j];
+                    }
+                }
+            }
+        }
+        tc_fence_before();
+        __syncthreads();   // accumulators, tiles and tables are free for the next run
+        tc_fence_after();
+        e0 = e1;
     }
-    tc_fence_before();
     __syncthreads();
-    if (warp == 0) tmem_dealloc(tmem, 64);
+    if (warp == 0) tmem_dealloc(tmem, DN_COLS);
 }
 
 // Quantisation of an activated row the way the row's down matrix wants it (Q8_K for K-quants, Q8_0 for Q8_0:
@@ -998,15 +1060,16 @@ bool prefill_down_supported(const LayerDev &L, bool routed, bool shared)
 template <int DT>
 static cudaError_t launch_down_t(const DownArgs &A, dim3 grid, cudaStream_t s)
 {
-    constexpr size_t smem = PF_M * DN_KSTEP * 2 + PF_NT * DN_KSTEP * 2 + ((PF_M * DownDequant<DT>::ROW_BYTES + 127) / 128) * 128 +
-                            sizeof(DownSmemHdr) + 128;
+    constexpr size_t smem = PF_M * DN_KSTEP * 2 + DownCfg<DT>::NB * PF_NT * DN_KSTEP * 2 +
+                            ((PF_M * DownDequant<DT>::ROW_BYTES + 127) / 128) * 128 + sizeof(DownSmemHdr) + 128;
+    static_assert(smem <= 115712, "two CTAs of the down GEMM share an SM");
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(k_down_prefill<DT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
         configured = true;
     }
-    k_down_prefill<DT><<<grid, PF_THREADS, smem, s>>>(A);
+    k_down_prefill<DT><<<grid, DN_THREADS, smem, s>>>(A);
     count_launch();
     return cudaGetLastError();
 }
@@ -1030,7 +1093,7 @@ static cudaError_t launch_down_gemm(const LayerDev &L, const Workspace &ws, cons
     A.partial = ws.partial;
     A.status = ws.status;
     const int tiles = (routed ? max_routed_tiles(L, n, top_k) : 0) + (shared ? (ws.sh_count + PF_NT - 1) / PF_NT : 0);
-    dim3 grid(L.H / PF_M, tiles);
+    dim3 grid(L.H / PF_M, (tiles + DN_TILES - 1) / DN_TILES);
     const int dt = routed ? L.down_dtype : L.sh_down_dtype;
     if (dt == PMOE_Q6_K) return launch_down_t<PMOE_Q6_K>(A, grid, s);
     if (dt == PMOE_Q8_0) return launch_down_t<PMOE_Q8_0>(A, grid, s);
