@@ -870,10 +870,13 @@ __global__ void __launch_bounds__(DN_THREADS, 2) k_down_prefill(const DownArgs A
                 fetch_b(i + AHEAD);
                 cp_async_wait<AHEAD>();   // this thread's copies of piece i have landed
                 const int buf = (base + i) % NB;
-                fence_proxy_async();
                 tc_fence_before();
                 __syncthreads();
                 if (tid == 0) {
+                    // everyone's stores and copies are complete and ordered before the barrier; the issuing thread
+                    // alone crosses over to the async proxy (a proxy fence in a thread with cp.async copies still in
+                    // flight waits for them, which would put the ring's look-ahead on the critical path)
+                    fence_proxy_async();
                     tc_fence_after();
                     // a K slice of 16 halves is two 16-byte chunks further on: the descriptor's address field moves with it
                     const uint64_t db0 = desc_b0 + (uint64_t)((buf * B_BYTES) >> 4);
