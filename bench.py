@@ -799,7 +799,7 @@ def pmoe_arm(args):
         dist.destroy_process_group()
 
 
-NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = (435.576064 + 6.948864) / 429.555712   # gate/up launch at batch 64, 362 experts hit
+NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = (435.556352 + 8.189952) / 429.555712   # gate/up launch at batch 64, 362 experts hit
 
 
 def main():
