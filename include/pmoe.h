@@ -93,7 +93,10 @@ typedef struct {
     const void *sh_gate, *sh_up, *sh_down;
     const float *sh_gate_inp;
 
-    int32_t router_dtype;     /* PMOE_F32, or PMOE_F16 / PMOE_BF16 (widened to f32 at create) */
+    int32_t router_dtype;     /* PMOE_F32, PMOE_F16 / PMOE_BF16 (widened to f32 at create), or a GGUF block type
+                                 (Q8_0, Q2_K ... Q6_K; [E, H / block] blocks): the router is then a quantised
+                                 mat-mul like the experts' (models/with_tracing.rs:324-335), rows quantised to
+                                 Q8_K / Q8_0, integer block dots, f32 scales */
     const void *router_w;
     const float *router_bias; /* [E] added to the logits, or NULL (not in the reference;
                                  used to skew synthetic routing) */

@@ -1327,6 +1327,21 @@ int pmo_shared_forward(const pmo_layer *L, const float *x, int n, float *out)
     return rc;
 }
 
+/* gate.forward (qwen3_next.rs:1916-1918).  ffn_gate_inp is a QMatMul (models/with_tracing.rs:324-335): held as f32 it
+   is the canonical-order GEMV; held quantised it takes the same CPU route as the expert matrices -- rows quantised to
+   Q8_K / Q8_0, integer block dots (candle k_quants::matmul). */
+int pmo_layer_router_logits(const pmo_layer *L, const float *x, int n, float *logits)
+{
+    if (L->router_dtype == PMO_F32 || !L->router_q) {
+        pmo_router_logits(L->router_w, L->router_bias, L->E, L->H, x, n, logits);
+        return 0;
+    }
+    int rc = pmo_qmatmul(L->router_dtype, L->router_q, (size_t)L->E, (size_t)L->H, x, (size_t)n, logits);
+    if (!rc && L->router_bias)
+        for (size_t i = 0; i < (size_t)n * L->E; i++) logits[i] += L->router_bias[i % L->E];
+    return rc;
+}
+
 /* MoeBlock::forward_with_stats (qwen3_next.rs:1903-1940): returns the unclamped logits */
 int pmo_moe_forward(const pmo_layer *L, const float *x, int n, float *out,
                     float *logits_out, uint32_t *idx_out, float *w_out)
@@ -1335,9 +1350,9 @@ int pmo_moe_forward(const pmo_layer *L, const float *x, int n, float *out,
     float *logits = logits_out ? logits_out : (float *)malloc(sizeof(float) * (size_t)n * E);
     uint32_t *idx = idx_out ? idx_out : (uint32_t *)malloc(sizeof(uint32_t) * (size_t)n * k);
     float *w = w_out ? w_out : (float *)malloc(sizeof(float) * (size_t)n * k);
-    pmo_router_logits(L->router_w, L->router_bias, E, H, x, n, logits);
+    int rc = pmo_layer_router_logits(L, x, n, logits);
     pmo_route_topk(logits, n, E, k, idx, w, NULL);
-    int rc = pmo_experts_forward(L, x, n, idx, w, k, out);
+    if (!rc) rc = pmo_experts_forward(L, x, n, idx, w, k, out);
     if (!rc && L->has_shared) {
         float *sh = (float *)malloc(sizeof(float) * (size_t)n * H);
         rc = pmo_shared_forward(L, x, n, sh);

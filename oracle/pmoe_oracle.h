@@ -43,6 +43,8 @@ typedef struct {
     const float *sh_gate_inp;     /* [H] f32 */
     const float *router_w;        /* [E,H] f32 */
     const float *router_bias;     /* [E] f32 or NULL; synthetic-workload knob, added to the logits */
+    int32_t router_dtype;         /* PMO_F32 (router_w), or a block type: the router is a quantised mat-mul over router_q */
+    const void *router_q;         /* [E, H / block] blocks when router_dtype is a block type */
 } pmo_layer;
 
 size_t pmo_block_size(int dtype);      /* weights per block */
@@ -64,6 +66,8 @@ void pmo_quantize_q8_0_act(const float *x, size_t n, uint16_t *d_f16, int8_t *qs
 /* y[m,rows] = x[m,cols] * W[rows,cols]^T with W quantised (candle k_quants::matmul) */
 int pmo_qmatmul(int dtype, const void *w, size_t rows, size_t cols, const float *x, size_t m, float *y);
 
+/* the layer's router, f32 or quantised (a QMatMul like the experts': models/with_tracing.rs:324-335): unclamped logits */
+int pmo_layer_router_logits(const pmo_layer *L, const float *x, int n, float *logits);
 /* router: canonical-order f32 GEMV + optional bias; unclamped logits out */
 void pmo_router_logits(const float *router_w, const float *bias, int E, int H, const float *x, int n, float *logits);
 /* clamp(+-100) -> softmax -> first k of a stable descending sort -> renormalise */

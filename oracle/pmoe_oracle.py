@@ -42,6 +42,7 @@ class _Layer(C.Structure):
         ("sh_gate_dtype", C.c_int32), ("sh_up_dtype", C.c_int32), ("sh_down_dtype", C.c_int32),
         ("sh_gate", C.c_void_p), ("sh_up", C.c_void_p), ("sh_down", C.c_void_p),
         ("sh_gate_inp", C.c_void_p), ("router_w", C.c_void_p), ("router_bias", C.c_void_p),
+        ("router_dtype", C.c_int32), ("router_q", C.c_void_p),
     ]
 
 
@@ -67,6 +68,8 @@ def lib():
         L.pmo_qmatmul.argtypes = [C.c_int, C.c_void_p, C.c_size_t, C.c_size_t, C.c_void_p, C.c_size_t, C.c_void_p]
         L.pmo_router_logits.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_void_p]
         L.pmo_router_logits.restype = None
+        L.pmo_layer_router_logits.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]
+        L.pmo_layer_router_logits.restype = C.c_int
         L.pmo_route_topk.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]
         L.pmo_route_topk.restype = None
         L.pmo_experts_forward.argtypes = [C.POINTER(_Layer), C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]
@@ -168,7 +171,7 @@ class Layer:
     """Host copy of one MoE block's tensors (numpy arrays of raw GGUF block bytes)."""
 
     def __init__(self, H, F, E, k, gate, up, down, gate_dtype, up_dtype, down_dtype, router_w,
-                 shared=None, router_bias=None):
+                 shared=None, router_bias=None, router_dtype=0, router_q=None):
         self.H, self.F, self.E, self.k = H, F, E, k
         self.gate, self.up, self.down = (_c(a, np.uint8) for a in (gate, up, down))
         self.gate_dtype, self.up_dtype, self.down_dtype = gate_dtype, up_dtype, down_dtype
@@ -192,13 +195,20 @@ class Layer:
             s.sh_gate_inp = self.shared["gate_inp"].ctypes.data
         s.router_w = self.router_w.ctypes.data
         s.router_bias = None if self.router_bias is None else self.router_bias.ctypes.data
+        # a quantised router: raw blocks [E, H / block] of type router_dtype (router_w stays as the f32 it was made from)
+        self.router_dtype = int(router_dtype)
+        self.router_q = None if router_q is None else _c(router_q, np.uint8)
+        s.router_dtype = self.router_dtype if self.router_q is not None else 0
+        s.router_q = None if self.router_q is None else self.router_q.ctypes.data
         self._s = s
 
     # -- pieces -----------------------------------------------------------------
     def router_logits(self, x):
         x = _c(x, np.float32).reshape(-1, self.H)
         out = np.empty((x.shape[0], self.E), np.float32)
-        lib().pmo_router_logits(_p(self.router_w), _p(self.router_bias), self.E, self.H, _p(x), x.shape[0], _p(out))
+        rc = lib().pmo_layer_router_logits(C.byref(self._s), _p(x), x.shape[0], _p(out))
+        if rc:
+            raise RuntimeError(f"pmo_layer_router_logits failed ({rc})")
         return out
 
     def route_topk(self, logits, with_probs=False):

@@ -279,8 +279,11 @@ int pmoe_layer_create(const pmoe_layer_desc *desc, pmoe_layer **out)
     if (d.gate_dtype != d.up_dtype)
         return fail(PMOE_ERR_UNSUPPORTED_DTYPE, "gate and up experts must share one dtype (got %d and %d)", d.gate_dtype,
                     d.up_dtype);
-    if (d.router_dtype != PMOE_F32 && d.router_dtype != PMOE_F16 && d.router_dtype != PMOE_BF16)
-        return fail(PMOE_ERR_UNSUPPORTED_DTYPE, "router weights must be F32, F16 or BF16 (got %d)", d.router_dtype);
+    const bool router_quantised = dtype_known(d.router_dtype) && block_elems(d.router_dtype) > 1;
+    if (d.router_dtype != PMOE_F32 && d.router_dtype != PMOE_F16 && d.router_dtype != PMOE_BF16 && !router_quantised)
+        return fail(PMOE_ERR_UNSUPPORTED_DTYPE, "router weights must be F32, F16, BF16 or a GGUF block type (got %d)", d.router_dtype);
+    if (router_quantised && d.H % block_elems(d.router_dtype))
+        return fail(PMOE_ERR_UNSUPPORTED_SHAPE, "H must be a multiple of the router's block size");
     const char *why = "";
     if (!gemv_supported(d.gate_dtype, d.H, d.F, &why) || !gemv_supported(d.down_dtype, d.F, d.H, &why))
         return fail(dtype_known(d.gate_dtype) && (block_elems(d.gate_dtype) > 1) && (block_elems(d.down_dtype) > 1)
@@ -342,9 +345,15 @@ int pmoe_layer_create(const pmoe_layer_desc *desc, pmoe_layer **out)
         if (!rc) rc = place_tensor(L, d.sh_gate_inp, (size_t)d.H * 4, loc, &tmp, "sh_gate_inp");
         v.sh_gate_inp = (const float *)tmp;
     }
+    v.router_q = nullptr;
+    v.router_dtype = PMOE_F32;
     if (!rc && d.router_dtype == PMOE_F32) {
         rc = place_tensor(L, d.router_w, (size_t)d.E * d.H * 4, loc, &tmp, "router_w");
         v.router_w = (const float *)tmp;
+    } else if (!rc && router_quantised) {
+        rc = place_tensor(L, d.router_w, (size_t)d.E * row_bytes(d.router_dtype, d.H), loc, &v.router_q, "router_w");
+        v.router_w = nullptr;
+        v.router_dtype = d.router_dtype;
     } else if (!rc) {
         // 16-bit router weights are widened to f32 once, like the dequantised tensor the reference's
         // QMatMul holds for an F16/BF16 ffn_gate_inp (models/with_tracing.rs:120-124)

@@ -258,7 +258,9 @@ struct LayerDev {
     int has_shared, sh_gate_dtype, sh_up_dtype, sh_down_dtype;
     const uint8_t *sh_gate, *sh_up, *sh_down;
     const float *sh_gate_inp;
-    const float *router_w, *router_bias;
+    const float *router_w, *router_bias;   // router_w: f32 [E, H], or null when the router is quantised
+    const uint8_t *router_q;               // quantised router: GGUF blocks [E, H / block] of type router_dtype
+    int router_dtype;                      // PMOE_F32 (16-bit weights are widened at create) or a block type
 };
 
 struct Workspace {
@@ -284,6 +286,8 @@ struct Workspace {
 // pmoe_route.cu
 cudaError_t launch_prep(const LayerDev &L, const Workspace &ws, const void *x, int x_dtype, int n,
                         bool need_q8k, bool need_q80, bool need_gate, cudaStream_t s);
+// y[m, rows] = quantised rows x W^T over activations that are already quantised (the type W's dots take)
+cudaError_t launch_qmatmul_quantised(int dtype, const void *w, int rows, int K, const QAct &a, int m, float *y, cudaStream_t s);
 cudaError_t launch_router(const LayerDev &L, const Workspace &ws, const void *x, int x_dtype, int n,
                           float *logits, cudaStream_t s, bool prep = false, bool need_q8k = false,
                           bool need_q80 = false, bool need_gate = false);

@@ -301,6 +301,12 @@ cudaError_t launch_qmatmul(int dtype, const void *w, int rows, int K, const floa
     a.bsums = (int16_t *)p;
     const bool kq = is_kquant(dtype);
     k_quant_rows<<<m, 64, 0, s>>>(x, K, kq, a, a);
+    count_launch();
+    return launch_qmatmul_quantised(dtype, w, rows, K, a, m, y, s);
+}
+
+cudaError_t launch_qmatmul_quantised(int dtype, const void *w, int rows, int K, const QAct &a, int m, float *y, cudaStream_t s)
+{
     dim3 grid((rows + 3) / 4, (m + TG - 1) / TG);
     const uint8_t *wb = (const uint8_t *)w;
     if (dtype == PMOE_Q4_K) k_qmatmul<PMOE_Q4_K><<<grid, 128, 0, s>>>(wb, rows, K, a, m, y);
@@ -309,7 +315,7 @@ cudaError_t launch_qmatmul(int dtype, const void *w, int rows, int K, const floa
     else if (dtype == PMOE_Q5_K) k_qmatmul<PMOE_Q5_K><<<grid, 128, 0, s>>>(wb, rows, K, a, m, y);
     else if (dtype == PMOE_Q6_K) k_qmatmul<PMOE_Q6_K><<<grid, 128, 0, s>>>(wb, rows, K, a, m, y);
     else k_qmatmul<PMOE_Q8_0><<<grid, 128, 0, s>>>(wb, rows, K, a, m, y);
-    count_launch(2);
+    count_launch();
     return cudaGetLastError();
 }
 

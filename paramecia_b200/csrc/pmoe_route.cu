@@ -268,12 +268,31 @@ static cudaError_t launch_router_tiled(const LayerDev &L, const void *x, int n, 
     return e;
 }
 
+__global__ void k_add_bias(float *__restrict__ logits, const float *__restrict__ bias, int n, int E)
+{
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n * E) logits[i] += bias[i % E];
+}
+
 // Router launch.  With `prep` set the same launch also prepares the tokens (quantised rows, shared
 // gate) in extra CTAs, which saves the separate k_prep launch of a decode-sized call.
 cudaError_t launch_router(const LayerDev &L, const Workspace &ws, const void *x, int x_dtype, int n, float *logits,
                           cudaStream_t s, bool prep, bool need_q8k, bool need_q80, bool need_gate)
 {
     if (n <= 0) return cudaSuccess;
+    if (L.router_q) {
+        // A quantised ffn_gate_inp is a QMatMul like the experts' (models/with_tracing.rs:324-335): the rows are
+        // quantised to the type its block dots take and the logits are integer block sums with f32 scales.  The
+        // preparation runs first, whether or not the caller wants it for the experts.
+        const bool kq = is_kquant(L.router_dtype);
+        cudaError_t e = launch_prep(L, ws, x, x_dtype, n, need_q8k || kq, need_q80 || !kq, prep && need_gate, s);
+        if (e != cudaSuccess) return e;
+        e = launch_qmatmul_quantised(L.router_dtype, L.router_q, L.E, L.H, kq ? ws.x_q8k : ws.x_q80, n, logits, s);
+        if (e != cudaSuccess || !L.router_bias) return e;
+        k_add_bias<<<(n * L.E + 255) / 256, 256, 0, s>>>(logits, L.router_bias, n, L.E);
+        count_launch();
+        return cudaGetLastError();
+    }
     const bool f32 = x_dtype == PMOE_F32;
     using BT = __nv_bfloat16;
     const PrepArgs P = make_prep_args(L, ws, prep ? n : 0, need_q8k, need_q80, need_gate);

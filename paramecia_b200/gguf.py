@@ -239,10 +239,14 @@ def load_moe_block(f: GGUFFile, layer: int, device="cuda:0", max_tokens: int = 2
     router_info = f.tensors[names["router"]]
     if router_info.shape != (E, H):
         raise GGUFError(f"{router_info.name}: shape {router_info.shape}, expected {(E, H)}")
-    if router_info.dtype not in (F32, F16, BF16):
-        # the reference would run a quantised mat-mul here (Q8 activations); widening would not match it
-        raise GGUFError(f"{router_info.name}: quantised router weights (ggml type {router_info.dtype}) are not supported")
-    router = _float_tensor(f, names["router"], device, keep_16bit=True)
+    if router_info.dtype in (F32, F16, BF16):
+        router = _float_tensor(f, names["router"], device, keep_16bit=True)
+    else:
+        # a quantised router is a quantised mat-mul in the reference (Q8 activations, integer block dots); the
+        # library runs it that way, so the blocks go over as they are
+        if row_bytes(router_info.dtype, H) <= 0:
+            raise GGUFError(f"{router_info.name}: ggml type {router_info.dtype} is not a type this library serves")
+        router = QTensor(_host_tensor(f.tensor_bytes(router_info.name)).to(device), router_info.dtype, (E, H))
 
     shared = None
     if names["sh_up"] in f.tensors:   # SharedExpert::new returns None without ffn_up_shexp (qwen3_next.rs:1751-1754)

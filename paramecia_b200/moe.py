@@ -190,7 +190,7 @@ class MoeBlock:
     """One Qwen3-Next sparse MoE FFN block resident on one GPU.
 
     gate_exps / up_exps: QTensor [E_local, F, H]; down_exps: QTensor [E_local, H, F];
-    gate (router): f32 tensor [E, H].  With expert parallelism a rank passes its slice of the
+    gate (router): f32 / f16 / bf16 tensor [E, H], or a QTensor [E, H] (quantised router).  With expert parallelism a rank passes its slice of the
     experts and ``expert_base``; indices outside the slice contribute nothing.
     """
 
@@ -219,9 +219,13 @@ class MoeBlock:
             raise ValueError("expert tensor shapes must be [E,F,H], [E,F,H], [E,H,F]")
         if tuple(gate.shape) != (self.num_experts, H):
             raise ValueError("router weight must be [E, H]")
-        # f16 / bf16 router weights go to the library as they are (it widens them once); others as f32
-        router_dt = {torch.float16: F16, torch.bfloat16: BF16}.get(gate.dtype, F32)
-        router = gate.to(self.device).contiguous() if router_dt != F32 else gate.to(self.device, torch.float32).contiguous()
+        if isinstance(gate, QTensor):
+            # a quantised ffn_gate_inp: the library runs it as a quantised mat-mul, like the reference's QMatMul
+            router_dt, router = int(gate.dtype), gate.data.to(self.device).contiguous()
+        else:
+            # f16 / bf16 router weights go to the library as they are (it widens them once); others as f32
+            router_dt = {torch.float16: F16, torch.bfloat16: BF16}.get(gate.dtype, F32)
+            router = gate.to(self.device).contiguous() if router_dt != F32 else gate.to(self.device, torch.float32).contiguous()
         # the library adopts these device buffers in place (weights_location = 2); keep them alive
         self._keep = dict(
             gate=gate_exps.data.to(self.device), up=up_exps.data.to(self.device),

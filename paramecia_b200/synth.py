@@ -211,9 +211,10 @@ def zipf_router_bias(E: int, seed: int, device="cpu") -> torch.Tensor:
 
 
 def make_layer(H=2048, F=512, E=512, k=10, preset="q4k_m", seed=0, device="cpu", shared=True,
-               zipf=False, layer=0) -> Dict[str, object]:
+               zipf=False, layer=0, router_dtype: Optional[int] = None) -> Dict[str, object]:
     """One synthetic MoE block as raw tensors.  Returns a dict with the GGUF block bytes
-    (uint8 tensors on `device`), dtypes and the float tensors."""
+    (uint8 tensors on `device`), dtypes and the float tensors.  `router_dtype` (a block type) also gives the
+    router quantised: `router_q`, blocks [E, H / block] made from `router_w`."""
     gu_dt, dn_dt, sh_dt = PRESETS[preset]
     sh_gu, sh_dn = sh_dt if isinstance(sh_dt, tuple) else (sh_dt, sh_dt)
     dev = torch.device(device)
@@ -227,6 +228,8 @@ def make_layer(H=2048, F=512, E=512, k=10, preset="q4k_m", seed=0, device="cpu",
              router_w=torch.randn((E, H), generator=gen, device=dev) * 0.02,
              router_bias=zipf_router_bias(E, seed + 17, dev) if zipf else None,
              shared=None)
+    t["router_dtype"] = router_dtype
+    t["router_q"] = None if router_dtype is None else quantize(t["router_w"].float(), router_dtype)
     if shared:
         t["shared"] = dict(gate_dtype=sh_gu, up_dtype=sh_gu, down_dtype=sh_dn,
                            gate=random_quantized((1, F * H), sh_gu, gen, dev),
@@ -253,8 +256,9 @@ def make_block(t: Dict[str, object], device="cuda:0", max_tokens=256, expert_bas
         s = t["shared"]
         sh = SharedExpertWeights(QTensor(s["gate"], s["gate_dtype"], (F, H)), QTensor(s["up"], s["up_dtype"], (F, H)),
                                  QTensor(s["down"], s["down_dtype"], (H, F)), s["gate_inp"])
+    router = t["router_w"] if t.get("router_q") is None else QTensor(t["router_q"], t["router_dtype"], (E, H))
     return MoeBlock(sl("gate", t["gate_dtype"], F, H), sl("up", t["up_dtype"], F, H), sl("down", t["down_dtype"], H, F),
-                    t["router_w"], k, shared_expert=sh, device=device, max_tokens=max_tokens,
+                    router, k, shared_expert=sh, device=device, max_tokens=max_tokens,
                     router_bias=t["router_bias"], num_experts=E, expert_base=expert_base,
                     training_mode=training_mode, ep_rank=ep_rank, ep_size=ep_size)
 

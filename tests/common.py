@@ -17,7 +17,8 @@ def oracle_layer(t) -> "po.Layer":
     bias = None if t["router_bias"] is None else t["router_bias"].cpu().numpy()
     return po.Layer(t["H"], t["F"], t["E"], t["k"], u8(t["gate"]), u8(t["up"]), u8(t["down"]),
                     t["gate_dtype"], t["up_dtype"], t["down_dtype"], t["router_w"].cpu().numpy(),
-                    shared=shared, router_bias=bias)
+                    shared=shared, router_bias=bias, router_dtype=t.get("router_dtype") or 0,
+                    router_q=None if t.get("router_q") is None else u8(t["router_q"]))
 
 
 def rel_l2(a, b):

@@ -128,6 +128,27 @@ def test_block_matches_oracle(preset, E, k, n, xdtype):
     assert rel_l2(got, want) <= 5e-4
 
 
+@pytest.mark.parametrize("router_dtype,n,xdtype", [(8, 5, torch.float32), (12, 40, torch.bfloat16), (14, 700, torch.float32)])
+def test_quantised_router(router_dtype, n, xdtype):
+    """ffn_gate_inp held as Q8_0 / Q4_K / Q6_K blocks: the router is a quantised mat-mul like the experts'
+    (models/with_tracing.rs:324-335).  The logits are integer block sums with f32 scales, so they match the oracle
+    to f32 re-association; the seeded inputs have no near-ties, so the indices are equal."""
+    t = synth.make_layer(E=64, k=6, preset="q4k_m", seed=31, router_dtype=router_dtype)
+    blk = synth.make_block(t, DEV, max_tokens=max(n, 8))
+    x = seeded_x(n, 2048, 300 + n, xdtype)
+    out, (logits, idx) = blk.forward_with_stats(x.to(DEV), out_dtype=torch.float32)
+    blk.status()
+    ol = oracle_layer(t)
+    want, want_logits, want_idx, _ = ol.forward(x.float().numpy())
+    assert np.allclose(logits.cpu().numpy(), want_logits, rtol=1e-5, atol=1e-6)
+    assert np.array_equal(idx.cpu().numpy().astype(np.uint32), want_idx)
+    got = out.cpu().numpy()
+    assert max_abs(got, want) <= MAX_ABS_TOL and rel_l2(got, want) <= 5e-4
+    # the routing-only entry point takes the same path
+    lg2, w2, idx2 = blk.route(x.to(DEV))
+    assert torch.equal(lg2, logits.reshape(lg2.shape)) and torch.equal(idx2.reshape(idx.shape), idx)
+
+
 def test_experts_and_shared_entry_points():
     t = synth.make_layer(E=32, k=4, preset="q4k_m", seed=8)
     blk = synth.make_block(t, DEV, max_tokens=32)

@@ -208,3 +208,28 @@ def test_simd_block_dots_equal_the_portable_ones_bit_for_bit(dtype):
     finally:
         po.set_simd(True)
     assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
+
+
+def test_quantised_router_is_a_quantised_matmul():
+    """A router held as GGUF blocks takes candle's quantised mat-mul (rows to Q8_K / Q8_0, integer block dots),
+    not a dequantise-and-GEMV: the layer's logits are pmo_qmatmul of the router blocks, plus the bias."""
+    rng = np.random.default_rng(5)
+    E, H, F, k, n = 16, 256, 256, 3, 7
+    wf = (rng.standard_normal((E, H)) * 0.02).astype(np.float32)
+    x = rng.standard_normal((n, H)).astype(np.float32)
+    bias = rng.standard_normal(E).astype(np.float32)
+    for dt in (po.Q8_0, po.Q4_K, po.Q6_K):
+        rq = po.quantize(dt, wf)
+        gate = po.quantize(po.Q4_K, (rng.standard_normal((E, F * H)) * 0.02).astype(np.float32))
+        down = po.quantize(po.Q4_K, (rng.standard_normal((E, H * F)) * 0.02).astype(np.float32))
+        L = po.Layer(H, F, E, k, gate, gate, down, po.Q4_K, po.Q4_K, po.Q4_K, wf, router_bias=bias,
+                     router_dtype=dt, router_q=rq)
+        want = po.qmatmul(dt, rq, E, H, x) + bias[None, :]
+        got = L.router_logits(x)
+        assert np.array_equal(got, want.astype(np.float32))
+        # and it differs from the f32 router over the dequantised weights (the activations are quantised too)
+        plain = po.Layer(H, F, E, k, gate, gate, down, po.Q4_K, po.Q4_K, po.Q4_K, po.dequantize(dt, rq, E * H).reshape(E, H),
+                         router_bias=bias).router_logits(x)
+        assert not np.array_equal(got, plain) and np.allclose(got, plain, atol=2e-2)
+        out, logits, idx, w = L.forward(x)
+        assert np.array_equal(logits, got)
