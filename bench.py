@@ -186,7 +186,7 @@ def run_cpu_baseline(layer_host, batch, seconds, seed=1234, what="whole-block fo
         ol.forward(x)
         reps += 1
         el = time.perf_counter() - t0
-        if el >= seconds or reps >= 50:
+        if el >= seconds or reps >= 2000:
             break
     return dict(value=batch * reps / el, unit=UNIT, cores=th["threads"], kind="port",
                 sample=f"{reps} {what} of {batch} tokens on one layer, {el:.1f} s; C restatement of the reference "
