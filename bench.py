@@ -61,6 +61,9 @@ def parse():
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--ep-mode", default="auto", choices=["auto", "native", "all_to_all", "all_gather"])
     ap.add_argument("--placement", default="contiguous", choices=["contiguous", "round_robin"])
+    ap.add_argument("--ep-prefill-placement", default="round_robin", choices=["contiguous", "round_robin"],
+                    help="expert -> rank table of the ep_prefill record (its router is Zipf-skewed: neighbouring hot "
+                         "experts would pile up on one rank of a contiguous split)")
     ap.add_argument("--stack-layers", type=int, default=48)
     ap.add_argument("--stack-batch", type=int, default=256, help="global decode batch of the stack48 record")
     ap.add_argument("--prefill-tokens", type=int, default=4096)
@@ -436,14 +439,14 @@ def make_ep(ctx, block):
     return ExpertParallelMoe(block, mode=mode)
 
 
-def build_rank_blocks(ctx, n_layers, preset, max_tokens, zipf=False, seed=0, layer0=0):
+def build_rank_blocks(ctx, n_layers, preset, max_tokens, zipf=False, seed=0, layer0=0, placement=None):
     """Every rank builds the same seeded layers and keeps its slice of the experts."""
     from paramecia_b200 import synth
     N, rank = ctx.N, ctx.rank
     blocks = []
     for li in range(n_layers):
         t = synth.make_layer(H, F, E, TOPK, preset, seed=seed, device=ctx.dev, layer=layer0 + li, zipf=zipf)
-        blocks.append(synth.make_rank_block(t, ctx.dev, max_tokens, rank, N, ctx.args.placement))
+        blocks.append(synth.make_rank_block(t, ctx.dev, max_tokens, rank, N, placement or ctx.args.placement))
         del t
     ctx.torch.cuda.synchronize()
     return blocks
@@ -531,7 +534,7 @@ def ep_prefill_record(ctx):
     torch, args, N = ctx.torch, ctx.args, ctx.N
     nl, gt = args.ep_prefill_layers, args.ep_prefill_tokens
     n_home = gt // N
-    blocks = build_rank_blocks(ctx, nl, "q8_0", max_tokens=gt, zipf=True, seed=5)
+    blocks = build_rank_blocks(ctx, nl, "q8_0", max_tokens=gt, zipf=True, seed=5, placement=args.ep_prefill_placement)
     eps = [make_ep(ctx, b) for b in blocks]
     h0 = ctx.x(n_home, 900).float()
     resid, y, delta = torch.empty_like(h0), torch.empty_like(h0), torch.empty_like(h0)
@@ -555,7 +558,7 @@ def ep_prefill_record(ctx):
                ms_per_layer=ms_step / nl, steps=steps, repeats=R, spread_ms_per_step=[min(ms) / steps, max(ms) / steps],
                config=dict(workload=f"{nl} stacked all-Q8_0 qwen3next-moe blocks, {gt} bf16-valued tokens (global), Zipf-biased "
                                     f"router, residual + RMSNorm between blocks", global_tokens=gt, tokens_per_gpu=n_home,
-                           parallelism=f"ep{N}", placement=args.placement),
+                           parallelism=f"ep{N}", placement=args.ep_prefill_placement),
                block_tflops=gt * FLOPS_PER_TOKEN / (1e-3 * ms_step / nl) / 1e12,
                exposed_collective_us_per_layer=ep_exposed_us(ctx, eps, y, delta, reps=3),
                pairs_per_gpu=[int(v.item()) for v in load], ep_mode=eps[0].mode)
