@@ -83,14 +83,6 @@ __device__ inline void tmem_ld16(uint32_t taddr, uint32_t (&v)[16])
 }
 __device__ inline void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
-// 16 bytes global -> shared without passing through registers; src_bytes = 0 writes zeros
-__device__ inline void cp_async16(void *smem_dst, const void *gmem_src, uint32_t src_bytes)
-{
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(smem_dst)), "l"(gmem_src), "r"(src_bytes) : "memory");
-}
-__device__ inline void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N> __device__ inline void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
-
 // Shared-memory matrix descriptor, K-major, no swizzle: core matrices of 8 rows x 16 bytes;
 // lbo = bytes between the two 16-byte K chunks of one MMA, sbo = bytes between 8-row groups.
 __device__ inline uint64_t smem_desc(const void *p, uint32_t lbo, uint32_t sbo)
@@ -721,7 +713,7 @@ template <> struct DownDequant<PMOE_Q8_0> {
 // 64).  Entries of the same expert form a run: the run's raw GGUF rows arrive with one bulk copy, every K step
 // dequantises them ONCE (two threads per row) and feeds all the run's token tiles, each with its own 64 columns of
 // f32 in tensor memory -- a hot expert's weights are not decoded once per token tile.  The B tiles go through a ring
-// of buffers filled by cp.async ahead of their use, straight into the core-matrix layout.  Two CTAs share an SM
+// of buffers, each loaded into registers one piece ahead and stored in the core-matrix layout.  Two CTAs share an SM
 // (half of tensor memory and of shared memory each), so that one's copies, dequantisation and drain overlap the
 // other's MMAs.
 constexpr int DN_THREADS = 256;
@@ -729,9 +721,8 @@ constexpr int DN_TILES = 4;      // 4 x 64 columns = half of tensor memory
 constexpr int DN_COLS = 64 * DN_TILES;
 
 template <int DT> struct DownCfg {
-    // Q8_0 rows are the widest: three B buffers filled one piece ahead; the others take four, two ahead
+    // B buffers; Q8_0 rows are the widest and leave room for three
     static constexpr int NB = DT == PMOE_Q8_0 ? 3 : 4;
-    static constexpr int AHEAD = NB - 2;
 };
 
 struct DownSmemHdr {
@@ -748,7 +739,7 @@ __global__ void __launch_bounds__(DN_THREADS, 2) k_down_prefill(const DownArgs A
 {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     using DQ = DownDequant<DT>;
-    constexpr int NB = DownCfg<DT>::NB, AHEAD = DownCfg<DT>::AHEAD;
+    constexpr int NB = DownCfg<DT>::NB;
     constexpr int RAW_BYTES = PF_M * DQ::ROW_BYTES;
     constexpr int B_BYTES = PF_NT * DN_KSTEP * 2;
     uint8_t *a_tile = smem_raw;                                  // [128 rows][64 K] fp16, core-matrix layout
@@ -840,43 +831,46 @@ __global__ void __launch_bounds__(DN_THREADS, 2) k_down_prefill(const DownArgs A
         }
         __syncthreads();
 
-        // B pieces are numbered i = s * T + t; piece i is the CTA's commit base + i and sits in that commit's buffer
+        // B pieces are numbered i = s * T + t; piece i is the CTA's commit base + i and sits in that commit's buffer.
+        // A piece travels global -> registers -> shared memory (two 16-byte loads and stores a thread), loaded one
+        // piece ahead.  (A cp.async ring two pieces ahead measured the same; its copies cost one shared-memory
+        // wavefront per lane where these stores take four per warp.)
         const int pieces = steps * T, base = committed;
-        auto fetch_b = [&](int i) {
+        uint4 nb[2];
+        auto load_b = [&](int i) {
+            nb[0] = nb[1] = make_uint4(0, 0, 0, 0);
             if (i < pieces) {
                 const int s = i / T, t = i - s * T;
-                wait_mma(base + i - NB + 1);   // the MMAs that read this buffer NB pieces ago
                 const int rin = S.row_in[t][tk];
-                const __half *src = A.act_h + (size_t)(rin >= 0 ? rin : 0) * A.F + s * DN_KSTEP + 16 * quarter;
-                uint8_t *bt = b_tile + ((base + i) % NB) * B_BYTES;
-#pragma unroll
-                for (int c = 0; c < 2; c++)
-                    cp_async16(bt + core_off(PF_NT, tk, 2 * (16 * quarter + 8 * c)), src + 8 * c, rin >= 0 ? 16u : 0u);
+                if (rin >= 0) {
+                    const uint4 *src = reinterpret_cast<const uint4 *>(A.act_h + (size_t)rin * A.F + s * DN_KSTEP + 16 * quarter);
+                    nb[0] = src[0];
+                    nb[1] = src[1];
+                }
             }
-            cp_async_commit();   // one group per piece, empty past the end, so that the counts below stay fixed
         };
-#pragma unroll
-        for (int i = 0; i < AHEAD; i++) fetch_b(i);
+        load_b(0);
         if (!mbar_wait(&S.bar_raw, ph_raw)) {
             set_status(A.status, PMOE_ERR_TIMEOUT, 31, e0);
             ok = false;
         }
         ph_raw ^= 1;
+        const uint32_t b_off = core_off(PF_NT, tk, 32 * quarter);
         for (int s = 0, i = 0; s < steps && ok; s++) {
             wait_mma(base + i);   // the previous step's MMAs still read the A tile
             tc_fence_after();
             DQ::step(raw + (size_t)r * DQ::ROW_BYTES, s, a_tile, r, part);
             for (int t = 0; t < T && ok; t++, i++) {
-                fetch_b(i + AHEAD);
-                cp_async_wait<AHEAD>();   // this thread's copies of piece i have landed
                 const int buf = (base + i) % NB;
+                wait_mma(base + i - NB + 1);   // the MMAs that read this buffer NB pieces ago
+                uint8_t *bt = b_tile + buf * B_BYTES + b_off;
+                *reinterpret_cast<uint4 *>(bt) = nb[0];
+                *reinterpret_cast<uint4 *>(bt + PF_NT * 16) = nb[1];   // the next 16-byte K chunk
+                load_b(i + 1);
                 tc_fence_before();
                 __syncthreads();
                 if (tid == 0) {
-                    // everyone's stores and copies are complete and ordered before the barrier; the issuing thread
-                    // alone crosses over to the async proxy (a proxy fence in a thread with cp.async copies still in
-                    // flight waits for them, which would put the ring's look-ahead on the critical path)
-                    fence_proxy_async();
+                    fence_proxy_async();   // the stores above went through the generic proxy
                     tc_fence_after();
                     // a K slice of 16 halves is two 16-byte chunks further on: the descriptor's address field moves with it
                     const uint64_t db0 = desc_b0 + (uint64_t)((buf * B_BYTES) >> 4);
@@ -889,7 +883,6 @@ __global__ void __launch_bounds__(DN_THREADS, 2) k_down_prefill(const DownArgs A
                 committed++;
             }
         }
-        cp_async_wait<0>();
         wait_mma(committed);
         tc_fence_after();
         if (ok) {
@@ -1041,6 +1034,7 @@ cudaError_t launch_gate_up_prefill(const LayerDev &L, const Workspace &ws, int n
         cudaError_t e = cudaFuncSetAttribute(k_gu_prefill, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(GuSmem) + 128);
         if (e == cudaSuccess)
             e = cudaFuncSetAttribute(k_gu_prefill_q80, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Gu80Smem) + 128);
+
         if (e != cudaSuccess) return e;
         configured = true;
     }
