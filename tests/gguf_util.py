@@ -25,7 +25,10 @@ def write_layer_gguf(path, t, layer=0, router_dtype="f32", arch="qwen3next", alt
         arr, dt = raw(t[key], t[f"{key}_dtype"], *dims)
         w.add_tensor(f"{p}.{name}.weight", arr, raw_dtype=dt)
     r = t["router_w"].cpu()
-    if router_dtype == "f32":
+    if router_dtype == "blocks":   # the quantised router of make_layer(router_dtype=...)
+        arr, dt = raw(t["router_q"], t["router_dtype"], E, H)
+        w.add_tensor(f"{p}.ffn_gate_inp.weight", arr, raw_dtype=dt)
+    elif router_dtype == "f32":
         w.add_tensor(f"{p}.ffn_gate_inp.weight", r.float().numpy())
     elif router_dtype == "f16":
         w.add_tensor(f"{p}.ffn_gate_inp.weight", r.half().numpy())

@@ -70,3 +70,20 @@ def test_sixteen_bit_router_weights(tmp_path, router):
     want = ol.router_logits(x.cpu().numpy())
     assert np.array_equal(logits.cpu().numpy().view(np.uint32), want.view(np.uint32))
     assert np.array_equal(idx.cpu().numpy().astype(np.uint32), ol.route_topk(want)[0])
+
+
+def test_quantised_router_from_gguf(tmp_path):
+    # a GGUF whose ffn_gate_inp is Q8_0 blocks: the router runs as a quantised mat-mul, as the reference's QMatMul does
+    t = synth.make_layer(E=32, k=4, preset="q4k_m", seed=34, router_dtype=8)
+    path = str(tmp_path / "l.gguf")
+    write_layer_gguf(path, t, router_dtype="blocks")
+    x = seeded_x(20, 2048, 7).to(DEV)
+    with GGUFFile(path) as f:
+        blk = load_moe_block(f, 0, DEV, max_tokens=32)
+    direct = synth.make_block(t, DEV, max_tokens=32)
+    out, (logits, idx) = blk.forward_with_stats(x, out_dtype=torch.float32)
+    want, (wl, wi) = direct.forward_with_stats(x, out_dtype=torch.float32)
+    assert torch.equal(out, want) and torch.equal(logits, wl) and torch.equal(idx, wi)
+    ref = oracle_layer(t).forward(x.cpu().numpy())
+    assert np.allclose(logits.cpu().numpy(), ref[1], rtol=1e-5, atol=1e-6)
+    assert rel_l2(out.cpu().numpy(), ref[0]) <= REL_L2_TOL
