@@ -314,6 +314,9 @@ cudaError_t launch_router(const LayerDev &L, const Workspace &ws, const void *x,
             return f32 ? launch_router_tiled<float, 4, 8>(L, x, n, passes, logits, P, s)
                        : launch_router_tiled<BT, 4, 8>(L, x, n, passes, logits, P, s);
         }
+        if (n <= 8)   // one token tile: one row per warp spreads the rows of W over twice the SMs
+            return f32 ? launch_router_tiled<float, 1, 8>(L, x, n, 1, logits, P, s)
+                       : launch_router_tiled<BT, 1, 8>(L, x, n, 1, logits, P, s);
         return f32 ? launch_router_tiled<float, 2, 8>(L, x, n, 1, logits, P, s)
                    : launch_router_tiled<BT, 2, 8>(L, x, n, 1, logits, P, s);
     }
