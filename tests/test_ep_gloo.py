@@ -103,6 +103,18 @@ def test_two_ranks_equal_one(mode, k):
         assert err < 1e-6, (rank, err)   # fp32 re-association of the cross-rank sum only
 
 
+def test_four_ranks_equal_one():
+    # the all-to-all-v plan with more than one peer: 8 experts over 4 ranks, tokens visit 1 to 3 of them
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_worker, args=(4, port, "a2av", ret, 3), nprocs=4, join=True)
+    assert len(ret) == 4
+    for rank in range(4):
+        err, same_idx = ret[rank]
+        assert same_idx and err < 1e-6, (rank, err)
+
+
 def test_destination_masks():
     from paramecia_b200.ep import INVALID_EXPERT, expert_owner, mask_for_destinations
     idx = torch.tensor([[0, 5, 7], [3, 4, 6]], dtype=torch.int32)
