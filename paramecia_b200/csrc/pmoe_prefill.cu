@@ -720,9 +720,11 @@ constexpr int DN_THREADS = 256;
 constexpr int DN_TILES = 4;      // 4 x 64 columns = half of tensor memory
 constexpr int DN_COLS = 64 * DN_TILES;
 
+// A B piece holds 128 tokens -- two token tiles of a run share an MMA of N = 128 -- in two buffers; Q8_0 rows are
+// the widest and leave room for 64-token pieces in three buffers only.
 template <int DT> struct DownCfg {
-    // B buffers; Q8_0 rows are the widest and leave room for three
-    static constexpr int NB = DT == PMOE_Q8_0 ? 3 : 4;
+    static constexpr int PT = DT == PMOE_Q8_0 ? PF_NT : 2 * PF_NT;   // tokens of a B piece
+    static constexpr int NB = DT == PMOE_Q8_0 ? 3 : 2;               // B buffers
 };
 
 struct DownSmemHdr {
@@ -741,9 +743,11 @@ __global__ void __launch_bounds__(DN_THREADS, 2) k_down_prefill(const DownArgs A
     using DQ = DownDequant<DT>;
     constexpr int NB = DownCfg<DT>::NB;
     constexpr int RAW_BYTES = PF_M * DQ::ROW_BYTES;
-    constexpr int B_BYTES = PF_NT * DN_KSTEP * 2;
+    constexpr int PT = DownCfg<DT>::PT, TPP = PT / PF_NT;        // tokens and token tiles of a B piece
+    constexpr int TPT = DN_THREADS / PT, CPT = 8 / TPT;          // threads of a token, 16-byte chunks of a thread
+    constexpr int B_BYTES = PT * DN_KSTEP * 2;
     uint8_t *a_tile = smem_raw;                                  // [128 rows][64 K] fp16, core-matrix layout
-    uint8_t *b_tile = a_tile + PF_M * DN_KSTEP * 2;              // NB x [64 tokens][64 K] fp16
+    uint8_t *b_tile = a_tile + PF_M * DN_KSTEP * 2;              // NB x [PT tokens][64 K] fp16, same layout
     uint8_t *raw = b_tile + NB * B_BYTES;                        // the run's GGUF rows
     DownSmemHdr &S = *reinterpret_cast<DownSmemHdr *>(raw + ((RAW_BYTES + 127) / 128) * 128);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -774,11 +778,11 @@ __global__ void __launch_bounds__(DN_THREADS, 2) k_down_prefill(const DownArgs A
     const uint32_t tmem = S.tmem_base;
     const int n_entries = S.n_entries;
     const int h0 = blockIdx.x * PF_M;
-    constexpr uint32_t IDESC = make_idesc(1, 0, 0, PF_NT, PF_M);  // f16 x f16 -> f32
+    constexpr uint32_t IDESC1 = make_idesc(1, 0, 0, PF_NT, PF_M), IDESC2 = make_idesc(1, 0, 0, 2 * PF_NT, PF_M);  // f16 x f16 -> f32
     const int steps = A.F / DN_KSTEP;
     const int r = tid & (PF_M - 1), part = tid >> 7;               // dequantisation: row and half of the step
-    const int tk = tid >> 2, quarter = tid & 3;                    // B side: 16 halves of one token per thread
-    const uint64_t desc_a0 = smem_desc(a_tile, PF_M * 16, 128), desc_b0 = smem_desc(b_tile, PF_NT * 16, 128);
+    const int tk = tid / TPT, ksub = tid % TPT;                    // B side: CPT chunks of one of a piece's PT tokens per thread
+    const uint64_t desc_a0 = smem_desc(a_tile, PF_M * 16, 128), desc_b0 = smem_desc(b_tile, PT * 16, 128);
 
     // MMA commits are counted over the CTA's life: commit c lands on barrier c % NB as its (c / NB)-th completion
     int committed = 0, seen = 0;
@@ -831,42 +835,46 @@ __global__ void __launch_bounds__(DN_THREADS, 2) k_down_prefill(const DownArgs A
         }
         __syncthreads();
 
-        // B pieces are numbered i = s * T + t; piece i is the CTA's commit base + i and sits in that commit's buffer.
-        // A piece travels global -> registers -> shared memory (two 16-byte loads and stores a thread), loaded one
-        // piece ahead.  (A cp.async ring two pieces ahead measured the same; its copies cost one shared-memory
-        // wavefront per lane where these stores take four per warp.)
-        const int pieces = steps * T, base = committed;
-        uint4 nb[2];
-        auto load_b = [&](int i) {
-            nb[0] = nb[1] = make_uint4(0, 0, 0, 0);
-            if (i < pieces) {
-                const int s = i / T, t = i - s * T;
-                const int rin = S.row_in[t][tk];
+        // A B piece holds the activations of TPP token tiles of the run (the last one of an odd run holds one): pieces
+        // are numbered i = s * P + p with P = ceil(T / TPP); piece i is the CTA's commit base + i and sits in that
+        // commit's buffer.  It travels global -> registers -> shared memory (16-byte loads and stores), loaded one
+        // piece ahead.  (A cp.async ring two pieces ahead measured the same; its copies cost one
+        // shared-memory wavefront per lane where these stores take four per warp.)
+        const int P = (T + TPP - 1) / TPP, base = committed;
+        uint4 nb[CPT];
+        int ls = 0, lp = 0;   // step and pair of the next piece to load
+        auto load_b = [&]() {
+#pragma unroll
+            for (int c = 0; c < CPT; c++) nb[c] = make_uint4(0, 0, 0, 0);
+            if (ls < steps) {
+                const int t = TPP * lp + (tk >> 6);
+                const int rin = t < T ? S.row_in[t][tk & 63] : -1;
                 if (rin >= 0) {
-                    const uint4 *src = reinterpret_cast<const uint4 *>(A.act_h + (size_t)rin * A.F + s * DN_KSTEP + 16 * quarter);
-                    nb[0] = src[0];
-                    nb[1] = src[1];
+                    const uint4 *src = reinterpret_cast<const uint4 *>(A.act_h + (size_t)rin * A.F + ls * DN_KSTEP + 8 * CPT * ksub);
+#pragma unroll
+                    for (int c = 0; c < CPT; c++) nb[c] = src[c];
                 }
+                if (++lp == P) { lp = 0; ls++; }
             }
         };
-        load_b(0);
+        load_b();
         if (!mbar_wait(&S.bar_raw, ph_raw)) {
             set_status(A.status, PMOE_ERR_TIMEOUT, 31, e0);
             ok = false;
         }
         ph_raw ^= 1;
-        const uint32_t b_off = core_off(PF_NT, tk, 32 * quarter);
+        const uint32_t b_off = core_off(PT, tk, 16 * CPT * ksub);
         for (int s = 0, i = 0; s < steps && ok; s++) {
             wait_mma(base + i);   // the previous step's MMAs still read the A tile
             tc_fence_after();
             DQ::step(raw + (size_t)r * DQ::ROW_BYTES, s, a_tile, r, part);
-            for (int t = 0; t < T && ok; t++, i++) {
+            for (int p = 0; p < P && ok; p++, i++) {
                 const int buf = (base + i) % NB;
                 wait_mma(base + i - NB + 1);   // the MMAs that read this buffer NB pieces ago
                 uint8_t *bt = b_tile + buf * B_BYTES + b_off;
-                *reinterpret_cast<uint4 *>(bt) = nb[0];
-                *reinterpret_cast<uint4 *>(bt + PF_NT * 16) = nb[1];   // the next 16-byte K chunk
-                load_b(i + 1);
+#pragma unroll
+                for (int c = 0; c < CPT; c++) *reinterpret_cast<uint4 *>(bt + c * (PT * 16)) = nb[c];   // consecutive 16-byte K chunks
+                load_b();
                 tc_fence_before();
                 __syncthreads();
                 if (tid == 0) {
@@ -874,10 +882,11 @@ __global__ void __launch_bounds__(DN_THREADS, 2) k_down_prefill(const DownArgs A
                     tc_fence_after();
                     // a K slice of 16 halves is two 16-byte chunks further on: the descriptor's address field moves with it
                     const uint64_t db0 = desc_b0 + (uint64_t)((buf * B_BYTES) >> 4);
+                    const uint32_t idesc = (TPP == 2 && 2 * p + 1 < T) ? IDESC2 : IDESC1;   // two tiles: N = 128 over their 128 columns
 #pragma unroll
                     for (int ks = 0; ks < DN_KSTEP / 16; ks++)   // 16 halves = 32 bytes of K per instruction
-                        mma_f16(tmem + 64 * t, desc_a0 + (uint64_t)(ks * ((2 * PF_M * 16) >> 4)),
-                                db0 + (uint64_t)(ks * ((2 * PF_NT * 16) >> 4)), IDESC, (s > 0 || ks > 0) ? 1u : 0u);
+                        mma_f16(tmem + 64 * TPP * p, desc_a0 + (uint64_t)(ks * ((2 * PF_M * 16) >> 4)),
+                                db0 + (uint64_t)(ks * ((2 * PT * 16) >> 4)), idesc, (s > 0 || ks > 0) ? 1u : 0u);
                     tc_commit(&S.bar_b[buf]);
                 }
                 committed++;
@@ -1057,7 +1066,7 @@ bool prefill_down_supported(const LayerDev &L, bool routed, bool shared)
 template <int DT>
 static cudaError_t launch_down_t(const DownArgs &A, dim3 grid, cudaStream_t s)
 {
-    constexpr size_t smem = PF_M * DN_KSTEP * 2 + DownCfg<DT>::NB * PF_NT * DN_KSTEP * 2 +
+    constexpr size_t smem = PF_M * DN_KSTEP * 2 + DownCfg<DT>::NB * DownCfg<DT>::PT * DN_KSTEP * 2 +
                             ((PF_M * DownDequant<DT>::ROW_BYTES + 127) / 128) * 128 + sizeof(DownSmemHdr) + 128;
     static_assert(smem <= 115712, "two CTAs of the down GEMM share an SM");
     static bool configured = false;
