@@ -94,6 +94,19 @@ __device__ inline uint64_t smem_desc(const void *p, uint32_t lbo, uint32_t sbo)
     d |= (uint64_t)1 << 46;  // descriptor version of this architecture
     return d;
 }
+// The same for the 128-byte swizzled K-major layout: a row is 128 contiguous bytes (64 halves of K) whose 16-byte
+// chunks sit at chunk ^ (row & 7); 8-row groups are 1024 bytes apart; the tile starts on a 1024-byte boundary.  A K
+// slice of 16 halves is 32 bytes further on in the start address.
+__device__ inline uint64_t smem_desc_sw128(const void *p)
+{
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_u32(p) & 0x3FFFF) >> 4);
+    d |= (uint64_t)1 << 16;            // leading byte offset: not used by this layout
+    d |= (uint64_t)(1024 >> 4) << 32;  // stride between 8-row groups
+    d |= (uint64_t)1 << 46;            // descriptor version of this architecture
+    d |= (uint64_t)2 << 61;            // 128-byte swizzle
+    return d;
+}
 // Instruction descriptor: D format (1 = f32, 2 = s32) | A/B formats | N/8 | M/16; K-major A and B.
 __device__ constexpr uint32_t make_idesc(uint32_t cfmt, uint32_t afmt, uint32_t bfmt, uint32_t n, uint32_t m)
 {
@@ -744,11 +757,12 @@ __global__ void __launch_bounds__(DN_THREADS, 2) k_down_prefill(const DownArgs A
     constexpr int NB = DownCfg<DT>::NB;
     constexpr int RAW_BYTES = PF_M * DQ::ROW_BYTES;
     constexpr int PT = DownCfg<DT>::PT, TPP = PT / PF_NT;        // tokens and token tiles of a B piece
-    constexpr int TPT = DN_THREADS / PT, CPT = 8 / TPT;          // threads of a token, 16-byte chunks of a thread
+    constexpr int LPT = PT / 32;                                 // B side: tokens of a thread (eight threads share a token)
     constexpr int B_BYTES = PT * DN_KSTEP * 2;
-    uint8_t *a_tile = smem_raw;                                  // [128 rows][64 K] fp16, core-matrix layout
-    uint8_t *b_tile = a_tile + PF_M * DN_KSTEP * 2;              // NB x [PT tokens][64 K] fp16, same layout
-    uint8_t *raw = b_tile + NB * B_BYTES;                        // the run's GGUF rows
+    // B tiles first, on a 1024-byte boundary (their swizzled layout wants it)
+    uint8_t *b_tile = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);   // NB x [PT tokens][64 K] fp16, 128-byte swizzle
+    uint8_t *a_tile = b_tile + NB * B_BYTES;                     // [128 rows][64 K] fp16, core-matrix layout
+    uint8_t *raw = a_tile + PF_M * DN_KSTEP * 2;                 // the run's GGUF rows
     DownSmemHdr &S = *reinterpret_cast<DownSmemHdr *>(raw + ((RAW_BYTES + 127) / 128) * 128);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
@@ -781,8 +795,8 @@ __global__ void __launch_bounds__(DN_THREADS, 2) k_down_prefill(const DownArgs A
     constexpr uint32_t IDESC1 = make_idesc(1, 0, 0, PF_NT, PF_M), IDESC2 = make_idesc(1, 0, 0, 2 * PF_NT, PF_M);  // f16 x f16 -> f32
     const int steps = A.F / DN_KSTEP;
     const int r = tid & (PF_M - 1), part = tid >> 7;               // dequantisation: row and half of the step
-    const int tk = tid / TPT, ksub = tid % TPT;                    // B side: CPT chunks of one of a piece's PT tokens per thread
-    const uint64_t desc_a0 = smem_desc(a_tile, PF_M * 16, 128), desc_b0 = smem_desc(b_tile, PT * 16, 128);
+    const int tk0 = tid >> 3, chunk = tid & 7;                     // B side: chunk `chunk` of tokens tk0 + 32 j: a warp reads four whole rows
+    const uint64_t desc_a0 = smem_desc(a_tile, PF_M * 16, 128), desc_b0 = smem_desc_sw128(b_tile);
 
     // MMA commits are counted over the CTA's life: commit c lands on barrier c % NB as its (c / NB)-th completion
     int committed = 0, seen = 0;
@@ -837,22 +851,22 @@ __global__ void __launch_bounds__(DN_THREADS, 2) k_down_prefill(const DownArgs A
 
         // A B piece holds the activations of TPP token tiles of the run (the last one of an odd run holds one): pieces
         // are numbered i = s * P + p with P = ceil(T / TPP); piece i is the CTA's commit base + i and sits in that
-        // commit's buffer.  It travels global -> registers -> shared memory (16-byte loads and stores), loaded one
-        // piece ahead.  (A cp.async ring two pieces ahead measured the same; its copies cost one
+        // commit's buffer.  It travels global -> registers -> shared memory, loaded one piece ahead: eight threads read
+        // a token's 128 bytes (a warp reads four whole rows) and store them into one row of the 128-byte swizzled
+        // layout, without bank conflicts on either side.  (A cp.async ring two pieces ahead measured the same; its copies cost one
         // shared-memory wavefront per lane where these stores take four per warp.)
         const int P = (T + TPP - 1) / TPP, base = committed;
-        uint4 nb[CPT];
+        uint4 nb[LPT];
         int ls = 0, lp = 0;   // step and pair of the next piece to load
         auto load_b = [&]() {
 #pragma unroll
-            for (int c = 0; c < CPT; c++) nb[c] = make_uint4(0, 0, 0, 0);
+            for (int j = 0; j < LPT; j++) nb[j] = make_uint4(0, 0, 0, 0);
             if (ls < steps) {
-                const int t = TPP * lp + (tk >> 6);
-                const int rin = t < T ? S.row_in[t][tk & 63] : -1;
-                if (rin >= 0) {
-                    const uint4 *src = reinterpret_cast<const uint4 *>(A.act_h + (size_t)rin * A.F + ls * DN_KSTEP + 8 * CPT * ksub);
 #pragma unroll
-                    for (int c = 0; c < CPT; c++) nb[c] = src[c];
+                for (int j = 0; j < LPT; j++) {
+                    const int tok = tk0 + 32 * j, t = TPP * lp + (tok >> 6);
+                    const int rin = t < T ? S.row_in[t][tok & 63] : -1;
+                    if (rin >= 0) nb[j] = *reinterpret_cast<const uint4 *>(A.act_h + (size_t)rin * A.F + ls * DN_KSTEP + 8 * chunk);
                 }
                 if (++lp == P) { lp = 0; ls++; }
             }
@@ -863,7 +877,8 @@ __global__ void __launch_bounds__(DN_THREADS, 2) k_down_prefill(const DownArgs A
             ok = false;
         }
         ph_raw ^= 1;
-        const uint32_t b_off = core_off(PT, tk, 16 * CPT * ksub);
+        // token tk0 + 32 j: row group (tk0 >> 3) + 4 j, row tk0 & 7 of it, chunk at chunk ^ row
+        const uint32_t b_off = (uint32_t)((tk0 >> 3) * 1024 + (tk0 & 7) * 128 + ((chunk ^ (tk0 & 7)) << 4));
         for (int s = 0, i = 0; s < steps && ok; s++) {
             wait_mma(base + i);   // the previous step's MMAs still read the A tile
             tc_fence_after();
@@ -873,7 +888,7 @@ __global__ void __launch_bounds__(DN_THREADS, 2) k_down_prefill(const DownArgs A
                 wait_mma(base + i - NB + 1);   // the MMAs that read this buffer NB pieces ago
                 uint8_t *bt = b_tile + buf * B_BYTES + b_off;
 #pragma unroll
-                for (int c = 0; c < CPT; c++) *reinterpret_cast<uint4 *>(bt + c * (PT * 16)) = nb[c];   // consecutive 16-byte K chunks
+                for (int j = 0; j < LPT; j++) *reinterpret_cast<uint4 *>(bt + 4096 * j) = nb[j];   // 32 tokens = four row groups on
                 load_b();
                 tc_fence_before();
                 __syncthreads();
@@ -886,7 +901,7 @@ __global__ void __launch_bounds__(DN_THREADS, 2) k_down_prefill(const DownArgs A
 #pragma unroll
                     for (int ks = 0; ks < DN_KSTEP / 16; ks++)   // 16 halves = 32 bytes of K per instruction
                         mma_f16(tmem + 64 * TPP * p, desc_a0 + (uint64_t)(ks * ((2 * PF_M * 16) >> 4)),
-                                db0 + (uint64_t)(ks * ((2 * PT * 16) >> 4)), idesc, (s > 0 || ks > 0) ? 1u : 0u);
+                                db0 + (uint64_t)(ks * (32 >> 4)), idesc, (s > 0 || ks > 0) ? 1u : 0u);
                     tc_commit(&S.bar_b[buf]);
                 }
                 committed++;
@@ -1067,7 +1082,7 @@ template <int DT>
 static cudaError_t launch_down_t(const DownArgs &A, dim3 grid, cudaStream_t s)
 {
     constexpr size_t smem = PF_M * DN_KSTEP * 2 + DownCfg<DT>::NB * DownCfg<DT>::PT * DN_KSTEP * 2 +
-                            ((PF_M * DownDequant<DT>::ROW_BYTES + 127) / 128) * 128 + sizeof(DownSmemHdr) + 128;
+                            ((PF_M * DownDequant<DT>::ROW_BYTES + 127) / 128) * 128 + sizeof(DownSmemHdr) + 128 + 1024;
     static_assert(smem <= 115712, "two CTAs of the down GEMM share an SM");
     static bool configured = false;
     if (!configured) {
