@@ -733,11 +733,12 @@ constexpr int DN_THREADS = 256;
 constexpr int DN_TILES = 4;      // 4 x 64 columns = half of tensor memory
 constexpr int DN_COLS = 64 * DN_TILES;
 
-// A B piece holds 128 tokens -- two token tiles of a run share an MMA of N = 128 -- in two buffers; Q8_0 rows are
-// the widest and leave room for 64-token pieces in three buffers only.
+// A B piece holds all four token tiles of a run (256 tokens: one MMA of N = 64 .. 256 per K slice) in a single buffer:
+// a step is then one wait, one dequantisation, one store of the piece, one barrier.  Q8_0 rows are the widest and
+// leave room for 128-token pieces only.
 template <int DT> struct DownCfg {
-    static constexpr int PT = DT == PMOE_Q8_0 ? PF_NT : 2 * PF_NT;   // tokens of a B piece
-    static constexpr int NB = DT == PMOE_Q8_0 ? 3 : 2;               // B buffers
+    static constexpr int PT = DT == PMOE_Q8_0 ? 2 * PF_NT : 4 * PF_NT;   // tokens of a B piece
+    static constexpr int NB = 1;                                         // B buffers
 };
 
 struct DownSmemHdr {
@@ -792,7 +793,6 @@ __global__ void __launch_bounds__(DN_THREADS, 2) k_down_prefill(const DownArgs A
     const uint32_t tmem = S.tmem_base;
     const int n_entries = S.n_entries;
     const int h0 = blockIdx.x * PF_M;
-    constexpr uint32_t IDESC1 = make_idesc(1, 0, 0, PF_NT, PF_M), IDESC2 = make_idesc(1, 0, 0, 2 * PF_NT, PF_M);  // f16 x f16 -> f32
     const int steps = A.F / DN_KSTEP;
     const int r = tid & (PF_M - 1), part = tid >> 7;               // dequantisation: row and half of the step
     const int tk0 = tid >> 3, chunk = tid & 7;                     // B side: chunk `chunk` of tokens tk0 + 32 j: a warp reads four whole rows
@@ -888,7 +888,7 @@ __global__ void __launch_bounds__(DN_THREADS, 2) k_down_prefill(const DownArgs A
                 wait_mma(base + i - NB + 1);   // the MMAs that read this buffer NB pieces ago
                 uint8_t *bt = b_tile + buf * B_BYTES + b_off;
 #pragma unroll
-                for (int j = 0; j < LPT; j++) *reinterpret_cast<uint4 *>(bt + 4096 * j) = nb[j];   // 32 tokens = four row groups on
+                for (int j = 0; j < LPT; j++) *reinterpret_cast<uint4 *>(bt + 4096 * j) = nb[j];   // 32 tokens on = four row groups on
                 load_b();
                 tc_fence_before();
                 __syncthreads();
@@ -897,7 +897,8 @@ __global__ void __launch_bounds__(DN_THREADS, 2) k_down_prefill(const DownArgs A
                     tc_fence_after();
                     // a K slice of 16 halves is two 16-byte chunks further on: the descriptor's address field moves with it
                     const uint64_t db0 = desc_b0 + (uint64_t)((buf * B_BYTES) >> 4);
-                    const uint32_t idesc = (TPP == 2 && 2 * p + 1 < T) ? IDESC2 : IDESC1;   // two tiles: N = 128 over their 128 columns
+                    const int tp = T - TPP * p < TPP ? T - TPP * p : TPP;               // token tiles of this piece
+                    const uint32_t idesc = make_idesc(1, 0, 0, PF_NT * tp, PF_M);       // f16 x f16 -> f32, N = 64 tp over its columns
 #pragma unroll
                     for (int ks = 0; ks < DN_KSTEP / 16; ks++)   // 16 halves = 32 bytes of K per instruction
                         mma_f16(tmem + 64 * TPP * p, desc_a0 + (uint64_t)(ks * ((2 * PF_M * 16) >> 4)),
