@@ -235,13 +235,15 @@ __global__ void __launch_bounds__(GU_THREADS, 2) k_gu_prefill(const GuArgs A)
 
     for (int b = 0; b < nblk && ok; b++) {
         // ---- start this block's activation loads first: they fly while the weights are decoded
-        const int tk = tid >> 2, quarter = tid & 3;   // 64 bytes of one token's block per thread
+        // 64 bytes of one token's block per thread: chunks quarter, quarter + 4, ... so that the four threads of a token
+        // read 64 contiguous bytes with every load (a warp's load touches 16 whole sectors instead of 32 half-used ones)
+        const int tk = tid >> 2, quarter = tid & 3;
         const int rin_b = S.row_in[tk];
         uint4 bv[4];
         {
-            const uint4 *src = reinterpret_cast<const uint4 *>(A.xq.qs + (size_t)(rin_b >= 0 ? rin_b : 0) * A.H + b * QK_K + 64 * quarter);
+            const uint4 *src = reinterpret_cast<const uint4 *>(A.xq.qs + (size_t)(rin_b >= 0 ? rin_b : 0) * A.H + b * QK_K) + quarter;
 #pragma unroll
-            for (int i = 0; i < 4; i++) bv[i] = rin_b >= 0 ? src[i] : make_uint4(0, 0, 0, 0);
+            for (int i = 0; i < 4; i++) bv[i] = rin_b >= 0 ? src[4 * i] : make_uint4(0, 0, 0, 0);
         }
         uint4 bs0 = make_uint4(0, 0, 0, 0), bs1 = make_uint4(0, 0, 0, 0);
         float dx_reg = 0.f;
@@ -296,7 +298,7 @@ __global__ void __launch_bounds__(GU_THREADS, 2) k_gu_prefill(const GuArgs A)
         // ---- B: the tile's quantised activations for this block; token = tid / 4, 64 bytes each
 #pragma unroll
         for (int i = 0; i < 4; i++)
-            *reinterpret_cast<uint4 *>(S.b + core_off(PF_NT, tk, 64 * quarter + 16 * i)) = bv[i];
+            *reinterpret_cast<uint4 *>(S.b + core_off(PF_NT, tk, 16 * (quarter + 4 * i))) = bv[i];
         if (tid < PF_NT) {  // partial sums of 16 quants as two digits: bsum = 64*h + l, l in [0,63]
             uint32_t hw[4] = {0, 0, 0, 0}, lw[4] = {0, 0, 0, 0};
             const float dx = dx_reg;
@@ -313,11 +315,11 @@ __global__ void __launch_bounds__(GU_THREADS, 2) k_gu_prefill(const GuArgs A)
             *reinterpret_cast<uint4 *>(S.bl + core_off(PF_NT, tid, 16)) = make_uint4(0, 0, 0, 0);
             S.dx[tid] = dx;
         }
-        fence_proxy_async();   // generic-proxy writes above become visible to the tensor core
         tc_fence_before();
         __syncthreads();
         // ---- MMAs of this block, issued by one thread
         if (tid == 0) {
+            fence_proxy_async();   // everyone's stores are ordered before the barrier; the issuing thread crosses over to the async proxy
             tc_fence_after();
 #pragma unroll
             for (int ks = 0; ks < 8; ks++) {  // 32 bytes of K per instruction: two 16-byte chunks further on per step
@@ -519,10 +521,10 @@ __global__ void __launch_bounds__(GU_THREADS, 2) k_gu_prefill_q80(const GuArgs A
         *reinterpret_cast<uint4 *>(S.o.b + core_off(PF_NT, tk, 32 * quarter)) = bv[0];
         *reinterpret_cast<uint4 *>(S.o.b + core_off(PF_NT, tk, 32 * quarter + 16)) = bv[1];
         S.o.dx[quarter][tk] = dxv;
-        fence_proxy_async();   // generic-proxy writes above become visible to the tensor core
         tc_fence_before();
         __syncthreads();
         if (tid == 0) {
+            fence_proxy_async();   // everyone's stores are ordered before the barrier; the issuing thread crosses over to the async proxy
             tc_fence_after();
 #pragma unroll
             for (int j = 0; j < 4; j++)   // one block = 32 bytes of K = one instruction, its own 64 columns
