@@ -31,6 +31,7 @@ namespace pmoe {
 constexpr int PF_NT = 64;        // tokens per tile (MMA N)
 constexpr int PF_M = 128;        // rows per tile (MMA M): 64 gate + 64 up
 constexpr int PF_THREADS = 128;
+constexpr int GU_REPS = 2;        // token tiles a CTA of the Q4_K gate/up kernel takes, one after the other
 constexpr int GU_THREADS = 256;   // gate/up kernel: two threads per weight row (one per half of a 256-wide block)
 constexpr int PF_TMEM_COLS = 256;  // D0, D1, Dh, Dl: 4 x 64 columns of s32
 
@@ -159,8 +160,23 @@ __global__ void __launch_bounds__(GU_THREADS, 2) k_gu_prefill(const GuArgs A)
     const int n_active = A.routed ? *A.g.n_active : 0;
     const int routed_tiles = n_active ? A.tile_prefix[n_active] : 0;
     const int shared_tiles = A.has_shared ? (A.sh_count + PF_NT - 1) / PF_NT : 0;
-    const int tile = blockIdx.y;
-    if (tile >= routed_tiles + shared_tiles) return;
+    const int total_tiles = routed_tiles + shared_tiles, first = blockIdx.y * GU_REPS;
+    if (first >= total_tiles) return;
+    if (tid == 0) {
+        mbar_init(&S.bar, 1);
+        fence_mbar_init();
+    }
+    if (warp == 0) tmem_alloc(&S.tmem_base, PF_TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = S.tmem_base;
+    uint32_t phase = 0;
+    bool ok = true;
+    // the CTA's tiles, one after the other: set-up (tensor memory, barrier) is paid once, and the second tile of an
+    // expert finds the rows the first one read in the caches
+    for (int rep = 0; rep < GU_REPS && first + rep < total_tiles && ok; rep++) {
+    const int tile = first + rep;
     if (tid == 0) {
         if (tile < routed_tiles) {
             const int2 ti = A.g.tile_table[tile];  // (local expert, tile inside the expert)
@@ -170,14 +186,8 @@ __global__ void __launch_bounds__(GU_THREADS, 2) k_gu_prefill(const GuArgs A)
             S.slot = -1;
             S.tile_in_slot = tile - routed_tiles;
         }
-        mbar_init(&S.bar, 1);
-        fence_mbar_init();
     }
-    if (warp == 0) tmem_alloc(&S.tmem_base, PF_TMEM_COLS);
-    tc_fence_before();
     __syncthreads();
-    tc_fence_after();
-    const uint32_t tmem = S.tmem_base;
     const int slot = S.slot, t0 = S.tile_in_slot * PF_NT;
     const bool is_shared = slot < 0;
     int m;
@@ -223,8 +233,6 @@ __global__ void __launch_bounds__(GU_THREADS, 2) k_gu_prefill(const GuArgs A)
     float acc[NC];
 #pragma unroll
     for (int i = 0; i < NC; i++) acc[i] = 0.f;
-    uint32_t phase = 0;
-    bool ok = true;
 
     // the thread's half of the row's current block lives in registers (header + 64 bytes of quants);
     // the next one is fetched while the MMAs run
@@ -384,7 +392,10 @@ __global__ void __launch_bounds__(GU_THREADS, 2) k_gu_prefill(const GuArgs A)
             A.act[(size_t)rout * A.F + f0 + f] = g / (1.f + expf(-g)) * u;
         }
     }
-    __syncthreads();
+    tc_fence_before();
+    __syncthreads();   // tiles, tables and accumulators are free for the CTA's next tile
+    tc_fence_after();
+    }
     if (warp == 0) tmem_dealloc(tmem, PF_TMEM_COLS);
 }
 
@@ -1068,7 +1079,7 @@ cudaError_t launch_gate_up_prefill(const LayerDev &L, const Workspace &ws, int n
     const int tiles = (routed ? max_routed_tiles(L, n, top_k) : 0) + (shared ? (ws.sh_count + PF_NT - 1) / PF_NT : 0);
     dim3 grid(L.F / 64, tiles);
     if (dt == PMOE_Q8_0) k_gu_prefill_q80<<<grid, GU_THREADS, sizeof(Gu80Smem) + 128, s>>>(A);
-    else k_gu_prefill<<<grid, GU_THREADS, sizeof(GuSmem) + 128, s>>>(A);
+    else k_gu_prefill<<<dim3(L.F / 64, (tiles + GU_REPS - 1) / GU_REPS), GU_THREADS, sizeof(GuSmem) + 128, s>>>(A);
     count_launch();
     return cudaGetLastError();
 }
