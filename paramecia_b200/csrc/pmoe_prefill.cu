@@ -384,12 +384,24 @@ __global__ void __launch_bounds__(GU_THREADS, 2) k_gu_prefill(const GuArgs A)
     for (int j = 0; j < NC; j++) xch[r * (PF_NT + 1) + kh * NC + j] = acc[j];
     __syncthreads();
     if (ok) {
-        for (int o = tid; o < 64 * PF_NT; o += GU_THREADS) {
-            const int f = o & 63, j = o >> 6;
-            const int rout = S.row_out[j];
-            if (rout < 0) continue;
-            const float g = xch[f * (PF_NT + 1) + j], u = xch[(64 + f) * (PF_NT + 1) + j];
-            A.act[(size_t)rout * A.F + f0 + f] = g / (1.f + expf(-g)) * u;
+        // thread: column f = tid & 63 of tokens (tid >> 6) + 4 i; four tokens at a time, so that their exponentials
+        // and divisions overlap
+        const int f = tid & 63;
+        const float *xg = xch + f * (PF_NT + 1), *xu = xch + (64 + f) * (PF_NT + 1);
+#pragma unroll 1
+        for (int j0 = tid >> 6; j0 < PF_NT; j0 += 16) {
+            float v[4];
+            int rout[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const int j = j0 + 4 * i;
+                rout[i] = S.row_out[j];
+                const float g = xg[j], u = xu[j];
+                v[i] = g / (1.f + expf(-g)) * u;
+            }
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+                if (rout[i] >= 0) A.act[(size_t)rout[i] * A.F + f0 + f] = v[i];
         }
     }
     tc_fence_before();
