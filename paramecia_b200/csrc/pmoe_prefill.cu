@@ -512,11 +512,26 @@ __global__ void __launch_bounds__(GU_THREADS, 2) k_gu_prefill_q80(const GuArgs A
     // the thread's two blocks of the current step: 68 bytes from a 4-byte boundary
     //   [0,2) d of block 0 | [2,34) its quants | [34,36) d of block 1 | [36,68) its quants
     uint32_t raw[17];
-    {
-        const uint32_t *src = reinterpret_cast<const uint32_t *>(wrow + 68 * kh);
+    // 8-byte loads: a row's step starts on an 8-byte boundary (136 s), its second half 4 bytes off one
+    auto load_raw = [&](int s) {
+        const uint8_t *p = wrow + (size_t)s * 136 + 68 * kh;
+        if (kh == 0) {
 #pragma unroll
-        for (int i = 0; i < 17; i++) raw[i] = src[i];
-    }
+            for (int i = 0; i < 8; i++) {
+                const uint2 v = reinterpret_cast<const uint2 *>(p)[i];
+                raw[2 * i] = v.x; raw[2 * i + 1] = v.y;
+            }
+            raw[16] = *reinterpret_cast<const uint32_t *>(p + 64);
+        } else {
+            raw[0] = *reinterpret_cast<const uint32_t *>(p);
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const uint2 v = reinterpret_cast<const uint2 *>(p + 4)[i];
+                raw[1 + 2 * i] = v.x; raw[2 + 2 * i] = v.y;
+            }
+        }
+    };
+    load_raw(0);
     for (int s = 0; s < steps && ok; s++) {
         // ---- this step's activations first: they fly while the weights are laid out
         uint4 bv[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
@@ -555,11 +570,7 @@ __global__ void __launch_bounds__(GU_THREADS, 2) k_gu_prefill_q80(const GuArgs A
                        IDESC_SS, 0);
             tc_commit(&S.bar);
         }
-        if (s + 1 < steps) {   // the next step's blocks, in flight during the MMAs and the fold
-            const uint32_t *src = reinterpret_cast<const uint32_t *>(wrow + (size_t)(s + 1) * 136 + 68 * kh);
-#pragma unroll
-            for (int i = 0; i < 17; i++) raw[i] = src[i];
-        }
+        if (s + 1 < steps) load_raw(s + 1);   // the next step's blocks, in flight during the MMAs and the fold
         if (!mbar_wait_spin(&S.bar, phase)) {
             set_status(A.status, PMOE_ERR_TIMEOUT, 35, s);
             ok = false;
