@@ -429,12 +429,17 @@ struct Gu80Smem {
         Gu80Ops o;                           // operands and scales of one step
         float xch[PF_M * (PF_NT + 1)];       // the accumulators' way to silu(gate) * up at the end
     };
+    // the rows' raw bytes, two steps (eight blocks, 272 bytes a row) at a time, double-buffered: one bulk copy a row
+    // (whole lines from memory, where 32 lanes loading from 32 rows would touch 32 lines with every instruction)
+    uint8_t raw[2][PF_M][8 * Q8_0_BYTES];
     int row_in[PF_NT];
     int row_out[PF_NT];
-    uint64_t bar;
+    uint64_t bar, bar_raw[2];
     uint32_t tmem_base;
     int slot, tile_in_slot;
 };
+static_assert(sizeof(Gu80Smem) + 128 <= 115712, "two CTAs of the Q8_0 gate/up GEMM share an SM");
+static_assert((8 * Q8_0_BYTES) % 16 == 0, "bulk copies need 16-byte alignment");
 
 __global__ void __launch_bounds__(GU_THREADS, 2) k_gu_prefill_q80(const GuArgs A)
 {
@@ -457,6 +462,8 @@ __global__ void __launch_bounds__(GU_THREADS, 2) k_gu_prefill_q80(const GuArgs A
             S.tile_in_slot = tile - routed_tiles;
         }
         mbar_init(&S.bar, 1);
+        mbar_init(&S.bar_raw[0], 1);
+        mbar_init(&S.bar_raw[1], 1);
         fence_mbar_init();
     }
     if (warp == 0) tmem_alloc(&S.tmem_base, PF_TMEM_COLS);
@@ -511,28 +518,47 @@ __global__ void __launch_bounds__(GU_THREADS, 2) k_gu_prefill_q80(const GuArgs A
 
     // the thread's two blocks of the current step: 68 bytes from a 4-byte boundary
     //   [0,2) d of block 0 | [2,34) its quants | [34,36) d of block 1 | [36,68) its quants
+    // chunk c = steps 2c, 2c + 1 of all 128 rows -> raw[c & 1]; its barrier completes for the (c >> 1)-th time
+    constexpr int CHUNK = 8 * Q8_0_BYTES;
+    const int chunks = steps / 2;
+    auto fetch_chunk = [&](int c) {
+        if (tid == 0) mbar_expect_tx(&S.bar_raw[c & 1], PF_M * CHUNK);
+        if (tid < PF_M) bulk_g2s(S.raw[c & 1][r], wrow + (size_t)c * CHUNK, CHUNK, &S.bar_raw[c & 1]);
+    };
+    fetch_chunk(0);
+    if (chunks > 1) fetch_chunk(1);
+    int chunks_seen = 0, chunks_issued = chunks > 1 ? 2 : 1;
     uint32_t raw[17];
-    // 8-byte loads: a row's step starts on an 8-byte boundary (136 s), its second half 4 bytes off one
-    auto load_raw = [&](int s) {
-        const uint8_t *p = wrow + (size_t)s * 136 + 68 * kh;
-        if (kh == 0) {
-#pragma unroll
-            for (int i = 0; i < 8; i++) {
-                const uint2 v = reinterpret_cast<const uint2 *>(p)[i];
-                raw[2 * i] = v.x; raw[2 * i + 1] = v.y;
+    for (int s = 0; s < steps && ok; s++) {
+        if ((s & 1) == 0) {
+            const int c = s >> 1;
+            // the buffer chunk c - 1 sat in is free: its last readers passed the barrier that ended step s - 1
+            if (c >= 1 && c + 1 < chunks) { fetch_chunk(c + 1); chunks_issued = c + 2; }
+            if (!mbar_wait(&S.bar_raw[c & 1], (uint32_t)((c >> 1) & 1))) {
+                set_status(A.status, PMOE_ERR_TIMEOUT, 36, c);
+                ok = false;
+                break;
             }
-            raw[16] = *reinterpret_cast<const uint32_t *>(p + 64);
-        } else {
-            raw[0] = *reinterpret_cast<const uint32_t *>(p);
+            chunks_seen = c + 1;
+        }
+        {   // this thread's two blocks: 68 bytes, 4-byte aligned (a step starts on an 8-byte boundary)
+            const uint8_t *p = S.raw[(s >> 1) & 1][r] + 136 * (s & 1) + 68 * kh;
+            if (kh == 0) {
 #pragma unroll
-            for (int i = 0; i < 8; i++) {
-                const uint2 v = reinterpret_cast<const uint2 *>(p + 4)[i];
-                raw[1 + 2 * i] = v.x; raw[2 + 2 * i] = v.y;
+                for (int i = 0; i < 8; i++) {
+                    const uint2 v = reinterpret_cast<const uint2 *>(p)[i];
+                    raw[2 * i] = v.x; raw[2 * i + 1] = v.y;
+                }
+                raw[16] = *reinterpret_cast<const uint32_t *>(p + 64);
+            } else {
+                raw[0] = *reinterpret_cast<const uint32_t *>(p);
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    const uint2 v = reinterpret_cast<const uint2 *>(p + 4)[i];
+                    raw[1 + 2 * i] = v.x; raw[2 + 2 * i] = v.y;
+                }
             }
         }
-    };
-    load_raw(0);
-    for (int s = 0; s < steps && ok; s++) {
         // ---- this step's activations first: they fly while the weights are laid out
         uint4 bv[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
         float dxv = 0.f;
@@ -570,7 +596,6 @@ __global__ void __launch_bounds__(GU_THREADS, 2) k_gu_prefill_q80(const GuArgs A
                        IDESC_SS, 0);
             tc_commit(&S.bar);
         }
-        if (s + 1 < steps) load_raw(s + 1);   // the next step's blocks, in flight during the MMAs and the fold
         if (!mbar_wait_spin(&S.bar, phase)) {
             set_status(A.status, PMOE_ERR_TIMEOUT, 35, s);
             ok = false;
@@ -617,6 +642,9 @@ __global__ void __launch_bounds__(GU_THREADS, 2) k_gu_prefill_q80(const GuArgs A
             const float g = xch[f * (PF_NT + 1) + j], u = xch[(64 + f) * (PF_NT + 1) + j];
             A.act[(size_t)rout * A.F + f0 + f] = g / (1.f + expf(-g)) * u;
         }
+    }
+    if (!ok) {   // gave up somewhere: chunks may still be on their way into this CTA's shared memory
+        for (int c = chunks_seen; c < chunks_issued; c++) mbar_wait(&S.bar_raw[c & 1], (uint32_t)((c >> 1) & 1));
     }
     __syncthreads();
     if (warp == 0) tmem_dealloc(tmem, PF_TMEM_COLS);
