@@ -530,6 +530,16 @@ __global__ void __launch_bounds__(GU_THREADS, 2) k_gu_prefill_q80(const GuArgs A
     int chunks_seen = 0, chunks_issued = chunks > 1 ? 2 : 1;
     uint32_t raw[17];
     for (int s = 0; s < steps && ok; s++) {
+        // ---- this step's activations first: they fly while the weights are laid out.  Chunks quarter and quarter + 4
+        // of the token's 128 bytes: the four threads of a token read 64 contiguous bytes with each load.
+        uint4 bv[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
+        float dxv = 0.f;
+        if (rin_b >= 0) {
+            const uint4 *src = reinterpret_cast<const uint4 *>(A.xq.qs + (size_t)rin_b * A.H + 128 * s) + quarter;
+            bv[0] = src[0];
+            bv[1] = src[4];
+            dxv = A.xq.d[(size_t)rin_b * nkb + 4 * s + quarter];
+        }
         if ((s & 1) == 0) {
             const int c = s >> 1;
             // the buffer chunk c - 1 sat in is free: its last readers passed the barrier that ended step s - 1
@@ -559,15 +569,6 @@ __global__ void __launch_bounds__(GU_THREADS, 2) k_gu_prefill_q80(const GuArgs A
                 }
             }
         }
-        // ---- this step's activations first: they fly while the weights are laid out
-        uint4 bv[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
-        float dxv = 0.f;
-        if (rin_b >= 0) {
-            const uint4 *src = reinterpret_cast<const uint4 *>(A.xq.qs + (size_t)rin_b * A.H + 128 * s + 32 * quarter);
-            bv[0] = src[0];
-            bv[1] = src[1];
-            dxv = A.xq.d[(size_t)rin_b * nkb + 4 * s + quarter];
-        }
         // ---- A: the row's two blocks of quants
         {
             uint32_t q0[8];
@@ -582,8 +583,8 @@ __global__ void __launch_bounds__(GU_THREADS, 2) k_gu_prefill_q80(const GuArgs A
             S.o.dw[2 * kh + 1][r] = half_bits_to_float((uint16_t)(raw[8] >> 16));
         }
         // ---- B: block `quarter` of token tk
-        *reinterpret_cast<uint4 *>(S.o.b + core_off(PF_NT, tk, 32 * quarter)) = bv[0];
-        *reinterpret_cast<uint4 *>(S.o.b + core_off(PF_NT, tk, 32 * quarter + 16)) = bv[1];
+        *reinterpret_cast<uint4 *>(S.o.b + core_off(PF_NT, tk, 16 * quarter)) = bv[0];
+        *reinterpret_cast<uint4 *>(S.o.b + core_off(PF_NT, tk, 16 * (quarter + 4))) = bv[1];
         S.o.dx[quarter][tk] = dxv;
         tc_fence_before();
         __syncthreads();
@@ -635,12 +636,24 @@ __global__ void __launch_bounds__(GU_THREADS, 2) k_gu_prefill_q80(const GuArgs A
     for (int j = 0; j < NC; j++) xch[r * (PF_NT + 1) + kh * NC + j] = acc[j];
     __syncthreads();
     if (ok) {
-        for (int o = tid; o < 64 * PF_NT; o += GU_THREADS) {
-            const int f = o & 63, j = o >> 6;
-            const int rout = S.row_out[j];
-            if (rout < 0) continue;
-            const float g = xch[f * (PF_NT + 1) + j], u = xch[(64 + f) * (PF_NT + 1) + j];
-            A.act[(size_t)rout * A.F + f0 + f] = g / (1.f + expf(-g)) * u;
+        // thread: column f = tid & 63 of tokens (tid >> 6) + 4 i; four tokens at a time, so that their exponentials
+        // and divisions overlap
+        const int f = tid & 63;
+        const float *xg = xch + f * (PF_NT + 1), *xu = xch + (64 + f) * (PF_NT + 1);
+#pragma unroll 1
+        for (int j0 = tid >> 6; j0 < PF_NT; j0 += 16) {
+            float v[4];
+            int rout[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const int j = j0 + 4 * i;
+                rout[i] = S.row_out[j];
+                const float g = xg[j], u = xu[j];
+                v[i] = g / (1.f + expf(-g)) * u;
+            }
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+                if (rout[i] >= 0) A.act[(size_t)rout[i] * A.F + f0 + f] = v[i];
         }
     }
     if (!ok) {   // gave up somewhere: chunks may still be on their way into this CTA's shared memory
