@@ -268,6 +268,131 @@ static cudaError_t launch_router_tiled(const LayerDev &L, const void *x, int n, 
     return e;
 }
 
+// The prefill-sized form of the same product on the packed f32x2 multiply-add of this architecture: one instruction
+// advances the sums of two tokens (each half is an IEEE fma of its own, so every (row, token) sum is still built in
+// the order above and the bits are the same).  The token tile lies in shared memory with the tokens of a pair
+// interleaved, in the order a lane reads it: for pair p, step i and half hf, lane l finds
+// (x0[j], x1[j], x0[j + 1], x1[j + 1]), j = 2 hf, of its elements 128 i + 4 l + j, at
+// ((p * steps + i) * 2 + hf) * 32 + l: 16 consecutive bytes per lane, no bank conflicts.
+__device__ inline uint64_t pack2(float lo, float hi)
+{
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ inline void unpack2(uint64_t v, float &lo, float &hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ inline uint64_t ffma2(uint64_t a, uint64_t b, uint64_t c)
+{
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+
+template <typename XT, int R, int T, int NW>
+__global__ void __launch_bounds__(NW * 32) k_router_pairs(const float *__restrict__ W, const float *__restrict__ bias,
+                                                                const XT *__restrict__ x, int n, int E, int H, int passes,
+                                                                float *__restrict__ logits)
+{
+    extern __shared__ __align__(16) float xs[];  // [T / 2][steps][2][32] float4
+    static_assert(T % 2 == 0, "tokens go in pairs");
+    if ((int)blockIdx.y == 0) {   // the CTAs of the first token tile cover every row once
+        for (int pass = 0; pass < passes; pass++) {
+            const int e0 = ((blockIdx.x * passes + pass) * NW + (threadIdx.x >> 5)) * R;
+#pragma unroll
+            for (int r_ = 0; r_ < R; r_++)
+                if (e0 + r_ < E) prefetch_row_l2(W + (size_t)(e0 + r_) * H, H, threadIdx.x & 31);
+        }
+    }
+    pdl_wait();
+    pdl_launch_dependents();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t0 = blockIdx.y * T;
+    const int nt = n - t0 < T ? n - t0 : T;
+    const int steps = H / 128;  // <= 16
+    // fill: one (pair, step, lane) item = the lane's four elements of both tokens
+    for (int it = threadIdx.x; it < (T / 2) * steps * 32; it += NW * 32) {
+        const int l = it & 31, i = (it >> 5) % steps, pr = (it >> 5) / steps;
+        float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
+        if (2 * pr < nt) a = load_x4(x, (size_t)(t0 + 2 * pr) * H + 128 * i + 4 * l);
+        if (2 * pr + 1 < nt) b = load_x4(x, (size_t)(t0 + 2 * pr + 1) * H + 128 * i + 4 * l);
+        float4 *dst = reinterpret_cast<float4 *>(xs) + ((size_t)(pr * steps + i) * 2) * 32 + l;
+        dst[0] = make_float4(a.x, b.x, a.y, b.y);
+        dst[32] = make_float4(a.z, b.z, a.w, b.w);
+    }
+    __syncthreads();
+    const ulonglong2 *xp = reinterpret_cast<const ulonglong2 *>(xs);
+    for (int pass = 0; pass < passes; pass++) {
+        const int e0 = ((blockIdx.x * passes + pass) * NW + warp) * R;
+        if (e0 >= E) break;
+        const float4 *w4[R];
+#pragma unroll
+        for (int r = 0; r < R; r++) w4[r] = reinterpret_cast<const float4 *>(W + (size_t)(e0 + r < E ? e0 + r : E - 1) * H) + lane;
+        uint64_t acc2[R * (T / 2)];   // (row r, pair p): the sums of tokens 2p (low half) and 2p + 1
+#pragma unroll
+        for (int i = 0; i < R * (T / 2); i++) acc2[i] = 0ull;
+#pragma unroll 1
+        for (int i = 0; i < steps; i++) {
+            uint64_t wd[R][4];   // the lane's four elements of each row, each in both halves
+#pragma unroll
+            for (int r = 0; r < R; r++) {
+                const float4 wv = w4[r][32 * i];
+                wd[r][0] = pack2(wv.x, wv.x);
+                wd[r][1] = pack2(wv.y, wv.y);
+                wd[r][2] = pack2(wv.z, wv.z);
+                wd[r][3] = pack2(wv.w, wv.w);
+            }
+#pragma unroll
+            for (int pr = 0; pr < T / 2; pr++) {
+                const ulonglong2 xa = xp[((size_t)(pr * steps + i) * 2) * 32 + lane];
+                const ulonglong2 xb = xp[((size_t)(pr * steps + i) * 2 + 1) * 32 + lane];
+#pragma unroll
+                for (int r = 0; r < R; r++) {
+                    uint64_t a = acc2[r * (T / 2) + pr];
+                    a = ffma2(xa.x, wd[r][0], a);
+                    a = ffma2(xa.y, wd[r][1], a);
+                    a = ffma2(xb.x, wd[r][2], a);
+                    a = ffma2(xb.y, wd[r][3], a);
+                    acc2[r * (T / 2) + pr] = a;
+                }
+            }
+        }
+        float acc[R * T];
+#pragma unroll
+        for (int r = 0; r < R; r++)
+#pragma unroll
+            for (int pr = 0; pr < T / 2; pr++) unpack2(acc2[r * (T / 2) + pr], acc[r * T + 2 * pr], acc[r * T + 2 * pr + 1]);
+        // fold 32 totals at a time: value index = r * T + tt, lane holds it
+        constexpr int V = 32;
+        static_assert(R * T % V == 0, "whole folds");
+#pragma unroll
+        for (int c = 0; c < R * T / V; c++) {
+            const float v = transposed_reduce<V, 32>(*reinterpret_cast<float(*)[V]>(acc + c * V), lane);
+            const int vi = c * V + lane;
+            const int r = vi / T, tt = vi % T;
+            if (tt < nt && e0 + r < E) logits[(size_t)(t0 + tt) * E + e0 + r] = bias ? __fadd_rn(v, bias[e0 + r]) : v;
+        }
+    }
+}
+
+template <typename XT, int R, int T, int NW>
+static cudaError_t launch_router_pairs(const LayerDev &L, const void *x, int n, int passes, float *logits, cudaStream_t s)
+{
+    auto kern = k_router_pairs<XT, R, T, NW>;
+    const size_t smem = (size_t)T * L.H * sizeof(float);
+    static bool configured = false;  // per instantiation
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, T * 2048 * (int)sizeof(float));
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    const int rows_per_cta = NW * R * passes;
+    dim3 grid((L.E + rows_per_cta - 1) / rows_per_cta, (n + T - 1) / T);
+    cudaError_t e = launch_pdl(kern, grid, dim3(NW * 32), smem, s, L.router_w, L.router_bias, (const XT *)x, n, L.E, L.H,
+                               passes, logits);
+    count_launch();
+    return e;
+}
+
 __global__ void k_add_bias(float *__restrict__ logits, const float *__restrict__ bias, int n, int E)
 {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -299,15 +424,15 @@ cudaError_t launch_router(const LayerDev &L, const Workspace &ws, const void *x,
     // (also for one token: with W cold in HBM, as it is when a model's layers take turns, the tiled kernel's
     // eight loads in flight per lane beat the row-per-warp kernel below: 27 -> 16 us)
     if (L.H <= 2048 && L.H % 128 == 0) {
-        if (n > 512) {  // prefill sizes: 16-token tiles (128 KB of shared memory), 64 rows per CTA
+        if (n > 512) {  // prefill sizes: 16-token tiles (128 KB of shared memory: one CTA per SM), 128 rows per CTA, packed
+            // multiply-adds; sixteen warps of 4 rows x 16 tokens each measured a little faster than eight of 8 x 16
             // (token preparation in its own launch: riding along it would hold 128 KB per token)
             if (prep) {
                 cudaError_t e = launch_prep(L, ws, x, x_dtype, n, need_q8k, need_q80, need_gate, s);
                 if (e != cudaSuccess) return e;
             }
-            const PrepArgs none = make_prep_args(L, ws, 0, need_q8k, need_q80, need_gate);
-            return f32 ? launch_router_tiled<float, 4, 16>(L, x, n, 8, logits, none, s)
-                       : launch_router_tiled<BT, 4, 16>(L, x, n, 8, logits, none, s);
+            return f32 ? launch_router_pairs<float, 4, 16, 16>(L, x, n, 2, logits, s)
+                       : launch_router_pairs<BT, 4, 16, 16>(L, x, n, 2, logits, s);
         }
         if (n >= 128) {   // (at 64 tokens two rows per warp = twice the CTAs measured faster: 21 -> 17.5 us)
             const int tiles = (n + 7) / 8, passes = tiles >= 32 ? tiles / 16 : 1;  // about 256 CTAs
