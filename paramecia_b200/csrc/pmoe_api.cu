@@ -96,6 +96,7 @@ void carve_workspace(pmoe_layer *L, Carver &c)
     w.groups.cost_prefix_mma = c.take<int>(El + 1);
     w.groups.tile_prefix = c.take<int>(El + 1);
     w.groups.tile_table = c.take<int2>(n * k / PREFILL_NT + El + 1);
+    w.groups.chunk_cnt = c.take<int>((n * k + GROUP_CHUNK - 1) / GROUP_CHUNK * El);
     w.act = c.take<float>(rows * F);
     w.act_q8k.qs = c.take<int8_t>(rows * F);
     w.act_q8k.d = c.take<float>(rows * (F / QK_K));

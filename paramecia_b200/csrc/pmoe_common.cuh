@@ -230,7 +230,10 @@ struct Groups {
     int *cost_prefix_mma;  // same with ceil(count / GEMV_TG_MMA): 8-token groups of the tensor-core GEMV
     int *tile_prefix; // [E_local + 1] exclusive prefix over active slots of ceil(count / PREFILL_NT)
     int2 *tile_table; // [tile_prefix[n_active]] (local expert id, tile index inside the expert) per prefill tile
+    int *chunk_cnt;   // [ceil(n*k / GROUP_CHUNK), E_local] scratch of the multi-CTA grouping: per chunk of pairs and
+                      // expert, the count, then the number of the expert's pairs in earlier chunks
 };
+constexpr int GROUP_CHUNK = 1024;   // pairs per CTA of the multi-CTA grouping
 
 // Local index of global expert id `g` on this handle, or -1 when another rank holds it (or the id is out of range).
 __host__ __device__ inline int local_expert(uint32_t g, int base, int E_local, int stride, int rem)

@@ -611,11 +611,15 @@ cudaError_t launch_topk(const LayerDev &L, const Workspace &ws, const float *log
 }
 
 // ---------------------------------------------------------------- grouping by expert
-// Counting sort of the n*k (token, slot) pairs by local expert id in one CTA:
-// counts through shared-memory atomics, a scan, then the scatter.  The order of
-// pairs inside one expert's list depends on atomic arrival order; no result depends on it
-// (every pair's rows are computed on their own and combined in slot order).
+// Counting sort of the n*k (token, slot) pairs by local expert id: counts through shared-memory
+// atomics, a scan, then the scatter.  The order of pairs inside one expert's list depends on
+// atomic arrival order; no result depends on it (every pair's rows are computed on their own and
+// combined in slot order).  Decode-sized calls do all of it in one CTA (k_group alone); from
+// GROUP_MULTI_MIN pairs on, the counting and the scatter, which walk the pairs, are spread over
+// one CTA per GROUP_CHUNK pairs (k_group_count, k_group_scatter) around the same one-CTA scan.
 constexpr int GROUP_THREADS = 1024;
+constexpr int GROUP_MULTI_MIN = 8192;
+static_assert(GROUP_CHUNK == GROUP_THREADS, "one pair per thread of a counting CTA");
 
 // inclusive scan of six integers per thread across the CTA: shuffles inside a warp, one pass
 // over the 32 warp totals, three barriers in all
@@ -663,8 +667,29 @@ __device__ inline Scan5 block_scan5(Scan5 x, int (*warp_tot)[NSCAN], int tid)
     return x;
 }
 
+// per chunk of pairs: every pair's position among its chunk's pairs of the same expert, and the chunk's counts
+__global__ void __launch_bounds__(GROUP_THREADS) k_group_count(const uint32_t *__restrict__ idx, int npairs, int base,
+                                                               int E_local, int stride, int rem, Groups g)
+{
+    __shared__ int cnt[1024];
+    const int tid = threadIdx.x;
+    cnt[tid] = 0;
+    pdl_wait();
+    pdl_launch_dependents();
+    __syncthreads();
+    const int p = blockIdx.x * GROUP_CHUNK + tid;
+    if (p < npairs) {
+        const int e = local_expert(idx[p], base, E_local, stride, rem);
+        g.pos[p] = e >= 0 ? atomicAdd(&cnt[e], 1) : -1;
+    }
+    __syncthreads();
+    if (tid < E_local) g.chunk_cnt[(size_t)blockIdx.x * E_local + tid] = cnt[tid];
+}
+
+// n_chunks == 0: the whole sort in this CTA.  Otherwise k_group_count has run: the counts are the sums over the
+// chunks (whose entries become the expert's pairs in earlier chunks), and k_group_scatter follows.
 __global__ void __launch_bounds__(GROUP_THREADS) k_group(const uint32_t *__restrict__ idx, int npairs, int base,
-                                                         int E_local, int stride, int rem, Groups g)
+                                                         int E_local, int stride, int rem, Groups g, int n_chunks)
 {
     __shared__ int cnt[1024];
     __shared__ int warp_tot[32][NSCAN];
@@ -673,14 +698,23 @@ __global__ void __launch_bounds__(GROUP_THREADS) k_group(const uint32_t *__restr
     pdl_wait();
     pdl_launch_dependents();
     __syncthreads();
-    for (int p = tid; p < npairs; p += GROUP_THREADS) {
-        const int e = local_expert(idx[p], base, E_local, stride, rem);
-        int pos = -1;
-        if (e >= 0) pos = atomicAdd(&cnt[e], 1);
-        g.pos[p] = pos;
+    int c = 0;
+    if (n_chunks == 0) {
+        for (int p = tid; p < npairs; p += GROUP_THREADS) {
+            const int e = local_expert(idx[p], base, E_local, stride, rem);
+            int pos = -1;
+            if (e >= 0) pos = atomicAdd(&cnt[e], 1);
+            g.pos[p] = pos;
+        }
+        __syncthreads();
+        c = tid < E_local ? cnt[tid] : 0;
+    } else if (tid < E_local) {
+        for (int b = 0; b < n_chunks; b++) {
+            const int v = g.chunk_cnt[(size_t)b * E_local + tid];
+            g.chunk_cnt[(size_t)b * E_local + tid] = c;
+            c += v;
+        }
     }
-    __syncthreads();
-    const int c = tid < E_local ? cnt[tid] : 0;
     const int flag = c > 0 ? 1 : 0;
     const int cost = (c + GEMV_TG - 1) / GEMV_TG;
     const int tiles = (c + PREFILL_NT - 1) / PREFILL_NT;
@@ -711,6 +745,7 @@ __global__ void __launch_bounds__(GROUP_THREADS) k_group(const uint32_t *__restr
         g.cost_prefix_mma[sc.v[1]] = sc.v[5];
         g.tile_prefix[sc.v[1]] = sc.v[3];
     }
+    if (n_chunks) return;
     __syncthreads();   // every thread has read its count
     cnt[tid] = excl;   // reuse as the per-expert base
     __syncthreads();
@@ -723,11 +758,40 @@ __global__ void __launch_bounds__(GROUP_THREADS) k_group(const uint32_t *__restr
     }
 }
 
+// per chunk of pairs: positions inside the chunk become positions inside the expert's list, and the pairs go to their places
+__global__ void __launch_bounds__(GROUP_THREADS) k_group_scatter(const uint32_t *__restrict__ idx, int npairs, int base,
+                                                                 int E_local, int stride, int rem, Groups g)
+{
+    pdl_wait();
+    pdl_launch_dependents();
+    const int p = blockIdx.x * GROUP_CHUNK + threadIdx.x;
+    if (p >= npairs) return;
+    const int pos = g.pos[p];
+    if (pos < 0) return;
+    const int e = local_expert(idx[p], base, E_local, stride, rem);
+    const int fp = g.chunk_cnt[(size_t)blockIdx.x * E_local + e] + pos;
+    g.pos[p] = fp;
+    g.pairs[g.offset[e] + fp] = p;
+}
+
 cudaError_t launch_group(const LayerDev &L, const Workspace &ws, const uint32_t *idx, int n, int top_k,
                          cudaStream_t s)
 {
-    cudaError_t e = launch_pdl(k_group, dim3(1), dim3(GROUP_THREADS), 0, s, idx, n * top_k, L.expert_base, L.E_local, L.ep_stride, L.ep_rem,
-                               ws.groups);
+    const int npairs = n * top_k;
+    const int n_chunks = npairs >= GROUP_MULTI_MIN ? (npairs + GROUP_CHUNK - 1) / GROUP_CHUNK : 0;
+    cudaError_t e = cudaSuccess;
+    if (n_chunks) {
+        e = launch_pdl(k_group_count, dim3(n_chunks), dim3(GROUP_THREADS), 0, s, idx, npairs, L.expert_base, L.E_local, L.ep_stride,
+                       L.ep_rem, ws.groups);
+        count_launch();
+        if (e != cudaSuccess) return e;
+    }
+    e = launch_pdl(k_group, dim3(1), dim3(GROUP_THREADS), 0, s, idx, npairs, L.expert_base, L.E_local, L.ep_stride, L.ep_rem,
+                   ws.groups, n_chunks);
+    count_launch();
+    if (e != cudaSuccess || !n_chunks) return e;
+    e = launch_pdl(k_group_scatter, dim3(n_chunks), dim3(GROUP_THREADS), 0, s, idx, npairs, L.expert_base, L.E_local, L.ep_stride,
+                   L.ep_rem, ws.groups);
     count_launch();
     return e;
 }
