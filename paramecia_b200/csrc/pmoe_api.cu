@@ -213,7 +213,7 @@ int pmoe::run_experts(pmoe_layer *L, Workspace &ws, const void *x, int x_dtype, 
     const bool split = want_prefill && !prefill && routed && shared && prefill_supported(d, true, false);
     if (split) {
         PHASE(L, 4, s, launch_gate_up_prefill(d, ws, n, top_k, true, false, s));
-        if (prefill_down_supported(d, true, false)) {
+        if (prefill_down_supported(d, ws, true, false)) {
             CU(launch_down_prefill(d, ws, w, n, top_k, true, false, s));
         } else {
             CU(launch_act_quant(d, ws, idx, n, top_k, true, false, s));
@@ -228,7 +228,7 @@ int pmoe::run_experts(pmoe_layer *L, Workspace &ws, const void *x, int x_dtype, 
         PHASE(L, 4, s, launch_gate_up_prefill(d, ws, n, top_k, routed, shared, s));
     else
         PHASE(L, 4, s, launch_gate_up(d, ws, n, top_k, routed, shared, s));
-    if (prefill && prefill_down_supported(d, routed, shared)) {
+    if (prefill && prefill_down_supported(d, ws, routed, shared)) {
         PHASE(L, 6, s, launch_down_prefill(d, ws, w, n, top_k, routed, shared, s));
     } else {
         // the decode gate/up kernel has already re-quantised every expert's activated rows (last-CTA
@@ -390,7 +390,11 @@ int pmoe_layer_create(const pmoe_layer_desc *desc, pmoe_layer **out)
             carve_workspace(L, real);
             e = cudaMemset(L->ws.status, 0, sizeof(DevStatus));
             if (e == cudaSuccess) e = cudaMemset(L->ws.slot_done, 0, sizeof(int) * (El + 1 + ((size_t)d.max_tokens + 7) / 8));
+            // (the down GEMM's copies take whole 64-row boxes: rows no call has written yet must hold numbers)
+            const size_t act_rows = (size_t)d.max_tokens * (d.k + 1);
+            if (e == cudaSuccess) e = cudaMemset(L->ws.act_h, 0, act_rows * d.F * sizeof(__half));
             if (e != cudaSuccess) rc = fail_cuda(e, "workspace");
+            L->ws.act_h_map_ok = !rc && make_act_h_map(L->ws, act_rows, d.F);
         }
     }
     if (rc) {

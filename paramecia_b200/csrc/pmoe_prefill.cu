@@ -25,6 +25,8 @@
 // shared memory in the K-major core-matrix layout (8 rows x 16 bytes, no swizzle).  Every wait
 // is bounded and reports through the status word; tensor memory is freed on every path.
 #include "pmoe_common.cuh"
+#include <cstring>
+#include <cuda.h>   // CUtensorMap and its enums; the encoder itself comes from the driver at run time
 
 namespace pmoe {
 
@@ -679,7 +681,8 @@ struct DownArgs {
     int sh_begin, sh_count;
     Groups g;
     const int *tile_prefix;
-    const __half *act_h;           // [n*(k+1), F] fake-quantised activation
+    const __half *act_h;           // [n*(k+1), F] fake-quantised activation, routed rows in expert-sorted order
+    CUtensorMap act_map;           // its TMA descriptor: boxes of 64 rows x 64 halves, 128-byte swizzle
     const float *act_h_scale;      // [n*(k+1)] power of two each row of act_h was divided by
     const float *scale_r;          // routing weights [n*k]
     const float *scale_s;          // shared gate [n]
@@ -813,22 +816,36 @@ constexpr int DN_COLS = 64 * DN_TILES;
 // A B piece holds all four token tiles of a run (256 tokens: one MMA of N = 64 .. 256 per K slice) in a single buffer:
 // a step is then one wait, one dequantisation, one store of the piece, one barrier.  Q8_0 rows are the widest and
 // leave room for 128-token pieces only.
+// The K-quant kernels fetch their pieces (128 tokens, two buffers) with TMA tensor copies straight into the swizzled
+// layout, a piece ahead, and a step has one barrier (for the dequantised A tile); the Q8_0 kernel, whose rows leave
+// room for one buffer only, loads its piece into registers a piece ahead and stores it.
 template <int DT> struct DownCfg {
-    static constexpr int PT = DT == PMOE_Q8_0 ? 2 * PF_NT : 4 * PF_NT;   // tokens of a B piece
-    static constexpr int NB = 1;                                         // B buffers
+    static constexpr bool TMA_B = DT != PMOE_Q8_0;
+    static constexpr int PT = 2 * PF_NT;                                 // tokens of a B piece
+    static constexpr int NB = TMA_B ? 2 : 1;                             // B buffers
+    static constexpr int THREADS = DN_THREADS + (TMA_B ? 32 : 0);        // the copy warp comes after the eight working warps
 };
 
 struct DownSmemHdr {
     float scale[DN_TILES][PF_NT];
-    int row_in[DN_TILES][PF_NT];
+    int row_in[DN_TILES][PF_NT];    // the pair (or shared-expert row) a token's output goes to, -1: none
+    int row_act[DN_TILES][PF_NT];   // the row of act_h its activation sits in
     int2 entry[DN_TILES];          // (slot or -1 for the shared expert, tile inside the expert)
-    uint64_t bar_raw, bar_b[4];
+    uint64_t bar_raw, bar_b[4], bar_full[4];
     uint32_t tmem_base;
     int n_entries;
 };
 
+// one box of the tensor map (its rows y .. y + 63, halves x .. x + 63) into shared memory; the bytes count on `bar`
+__device__ inline void tma_load_2d(void *smem_dst, const CUtensorMap *map, int x, int y, uint64_t *bar)
+{
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y)
+                 : "memory");
+}
+
 template <int DT>
-__global__ void __launch_bounds__(DN_THREADS, 2) k_down_prefill(const DownArgs A)
+__global__ void __launch_bounds__(DownCfg<DT>::THREADS, 2) k_down_prefill(const __grid_constant__ DownArgs A)
 {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     using DQ = DownDequant<DT>;
@@ -861,6 +878,7 @@ __global__ void __launch_bounds__(DN_THREADS, 2) k_down_prefill(const DownArgs A
         S.n_entries = left < DN_TILES ? left : DN_TILES;
         mbar_init(&S.bar_raw, 1);
         for (int i = 0; i < NB; i++) mbar_init(&S.bar_b[i], 1);
+        for (int i = 0; i < 4; i++) mbar_init(&S.bar_full[i], 1);
         fence_mbar_init();
     }
     if (warp == 0) tmem_alloc(&S.tmem_base, DN_COLS);
@@ -911,28 +929,106 @@ __global__ void __launch_bounds__(DN_THREADS, 2) k_down_prefill(const DownArgs A
             for (int off = 0; off < RAW_BYTES; off += 16384)
                 bulk_g2s(raw + off, src + off, RAW_BYTES - off < 16384 ? RAW_BYTES - off : 16384, &S.bar_raw);
         }
-        for (int i = tid; i < T * PF_NT; i += DN_THREADS) {
+        for (int i = tid; i < T * PF_NT; i += (int)blockDim.x) {
             const int t = i / PF_NT, j = i % PF_NT;
             const int tok = S.entry[e0 + t].y * PF_NT + j;
-            int rin = -1;
+            int rin = -1, ract = 0;
             float sc = 0.f;
             if (tok < m) {
-                if (is_shared) { rin = A.n * A.top_k + A.sh_begin + tok; sc = A.scale_s[A.sh_begin + tok]; }
-                else { rin = list[tok]; sc = A.scale_r[rin]; }
+                if (is_shared) { rin = ract = A.n * A.top_k + A.sh_begin + tok; sc = A.scale_s[A.sh_begin + tok]; }
+                else { rin = list[tok]; ract = A.g.offset[slot] + tok; sc = A.scale_r[rin]; }
                 sc *= A.act_h_scale[rin];
             }
             S.row_in[t][j] = rin;
+            S.row_act[t][j] = ract;
             S.scale[t][j] = sc;
         }
         __syncthreads();
 
         // A B piece holds the activations of TPP token tiles of the run (the last one of an odd run holds one): pieces
         // are numbered i = s * P + p with P = ceil(T / TPP); piece i is the CTA's commit base + i and sits in that
-        // commit's buffer.  It travels global -> registers -> shared memory, loaded one piece ahead: eight threads read
+        // commit's buffer.
+        const int P = (T + TPP - 1) / TPP, base = committed;
+        if constexpr (DownCfg<DT>::TMA_B) {
+            // The run's tokens are consecutive rows of act_h (it is written in expert-sorted order), a token tile is
+            // one box of the tensor map: 64 rows x 64 halves land in the 128-byte swizzled layout the MMAs read, and the
+            // bytes count on the buffer's barrier.  Rows past the expert's last token belong to the next expert (or lie
+            // past the array: zeros): their columns of the accumulators are never stored.  A ninth warp issues the copies
+            // (the eight working warps meet at a barrier of their own), so that no working thread waits for them.
+            const int n_pieces = steps * P;
+            const int row0 = (is_shared ? A.n * A.top_k + A.sh_begin : A.g.offset[slot]) + S.entry[e0].y * PF_NT;
+            if (warp == DN_THREADS / 32) {
+                // the copy warp: piece j goes out as soon as the MMAs that read its buffer (piece j - NB) are done
+                for (int j = 0; j < n_pieces && ok; j++) {
+                    wait_mma(base + j - NB + 1);
+                    if (ok && lane == 0) {
+                        const int s_ = j / P, p_ = j % P, buf = (base + j) % NB;
+                        const int tp = T - TPP * p_ < TPP ? T - TPP * p_ : TPP;
+                        mbar_expect_tx(&S.bar_full[buf], (uint32_t)(tp * PF_NT * DN_KSTEP * 2));
+                        for (int t = 0; t < tp; t++)
+                            tma_load_2d(b_tile + buf * B_BYTES + t * (PF_NT * DN_KSTEP * 2), &A.act_map, s_ * DN_KSTEP,
+                                        row0 + (TPP * p_ + t) * PF_NT, &S.bar_full[buf]);
+                    }
+                }
+                // (a warp that gave up may have copies under way: they land, bounded, before the buffers go)
+                if (!ok && lane == 0)
+                    for (int g = base; g < base + n_pieces; g++)
+                        if (!mbar_wait(&S.bar_full[g % NB], (uint32_t)((g / NB) & 1), 1u << 8)) break;
+                committed += n_pieces;
+                ph_raw ^= 1;
+            } else {
+                if (!mbar_wait(&S.bar_raw, ph_raw)) {
+                    set_status(A.status, PMOE_ERR_TIMEOUT, 31, e0);
+                    ok = false;
+                }
+                ph_raw ^= 1;
+                for (int s = 0; s < steps; s++) {
+                    wait_mma(base + s * P);   // the previous step's MMAs still read the A tile
+                    tc_fence_after();
+                    if (ok) DQ::step(raw + (size_t)r * DQ::ROW_BYTES, s, a_tile, r, part);
+                    tc_fence_before();
+                    // the working warps meet: the A tile is whole; a thread that gave up takes all of them out together
+                    {
+                        uint32_t all_ok;
+                        asm volatile(
+                            "{\n\t.reg .pred p, q;\n\t"
+                            "setp.ne.u32 q, %1, 0;\n\t"
+                            "barrier.cta.red.and.pred p, 1, %2, q;\n\t"
+                            "selp.u32 %0, 1, 0, p;\n\t}"
+                            : "=r"(all_ok)
+                            : "r"((uint32_t)ok), "n"(DN_THREADS)
+                            : "memory");
+                        ok = all_ok != 0;
+                    }
+                    if (!ok) break;
+                    if (tid == 0) {
+                        fence_proxy_async();   // the A tile's stores went through the generic proxy
+                        tc_fence_after();
+                        for (int p = 0; p < P && ok; p++) {
+                            const int g = base + s * P + p, buf = g % NB;
+                            if (!mbar_wait_spin(&S.bar_full[buf], (uint32_t)((g / NB) & 1))) {
+                                set_status(A.status, PMOE_ERR_TIMEOUT, 33, g);
+                                ok = false;
+                                break;
+                            }
+                            const uint64_t db0 = desc_b0 + (uint64_t)((buf * B_BYTES) >> 4);
+                            const int tp = T - TPP * p < TPP ? T - TPP * p : TPP;               // token tiles of this piece
+                            const uint32_t idesc = make_idesc(1, 0, 0, PF_NT * tp, PF_M);       // f16 x f16 -> f32, N = 64 tp over its columns
+#pragma unroll
+                            for (int ks = 0; ks < DN_KSTEP / 16; ks++)   // 16 halves = 32 bytes of K per instruction
+                                mma_f16(tmem + 64 * TPP * p, desc_a0 + (uint64_t)(ks * ((2 * PF_M * 16) >> 4)),
+                                        db0 + (uint64_t)(ks * (32 >> 4)), idesc, (s > 0 || ks > 0) ? 1u : 0u);
+                            tc_commit(&S.bar_b[buf]);
+                        }
+                    }
+                    committed += P;
+                }
+            }
+        } else {
+        // The piece travels global -> registers -> shared memory, loaded one piece ahead: eight threads read
         // a token's 128 bytes (a warp reads four whole rows) and store them into one row of the 128-byte swizzled
         // layout, without bank conflicts on either side.  (A cp.async ring two pieces ahead measured the same; its copies cost one
         // shared-memory wavefront per lane where these stores take four per warp.)
-        const int P = (T + TPP - 1) / TPP, base = committed;
         uint4 nb[LPT];
         int ls = 0, lp = 0;   // step and pair of the next piece to load
         auto load_b = [&]() {
@@ -943,7 +1039,7 @@ __global__ void __launch_bounds__(DN_THREADS, 2) k_down_prefill(const DownArgs A
                 for (int j = 0; j < LPT; j++) {
                     const int tok = tk0 + 32 * j, t = TPP * lp + (tok >> 6);
                     const int rin = t < T ? S.row_in[t][tok & 63] : -1;
-                    if (rin >= 0) nb[j] = *reinterpret_cast<const uint4 *>(A.act_h + (size_t)rin * A.F + ls * DN_KSTEP + 8 * chunk);
+                    if (rin >= 0) nb[j] = *reinterpret_cast<const uint4 *>(A.act_h + (size_t)S.row_act[t][tok & 63] * A.F + ls * DN_KSTEP + 8 * chunk);
                 }
                 if (++lp == P) { lp = 0; ls++; }
             }
@@ -985,9 +1081,10 @@ __global__ void __launch_bounds__(DN_THREADS, 2) k_down_prefill(const DownArgs A
                 committed++;
             }
         }
+        }
         wait_mma(committed);
         tc_fence_after();
-        if (ok) {
+        if (ok && warp < DN_THREADS / 32) {
             // row (32 * (warp & 3) + lane) of the block: a warp reaches the 32 lanes of its quarter; the two warps
             // of a quarter split the run's tiles
             const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16);
@@ -1007,7 +1104,7 @@ __global__ void __launch_bounds__(DN_THREADS, 2) k_down_prefill(const DownArgs A
             }
         }
         tc_fence_before();
-        __syncthreads();   // accumulators, tiles and tables are free for the next run
+        ok = __syncthreads_and(ok);   // accumulators, tiles and tables are free for the next run; a failure ends the CTA as one
         tc_fence_after();
         e0 = e1;
     }
@@ -1020,13 +1117,16 @@ __global__ void __launch_bounds__(DN_THREADS, 2) k_down_prefill(const DownArgs A
 // A row whose largest magnitude would leave the fp16 range is written times a power of two 2^-e (exact), and
 // row_scale[r] = 2^e goes back in when the down GEMM's accumulators are drained; other rows have scale 1.
 __global__ void __launch_bounds__(64) k_act_fakequant_h(const float *__restrict__ act, int F, int n_routed_rows,
-                                                        const int *__restrict__ pos, bool routed, bool kq_routed,
-                                                        bool kq_shared, __half *__restrict__ out,
-                                                        float *__restrict__ row_scale)
+                                                        const int *__restrict__ sorted_pairs, const int *__restrict__ n_sorted,
+                                                        bool routed, bool kq_routed, bool kq_shared,
+                                                        __half *__restrict__ out, float *__restrict__ row_scale)
 {
     __shared__ float s_amax[2];
-    const int r = blockIdx.x;
-    if (r < n_routed_rows && (!routed || pos[r] < 0)) return;
+    // CTA w < n_routed_rows writes row w of the output: the w-th pair in expert-sorted order (the down GEMM fetches
+    // an expert's token tiles as boxes of consecutive rows); the shared expert's rows keep their places
+    const int w = blockIdx.x;
+    if (w < n_routed_rows && (!routed || w >= *n_sorted)) return;
+    const int r = w < n_routed_rows ? sorted_pairs[w] : w;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const bool kq = r < n_routed_rows ? kq_routed : kq_shared;
     float down = 1.f;   // 2^-e
@@ -1054,7 +1154,7 @@ __global__ void __launch_bounds__(64) k_act_fakequant_h(const float *__restrict_
             const float id = d != 0.f ? __fdiv_rn(1.f, d) : 0.f;
             const float q = roundf(__fmul_rn(x, id));
             const float df = __half2float(__float2half_rn(d));
-            out[(size_t)r * F + b * QK8_0 + lane] = __float2half_rn((q * df) * down);
+            out[(size_t)w * F + b * QK8_0 + lane] = __float2half_rn((q * df) * down);
         }
         return;
     }
@@ -1087,7 +1187,7 @@ __global__ void __launch_bounds__(64) k_act_fakequant_h(const float *__restrict_
             o = make_uint4(*reinterpret_cast<uint32_t *>(&h[0]), *reinterpret_cast<uint32_t *>(&h[1]),
                            *reinterpret_cast<uint32_t *>(&h[2]), *reinterpret_cast<uint32_t *>(&h[3]));
         }
-        *reinterpret_cast<uint4 *>(out + (size_t)r * F + b * QK_K + 8 * lane) = o;
+        *reinterpret_cast<uint4 *>(out + (size_t)w * F + b * QK_K + 8 * lane) = o;
     }
 }
 
@@ -1148,9 +1248,36 @@ cudaError_t launch_gate_up_prefill(const LayerDev &L, const Workspace &ws, int n
     return cudaGetLastError();
 }
 
-bool prefill_down_supported(const LayerDev &L, bool routed, bool shared)
+bool make_act_h_map(Workspace &ws, size_t rows, int F)
+{
+    using Encode = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    static Encode encode = nullptr;
+    if (!encode) {
+        void *fn = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess || !fn ||
+            q != cudaDriverEntryPointSuccess)
+            return false;
+        encode = (Encode)fn;
+    }
+    if (F % DN_KSTEP != 0 || rows == 0) return false;
+    CUtensorMap m;
+    const cuuint64_t dims[2] = {(cuuint64_t)F, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)F * sizeof(__half)};
+    const cuuint32_t box[2] = {DN_KSTEP, PF_NT}, estr[2] = {1, 1};
+    if (encode(&m, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, ws.act_h, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return false;
+    memcpy(ws.act_h_map, &m, sizeof(m));
+    return true;
+}
+
+bool prefill_down_supported(const LayerDev &L, const Workspace &ws, bool routed, bool shared)
 {
     if (L.H != 2048 || L.F != 512) return false;
+    if (!ws.act_h_map_ok) return false;
     if (routed && !pf_dn_ok(L.down_dtype)) return false;
     if (shared && !pf_dn_ok(L.sh_down_dtype)) return false;
     return true;
@@ -1168,7 +1295,7 @@ static cudaError_t launch_down_t(const DownArgs &A, dim3 grid, cudaStream_t s)
         if (e != cudaSuccess) return e;
         configured = true;
     }
-    k_down_prefill<DT><<<grid, DN_THREADS, smem, s>>>(A);
+    k_down_prefill<DT><<<grid, DownCfg<DT>::THREADS, smem, s>>>(A);
     count_launch();
     return cudaGetLastError();
 }
@@ -1186,6 +1313,8 @@ static cudaError_t launch_down_gemm(const LayerDev &L, const Workspace &ws, cons
     A.g = ws.groups;
     A.tile_prefix = ws.groups.tile_prefix;
     A.act_h = ws.act_h;
+    static_assert(sizeof(CUtensorMap) == sizeof(ws.act_h_map), "the workspace holds the descriptor as bytes");
+    memcpy(&A.act_map, ws.act_h_map, sizeof(CUtensorMap));
     A.act_h_scale = ws.act_h_scale;
     A.scale_r = w;
     A.scale_s = ws.sh_sigmoid;
@@ -1203,8 +1332,8 @@ cudaError_t launch_down_prefill(const LayerDev &L, const Workspace &ws, const fl
                                 bool shared, cudaStream_t s)
 {
     const int rows = n * top_k + (shared ? n : 0);
-    k_act_fakequant_h<<<rows, 64, 0, s>>>(ws.act, L.F, n * top_k, ws.groups.pos, routed, is_kquant(L.down_dtype),
-                                          is_kquant(L.sh_down_dtype), ws.act_h, ws.act_h_scale);
+    k_act_fakequant_h<<<rows, 64, 0, s>>>(ws.act, L.F, n * top_k, ws.groups.pairs, ws.groups.offset + L.E_local, routed,
+                                          is_kquant(L.down_dtype), is_kquant(L.sh_down_dtype), ws.act_h, ws.act_h_scale);
     count_launch();
     if (routed && shared && L.down_dtype != L.sh_down_dtype) {   // two types: one launch each
         cudaError_t e = launch_down_gemm(L, ws, w, n, top_k, true, false, s);
