@@ -207,10 +207,10 @@ int pmoe::run_experts(pmoe_layer *L, Workspace &ws, const void *x, int x_dtype, 
     // expected number of tokens per routed expert is n * top_k / E whatever slice this layer holds.
     const char *force = getenv("PMOE_PREFILL");
     const bool want_prefill = force ? atoi(force) != 0 : (long)n * top_k >= 8L * d.E && n >= 512;
-    bool prefill = want_prefill && prefill_supported(d, routed, shared);
+    bool prefill = want_prefill && prefill_supported(d, ws, routed, shared);
     // A shared expert the tensor-core kernels do not take (e.g. Q8_0) does not hold the routed experts
     // back: they go through the tensor-core kernels and the shared expert through the streaming ones.
-    const bool split = want_prefill && !prefill && routed && shared && prefill_supported(d, true, false);
+    const bool split = want_prefill && !prefill && routed && shared && prefill_supported(d, ws, true, false);
     if (split) {
         PHASE(L, 4, s, launch_gate_up_prefill(d, ws, n, top_k, true, false, s));
         if (prefill_down_supported(d, ws, true, false)) {
@@ -395,6 +395,7 @@ int pmoe_layer_create(const pmoe_layer_desc *desc, pmoe_layer **out)
             if (e == cudaSuccess) e = cudaMemset(L->ws.act_h, 0, act_rows * d.F * sizeof(__half));
             if (e != cudaSuccess) rc = fail_cuda(e, "workspace");
             L->ws.act_h_map_ok = !rc && make_act_h_map(L->ws, act_rows, d.F);
+            L->ws.xq_map_ok = !rc && make_xq_map(L->ws, (size_t)d.max_tokens, d.H);
         }
     }
     if (rc) {

@@ -282,6 +282,9 @@ struct Workspace {
                          // expert-sorted order (row offset[e] + pos), then the shared expert's rows at n*k + token
     alignas(64) unsigned char act_h_map[128];   // TMA descriptor (CUtensorMap) of act_h: boxes of 64 rows x 64 halves, 128-byte swizzle
     bool act_h_map_ok;
+    alignas(64) unsigned char xq_map[128];      // TMA descriptor of x_q8k.qs: boxes of one row x 128 bytes, 128-byte swizzle
+    const void *xq_map_base;                    // the array it was made for
+    bool xq_map_ok;
     float *act_h_scale;  // [n*(k+1)]     power of two a row of act_h was divided by (1 unless it would leave the fp16 range)
     float *partial;      // [n*(k+1), H]  weighted down-projection rows
     int *slot_done;      // [E_local + 1 + max_tokens/8] completion counters of the gate/up kernel: per expert, the shared
@@ -319,12 +322,14 @@ cudaError_t launch_qmatmul(int dtype, const void *w, int rows, int K, const floa
 size_t qmatmul_scratch_bytes(int m, int K);
 cudaError_t qmatmul_static_scratch(int device, void **ptr, size_t *bytes);
 // pmoe_prefill.cu
-bool prefill_supported(const LayerDev &L, bool routed, bool shared);
+bool prefill_supported(const LayerDev &L, const Workspace &ws, bool routed, bool shared);
 cudaError_t launch_gate_up_prefill(const LayerDev &L, const Workspace &ws, int n, int top_k, bool routed, bool shared,
                                    cudaStream_t s);
 bool prefill_down_supported(const LayerDev &L, const Workspace &ws, bool routed, bool shared);
 // fills ws.act_h_map for ws.act_h of `rows` rows of F halves; false when the driver refuses
 bool make_act_h_map(Workspace &ws, size_t rows, int F);
+// the same for ws.x_q8k.qs of `rows` rows of H bytes
+bool make_xq_map(Workspace &ws, size_t rows, int H);
 cudaError_t launch_down_prefill(const LayerDev &L, const Workspace &ws, const float *w, int n, int top_k, bool routed,
                                 bool shared, cudaStream_t s);
 // pmoe_codec.cu

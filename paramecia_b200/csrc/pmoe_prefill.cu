@@ -122,6 +122,22 @@ __device__ inline uint32_t core_off(int rows, int row, int kbyte)
     return (uint32_t)((kbyte >> 4) * (rows * 16) + (row >> 3) * 128 + (row & 7) * 16 + (kbyte & 15));
 }
 
+// one box of a 2-D tensor map (rows y .. y + 63, 64 halves from x on) into shared memory; the bytes count on `bar`
+__device__ inline void tma_load_2d(void *smem_dst, const CUtensorMap *map, int x, int y, uint64_t *bar)
+{
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y)
+                 : "memory");
+}
+// four rows y0 .. y3 of a 2-D tensor map (box: one row), columns from x on, into four consecutive rows of shared memory
+__device__ inline void tma_gather4(void *smem_dst, const CUtensorMap *map, int x, int y0, int y1, int y2, int y3, uint64_t *bar)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile::gather4.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+        ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y0), "r"(y1), "r"(y2), "r"(y3)
+        : "memory");
+}
+
 // ---------------------------------------------------------------- gate/up, Q4_K, exact integer block sums
 struct GuArgs {
     const uint8_t *gate, *up;      // routed [E_local, F, H] Q4_K
@@ -133,29 +149,33 @@ struct GuArgs {
     Groups g;
     const int *tile_prefix;        // [n_active + 1] exclusive prefix of ceil(count / PF_NT) over active slots
     QAct xq;                       // Q8_K rows of the input [n, H]
+    CUtensorMap xq_map;            // TMA descriptor of xq.qs for the Q4_K kernel: boxes of one row x 128 bytes, 128-byte swizzle
     float *act;                    // [n*(k+1), F]
     DevStatus *status;
 };
 
 struct GuSmem {
+    // the tile's quants of one 256-wide block, two buffers: per half of the block 64 rows of 128 bytes in the
+    // 128-byte swizzled K-major layout (what a gather copy of four token rows writes); on a 1024-byte boundary
+    uint8_t b[2][2][PF_NT * 128];
     uint8_t a0[PF_M * 256];
     uint8_t a1[PF_M * 256];
-    uint8_t b[PF_NT * 256];
     uint8_t am[PF_M * 32];
     uint8_t bh[PF_NT * 32];
     uint8_t bl[PF_NT * 32];
     float dx[PF_NT];
     int row_in[PF_NT];
     int row_out[PF_NT];
-    uint64_t bar;
+    uint64_t bar, bar_full[2];
     uint32_t tmem_base;
     int slot, tile_in_slot;
 };
+static_assert(sizeof(GuSmem) + 1024 + 128 <= 115712, "two CTAs of the gate/up GEMM share an SM");
 
-__global__ void __launch_bounds__(GU_THREADS, 2) k_gu_prefill(const GuArgs A)
+__global__ void __launch_bounds__(GU_THREADS, 2) k_gu_prefill(const __grid_constant__ GuArgs A)
 {
     extern __shared__ __align__(128) uint8_t smem_raw[];
-    GuSmem &S = *reinterpret_cast<GuSmem *>(smem_raw);
+    GuSmem &S = *reinterpret_cast<GuSmem *>(smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u));
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
     // ---- which (expert slot, token tile) is this CTA's
@@ -166,6 +186,8 @@ __global__ void __launch_bounds__(GU_THREADS, 2) k_gu_prefill(const GuArgs A)
     if (first >= total_tiles) return;
     if (tid == 0) {
         mbar_init(&S.bar, 1);
+        mbar_init(&S.bar_full[0], 1);
+        mbar_init(&S.bar_full[1], 1);
         fence_mbar_init();
     }
     if (warp == 0) tmem_alloc(&S.tmem_base, PF_TMEM_COLS);
@@ -175,6 +197,21 @@ __global__ void __launch_bounds__(GU_THREADS, 2) k_gu_prefill(const GuArgs A)
     const uint32_t tmem = S.tmem_base;
     uint32_t phase = 0;
     bool ok = true;
+    // The tile's quants arrive by TMA gather copies, a block ahead: block number i of the CTA (over its tiles) lands
+    // in buffer i & 1, whose barrier is then in its (i >> 1)-th use.  Four lanes of every warp issue them (one
+    // instruction a warp: issuing a copy is not cheap for the thread that does it), four token rows and one half of the
+    // block per copy; padding rows of a ragged tile read row 0 (their columns are never
+    // stored).  The buffer of block i + 1 was last read by block i - 1, whose MMAs every thread has waited for.
+    uint32_t img = 0;   // blocks this CTA has started
+    auto fetch_b = [&](uint32_t i, int blk) {
+        if (tid == 0) mbar_expect_tx(&S.bar_full[i & 1], 2 * PF_NT * 128);
+        if (lane < 4) {   // copy g = 4 warp + lane of the block's 32: rows 4 (g / 2) .. + 3, half g % 2
+            const int g = 4 * warp + lane;
+            const int4 rr = *reinterpret_cast<const int4 *>(&S.row_in[4 * (g >> 1)]);
+            const int y0 = rr.x < 0 ? 0 : rr.x, y1 = rr.y < 0 ? 0 : rr.y, y2 = rr.z < 0 ? 0 : rr.z, y3 = rr.w < 0 ? 0 : rr.w;
+            tma_gather4(&S.b[i & 1][g & 1][4 * (g >> 1) * 128], &A.xq_map, blk * QK_K + 128 * (g & 1), y0, y1, y2, y3, &S.bar_full[i & 1]);
+        }
+    };
     // the CTA's tiles, one after the other: set-up (tensor memory, barrier) is paid once, and the second tile of an
     // expert finds the rows the first one read in the caches
     for (int rep = 0; rep < GU_REPS && first + rep < total_tiles && ok; rep++) {
@@ -216,6 +253,7 @@ __global__ void __launch_bounds__(GU_THREADS, 2) k_gu_prefill(const GuArgs A)
         S.row_out[tid] = rout;
     }
     __syncthreads();
+    fetch_b(img, 0);
 
     // this thread's weight row r: rows 0..63 are gate rows, 64..127 the up rows of the same 64 outputs.
     // Threads r and r + 128 share a row: kh = 0 decodes sub-blocks 0..3 of each block and drains
@@ -229,7 +267,7 @@ __global__ void __launch_bounds__(GU_THREADS, 2) k_gu_prefill(const GuArgs A)
     constexpr uint32_t IDESC_UU_U = make_idesc(2, 0, 0, PF_NT, PF_M);  // u8 x u8
     // shared-memory descriptors of the operand tiles (the tiles do not move; a K slice is an address offset)
     const uint64_t desc_a0 = smem_desc(S.a0, PF_M * 16, 128), desc_a1 = smem_desc(S.a1, PF_M * 16, 128);
-    const uint64_t desc_b = smem_desc(S.b, PF_NT * 16, 128), desc_am = smem_desc(S.am, PF_M * 16, 128);
+    const uint64_t desc_am = smem_desc(S.am, PF_M * 16, 128);
     const uint64_t desc_bh = smem_desc(S.bh, PF_NT * 16, 128), desc_bl = smem_desc(S.bl, PF_NT * 16, 128);
     constexpr int NC = PF_NT / 2;  // token columns this thread drains
     float acc[NC];
@@ -244,17 +282,8 @@ __global__ void __launch_bounds__(GU_THREADS, 2) k_gu_prefill(const GuArgs A)
     for (int i = 0; i < 4; i++) blk[1 + i] = reinterpret_cast<const uint4 *>(wrow)[1 + 4 * kh + i];
 
     for (int b = 0; b < nblk && ok; b++) {
-        // ---- start this block's activation loads first: they fly while the weights are decoded
-        // 64 bytes of one token's block per thread: chunks quarter, quarter + 4, ... so that the four threads of a token
-        // read 64 contiguous bytes with every load (a warp's load touches 16 whole sectors instead of 32 half-used ones)
-        const int tk = tid >> 2, quarter = tid & 3;
-        const int rin_b = S.row_in[tk];
-        uint4 bv[4];
-        {
-            const uint4 *src = reinterpret_cast<const uint4 *>(A.xq.qs + (size_t)(rin_b >= 0 ? rin_b : 0) * A.H + b * QK_K) + quarter;
-#pragma unroll
-            for (int i = 0; i < 4; i++) bv[i] = rin_b >= 0 ? src[4 * i] : make_uint4(0, 0, 0, 0);
-        }
+        // ---- the next block's quants set out first
+        if (b + 1 < nblk) fetch_b(img + 1, b + 1);
         uint4 bs0 = make_uint4(0, 0, 0, 0), bs1 = make_uint4(0, 0, 0, 0);
         float dx_reg = 0.f;
         const int rin_s = tid < PF_NT ? S.row_in[tid] : -1;
@@ -305,10 +334,6 @@ __global__ void __launch_bounds__(GU_THREADS, 2) k_gu_prefill(const GuArgs A)
             *reinterpret_cast<uint4 *>(S.am + core_off(PF_M, r, 0)) = make_uint4(w0, w1, w2, w3);
             *reinterpret_cast<uint4 *>(S.am + core_off(PF_M, r, 16)) = make_uint4(0, 0, 0, 0);
         }
-        // ---- B: the tile's quantised activations for this block; token = tid / 4, 64 bytes each
-#pragma unroll
-        for (int i = 0; i < 4; i++)
-            *reinterpret_cast<uint4 *>(S.b + core_off(PF_NT, tk, 16 * (quarter + 4 * i))) = bv[i];
         if (tid < PF_NT) {  // partial sums of 16 quants as two digits: bsum = 64*h + l, l in [0,63]
             uint32_t hw[4] = {0, 0, 0, 0}, lw[4] = {0, 0, 0, 0};
             const float dx = dx_reg;
@@ -331,11 +356,13 @@ __global__ void __launch_bounds__(GU_THREADS, 2) k_gu_prefill(const GuArgs A)
         if (tid == 0) {
             fence_proxy_async();   // everyone's stores are ordered before the barrier; the issuing thread crosses over to the async proxy
             tc_fence_after();
+            if (!mbar_wait_spin(&S.bar_full[img & 1], (img >> 1) & 1)) set_status(A.status, PMOE_ERR_TIMEOUT, 31, b);   // (the MMAs then run on what is there; the status word says so)
 #pragma unroll
-            for (int ks = 0; ks < 8; ks++) {  // 32 bytes of K per instruction: two 16-byte chunks further on per step
-                const uint64_t ka = (uint64_t)(ks * ((2 * PF_M * 16) >> 4)), kb = (uint64_t)(ks * ((2 * PF_NT * 16) >> 4));
-                mma_i8(tmem + 0, desc_a0 + ka, desc_b + kb, IDESC_UU_S, ks > 0);
-                mma_i8(tmem + 64, desc_a1 + ka, desc_b + kb, IDESC_UU_S, ks > 0);
+            for (int ks = 0; ks < 8; ks++) {  // 32 bytes of K per instruction: A two 16-byte chunks further on per step, B 32 bytes inside its half's swizzled rows
+                const uint64_t ka = (uint64_t)(ks * ((2 * PF_M * 16) >> 4));
+                const uint64_t db = smem_desc_sw128(S.b[img & 1][ks >> 2]) + (uint64_t)((ks & 3) * (32 >> 4));
+                mma_i8(tmem + 0, desc_a0 + ka, db, IDESC_UU_S, ks > 0);
+                mma_i8(tmem + 64, desc_a1 + ka, db, IDESC_UU_S, ks > 0);
             }
             mma_i8(tmem + 128, desc_am, desc_bh, IDESC_UU_S, 0);
             mma_i8(tmem + 192, desc_am, desc_bl, IDESC_UU_U, 0);
@@ -376,6 +403,7 @@ __global__ void __launch_bounds__(GU_THREADS, 2) k_gu_prefill(const GuArgs A)
         tc_fence_before();
         __syncthreads();  // operands and accumulators are free for the next block
         tc_fence_after();
+        img++;
     }
 
     // ---- silu(gate) * up: all rows hand their sums over through shared memory ([128][PF_NT + 1]
@@ -410,6 +438,9 @@ __global__ void __launch_bounds__(GU_THREADS, 2) k_gu_prefill(const GuArgs A)
     __syncthreads();   // tiles, tables and accumulators are free for the CTA's next tile
     tc_fence_after();
     }
+    // a CTA that gave up may have a block's copies under way: they land (bounded wait) before its shared memory goes
+    if (!ok && tid == 0) mbar_wait(&S.bar_full[img & 1], (img >> 1) & 1, 1u << 8);
+    __syncthreads();
     if (warp == 0) tmem_dealloc(tmem, PF_TMEM_COLS);
 }
 
@@ -836,14 +867,6 @@ struct DownSmemHdr {
     int n_entries;
 };
 
-// one box of the tensor map (its rows y .. y + 63, halves x .. x + 63) into shared memory; the bytes count on `bar`
-__device__ inline void tma_load_2d(void *smem_dst, const CUtensorMap *map, int x, int y, uint64_t *bar)
-{
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-                 ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y)
-                 : "memory");
-}
-
 template <int DT>
 __global__ void __launch_bounds__(DownCfg<DT>::THREADS, 2) k_down_prefill(const __grid_constant__ DownArgs A)
 {
@@ -1202,9 +1225,13 @@ static int max_routed_tiles(const LayerDev &L, int n, int top_k)
 static bool pf_gu_ok(int dt) { return dt == PMOE_Q4_K || dt == PMOE_Q8_0; }
 static bool pf_dn_ok(int dt) { return dt == PMOE_Q6_K || dt == PMOE_Q4_K || dt == PMOE_Q8_0; }
 
-bool prefill_supported(const LayerDev &L, bool routed, bool shared)
+bool prefill_supported(const LayerDev &L, const Workspace &ws, bool routed, bool shared)
 {
     if (L.H != 2048 || L.F != 512) return false;
+    // the Q4_K kernel gathers the quantised rows through a tensor map made for the workspace's own array
+    if (((routed && L.gate_dtype == PMOE_Q4_K) || (shared && L.sh_gate_dtype == PMOE_Q4_K)) &&
+        !(ws.xq_map_ok && ws.xq_map_base == ws.x_q8k.qs))
+        return false;
     if (routed && !pf_gu_ok(L.gate_dtype)) return false;
     if (shared && !pf_gu_ok(L.sh_gate_dtype)) return false;
     return true;
@@ -1229,11 +1256,12 @@ cudaError_t launch_gate_up_prefill(const LayerDev &L, const Workspace &ws, int n
     A.g = ws.groups;
     A.tile_prefix = ws.groups.tile_prefix;
     A.xq = dt == PMOE_Q8_0 ? ws.x_q80 : ws.x_q8k;
+    memcpy(&A.xq_map, ws.xq_map, sizeof(CUtensorMap));
     A.act = ws.act;
     A.status = ws.status;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(k_gu_prefill, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(GuSmem) + 128);
+        cudaError_t e = cudaFuncSetAttribute(k_gu_prefill, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(GuSmem) + 1024 + 128);
         if (e == cudaSuccess)
             e = cudaFuncSetAttribute(k_gu_prefill_q80, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Gu80Smem) + 128);
 
@@ -1243,35 +1271,53 @@ cudaError_t launch_gate_up_prefill(const LayerDev &L, const Workspace &ws, int n
     const int tiles = (routed ? max_routed_tiles(L, n, top_k) : 0) + (shared ? (ws.sh_count + PF_NT - 1) / PF_NT : 0);
     dim3 grid(L.F / 64, tiles);
     if (dt == PMOE_Q8_0) k_gu_prefill_q80<<<grid, GU_THREADS, sizeof(Gu80Smem) + 128, s>>>(A);
-    else k_gu_prefill<<<dim3(L.F / 64, (tiles + GU_REPS - 1) / GU_REPS), GU_THREADS, sizeof(GuSmem) + 128, s>>>(A);
+    else k_gu_prefill<<<dim3(L.F / 64, (tiles + GU_REPS - 1) / GU_REPS), GU_THREADS, sizeof(GuSmem) + 1024 + 128, s>>>(A);
     count_launch();
     return cudaGetLastError();
 }
 
-bool make_act_h_map(Workspace &ws, size_t rows, int F)
+using TmaEncode = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                               const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                               CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static TmaEncode tma_encoder()
 {
-    using Encode = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
-                                const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-    static Encode encode = nullptr;
+    static TmaEncode encode = nullptr;
     if (!encode) {
         void *fn = nullptr;
         cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess || !fn ||
-            q != cudaDriverEntryPointSuccess)
-            return false;
-        encode = (Encode)fn;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) == cudaSuccess && fn &&
+            q == cudaDriverEntryPointSuccess)
+            encode = (TmaEncode)fn;
     }
-    if (F % DN_KSTEP != 0 || rows == 0) return false;
+    return encode;
+}
+
+// row-major [rows, cols] of `elem_bytes`-byte elements, boxes of box_rows x box_cols, 128-byte swizzle
+static bool encode_2d(void *out_map, CUtensorMapDataType dt, size_t elem_bytes, void *base, size_t rows, size_t cols,
+                      uint32_t box_cols, uint32_t box_rows)
+{
+    TmaEncode encode = tma_encoder();
+    if (!encode || rows == 0 || cols % box_cols != 0 || box_cols * elem_bytes != 128) return false;
     CUtensorMap m;
-    const cuuint64_t dims[2] = {(cuuint64_t)F, (cuuint64_t)rows};
-    const cuuint64_t strides[1] = {(cuuint64_t)F * sizeof(__half)};
-    const cuuint32_t box[2] = {DN_KSTEP, PF_NT}, estr[2] = {1, 1};
-    if (encode(&m, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, ws.act_h, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)(cols * elem_bytes)};
+    const cuuint32_t box[2] = {box_cols, box_rows}, estr[2] = {1, 1};
+    if (encode(&m, dt, 2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+               CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return false;
-    memcpy(ws.act_h_map, &m, sizeof(m));
+    memcpy(out_map, &m, sizeof(m));
     return true;
+}
+
+bool make_act_h_map(Workspace &ws, size_t rows, int F)
+{
+    return encode_2d(ws.act_h_map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, ws.act_h, rows, (size_t)F, DN_KSTEP, PF_NT);
+}
+
+bool make_xq_map(Workspace &ws, size_t rows, int H)
+{
+    ws.xq_map_base = ws.x_q8k.qs;
+    return encode_2d(ws.xq_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, ws.x_q8k.qs, rows, (size_t)H, 128, 1);
 }
 
 bool prefill_down_supported(const LayerDev &L, const Workspace &ws, bool routed, bool shared)
