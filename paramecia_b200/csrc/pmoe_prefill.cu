@@ -26,6 +26,8 @@
 // is bounded and reports through the status word; tensor memory is freed on every path.
 #include "pmoe_common.cuh"
 #include <cstring>
+#include <map>
+#include <mutex>
 #include <cuda.h>   // CUtensorMap and its enums; the encoder itself comes from the driver at run time
 
 namespace pmoe {
@@ -150,14 +152,17 @@ struct GuArgs {
     const int *tile_prefix;        // [n_active + 1] exclusive prefix of ceil(count / PF_NT) over active slots
     QAct xq;                       // Q8_K rows of the input [n, H]
     CUtensorMap xq_map;            // TMA descriptor of xq.qs for the Q4_K kernel: boxes of one row x 128 bytes, 128-byte swizzle
+    CUtensorMap w_map[4];          // ... of gate, up, sgate, sup as [rows, row bytes] bytes: boxes of 64 rows x one Q4_K block
     float *act;                    // [n*(k+1), F]
     DevStatus *status;
 };
 
 struct GuSmem {
-    // the tile's quants of one 256-wide block, two buffers: per half of the block 64 rows of 128 bytes in the
-    // 128-byte swizzled K-major layout (what a gather copy of four token rows writes); on a 1024-byte boundary
-    uint8_t b[2][2][PF_NT * 128];
+    // the tile's quants of one 256-wide block: per half of the block 64 rows of 128 bytes in the 128-byte swizzled
+    // K-major layout (what a gather copy of four token rows writes); on a 1024-byte boundary
+    uint8_t b[2][PF_NT * 128];
+    // the 128 rows' raw bytes of the current block (one Q4_K block of 144 bytes each): two TMA boxes, gate and up
+    uint8_t raw[PF_M][Q4_K_BYTES];
     uint8_t a0[PF_M * 256];
     uint8_t a1[PF_M * 256];
     uint8_t am[PF_M * 32];
@@ -166,7 +171,7 @@ struct GuSmem {
     float dx[PF_NT];
     int row_in[PF_NT];
     int row_out[PF_NT];
-    uint64_t bar, bar_full[2];
+    uint64_t bar, bar_full, bar_raw;
     uint32_t tmem_base;
     int slot, tile_in_slot;
 };
@@ -186,8 +191,8 @@ __global__ void __launch_bounds__(GU_THREADS, 2) k_gu_prefill(const __grid_const
     if (first >= total_tiles) return;
     if (tid == 0) {
         mbar_init(&S.bar, 1);
-        mbar_init(&S.bar_full[0], 1);
-        mbar_init(&S.bar_full[1], 1);
+        mbar_init(&S.bar_full, 1);
+        mbar_init(&S.bar_raw, 1);
         fence_mbar_init();
     }
     if (warp == 0) tmem_alloc(&S.tmem_base, PF_TMEM_COLS);
@@ -197,19 +202,20 @@ __global__ void __launch_bounds__(GU_THREADS, 2) k_gu_prefill(const __grid_const
     const uint32_t tmem = S.tmem_base;
     uint32_t phase = 0;
     bool ok = true;
-    // The tile's quants arrive by TMA gather copies, a block ahead: block number i of the CTA (over its tiles) lands
-    // in buffer i & 1, whose barrier is then in its (i >> 1)-th use.  Four lanes of every warp issue them (one
-    // instruction a warp: issuing a copy is not cheap for the thread that does it), four token rows and one half of the
-    // block per copy; padding rows of a ragged tile read row 0 (their columns are never
-    // stored).  The buffer of block i + 1 was last read by block i - 1, whose MMAs every thread has waited for.
-    uint32_t img = 0;   // blocks this CTA has started
-    auto fetch_b = [&](uint32_t i, int blk) {
-        if (tid == 0) mbar_expect_tx(&S.bar_full[i & 1], 2 * PF_NT * 128);
+    // Everything a block reads from memory arrives by TMA while the block before it is under way.  The tile's quants:
+    // gather copies of four token rows and one half of the block each, issued (four lanes of every warp, one
+    // instruction a warp: issuing a copy is not cheap for the thread that does it) once the MMAs of the block before
+    // have been waited for; padding rows of a ragged tile read row 0 (their columns are never stored).  The rows' raw
+    // bytes: two boxes (64 gate rows, 64 up rows, one Q4_K block each), issued once every thread has taken its share
+    // of the block before into registers.  `img` counts the CTA's blocks: the parity of both barriers.
+    uint32_t img = 0;
+    auto fetch_b = [&](int blk) {
+        if (tid == 0) mbar_expect_tx(&S.bar_full, 2 * PF_NT * 128);
         if (lane < 4) {   // copy g = 4 warp + lane of the block's 32: rows 4 (g / 2) .. + 3, half g % 2
             const int g = 4 * warp + lane;
             const int4 rr = *reinterpret_cast<const int4 *>(&S.row_in[4 * (g >> 1)]);
             const int y0 = rr.x < 0 ? 0 : rr.x, y1 = rr.y < 0 ? 0 : rr.y, y2 = rr.z < 0 ? 0 : rr.z, y3 = rr.w < 0 ? 0 : rr.w;
-            tma_gather4(&S.b[i & 1][g & 1][4 * (g >> 1) * 128], &A.xq_map, blk * QK_K + 128 * (g & 1), y0, y1, y2, y3, &S.bar_full[i & 1]);
+            tma_gather4(&S.b[g & 1][4 * (g >> 1) * 128], &A.xq_map, blk * QK_K + 128 * (g & 1), y0, y1, y2, y3, &S.bar_full);
         }
     };
     // the CTA's tiles, one after the other: set-up (tensor memory, barrier) is paid once, and the second tile of an
@@ -231,17 +237,24 @@ __global__ void __launch_bounds__(GU_THREADS, 2) k_gu_prefill(const __grid_const
     const bool is_shared = slot < 0;
     int m;
     const int *list = nullptr;
-    const uint8_t *wg, *wu;
+    int wrow0;   // the tile's first row in the gate / up matrices as the tensor maps see them
     if (is_shared) {
         m = A.sh_count;
-        wg = A.sgate; wu = A.sup;
+        wrow0 = blockIdx.x * 64;
     } else {
         const int e = slot;
         m = A.g.count[e];
         list = A.g.pairs + A.g.offset[e];
-        wg = A.gate + (size_t)e * A.expert_bytes;
-        wu = A.up + (size_t)e * A.expert_bytes;
+        wrow0 = e * A.F + blockIdx.x * 64;
     }
+    const CUtensorMap *map_g = &A.w_map[is_shared ? 2 : 0], *map_u = &A.w_map[is_shared ? 3 : 1];
+    auto fetch_w = [&](int blk) {   // one thread (not the one that issues the MMAs)
+        if (tid == 32) {
+            mbar_expect_tx(&S.bar_raw, PF_M * Q4_K_BYTES);
+            tma_load_2d(&S.raw[0][0], map_g, blk * Q4_K_BYTES, wrow0, &S.bar_raw);
+            tma_load_2d(&S.raw[64][0], map_u, blk * Q4_K_BYTES, wrow0, &S.bar_raw);
+        }
+    };
     const int cnt = m - t0 < PF_NT ? m - t0 : PF_NT;
     if (tid < PF_NT) {
         int rin = -1, rout = -1;
@@ -253,7 +266,8 @@ __global__ void __launch_bounds__(GU_THREADS, 2) k_gu_prefill(const __grid_const
         S.row_out[tid] = rout;
     }
     __syncthreads();
-    fetch_b(img, 0);
+    fetch_b(0);
+    fetch_w(0);
 
     // this thread's weight row r: rows 0..63 are gate rows, 64..127 the up rows of the same 64 outputs.
     // Threads r and r + 128 share a row: kh = 0 decodes sub-blocks 0..3 of each block and drains
@@ -261,7 +275,6 @@ __global__ void __launch_bounds__(GU_THREADS, 2) k_gu_prefill(const __grid_const
     const int r = tid & (PF_M - 1), kh = tid >> 7;
     const int f0 = blockIdx.x * 64;
     const int nblk = A.H / QK_K;
-    const uint8_t *wrow = (r < 64 ? wg : wu) + (size_t)(f0 + (r & 63)) * nblk * Q4_K_BYTES;
 
     constexpr uint32_t IDESC_UU_S = make_idesc(2, 0, 1, PF_NT, PF_M);  // u8 x s8
     constexpr uint32_t IDESC_UU_U = make_idesc(2, 0, 0, PF_NT, PF_M);  // u8 x u8
@@ -274,16 +287,16 @@ __global__ void __launch_bounds__(GU_THREADS, 2) k_gu_prefill(const __grid_const
 #pragma unroll
     for (int i = 0; i < NC; i++) acc[i] = 0.f;
 
-    // the thread's half of the row's current block lives in registers (header + 64 bytes of quants);
-    // the next one is fetched while the MMAs run
-    uint4 blk[5];
-    blk[0] = reinterpret_cast<const uint4 *>(wrow)[0];
-#pragma unroll
-    for (int i = 0; i < 4; i++) blk[1 + i] = reinterpret_cast<const uint4 *>(wrow)[1 + 4 * kh + i];
-
     for (int b = 0; b < nblk && ok; b++) {
-        // ---- the next block's quants set out first
-        if (b + 1 < nblk) fetch_b(img + 1, b + 1);
+        // ---- the thread's half of its row's block: header + 64 bytes of quants, from the rows the copies brought
+        if (!mbar_wait_spin(&S.bar_raw, img & 1)) {
+            set_status(A.status, PMOE_ERR_TIMEOUT, 32, b);
+            ok = false;
+        }
+        uint4 blk[5];
+        blk[0] = *reinterpret_cast<const uint4 *>(&S.raw[r][0]);
+#pragma unroll
+        for (int i = 0; i < 4; i++) blk[1 + i] = *reinterpret_cast<const uint4 *>(&S.raw[r][16 + 64 * kh + 16 * i]);
         uint4 bs0 = make_uint4(0, 0, 0, 0), bs1 = make_uint4(0, 0, 0, 0);
         float dx_reg = 0.f;
         const int rin_s = tid < PF_NT ? S.row_in[tid] : -1;
@@ -351,16 +364,18 @@ __global__ void __launch_bounds__(GU_THREADS, 2) k_gu_prefill(const __grid_const
             S.dx[tid] = dx;
         }
         tc_fence_before();
-        __syncthreads();
+        ok = __syncthreads_and(ok);
+        if (!ok) break;
+        if (b + 1 < nblk) fetch_w(b + 1);   // every thread has its share of this block's rows in registers
         // ---- MMAs of this block, issued by one thread
         if (tid == 0) {
             fence_proxy_async();   // everyone's stores are ordered before the barrier; the issuing thread crosses over to the async proxy
             tc_fence_after();
-            if (!mbar_wait_spin(&S.bar_full[img & 1], (img >> 1) & 1)) set_status(A.status, PMOE_ERR_TIMEOUT, 31, b);   // (the MMAs then run on what is there; the status word says so)
+            if (!mbar_wait_spin(&S.bar_full, img & 1)) set_status(A.status, PMOE_ERR_TIMEOUT, 31, b);   // (the MMAs then run on what is there; the status word says so)
 #pragma unroll
             for (int ks = 0; ks < 8; ks++) {  // 32 bytes of K per instruction: A two 16-byte chunks further on per step, B 32 bytes inside its half's swizzled rows
                 const uint64_t ka = (uint64_t)(ks * ((2 * PF_M * 16) >> 4));
-                const uint64_t db = smem_desc_sw128(S.b[img & 1][ks >> 2]) + (uint64_t)((ks & 3) * (32 >> 4));
+                const uint64_t db = smem_desc_sw128(S.b[ks >> 2]) + (uint64_t)((ks & 3) * (32 >> 4));
                 mma_i8(tmem + 0, desc_a0 + ka, db, IDESC_UU_S, ks > 0);
                 mma_i8(tmem + 64, desc_a1 + ka, db, IDESC_UU_S, ks > 0);
             }
@@ -368,18 +383,13 @@ __global__ void __launch_bounds__(GU_THREADS, 2) k_gu_prefill(const __grid_const
             mma_i8(tmem + 192, desc_am, desc_bl, IDESC_UU_U, 0);
             tc_commit(&S.bar);
         }
-        if (b + 1 < nblk) {  // next block of this thread's row, in flight during the MMAs and the fold
-            const uint4 *nx = reinterpret_cast<const uint4 *>(wrow + (size_t)(b + 1) * Q4_K_BYTES);
-            blk[0] = nx[0];
-#pragma unroll
-            for (int i = 0; i < 4; i++) blk[1 + i] = nx[1 + 4 * kh + i];
-        }
         if (!mbar_wait_spin(&S.bar, phase)) {
             set_status(A.status, PMOE_ERR_TIMEOUT, 30, b);
             ok = false;
         }
         phase ^= 1;
         tc_fence_after();
+        if (ok && b + 1 < nblk) fetch_b(b + 1);   // the MMAs that read the tile are done
         // ---- fold the block into the f32 accumulators: row r = TMEM lane r (a warp reaches the 32
         // lanes of its quarter, warp % 4), this thread's half of the token columns
         if (ok) {
@@ -401,7 +411,7 @@ __global__ void __launch_bounds__(GU_THREADS, 2) k_gu_prefill(const __grid_const
             }
         }
         tc_fence_before();
-        __syncthreads();  // operands and accumulators are free for the next block
+        ok = __syncthreads_and(ok);  // operands and accumulators are free for the next block; a thread that gave up takes the CTA with it
         tc_fence_after();
         img++;
     }
@@ -439,7 +449,10 @@ __global__ void __launch_bounds__(GU_THREADS, 2) k_gu_prefill(const __grid_const
     tc_fence_after();
     }
     // a CTA that gave up may have a block's copies under way: they land (bounded wait) before its shared memory goes
-    if (!ok && tid == 0) mbar_wait(&S.bar_full[img & 1], (img >> 1) & 1, 1u << 8);
+    if (!ok && tid == 0) {
+        mbar_wait(&S.bar_full, img & 1, 1u << 8);
+        mbar_wait(&S.bar_raw, img & 1, 1u << 8);
+    }
     __syncthreads();
     if (warp == 0) tmem_dealloc(tmem, PF_TMEM_COLS);
 }
@@ -1222,6 +1235,8 @@ static int max_routed_tiles(const LayerDev &L, int n, int top_k)
     return (int)(pairs / PF_NT + act);
 }
 
+static bool q4k_rows_map(const uint8_t *w, size_t rows, int H, CUtensorMap *out);
+
 static bool pf_gu_ok(int dt) { return dt == PMOE_Q4_K || dt == PMOE_Q8_0; }
 static bool pf_dn_ok(int dt) { return dt == PMOE_Q6_K || dt == PMOE_Q4_K || dt == PMOE_Q8_0; }
 
@@ -1257,6 +1272,13 @@ cudaError_t launch_gate_up_prefill(const LayerDev &L, const Workspace &ws, int n
     A.tile_prefix = ws.groups.tile_prefix;
     A.xq = dt == PMOE_Q8_0 ? ws.x_q80 : ws.x_q8k;
     memcpy(&A.xq_map, ws.xq_map, sizeof(CUtensorMap));
+    if (dt == PMOE_Q4_K) {
+        bool got = true;
+        if (routed) got = q4k_rows_map(L.gate_exps, (size_t)L.E_local * L.F, L.H, &A.w_map[0]) &&
+                          q4k_rows_map(L.up_exps, (size_t)L.E_local * L.F, L.H, &A.w_map[1]);
+        if (got && shared) got = q4k_rows_map(L.sh_gate, (size_t)L.F, L.H, &A.w_map[2]) && q4k_rows_map(L.sh_up, (size_t)L.F, L.H, &A.w_map[3]);
+        if (!got) return cudaErrorInvalidValue;
+    }
     A.act = ws.act;
     A.status = ws.status;
     static bool configured = false;
@@ -1292,18 +1314,21 @@ static TmaEncode tma_encoder()
     return encode;
 }
 
-// row-major [rows, cols] of `elem_bytes`-byte elements, boxes of box_rows x box_cols, 128-byte swizzle
-static bool encode_2d(void *out_map, CUtensorMapDataType dt, size_t elem_bytes, void *base, size_t rows, size_t cols,
-                      uint32_t box_cols, uint32_t box_rows)
+// row-major [rows, cols] of `elem_bytes`-byte elements, boxes of box_rows x box_cols; 128-byte swizzle (box rows of 128
+// bytes) or none (box rows a multiple of 16 bytes)
+static bool encode_2d(void *out_map, CUtensorMapDataType dt, size_t elem_bytes, const void *base, size_t rows, size_t cols,
+                      uint32_t box_cols, uint32_t box_rows, bool swizzle = true)
 {
     TmaEncode encode = tma_encoder();
-    if (!encode || rows == 0 || cols % box_cols != 0 || box_cols * elem_bytes != 128) return false;
+    if (!encode || rows == 0 || cols % box_cols != 0 || ((uintptr_t)base & 15) || (cols * elem_bytes) % 16 != 0) return false;
+    if (swizzle ? box_cols * elem_bytes != 128 : (box_cols * elem_bytes) % 16 != 0) return false;
     CUtensorMap m;
     const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
     const cuuint64_t strides[1] = {(cuuint64_t)(cols * elem_bytes)};
     const cuuint32_t box[2] = {box_cols, box_rows}, estr[2] = {1, 1};
-    if (encode(&m, dt, 2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-               CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    if (encode(&m, dt, 2, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+               swizzle ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return false;
     memcpy(out_map, &m, sizeof(m));
     return true;
@@ -1312,6 +1337,32 @@ static bool encode_2d(void *out_map, CUtensorMapDataType dt, size_t elem_bytes, 
 bool make_act_h_map(Workspace &ws, size_t rows, int F)
 {
     return encode_2d(ws.act_h_map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, ws.act_h, rows, (size_t)F, DN_KSTEP, PF_NT);
+}
+
+// Descriptor of a Q4_K matrix [rows, H / 256 blocks] as bytes, boxes of 64 rows x one block.  The matrices are static
+// (a call with block multipliers installed brings other arrays): the descriptors are kept by array and shape.
+static bool q4k_rows_map(const uint8_t *w, size_t rows, int H, CUtensorMap *out)
+{
+    struct Key {
+        const uint8_t *w;
+        size_t rows;
+        int H;
+        bool operator<(const Key &o) const { return w != o.w ? w < o.w : rows != o.rows ? rows < o.rows : H < o.H; }
+    };
+    static std::mutex mu;
+    static std::map<Key, CUtensorMap> cache;
+    std::lock_guard<std::mutex> lock(mu);
+    const Key key{w, rows, H};
+    auto it = cache.find(key);
+    if (it == cache.end()) {
+        CUtensorMap m;
+        if (!encode_2d(&m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w, rows, (size_t)(H / QK_K) * Q4_K_BYTES, Q4_K_BYTES, 64, false))
+            return false;
+        if (cache.size() > 4096) cache.clear();
+        it = cache.emplace(key, m).first;
+    }
+    *out = it->second;
+    return true;
 }
 
 bool make_xq_map(Workspace &ws, size_t rows, int H)
