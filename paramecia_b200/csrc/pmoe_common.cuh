@@ -285,6 +285,10 @@ struct Workspace {
     alignas(64) unsigned char xq_map[128];      // TMA descriptor of x_q8k.qs: boxes of one row x 128 bytes, 128-byte swizzle
     const void *xq_map_base;                    // the array it was made for
     bool xq_map_ok;
+    alignas(64) unsigned char xq80_map[128];    // the same of x_q80.qs ...
+    alignas(64) unsigned char xd80_map[128];    // ... and of x_q80.d as [n, H / 32] floats: boxes of one row x four floats
+    const void *xq80_map_base, *xd80_map_base;
+    bool xq80_map_ok;
     float *act_h_scale;  // [n*(k+1)]     power of two a row of act_h was divided by (1 unless it would leave the fp16 range)
     float *partial;      // [n*(k+1), H]  weighted down-projection rows
     int *slot_done;      // [E_local + 1 + max_tokens/8] completion counters of the gate/up kernel: per expert, the shared

@@ -21,9 +21,14 @@
 //                  end (gate rows and up rows share one M = 128 tile) and written as f32.
 //   k_down_prefill down projection over the re-quantised activation (see below).
 //
-// Tiles: M = 128 weight rows (64 gate + 64 up), N = 64 tokens of one expert, operands staged in
-// shared memory in the K-major core-matrix layout (8 rows x 16 bytes, no swizzle).  Every wait
-// is bounded and reports through the status word; tensor memory is freed on every path.
+// Tiles: M = 128 weight rows (64 gate + 64 up), N = 64 tokens of one expert.  Decoded weight tiles
+// are staged in shared memory in the K-major core-matrix layout (8 rows x 16 bytes, no swizzle);
+// token tiles arrive by TMA (cp.async.bulk.tensor, no multicast) in the 128-byte swizzled K-major
+// layout: gather copies of four token rows for the Q4_K gate/up kernel, boxes of the expert-sorted
+// activation array for the K-quant down kernels; the Q4_K rows' raw blocks come through tensor
+// maps over the matrices as bytes.  The maps are encoded on the host with the driver's
+// cuTensorMapEncodeTiled, looked up at run time.  Every wait is bounded and reports through the
+// status word; tensor memory is freed on every path.
 #include "pmoe_common.cuh"
 #include <cstring>
 #include <map>
@@ -152,7 +157,9 @@ struct GuArgs {
     const int *tile_prefix;        // [n_active + 1] exclusive prefix of ceil(count / PF_NT) over active slots
     QAct xq;                       // Q8_K rows of the input [n, H]
     CUtensorMap xq_map;            // TMA descriptor of xq.qs for the Q4_K kernel: boxes of one row x 128 bytes, 128-byte swizzle
-    CUtensorMap w_map[4];          // ... of gate, up, sgate, sup as [rows, row bytes] bytes: boxes of 64 rows x one Q4_K block
+    CUtensorMap w_map[4];          // ... of gate, up, sgate, sup as [rows, row bytes / 4] words: boxes of 64 rows x one Q4_K block
+                                   // (Q8_0: x eight blocks)
+    CUtensorMap xd_map;            // Q8_0: ... of xq.d as [n, H / 32] floats: boxes of one row x 4 floats (a 128-wide step's scales)
     float *act;                    // [n*(k+1), F]
     DevStatus *status;
 };
@@ -251,8 +258,8 @@ __global__ void __launch_bounds__(GU_THREADS, 2) k_gu_prefill(const __grid_const
     auto fetch_w = [&](int blk) {   // one thread (not the one that issues the MMAs)
         if (tid == 32) {
             mbar_expect_tx(&S.bar_raw, PF_M * Q4_K_BYTES);
-            tma_load_2d(&S.raw[0][0], map_g, blk * Q4_K_BYTES, wrow0, &S.bar_raw);
-            tma_load_2d(&S.raw[64][0], map_u, blk * Q4_K_BYTES, wrow0, &S.bar_raw);
+            tma_load_2d(&S.raw[0][0], map_g, blk * (Q4_K_BYTES / 4), wrow0, &S.bar_raw);   // (the maps count 4-byte words)
+            tma_load_2d(&S.raw[64][0], map_u, blk * (Q4_K_BYTES / 4), wrow0, &S.bar_raw);
         }
     };
     const int cnt = m - t0 < PF_NT ? m - t0 : PF_NT;
@@ -465,33 +472,35 @@ __global__ void __launch_bounds__(GU_THREADS, 2) k_gu_prefill(const __grid_const
 // kernels, block after block in K order.  The weights need no decoding: a thread copies its row's quants into the
 // K-major core-matrix layout (the 34-byte blocks put every second block's quants 2 bytes off a word: funnel shifts).
 struct Gu80Ops {
-    uint8_t a[PF_M * 128];
-    uint8_t b[PF_NT * 128];
+    uint8_t a[PF_M * 128];          // the rows' quants of one step, core-matrix layout
+    uint8_t b[PF_NT * 128];         // the tokens' quants of one step: 64 rows of 128 bytes, 128-byte swizzle (gather copies)
     float dw[4][PF_M];
-    float dx[4][PF_NT];
 };
 struct Gu80Smem {
     union {
-        Gu80Ops o;                           // operands and scales of one step
+        Gu80Ops o;                           // operands and scales of one step (on a 1024-byte boundary)
         float xch[PF_M * (PF_NT + 1)];       // the accumulators' way to silu(gate) * up at the end
     };
-    // the rows' raw bytes, two steps (eight blocks, 272 bytes a row) at a time, double-buffered: one bulk copy a row
-    // (whole lines from memory, where 32 lanes loading from 32 rows would touch 32 lines with every instruction)
+    // the rows' raw bytes, two steps (eight blocks, 272 bytes a row) at a time, double-buffered: two TMA boxes (64 gate
+    // rows, 64 up rows) per chunk
     uint8_t raw[2][PF_M][8 * Q8_0_BYTES];
+    // the tokens' four scales of a step, two steps: a gather copy brings four tokens' scales (64 bytes) and wants a
+    // 128-byte aligned destination, so every group of four tokens has a 128-byte slot of which it fills half
+    float dx[2][PF_NT / 4][32];
     int row_in[PF_NT];
     int row_out[PF_NT];
-    uint64_t bar, bar_raw[2];
+    uint64_t bar, bar_raw[2], bar_full;
     uint32_t tmem_base;
     int slot, tile_in_slot;
 };
-static_assert(sizeof(Gu80Smem) + 128 <= 115712, "two CTAs of the Q8_0 gate/up GEMM share an SM");
-static_assert((8 * Q8_0_BYTES) % 16 == 0, "bulk copies need 16-byte alignment");
+static_assert(sizeof(Gu80Smem) + 1024 + 128 <= 115712, "two CTAs of the Q8_0 gate/up GEMM share an SM");
+static_assert((8 * Q8_0_BYTES) % 16 == 0, "TMA boxes need rows of a multiple of 16 bytes");
 
-__global__ void __launch_bounds__(GU_THREADS, 2) k_gu_prefill_q80(const GuArgs A)
+__global__ void __launch_bounds__(GU_THREADS, 2) k_gu_prefill_q80(const __grid_constant__ GuArgs A)
 {
     extern __shared__ __align__(128) uint8_t smem_raw[];
-    Gu80Smem &S = *reinterpret_cast<Gu80Smem *>(smem_raw);
-    const int tid = threadIdx.x, warp = tid >> 5;
+    Gu80Smem &S = *reinterpret_cast<Gu80Smem *>(smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u));
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
     const int n_active = A.routed ? *A.g.n_active : 0;
     const int routed_tiles = n_active ? A.tile_prefix[n_active] : 0;
@@ -510,6 +519,7 @@ __global__ void __launch_bounds__(GU_THREADS, 2) k_gu_prefill_q80(const GuArgs A
         mbar_init(&S.bar, 1);
         mbar_init(&S.bar_raw[0], 1);
         mbar_init(&S.bar_raw[1], 1);
+        mbar_init(&S.bar_full, 1);
         fence_mbar_init();
     }
     if (warp == 0) tmem_alloc(&S.tmem_base, PF_TMEM_COLS);
@@ -521,16 +531,16 @@ __global__ void __launch_bounds__(GU_THREADS, 2) k_gu_prefill_q80(const GuArgs A
     const bool is_shared = slot < 0;
     int m;
     const int *list = nullptr;
-    const uint8_t *wg, *wu;
+    int wrow0;   // the tile's first row in the gate / up matrices as the tensor maps see them
     if (is_shared) {
         m = A.sh_count;
-        wg = A.sgate; wu = A.sup;
+        wrow0 = blockIdx.x * 64;
     } else {
         m = A.g.count[slot];
         list = A.g.pairs + A.g.offset[slot];
-        wg = A.gate + (size_t)slot * A.expert_bytes;
-        wu = A.up + (size_t)slot * A.expert_bytes;
+        wrow0 = slot * A.F + blockIdx.x * 64;
     }
+    const CUtensorMap *map_g = &A.w_map[is_shared ? 2 : 0], *map_u = &A.w_map[is_shared ? 3 : 1];
     const int cnt = m - t0 < PF_NT ? m - t0 : PF_NT;
     if (tid < PF_NT) {
         int rin = -1, rout = -1;
@@ -548,13 +558,10 @@ __global__ void __launch_bounds__(GU_THREADS, 2) k_gu_prefill_q80(const GuArgs A
     const int r = tid & (PF_M - 1), kh = tid >> 7;
     const int f0 = blockIdx.x * 64;
     const int nkb = A.H / QK8_0;   // blocks per row
-    const uint8_t *wrow = (r < 64 ? wg : wu) + (size_t)(f0 + (r & 63)) * nkb * Q8_0_BYTES;
     const int steps = A.H / 128;
-    const int tk = tid >> 2, quarter = tid & 3;   // B side: one block of one token per thread
-    const int rin_b = S.row_in[tk];
 
     constexpr uint32_t IDESC_SS = make_idesc(2, 1, 1, PF_NT, PF_M);  // s8 x s8 -> s32
-    const uint64_t desc_a = smem_desc(S.o.a, PF_M * 16, 128), desc_b = smem_desc(S.o.b, PF_NT * 16, 128);
+    const uint64_t desc_a = smem_desc(S.o.a, PF_M * 16, 128), desc_b = smem_desc_sw128(S.o.b);
     constexpr int NC = PF_NT / 2;
     float acc[NC];
 #pragma unroll
@@ -568,34 +575,42 @@ __global__ void __launch_bounds__(GU_THREADS, 2) k_gu_prefill_q80(const GuArgs A
     constexpr int CHUNK = 8 * Q8_0_BYTES;
     const int chunks = steps / 2;
     auto fetch_chunk = [&](int c) {
-        if (tid == 0) mbar_expect_tx(&S.bar_raw[c & 1], PF_M * CHUNK);
-        if (tid < PF_M) bulk_g2s(S.raw[c & 1][r], wrow + (size_t)c * CHUNK, CHUNK, &S.bar_raw[c & 1]);
+        if (tid == 32) {   // (not the thread that issues the MMAs)
+            mbar_expect_tx(&S.bar_raw[c & 1], PF_M * CHUNK);
+            tma_load_2d(&S.raw[c & 1][0][0], map_g, c * (CHUNK / 4), wrow0, &S.bar_raw[c & 1]);   // (the maps count 4-byte words)
+            tma_load_2d(&S.raw[c & 1][64][0], map_u, c * (CHUNK / 4), wrow0, &S.bar_raw[c & 1]);
+        }
     };
+    // The tokens' side of step s: their quants (64 rows of 128 bytes) and their four scales, by gather copies of four
+    // token rows each, one instruction per warp (lanes 0..3: copy g = 4 warp + lane; the first sixteen bring quants,
+    // the others scales); padding rows of a ragged tile read row 0, their columns are never stored.  Issued when the
+    // MMAs of step s - 1 are done; the scales have two buffers, since the drain of step s - 1 still reads its own.
+    auto fetch_x = [&](int s_) {
+        if (tid == 0) mbar_expect_tx(&S.bar_full, PF_NT * 128 + PF_NT * 16);
+        if (lane < 4) {
+            const int g = 4 * warp + lane, grp = g & 15;
+            const int4 rr = *reinterpret_cast<const int4 *>(&S.row_in[4 * grp]);
+            const int y0 = rr.x < 0 ? 0 : rr.x, y1 = rr.y < 0 ? 0 : rr.y, y2 = rr.z < 0 ? 0 : rr.z, y3 = rr.w < 0 ? 0 : rr.w;
+            if (g < 16) tma_gather4(&S.o.b[4 * grp * 128], &A.xq_map, 128 * s_, y0, y1, y2, y3, &S.bar_full);
+            else tma_gather4(&S.dx[s_ & 1][grp][0], &A.xd_map, 4 * s_, y0, y1, y2, y3, &S.bar_full);
+        }
+    };
+    fetch_x(0);
     fetch_chunk(0);
     if (chunks > 1) fetch_chunk(1);
     int chunks_seen = 0, chunks_issued = chunks > 1 ? 2 : 1;
     uint32_t raw[17];
     for (int s = 0; s < steps && ok; s++) {
-        // ---- this step's activations first: they fly while the weights are laid out.  Chunks quarter and quarter + 4
-        // of the token's 128 bytes: the four threads of a token read 64 contiguous bytes with each load.
-        uint4 bv[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
-        float dxv = 0.f;
-        if (rin_b >= 0) {
-            const uint4 *src = reinterpret_cast<const uint4 *>(A.xq.qs + (size_t)rin_b * A.H + 128 * s) + quarter;
-            bv[0] = src[0];
-            bv[1] = src[4];
-            dxv = A.xq.d[(size_t)rin_b * nkb + 4 * s + quarter];
-        }
         if ((s & 1) == 0) {
             const int c = s >> 1;
             // the buffer chunk c - 1 sat in is free: its last readers passed the barrier that ended step s - 1
             if (c >= 1 && c + 1 < chunks) { fetch_chunk(c + 1); chunks_issued = c + 2; }
-            if (!mbar_wait(&S.bar_raw[c & 1], (uint32_t)((c >> 1) & 1))) {
+            if (!mbar_wait(&S.bar_raw[c & 1], (uint32_t)((c >> 1) & 1))) {   // (the vote below takes the CTA out as one)
                 set_status(A.status, PMOE_ERR_TIMEOUT, 36, c);
                 ok = false;
-                break;
+            } else {
+                chunks_seen = c + 1;
             }
-            chunks_seen = c + 1;
         }
         {   // this thread's two blocks: 68 bytes, 4-byte aligned (a step starts on an 8-byte boundary)
             const uint8_t *p = S.raw[(s >> 1) & 1][r] + 136 * (s & 1) + 68 * kh;
@@ -628,19 +643,20 @@ __global__ void __launch_bounds__(GU_THREADS, 2) k_gu_prefill_q80(const GuArgs A
             S.o.dw[2 * kh][r] = half_bits_to_float((uint16_t)(raw[0] & 0xffffu));
             S.o.dw[2 * kh + 1][r] = half_bits_to_float((uint16_t)(raw[8] >> 16));
         }
-        // ---- B: block `quarter` of token tk
-        *reinterpret_cast<uint4 *>(S.o.b + core_off(PF_NT, tk, 16 * quarter)) = bv[0];
-        *reinterpret_cast<uint4 *>(S.o.b + core_off(PF_NT, tk, 16 * (quarter + 4))) = bv[1];
-        S.o.dx[quarter][tk] = dxv;
+        // ---- the tokens' side must have landed (every thread looks: the drain reads the scales)
+        if (!mbar_wait_spin(&S.bar_full, (uint32_t)(s & 1))) {
+            set_status(A.status, PMOE_ERR_TIMEOUT, 37, s);
+            ok = false;
+        }
         tc_fence_before();
-        __syncthreads();
+        ok = __syncthreads_and(ok);
+        if (!ok) break;
         if (tid == 0) {
             fence_proxy_async();   // everyone's stores are ordered before the barrier; the issuing thread crosses over to the async proxy
             tc_fence_after();
 #pragma unroll
             for (int j = 0; j < 4; j++)   // one block = 32 bytes of K = one instruction, its own 64 columns
-                mma_i8(tmem + 64 * j, desc_a + (uint64_t)(j * ((2 * PF_M * 16) >> 4)), desc_b + (uint64_t)(j * ((2 * PF_NT * 16) >> 4)),
-                       IDESC_SS, 0);
+                mma_i8(tmem + 64 * j, desc_a + (uint64_t)(j * ((2 * PF_M * 16) >> 4)), desc_b + (uint64_t)(j * (32 >> 4)), IDESC_SS, 0);
             tc_commit(&S.bar);
         }
         if (!mbar_wait_spin(&S.bar, phase)) {
@@ -649,29 +665,33 @@ __global__ void __launch_bounds__(GU_THREADS, 2) k_gu_prefill_q80(const GuArgs A
         }
         phase ^= 1;
         tc_fence_after();
+        if (ok && s + 1 < steps) fetch_x(s + 1);   // the MMAs that read the tile are done
         if (ok) {
             const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16) + kh * NC;
+            const float dw0 = S.o.dw[0][r], dw1 = S.o.dw[1][r], dw2 = S.o.dw[2][r], dw3 = S.o.dw[3][r];
 #pragma unroll
-            for (int j = 0; j < 4; j++) {
-                const float dw = S.o.dw[j][r];
+            for (int cc = 0; cc < NC / 16; cc++) {
+                uint32_t v0[16], v1[16], v2[16], v3[16];
+                tmem_ld16(lane_addr + 0 + cc * 16, v0);
+                tmem_ld16(lane_addr + 64 + cc * 16, v1);
+                tmem_ld16(lane_addr + 128 + cc * 16, v2);
+                tmem_ld16(lane_addr + 192 + cc * 16, v3);
+                tmem_ld_wait();
 #pragma unroll
-                for (int cc = 0; cc < NC / 16; cc++) {
-                    uint32_t v[16];
-                    tmem_ld16(lane_addr + 64 * j + cc * 16, v);
-                    tmem_ld_wait();
-#pragma unroll
-                    for (int q = 0; q < 4; q++) {
-                        const float4 dx = *reinterpret_cast<const float4 *>(&S.o.dx[j][kh * NC + cc * 16 + 4 * q]);
-                        acc[cc * 16 + 4 * q + 0] += (dw * dx.x) * (float)(int)v[4 * q + 0];
-                        acc[cc * 16 + 4 * q + 1] += (dw * dx.y) * (float)(int)v[4 * q + 1];
-                        acc[cc * 16 + 4 * q + 2] += (dw * dx.z) * (float)(int)v[4 * q + 2];
-                        acc[cc * 16 + 4 * q + 3] += (dw * dx.w) * (float)(int)v[4 * q + 3];
-                    }
+                for (int t = 0; t < 16; t++) {   // a token's sum takes the step's four blocks in K order
+                    const int tk = kh * NC + cc * 16 + t;
+                    const float4 dx = *reinterpret_cast<const float4 *>(&S.dx[s & 1][tk >> 2][4 * (tk & 3)]);
+                    float a = acc[cc * 16 + t];
+                    a += (dw0 * dx.x) * (float)(int)v0[t];
+                    a += (dw1 * dx.y) * (float)(int)v1[t];
+                    a += (dw2 * dx.z) * (float)(int)v2[t];
+                    a += (dw3 * dx.w) * (float)(int)v3[t];
+                    acc[cc * 16 + t] = a;
                 }
             }
         }
         tc_fence_before();
-        __syncthreads();  // operands, scales and accumulators are free for the next step
+        ok = __syncthreads_and(ok);  // operands, scales and accumulators are free for the next step
         tc_fence_after();
     }
 
@@ -702,8 +722,10 @@ __global__ void __launch_bounds__(GU_THREADS, 2) k_gu_prefill_q80(const GuArgs A
                 if (rout[i] >= 0) A.act[(size_t)rout[i] * A.F + f0 + f] = v[i];
         }
     }
-    if (!ok) {   // gave up somewhere: chunks may still be on their way into this CTA's shared memory
-        for (int c = chunks_seen; c < chunks_issued; c++) mbar_wait(&S.bar_raw[c & 1], (uint32_t)((c >> 1) & 1));
+    if (!ok && tid == 0) {   // gave up somewhere: copies may still be on their way into this CTA's shared memory
+        for (int c = chunks_seen; c < chunks_issued; c++) mbar_wait(&S.bar_raw[c & 1], (uint32_t)((c >> 1) & 1), 1u << 8);
+        mbar_wait(&S.bar_full, 0, 1u << 8);
+        mbar_wait(&S.bar_full, 1, 1u << 8);
     }
     __syncthreads();
     if (warp == 0) tmem_dealloc(tmem, PF_TMEM_COLS);
@@ -1235,7 +1257,9 @@ static int max_routed_tiles(const LayerDev &L, int n, int top_k)
     return (int)(pairs / PF_NT + act);
 }
 
-static bool q4k_rows_map(const uint8_t *w, size_t rows, int H, CUtensorMap *out);
+static bool rows_map(const uint8_t *w, size_t rows, size_t row_bytes, uint32_t box_bytes, CUtensorMap *out);
+
+static size_t row_bytes_of_gate(const LayerDev &L, int dt) { return row_bytes(dt, L.H); }
 
 static bool pf_gu_ok(int dt) { return dt == PMOE_Q4_K || dt == PMOE_Q8_0; }
 static bool pf_dn_ok(int dt) { return dt == PMOE_Q6_K || dt == PMOE_Q4_K || dt == PMOE_Q8_0; }
@@ -1246,6 +1270,9 @@ bool prefill_supported(const LayerDev &L, const Workspace &ws, bool routed, bool
     // the Q4_K kernel gathers the quantised rows through a tensor map made for the workspace's own array
     if (((routed && L.gate_dtype == PMOE_Q4_K) || (shared && L.sh_gate_dtype == PMOE_Q4_K)) &&
         !(ws.xq_map_ok && ws.xq_map_base == ws.x_q8k.qs))
+        return false;
+    if (((routed && L.gate_dtype == PMOE_Q8_0) || (shared && L.sh_gate_dtype == PMOE_Q8_0)) &&
+        !(ws.xq80_map_ok && ws.xq80_map_base == ws.x_q80.qs && ws.xd80_map_base == ws.x_q80.d))
         return false;
     if (routed && !pf_gu_ok(L.gate_dtype)) return false;
     if (shared && !pf_gu_ok(L.sh_gate_dtype)) return false;
@@ -1271,12 +1298,16 @@ cudaError_t launch_gate_up_prefill(const LayerDev &L, const Workspace &ws, int n
     A.g = ws.groups;
     A.tile_prefix = ws.groups.tile_prefix;
     A.xq = dt == PMOE_Q8_0 ? ws.x_q80 : ws.x_q8k;
-    memcpy(&A.xq_map, ws.xq_map, sizeof(CUtensorMap));
-    if (dt == PMOE_Q4_K) {
+    {
+        const bool q80 = dt == PMOE_Q8_0;
+        memcpy(&A.xq_map, q80 ? ws.xq80_map : ws.xq_map, sizeof(CUtensorMap));
+        memcpy(&A.xd_map, ws.xd80_map, sizeof(CUtensorMap));
+        const size_t row_bytes = row_bytes_of_gate(L, dt);
+        const uint32_t box = q80 ? 8 * Q8_0_BYTES : Q4_K_BYTES;
         bool got = true;
-        if (routed) got = q4k_rows_map(L.gate_exps, (size_t)L.E_local * L.F, L.H, &A.w_map[0]) &&
-                          q4k_rows_map(L.up_exps, (size_t)L.E_local * L.F, L.H, &A.w_map[1]);
-        if (got && shared) got = q4k_rows_map(L.sh_gate, (size_t)L.F, L.H, &A.w_map[2]) && q4k_rows_map(L.sh_up, (size_t)L.F, L.H, &A.w_map[3]);
+        if (routed) got = rows_map(L.gate_exps, (size_t)L.E_local * L.F, row_bytes, box, &A.w_map[0]) &&
+                          rows_map(L.up_exps, (size_t)L.E_local * L.F, row_bytes, box, &A.w_map[1]);
+        if (got && shared) got = rows_map(L.sh_gate, (size_t)L.F, row_bytes, box, &A.w_map[2]) && rows_map(L.sh_up, (size_t)L.F, row_bytes, box, &A.w_map[3]);
         if (!got) return cudaErrorInvalidValue;
     }
     A.act = ws.act;
@@ -1285,14 +1316,14 @@ cudaError_t launch_gate_up_prefill(const LayerDev &L, const Workspace &ws, int n
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(k_gu_prefill, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(GuSmem) + 1024 + 128);
         if (e == cudaSuccess)
-            e = cudaFuncSetAttribute(k_gu_prefill_q80, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Gu80Smem) + 128);
+            e = cudaFuncSetAttribute(k_gu_prefill_q80, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Gu80Smem) + 1024 + 128);
 
         if (e != cudaSuccess) return e;
         configured = true;
     }
     const int tiles = (routed ? max_routed_tiles(L, n, top_k) : 0) + (shared ? (ws.sh_count + PF_NT - 1) / PF_NT : 0);
     dim3 grid(L.F / 64, tiles);
-    if (dt == PMOE_Q8_0) k_gu_prefill_q80<<<grid, GU_THREADS, sizeof(Gu80Smem) + 128, s>>>(A);
+    if (dt == PMOE_Q8_0) k_gu_prefill_q80<<<grid, GU_THREADS, sizeof(Gu80Smem) + 1024 + 128, s>>>(A);
     else k_gu_prefill<<<dim3(L.F / 64, (tiles + GU_REPS - 1) / GU_REPS), GU_THREADS, sizeof(GuSmem) + 1024 + 128, s>>>(A);
     count_launch();
     return cudaGetLastError();
@@ -1339,24 +1370,32 @@ bool make_act_h_map(Workspace &ws, size_t rows, int F)
     return encode_2d(ws.act_h_map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, ws.act_h, rows, (size_t)F, DN_KSTEP, PF_NT);
 }
 
-// Descriptor of a Q4_K matrix [rows, H / 256 blocks] as bytes, boxes of 64 rows x one block.  The matrices are static
+// Descriptor of a quantised matrix [rows, row_bytes / 4] as 4-byte words, boxes of 64 rows x box_bytes.  The matrices are static
 // (a call with block multipliers installed brings other arrays): the descriptors are kept by array and shape.
-static bool q4k_rows_map(const uint8_t *w, size_t rows, int H, CUtensorMap *out)
+static bool rows_map(const uint8_t *w, size_t rows, size_t row_bytes, uint32_t box_bytes, CUtensorMap *out)
 {
     struct Key {
         const uint8_t *w;
-        size_t rows;
-        int H;
-        bool operator<(const Key &o) const { return w != o.w ? w < o.w : rows != o.rows ? rows < o.rows : H < o.H; }
+        size_t rows, row_bytes;
+        uint32_t box;
+        bool operator<(const Key &o) const
+        {
+            if (w != o.w) return w < o.w;
+            if (rows != o.rows) return rows < o.rows;
+            if (row_bytes != o.row_bytes) return row_bytes < o.row_bytes;
+            return box < o.box;
+        }
     };
     static std::mutex mu;
     static std::map<Key, CUtensorMap> cache;
     std::lock_guard<std::mutex> lock(mu);
-    const Key key{w, rows, H};
+    const Key key{w, rows, row_bytes, box_bytes};
     auto it = cache.find(key);
     if (it == cache.end()) {
         CUtensorMap m;
-        if (!encode_2d(&m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w, rows, (size_t)(H / QK_K) * Q4_K_BYTES, Q4_K_BYTES, 64, false))
+        // (as 4-byte words: a box dimension may not exceed 256 elements, and eight Q8_0 blocks are 272 bytes)
+        if (row_bytes % 4 != 0 || box_bytes % 4 != 0 ||
+            !encode_2d(&m, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, w, rows, row_bytes / 4, box_bytes / 4, 64, false))
             return false;
         if (cache.size() > 4096) cache.clear();
         it = cache.emplace(key, m).first;
@@ -1368,6 +1407,10 @@ static bool q4k_rows_map(const uint8_t *w, size_t rows, int H, CUtensorMap *out)
 bool make_xq_map(Workspace &ws, size_t rows, int H)
 {
     ws.xq_map_base = ws.x_q8k.qs;
+    ws.xq80_map_base = ws.x_q80.qs;
+    ws.xd80_map_base = ws.x_q80.d;
+    ws.xq80_map_ok = encode_2d(ws.xq80_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, ws.x_q80.qs, rows, (size_t)H, 128, 1) &&
+                     encode_2d(ws.xd80_map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, ws.x_q80.d, rows, (size_t)H / QK8_0, 4, 1, false);
     return encode_2d(ws.xq_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, ws.x_q8k.qs, rows, (size_t)H, 128, 1);
 }
 
