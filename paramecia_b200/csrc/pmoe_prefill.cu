@@ -209,6 +209,11 @@ __global__ void __launch_bounds__(GU_THREADS, 2) k_gu_prefill(const __grid_const
     const uint32_t tmem = S.tmem_base;
     uint32_t phase = 0;
     bool ok = true;
+    // K positions 16 .. 31 of the partial-sum digit tiles stay zero for the CTA's life (the MMA's K is 32)
+    if (tid < PF_NT) {
+        *reinterpret_cast<uint4 *>(S.bh + core_off(PF_NT, tid, 16)) = make_uint4(0, 0, 0, 0);
+        *reinterpret_cast<uint4 *>(S.bl + core_off(PF_NT, tid, 16)) = make_uint4(0, 0, 0, 0);
+    }
     // Everything a block reads from memory arrives by TMA while the block before it is under way.  The tile's quants:
     // gather copies of four token rows and one half of the block each, issued (four lanes of every warp, one
     // instruction a warp: issuing a copy is not cheap for the thread that does it) once the MMAs of the block before
@@ -304,14 +309,15 @@ __global__ void __launch_bounds__(GU_THREADS, 2) k_gu_prefill(const __grid_const
         blk[0] = *reinterpret_cast<const uint4 *>(&S.raw[r][0]);
 #pragma unroll
         for (int i = 0; i < 4; i++) blk[1 + i] = *reinterpret_cast<const uint4 *>(&S.raw[r][16 + 64 * kh + 16 * i]);
-        uint4 bs0 = make_uint4(0, 0, 0, 0), bs1 = make_uint4(0, 0, 0, 0);
+        // the tile's partial sums of 16 quants: four threads per token, four sums each (every warp takes its share of
+        // this, the loads are whole sectors)
+        const int tq = tid >> 2, qq = tid & 3;
+        const int rin_q = S.row_in[tq];
+        uint2 bsq = make_uint2(0u, 0u);
         float dx_reg = 0.f;
-        const int rin_s = tid < PF_NT ? S.row_in[tid] : -1;
-        if (rin_s >= 0) {
-            const uint4 *bsp = reinterpret_cast<const uint4 *>(A.xq.bsums + (size_t)rin_s * (A.H / 16) + b * 16);
-            bs0 = bsp[0];
-            bs1 = bsp[1];
-            dx_reg = A.xq.d[(size_t)rin_s * nblk + b];
+        if (rin_q >= 0) {
+            bsq = *reinterpret_cast<const uint2 *>(A.xq.bsums + (size_t)rin_q * (A.H / 16) + b * 16 + 4 * qq);
+            if (qq == 0) dx_reg = A.xq.d[(size_t)rin_q * nblk + b];
         }
         // ---- A: two digit tiles and the mins tile for this thread's row
         const uint4 hdr = blk[0];
@@ -354,21 +360,18 @@ __global__ void __launch_bounds__(GU_THREADS, 2) k_gu_prefill(const __grid_const
             *reinterpret_cast<uint4 *>(S.am + core_off(PF_M, r, 0)) = make_uint4(w0, w1, w2, w3);
             *reinterpret_cast<uint4 *>(S.am + core_off(PF_M, r, 16)) = make_uint4(0, 0, 0, 0);
         }
-        if (tid < PF_NT) {  // partial sums of 16 quants as two digits: bsum = 64*h + l, l in [0,63]
-            uint32_t hw[4] = {0, 0, 0, 0}, lw[4] = {0, 0, 0, 0};
-            const float dx = dx_reg;
-            const uint32_t bw[8] = {bs0.x, bs0.y, bs0.z, bs0.w, bs1.x, bs1.y, bs1.z, bs1.w};  // 16 x int16
+        {   // partial sums as two digits: bsum = 64*h + l, l in [0,63]; K positions 4 qq .. 4 qq + 3 of token tq
+            uint32_t hw = 0, lw = 0;
+            const uint32_t bw[2] = {bsq.x, bsq.y};   // 4 x int16
 #pragma unroll
-            for (int i = 0; i < 16; i++) {
+            for (int i = 0; i < 4; i++) {
                 const int v = (int)(int16_t)(bw[i >> 1] >> (16 * (i & 1)));
-                hw[i >> 2] |= (uint32_t)((v >> 6) & 0xFF) << (8 * (i & 3));
-                lw[i >> 2] |= (uint32_t)(v & 63) << (8 * (i & 3));
+                hw |= (uint32_t)((v >> 6) & 0xFF) << (8 * i);
+                lw |= (uint32_t)(v & 63) << (8 * i);
             }
-            *reinterpret_cast<uint4 *>(S.bh + core_off(PF_NT, tid, 0)) = make_uint4(hw[0], hw[1], hw[2], hw[3]);
-            *reinterpret_cast<uint4 *>(S.bh + core_off(PF_NT, tid, 16)) = make_uint4(0, 0, 0, 0);
-            *reinterpret_cast<uint4 *>(S.bl + core_off(PF_NT, tid, 0)) = make_uint4(lw[0], lw[1], lw[2], lw[3]);
-            *reinterpret_cast<uint4 *>(S.bl + core_off(PF_NT, tid, 16)) = make_uint4(0, 0, 0, 0);
-            S.dx[tid] = dx;
+            *reinterpret_cast<uint32_t *>(S.bh + core_off(PF_NT, tq, 4 * qq)) = hw;
+            *reinterpret_cast<uint32_t *>(S.bl + core_off(PF_NT, tq, 4 * qq)) = lw;
+            if (qq == 0) S.dx[tq] = dx_reg;
         }
         tc_fence_before();
         ok = __syncthreads_and(ok);
