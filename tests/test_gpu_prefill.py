@@ -49,6 +49,31 @@ def test_forced_prefill_matches_oracle(force_prefill, preset, E, k, n):
     assert rel_l2(got, want) <= 6e-4   # fp16 down GEMM: expected about 3e-4
 
 
+@pytest.mark.parametrize("prefill", ["0", "1"])
+def test_grouping_spread_over_ctas(prefill):
+    # 1100 tokens x top-8 = 8800 (token, slot) pairs: from 8192 pairs on the counting and the scatter of the
+    # grouping run one CTA per 1024 pairs (here nine, the last one ragged) around the one-CTA scan; both the
+    # tensor-core kernels and the streaming ones read its lists
+    n = 1100
+    old = os.environ.get("PMOE_PREFILL")
+    os.environ["PMOE_PREFILL"] = prefill
+    try:
+        t = synth.make_layer(E=64, k=8, preset="q4k_q6k_all", seed=17, zipf=True)
+        blk = synth.make_block(t, DEV, max_tokens=n)
+        x = seeded_x(n, 2048, 77, torch.bfloat16)
+        out, (logits, idx) = blk.forward_with_stats(x.to(DEV), out_dtype=torch.float32)
+        blk.status()
+    finally:
+        if old is None:
+            del os.environ["PMOE_PREFILL"]
+        else:
+            os.environ["PMOE_PREFILL"] = old
+    want, _, want_idx, _ = oracle_layer(t).forward(x.float().numpy())
+    assert np.array_equal(idx.cpu().numpy().astype(np.uint32), want_idx)
+    got = out.cpu().numpy()
+    assert max_abs(got, want) <= MAX_ABS_TOL and rel_l2(got, want) <= REL_L2_TOL
+
+
 def test_skewed_routing_takes_the_prefill_path_by_itself():
     # Zipf-biased router: a few experts get most tokens, some get none, tiles are ragged
     n = 700
