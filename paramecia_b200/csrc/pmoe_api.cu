@@ -206,7 +206,12 @@ int pmoe::run_experts(pmoe_layer *L, Workspace &ws, const void *x, int x_dtype, 
     // prefill: many tokens per expert -> grouped tensor-core GEMM; decode: streaming GEMV.  The
     // expected number of tokens per routed expert is n * top_k / E whatever slice this layer holds.
     const char *force = getenv("PMOE_PREFILL");
-    const bool want_prefill = force ? atoi(force) != 0 : (long)n * top_k >= 8L * d.E && n >= 512;
+    // Measured with uniform routing (every expert meets about n k / E tokens, so there are at least as many token tiles
+    // as experts): the streaming kernels take 150 us + 0.7 us per token, the tensor-core kernels 970 us flat up to
+    // 1 024 tokens and little more beyond; they cross at 23 tokens per expert.  One rank of eight (512 rows, 64 local
+    // experts, 10 tokens each): 94 us against 219.  A router that sends most tokens to few experts fills its tiles
+    // earlier, but the host does not see the counts.
+    const bool want_prefill = force ? atoi(force) != 0 : (long)n * top_k >= 24L * d.E && n >= 512;
     bool prefill = want_prefill && prefill_supported(d, ws, routed, shared);
     // A shared expert the tensor-core kernels do not take (e.g. Q8_0) does not hold the routed experts
     // back: they go through the tensor-core kernels and the shared expert through the streaming ones.
