@@ -471,7 +471,7 @@ const char *pmoe_trace_phase_name(int phase)
 int pmoe_route(pmoe_layer *L, const void *x, int x_dtype, int n, float *logits_out, uint32_t *idx_out, float *w_out,
                void *stream)
 {
-    float dummy;
+    float dummy = 0.f;
     int rc = check_call(L, x, x_dtype, n, &dummy, PMOE_F32);
     if (rc) return rc;
     if (n == 0) return PMOE_OK;

@@ -39,7 +39,6 @@ namespace pmoe {
 
 constexpr int PF_NT = 64;        // tokens per tile (MMA N)
 constexpr int PF_M = 128;        // rows per tile (MMA M): 64 gate + 64 up
-constexpr int PF_THREADS = 128;
 constexpr int GU_REPS = 2;        // token tiles a CTA of the Q4_K gate/up kernel takes, one after the other
 constexpr int GU_THREADS = 256;   // gate/up kernel: two threads per weight row (one per half of a 256-wide block)
 constexpr int PF_TMEM_COLS = 256;  // D0, D1, Dh, Dl: 4 x 64 columns of s32
@@ -560,7 +559,6 @@ __global__ void __launch_bounds__(GU_THREADS, 2) k_gu_prefill_q80(const __grid_c
     // afterwards it drains token columns 32 kh .. 32 kh + 31 of row r
     const int r = tid & (PF_M - 1), kh = tid >> 7;
     const int f0 = blockIdx.x * 64;
-    const int nkb = A.H / QK8_0;   // blocks per row
     const int steps = A.H / 128;
 
     constexpr uint32_t IDESC_SS = make_idesc(2, 1, 1, PF_NT, PF_M);  // s8 x s8 -> s32
